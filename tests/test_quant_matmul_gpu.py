@@ -1,0 +1,136 @@
+"""Parity of the W4A16 / W8A16 dequant-fused matmul kernels with the CPU oracle (through the
+C ABI). Integer unpacking must be bit-exact; outputs are compared at max-abs 2e-2 relative to
+the output scale (bf16 output rounding), the tolerance the bf16 decode path is held to."""
+import numpy as np
+import pytest
+import torch
+
+from gptrs_b200 import ops
+from oracle import quant_ref as qr
+
+pytestmark = pytest.mark.gpu
+
+
+def _scales(rng, shape):
+    return np.exp(rng.normal(-5.0, 0.5, size=shape)).astype(np.float16)
+
+
+def _w4_case(rng, n, k):
+    q = rng.integers(-8, 8, size=(n, k), dtype=np.int8)
+    return qr.pack_int4(q), _scales(rng, (n, k // 128))
+
+
+def _dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+@pytest.mark.parametrize("n,k", [(16, 128), (48, 384), (256, 1024), (3072, 3072)])
+def test_w4_repack_unpack_bit_exact(cuda, n, k):
+    rng = np.random.default_rng(n + k)
+    p, s = _w4_case(rng, n, k)
+    for inter in (False, True) if n % 32 == 0 else (False,):
+        packed = ops.w4a16_repack(_dev(p, cuda), _dev(s, cuda), n, k, inter)
+        q2, s2 = ops.w4a16_unpack(packed, n, k, inter)
+        assert np.array_equal(q2.cpu().numpy(), p)
+        assert np.array_equal(s2.cpu().numpy().view(np.uint16), s.view(np.uint16))
+
+
+@pytest.mark.parametrize("n,k", [(16, 128), (48, 384), (3072, 3072)])
+def test_w8_repack_unpack_bit_exact(cuda, n, k):
+    rng = np.random.default_rng(n * 3 + k)
+    q = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    s = _scales(rng, (n,))
+    packed = ops.w8a16_repack(_dev(q, cuda), _dev(s, cuda), n, k)
+    q2, s2 = ops.w8a16_unpack(packed, n, k)
+    assert np.array_equal(q2.cpu().numpy(), q)
+    assert np.array_equal(s2.cpu().numpy().view(np.uint16), s.view(np.uint16))
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+def test_quantize_kernels_bit_exact(cuda, transposed):
+    rng = np.random.default_rng(11)
+    n, k = 80, 512
+    w_nk = rng.normal(0, 0.02, size=(n, k)).astype(np.float32)
+    w_nk[3, 128:256] = 0.0  # an all-zero group
+    src = w_nk if transposed else np.ascontiguousarray(w_nk.T)
+    q4, s4 = ops.quantize_w4(_dev(src, cuda), transposed)
+    p_ref, s_ref = qr.quantize_w4(w_nk)
+    assert np.array_equal(s4.cpu().numpy().view(np.uint16), s_ref.view(np.uint16))
+    assert np.array_equal(q4.cpu().numpy(), p_ref)
+    q8, s8 = ops.quantize_w8(_dev(src, cuda), transposed)
+    q_ref, s8_ref = qr.quantize_w8(w_nk)
+    assert np.array_equal(s8.cpu().numpy().view(np.uint16), s8_ref.view(np.uint16))
+    assert np.array_equal(q8.cpu().numpy(), q_ref)
+
+
+def _check(got, want, tol=2e-2):
+    scale = max(1.0, float(np.max(np.abs(want))))
+    err = float(np.max(np.abs(got - want)))
+    assert err <= tol * scale, f"max-abs err {err} (scale {scale})"
+
+
+SHAPES = [
+    (1, 16, 128), (1, 3072, 3072), (3, 48, 384), (8, 256, 1024), (9, 144, 640), (16, 3072, 3072),
+    (17, 272, 256), (33, 512, 1536), (64, 3072, 3072), (64, 9216, 3072), (1, 9216, 3072),
+    (65, 256, 512), (200, 384, 1280), (256, 3072, 3072),
+]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_w4a16_matmul_matches_oracle(cuda, m, n, k):
+    rng = np.random.default_rng(m * 7 + n + k)
+    p, s = _w4_case(rng, n, k)
+    x = qr.to_bf16(rng.normal(0, 1, size=(m, k)).astype(np.float32))
+    want = qr.quant_matmul(x, qr.dequant_w4(p, s))
+    packed = ops.w4a16_repack(_dev(p, cuda), _dev(s, cuda), n, k)
+    xd = _dev(x, cuda).to(torch.bfloat16)
+    y = ops.quant_matmul_w4a16(xd, packed, m, n, k)
+    _check(y.float().cpu().numpy(), qr.to_bf16(want))
+    y32 = ops.quant_matmul_w4a16(xd, packed, m, n, k, out_f32=True)
+    # f32 output: only accumulation-order noise remains
+    assert np.allclose(y32.cpu().numpy(), want, rtol=1e-4, atol=1e-4 * max(1.0, np.abs(want).max()))
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_w8a16_matmul_matches_oracle(cuda, m, n, k):
+    rng = np.random.default_rng(m * 5 + n + k)
+    q = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    s = _scales(rng, (n,))
+    x = qr.to_bf16(rng.normal(0, 1, size=(m, k)).astype(np.float32))
+    want = qr.quant_matmul(x, qr.dequant_w8(q, s))
+    packed = ops.w8a16_repack(_dev(q, cuda), _dev(s, cuda), n, k)
+    xd = _dev(x, cuda).to(torch.bfloat16)
+    y32 = ops.quant_matmul_w8a16(xd, packed, m, n, k, out_f32=True)
+    assert np.allclose(y32.cpu().numpy(), want, rtol=1e-4, atol=1e-4 * max(1.0, np.abs(want).max()))
+    y = ops.quant_matmul_w8a16(xd, packed, m, n, k)
+    _check(y.float().cpu().numpy(), qr.to_bf16(want))
+
+
+def test_w4a16_epilogues(cuda):
+    rng = np.random.default_rng(99)
+    m, n, k = 5, 256, 384
+    p, s = _w4_case(rng, n, k)
+    x = qr.to_bf16(rng.normal(0, 1, size=(m, k)).astype(np.float32))
+    base = qr.quant_matmul(x, qr.dequant_w4(p, s))
+    xd = _dev(x, cuda).to(torch.bfloat16)
+    packed = ops.w4a16_repack(_dev(p, cuda), _dev(s, cuda), n, k)
+    bias = rng.normal(0, 1, size=n).astype(np.float32)
+    res = rng.normal(0, 1, size=(m, n)).astype(np.float32)
+    y = ops.quant_matmul_w4a16(xd, packed, m, n, k, out_f32=True, bias=_dev(bias, cuda), residual=_dev(res, cuda))
+    want = base + bias[None, :] + res
+    assert np.allclose(y.cpu().numpy(), want, rtol=1e-4, atol=1e-3)
+    # SwiGLU: rows [0, n/2) are gate, [n/2, n) are up
+    from oracle import functional_ref as fr
+    packed_gu = ops.w4a16_repack(_dev(p, cuda), _dev(s, cuda), n, k, True)
+    y = ops.quant_matmul_w4a16(xd, packed_gu, m, n, k, out_f32=True, swiglu=True)
+    want = fr.swiglu(base[:, : n // 2], base[:, n // 2:])
+    assert y.shape == (m, n // 2)
+    assert np.allclose(y.cpu().numpy(), want, rtol=1e-3, atol=1e-3 * max(1.0, np.abs(want).max()))
+
+
+def test_matmul_rejects_bad_arguments(cuda):
+    from gptrs_b200 import BackendError
+    x = torch.zeros((1, 100), dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(BackendError) as e:
+        ops.quant_matmul_w4a16(x, x, 1, 16, 100)
+    assert e.value.kind == "SpecViolation"
