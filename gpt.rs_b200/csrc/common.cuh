@@ -44,6 +44,45 @@ static inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b)
 // Number of SMs of the current device (cached per process; B200 = 148).
 int sm_count();
 
+// Non-zero while the decode engine records a step: kernels are then launched with
+// programmatic stream serialisation (every kernel of this library executes
+// griddepcontrol.wait before it touches memory written by its predecessor).
+extern int g_use_pdl;
+
+#ifdef __CUDACC__
+// Launch through cudaLaunchKernelEx with the optional cluster (along grid.y) and
+// programmatic-dependent-launch attributes.
+template <typename P>
+int launch_kernel(void (*kern)(P), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                  int cluster_y, const P& params) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attrs[2];
+    int na = 0;
+    if (cluster_y > 1) {
+        attrs[na].id = cudaLaunchAttributeClusterDimension;
+        attrs[na].val.clusterDim.x = 1;
+        attrs[na].val.clusterDim.y = (unsigned)cluster_y;
+        attrs[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (g_use_pdl) {
+        attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, params);
+    if (e != cudaSuccess)
+        return fail(GPTRS_EXECUTION, std::string("kernel launch failed: ") + cudaGetErrorString(e));
+    return GPTRS_OK;
+}
+#endif
+
 // ---------------------------------------------------------------------------------------------
 // Device side.
 // ---------------------------------------------------------------------------------------------
@@ -51,7 +90,7 @@ int sm_count();
 
 // Upper bound for every spin on an mbarrier: after this many polls the kernel records an error
 // in its status word and leaves instead of hanging the device.
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -1,0 +1,372 @@
+// Row-wise kernels of the decode step: fused residual-add + RMSNorm / LayerNorm, embedding
+// gather, elementwise activations, softmax and the device-side sampler.
+//
+// Reference semantics:
+//   layer_norm          crates/gpt-rs/src/ops/functional/normalization.rs:123-174
+//   rms_norm            crates/gpt-rs/src/ops/functional/normalization.rs:183-217
+//   residual add        crates/gpt-rs/src/ops/functional/common.rs:58-65
+//   embedding_lookup    crates/gpt-rs/src/ops/functional/embedding.rs:37-54
+//   gelu / silu / swiglu crates/gpt-rs/src/ops/functional/activation.rs:96-162
+//   softmax_last_dim    crates/gpt-rs/src/ops/functional/activation.rs:77-89, common.rs:22-31
+//   add_bias            crates/gpt-rs/src/ops/functional/tensor_ops.rs:42-56
+//   sample_decode_token crates/gpt-rs/src/backend/spec.rs:1336-1348 (greedy: ties -> smallest
+//                       index, docs/backend.md:270; Gumbel-max for temperature > 0 as in
+//                       crates/gpt-rs-backend-triton/src/kernels/sample_temperature_last_axis_f32.triton:45-69)
+#include "common.cuh"
+
+namespace gptrs {
+namespace {
+
+constexpr int kNormThreads = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+    v = warp_sum(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (l == 0) sh[w] = v;
+    __syncthreads();
+    float r = (l < nw) ? sh[l] : 0.f;
+    return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* sh) {
+    v = warp_max(v);
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (l == 0) sh[w] = v;
+    __syncthreads();
+    float r = (l < nw) ? sh[l] : -INFINITY;
+    return warp_max(r);
+}
+
+struct NormParams {
+    float* hidden;             // [T][D] f32 residual stream (updated in place when delta != null)
+    const void* delta;         // optional [T][D] to add first (f32 or bf16)
+    const float* delta_bias;   // optional [D] f32 added together with delta
+    const float* gamma;        // [D]
+    const float* beta;         // [D] (LayerNorm) or null (RMSNorm)
+    void* out;                 // [T][D] bf16 or f32
+    float* stat0;              // optional [T]: mean (LN) / inv_rms (RMS)
+    float* stat1;              // optional [T]: inv_std (LN)
+    int T, D;
+    float eps;
+    int delta_bf16, out_f32, layer_norm;
+};
+
+// One CTA per row. The row is kept in registers between the statistics and the output pass
+// (up to 16 values per thread, D <= 4096); longer rows are re-read.
+__global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams p) {
+    __shared__ float sh[32];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    pdl_wait();
+    float* h = p.hidden + (size_t)row * p.D;
+    constexpr int kKeep = 16;
+    constexpr int kKeepSpan = kKeep * kNormThreads;  // elements held in registers
+    float keep[kKeep];
+    auto load = [&](int i) {
+        float v = h[i];
+        if (p.delta) {
+            float d = p.delta_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.delta)[(size_t)row * p.D + i])
+                                   : static_cast<const float*>(p.delta)[(size_t)row * p.D + i];
+            if (p.delta_bias) d += p.delta_bias[i];
+            v += d;
+            h[i] = v;
+        }
+        return v;
+    };
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j) {
+        const int i = tid + j * kNormThreads;
+        keep[j] = 0.f;
+        if (i < p.D) {
+            keep[j] = load(i);
+            sum += p.layer_norm ? keep[j] : keep[j] * keep[j];
+        }
+    }
+    for (int i = kKeepSpan + tid; i < p.D; i += kNormThreads) {
+        float v = load(i);
+        sum += p.layer_norm ? v : v * v;
+    }
+    const float inv_n = 1.f / (float)p.D;
+    float mean = 0.f, inv;
+    if (p.layer_norm) {
+        mean = block_sum(sum, sh) * inv_n;
+        float sq = 0.f;
+#pragma unroll
+        for (int j = 0; j < kKeep; ++j) {
+            const int i = tid + j * kNormThreads;
+            if (i < p.D) { float c = keep[j] - mean; sq += c * c; }
+        }
+        for (int i = kKeepSpan + tid; i < p.D; i += kNormThreads) { float c = h[i] - mean; sq += c * c; }
+        const float var = block_sum(sq, sh) * inv_n;
+        inv = 1.f / sqrtf(var + p.eps);
+    } else {
+        const float ms = block_sum(sum, sh) * inv_n;
+        inv = 1.f / sqrtf(ms + p.eps);
+    }
+    pdl_launch_dependents();
+    if (tid == 0) {
+        if (p.stat0) p.stat0[row] = p.layer_norm ? mean : inv;
+        if (p.stat1 && p.layer_norm) p.stat1[row] = inv;
+    }
+    auto store = [&](int i, float v) {
+        float y = (v - mean) * inv * p.gamma[i];
+        if (p.beta) y += p.beta[i];
+        if (p.out_f32) static_cast<float*>(p.out)[(size_t)row * p.D + i] = y;
+        else static_cast<__nv_bfloat16*>(p.out)[(size_t)row * p.D + i] = __float2bfloat16_rn(y);
+    };
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j) {
+        const int i = tid + j * kNormThreads;
+        if (i < p.D) store(i, keep[j]);
+    }
+    for (int i = kKeepSpan + tid; i < p.D; i += kNormThreads) store(i, h[i]);
+}
+
+struct EmbedParams {
+    const void* weight;     // [V][D] f32 or bf16
+    const float* pos_weight;  // optional [P][D] f32 added (GPT-2 position embeddings)
+    const int* ids;         // [T]
+    const int* pos_ids;     // [T] (with pos_weight)
+    float* out;             // [T][D] f32
+    int* status;
+    int T, D, V, P, weight_bf16;
+};
+
+__global__ void __launch_bounds__(256) embedding_kernel(const EmbedParams p) {
+    const int row = blockIdx.x;
+    pdl_wait();
+    const int id = p.ids[row];
+    const bool ok = id >= 0 && id < p.V;
+    int pid = 0;
+    bool pok = true;
+    if (p.pos_weight) {
+        pid = p.pos_ids[row];
+        pok = pid >= 0 && pid < p.P;
+    }
+    if ((!ok || !pok) && threadIdx.x == 0) atomicExch(p.status, 2);
+    pdl_launch_dependents();
+    for (int i = threadIdx.x; i < p.D; i += blockDim.x) {
+        float v = 0.f;
+        if (ok)
+            v = p.weight_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.weight)[(size_t)id * p.D + i])
+                              : static_cast<const float*>(p.weight)[(size_t)id * p.D + i];
+        if (p.pos_weight && pok) v += p.pos_weight[(size_t)pid * p.D + i];
+        p.out[(size_t)row * p.D + i] = v;
+    }
+}
+
+// ---- elementwise f32 -----------------------------------------------------------------------
+enum { kGelu = 0, kSilu = 1, kSwiglu = 2, kAddBias = 3, kAdd = 4 };
+struct EwParams {
+    const float* a;
+    const float* b;
+    float* out;
+    int64_t n;
+    int64_t inner;  // add_bias: length of the bias vector
+    int op;
+};
+__global__ void elementwise_kernel(const EwParams p) {
+    pdl_wait();
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.n) return;
+    float x = p.a[i], y;
+    switch (p.op) {
+        case kGelu: y = (0.5f * x) * (1.f + erff(x / 1.4142135f)); break;
+        case kSilu: y = x / (1.f + expf(-x)); break;
+        case kSwiglu: y = x / (1.f + expf(-x)) * p.b[i]; break;
+        case kAddBias: y = x + p.b[i % p.inner]; break;
+        default: y = x + p.b[i]; break;
+    }
+    p.out[i] = y;
+}
+
+struct SoftmaxParams {
+    const float* x;
+    float* out;
+    int rows, n;
+};
+__global__ void __launch_bounds__(256) softmax_kernel(const SoftmaxParams p) {
+    __shared__ float sh[32];
+    pdl_wait();
+    const float* x = p.x + (size_t)blockIdx.x * p.n;
+    float* o = p.out + (size_t)blockIdx.x * p.n;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < p.n; i += blockDim.x) mx = fmaxf(mx, x[i]);
+    mx = block_max(mx, sh);
+    float s = 0.f;
+    for (int i = threadIdx.x; i < p.n; i += blockDim.x) s += expf(x[i] - mx);
+    s = block_sum(s, sh);
+    for (int i = threadIdx.x; i < p.n; i += blockDim.x) o[i] = expf(x[i] - mx) / s;
+}
+
+// ---- sampler ----------------------------------------------------------------------------------
+struct SampleParams {
+    const float* logits;  // [rows][vocab]
+    int* tokens;          // [rows]
+    int rows, vocab;
+    float temperature;    // <= 0: greedy
+    uint32_t seed;
+};
+
+__device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
+    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+    return x;
+}
+
+__global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    pdl_wait();
+    const int row = blockIdx.x;
+    const float* x = p.logits + (size_t)row * p.vocab;
+    float best = -INFINITY;
+    int besti = 0x7fffffff;
+    for (int i = threadIdx.x; i < p.vocab; i += blockDim.x) {
+        float v = x[i];
+        if (p.temperature > 0.f) {
+            // Gumbel-max: argmax(logit / T + g), g = -log(-log(u)), u from a stateless hash
+            uint32_t hsh = hash_u32(p.seed ^ hash_u32((uint32_t)i + 0x9e3779b9u * (uint32_t)(row + 1)));
+            float u = ((float)(hsh >> 8) + 0.5f) * (1.f / 16777216.f);
+            v = v / p.temperature - logf(-logf(u));
+        }
+        if (v > best || (v == best && i < besti)) { best = v; besti = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+        if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) { sv[w] = best; si[w] = besti; }
+    __syncthreads();
+    if (w == 0) {
+        const int nw = blockDim.x >> 5;
+        best = l < nw ? sv[l] : -INFINITY;
+        besti = l < nw ? si[l] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+            if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+        }
+        if (l == 0) p.tokens[row] = besti == 0x7fffffff ? 0 : besti;
+    }
+}
+
+}  // namespace
+}  // namespace gptrs
+
+using namespace gptrs;
+
+extern "C" {
+
+static int norm_common(float* d_hidden, const void* d_delta, int delta_dtype, const float* d_delta_bias,
+                       const float* d_gamma, const float* d_beta, float eps, void* d_out, int out_dtype,
+                       float* d_stat0, float* d_stat1, int64_t rows, int64_t dim, int layer_norm, void* stream) {
+    GPTRS_REQUIRE(d_hidden && d_gamma && d_out, "null pointer");
+    GPTRS_REQUIRE(rows >= 0 && dim > 0 && dim < (1ll << 31) && rows < (1ll << 31), "bad shape");
+    GPTRS_REQUIRE(out_dtype == GPTRS_BF16 || out_dtype == GPTRS_F32, "out_dtype must be bf16 or f32");
+    GPTRS_REQUIRE(!d_delta || delta_dtype == GPTRS_BF16 || delta_dtype == GPTRS_F32, "delta dtype must be bf16 or f32");
+    GPTRS_REQUIRE(!layer_norm || d_beta, "layer_norm needs beta");
+    if (rows == 0) return GPTRS_OK;
+    NormParams p = {};
+    p.hidden = d_hidden; p.delta = d_delta; p.delta_bias = d_delta_bias; p.gamma = d_gamma; p.beta = d_beta;
+    p.out = d_out; p.stat0 = d_stat0; p.stat1 = d_stat1;
+    p.T = (int)rows; p.D = (int)dim; p.eps = eps;
+    p.delta_bf16 = delta_dtype == GPTRS_BF16; p.out_f32 = out_dtype == GPTRS_F32; p.layer_norm = layer_norm;
+    return launch_kernel(add_norm_kernel, dim3((unsigned)rows), dim3(kNormThreads), 0, as_stream(stream), 1, p);
+}
+
+int gptrs_cuda_add_rms_norm(float* d_hidden, const void* d_delta, int delta_dtype, const float* d_gamma,
+                            float eps, void* d_out, int out_dtype, float* d_inv_rms, int64_t rows, int64_t dim,
+                            void* stream) {
+    return norm_common(d_hidden, d_delta, delta_dtype, nullptr, d_gamma, nullptr, eps, d_out, out_dtype, d_inv_rms,
+                       nullptr, rows, dim, 0, stream);
+}
+
+int gptrs_cuda_add_layer_norm(float* d_hidden, const void* d_delta, int delta_dtype, const float* d_delta_bias,
+                              const float* d_gamma, const float* d_beta, float eps, void* d_out, int out_dtype,
+                              float* d_mean, float* d_inv_std, int64_t rows, int64_t dim, void* stream) {
+    return norm_common(d_hidden, d_delta, delta_dtype, d_delta_bias, d_gamma, d_beta, eps, d_out, out_dtype, d_mean,
+                       d_inv_std, rows, dim, 1, stream);
+}
+
+int gptrs_cuda_embedding_lookup(const void* d_weight, int weight_dtype, int64_t vocab, int64_t dim,
+                                const int32_t* d_ids, int64_t n_tokens, const float* d_pos_weight,
+                                int64_t n_positions, const int32_t* d_pos_ids, float* d_out, int32_t* d_status,
+                                void* stream) {
+    GPTRS_REQUIRE(d_weight && d_ids && d_out && d_status, "null pointer");
+    GPTRS_REQUIRE(weight_dtype == GPTRS_F32 || weight_dtype == GPTRS_BF16, "embedding weight must be f32 or bf16");
+    GPTRS_REQUIRE(!d_pos_weight || d_pos_ids, "position ids missing");
+    GPTRS_REQUIRE(vocab > 0 && dim > 0 && n_tokens >= 0, "bad shape");
+    if (n_tokens == 0) return GPTRS_OK;
+    EmbedParams p = {};
+    p.weight = d_weight; p.pos_weight = d_pos_weight; p.ids = d_ids; p.pos_ids = d_pos_ids; p.out = d_out;
+    p.status = d_status; p.T = (int)n_tokens; p.D = (int)dim; p.V = (int)vocab; p.P = (int)n_positions;
+    p.weight_bf16 = weight_dtype == GPTRS_BF16;
+    return launch_kernel(embedding_kernel, dim3((unsigned)n_tokens), dim3(256), 0, as_stream(stream), 1, p);
+}
+
+static int elementwise(int op, const float* a, const float* b, float* out, int64_t n, int64_t inner, void* stream) {
+    GPTRS_REQUIRE(a && out && n >= 0, "null pointer");
+    GPTRS_REQUIRE(op == kGelu || op == kSilu || b, "second operand missing");
+    if (n == 0) return GPTRS_OK;
+    EwParams p = {a, b, out, n, inner > 0 ? inner : 1, op};
+    return launch_kernel(elementwise_kernel, dim3((unsigned)ceil_div(n, 256)), dim3(256), 0, as_stream(stream), 1, p);
+}
+int gptrs_cuda_gelu(const float* d_x, float* d_out, int64_t n, void* stream) { return elementwise(kGelu, d_x, nullptr, d_out, n, 0, stream); }
+int gptrs_cuda_silu(const float* d_x, float* d_out, int64_t n, void* stream) { return elementwise(kSilu, d_x, nullptr, d_out, n, 0, stream); }
+int gptrs_cuda_swiglu(const float* d_gate, const float* d_up, float* d_out, int64_t n, void* stream) { return elementwise(kSwiglu, d_gate, d_up, d_out, n, 0, stream); }
+int gptrs_cuda_add_bias(const float* d_x, const float* d_bias, float* d_out, int64_t rows, int64_t dim, void* stream) {
+    GPTRS_REQUIRE(dim > 0, "bad shape");
+    return elementwise(kAddBias, d_x, d_bias, d_out, rows * dim, dim, stream);
+}
+int gptrs_cuda_add(const float* d_a, const float* d_b, float* d_out, int64_t n, void* stream) { return elementwise(kAdd, d_a, d_b, d_out, n, 0, stream); }
+
+int gptrs_cuda_softmax_last_dim(const float* d_x, float* d_out, int64_t rows, int64_t n, void* stream) {
+    GPTRS_REQUIRE(d_x && d_out, "null pointer");
+    GPTRS_REQUIRE(rows >= 0 && n > 0 && n < (1ll << 31) && rows < (1ll << 31), "bad shape");
+    if (rows == 0) return GPTRS_OK;
+    SoftmaxParams p = {d_x, d_out, (int)rows, (int)n};
+    return launch_kernel(softmax_kernel, dim3((unsigned)rows), dim3(256), 0, as_stream(stream), 1, p);
+}
+
+int gptrs_cuda_supports_decode_sampling(float temperature, int has_top_k) {
+    (void)temperature;
+    return has_top_k ? 0 : 1;  // top-k is left to the host sampler, as in the reference
+}
+
+int gptrs_cuda_sample_rows(const float* d_logits, int64_t rows, int64_t vocab, float temperature, uint32_t seed,
+                           int32_t* d_tokens, void* stream) {
+    GPTRS_REQUIRE(d_logits && d_tokens, "null pointer");
+    GPTRS_REQUIRE(rows >= 0 && vocab > 0 && vocab < (1ll << 31) && rows < (1ll << 31), "bad shape");
+    if (rows == 0) return GPTRS_OK;
+    SampleParams p = {d_logits, d_tokens, (int)rows, (int)vocab, temperature, seed};
+    return launch_kernel(sample_kernel, dim3((unsigned)rows), dim3(1024), 0, as_stream(stream), 1, p);
+}
+
+int gptrs_cuda_sample_decode_token(const float* d_logits, int64_t rows, int64_t vocab, float temperature,
+                                   int has_random_u, float random_u, int* has_token, uint64_t* token, void* stream) {
+    GPTRS_REQUIRE(d_logits && has_token && token, "null pointer");
+    GPTRS_REQUIRE(rows >= 1 && vocab > 0, "bad shape");
+    *has_token = 0;
+    int32_t* d_tok = nullptr;
+    GPTRS_CUDA_OK(cudaMalloc(&d_tok, sizeof(int32_t)));
+    uint32_t seed = 0;
+    if (has_random_u) { float u = random_u; seed = *reinterpret_cast<uint32_t*>(&u); }
+    int rc = gptrs_cuda_sample_rows(d_logits + (size_t)(rows - 1) * vocab, 1, vocab, temperature, seed, d_tok, stream);
+    int32_t h = 0;
+    cudaError_t e = cudaSuccess;
+    if (rc == GPTRS_OK) e = cudaMemcpyAsync(&h, d_tok, sizeof(h), cudaMemcpyDeviceToHost, as_stream(stream));
+    if (rc == GPTRS_OK && e == cudaSuccess) e = cudaStreamSynchronize(as_stream(stream));
+    cudaFree(d_tok);
+    if (rc != GPTRS_OK) return rc;
+    GPTRS_CUDA_OK(e);
+    *has_token = 1;
+    *token = (uint64_t)h;
+    return GPTRS_OK;
+}
+
+}  // extern "C"

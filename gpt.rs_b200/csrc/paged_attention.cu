@@ -1,0 +1,449 @@
+// Decode attention over a paged bf16 KV cache (split-K flash decoding), RoPE + KV append, and
+// the split combiner.
+//
+// Stands in for functional::attention_decode_cache
+// (crates/gpt-rs/src/ops/functional/attention.rs:657-779) and apply_rope_qkv_packed
+// (crates/gpt-rs/src/ops/functional/rotary.rs:430-536). The reference attends over a dense
+// f32 cache [kv_heads, capacity, head_dim] with an additive 0 / -1e9 mask; masked terms
+// underflow to exactly 0 in f32, so visiting only the `len` live tokens gives the same sum.
+//
+// KV pool layout (one pool per layer), bf16:
+//   pool[page][kv_head][0 = K | 1 = V][16 tokens][128 channels], 4096 bytes per K or V block.
+//   Inside a block the 16-byte chunk c of token t is stored at chunk position c ^ (t & 7).
+// A (page, kv_head) pair is therefore one contiguous 8 KB block that a single bulk async
+// copy (TMA engine, untiled form) drops into shared memory already swizzled for
+// conflict-free ldmatrix.
+//
+// Attention kernel: one CTA per (split, kv_head, token). Each of its 4 warps owns a private
+// ring of 8 KB stages fed by bulk copies completing on warp-private mbarriers, keeps its own
+// running (max, sum, O) state for the GQA group's query heads and visits every 4th page of
+// the CTA's chunk; the warps' states are merged through shared memory at the end. No
+// CTA-wide synchronisation happens inside the streaming loop.
+#include "common.cuh"
+
+namespace gptrs {
+namespace {
+
+constexpr int kHD = 128;
+constexpr int kPageTokens = 16;
+constexpr int kBlockBytes = kPageTokens * kHD * 2;  // 4096: one K or V block
+constexpr int kPageHeadBytes = 2 * kBlockBytes;     // 8192: K + V of one (page, head)
+constexpr int kAttnWarps = 4;
+constexpr int kDepth = 3;                           // stages per warp
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnParams {
+    const __nv_bfloat16* q;       // [T][Hq][128] (RoPE applied)
+    const unsigned char* pool;    // KV pool of this layer
+    const int* page_table;        // [n_slots][max_pages]
+    const int* slot;              // [T] page-table row of each token
+    const int* ctx_len;           // [T] number of visible tokens (position + 1)
+    __nv_bfloat16* out;           // [T][Hq*128]
+    float* part_o;                // [T][Hq][max_splits][128]
+    float* part_ml;               // [T][Hq][max_splits][2]
+    int* status;                  // device error word (0 = ok)
+    int T, Hq, Hkv, max_pages, chunk_pages, max_splits;
+    float scale_log2;
+};
+
+__device__ __forceinline__ int swz(int tok, int chunk) { return tok * 256 + ((chunk ^ (tok & 7)) << 4); }
+
+__global__ void __launch_bounds__(kAttnWarps * 32, 2) paged_attention_kernel(const AttnParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(8) uint64_t full_bar[kAttnWarps][kDepth];
+
+    const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int group = p.Hq / p.Hkv;
+
+    pdl_wait();
+    const int len = p.ctx_len[b];
+    const int chunk_tokens = p.chunk_pages * kPageTokens;
+    const int first_tok = split * chunk_tokens;
+    if (first_tok >= len) return;  // whole CTA leaves together, before any barrier
+    const int n_tok = min(chunk_tokens, len - first_tok);
+    const int n_pages = (n_tok + kPageTokens - 1) / kPageTokens;
+    const int n_splits = (len + chunk_tokens - 1) / chunk_tokens;
+    const int* pt = p.page_table + (size_t)p.slot[b] * p.max_pages + first_tok / kPageTokens;
+
+    unsigned char* my_ring = smem + warp * (kDepth * kPageHeadBytes);
+    if (lane == 0) {
+        for (int s = 0; s < kDepth; ++s) mbar_init(&full_bar[warp][s], 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+
+    // pages of this warp: warp, warp+4, ...; lane j keeps the id of the j-th one
+    const int n_my = (n_pages > warp) ? (n_pages - warp + kAttnWarps - 1) / kAttnWarps : 0;
+    int my_page = 0;
+    if (lane < n_my) my_page = pt[warp + lane * kAttnWarps];
+
+    auto issue = [&](int j) {  // executed by lane 0 with the page id already broadcast
+        int pg = __shfl_sync(0xffffffffu, my_page, j);
+        if (lane == 0) {
+            const unsigned char* src = p.pool + ((size_t)pg * p.Hkv + h) * kPageHeadBytes;
+            uint64_t* bar = &full_bar[warp][j % kDepth];
+            mbar_expect_tx(bar, kPageHeadBytes);
+            bulk_g2s(my_ring + (j % kDepth) * kPageHeadBytes, src, kPageHeadBytes, bar);
+        }
+    };
+    for (int j = 0; j < kDepth && j < n_my; ++j) issue(j);
+
+    // Q fragments: row g of the A tile = query head h*group + g (rows >= group are zero).
+    uint32_t qf[8][2];
+    {
+        const bool valid = g < group;
+        const __nv_bfloat16* qrow = p.q + ((size_t)b * p.Hq + h * group + (valid ? g : 0)) * kHD;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            qf[ks][0] = valid ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+            qf[ks][1] = valid ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+        }
+    }
+
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool failed = false;
+
+    const uint32_t ring_addr = smem_u32(my_ring);
+    const int k_tok = ((lane >> 4) << 3) + (lane & 7), k_half = (lane >> 3) & 1;  // K ldmatrix
+    const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7), v_chunk = lane >> 4;  // V ldmatrix
+
+    for (int j = 0; j < n_my; ++j) {
+        const int st = j % kDepth;
+        if (!mbar_wait_bounded(&full_bar[warp][st], (j / kDepth) & 1)) {
+            failed = true;
+            break;
+        }
+        const uint32_t kb = ring_addr + st * kPageHeadBytes, vb = kb + kBlockBytes;
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t bf[4];
+            ldmatrix_x4(bf, kb + swz(k_tok, 2 * ks + k_half));
+            uint32_t a[4] = {qf[ks][0], 0u, qf[ks][1], 0u};
+            mma_bf16_16816(s[0], a, bf[0], bf[1]);
+            mma_bf16_16816(s[1], a, bf[2], bf[3]);
+        }
+        // scale, mask the tail of the last page, online softmax for row g
+        const int tok0 = first_tok + (warp + j * kAttnWarps) * kPageTokens;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                int tok = tok0 + nt * 8 + 2 * t + e;
+                float v = s[nt][e] * p.scale_log2;
+                v = tok < len ? v : -INFINITY;
+                s[nt][e] = v;
+                mx = fmaxf(mx, v);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);  // finite: token tok0 is always visible
+        const float alpha = exp2f(m_run - m_new);
+        float pr[2][2];
+        float psum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                pr[nt][e] = exp2f(s[nt][e] - m_new);
+                psum += pr[nt][e];
+            }
+        l_run = l_run * alpha + psum;
+        m_run = m_new;
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                o[i][0] *= alpha;
+                o[i][1] *= alpha;
+            }
+        }
+        uint32_t pa[4] = {pack_bf16x2(pr[0][0], pr[0][1]), 0u, pack_bf16x2(pr[1][0], pr[1][1]), 0u};
+#pragma unroll
+        for (int np = 0; np < 8; ++np) {
+            uint32_t bf[4];
+            ldmatrix_x4_trans(bf, vb + swz(v_tok, 2 * np + v_chunk));
+            mma_bf16_16816(o[2 * np], pa, bf[0], bf[1]);
+            mma_bf16_16816(o[2 * np + 1], pa, bf[2], bf[3]);
+        }
+        __syncwarp();
+        if (j + kDepth < n_my) {
+            fence_proxy_async();
+            issue(j + kDepth);
+        }
+    }
+    pdl_launch_dependents();
+    if (failed && lane == 0) atomicExch(p.status, 1);
+
+    // ---- merge the 4 warps (rows g < group live in lanes 0..15 when group <= 4, else all) ---
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    __syncthreads();  // every stage has been consumed; the rings can be reused
+    float* mo = reinterpret_cast<float*>(smem);                       // [warp][8][128]
+    float* mml = mo + kAttnWarps * 8 * kHD;                           // [warp][8][2]
+    if (g < group) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float2 v = make_float2(o[i][0], o[i][1]);
+            *reinterpret_cast<float2*>(mo + (warp * 8 + g) * kHD + i * 8 + 2 * t) = v;
+        }
+        if (t == 0) {
+            mml[(warp * 8 + g) * 2] = m_run;
+            mml[(warp * 8 + g) * 2 + 1] = l_run;
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < group * (kHD / 4); idx += kAttnWarps * 32) {
+        const int r = idx / (kHD / 4), c4 = (idx % (kHD / 4)) * 4;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, mml[(w * 8 + r) * 2]);
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            float f = exp2f(mml[(w * 8 + r) * 2] - M);
+            L += mml[(w * 8 + r) * 2 + 1] * f;
+            float4 v = *reinterpret_cast<const float4*>(mo + (w * 8 + r) * kHD + c4);
+            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+        }
+        const int hq = h * group + r;
+        if (n_splits == 1) {
+            const float inv = 1.f / L;
+            uint2 ov = make_uint2(pack_bf16x2(acc.x * inv, acc.y * inv), pack_bf16x2(acc.z * inv, acc.w * inv));
+            *reinterpret_cast<uint2*>(p.out + ((size_t)b * p.Hq + hq) * kHD + c4) = ov;
+        } else {
+            const size_t pi = ((size_t)b * p.Hq + hq) * p.max_splits + split;
+            *reinterpret_cast<float4*>(p.part_o + pi * kHD + c4) = acc;
+            if (c4 == 0) {
+                p.part_ml[pi * 2] = M;
+                p.part_ml[pi * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// One CTA per (token, query head): merges the splits written by paged_attention_kernel.
+__global__ void __launch_bounds__(128) attention_combine_kernel(const AttnParams p) {
+    const int b = blockIdx.x, hq = blockIdx.y, c = threadIdx.x;
+    pdl_wait();
+    const int len = p.ctx_len[b];
+    const int chunk_tokens = p.chunk_pages * kPageTokens;
+    const int n_splits = (len + chunk_tokens - 1) / chunk_tokens;
+    if (n_splits <= 1) return;
+    const size_t base = ((size_t)b * p.Hq + hq) * p.max_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p.part_ml[(base + s) * 2]);
+    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        float f = exp2f(p.part_ml[(base + s) * 2] - M);
+        L += p.part_ml[(base + s) * 2 + 1] * f;
+        acc += p.part_o[(base + s) * kHD + c] * f;
+    }
+    pdl_launch_dependents();
+    p.out[((size_t)b * p.Hq + hq) * kHD + c] = __float2bfloat16_rn(acc / L);
+}
+
+// RoPE (half-split, f32 math on the caller's cos/sin tables) on the Q and K heads of packed
+// bf16 qkv rows, K/V scattered into the token's page. One CTA per (head, token), 64 threads.
+struct RopeAppendParams {
+    const __nv_bfloat16* qkv;   // [T][(Hq + 2 Hkv) * 128]
+    const int* positions;       // [T]
+    const int* slot;            // [T]
+    const int* page_table;      // [n_slots][max_pages]
+    const float* cos_table;     // [n_pos][half]
+    const float* sin_table;
+    __nv_bfloat16* q_out;       // [T][Hq][128]
+    unsigned char* pool;
+    int T, Hq, Hkv, max_pages, half;  // half = rotary_dim / 2 (<= 64)
+};
+
+__global__ void __launch_bounds__(64) rope_append_kernel(const RopeAppendParams p) {
+    const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x;  // i: channel pair (i, i + 64)
+    pdl_wait();
+    const int pos = p.positions[b];
+    const int width = (p.Hq + 2 * p.Hkv) * kHD;
+    const __nv_bfloat16* src = p.qkv + (size_t)b * width + head * kHD;
+    float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[i + 64]);
+    const bool is_v = head >= p.Hq + p.Hkv;
+    if (!is_v) {
+        // rotary pairs are (c, c + half) for c < half; channels >= 2*half pass through
+        // (head_dim 128: with half == 64 every pair (i, i+64) rotates).
+        if (p.half == 64) {
+            float c = p.cos_table[(size_t)pos * 64 + i], s = p.sin_table[(size_t)pos * 64 + i];
+            float r1 = x1 * c - x2 * s, r2 = x2 * c + x1 * s;
+            x1 = r1; x2 = r2;
+        } else {
+            // general case: fetch partners explicitly
+            auto rot = [&](int ch, float x) {
+                if (ch >= 2 * p.half) return x;
+                int k = ch < p.half ? ch : ch - p.half;
+                float c = p.cos_table[(size_t)pos * p.half + k], s = p.sin_table[(size_t)pos * p.half + k];
+                float other = __bfloat162float(src[ch < p.half ? ch + p.half : ch - p.half]);
+                return ch < p.half ? x * c - other * s : x * c + other * s;
+            };
+            x1 = rot(i, x1);
+            x2 = rot(i + 64, x2);
+        }
+    }
+    pdl_launch_dependents();
+    const __nv_bfloat16 y1 = __float2bfloat16_rn(x1), y2 = __float2bfloat16_rn(x2);
+    if (head < p.Hq) {
+        __nv_bfloat16* dst = p.q_out + ((size_t)b * p.Hq + head) * kHD;
+        dst[i] = y1;
+        dst[i + 64] = y2;
+    } else {
+        const int kvh = is_v ? head - p.Hq - p.Hkv : head - p.Hq;
+        const int page = p.page_table[(size_t)p.slot[b] * p.max_pages + pos / kPageTokens];
+        const int tok = pos % kPageTokens;
+        unsigned char* blk = p.pool + ((size_t)page * p.Hkv + kvh) * kPageHeadBytes + (is_v ? kBlockBytes : 0);
+        *reinterpret_cast<__nv_bfloat16*>(blk + swz(tok, i >> 3) + (i & 7) * 2) = y1;
+        *reinterpret_cast<__nv_bfloat16*>(blk + swz(tok, (i + 64) >> 3) + (i & 7) * 2) = y2;
+    }
+}
+
+// Pool -> dense [n_tokens][Hkv][128] K and V for one page-table row (tests / export).
+__global__ void kv_gather_kernel(const unsigned char* pool, const int* page_row, int n_tokens, int Hkv,
+                                 __nv_bfloat16* k_out, __nv_bfloat16* v_out) {
+    const int tok = blockIdx.x, h = blockIdx.y, c = threadIdx.x;
+    const int page = page_row[tok / kPageTokens], tk = tok % kPageTokens;
+    const unsigned char* blk = pool + ((size_t)page * Hkv + h) * kPageHeadBytes;
+    const size_t o = ((size_t)tok * Hkv + h) * kHD + c;
+    k_out[o] = *reinterpret_cast<const __nv_bfloat16*>(blk + swz(tk, c >> 3) + (c & 7) * 2);
+    v_out[o] = *reinterpret_cast<const __nv_bfloat16*>(blk + kBlockBytes + swz(tk, c >> 3) + (c & 7) * 2);
+}
+
+}  // namespace
+
+}  // namespace gptrs
+
+using namespace gptrs;
+
+extern "C" {
+
+size_t gptrs_cuda_kv_pool_bytes(int64_t n_pages, int64_t n_kv_heads, int64_t head_dim) {
+    if (head_dim != kHD || n_pages <= 0 || n_kv_heads <= 0) return 0;
+    return (size_t)n_pages * n_kv_heads * kPageHeadBytes;
+}
+
+int gptrs_cuda_attention_chunk_pages(int64_t max_ctx_len, int64_t n_tokens, int64_t n_kv_heads) {
+    // Smallest power-of-two chunk (in pages, 4..128) that still yields >= 4 CTAs per SM.
+    const int64_t target = 4ll * sm_count();
+    int chunk = 128;
+    while (chunk > 4) {
+        int64_t splits = (max_ctx_len + chunk * kPageTokens - 1) / (chunk * kPageTokens);
+        if (splits * n_tokens * n_kv_heads >= target) break;
+        chunk >>= 1;
+    }
+    return chunk;
+}
+
+size_t gptrs_cuda_attention_scratch_bytes(int64_t n_tokens, int64_t n_q_heads, int64_t max_ctx_len,
+                                          int64_t chunk_pages) {
+    if (chunk_pages <= 0) return 0;
+    int64_t splits = (max_ctx_len + chunk_pages * kPageTokens - 1) / (chunk_pages * kPageTokens);
+    return (size_t)n_tokens * n_q_heads * splits * (kHD + 2) * sizeof(float);
+}
+
+int gptrs_cuda_rope_kv_append(const void* d_qkv, const int32_t* d_positions, const int32_t* d_slot,
+                              const int32_t* d_page_table, int64_t max_pages, const float* d_cos,
+                              const float* d_sin, int64_t rotary_dim, void* d_q_out, void* d_kv_pool,
+                              int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
+                              void* stream) {
+    GPTRS_REQUIRE(d_qkv && d_positions && d_slot && d_page_table && d_q_out && d_kv_pool, "null pointer");
+    GPTRS_REQUIRE(head_dim == kHD, "paged bf16 attention supports head_dim 128 only");
+    GPTRS_REQUIRE(rotary_dim >= 0 && rotary_dim <= kHD && rotary_dim % 2 == 0, "bad rotary_dim");
+    GPTRS_REQUIRE(rotary_dim == 0 || (d_cos && d_sin), "rotary tables missing");
+    GPTRS_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "bad head counts");
+    if (n_tokens == 0) return GPTRS_OK;
+    RopeAppendParams p = {};
+    p.qkv = static_cast<const __nv_bfloat16*>(d_qkv);
+    p.positions = d_positions; p.slot = d_slot; p.page_table = d_page_table;
+    p.cos_table = d_cos; p.sin_table = d_sin;
+    p.q_out = static_cast<__nv_bfloat16*>(d_q_out);
+    p.pool = static_cast<unsigned char*>(d_kv_pool);
+    p.T = (int)n_tokens; p.Hq = (int)n_q_heads; p.Hkv = (int)n_kv_heads;
+    p.max_pages = (int)max_pages; p.half = (int)(rotary_dim / 2);
+    dim3 grid((unsigned)(n_q_heads + 2 * n_kv_heads), (unsigned)n_tokens);
+    return launch_kernel(rope_append_kernel, grid, dim3(64), 0, as_stream(stream), 1, p);
+}
+
+int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                      int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                      void* d_out, void* d_scratch, size_t scratch_bytes, int32_t* d_status,
+                                      int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
+                                      int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
+                                      void* stream) {
+    GPTRS_REQUIRE(d_q && d_kv_pool && d_page_table && d_slot && d_ctx_len && d_out && d_status, "null pointer");
+    GPTRS_REQUIRE(head_dim == kHD, "paged bf16 attention supports head_dim 128 only");
+    GPTRS_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "bad head counts");
+    GPTRS_REQUIRE(n_q_heads / n_kv_heads <= 8, "GQA group size above 8 is not supported");
+    GPTRS_REQUIRE(chunk_pages >= 1 && chunk_pages <= 128, "chunk_pages must be in [1,128]");
+    GPTRS_REQUIRE(max_ctx_len >= 1 && max_ctx_len <= max_pages * kPageTokens, "max_ctx_len exceeds the page table");
+    if (n_tokens == 0) return GPTRS_OK;
+    const int64_t splits = (max_ctx_len + chunk_pages * kPageTokens - 1) / (chunk_pages * kPageTokens);
+    GPTRS_REQUIRE(splits <= 65535 && n_kv_heads <= 65535 && n_tokens <= 65535 * 1024, "grid too large");
+    const size_t need = gptrs_cuda_attention_scratch_bytes(n_tokens, n_q_heads, max_ctx_len, chunk_pages);
+    GPTRS_REQUIRE(splits == 1 || (d_scratch && scratch_bytes >= need), "attention scratch too small");
+    AttnParams p = {};
+    p.q = static_cast<const __nv_bfloat16*>(d_q);
+    p.pool = static_cast<const unsigned char*>(d_kv_pool);
+    p.page_table = d_page_table; p.slot = d_slot; p.ctx_len = d_ctx_len;
+    p.out = static_cast<__nv_bfloat16*>(d_out);
+    p.part_o = static_cast<float*>(d_scratch);
+    p.part_ml = p.part_o ? p.part_o + (size_t)n_tokens * n_q_heads * splits * kHD : nullptr;
+    p.status = d_status;
+    p.T = (int)n_tokens; p.Hq = (int)n_q_heads; p.Hkv = (int)n_kv_heads;
+    p.max_pages = (int)max_pages; p.chunk_pages = (int)chunk_pages; p.max_splits = (int)splits;
+    p.scale_log2 = kLog2e / sqrtf((float)head_dim);
+    const size_t smem = (size_t)kAttnWarps * kDepth * kPageHeadBytes;
+    static bool attr_done = false;
+    if (!attr_done) {
+        GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_done = true;
+    }
+    cudaStream_t st = as_stream(stream);
+    // tokens beyond 65535 go through blockIdx.z in slabs
+    for (int64_t t0 = 0; t0 < n_tokens; t0 += 65535) {
+        AttnParams q = p;
+        int64_t nt = n_tokens - t0 < 65535 ? n_tokens - t0 : 65535;
+        q.q = p.q + (size_t)t0 * n_q_heads * kHD;
+        q.slot = p.slot + t0; q.ctx_len = p.ctx_len + t0;
+        q.out = p.out + (size_t)t0 * n_q_heads * kHD;
+        if (p.part_o) {
+            q.part_o = p.part_o + (size_t)t0 * n_q_heads * splits * kHD;
+            q.part_ml = p.part_ml + (size_t)t0 * n_q_heads * splits * 2;
+        }
+        q.T = (int)nt;
+        int rc = launch_kernel(paged_attention_kernel, dim3((unsigned)splits, (unsigned)n_kv_heads, (unsigned)nt),
+                               dim3(kAttnWarps * 32), smem, st, 1, q);
+        if (rc) return rc;
+        if (splits > 1) {
+            // combine in slabs of 65535 tokens along x is not needed: x may hold up to 2^31-1
+            rc = launch_kernel(attention_combine_kernel, dim3((unsigned)nt, (unsigned)n_q_heads), dim3(128), 0, st, 1, q);
+            if (rc) return rc;
+        }
+    }
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_kv_gather(const void* d_kv_pool, const int32_t* d_page_row, int64_t n_tokens, int64_t n_kv_heads,
+                         int64_t head_dim, void* d_k_out, void* d_v_out, void* stream) {
+    GPTRS_REQUIRE(d_kv_pool && d_page_row && d_k_out && d_v_out, "null pointer");
+    GPTRS_REQUIRE(head_dim == kHD, "head_dim 128 only");
+    if (n_tokens == 0) return GPTRS_OK;
+    kv_gather_kernel<<<dim3((unsigned)n_tokens, (unsigned)n_kv_heads), kHD, 0, as_stream(stream)>>>(
+        static_cast<const unsigned char*>(d_kv_pool), d_page_row, (int)n_tokens, (int)n_kv_heads,
+        static_cast<__nv_bfloat16*>(d_k_out), static_cast<__nv_bfloat16*>(d_v_out));
+    GPTRS_CUDA_OK(cudaGetLastError());
+    return GPTRS_OK;
+}
+
+}  // extern "C"

@@ -504,30 +504,13 @@ __global__ void quantize_w8_kernel(const float* w, int64_t K, int64_t N, int tra
 
 template <int MT, int BITS>
 int launch_matmul(const MatmulParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kern = quant_matmul_kernel<MT, BITS>;
+    void (*kern)(MatmulParams) = quant_matmul_kernel<MT, BITS>;
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
         GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
         attr_done = true;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kWarps * 32);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attrs[2];
-    int na = 0;
-    if (p.n_split > 1) {
-        attrs[na].id = cudaLaunchAttributeClusterDimension;
-        attrs[na].val.clusterDim.x = 1;
-        attrs[na].val.clusterDim.y = p.n_split;
-        attrs[na].val.clusterDim.z = 1;
-        ++na;
-    }
-    cfg.attrs = attrs;
-    cfg.numAttrs = na;
-    GPTRS_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
-    return GPTRS_OK;
+    return launch_kernel(kern, grid, dim3(kWarps * 32), smem, stream, p.n_split, p);
 }
 
 int pick_split(int n_blocks, int groups) {

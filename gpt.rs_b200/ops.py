@@ -108,3 +108,162 @@ def quant_matmul_w4a16(x, packed, m, n, k, out=None, out_f32=False, bias=None, r
 
 def quant_matmul_w8a16(x, packed, m, n, k, out=None, out_f32=False, bias=None, residual=None, swiglu=False):
     return _quant_matmul(lib().gptrs_cuda_quant_matmul_w8a16, x, packed, m, n, k, out, out_f32, bias, residual, swiglu)
+
+
+# ---- paged bf16 KV cache + decode attention ------------------------------------------------------
+PAGE_TOKENS = 16
+
+
+def kv_pool_bytes(n_pages: int, n_kv_heads: int, head_dim: int = 128) -> int:
+    return lib().gptrs_cuda_kv_pool_bytes(n_pages, n_kv_heads, head_dim)
+
+
+def new_kv_pool(n_pages: int, n_kv_heads: int, device, head_dim: int = 128) -> torch.Tensor:
+    nbytes = kv_pool_bytes(n_pages, n_kv_heads, head_dim)
+    assert nbytes > 0, "unsupported KV pool geometry"
+    return torch.zeros(nbytes, dtype=torch.uint8, device=device)
+
+
+def rope_kv_append(qkv, positions, slot, page_table, cos, sin, rotary_dim, kv_pool, n_q, n_kv, head_dim=128):
+    """qkv bf16 [T][(Hq+2Hkv)*hd] -> q_rot bf16 [T][Hq][hd]; K/V rows scattered into the pool."""
+    t = qkv.shape[0]
+    q_out = torch.empty((t, n_q, head_dim), dtype=torch.bfloat16, device=qkv.device)
+    check(lib().gptrs_cuda_rope_kv_append(_ptr(qkv), _ptr(positions), _ptr(slot), _ptr(page_table),
+                                          page_table.shape[1], _ptr(cos), _ptr(sin), rotary_dim, _ptr(q_out),
+                                          _ptr(kv_pool), t, n_q, n_kv, head_dim, _stream()))
+    return q_out
+
+
+def paged_attention_decode(q, kv_pool, page_table, slot, ctx_len, n_q, n_kv, max_ctx_len, head_dim=128,
+                           chunk_pages=None, status=None):
+    """q bf16 [T][Hq][hd] -> out bf16 [T][Hq*hd]."""
+    t = q.shape[0]
+    if chunk_pages is None:
+        chunk_pages = lib().gptrs_cuda_attention_chunk_pages(max_ctx_len, t, n_kv)
+    nbytes = lib().gptrs_cuda_attention_scratch_bytes(t, n_q, max_ctx_len, chunk_pages)
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    out = torch.empty((t, n_q * head_dim), dtype=torch.bfloat16, device=q.device)
+    check(lib().gptrs_cuda_paged_attention_decode(_ptr(q), _ptr(kv_pool), _ptr(page_table), page_table.shape[1],
+                                                  _ptr(slot), _ptr(ctx_len), _ptr(out), _ptr(scratch), nbytes,
+                                                  _ptr(status), t, n_q, n_kv, head_dim, max_ctx_len, chunk_pages,
+                                                  _stream()))
+    return out, status
+
+
+def kv_gather(kv_pool, page_row, n_tokens, n_kv, head_dim=128):
+    k = torch.empty((n_tokens, n_kv, head_dim), dtype=torch.bfloat16, device=kv_pool.device)
+    v = torch.empty_like(k)
+    check(lib().gptrs_cuda_kv_gather(_ptr(kv_pool), _ptr(page_row), n_tokens, n_kv, head_dim, _ptr(k), _ptr(v), _stream()))
+    return k, v
+
+
+# ---- row-wise functionals ------------------------------------------------------------------------
+def _dt(t):
+    return {torch.float32: F32, torch.bfloat16: BF16}[t.dtype]
+
+
+def add_rms_norm(hidden, gamma, eps, delta=None, out_dtype=torch.bfloat16, want_inv_rms=False):
+    """hidden f32 [T][D] (+= delta in place) -> rms_norm output (and inv_rms [T])."""
+    rows, dim = hidden.shape
+    out = torch.empty((rows, dim), dtype=out_dtype, device=hidden.device)
+    inv = torch.empty(rows, dtype=torch.float32, device=hidden.device) if want_inv_rms else None
+    check(lib().gptrs_cuda_add_rms_norm(_ptr(hidden), _ptr(delta), _dt(delta) if delta is not None else F32,
+                                        _ptr(gamma), eps, _ptr(out), _dt(out), _ptr(inv), rows, dim, _stream()))
+    return (out, inv) if want_inv_rms else out
+
+
+def add_layer_norm(hidden, gamma, beta, eps, delta=None, delta_bias=None, out_dtype=torch.float32, want_stats=False):
+    rows, dim = hidden.shape
+    out = torch.empty((rows, dim), dtype=out_dtype, device=hidden.device)
+    mean = torch.empty(rows, dtype=torch.float32, device=hidden.device) if want_stats else None
+    inv = torch.empty(rows, dtype=torch.float32, device=hidden.device) if want_stats else None
+    check(lib().gptrs_cuda_add_layer_norm(_ptr(hidden), _ptr(delta), _dt(delta) if delta is not None else F32,
+                                          _ptr(delta_bias), _ptr(gamma), _ptr(beta), eps, _ptr(out), _dt(out),
+                                          _ptr(mean), _ptr(inv), rows, dim, _stream()))
+    return (out, mean, inv) if want_stats else out
+
+
+def embedding_lookup(weight, ids, pos_weight=None, pos_ids=None, status=None):
+    vocab, dim = weight.shape
+    t = ids.shape[0]
+    out = torch.empty((t, dim), dtype=torch.float32, device=weight.device)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=weight.device)
+    check(lib().gptrs_cuda_embedding_lookup(_ptr(weight), _dt(weight), vocab, dim, _ptr(ids), t, _ptr(pos_weight),
+                                            pos_weight.shape[0] if pos_weight is not None else 0, _ptr(pos_ids),
+                                            _ptr(out), _ptr(status), _stream()))
+    return out, status
+
+
+def _unary(fn, x):
+    out = torch.empty_like(x)
+    check(fn(_ptr(x), _ptr(out), x.numel(), _stream()))
+    return out
+
+
+def gelu(x):
+    return _unary(lib().gptrs_cuda_gelu, x)
+
+
+def silu(x):
+    return _unary(lib().gptrs_cuda_silu, x)
+
+
+def swiglu(gate, up):
+    out = torch.empty_like(gate)
+    check(lib().gptrs_cuda_swiglu(_ptr(gate), _ptr(up), _ptr(out), gate.numel(), _stream()))
+    return out
+
+
+def add_bias(x, bias):
+    out = torch.empty_like(x)
+    check(lib().gptrs_cuda_add_bias(_ptr(x), _ptr(bias), _ptr(out), x.numel() // bias.numel(), bias.numel(), _stream()))
+    return out
+
+
+def softmax_last_dim(x):
+    out = torch.empty_like(x)
+    n = x.shape[-1]
+    check(lib().gptrs_cuda_softmax_last_dim(_ptr(x), _ptr(out), x.numel() // n, n, _stream()))
+    return out
+
+
+def sample_rows(logits, temperature=0.0, seed=0):
+    rows, vocab = logits.shape
+    tok = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    check(lib().gptrs_cuda_sample_rows(_ptr(logits), rows, vocab, temperature, seed, _ptr(tok), _stream()))
+    return tok
+
+
+def sample_decode_token(logits, temperature=0.0, random_u=None):
+    """PortableBackend::sample_decode_token: token of the LAST row, or None when unsupported."""
+    rows, vocab = logits.shape
+    has = ctypes.c_int(0)
+    tok = ctypes.c_uint64(0)
+    check(lib().gptrs_cuda_sample_decode_token(_ptr(logits), rows, vocab, temperature, int(random_u is not None),
+                                               float(random_u or 0.0), ctypes.byref(has), ctypes.byref(tok), _stream()))
+    return int(tok.value) if has.value else None
+
+
+# ---- f32 path ----------------------------------------------------------------------------------------
+def matmul_f32(x, w_in_out, bias=None, residual=None, gelu=False):
+    m, k = x.shape
+    n = w_in_out.shape[1]
+    y = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    check(lib().gptrs_cuda_matmul_f32(_ptr(x), _ptr(w_in_out), _ptr(y), m, n, k, _ptr(bias), _ptr(residual), int(gelu), _stream()))
+    return y
+
+
+def kv_append_f32(qkv, positions, slot, k_cache, v_cache, n_q, n_kv, head_dim):
+    check(lib().gptrs_cuda_kv_append_f32(_ptr(qkv), _ptr(positions), _ptr(slot), _ptr(k_cache), _ptr(v_cache),
+                                         qkv.shape[0], n_q, n_kv, head_dim, k_cache.shape[2], _stream()))
+
+
+def attention_decode_f32(qkv, k_cache, v_cache, positions, slot, n_q, n_kv, head_dim):
+    t = qkv.shape[0]
+    out = torch.empty((t, n_q * head_dim), dtype=torch.float32, device=qkv.device)
+    check(lib().gptrs_cuda_attention_decode_f32(_ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(slot),
+                                                _ptr(out), t, n_q, n_kv, head_dim, k_cache.shape[2], _stream()))
+    return out

@@ -102,6 +102,107 @@ int gptrs_cuda_quant_matmul_w8a16(const void* d_x_bf16, const void* d_packed, vo
                                   int64_t m, int64_t n, int64_t k,
                                   const gptrs_matmul_epilogue* epilogue, void* stream);
 
+/* ==============================================================================================
+ * Paged bf16 KV cache and decode attention (split-K flash decoding).
+ * Stand in for functional::apply_rope_qkv_packed (crates/gpt-rs/src/ops/functional/rotary.rs:430-536)
+ * followed by functional::attention_decode_cache (crates/gpt-rs/src/ops/functional/attention.rs:657-779).
+ * The reference keeps one dense f32 cache [kv_heads, capacity, head_dim] per layer and sequence
+ * (attention.rs:35-39); here all sequences of a layer share one pool of 16-token pages:
+ *   pool[page][kv_head][K|V][16 tokens][128 channels] bf16, chunk-swizzled inside each block,
+ * addressed through page_table[slot][page index] (int32). A "token" below is one query row with
+ * its own page-table row (`slot`), position and visible length, so a decode batch (one token per
+ * sequence) and a prefill chunk (many tokens of one sequence) use the same calls.
+ * head_dim must be 128 and n_q_heads / n_kv_heads <= 8.
+ * ============================================================================================ */
+size_t gptrs_cuda_kv_pool_bytes(int64_t n_pages, int64_t n_kv_heads, int64_t head_dim);
+/* Pages per attention split for a launch (power of two in [4,128]); max_ctx_len is an upper
+ * bound of every token's visible length. */
+int gptrs_cuda_attention_chunk_pages(int64_t max_ctx_len, int64_t n_tokens, int64_t n_kv_heads);
+size_t gptrs_cuda_attention_scratch_bytes(int64_t n_tokens, int64_t n_q_heads, int64_t max_ctx_len,
+                                          int64_t chunk_pages);
+/* Rotates the Q and K heads of packed bf16 rows qkv[T][(Hq+2Hkv)*128] with the caller's f32
+ * tables cos/sin[position][rotary_dim/2] (half-split pairing, rotary.rs:289-336), writes Q to
+ * q_out[T][Hq][128] and scatters K / V into page_table[slot[t]][positions[t] / 16]. */
+int gptrs_cuda_rope_kv_append(const void* d_qkv, const int32_t* d_positions, const int32_t* d_slot,
+                              const int32_t* d_page_table, int64_t max_pages, const float* d_cos,
+                              const float* d_sin, int64_t rotary_dim, void* d_q_out, void* d_kv_pool,
+                              int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
+                              void* stream);
+/* out[T][Hq*128] (bf16) = softmax(q K^T / sqrt(128)) V over the first ctx_len[t] tokens of the
+ * token's sequence. d_scratch (gptrs_cuda_attention_scratch_bytes) holds the split partials;
+ * *d_status becomes non-zero if a bounded wait inside the kernel gave up. */
+int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                      int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                      void* d_out, void* d_scratch, size_t scratch_bytes, int32_t* d_status,
+                                      int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
+                                      int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
+                                      void* stream);
+/* Copies the first n_tokens of one page-table row out of the pool into dense bf16
+ * K / V [n_tokens][n_kv_heads][128] (export and test helper). */
+int gptrs_cuda_kv_gather(const void* d_kv_pool, const int32_t* d_page_row, int64_t n_tokens, int64_t n_kv_heads,
+                         int64_t head_dim, void* d_k_out, void* d_v_out, void* stream);
+
+/* ==============================================================================================
+ * Row-wise functionals.
+ * ============================================================================================ */
+/* hidden[T][D] (f32) += delta (optional, f32 or bf16), then rms_norm
+ * (crates/gpt-rs/src/ops/functional/normalization.rs:183-217): out = x * rsqrt(mean(x^2)+eps) * gamma.
+ * d_inv_rms (optional [T]) receives the third result of the functional. */
+int gptrs_cuda_add_rms_norm(float* d_hidden, const void* d_delta, int delta_dtype, const float* d_gamma,
+                            float eps, void* d_out, int out_dtype, float* d_inv_rms, int64_t rows, int64_t dim,
+                            void* stream);
+/* Same with layer_norm (normalization.rs:123-174); d_delta_bias is an optional [D] bias folded
+ * into the residual add (the bias of the preceding Linear); d_mean / d_inv_std optional [T]. */
+int gptrs_cuda_add_layer_norm(float* d_hidden, const void* d_delta, int delta_dtype, const float* d_delta_bias,
+                              const float* d_gamma, const float* d_beta, float eps, void* d_out, int out_dtype,
+                              float* d_mean, float* d_inv_std, int64_t rows, int64_t dim, void* stream);
+/* functional::embedding_lookup (crates/gpt-rs/src/ops/functional/embedding.rs:37-54), optionally
+ * fused with the position-embedding add of Gpt::forward (crates/gpt-rs/src/model/gpt.rs:659-693).
+ * An out-of-range id writes zeros and sets *d_status = 2 (ref-cpu reports an error,
+ * crates/gpt-rs-backend-ref-cpu/src/cpu.rs:1631-1634). */
+int gptrs_cuda_embedding_lookup(const void* d_weight, int weight_dtype, int64_t vocab, int64_t dim,
+                                const int32_t* d_ids, int64_t n_tokens, const float* d_pos_weight,
+                                int64_t n_positions, const int32_t* d_pos_ids, float* d_out, int32_t* d_status,
+                                void* stream);
+/* activation.rs:96-162, tensor_ops.rs:42-56, common.rs:58-65 (f32, elementwise). */
+int gptrs_cuda_gelu(const float* d_x, float* d_out, int64_t n, void* stream);
+int gptrs_cuda_silu(const float* d_x, float* d_out, int64_t n, void* stream);
+int gptrs_cuda_swiglu(const float* d_gate, const float* d_up, float* d_out, int64_t n, void* stream);
+int gptrs_cuda_add_bias(const float* d_x, const float* d_bias, float* d_out, int64_t rows, int64_t dim, void* stream);
+int gptrs_cuda_add(const float* d_a, const float* d_b, float* d_out, int64_t n, void* stream);
+/* activation.rs:77-89. */
+int gptrs_cuda_softmax_last_dim(const float* d_x, float* d_out, int64_t rows, int64_t n, void* stream);
+
+/* PortableBackend::supports_decode_sampling / sample_decode_token
+ * (crates/gpt-rs/src/backend/spec.rs:1331-1348): greedy (temperature <= 0; ties -> smallest
+ * index) or Gumbel-max temperature sampling; top-k is refused (has_top_k -> 0), as the reference's
+ * device sampler does. sample_decode_token samples the LAST row of logits[rows][vocab]
+ * (crates/gpt-rs-backend-triton/src/runtime/sampling.rs:61-87) and synchronises the stream. */
+int gptrs_cuda_supports_decode_sampling(float temperature, int has_top_k);
+int gptrs_cuda_sample_decode_token(const float* d_logits, int64_t rows, int64_t vocab, float temperature,
+                                   int has_random_u, float random_u, int* has_token, uint64_t* token, void* stream);
+/* Batched form: one token per row, written to d_tokens[rows] (asynchronous). */
+int gptrs_cuda_sample_rows(const float* d_logits, int64_t rows, int64_t vocab, float temperature, uint32_t seed,
+                           int32_t* d_tokens, void* stream);
+
+/* ==============================================================================================
+ * f32 path (unquantised models, e.g. GPT-2 small).
+ * ============================================================================================ */
+/* y[M][N] = x[M][K] . w[K][N] (+ bias[N]) (gelu) (+ residual[M][N]); weights in the Linear layout
+ * [in, out] (crates/gpt-rs/src/nn/layers/linear.rs:14, 50-71). */
+int gptrs_cuda_matmul_f32(const float* d_x, const float* d_w, float* d_y, int64_t m, int64_t n, int64_t k,
+                          const float* d_bias, const float* d_residual, int gelu, void* stream);
+/* Dense f32 KV cache [slot][kv_head][capacity][head_dim] (attention.rs:35-39): append the K / V
+ * part of packed f32 qkv rows at their positions (start clamped like DynamicUpdateSlice,
+ * docs/backend.md:452-474), then attend over positions 0..pos. */
+int gptrs_cuda_kv_append_f32(const float* d_qkv, const int32_t* d_positions, const int32_t* d_slot, float* d_k_cache,
+                             float* d_v_cache, int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
+                             int64_t head_dim, int64_t capacity, void* stream);
+int gptrs_cuda_attention_decode_f32(const float* d_qkv, const float* d_k_cache, const float* d_v_cache,
+                                    const int32_t* d_positions, const int32_t* d_slot, float* d_out,
+                                    int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
+                                    int64_t capacity, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
