@@ -1,0 +1,762 @@
+// Decode engine: the C++ counterpart of gpt.rs' model + generator layer for the transformer
+// decode path, driving the kernels of this library.
+//
+//   Gpt::forward_with_decode_cache_internal_device      crates/gpt-rs/src/model/gpt.rs:585-751
+//   Ministral::forward_with_decode_cache_internal        crates/gpt-rs/src/model/ministral.rs:613-766
+//   Generator::{new_with_kv_cache_capacity, step}        crates/gpt-rs/src/inference/generate.rs:59-203
+//   ParamSource / ParamResolver memo of derived weights  crates/gpt-rs/src/params.rs:25-48,
+//                                                        backend/param_resolver.rs:11-50
+//
+// Differences from the reference that do not change results: a batch of independent sequences
+// is processed per step (each row follows the single-sequence graph), the KV cache is paged
+// (bf16 modes) or dense with a fixed capacity (f32 mode) instead of power-of-two buckets, and
+// a prompt is prefilled as a chunk of tokens that each attend to positions 0..pos (the
+// reference's own property "decode with cache == full forward", crates/gpt-rs/tests/ministral.rs:65-89).
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "tensor.h"
+
+namespace gptrs {
+namespace {
+
+enum { kKindGpt = 0, kKindMinistral = 1 };
+enum { kModeF32 = 0, kModeW4 = 1, kModeW8 = 2 };
+constexpr int kPage = 16;
+
+struct DevBuf {
+    void* p = nullptr;
+    size_t n = 0;
+    int alloc(size_t bytes, bool zero = false) {
+        release();
+        if (bytes == 0) return GPTRS_OK;
+        cudaError_t e = cudaMalloc(&p, bytes);
+        if (e != cudaSuccess) return fail(GPTRS_EXECUTION, std::string("cudaMalloc(") + std::to_string(bytes) + "): " + cudaGetErrorString(e));
+        n = bytes;
+        if (zero) cudaMemset(p, 0, bytes);
+        return GPTRS_OK;
+    }
+    void release() { if (p) cudaFree(p); p = nullptr; n = 0; }
+    ~DevBuf() { release(); }
+    template <typename T> T* as() const { return static_cast<T*>(p); }
+};
+
+struct Weight {        // one Linear
+    Tensor* f32 = nullptr;     // [in][out] (f32 mode)
+    Tensor* packed = nullptr;  // quantised + repacked (W4/W8 modes)
+    Tensor* bias = nullptr;    // optional [out]
+    int64_t in = 0, out = 0;
+};
+
+struct Layer {
+    Tensor *ln1_g = nullptr, *ln1_b = nullptr, *ln2_g = nullptr, *ln2_b = nullptr;
+    Weight qkv, attn_out, mlp_in, mlp_gate, mlp_up, mlp_gate_up, mlp_out;
+};
+
+struct GraphKey {
+    int batch, chunk_pages, splits;
+    bool operator<(const GraphKey& o) const {
+        return std::tie(batch, chunk_pages, splits) < std::tie(o.batch, o.chunk_pages, o.splits);
+    }
+};
+
+}  // namespace
+
+struct Model {
+    gptrs_model_config cfg;
+    bool finalized = false;
+    std::map<std::string, Tensor*> raw;  // name -> f32 leaf (retained)
+    std::map<std::string, std::pair<uint64_t, uint64_t>> ids;
+    Tensor *tok_emb = nullptr, *pos_emb = nullptr, *final_g = nullptr, *final_b = nullptr;
+    Weight lm_head;
+    std::vector<Layer> layers;
+    int quantised_now = 0, memo_hits = 0;
+
+    // activations
+    DevBuf hidden, xn, qkv, q_rot, attn, mlp_h, mlp_g, mlp_u, logits, xn_rows;
+    DevBuf d_tokens, d_slot, d_pos, d_ctx, d_rows, d_sampled, d_status, attn_scratch;
+    DevBuf cos_tab, sin_tab;
+    int n_rope_pos = 0;
+    // KV
+    DevBuf kv_pool;                 // bf16 modes: [layer][page][kv_head][K|V][16][128]
+    size_t pool_layer_bytes = 0;
+    DevBuf k_cache, v_cache;        // f32 mode: [layer][slot][kv_head][capacity][hd]
+    size_t cache_layer_elems = 0;
+    DevBuf d_page_table;
+    int32_t* h_page_table = nullptr;  // pinned mirror [max_seqs][max_pages_per_seq]
+    bool table_dirty = true;
+    std::vector<int32_t> free_pages;
+    std::vector<int> seq_pages, seq_len;
+    // staging (pinned)
+    int32_t* h_stage = nullptr;  // 6 * max_tokens int32
+    float* h_logits = nullptr;
+    cudaStream_t stream = nullptr;
+    struct GraphEntry { cudaGraphExec_t exec; int64_t kernels; };
+    std::map<GraphKey, GraphEntry> graphs;
+    int gen_batch = 0;  // slots 0..gen_batch-1 are driven by generator_step
+    int64_t launches = 0;
+    uint32_t sample_seed = 0;
+
+    int QKV() const { return (cfg.n_q_heads + 2 * cfg.n_kv_heads) * cfg.head_dim; }
+    int QD() const { return cfg.n_q_heads * cfg.head_dim; }
+    bool f32() const { return cfg.weight_mode == kModeF32; }
+
+    ~Model() {
+        for (auto& g : graphs) cudaGraphExecDestroy(g.second.exec);
+        for (auto& r : raw) tensor_release(r.second);
+        auto relw = [](Weight& w) { tensor_release(w.f32); tensor_release(w.packed); tensor_release(w.bias); };
+        for (auto& l : layers) {
+            for (Tensor* t : {l.ln1_g, l.ln1_b, l.ln2_g, l.ln2_b}) tensor_release(t);
+            for (Weight* w : {&l.qkv, &l.attn_out, &l.mlp_in, &l.mlp_gate, &l.mlp_up, &l.mlp_gate_up, &l.mlp_out}) relw(*w);
+        }
+        relw(lm_head);
+        for (Tensor* t : {tok_emb, pos_emb, final_g, final_b}) tensor_release(t);
+        if (h_page_table) cudaFreeHost(h_page_table);
+        if (h_stage) cudaFreeHost(h_stage);
+        if (h_logits) cudaFreeHost(h_logits);
+        if (stream) cudaStreamDestroy(stream);
+    }
+};
+
+namespace {
+
+// Derived-parameter id: FNV-1a mix of the leaf id and a layout tag, top bit set (derived ids
+// never collide with blake3-derived leaf ids in practice; the reference uses the same idea,
+// crates/gpt-rs/src/backend/passes/param_only_fold_to_param.rs:503-525).
+std::pair<uint64_t, uint64_t> derived_id(std::pair<uint64_t, uint64_t> leaf, const std::string& tag) {
+    uint64_t h = 1469598103934665603ull;
+    auto mix = [&](uint64_t v) { for (int i = 0; i < 8; ++i) { h ^= (v >> (8 * i)) & 0xff; h *= 1099511628211ull; } };
+    mix(leaf.first); mix(leaf.second);
+    for (char c : tag) { h ^= (unsigned char)c; h *= 1099511628211ull; }
+    uint64_t h2 = h;
+    mix(h2 ^ 0x9e3779b97f4a7c15ull);
+    return {h, h2 | (1ull << 63)};
+}
+
+int get_raw(Model& m, const std::string& name, std::vector<int64_t> want_dims, Tensor** out) {
+    auto it = m.raw.find(name);
+    if (it == m.raw.end()) return fail(GPTRS_SPEC_VIOLATION, "missing parameter '" + name + "'");
+    if (it->second->dims != want_dims) return fail(GPTRS_SPEC_VIOLATION, "parameter '" + name + "' has the wrong shape");
+    tensor_retain(it->second);
+    *out = it->second;
+    return GPTRS_OK;
+}
+
+// Builds a Linear from leaf weights `names` (each [in][out_i], concatenated along out) in the
+// model's weight mode. Quantised layouts are looked up / stored in the process-wide memo.
+int build_linear(Model& m, const std::vector<std::string>& names, const std::string& bias_name, int64_t in,
+                 const std::vector<int64_t>& outs, bool gate_up, Weight* w) {
+    int64_t out_total = 0;
+    for (int64_t o : outs) out_total += o;
+    w->in = in; w->out = out_total;
+    if (!bias_name.empty()) { int rc = get_raw(m, bias_name, {out_total}, &w->bias); if (rc) return rc; }
+    std::vector<Tensor*> leaves(names.size(), nullptr);
+    for (size_t i = 0; i < names.size(); ++i) {
+        int rc = get_raw(m, names[i], {in, outs[i]}, &leaves[i]);
+        if (rc) { for (Tensor* t : leaves) tensor_release(t); return rc; }
+    }
+    auto drop = [&]() { for (Tensor* t : leaves) tensor_release(t); };
+    if (m.f32()) {
+        if (names.size() != 1) { drop(); return fail(GPTRS_EXECUTION, "f32 mode keeps Linear weights separate"); }
+        w->f32 = leaves[0];
+        return GPTRS_OK;
+    }
+    const bool w4 = m.cfg.weight_mode == kModeW4;
+    std::string tag = std::string(w4 ? "w4g128" : "w8pc") + (gate_up ? ":gate_up" : "");
+    std::pair<uint64_t, uint64_t> key = m.ids[names[0]];
+    for (size_t i = 1; i < names.size(); ++i) { key.first ^= m.ids[names[i]].first * 31; key.second ^= m.ids[names[i]].second * 131; }
+    auto did = derived_id(key, tag);
+    if (Tensor* hit = param_lookup(did.first, did.second)) {
+        size_t need = w4 ? gptrs_cuda_w4a16_packed_bytes(out_total, in) : gptrs_cuda_w8a16_packed_bytes(out_total, in);
+        if (hit->bytes == need) { w->packed = hit; ++m.memo_hits; drop(); return GPTRS_OK; }
+        tensor_release(hit);
+    }
+    size_t need = w4 ? gptrs_cuda_w4a16_packed_bytes(out_total, in) : gptrs_cuda_w8a16_packed_bytes(out_total, in);
+    if (need == 0) { drop(); return fail(GPTRS_SPEC_VIOLATION, "quantised Linear needs in % 128 == 0 and out % 16 == 0"); }
+    DevBuf q, s;
+    const int64_t groups = in / 128;
+    int rc = q.alloc(w4 ? (size_t)out_total * in / 2 : (size_t)out_total * in);
+    if (!rc) rc = s.alloc(w4 ? (size_t)out_total * groups * 2 : (size_t)out_total * 2);
+    int64_t row0 = 0;
+    for (size_t i = 0; i < names.size() && !rc; ++i) {
+        const float* src = static_cast<const float*>(leaves[i]->data);
+        if (w4) rc = gptrs_cuda_quantize_w4(src, in, outs[i], 0, q.as<uint8_t>() + (size_t)row0 * in / 2,
+                                            s.as<uint16_t>() + (size_t)row0 * groups, m.stream);
+        else rc = gptrs_cuda_quantize_w8(src, in, outs[i], 0, q.as<int8_t>() + (size_t)row0 * in,
+                                         s.as<uint16_t>() + row0, m.stream);
+        row0 += outs[i];
+    }
+    Tensor* packed = nullptr;
+    int64_t pd[1] = {(int64_t)need};
+    if (!rc) rc = tensor_alloc(GPTRS_UI8, 1, pd, false, &packed);
+    if (!rc) rc = w4 ? gptrs_cuda_w4a16_repack(q.as<uint8_t>(), s.as<uint16_t>(), out_total, in, gate_up ? 1 : 0, packed->data, m.stream)
+                     : gptrs_cuda_w8a16_repack(q.as<int8_t>(), s.as<uint16_t>(), out_total, in, packed->data, m.stream);
+    if (!rc && cudaStreamSynchronize(m.stream) != cudaSuccess) rc = fail(GPTRS_EXECUTION, "quantise/repack failed");
+    drop();
+    if (rc) { tensor_release(packed); return rc; }
+    param_store(did.first, did.second, packed);
+    w->packed = packed;
+    ++m.quantised_now;
+    return GPTRS_OK;
+}
+
+int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool out_f32, const float* residual,
+           bool swiglu, bool gelu) {
+    ++m.launches;
+    if (m.f32()) {
+        return gptrs_cuda_matmul_f32(static_cast<const float*>(x), static_cast<const float*>(w.f32->data),
+                                     static_cast<float*>(y), rows, w.out, w.in,
+                                     w.bias ? static_cast<const float*>(w.bias->data) : nullptr, residual, gelu ? 1 : 0, m.stream);
+    }
+    gptrs_matmul_epilogue ep = {};
+    ep.out_dtype = out_f32 ? GPTRS_F32 : GPTRS_BF16;
+    ep.d_bias = w.bias ? static_cast<const float*>(w.bias->data) : nullptr;
+    ep.d_residual = residual;
+    ep.swiglu = swiglu ? 1 : 0;
+    return m.cfg.weight_mode == kModeW4
+               ? gptrs_cuda_quant_matmul_w4a16(x, w.packed->data, y, rows, w.out, w.in, &ep, m.stream)
+               : gptrs_cuda_quant_matmul_w8a16(x, w.packed->data, y, rows, w.out, w.in, &ep, m.stream);
+}
+
+__global__ void rope_f32_inplace_kernel(float* qkv, const int* positions, const float* cos_t, const float* sin_t,
+                                        int n_rot_heads, int width, int hd, int half) {
+    // one CTA per (head, token); rotates pairs (c, c + half), c < half
+    const int head = blockIdx.x, b = blockIdx.y;
+    pdl_wait();
+    const int pos = positions[b];
+    float* x = qkv + (size_t)b * width + head * hd;
+    (void)n_rot_heads;
+    for (int c = threadIdx.x; c < half; c += blockDim.x) {
+        float cs = cos_t[(size_t)pos * half + c], sn = sin_t[(size_t)pos * half + c];
+        float a = x[c], bb = x[c + half];
+        x[c] = a * cs - bb * sn;
+        x[c + half] = bb * cs + a * sn;
+    }
+}
+
+struct GatherParams { const void* src; void* dst; const int* rows; int n_rows, row_bytes; };
+__global__ void gather_rows_kernel(const GatherParams p) {
+    pdl_wait();
+    const unsigned char* s = static_cast<const unsigned char*>(p.src) + (size_t)p.rows[blockIdx.x] * p.row_bytes;
+    unsigned char* d = static_cast<unsigned char*>(p.dst) + (size_t)blockIdx.x * p.row_bytes;
+    for (int i = threadIdx.x * 4; i < p.row_bytes; i += blockDim.x * 4)
+        *reinterpret_cast<uint32_t*>(d + i) = *reinterpret_cast<const uint32_t*>(s + i);
+}
+
+struct AdvanceParams { int* pos; int* ctx; int n; };
+__global__ void advance_kernel(const AdvanceParams p) {
+    pdl_wait();
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < p.n) { p.pos[i] += 1; p.ctx[i] += 1; }
+}
+
+// Enqueues one forward pass over T tokens whose ids / slots / positions / visible lengths are
+// already in the device arrays. `rows`: number of rows that get logits (row indices in d_rows,
+// or all T rows in order when rows_identity).
+int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, bool rows_identity, float temperature) {
+    const auto& c = m.cfg;
+    const int D = c.d_model;
+    cudaStream_t st = m.stream;
+    float* hidden = m.hidden.as<float>();
+    const int act_dt = m.f32() ? GPTRS_F32 : GPTRS_BF16;
+    int rc = gptrs_cuda_embedding_lookup(m.tok_emb->data, GPTRS_F32, c.vocab, D, m.d_tokens.as<int32_t>(), T,
+                                         m.pos_emb ? static_cast<const float*>(m.pos_emb->data) : nullptr,
+                                         m.pos_emb ? c.context_length : 0, m.d_pos.as<int32_t>(), hidden,
+                                         m.d_status.as<int32_t>(), st);
+    ++m.launches;
+    if (rc) return rc;
+    const bool gpt = c.kind == kKindGpt;
+    for (int l = 0; l < c.n_layers; ++l) {
+        Layer& L = m.layers[l];
+        auto norm = [&](Tensor* g, Tensor* b) {
+            ++m.launches;
+            return gpt ? gptrs_cuda_add_layer_norm(hidden, nullptr, GPTRS_F32, nullptr, (const float*)g->data, (const float*)b->data,
+                                                   c.norm_eps, m.xn.p, act_dt, nullptr, nullptr, T, D, st)
+                       : gptrs_cuda_add_rms_norm(hidden, nullptr, GPTRS_F32, (const float*)g->data, c.norm_eps, m.xn.p, act_dt,
+                                                 nullptr, T, D, st);
+        };
+        if ((rc = norm(L.ln1_g, L.ln1_b))) return rc;
+        if ((rc = linear(m, L.qkv, m.xn.p, m.qkv.p, T, false, nullptr, false, false))) return rc;
+        if (m.f32()) {
+            if (!gpt && c.rotary_dim > 0) {
+                ++m.launches;
+                rope_f32_inplace_kernel<<<dim3(c.n_q_heads + c.n_kv_heads, T), 64, 0, st>>>(
+                    m.qkv.as<float>(), m.d_pos.as<int32_t>(), m.cos_tab.as<float>(), m.sin_tab.as<float>(),
+                    c.n_q_heads + c.n_kv_heads, m.QKV(), c.head_dim, c.rotary_dim / 2);
+                GPTRS_CUDA_OK(cudaGetLastError());
+            }
+            float* kc = m.k_cache.as<float>() + (size_t)l * m.cache_layer_elems;
+            float* vc = m.v_cache.as<float>() + (size_t)l * m.cache_layer_elems;
+            m.launches += 2;
+            if ((rc = gptrs_cuda_kv_append_f32(m.qkv.as<float>(), m.d_pos.as<int32_t>(), m.d_slot.as<int32_t>(), kc, vc, T,
+                                               c.n_q_heads, c.n_kv_heads, c.head_dim, c.context_length, st))) return rc;
+            if ((rc = gptrs_cuda_attention_decode_f32(m.qkv.as<float>(), kc, vc, m.d_pos.as<int32_t>(), m.d_slot.as<int32_t>(),
+                                                      m.attn.as<float>(), T, c.n_q_heads, c.n_kv_heads, c.head_dim,
+                                                      c.context_length, st))) return rc;
+        } else {
+            unsigned char* pool = m.kv_pool.as<unsigned char>() + (size_t)l * m.pool_layer_bytes;
+            m.launches += 2;
+            if ((rc = gptrs_cuda_rope_kv_append(m.qkv.p, m.d_pos.as<int32_t>(), m.d_slot.as<int32_t>(),
+                                                m.d_page_table.as<int32_t>(), c.max_pages_per_seq, m.cos_tab.as<float>(),
+                                                m.sin_tab.as<float>(), c.rotary_dim, m.q_rot.p, pool, T, c.n_q_heads,
+                                                c.n_kv_heads, c.head_dim, st))) return rc;
+            const int splits = (max_ctx + chunk_pages * kPage - 1) / (chunk_pages * kPage);
+            if (splits > 1) ++m.launches;
+            if ((rc = gptrs_cuda_paged_attention_decode(m.q_rot.p, pool, m.d_page_table.as<int32_t>(), c.max_pages_per_seq,
+                                                        m.d_slot.as<int32_t>(), m.d_ctx.as<int32_t>(), m.attn.p,
+                                                        m.attn_scratch.p, m.attn_scratch.n, m.d_status.as<int32_t>(), T,
+                                                        c.n_q_heads, c.n_kv_heads, c.head_dim, max_ctx, chunk_pages, st))) return rc;
+        }
+        // hidden += attn . W_out (+ b)   (residual add folded into the epilogue, in place)
+        if ((rc = linear(m, L.attn_out, m.attn.p, hidden, T, true, hidden, false, false))) return rc;
+        if ((rc = norm(L.ln2_g, L.ln2_b))) return rc;
+        if (gpt) {
+            if ((rc = linear(m, L.mlp_in, m.xn.p, m.mlp_h.p, T, false, nullptr, false, true))) return rc;
+        } else if (m.f32()) {
+            if ((rc = linear(m, L.mlp_gate, m.xn.p, m.mlp_g.p, T, false, nullptr, false, false))) return rc;
+            if ((rc = linear(m, L.mlp_up, m.xn.p, m.mlp_u.p, T, false, nullptr, false, false))) return rc;
+            ++m.launches;
+            if ((rc = gptrs_cuda_swiglu(m.mlp_g.as<float>(), m.mlp_u.as<float>(), m.mlp_h.as<float>(), (int64_t)T * c.d_mlp, st))) return rc;
+        } else {
+            if ((rc = linear(m, L.mlp_gate_up, m.xn.p, m.mlp_h.p, T, false, nullptr, true, false))) return rc;
+        }
+        if ((rc = linear(m, L.mlp_out, m.mlp_h.p, hidden, T, true, hidden, false, false))) return rc;
+    }
+    ++m.launches;
+    rc = gpt ? gptrs_cuda_add_layer_norm(hidden, nullptr, GPTRS_F32, nullptr, (const float*)m.final_g->data,
+                                         (const float*)m.final_b->data, c.norm_eps, m.xn.p, act_dt, nullptr, nullptr, T, D, st)
+             : gptrs_cuda_add_rms_norm(hidden, nullptr, GPTRS_F32, (const float*)m.final_g->data, c.norm_eps, m.xn.p, act_dt,
+                                       nullptr, T, D, st);
+    if (rc) return rc;
+    const void* xr = m.xn.p;
+    if (!rows_identity) {
+        ++m.launches;
+        GatherParams gp = {m.xn.p, m.xn_rows.p, m.d_rows.as<int32_t>(), n_rows, D * (m.f32() ? 4 : 2)};
+        if ((rc = launch_kernel(gather_rows_kernel, dim3(n_rows), dim3(128), 0, st, 1, gp))) return rc;
+        xr = m.xn_rows.p;
+    }
+    if ((rc = linear(m, m.lm_head, xr, m.logits.p, n_rows, true, nullptr, false, false))) return rc;
+    ++m.launches;
+    return gptrs_cuda_sample_rows(m.logits.as<float>(), n_rows, c.vocab, temperature, m.sample_seed, m.d_sampled.as<int32_t>(), st);
+}
+
+int ensure_pages(Model& m, int slot, int upto_pos) {
+    if (m.f32()) return GPTRS_OK;
+    const int need = upto_pos / kPage + 1;
+    if (need > m.cfg.max_pages_per_seq) return fail(GPTRS_SPEC_VIOLATION, "sequence exceeds max_pages_per_seq");
+    while (m.seq_pages[slot] < need) {
+        if (m.free_pages.empty()) return fail(GPTRS_EXECUTION, "KV page pool exhausted");
+        m.h_page_table[(size_t)slot * m.cfg.max_pages_per_seq + m.seq_pages[slot]] = m.free_pages.back();
+        m.free_pages.pop_back();
+        ++m.seq_pages[slot];
+        m.table_dirty = true;
+    }
+    return GPTRS_OK;
+}
+
+int sync_page_table(Model& m) {
+    if (m.f32() || !m.table_dirty) return GPTRS_OK;
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_page_table.p, m.h_page_table, m.d_page_table.n, cudaMemcpyHostToDevice, m.stream));
+    m.table_dirty = false;
+    return GPTRS_OK;
+}
+
+int check_status(Model& m) {
+    int32_t st = 0;
+    GPTRS_CUDA_OK(cudaMemcpyAsync(&st, m.d_status.p, 4, cudaMemcpyDeviceToHost, m.stream));
+    GPTRS_CUDA_OK(cudaStreamSynchronize(m.stream));
+    if (st != 0) {
+        cudaMemsetAsync(m.d_status.p, 0, 4, m.stream);
+        return fail(GPTRS_EXECUTION, st == 2 ? "token or position id out of range" : "a bounded device wait gave up");
+    }
+    return GPTRS_OK;
+}
+
+int attention_plan(const Model& m, int T, int max_ctx, int* chunk_pages) {
+    if (m.f32()) { *chunk_pages = 1; return GPTRS_OK; }
+    int chunk = gptrs_cuda_attention_chunk_pages(max_ctx, T, m.cfg.n_kv_heads);
+    // grow the chunk until the split partials fit the scratch buffer
+    while (chunk < 128 && gptrs_cuda_attention_scratch_bytes(T, m.cfg.n_q_heads, max_ctx, chunk) > m.attn_scratch.n) chunk *= 2;
+    *chunk_pages = chunk;
+    return GPTRS_OK;
+}
+
+}  // namespace
+}  // namespace gptrs
+
+using namespace gptrs;
+
+extern "C" {
+
+int gptrs_cuda_model_create(const gptrs_model_config* cfg, gptrs_model** out) {
+    GPTRS_REQUIRE(cfg && out, "null pointer");
+    const auto& c = *cfg;
+    GPTRS_REQUIRE(c.kind == kKindGpt || c.kind == kKindMinistral, "unknown model kind");
+    GPTRS_REQUIRE(c.weight_mode >= kModeF32 && c.weight_mode <= kModeW8, "unknown weight mode");
+    GPTRS_REQUIRE(c.n_layers > 0 && c.d_model > 0 && c.n_q_heads > 0 && c.n_kv_heads > 0 && c.head_dim > 0 &&
+                      c.d_mlp > 0 && c.vocab > 0 && c.context_length > 0, "bad model dimensions");
+    GPTRS_REQUIRE(c.n_q_heads % c.n_kv_heads == 0, "query heads must be a multiple of kv heads");
+    GPTRS_REQUIRE(c.max_seqs > 0 && c.max_tokens > 0, "max_seqs and max_tokens must be positive");
+    if (c.weight_mode != kModeF32) {
+        if (c.kind == kKindGpt) return fail(GPTRS_UNIMPLEMENTED, "quantised weights are implemented for the ministral kind only");
+        if (c.head_dim != 128) return fail(GPTRS_UNIMPLEMENTED, "paged bf16 attention needs head_dim 128");
+        GPTRS_REQUIRE(c.kv_pages > 0 && c.max_pages_per_seq > 0, "kv_pages and max_pages_per_seq must be positive");
+    }
+    if (c.kind == kKindMinistral) GPTRS_REQUIRE(c.rotary_dim >= 0 && c.rotary_dim <= c.head_dim && c.rotary_dim % 2 == 0, "bad rotary_dim");
+    auto m = std::make_unique<Model>();
+    m->cfg = c;
+    GPTRS_CUDA_OK(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+    *out = reinterpret_cast<gptrs_model*>(m.release());
+    return GPTRS_OK;
+}
+
+void gptrs_cuda_model_destroy(gptrs_model* h) {
+    if (!h) return;
+    Model* m = reinterpret_cast<Model*>(h);
+    cudaStreamSynchronize(m->stream);
+    delete m;
+}
+
+int gptrs_cuda_model_load_param(gptrs_model* h, const char* name, uint64_t id_lo, uint64_t id_hi, const float* data,
+                                int on_device, int rank, const int64_t* dims) {
+    GPTRS_REQUIRE(h && name && data, "null pointer");
+    Model& m = *reinterpret_cast<Model*>(h);
+    GPTRS_REQUIRE(!m.finalized, "model already finalized");
+    Tensor* t = nullptr;
+    int rc = tensor_alloc(GPTRS_F32, rank, dims, false, &t);
+    if (rc) return rc;
+    cudaError_t e = cudaMemcpy(t->data, data, t->bytes, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { tensor_release(t); return fail(GPTRS_EXECUTION, std::string("cudaMemcpy: ") + cudaGetErrorString(e)); }
+    auto it = m.raw.find(name);
+    if (it != m.raw.end()) { tensor_release(it->second); it->second = t; } else m.raw[name] = t;
+    m.ids[name] = {id_lo, id_hi};
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_model_set_rope_tables(gptrs_model* h, const float* h_cos, const float* h_sin, int64_t n_positions) {
+    GPTRS_REQUIRE(h && h_cos && h_sin && n_positions > 0, "null pointer");
+    Model& m = *reinterpret_cast<Model*>(h);
+    GPTRS_REQUIRE(m.cfg.rotary_dim > 0, "model has no rotary embedding");
+    size_t bytes = (size_t)n_positions * (m.cfg.rotary_dim / 2) * 4;
+    int rc = m.cos_tab.alloc(bytes);
+    if (!rc) rc = m.sin_tab.alloc(bytes);
+    if (rc) return rc;
+    GPTRS_CUDA_OK(cudaMemcpy(m.cos_tab.p, h_cos, bytes, cudaMemcpyHostToDevice));
+    GPTRS_CUDA_OK(cudaMemcpy(m.sin_tab.p, h_sin, bytes, cudaMemcpyHostToDevice));
+    m.n_rope_pos = (int)n_positions;
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
+    GPTRS_REQUIRE(h, "null pointer");
+    Model& m = *reinterpret_cast<Model*>(h);
+    GPTRS_REQUIRE(!m.finalized, "model already finalized");
+    const auto& c = m.cfg;
+    const int64_t D = c.d_model, QKV = m.QKV(), QD = m.QD(), MLP = c.d_mlp;
+    const bool gpt = c.kind == kKindGpt;
+    int rc;
+    if ((rc = get_raw(m, "tok_embeddings.weight", {c.vocab, D}, &m.tok_emb))) return rc;
+    if (gpt && (rc = get_raw(m, "pos_embeddings", {c.context_length, D}, &m.pos_emb))) return rc;
+    m.layers.resize(c.n_layers);
+    for (int l = 0; l < c.n_layers; ++l) {
+        Layer& L = m.layers[l];
+        const std::string p = "blocks." + std::to_string(l);
+        if (gpt) {
+            if ((rc = get_raw(m, p + ".ln_1.gamma", {D}, &L.ln1_g)) || (rc = get_raw(m, p + ".ln_1.beta", {D}, &L.ln1_b)) ||
+                (rc = get_raw(m, p + ".ln_2.gamma", {D}, &L.ln2_g)) || (rc = get_raw(m, p + ".ln_2.beta", {D}, &L.ln2_b))) return rc;
+            if ((rc = build_linear(m, {p + ".attention.w_qkv"}, p + ".attention.b_qkv", D, {QKV}, false, &L.qkv))) return rc;
+            if ((rc = build_linear(m, {p + ".attention.w_out"}, p + ".attention.b_out", QD, {D}, false, &L.attn_out))) return rc;
+            if ((rc = build_linear(m, {p + ".feed_forward.w_in"}, p + ".feed_forward.b_in", D, {MLP}, false, &L.mlp_in))) return rc;
+            if ((rc = build_linear(m, {p + ".feed_forward.w_out"}, p + ".feed_forward.b_out", MLP, {D}, false, &L.mlp_out))) return rc;
+        } else {
+            if ((rc = get_raw(m, p + ".norm_1.gamma", {D}, &L.ln1_g)) || (rc = get_raw(m, p + ".norm_2.gamma", {D}, &L.ln2_g))) return rc;
+            if ((rc = build_linear(m, {p + ".attention.w_qkv"}, "", D, {QKV}, false, &L.qkv))) return rc;
+            if ((rc = build_linear(m, {p + ".attention.w_out"}, "", QD, {D}, false, &L.attn_out))) return rc;
+            if (m.f32()) {
+                if ((rc = build_linear(m, {p + ".feed_forward.w_gate"}, "", D, {MLP}, false, &L.mlp_gate))) return rc;
+                if ((rc = build_linear(m, {p + ".feed_forward.w_up"}, "", D, {MLP}, false, &L.mlp_up))) return rc;
+            } else {
+                if ((rc = build_linear(m, {p + ".feed_forward.w_gate", p + ".feed_forward.w_up"}, "", D, {MLP, MLP}, true, &L.mlp_gate_up))) return rc;
+            }
+            if ((rc = build_linear(m, {p + ".feed_forward.w_down"}, "", MLP, {D}, false, &L.mlp_out))) return rc;
+        }
+        if (drop_f32_leaves && !m.f32()) {
+            // the f32 leaves of this layer's Linears are no longer needed once quantised
+            for (const char* s : {".attention.w_qkv", ".attention.w_out", ".feed_forward.w_gate", ".feed_forward.w_up", ".feed_forward.w_down"}) {
+                auto it = m.raw.find(p + s);
+                if (it != m.raw.end()) { tensor_release(it->second); m.raw.erase(it); }
+            }
+        }
+    }
+    if (gpt) {
+        if ((rc = get_raw(m, "final_ln.gamma", {D}, &m.final_g)) || (rc = get_raw(m, "final_ln.beta", {D}, &m.final_b))) return rc;
+    } else {
+        if ((rc = get_raw(m, "final_norm.gamma", {D}, &m.final_g))) return rc;
+    }
+    if ((rc = build_linear(m, {"lm_head"}, "", D, {c.vocab}, false, &m.lm_head))) return rc;
+    if (drop_f32_leaves && !m.f32()) {
+        auto it = m.raw.find("lm_head");
+        if (it != m.raw.end()) { tensor_release(it->second); m.raw.erase(it); }
+    }
+
+    // rotary tables (host formula of rotary.rs:75-215, RopeScaling::None) unless the caller set them
+    if (!gpt && c.rotary_dim > 0 && m.n_rope_pos == 0) {
+        const int half = c.rotary_dim / 2, np = c.context_length;
+        std::vector<float> cs((size_t)np * half), sn((size_t)np * half);
+        for (int i = 0; i < half; ++i) {
+            const float exponent = (2.0f * (float)i) / (float)c.rotary_dim;
+            const float inv = powf(c.rope_theta, -exponent);
+            for (int p = 0; p < np; ++p) {
+                const float ang = (float)p * inv;
+                cs[(size_t)p * half + i] = cosf(ang);
+                sn[(size_t)p * half + i] = sinf(ang);
+            }
+        }
+        if ((rc = gptrs_cuda_model_set_rope_tables(h, cs.data(), sn.data(), np))) return rc;
+    }
+    if (!gpt && c.rotary_dim > 0) GPTRS_REQUIRE(m.n_rope_pos >= c.context_length, "rotary tables shorter than context_length");
+
+    // activations
+    const int T = c.max_tokens;
+    const size_t act = m.f32() ? 4 : 2;
+    if ((rc = m.hidden.alloc((size_t)T * D * 4)) || (rc = m.xn.alloc((size_t)T * D * act)) || (rc = m.xn_rows.alloc((size_t)T * D * act)) ||
+        (rc = m.qkv.alloc((size_t)T * QKV * act)) || (rc = m.attn.alloc((size_t)T * QD * act)) ||
+        (rc = m.mlp_h.alloc((size_t)T * MLP * act))) return rc;
+    if (m.f32() && !gpt && ((rc = m.mlp_g.alloc((size_t)T * MLP * 4)) || (rc = m.mlp_u.alloc((size_t)T * MLP * 4)))) return rc;
+    if (!m.f32() && (rc = m.q_rot.alloc((size_t)T * QD * 2))) return rc;
+    const int max_rows = c.max_logit_rows > 0 ? c.max_logit_rows : c.max_seqs;
+    if ((rc = m.logits.alloc((size_t)max_rows * c.vocab * 4))) return rc;
+    for (DevBuf* b : {&m.d_tokens, &m.d_slot, &m.d_pos, &m.d_ctx, &m.d_rows, &m.d_sampled})
+        if ((rc = b->alloc((size_t)std::max(T, max_rows) * 4, true))) return rc;
+    if ((rc = m.d_status.alloc(4, true))) return rc;
+    GPTRS_CUDA_OK(cudaMallocHost(&m.h_stage, (size_t)6 * std::max(T, max_rows) * 4));
+    GPTRS_CUDA_OK(cudaMallocHost(&m.h_logits, (size_t)max_rows * c.vocab * 4));
+
+    // KV storage
+    m.seq_pages.assign(c.max_seqs, 0);
+    m.seq_len.assign(c.max_seqs, 0);
+    if (m.f32()) {
+        m.cache_layer_elems = (size_t)c.max_seqs * c.n_kv_heads * c.context_length * c.head_dim;
+        if ((rc = m.k_cache.alloc(m.cache_layer_elems * c.n_layers * 4, true)) ||
+            (rc = m.v_cache.alloc(m.cache_layer_elems * c.n_layers * 4, true))) return rc;
+    } else {
+        m.pool_layer_bytes = gptrs_cuda_kv_pool_bytes(c.kv_pages, c.n_kv_heads, c.head_dim);
+        if ((rc = m.kv_pool.alloc(m.pool_layer_bytes * c.n_layers))) return rc;
+        GPTRS_CUDA_OK(cudaMemsetAsync(m.kv_pool.p, 0, m.kv_pool.n, m.stream));
+        const size_t tbytes = (size_t)c.max_seqs * c.max_pages_per_seq * 4;
+        if ((rc = m.d_page_table.alloc(tbytes, true))) return rc;
+        GPTRS_CUDA_OK(cudaMallocHost(&m.h_page_table, tbytes));
+        memset(m.h_page_table, 0, tbytes);
+        for (int64_t p = c.kv_pages - 1; p >= 0; --p) m.free_pages.push_back((int32_t)p);
+        // scratch for the split partials at the worst case of a step
+        const int64_t max_ctx = (int64_t)c.max_pages_per_seq * kPage;
+        size_t worst = 0;
+        for (int chunk = 4; chunk <= 128; chunk *= 2)
+            worst = std::max(worst, gptrs_cuda_attention_scratch_bytes(T, c.n_q_heads, max_ctx, chunk));
+        // a chunk is never smaller than what keeps >= 4 CTAs per SM busy; cap the scratch at 1 GiB
+        worst = std::min<size_t>(worst, (size_t)1 << 30);
+        if ((rc = m.attn_scratch.alloc(worst))) return rc;
+    }
+    GPTRS_CUDA_OK(cudaStreamSynchronize(m.stream));
+    m.finalized = true;
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_model_stats(gptrs_model* h, int64_t* quantised_now, int64_t* memo_hits, int64_t* free_pages,
+                           int64_t* kernel_launches) {
+    GPTRS_REQUIRE(h, "null pointer");
+    Model& m = *reinterpret_cast<Model*>(h);
+    if (quantised_now) *quantised_now = m.quantised_now;
+    if (memo_hits) *memo_hits = m.memo_hits;
+    if (free_pages) *free_pages = (int64_t)m.free_pages.size();
+    if (kernel_launches) *kernel_launches = m.launches;
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_model_reset_sequence(gptrs_model* h, int slot) {
+    GPTRS_REQUIRE(h, "null pointer");
+    Model& m = *reinterpret_cast<Model*>(h);
+    GPTRS_REQUIRE(m.finalized && slot >= 0 && slot < m.cfg.max_seqs, "bad slot");
+    GPTRS_CUDA_OK(cudaStreamSynchronize(m.stream));
+    for (int i = 0; i < m.seq_pages[slot]; ++i)
+        m.free_pages.push_back(m.h_page_table[(size_t)slot * m.cfg.max_pages_per_seq + i]);
+    m.seq_pages[slot] = 0;
+    m.seq_len[slot] = 0;
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_model_sequence_length(gptrs_model* h, int slot, int* len) {
+    GPTRS_REQUIRE(h && len, "null pointer");
+    Model& m = *reinterpret_cast<Model*>(h);
+    GPTRS_REQUIRE(m.finalized && slot >= 0 && slot < m.cfg.max_seqs, "bad slot");
+    *len = m.seq_len[slot];
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* h, const int32_t* h_tokens, const int32_t* h_slots,
+                                               const int32_t* h_positions, int n_tokens, const int32_t* h_logit_rows,
+                                               int n_logit_rows, float* h_logits, int32_t* h_sampled, float temperature,
+                                               uint32_t seed) {
+    GPTRS_REQUIRE(h && h_tokens && h_slots && h_positions, "null pointer");
+    Model& m = *reinterpret_cast<Model*>(h);
+    const auto& c = m.cfg;
+    GPTRS_REQUIRE(m.finalized, "model not finalized");
+    GPTRS_REQUIRE(n_tokens > 0 && n_tokens <= c.max_tokens, "n_tokens out of range");
+    const int max_rows = c.max_logit_rows > 0 ? c.max_logit_rows : c.max_seqs;
+    GPTRS_REQUIRE(n_logit_rows >= 0 && n_logit_rows <= max_rows && (n_logit_rows == 0 || h_logit_rows), "bad logit rows");
+    const int T = n_tokens;
+    int max_ctx = 1;
+    int32_t* st = m.h_stage;
+    const int stride = std::max(c.max_tokens, max_rows);
+    for (int i = 0; i < T; ++i) {
+        GPTRS_REQUIRE(h_slots[i] >= 0 && h_slots[i] < c.max_seqs, "slot out of range");
+        GPTRS_REQUIRE(h_positions[i] >= 0 && h_positions[i] < c.context_length, "position beyond context_length");
+        GPTRS_REQUIRE(h_tokens[i] >= 0 && h_tokens[i] < c.vocab, "token id out of range");
+        int rc = ensure_pages(m, h_slots[i], h_positions[i]);
+        if (rc) return rc;
+        st[i] = h_tokens[i]; st[stride + i] = h_slots[i]; st[2 * stride + i] = h_positions[i];
+        st[3 * stride + i] = h_positions[i] + 1;
+        max_ctx = std::max(max_ctx, h_positions[i] + 1);
+        m.seq_len[h_slots[i]] = std::max(m.seq_len[h_slots[i]], h_positions[i] + 1);
+    }
+    for (int i = 0; i < n_logit_rows; ++i) {
+        GPTRS_REQUIRE(h_logit_rows[i] >= 0 && h_logit_rows[i] < T, "logit row out of range");
+        st[4 * stride + i] = h_logit_rows[i];
+    }
+    int rc = sync_page_table(m);
+    if (rc) return rc;
+    cudaStream_t s = m.stream;
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_tokens.p, st, (size_t)T * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_slot.p, st + stride, (size_t)T * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_pos.p, st + 2 * stride, (size_t)T * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_ctx.p, st + 3 * stride, (size_t)T * 4, cudaMemcpyHostToDevice, s));
+    if (n_logit_rows) GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_rows.p, st + 4 * stride, (size_t)n_logit_rows * 4, cudaMemcpyHostToDevice, s));
+    int chunk = 1;
+    attention_plan(m, T, max_ctx, &chunk);
+    m.sample_seed = seed;
+    // with no requested rows the pass still runs (it fills the KV cache); logits of row 0 are discarded
+    const int rows = n_logit_rows > 0 ? n_logit_rows : 1;
+    if (n_logit_rows == 0) GPTRS_CUDA_OK(cudaMemsetAsync(m.d_rows.p, 0, 4, s));
+    rc = enqueue_forward(m, T, max_ctx, chunk, rows, false, temperature);
+    if (rc) return rc;
+    if (h_logits && n_logit_rows)
+        GPTRS_CUDA_OK(cudaMemcpyAsync(m.h_logits, m.logits.p, (size_t)n_logit_rows * c.vocab * 4, cudaMemcpyDeviceToHost, s));
+    if (h_sampled && n_logit_rows)
+        GPTRS_CUDA_OK(cudaMemcpyAsync(st + 5 * stride, m.d_sampled.p, (size_t)n_logit_rows * 4, cudaMemcpyDeviceToHost, s));
+    rc = check_status(m);  // synchronises the stream
+    if (rc) return rc;
+    if (h_logits && n_logit_rows) memcpy(h_logits, m.h_logits, (size_t)n_logit_rows * c.vocab * 4);
+    if (h_sampled && n_logit_rows) memcpy(h_sampled, st + 5 * stride, (size_t)n_logit_rows * 4);
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_generator_begin(gptrs_model* h, int batch, const int32_t* h_first_tokens) {
+    GPTRS_REQUIRE(h && h_first_tokens, "null pointer");
+    Model& m = *reinterpret_cast<Model*>(h);
+    const auto& c = m.cfg;
+    GPTRS_REQUIRE(m.finalized && batch > 0 && batch <= c.max_seqs && batch <= c.max_tokens, "bad batch");
+    const int stride = std::max(c.max_tokens, c.max_logit_rows > 0 ? c.max_logit_rows : c.max_seqs);
+    int32_t* st = m.h_stage;
+    for (int b = 0; b < batch; ++b) {
+        GPTRS_REQUIRE(h_first_tokens[b] >= 0 && h_first_tokens[b] < c.vocab, "token id out of range");
+        GPTRS_REQUIRE(m.seq_len[b] < c.context_length, "sequence already at context_length");
+        st[b] = h_first_tokens[b]; st[stride + b] = b; st[2 * stride + b] = m.seq_len[b]; st[3 * stride + b] = m.seq_len[b] + 1;
+    }
+    cudaStream_t s = m.stream;
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_tokens.p, st, (size_t)batch * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_slot.p, st + stride, (size_t)batch * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_pos.p, st + 2 * stride, (size_t)batch * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_ctx.p, st + 3 * stride, (size_t)batch * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaStreamSynchronize(s));
+    m.gen_batch = batch;
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_generator_step(gptrs_model* h, const int32_t* h_tokens_in, int32_t* h_tokens_out, int use_graph) {
+    GPTRS_REQUIRE(h, "null pointer");
+    Model& m = *reinterpret_cast<Model*>(h);
+    const auto& c = m.cfg;
+    const int B = m.gen_batch;
+    GPTRS_REQUIRE(m.finalized && B > 0, "generator_begin has not been called");
+    int max_ctx = 1;
+    for (int b = 0; b < B; ++b) {
+        GPTRS_REQUIRE(m.seq_len[b] < c.context_length, "sequence reached context_length");
+        int rc = ensure_pages(m, b, m.seq_len[b]);
+        if (rc) return rc;
+        max_ctx = std::max(max_ctx, m.seq_len[b] + 1);
+    }
+    int rc = sync_page_table(m);
+    if (rc) return rc;
+    cudaStream_t s = m.stream;
+    if (h_tokens_in) {
+        GPTRS_CUDA_OK(cudaStreamSynchronize(s));  // the staging buffer may still feed an earlier copy
+        memcpy(m.h_stage, h_tokens_in, (size_t)B * 4);
+        GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_tokens.p, m.h_stage, (size_t)B * 4, cudaMemcpyHostToDevice, s));
+    }
+    // The launch geometry is fixed per graph: bucket the visible length (multiples of 512 tokens)
+    // so that graph keys change rarely.
+    const int cap = m.f32() ? c.context_length : c.max_pages_per_seq * kPage;
+    const int bucket = m.f32() ? c.context_length : std::min(cap, ((max_ctx + 511) / 512) * 512);
+    int chunk = 1;
+    attention_plan(m, B, bucket, &chunk);
+    const int splits = m.f32() ? 1 : (bucket + chunk * kPage - 1) / (chunk * kPage);
+    auto body = [&]() -> int {
+        int r = enqueue_forward(m, B, bucket, chunk, B, true, 0.f);
+        if (r) return r;
+        // next step: the sampled ids become the inputs, positions advance
+        GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_tokens.p, m.d_sampled.p, (size_t)B * 4, cudaMemcpyDeviceToDevice, s));
+        AdvanceParams ap = {m.d_pos.as<int>(), m.d_ctx.as<int>(), B};
+        ++m.launches;
+        return launch_kernel(advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s, 1, ap);
+    };
+    if (use_graph) {
+        GraphKey key{B, chunk, splits};
+        auto it = m.graphs.find(key);
+        if (it == m.graphs.end()) {
+            const int64_t launches_before = m.launches;
+            cudaGraph_t graph = nullptr;
+            GPTRS_CUDA_OK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+            g_use_pdl = c.use_pdl ? 1 : 0;
+            int r = body();
+            g_use_pdl = 0;
+            cudaError_t e = cudaStreamEndCapture(s, &graph);
+            const int64_t recorded = m.launches - launches_before;
+            m.launches = launches_before;  // capturing launches nothing
+            if (r) { if (graph) cudaGraphDestroy(graph); return r; }
+            GPTRS_CUDA_OK(e);
+            cudaGraphExec_t exec = nullptr;
+            e = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            GPTRS_CUDA_OK(e);
+            it = m.graphs.emplace(key, Model::GraphEntry{exec, recorded}).first;
+        }
+        GPTRS_CUDA_OK(cudaGraphLaunch(it->second.exec, s));
+        m.launches += it->second.kernels;
+    } else {
+        int r = body();
+        if (r) return r;
+    }
+    for (int b = 0; b < B; ++b) ++m.seq_len[b];
+    if (h_tokens_out) {
+        GPTRS_CUDA_OK(cudaMemcpyAsync(m.h_stage + B, m.d_sampled.p, (size_t)B * 4, cudaMemcpyDeviceToHost, s));
+        rc = check_status(m);
+        if (rc) return rc;
+        memcpy(h_tokens_out, m.h_stage + B, (size_t)B * 4);
+    }
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_generator_sync(gptrs_model* h) {
+    GPTRS_REQUIRE(h, "null pointer");
+    return check_status(*reinterpret_cast<Model*>(h));
+}
+
+void* gptrs_cuda_model_stream(gptrs_model* h) { return h ? reinterpret_cast<Model*>(h)->stream : nullptr; }
+
+}  // extern "C"

@@ -1,0 +1,152 @@
+// Backend-object level of the C ABI: reference-counted device tensors (the TensorHandle of
+// PortableBackend, crates/gpt-rs/src/backend/spec.rs:1287-1310), materialize / to_literal, and
+// the ParamResolver memo of leaf and derived parameters keyed by stable u128 ids
+// (crates/gpt-rs/src/backend/param_resolver.rs:11-50).
+#include "tensor.h"
+
+#include <cstring>
+#include <map>
+#include <mutex>
+
+namespace gptrs {
+
+size_t dtype_size(int dtype) {
+    switch (dtype) {
+        case GPTRS_F32: case GPTRS_SI32: return 4;
+        case GPTRS_F16: case GPTRS_BF16: return 2;
+        case GPTRS_I1: case GPTRS_SI8: case GPTRS_UI8: return 1;
+        default: return 0;
+    }
+}
+
+int64_t Tensor::numel() const {
+    int64_t n = 1;
+    for (int64_t d : dims) n *= d;
+    return n;
+}
+
+int tensor_alloc(int dtype, int rank, const int64_t* dims, bool zero, Tensor** out) {
+    GPTRS_REQUIRE(out, "null output");
+    GPTRS_REQUIRE(dtype_size(dtype) > 0, "unsupported dtype");
+    GPTRS_REQUIRE(rank >= 0 && rank <= 8 && (rank == 0 || dims), "bad rank");
+    auto* t = new Tensor();
+    t->dtype = dtype;
+    for (int i = 0; i < rank; ++i) {
+        if (dims[i] < 0) { delete t; return fail(GPTRS_SPEC_VIOLATION, "negative dimension"); }
+        t->dims.push_back(dims[i]);
+    }
+    t->bytes = (size_t)t->numel() * dtype_size(dtype);
+    if (t->bytes) {
+        cudaError_t e = cudaMalloc(&t->data, t->bytes);
+        if (e != cudaSuccess) { delete t; return fail(GPTRS_EXECUTION, std::string("cudaMalloc: ") + cudaGetErrorString(e)); }
+        if (zero) {
+            e = cudaMemset(t->data, 0, t->bytes);
+            if (e != cudaSuccess) { cudaFree(t->data); delete t; return fail(GPTRS_EXECUTION, "cudaMemset failed"); }
+        }
+    }
+    *out = t;
+    return GPTRS_OK;
+}
+
+void tensor_retain(Tensor* t) { if (t) t->refs.fetch_add(1, std::memory_order_relaxed); }
+
+void tensor_release(Tensor* t) {
+    if (t && t->refs.fetch_sub(1, std::memory_order_acq_rel) == 1) {
+        if (t->data && t->owns) cudaFree(t->data);
+        delete t;
+    }
+}
+
+namespace {
+std::mutex g_param_mu;
+std::map<std::pair<uint64_t, uint64_t>, Tensor*> g_params;  // (hi, lo) -> retained tensor
+}  // namespace
+
+Tensor* param_lookup(uint64_t lo, uint64_t hi) {
+    std::lock_guard<std::mutex> lk(g_param_mu);
+    auto it = g_params.find({hi, lo});
+    if (it == g_params.end()) return nullptr;
+    tensor_retain(it->second);
+    return it->second;
+}
+
+void param_store(uint64_t lo, uint64_t hi, Tensor* t) {
+    std::lock_guard<std::mutex> lk(g_param_mu);
+    tensor_retain(t);
+    auto it = g_params.find({hi, lo});
+    if (it != g_params.end()) { tensor_release(it->second); it->second = t; }
+    else g_params[{hi, lo}] = t;
+}
+
+}  // namespace gptrs
+
+using namespace gptrs;
+
+extern "C" {
+
+int gptrs_cuda_materialize_literal(int dtype, int rank, const int64_t* dims, const void* h_bytes, size_t n_bytes,
+                                   gptrs_tensor** out) {
+    Tensor* t = nullptr;
+    int rc = tensor_alloc(dtype, rank, dims, false, &t);
+    if (rc) return rc;
+    if (n_bytes != t->bytes || (t->bytes && !h_bytes)) {
+        tensor_release(t);
+        return fail(GPTRS_SPEC_VIOLATION, "literal byte length does not match dtype and shape");
+    }
+    if (t->bytes) {
+        cudaError_t e = cudaMemcpy(t->data, h_bytes, t->bytes, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { tensor_release(t); return fail(GPTRS_EXECUTION, std::string("cudaMemcpy: ") + cudaGetErrorString(e)); }
+    }
+    *out = reinterpret_cast<gptrs_tensor*>(t);
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_materialize_zeroed(int dtype, int rank, const int64_t* dims, gptrs_tensor** out) {
+    Tensor* t = nullptr;
+    int rc = tensor_alloc(dtype, rank, dims, true, &t);
+    if (rc) return rc;
+    *out = reinterpret_cast<gptrs_tensor*>(t);
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_tensor_spec(const gptrs_tensor* h, int* dtype, int* rank, int64_t* dims, int dims_cap) {
+    GPTRS_REQUIRE(h && dtype && rank, "null pointer");
+    const Tensor* t = reinterpret_cast<const Tensor*>(h);
+    *dtype = t->dtype;
+    *rank = (int)t->dims.size();
+    for (int i = 0; i < *rank && i < dims_cap && dims; ++i) dims[i] = t->dims[i];
+    return GPTRS_OK;
+}
+
+void* gptrs_cuda_tensor_data(const gptrs_tensor* h) {
+    return h ? reinterpret_cast<const Tensor*>(h)->data : nullptr;
+}
+
+int gptrs_cuda_to_literal(const gptrs_tensor* h, void* h_dst, size_t cap, size_t* written) {
+    GPTRS_REQUIRE(h && written, "null pointer");
+    const Tensor* t = reinterpret_cast<const Tensor*>(h);
+    *written = t->bytes;
+    GPTRS_REQUIRE(cap >= t->bytes && (h_dst || t->bytes == 0), "destination too small");
+    if (t->bytes) {
+        GPTRS_CUDA_OK(cudaDeviceSynchronize());
+        GPTRS_CUDA_OK(cudaMemcpy(h_dst, t->data, t->bytes, cudaMemcpyDeviceToHost));
+    }
+    return GPTRS_OK;
+}
+
+void gptrs_cuda_tensor_retain(gptrs_tensor* h) { tensor_retain(reinterpret_cast<Tensor*>(h)); }
+void gptrs_cuda_tensor_release(gptrs_tensor* h) { tensor_release(reinterpret_cast<Tensor*>(h)); }
+
+int gptrs_cuda_param_get(uint64_t id_lo, uint64_t id_hi, gptrs_tensor** out) {
+    GPTRS_REQUIRE(out, "null pointer");
+    *out = reinterpret_cast<gptrs_tensor*>(param_lookup(id_lo, id_hi));
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_param_set(uint64_t id_lo, uint64_t id_hi, gptrs_tensor* h) {
+    GPTRS_REQUIRE(h, "null tensor");
+    param_store(id_lo, id_hi, reinterpret_cast<Tensor*>(h));
+    return GPTRS_OK;
+}
+
+}  // extern "C"

@@ -203,6 +203,92 @@ int gptrs_cuda_attention_decode_f32(const float* d_qkv, const float* d_k_cache, 
                                     int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
                                     int64_t capacity, void* stream);
 
+/* ==============================================================================================
+ * Backend object level: tensor handles and the parameter memo.
+ * gptrs_tensor is the TensorHandle of PortableBackend (crates/gpt-rs/src/backend/spec.rs:1287-1288):
+ * reference counted (retain = Clone, release = Drop), thread safe, immutable once produced.
+ * ============================================================================================ */
+typedef struct gptrs_tensor gptrs_tensor;
+/* materialize(TensorInit::Literal | Zeroed) (spec.rs:295-300, 1312-1313): bytes are row-major
+ * little-endian, n_bytes must equal numel * sizeof(dtype). Synchronous. */
+int gptrs_cuda_materialize_literal(int dtype, int rank, const int64_t* dims, const void* h_bytes, size_t n_bytes,
+                                   gptrs_tensor** out);
+int gptrs_cuda_materialize_zeroed(int dtype, int rank, const int64_t* dims, gptrs_tensor** out);
+/* to_literal (spec.rs:1315-1316): synchronises the device, copies the dense bytes to the host. */
+int gptrs_cuda_to_literal(const gptrs_tensor* h, void* h_dst, size_t cap, size_t* written);
+int gptrs_cuda_tensor_spec(const gptrs_tensor* h, int* dtype, int* rank, int64_t* dims, int dims_cap);
+void* gptrs_cuda_tensor_data(const gptrs_tensor* h); /* device pointer */
+void gptrs_cuda_tensor_retain(gptrs_tensor* h);
+void gptrs_cuda_tensor_release(gptrs_tensor* h);
+/* ParamResolver::{get,set} (crates/gpt-rs/src/backend/param_resolver.rs:11-17): memo of leaf and
+ * derived (quantised + repacked) parameters by stable u128 id, passed as two 64-bit halves.
+ * get returns a retained handle, or NULL in *out when the id is unknown. */
+int gptrs_cuda_param_get(uint64_t id_lo, uint64_t id_hi, gptrs_tensor** out);
+int gptrs_cuda_param_set(uint64_t id_lo, uint64_t id_hi, gptrs_tensor* h);
+
+/* ==============================================================================================
+ * Model + generator level (C++ host code inside the library).
+ *   load_model / ParamSource           crates/gpt-rs/src/runtime/loader.rs:243-309, params.rs:25-48
+ *   Gpt / Ministral decode forward     crates/gpt-rs/src/model/gpt.rs:585-751, model/ministral.rs:613-766
+ *   Generator::step                    crates/gpt-rs/src/inference/generate.rs:123-169
+ * A model owns its activations, its KV storage for `max_seqs` independent sequences ("slots"),
+ * a CUDA stream and the CUDA graphs of its decode step. Weight modes: 0 = f32 weights and f32
+ * dense KV cache (both kinds), 1 = W4A16 group-128, 2 = W8A16 per-channel (ministral kind,
+ * head_dim 128; bf16 activations, paged bf16 KV cache, f32 residual stream and logits).
+ * ============================================================================================ */
+typedef struct gptrs_model gptrs_model;
+typedef struct {
+    int kind;            /* 0 = gpt (LayerNorm, learned positions, GELU MLP, biases), 1 = ministral */
+    int weight_mode;     /* 0 = f32, 1 = W4A16, 2 = W8A16 */
+    int n_layers, d_model, n_q_heads, n_kv_heads, head_dim, d_mlp, vocab, context_length;
+    float norm_eps;
+    float rope_theta;    /* ministral */
+    int rotary_dim;      /* ministral; 0 = no rotary embedding */
+    int max_seqs;        /* sequence slots */
+    int max_tokens;      /* rows per forward call (decode batch or prefill chunk) */
+    int max_logit_rows;  /* rows that may request logits per call (0 = max_seqs) */
+    int64_t kv_pages;    /* pages per layer pool (quantised modes) */
+    int max_pages_per_seq;
+    int use_pdl;         /* record the decode graph with programmatic dependent launches */
+} gptrs_model_config;
+
+int gptrs_cuda_model_create(const gptrs_model_config* cfg, gptrs_model** out);
+void gptrs_cuda_model_destroy(gptrs_model* m);
+/* Hands one f32 parameter to the model under the reference's name (model/gpt.rs:222-291,
+ * model/ministral.rs:376-421) and stable id (params.rs:29-48, two 64-bit halves). `data` is a host
+ * pointer, or a device pointer when on_device != 0. Linear weights are [in, out]. */
+int gptrs_cuda_model_load_param(gptrs_model* m, const char* name, uint64_t id_lo, uint64_t id_hi, const float* data,
+                                int on_device, int rank, const int64_t* dims);
+/* Optional: the caller's cos/sin tables [n_positions][rotary_dim/2] (the reference builds them on
+ * the host and passes them as inputs, model/ministral.rs:253-261); otherwise finalize computes
+ * them with the formula of ops/functional/rotary.rs:75-215 (no scaling). */
+int gptrs_cuda_model_set_rope_tables(gptrs_model* m, const float* h_cos, const float* h_sin, int64_t n_positions);
+/* Checks that every parameter is present, quantises + repacks Linear weights (memoised process-wide
+ * by stable id, see gptrs_cuda_param_get), allocates activations and KV storage. */
+int gptrs_cuda_model_finalize(gptrs_model* m, int drop_f32_leaves);
+int gptrs_cuda_model_stats(gptrs_model* m, int64_t* quantised_now, int64_t* memo_hits, int64_t* free_pages,
+                           int64_t* kernel_launches);
+int gptrs_cuda_model_reset_sequence(gptrs_model* m, int slot);
+int gptrs_cuda_model_sequence_length(gptrs_model* m, int slot, int* len);
+/* One forward pass over n_tokens rows (token id, slot, position each; host arrays). K/V of every
+ * row is appended to its slot's cache, each row attends to positions 0..position of its slot.
+ * Rows listed in h_logit_rows produce f32 logits (h_logits[n_logit_rows][vocab], optional) and a
+ * sampled id each (h_sampled, optional; temperature <= 0 = greedy). Synchronous. */
+int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* m, const int32_t* h_tokens, const int32_t* h_slots,
+                                               const int32_t* h_positions, int n_tokens, const int32_t* h_logit_rows,
+                                               int n_logit_rows, float* h_logits, int32_t* h_sampled, float temperature,
+                                               uint32_t seed);
+/* Generator over slots 0..batch-1 (already prefilled): begin() sets each slot's next input token;
+ * step() runs one greedy decode step for the whole batch. h_tokens_in (optional) overrides the
+ * device-resident inputs, h_tokens_out (optional) receives the sampled ids and makes the call
+ * synchronous; with both NULL the ids stay on the device and feed the next step. use_graph != 0
+ * replays a CUDA graph of the step (recorded on first use per launch geometry). */
+int gptrs_cuda_generator_begin(gptrs_model* m, int batch, const int32_t* h_first_tokens);
+int gptrs_cuda_generator_step(gptrs_model* m, const int32_t* h_tokens_in, int32_t* h_tokens_out, int use_graph);
+/* Waits for the model's stream and reports a device-side error recorded by any step. */
+int gptrs_cuda_generator_sync(gptrs_model* m);
+void* gptrs_cuda_model_stream(gptrs_model* m); /* cudaStream_t of the model */
+
 #ifdef __cplusplus
 }
 #endif
