@@ -196,7 +196,7 @@ int build_linear(Model& m, const std::vector<std::string>& names, const std::str
     int64_t pd[1] = {(int64_t)need};
     if (!rc) rc = tensor_alloc(GPTRS_UI8, 1, pd, false, &packed);
     if (!rc) rc = w4 ? gptrs_cuda_w4a16_repack(q.as<uint8_t>(), s.as<uint16_t>(), out_total, in, gate_up ? 1 : 0, packed->data, m.stream)
-                     : gptrs_cuda_w8a16_repack(q.as<int8_t>(), s.as<uint16_t>(), out_total, in, packed->data, m.stream);
+                     : gptrs_cuda_w8a16_repack(q.as<int8_t>(), s.as<uint16_t>(), out_total, in, gate_up ? 1 : 0, packed->data, m.stream);
     if (!rc && cudaStreamSynchronize(m.stream) != cudaSuccess) rc = fail(GPTRS_EXECUTION, "quantise/repack failed");
     drop();
     if (rc) { tensor_release(packed); return rc; }

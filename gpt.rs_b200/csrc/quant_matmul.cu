@@ -401,7 +401,7 @@ __global__ void w4_unpack_kernel(const uint32_t* in_w, const __half* in_s, int64
 }
 
 // Packed W8: [tile][K/32][lane][16 bytes]; byte order = A-fragment register order.
-__global__ void w8_repack_kernel(const int8_t* q, const __half* scales, int64_t N, int64_t K,
+__global__ void w8_repack_kernel(const int8_t* q, const __half* scales, int64_t N, int64_t K, int interleave,
                                  uint8_t* out_w, __half* out_s) {
     const int64_t chunks = K / 32;
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -413,16 +413,16 @@ __global__ void w8_repack_kernel(const int8_t* q, const __half* scales, int64_t 
         int s = b >> 3, e = b & 7;  // k16 step inside the chunk, element of the fragment
         int row = g + ((e >> 1) & 1) * 8;
         int k = (int)(chunk * 32 + s * 16 + 2 * t + (e & 1) + ((e >> 2) & 1) * 8);
-        out_w[i] = (uint8_t)(q[(tile * 16 + row) * K + k] + 128);
+        out_w[i] = (uint8_t)(q[source_row(tile * 16 + row, N, interleave) * K + k] + 128);
     }
     if (i < N) {
         int e = i & 15;
         int64_t tile = i >> 4;
-        out_s[i] = scales[tile * 16 + (e >> 1) + (e & 1) * 8];
+        out_s[i] = scales[source_row(tile * 16 + (e >> 1) + (e & 1) * 8, N, interleave)];
     }
 }
 
-__global__ void w8_unpack_kernel(const uint8_t* in_w, const __half* in_s, int64_t N, int64_t K,
+__global__ void w8_unpack_kernel(const uint8_t* in_w, const __half* in_s, int64_t N, int64_t K, int interleave,
                                  int8_t* q, __half* scales) {
     const int64_t chunks = K / 32;
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -434,12 +434,12 @@ __global__ void w8_unpack_kernel(const uint8_t* in_w, const __half* in_s, int64_
         int s = b >> 3, e = b & 7;
         int row = g + ((e >> 1) & 1) * 8;
         int k = (int)(chunk * 32 + s * 16 + 2 * t + (e & 1) + ((e >> 2) & 1) * 8);
-        q[(tile * 16 + row) * K + k] = (int8_t)((int)in_w[i] - 128);
+        q[source_row(tile * 16 + row, N, interleave) * K + k] = (int8_t)((int)in_w[i] - 128);
     }
     if (i < N) {
         int e = i & 15;
         int64_t tile = i >> 4;
-        scales[tile * 16 + (e >> 1) + (e & 1) * 8] = in_s[i];
+        scales[source_row(tile * 16 + (e >> 1) + (e & 1) * 8, N, interleave)] = in_s[i];
     }
 }
 
@@ -611,25 +611,26 @@ int gptrs_cuda_w4a16_unpack(const void* d_packed, int64_t n, int64_t k, int inte
 }
 
 int gptrs_cuda_w8a16_repack(const int8_t* d_q, const uint16_t* d_scales, int64_t n, int64_t k,
-                            void* d_packed, void* stream) {
+                            int interleave, void* d_packed, void* stream) {
     GPTRS_REQUIRE(d_q && d_scales && d_packed, "null pointer");
     GPTRS_REQUIRE(n > 0 && k > 0 && n % 16 == 0 && k % 128 == 0, "N % 16 == 0 and K % 128 == 0 required");
+    GPTRS_REQUIRE(!interleave || n % 32 == 0, "gate/up interleave needs N % 32 == 0");
     uint8_t* ow = static_cast<uint8_t*>(d_packed);
     __half* os = reinterpret_cast<__half*>(ow + (size_t)n * k);
     w8_repack_kernel<<<ceil_div(n * k, 256), 256, 0, as_stream(stream)>>>(
-        d_q, reinterpret_cast<const __half*>(d_scales), n, k, ow, os);
+        d_q, reinterpret_cast<const __half*>(d_scales), n, k, interleave, ow, os);
     GPTRS_CUDA_OK(cudaGetLastError());
     return GPTRS_OK;
 }
 
-int gptrs_cuda_w8a16_unpack(const void* d_packed, int64_t n, int64_t k, int8_t* d_q,
+int gptrs_cuda_w8a16_unpack(const void* d_packed, int64_t n, int64_t k, int interleave, int8_t* d_q,
                             uint16_t* d_scales, void* stream) {
     GPTRS_REQUIRE(d_q && d_scales && d_packed, "null pointer");
     GPTRS_REQUIRE(n > 0 && k > 0 && n % 16 == 0 && k % 128 == 0, "N % 16 == 0 and K % 128 == 0 required");
     const uint8_t* iw = static_cast<const uint8_t*>(d_packed);
     const __half* is = reinterpret_cast<const __half*>(iw + (size_t)n * k);
     w8_unpack_kernel<<<ceil_div(n * k, 256), 256, 0, as_stream(stream)>>>(
-        iw, is, n, k, d_q, reinterpret_cast<__half*>(d_scales));
+        iw, is, n, k, interleave, d_q, reinterpret_cast<__half*>(d_scales));
     GPTRS_CUDA_OK(cudaGetLastError());
     return GPTRS_OK;
 }

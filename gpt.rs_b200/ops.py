@@ -50,19 +50,19 @@ def w4a16_unpack(packed: torch.Tensor, n: int, k: int, interleave_gate_up: bool 
     return q, s
 
 
-def w8a16_repack(q: torch.Tensor, scales: torch.Tensor, n: int, k: int):
+def w8a16_repack(q: torch.Tensor, scales: torch.Tensor, n: int, k: int, interleave_gate_up: bool = False):
     nbytes = w8a16_packed_bytes(n, k)
     if nbytes == 0:
-        check(lib().gptrs_cuda_w8a16_repack(0, 0, n, k, 0, None))
+        check(lib().gptrs_cuda_w8a16_repack(0, 0, n, k, 0, 0, None))
     out = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-    check(lib().gptrs_cuda_w8a16_repack(_ptr(q), _ptr(scales), n, k, _ptr(out), _stream()))
+    check(lib().gptrs_cuda_w8a16_repack(_ptr(q), _ptr(scales), n, k, int(interleave_gate_up), _ptr(out), _stream()))
     return out
 
 
-def w8a16_unpack(packed: torch.Tensor, n: int, k: int):
+def w8a16_unpack(packed: torch.Tensor, n: int, k: int, interleave_gate_up: bool = False):
     q = torch.empty((n, k), dtype=torch.int8, device=packed.device)
     s = torch.empty((n,), dtype=torch.float16, device=packed.device)
-    check(lib().gptrs_cuda_w8a16_unpack(_ptr(packed), n, k, _ptr(q), _ptr(s), _stream()))
+    check(lib().gptrs_cuda_w8a16_unpack(_ptr(packed), n, k, int(interleave_gate_up), _ptr(q), _ptr(s), _stream()))
     return q, s
 
 

@@ -65,15 +65,17 @@ int gptrs_cuda_abi_version(void);
 size_t gptrs_cuda_w4a16_packed_bytes(int64_t n, int64_t k);
 size_t gptrs_cuda_w8a16_packed_bytes(int64_t n, int64_t k);
 
-/* Canonical -> kernel layout (device to device). */
+/* Canonical -> kernel layout (device to device). With interleave_gate_up the N rows are a fused
+ * [gate; up] weight (rows [0,N/2) gate, [N/2,N) up) and every 16-row tile receives 8 gate rows
+ * followed by the 8 matching up rows, which is what the SwiGLU epilogue expects. */
 int gptrs_cuda_w4a16_repack(const uint8_t* d_q, const uint16_t* d_scales, int64_t n, int64_t k,
                             int interleave_gate_up, void* d_packed, void* stream);
 int gptrs_cuda_w8a16_repack(const int8_t* d_q, const uint16_t* d_scales, int64_t n, int64_t k,
-                            void* d_packed, void* stream);
+                            int interleave_gate_up, void* d_packed, void* stream);
 /* Kernel layout -> canonical q/scales (the bit-exact unpack check). */
 int gptrs_cuda_w4a16_unpack(const void* d_packed, int64_t n, int64_t k, int interleave_gate_up,
                             uint8_t* d_q, uint16_t* d_scales, void* stream);
-int gptrs_cuda_w8a16_unpack(const void* d_packed, int64_t n, int64_t k, int8_t* d_q,
+int gptrs_cuda_w8a16_unpack(const void* d_packed, int64_t n, int64_t k, int interleave_gate_up, int8_t* d_q,
                             uint16_t* d_scales, void* stream);
 
 /* Quantise an f32 Linear weight stored [in=K][out=N] (nn/layers/linear.rs:14) to canonical

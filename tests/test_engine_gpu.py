@@ -14,11 +14,20 @@ from oracle import models_ref as mr
 pytestmark = pytest.mark.gpu
 
 
-def _load(cfg_ref: mr.Cfg, params, mode=gm.MODE_F32, **kw):
+_NAMESPACE = [100]
+
+
+def _load(cfg_ref: mr.Cfg, params, mode=gm.MODE_F32, namespace=None, **kw):
+    """Every distinct set of weights gets its own namespace: stable parameter ids (and with them
+    the memo of quantised layouts) are per namespace, as in runtime/namespace.rs:5-11."""
+    if namespace is None:
+        _NAMESPACE[0] += 1
+        namespace = _NAMESPACE[0]
     kind = gm.KIND_GPT if cfg_ref.kind == "gpt" else gm.KIND_MINISTRAL
+    kw.setdefault("max_logit_rows", kw.get("max_tokens", 64))
     cfg = gm.ModelConfig(kind, cfg_ref.n_layers, cfg_ref.d_model, cfg_ref.n_q, cfg_ref.n_kv, cfg_ref.hd, cfg_ref.d_mlp,
                          cfg_ref.vocab, cfg_ref.ctx, cfg_ref.eps, cfg_ref.theta, cfg_ref.rot, weight_mode=mode, **kw)
-    m = gm.LoadedModel(cfg)
+    m = gm.LoadedModel(cfg, namespace=namespace)
     for name, w in params.items():
         m.load_param(name, w)
     m.finalize()
@@ -91,7 +100,7 @@ def test_graph_and_eager_and_pdl_generators_agree(cuda):
     params = mr.random_params(cfg, seed=3, std=0.05)
     outs = []
     for use_graph, pdl in [(False, 0), (True, 0), (True, 1)]:
-        m = _load(cfg, params, mode=gm.MODE_W4A16, max_seqs=2, max_tokens=32, kv_pages=64, max_pages_per_seq=16, use_pdl=pdl)
+        m = _load(cfg, params, mode=gm.MODE_W4A16, namespace=78, max_seqs=2, max_tokens=32, kv_pages=64, max_pages_per_seq=16, use_pdl=pdl)
         firsts = [m.prefill(s, [7 + s, 9, 11, 200])[1] for s in range(2)]
         gen = gm.Generator(m, firsts, use_graph=use_graph)
         seq = []
@@ -125,10 +134,10 @@ def test_e2e_host_fed_tokens_equal_device_fed(cuda):
 def test_quantised_weights_are_memoised_by_stable_id(cuda):
     cfg = TINY_Q
     params = mr.random_params(cfg, seed=5, std=0.05)
-    m1 = _load(cfg, params, mode=gm.MODE_W4A16, max_seqs=1, max_tokens=8, kv_pages=16, max_pages_per_seq=8)
+    m1 = _load(cfg, params, mode=gm.MODE_W4A16, namespace=77, max_seqs=1, max_tokens=8, kv_pages=16, max_pages_per_seq=8)
     s1 = m1.stats()
     assert s1["quantised_now"] == cfg.n_layers * 4 + 1
-    m2 = _load(cfg, params, mode=gm.MODE_W4A16, max_seqs=1, max_tokens=8, kv_pages=16, max_pages_per_seq=8)
+    m2 = _load(cfg, params, mode=gm.MODE_W4A16, namespace=77, max_seqs=1, max_tokens=8, kv_pages=16, max_pages_per_seq=8)
     s2 = m2.stats()
     assert s2["quantised_now"] == 0 and s2["memo_hits"] == cfg.n_layers * 4 + 1
     a = gm.generate_tokens(m1, [1, 2, 3], 5)

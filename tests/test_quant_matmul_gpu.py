@@ -40,10 +40,11 @@ def test_w8_repack_unpack_bit_exact(cuda, n, k):
     rng = np.random.default_rng(n * 3 + k)
     q = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
     s = _scales(rng, (n,))
-    packed = ops.w8a16_repack(_dev(q, cuda), _dev(s, cuda), n, k)
-    q2, s2 = ops.w8a16_unpack(packed, n, k)
-    assert np.array_equal(q2.cpu().numpy(), q)
-    assert np.array_equal(s2.cpu().numpy().view(np.uint16), s.view(np.uint16))
+    for inter in (False, True) if n % 32 == 0 else (False,):
+        packed = ops.w8a16_repack(_dev(q, cuda), _dev(s, cuda), n, k, inter)
+        q2, s2 = ops.w8a16_unpack(packed, n, k, inter)
+        assert np.array_equal(q2.cpu().numpy(), q)
+        assert np.array_equal(s2.cpu().numpy().view(np.uint16), s.view(np.uint16))
 
 
 @pytest.mark.parametrize("transposed", [False, True])
@@ -126,6 +127,14 @@ def test_w4a16_epilogues(cuda):
     want = fr.swiglu(base[:, : n // 2], base[:, n // 2:])
     assert y.shape == (m, n // 2)
     assert np.allclose(y.cpu().numpy(), want, rtol=1e-3, atol=1e-3 * max(1.0, np.abs(want).max()))
+    # same epilogue on the W8 kernel
+    q8 = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    s8 = _scales(rng, (n,))
+    base8 = qr.quant_matmul(x, qr.dequant_w8(q8, s8))
+    packed8 = ops.w8a16_repack(_dev(q8, cuda), _dev(s8, cuda), n, k, True)
+    y8 = ops.quant_matmul_w8a16(xd, packed8, m, n, k, out_f32=True, swiglu=True)
+    want8 = fr.swiglu(base8[:, : n // 2], base8[:, n // 2:])
+    assert np.allclose(y8.cpu().numpy(), want8, rtol=1e-3, atol=1e-3 * max(1.0, np.abs(want8).max()))
 
 
 def test_matmul_rejects_bad_arguments(cuda):
