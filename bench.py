@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Decode-throughput benchmark of the sm_100a backend.
+
+  python bench.py --gpus N --steps K --warmup W            (our arm; torchrun for N > 1)
+  python bench.py --impl reference --gpus N --steps K --warmup W   (CPU arm: the reference's C kernels)
+
+Workload at every N: a Ministral-3B-shaped W4A16 (group-128) GQA decoder, batch 64 requests per
+GPU, prompts of 2048 random token ids prefilled through the engine, then greedy decode; a "step"
+is one decode step of the whole batch (64 tokens per GPU). Requests are independent, so ranks
+share nothing on the data path (request-partitioned, weak scaling).
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = "ministral3b-shaped W4A16-g128 decode, batch 64/GPU, 2048-token prompts prefilled, greedy"
+PROMPT_LEN = 2048
+BATCH = 64
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid: str | None):
+        self.uuid, self.rows, self.proc = uuid, [], None
+
+    def start(self):
+        cmd = ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"]
+        if self.uuid:
+            cmd += ["-i", self.uuid]
+        try:
+            self.proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_model(gm, torch, dev, steps_total: int, use_pdl: int, prefill_chunk: int):
+    ctx = ((PROMPT_LEN + steps_total + 64 + 15) // 16) * 16
+    pages_per_seq = ctx // 16
+    cfg = gm.ModelConfig.ministral_3b(context_length=ctx, weight_mode=gm.MODE_W4A16, max_seqs=BATCH,
+                                      max_tokens=prefill_chunk, max_logit_rows=BATCH,
+                                      kv_pages=BATCH * pages_per_seq + 8, max_pages_per_seq=pages_per_seq, use_pdl=use_pdl)
+    model = gm.LoadedModel(cfg, namespace=0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0)
+    for name, shape in cfg.param_shapes().items():
+        if name.endswith("gamma"):
+            w = torch.ones(shape, dtype=torch.float32, device=dev)
+        else:
+            w = torch.empty(shape, dtype=torch.float32, device=dev).normal_(0.0, 0.02, generator=gen)
+        model.load_param(name, w)
+        del w
+    model.finalize(drop_f32_leaves=True)
+    torch.cuda.empty_cache()
+    return model, cfg
+
+
+def time_attention_kernel(ops, torch, dev, ctx_len: int, launches: int = 20):
+    """CUDA-event time of the dominant kernel (paged decode attention of ONE layer) on a synthetic
+    pool of the bench geometry; every launch streams the whole pool (> L2)."""
+    n_q, n_kv = 32, 8
+    pages_per = (ctx_len + 15) // 16
+    total = BATCH * pages_per
+    pool = torch.randn(total * n_kv * 2 * 16 * 128, dtype=torch.bfloat16, device=dev).view(torch.uint8)
+    table = torch.randperm(total, device=dev, dtype=torch.int32).view(BATCH, pages_per).contiguous()
+    q = torch.randn((BATCH, n_q, 128), dtype=torch.bfloat16, device=dev)
+    slot = torch.arange(BATCH, dtype=torch.int32, device=dev)
+    lens = torch.full((BATCH,), ctx_len, dtype=torch.int32, device=dev)
+    bucket = ((ctx_len + 511) // 512) * 512
+    from gptrs_b200 import lib
+    chunk = lib().gptrs_cuda_attention_chunk_pages(bucket, BATCH, n_kv)
+    for _ in range(3):
+        ops.paged_attention_decode(q, pool, table, slot, lens, n_q, n_kv, min(bucket, pages_per * 16), chunk_pages=chunk)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        ops.paged_attention_decode(q, pool, table, slot, lens, n_q, n_kv, min(bucket, pages_per * 16), chunk_pages=chunk)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / launches
+    alg_bytes = BATCH * ctx_len * 4096 + 2 * BATCH * n_q * 128 * 2 + BATCH * pages_per * 4
+    del pool
+    return ms, alg_bytes, chunk
+
+
+def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3):
+    """W4A16 decode GEMV over a rotating set of distinct weight matrices (working set >> L2)."""
+    nbytes = ops.w4a16_packed_bytes(n, k)
+    mats = [torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device=dev) for _ in range(n_mats)]
+    for mt in mats:  # fp16 scale bits must stay finite: overwrite the scale tail with 0x1c00-ish values
+        mt[n * k // 2:] = 0x1C
+    x = torch.randn((m, k), dtype=torch.bfloat16, device=dev)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    for mt in mats[:4]:
+        ops.quant_matmul_w4a16(x, mt, m, n, k, out=y)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        for mt in mats:
+            ops.quant_matmul_w4a16(x, mt, m, n, k, out=y)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (iters * n_mats)
+    alg = nbytes + 2 * m * k + 2 * m * n
+    return us, alg
+
+
+def run_reference_arm(args):
+    """CPU arm: the gpt.rs C backend's kernel library (oracle/_ref) driving the restated f32 decode
+    step on the host, single thread like the reference; each step is one bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import cbaseline as cb
+    lib = cb.load(prefer_reference=True)
+    vals = []
+    res = None
+    for i in range(args.warmup + args.steps):
+        res = cb.time_ministral_step_sample(lib, batch=BATCH, ctx_len=PROMPT_LEN, sample_layers=1)
+        if i >= args.warmup:
+            vals.append(res["tokens_per_s"])
+    v = sum(vals) / len(vals)
+    n = args.gpus
+    line = {
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": n,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * BATCH / v, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "CPU arm: f32 weights (the reference has no quantised path), host cores only"},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": res["cores"], "kind": res["kind"], "sample": res["sample"]},
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prefill-chunk", type=int, default=1024)
+    ap.add_argument("--pdl", type=int, default=int(os.environ.get("GPTRS_PDL", "1")))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the kernel microbenchmarks")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import numpy as np
+    import torch
+    import __graft_entry__ as entry
+    entry.load_package()
+    from gptrs_b200 import model as gm
+    from gptrs_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    steps_total = args.warmup + 2 * args.steps + 8  # device-resident loop, then the end-to-end loop
+    t_setup = time.perf_counter()
+    model, cfg = build_model(gm, torch, dev, steps_total, args.pdl, args.prefill_chunk)
+    t_weights = time.perf_counter() - t_setup
+
+    rng = np.random.default_rng(1000 + rank)
+    t0 = time.perf_counter()
+    first = []
+    for s in range(BATCH):
+        prompt = rng.integers(0, cfg.vocab, size=PROMPT_LEN)
+        _, tok = model.prefill(s, prompt, chunk=args.prefill_chunk)
+        first.append(tok)
+    t_prefill = time.perf_counter() - t0
+
+    gen = gm.Generator(model, first, use_graph=True)
+    stream = torch.cuda.ExternalStream(lib_stream(model), device=dev)
+    for _ in range(args.warmup):
+        gen.step(read_back=False)
+    gen.sync()
+
+    uuid = None
+    try:
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(dev).uuid)
+    except Exception:
+        pass
+    sampler = ClockSampler(uuid)
+    # ---- device-resident timed region ---------------------------------------------------------
+    launches0 = model.stats()["kernel_launches"]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    e0.record(stream)
+    for _ in range(args.steps):
+        gen.step(read_back=False)
+    e1.record(stream)
+    gen.sync()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = model.stats()["kernel_launches"] - launches0
+    ctx_mid = PROMPT_LEN + args.warmup + args.steps // 2
+
+    # ---- end-to-end timed region: host token ids in, sampled ids out, every step ----------------
+    cur = gen.step()  # brings the current ids to the host
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cur = gen.step(tokens_in=cur)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    clocks = sampler.stop()
+
+    t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    tokens = world * BATCH * args.steps
+    value = tokens / (ms * 1e-3)
+    e2e_value = tokens / (e2e_ms * 1e-3)
+
+    line = {
+        "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 activations x int4 weights, f32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "parallelism": f"dp{world} (request-partitioned, no collective)",
+                   "context_tokens_during_timing": [PROMPT_LEN + args.warmup, PROMPT_LEN + args.warmup + args.steps],
+                   "l2": "inputs larger than L2 (1.8 GB weights + >14 GB KV streamed per step)",
+                   "cuda_graph": True, "pdl": bool(args.pdl), "lm_head": "W4A16", "kv_cache": "paged bf16, 16-token pages",
+                   "prefill_seconds": round(t_prefill, 2), "weight_setup_seconds": round(t_weights, 2)},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": BATCH * 4, "d2h_bytes_per_step": BATCH * 4,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+
+    if rank == 0:
+        peak, peak_kind = _peaks()
+        # whole-step roofline: weight + KV bytes per step
+        w_bytes = model_weight_bytes(cfg)
+        kv_bytes = cfg.n_layers * BATCH * ctx_mid * 4096
+        step_bytes = w_bytes + kv_bytes
+        line["step_roofline"] = {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms / args.steps * 1e-3) / 1e9,
+                                 "peak_gbs": peak, "frac": step_bytes / (ms / args.steps * 1e-3) / 1e9 / peak,
+                                 "peak_kind": peak_kind}
+    if rank == 0 and not args.no_extras:
+        peak, peak_kind = _peaks()
+        del gen
+        a_ms, a_bytes, chunk = time_attention_kernel(ops, torch, dev, ctx_mid)
+        ach = a_bytes / (a_ms * 1e-3) / 1e9
+        line["roofline"] = {"kernel": "paged_attention_kernel", "bound": "hbm", "achieved": ach, "peak": peak,
+                            "unit": "GB/s", "frac": ach / peak, "traffic": NCU_TRAFFIC.get("paged_attention_kernel"),
+                            "peak_kind": f"{peak_kind} copy bandwidth", "us_per_launch": a_ms * 1e3,
+                            "algorithmic_bytes_per_launch": a_bytes, "chunk_pages": chunk,
+                            "units": f"{BATCH} sequences x {ctx_mid} tokens x 4096 B KV (one layer)"}
+        g_us, g_bytes = time_gemv(ops, torch, dev)
+        line["gemv_w4a16"] = {"shape": "M=1 N=9216 K=3072", "us_per_launch": g_us, "achieved_gbs": g_bytes / (g_us * 1e-6) / 1e9,
+                              "frac_of_peak": g_bytes / (g_us * 1e-6) / 1e9 / peak, "frac_of_nominal_8tbs": g_bytes / (g_us * 1e-6) / 8e12,
+                              "note": "64 distinct weight matrices in rotation (0.94 GB working set), back-to-back launches"}
+        g_us, g_bytes = time_gemv(ops, torch, dev, n=131072, k=3072, n_mats=4, iters=3)
+        line["gemv_w4a16_lm_head"] = {"shape": "M=1 N=131072 K=3072", "us_per_launch": g_us,
+                                      "achieved_gbs": g_bytes / (g_us * 1e-6) / 1e9, "frac_of_peak": g_bytes / (g_us * 1e-6) / 1e9 / peak}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import cbaseline as cb
+        res = cb.time_ministral_step_sample(cb.load(prefer_reference=True), batch=BATCH, ctx_len=PROMPT_LEN, sample_layers=1)
+        line["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": res["kind"],
+                                "sample": res["sample"], "host_cores_available": os.cpu_count()}
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# DRAM traffic per launch of the dominant kernel from the committed ncu capture (profiles/), scaled
+# to the bench launch by the tokens processed; None until a capture exists.
+NCU_TRAFFIC: dict = {}
+
+
+def lib_stream(model):
+    from gptrs_b200 import lib
+    return lib().gptrs_cuda_model_stream(model._h)
+
+
+def model_weight_bytes(cfg) -> int:
+    d, qkv, qd, mlp = cfg.d_model, (cfg.n_q_heads + 2 * cfg.n_kv_heads) * cfg.head_dim, cfg.n_q_heads * cfg.head_dim, cfg.d_mlp
+    per_layer = d * qkv + qd * d + 2 * d * mlp + mlp * d
+    elems = cfg.n_layers * per_layer + d * cfg.vocab
+    return elems // 2 + elems // 128 * 2
+
+
+if __name__ == "__main__":
+    main()
