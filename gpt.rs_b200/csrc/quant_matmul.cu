@@ -16,31 +16,31 @@
 //    group scale is applied to the f32 group partial sum, so dequantisation is exact,
 //  * K is split across the CTAs of a thread-block cluster; partial tiles are reduced through
 //    distributed shared memory (deterministic, no atomics, no global scratch).
-#include "common.cuh"
+#include "matmul_common.cuh"
+
+#include <cstdlib>
 
 namespace gptrs {
 
+int umma_w4a16_matmul(MatmulParams p, cudaStream_t st);  // umma_matmul.cu
+int umma_status(int* out);
+
 namespace {
 
+bool umma_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("GPTRS_DISABLE_UMMA");
+        v = (e && e[0] == '1') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 constexpr int kWarps = 8;            // warps per CTA, 16 output channels each
-constexpr int kCtaN = kWarps * 16;   // 128 output channels per CTA
+static_assert(kWarps * 16 == kCtaN, "CTA tile is 128 output channels");
 constexpr int kGroupK = 128;         // k per pipeline chunk == W4 scale group
 constexpr int kXStages = 4;          // cp.async ring depth for the activation chunks
-constexpr int kRedStride = kCtaN + 4;
 
-struct MatmulParams {
-    const __nv_bfloat16* x;  // [M][K]
-    const uint4* wq;         // tile-interleaved weights
-    const __half* scales;    // W4: [n_tiles][K/128][16]; W8: [n_tiles][16]
-    void* y;
-    const float* bias;
-    const float* residual;
-    int M, N, K;
-    int groups_per_cta;  // K range of one CTA, in 128-k groups
-    int n_split;         // cluster size along K
-    int out_f32;
-    int swiglu;
-};
 
 __device__ __forceinline__ void dequant4(uint32_t q, uint32_t (&a)[4]) {
     const __nv_bfloat162 bias = __floats2bfloat162_rn(136.f, 136.f);
@@ -239,87 +239,7 @@ quant_matmul_kernel(const MatmulParams p) {
         red[m * kRedStride + c + 8] = acc[i][2];
         red[(m + 1) * kRedStride + c + 8] = acc[i][3];
     }
-    const int S = p.n_split;
-    uint32_t my_rank = 0;
-    if (S > 1) {
-        my_rank = cluster_ctarank();
-        cluster_sync_all();
-    } else {
-        __syncthreads();
-    }
-
-    // ---- cluster reduction + epilogue: CTA r owns batch rows m with m % S == r ---------------
-    const uint32_t red_addr = smem_u32(red);
-    const int n_cta0 = blockIdx.x * kCtaN;
-    if (!p.swiglu) {
-        for (int idx = tid; idx < MPAD * 32; idx += kWarps * 32) {
-            int row = idx >> 5, c4 = idx & 31;
-            if ((row % S) != (int)my_rank) continue;
-            int m = m0 + row, n = n_cta0 + c4 * 4;
-            if (m >= p.M || n >= p.N) continue;
-            uint32_t off = (row * kRedStride + c4 * 4) * 4;
-            float4 v;
-            if (S > 1) {
-                v = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int r = 0; r < S; ++r) {
-                    float4 u = ld_dsmem_f4(map_to_cta(red_addr + off, r));
-                    v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
-                }
-            } else {
-                v = *reinterpret_cast<const float4*>(red + row * kRedStride + c4 * 4);
-            }
-            if (p.bias) {
-                float4 b = *reinterpret_cast<const float4*>(p.bias + n);
-                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-            }
-            if (p.residual) {
-                float4 b = *reinterpret_cast<const float4*>(p.residual + (size_t)m * p.N + n);
-                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-            }
-            if (p.out_f32) {
-                *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + (size_t)m * p.N + n) = v;
-            } else {
-                uint2 o = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
-                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)m * p.N + n) = o;
-            }
-        }
-    } else {
-        // Each 16-channel tile holds 8 gate rows followed by the 8 matching up rows.
-        const int NO = p.N >> 1;
-        for (int idx = tid; idx < MPAD * 16; idx += kWarps * 32) {
-            int row = idx >> 4, q = idx & 15;
-            if ((row % S) != (int)my_rank) continue;
-            int tile = q >> 1, half = q & 1;
-            int m = m0 + row, n_out = (n_cta0 >> 1) + tile * 8 + half * 4;
-            if (m >= p.M || n_out >= NO) continue;
-            int cg = tile * 16 + half * 4;
-            uint32_t off_g = (row * kRedStride + cg) * 4, off_u = off_g + 8 * 4;
-            float4 gt = make_float4(0.f, 0.f, 0.f, 0.f), up = gt;
-            if (S > 1) {
-                for (int r = 0; r < S; ++r) {
-                    float4 a = ld_dsmem_f4(map_to_cta(red_addr + off_g, r));
-                    float4 b = ld_dsmem_f4(map_to_cta(red_addr + off_u, r));
-                    gt.x += a.x; gt.y += a.y; gt.z += a.z; gt.w += a.w;
-                    up.x += b.x; up.y += b.y; up.z += b.z; up.w += b.w;
-                }
-            } else {
-                gt = *reinterpret_cast<const float4*>(red + row * kRedStride + cg);
-                up = *reinterpret_cast<const float4*>(red + row * kRedStride + cg + 8);
-            }
-            float4 v;
-            v.x = gt.x / (1.f + expf(-gt.x)) * up.x;
-            v.y = gt.y / (1.f + expf(-gt.y)) * up.y;
-            v.z = gt.z / (1.f + expf(-gt.z)) * up.z;
-            v.w = gt.w / (1.f + expf(-gt.w)) * up.w;
-            if (p.out_f32) {
-                *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + (size_t)m * NO + n_out) = v;
-            } else {
-                uint2 o = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
-                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)m * NO + n_out) = o;
-            }
-        }
-    }
-    if (S > 1) cluster_sync_all();  // keep every CTA's tile alive until all peers have read it
+    reduce_and_store_tile<MPAD>(p, red, tid, kWarps * 32, m0, blockIdx.x * kCtaN);
 }
 
 // ---- layout conversion kernels --------------------------------------------------------------
@@ -550,12 +470,13 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
         GPTRS_REQUIRE(!(p.swiglu && (p.bias || p.residual)), "swiglu epilogue takes no bias/residual");
         GPTRS_REQUIRE(!p.swiglu || n % 32 == 0, "swiglu needs N % 32 == 0");
     }
+    cudaStream_t st = as_stream(stream);
+    if (BITS == 4 && m > 16 && umma_enabled()) return umma_w4a16_matmul(p, st);
     const int groups = (int)(k / 128);
     const int n_blocks = ceil_div(n, kCtaN);
     p.n_split = pick_split(n_blocks, groups);
     p.groups_per_cta = groups / p.n_split;
     dim3 grid(n_blocks, p.n_split, ceil_div(m, 64));
-    cudaStream_t st = as_stream(stream);
     const int64_t m_eff = m > 64 ? 64 : m;
     auto smem_for = [](int mt) {
         size_t stages = (size_t)kXStages * mt * 8 * kGroupK * 2;
@@ -654,6 +575,14 @@ int gptrs_cuda_quantize_w8(const float* d_w, int64_t k, int64_t n, int transpose
         d_w, k, n, transposed, d_q, reinterpret_cast<__half*>(d_scales));
     GPTRS_CUDA_OK(cudaGetLastError());
     return GPTRS_OK;
+}
+
+int gptrs_cuda_matmul_status(int32_t* h_status) {
+    GPTRS_REQUIRE(h_status, "null pointer");
+    int v = 0;
+    int rc = umma_status(&v);
+    *h_status = v;
+    return rc;
 }
 
 int gptrs_cuda_quant_matmul_w4a16(const void* d_x, const void* d_packed, void* d_y, int64_t m,

@@ -1,0 +1,365 @@
+// W4A16 dequant-fused matmul on the 5th-generation tensor cores (tcgen05 / TMEM) for batches
+// above 16 rows: y[M][N] = x[M][K] . dequant(W)^T.
+//
+// Same contract, weight layout and epilogues as quant_matmul.cu (functional::matmul,
+// crates/gpt-rs/src/ops/functional/linalg.rs:109-127, on quantised Linear weights).
+//
+// One CTA computes a 128 (output channels) x BN (batch rows) tile over its K range:
+//   warps 0-3  stream the packed int4 weights from HBM to registers (prefetch ring), dequantise
+//              them to bf16 (exact integer, then one bf16 multiply by the group scale) and store
+//              them into shared memory in the canonical K-major 128-byte-swizzled operand layout;
+//              afterwards they run the epilogue (TMEM -> registers -> shared tile),
+//   warp 4     issues one TMA tensor copy of the x tile [BN x 64] per stage (hardware swizzle,
+//              rows past M are zero-filled), and owns the TMEM allocation,
+//   warp 5     issues tcgen05.mma (M=128, N=BN, K=16, bf16 x bf16 -> f32 in TMEM), four per
+//              64-wide stage, and releases stages with tcgen05.commit.
+// Split-K partials of a thread-block cluster meet through distributed shared memory (shared
+// with the mma.sync kernels). Every wait on an mbarrier is bounded; on a timeout the kernel
+// records an error in *status, still frees its TMEM and leaves.
+#include <cuda.h>
+
+#include "matmul_common.cuh"
+
+namespace gptrs {
+namespace {
+
+constexpr int kStages = 4;
+constexpr int kBlockK = 64;                 // bf16 elements per 128-byte swizzle span
+constexpr int kABytes = kCtaN * 128;        // 16 KB: 128 rows x 128 bytes
+constexpr int kUmmaThreads = 192;
+constexpr int kRing = 4;                    // stages of packed weights kept in flight per thread
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    // K-major, SWIZZLE_128B: 8-row atoms of 1024 bytes (SBO = 1024), LBO unused (1), version 1.
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+            "r"(smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+// 32 lanes x 32 consecutive f32 columns of this warp's TMEM lane quarter.
+__device__ __forceinline__ void tmem_ld_32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_map, int* status) {
+    constexpr int kBBytes = BN * 128;
+    constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+    constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kStages];
+    __shared__ __align__(8) uint64_t empty_bar[kStages];
+    __shared__ __align__(8) uint64_t done_bar;
+    __shared__ uint32_t tmem_holder;
+
+    unsigned char* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + kStages * kABytes;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_cta0 = blockIdx.x * kCtaN;
+    const int m0 = blockIdx.z * BN;
+    const int n_it = p.groups_per_cta * 2;                  // 64-wide stages of this CTA
+    const int chunk0 = blockIdx.y * p.groups_per_cta * 2;   // first 64-k chunk of this CTA
+    const int chunks_total = p.K / kBlockK;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full_bar[s], 128 + 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&done_bar, 1);
+        mbar_fence_init();
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_holder)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_holder;
+    bool failed = false;
+
+    if (warp < 4) {
+        // ---------------- dequant producers: tiles 2*warp and 2*warp+1 of the CTA's 8 ------------
+        const int g = lane >> 2, t = lane & 3;
+        const int n_tiles_total = p.N >> 4;
+        const uint4* wp[2];
+        const uint32_t* sp[2];
+        bool tv[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int tile = blockIdx.x * 8 + warp * 2 + j;
+            tv[j] = tile < n_tiles_total;
+            const size_t tl = tv[j] ? tile : 0;
+            wp[j] = p.wq + (tl * chunks_total + chunk0) * 32 + lane;
+            sp[j] = reinterpret_cast<const uint32_t*>(p.scales) + (tl * (chunks_total / 2) + chunk0 / 2) * 8 + g;
+        }
+        uint4 ring[kRing][2];
+        uint32_t sring[kRing][2];
+#pragma unroll
+        for (int r = 0; r < kRing; ++r)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                ring[r][j] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // zeros after -8
+                sring[r][j] = 0;
+                if (tv[j] && r < n_it) {
+                    ring[r][j] = ldg_stream_16(wp[j] + (size_t)r * 32);
+                    sring[r][j] = __ldg(sp[j] + (r >> 1) * 8);
+                }
+            }
+        pdl_wait();
+        const __nv_bfloat162 c136 = __floats2bfloat162_rn(136.f, 136.f);
+        for (int it0 = 0; it0 < n_it && !failed; it0 += kRing) {
+#pragma unroll
+            for (int r = 0; r < kRing; ++r) {
+                const int it = it0 + r;
+                if (it < n_it && !failed) {
+                    const int s = it % kStages;
+                    if (!mbar_wait_bounded(&empty_bar[s], ((it / kStages) & 1) ^ 1)) { failed = true; }
+                    uint4 cur[2] = {ring[r][0], ring[r][1]};
+                    uint32_t csc[2] = {sring[r][0], sring[r][1]};
+                    if (it + kRing < n_it) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+                            if (tv[j]) {
+                                ring[r][j] = ldg_stream_16(wp[j] + (size_t)(it + kRing) * 32);
+                                sring[r][j] = __ldg(sp[j] + ((it + kRing) >> 1) * 8);
+                            }
+                    }
+                    unsigned char* a_stage = sA + s * kABytes;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const __half2 sc = *reinterpret_cast<const __half2*>(&csc[j]);
+                        const __nv_bfloat162 s_lo = __float2bfloat162_rn(__low2float(sc));
+                        const __nv_bfloat162 s_hi = __float2bfloat162_rn(__high2float(sc));
+                        const int row = (warp * 2 + j) * 16 + g;  // row & 7 == g for row and row + 8
+                        unsigned char* r_lo = a_stage + row * 128 + 4 * t;
+                        unsigned char* r_hi = r_lo + 8 * 128;
+                        const uint32_t q4[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            const uint32_t q = q4[ks];
+                            uint32_t v[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;
+                                __nv_bfloat162 d = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136);
+                                d = __hmul2(d, (i & 1) ? s_hi : s_lo);
+                                v[i] = *reinterpret_cast<uint32_t*>(&d);
+                            }
+                            const int c0 = ((2 * ks) ^ g) << 4, c1 = ((2 * ks + 1) ^ g) << 4;
+                            *reinterpret_cast<uint32_t*>(r_lo + c0) = v[0];  // row g,   k = 16ks + 2t, +1
+                            *reinterpret_cast<uint32_t*>(r_hi + c0) = v[1];  // row g+8, same k
+                            *reinterpret_cast<uint32_t*>(r_lo + c1) = v[2];  // row g,   k + 8
+                            *reinterpret_cast<uint32_t*>(r_hi + c1) = v[3];  // row g+8, k + 8
+                        }
+                    }
+                    fence_proxy_async();
+                    mbar_arrive(&full_bar[s]);
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ---------------- TMA producer for the activation tile -----------------------------------
+        pdl_wait();
+        if (lane == 0) {
+            for (int it = 0; it < n_it; ++it) {
+                const int s = it % kStages;
+                if (!mbar_wait_bounded(&empty_bar[s], ((it / kStages) & 1) ^ 1)) { failed = true; break; }
+                mbar_expect_tx(&full_bar[s], kBBytes);
+                tma_load_2d(sB + s * kBBytes, &x_map, (chunk0 + it) * kBlockK, m0, &full_bar[s]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- MMA issuer ---------------------------------------------------------------
+        pdl_wait();  // this warp later reads the residual in the epilogue
+        for (int it = 0; it < n_it; ++it) {
+            const int s = it % kStages;
+            if (!mbar_wait_bounded(&full_bar[s], (it / kStages) & 1)) { failed = true; break; }
+            tc_fence_after();
+            if (lane == 0) {
+                const uint64_t a_desc = make_smem_desc(smem_u32(sA + s * kABytes));
+                const uint64_t b_desc = make_smem_desc(smem_u32(sB + s * kBBytes));
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4)
+                    umma_bf16(tmem, a_desc + 2 * k4, b_desc + 2 * k4, kIdesc, (it > 0 || k4 > 0) ? 1u : 0u);
+                umma_commit(&empty_bar[s]);
+            }
+            __syncwarp();
+        }
+        if (lane == 0) umma_commit(&done_bar);
+        __syncwarp();
+    }
+    pdl_launch_dependents();
+
+    // ---------------- epilogue: TMEM -> registers -> shared tile [BN][kRedStride] ----------------
+    float* red = reinterpret_cast<float*>(smem);
+    if (warp < 4) {
+        if (!mbar_wait_bounded(&done_bar, 0)) failed = true;
+        tc_fence_after();
+        const int col = warp * 32 + lane;  // output channel within the CTA tile == TMEM lane
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            float v[32];
+            tmem_ld_32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) red[(c0 + i) * kRedStride + col] = v[i];
+        }
+    }
+    if (failed && lane == 0) atomicExch(status, 3);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+    reduce_and_store_tile<BN>(p, red, tid, kUmmaThreads, m0, n_cta0);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+int* umma_status_word() {
+    static int* d = nullptr;
+    if (!d) {
+        if (cudaMalloc(&d, sizeof(int)) != cudaSuccess) return nullptr;
+        cudaMemset(d, 0, sizeof(int));
+    }
+    return d;
+}
+
+template <int BN>
+int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(GPTRS_EXECUTION, "cuTensorMapEncodeTiled is not available");
+    CUtensorMap map;
+    cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.M};
+    cuuint64_t strides[1] = {(cuuint64_t)p.K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)BN};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(p.x), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(GPTRS_EXECUTION, "cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
+    int* status = umma_status_word();
+    if (!status) return fail(GPTRS_EXECUTION, "cannot allocate the status word");
+    constexpr size_t smem = (size_t)kStages * (kABytes + BN * 128) + 1024;
+    auto kern = umma_w4a16_kernel<BN>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_done = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kUmmaThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attrs[2];
+    int na = 0;
+    if (p.n_split > 1) {
+        attrs[na].id = cudaLaunchAttributeClusterDimension;
+        attrs[na].val.clusterDim.x = 1;
+        attrs[na].val.clusterDim.y = (unsigned)p.n_split;
+        attrs[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (g_use_pdl) {
+        attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = na;
+    GPTRS_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p, map, status));
+    return GPTRS_OK;
+}
+
+}  // namespace
+
+// Called by quant_matmul.cu for W4 weights when M > 16. Returns GPTRS_UNIMPLEMENTED when the
+// tensor-core path does not apply, so that the caller falls back to the mma.sync kernel.
+int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
+    const int groups = p.K / 128;
+    const int n_blocks = ceil_div(p.N, kCtaN);
+    const int target = sm_count();
+    int split = 1;
+    for (int s = 1; s <= 8; s *= 2) {
+        if (groups % s != 0) break;
+        split = s;
+        if (n_blocks * s >= target) break;
+    }
+    p.n_split = split;
+    p.groups_per_cta = groups / split;
+    if (p.M <= 64) return launch_umma<64>(p, dim3(n_blocks, split, 1), st);
+    if (p.M <= 128) return launch_umma<128>(p, dim3(n_blocks, split, 1), st);
+    return launch_umma<256>(p, dim3(n_blocks, split, ceil_div(p.M, 256)), st);
+}
+
+int umma_status(int* out) {
+    int* d = umma_status_word();
+    if (!d) return fail(GPTRS_EXECUTION, "cannot allocate the status word");
+    GPTRS_CUDA_OK(cudaMemcpy(out, d, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*out) cudaMemset(d, 0, sizeof(int));
+    return GPTRS_OK;
+}
+
+}  // namespace gptrs

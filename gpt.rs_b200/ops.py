@@ -110,6 +110,13 @@ def quant_matmul_w8a16(x, packed, m, n, k, out=None, out_f32=False, bias=None, r
     return _quant_matmul(lib().gptrs_cuda_quant_matmul_w8a16, x, packed, m, n, k, out, out_f32, bias, residual, swiglu)
 
 
+def matmul_status() -> int:
+    """Error word of the tensor-core matmul kernels (0 = ok); synchronises the device."""
+    v = ctypes.c_int32(0)
+    check(lib().gptrs_cuda_matmul_status(ctypes.byref(v)))
+    return v.value
+
+
 # ---- paged bf16 KV cache + decode attention ------------------------------------------------------
 PAGE_TOKENS = 16
 

@@ -96,13 +96,19 @@ typedef struct {
                                  silu(gate)*up with N/2 columns (activation.rs:153-160) */
 } gptrs_matmul_epilogue;
 
-/* y[M][N] = x[M][K] (bf16) . dequant(W)^T, f32 accumulate. */
+/* y[M][N] = x[M][K] (bf16) . dequant(W)^T, f32 accumulate. Up to 16 rows the group scale is
+ * applied to f32 partial sums (exact dequantisation); above 16 rows W4 weights run on the
+ * tcgen05 tensor cores with weights dequantised to bf16 (one bf16 rounding per weight). */
 int gptrs_cuda_quant_matmul_w4a16(const void* d_x_bf16, const void* d_packed, void* d_y,
                                   int64_t m, int64_t n, int64_t k,
                                   const gptrs_matmul_epilogue* epilogue, void* stream);
 int gptrs_cuda_quant_matmul_w8a16(const void* d_x_bf16, const void* d_packed, void* d_y,
                                   int64_t m, int64_t n, int64_t k,
                                   const gptrs_matmul_epilogue* epilogue, void* stream);
+
+/* Synchronises the device and returns (then clears) the error word of the tensor-core matmul
+ * kernels: 0 = ok, 3 = a bounded wait inside a kernel gave up. */
+int gptrs_cuda_matmul_status(int32_t* h_status);
 
 /* ==============================================================================================
  * Paged bf16 KV cache and decode attention (split-K flash decoding).

@@ -46,6 +46,7 @@ def load(prefer_reference: bool = True) -> ctypes.CDLL:
     lib = ctypes.CDLL(str(path))
     lib.oracle_kind.restype = ctypes.c_char_p
     lib.oracle_now_seconds.restype = ctypes.c_double
+    lib.oracle_clear_caches.restype = None
     lib.oracle_matmul_f32.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_size_t] * 3
     lib.oracle_block_decode_step.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                              ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
@@ -88,6 +89,7 @@ def time_ministral_step_sample(lib, batch=64, ctx_len=2048, n_layers_total=26, s
     extrapolates to the full step (n_layers_total blocks + lm_head for the whole batch).
     Returns dict(tokens_per_s, step_seconds, layer_seconds, head_seconds, ...)."""
     from types import SimpleNamespace
+    lib.oracle_clear_caches()
     rng = np.random.default_rng(seed)
     cfg = SimpleNamespace(kind="ministral", d_model=d_model, n_q=n_q, n_kv=n_kv, hd=hd, d_mlp=d_mlp, rot=hd, eps=1e-5)
     qkvw = (n_q + 2 * n_kv) * hd

@@ -51,11 +51,24 @@ static gpt_rs_bpack_cache* cache_for(const float* b) {
     return &g_caches[g_n_caches++];
 }
 const char* oracle_kind(void) { return "reference"; }
+/* The pack cache is keyed by the weight pointer: call this whenever weight buffers are replaced. */
+void oracle_clear_caches(void) {
+    for (int i = 0; i < g_n_caches; ++i) {
+        if (g_caches[i].bpack) gpt_rs_aligned_free(g_caches[i].bpack);
+        if (g_caches[i].bpack32) gpt_rs_aligned_free(g_caches[i].bpack32);
+        if (g_caches[i].bpack64) gpt_rs_aligned_free(g_caches[i].bpack64);
+    }
+    g_n_caches = 0;
+}
 void oracle_matmul_f32(const float* a, const float* b, float* c, size_t m, size_t n, size_t k) {
+    gpt_rs_c_matmul_f32(a, b, c, m, n, k);
+}
+static void matmul_w(const float* a, const float* b, float* c, size_t m, size_t n, size_t k) {
     gpt_rs_c_matmul_f32_cached_b(a, b, c, m, n, k, cache_for(b));
 }
 #else
 const char* oracle_kind(void) { return "port"; }
+void oracle_clear_caches(void) {}
 /* c[m][n] = a[m][k] . b[k][n]; i-k-j order so the inner loop streams rows of b and c. */
 void oracle_matmul_f32(const float* a, const float* b, float* c, size_t m, size_t n, size_t k) {
     memset(c, 0, m * n * sizeof(float));
@@ -72,6 +85,7 @@ void oracle_matmul_f32(const float* a, const float* b, float* c, size_t m, size_
         }
     }
 }
+#define matmul_w oracle_matmul_f32
 #endif
 
 static void add_bias(float* x, const float* b, size_t rows, size_t n) {
@@ -166,7 +180,7 @@ int oracle_block_decode_step(const oracle_layer* L, float* hidden, float* kc, fl
     if (!xn || !qkv || !ctx || !tmp || !h1 || !h2 || !scores) return -1;
     if (L->kind == 0) oracle_layer_norm(hidden, L->ln1_g, L->ln1_b, L->eps, xn, batch, d);
     else oracle_rms_norm(hidden, L->ln1_g, L->eps, xn, batch, d);
-    oracle_matmul_f32(xn, L->w_qkv, qkv, batch, qkvw, d);
+    matmul_w(xn, L->w_qkv, qkv, batch, qkvw, d);
     add_bias(qkv, L->b_qkv, batch, qkvw);
     const size_t cache_seq = (size_t)L->n_kv * cap * L->hd;
     for (int b = 0; b < batch; ++b) {
@@ -187,12 +201,12 @@ int oracle_block_decode_step(const oracle_layer* L, float* hidden, float* kc, fl
         attention_decode(row, kc + b * cache_seq, vc + b * cache_seq, pos[b], cap, L->n_q, L->n_kv, L->hd,
                          ctx + (size_t)b * qd, scores);
     }
-    oracle_matmul_f32(ctx, L->w_out, tmp, batch, d, qd);
+    matmul_w(ctx, L->w_out, tmp, batch, d, qd);
     add_bias(tmp, L->b_out, batch, d);
     for (size_t i = 0; i < (size_t)batch * d; ++i) hidden[i] += tmp[i];
     if (L->kind == 0) {
         oracle_layer_norm(hidden, L->ln2_g, L->ln2_b, L->eps, xn, batch, d);
-        oracle_matmul_f32(xn, L->w_in, h1, batch, mlp, d);
+        matmul_w(xn, L->w_in, h1, batch, mlp, d);
         add_bias(h1, L->b_in, batch, mlp);
         for (size_t i = 0; i < (size_t)batch * mlp; ++i) {
             const float x = h1[i];
@@ -200,14 +214,14 @@ int oracle_block_decode_step(const oracle_layer* L, float* hidden, float* kc, fl
         }
     } else {
         oracle_rms_norm(hidden, L->ln2_g, L->eps, xn, batch, d);
-        oracle_matmul_f32(xn, L->w_gate, h1, batch, mlp, d);
-        oracle_matmul_f32(xn, L->w_up, h2, batch, mlp, d);
+        matmul_w(xn, L->w_gate, h1, batch, mlp, d);
+        matmul_w(xn, L->w_up, h2, batch, mlp, d);
         for (size_t i = 0; i < (size_t)batch * mlp; ++i) {
             const float g = h1[i];
             h1[i] = g / (1.0f + expf(-g)) * h2[i];
         }
     }
-    oracle_matmul_f32(h1, L->w_down, tmp, batch, d, mlp);
+    matmul_w(h1, L->w_down, tmp, batch, d, mlp);
     add_bias(tmp, L->b_down, batch, d);
     for (size_t i = 0; i < (size_t)batch * d; ++i) hidden[i] += tmp[i];
     free(xn); free(qkv); free(ctx); free(tmp); free(h1); free(h2); free(scores);
@@ -222,7 +236,7 @@ int oracle_head_step(int kind, const float* hidden, const float* g, const float*
     if (!xn) return -1;
     if (kind == 0) oracle_layer_norm(hidden, g, b, eps, xn, batch, d);
     else oracle_rms_norm(hidden, g, eps, xn, batch, d);
-    oracle_matmul_f32(xn, lm_head, logits, batch, vocab, d);
+    matmul_w(xn, lm_head, logits, batch, vocab, d);
     for (int r = 0; r < batch; ++r) {
         int best = 0;
         float bv = logits[(size_t)r * vocab];

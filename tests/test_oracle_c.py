@@ -53,6 +53,7 @@ def test_block_decode_step_matches_numpy_oracle(clib, kind):
         hidden = hidden + params["pos_embeddings"][5:6]
     hidden = np.ascontiguousarray(hidden, np.float32)
     want_logits = ref.forward([tok])[-1]
+    clib.oracle_clear_caches()  # the reference's pack cache is keyed by weight pointers
     L, keep = cb.make_layer(cfg, params, 0)
     cos, sin = fr.rotary_cos_sin(0, 16, max(cfg.rot, 2), cfg.theta)
     pos = np.array([5], np.int32)

@@ -88,8 +88,13 @@ def test_w4a16_matmul_matches_oracle(cuda, m, n, k):
     y = ops.quant_matmul_w4a16(xd, packed, m, n, k)
     _check(y.float().cpu().numpy(), qr.to_bf16(want))
     y32 = ops.quant_matmul_w4a16(xd, packed, m, n, k, out_f32=True)
-    # f32 output: only accumulation-order noise remains
-    assert np.allclose(y32.cpu().numpy(), want, rtol=1e-4, atol=1e-4 * max(1.0, np.abs(want).max()))
+    if m <= 16:
+        # exact dequantisation, f32 output: only accumulation-order noise remains
+        assert np.allclose(y32.cpu().numpy(), want, rtol=1e-4, atol=1e-4 * max(1.0, np.abs(want).max()))
+    else:
+        # tensor-core path: weights are rounded to bf16 once (relative 2^-9 per weight)
+        assert np.max(np.abs(y32.cpu().numpy() - want)) <= 4e-3 * max(1.0, np.abs(want).max())
+    assert ops.matmul_status() == 0
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES)
