@@ -82,49 +82,58 @@ def make_layer(cfg, params, l: int):
     return L, keep
 
 
-def time_ministral_step_sample(lib, batch=64, ctx_len=2048, n_layers_total=26, sample_layers=1, d_model=3072, n_q=32,
-                               n_kv=8, hd=128, d_mlp=9216, vocab=131072, head_rows=4, seed=0):
-    """Times `sample_layers` decoder blocks (+ lm_head on `head_rows` of the batch rows) of one
-    Ministral-3B-shaped f32 decode step at `batch` x `ctx_len` on this host, single thread, and
-    extrapolates to the full step (n_layers_total blocks + lm_head for the whole batch).
-    Returns dict(tokens_per_s, step_seconds, layer_seconds, head_seconds, ...)."""
+def time_ministral_step_sample(lib, batch=64, ctx_len=2048, n_layers_total=26, sample_rows=2, d_model=3072, n_q=32,
+                               n_kv=8, hd=128, d_mlp=9216, vocab=131072, vocab_sample=16384, seed=0, state=None):
+    """Times a bounded sample of one Ministral-3B-shaped f32 decode step of `batch` requests at context
+    `ctx_len` on this host. The reference's language-model path has no batch dimension (one sequence per
+    call, crates/gpt-rs/src/inference/mod.rs:14-21), so a batch is `batch` single-sequence steps; the
+    sample runs ONE decoder block for `sample_rows` of those sequences plus the final norm + lm_head +
+    argmax for one over `vocab_sample` of the `vocab` columns, single thread, and extrapolates linearly:
+    step = batch * (n_layers * t_block + t_head * vocab / vocab_sample).
+    `state` (returned) carries the allocated weights between calls."""
     from types import SimpleNamespace
-    lib.oracle_clear_caches()
-    rng = np.random.default_rng(seed)
-    cfg = SimpleNamespace(kind="ministral", d_model=d_model, n_q=n_q, n_kv=n_kv, hd=hd, d_mlp=d_mlp, rot=hd, eps=1e-5)
-    qkvw = (n_q + 2 * n_kv) * hd
-    n = lambda *s: (rng.standard_normal(size=s, dtype=F) * F(0.02))  # noqa: E731
-    params = {"blocks.0.norm_1.gamma": np.ones(d_model, F), "blocks.0.norm_2.gamma": np.ones(d_model, F),
-              "blocks.0.attention.w_qkv": n(d_model, qkvw), "blocks.0.attention.w_out": n(n_q * hd, d_model),
-              "blocks.0.feed_forward.w_gate": n(d_model, d_mlp), "blocks.0.feed_forward.w_up": n(d_model, d_mlp),
-              "blocks.0.feed_forward.w_down": n(d_mlp, d_model)}
-    L, keep = make_layer(cfg, params, 0)
-    cap = 1 << (ctx_len).bit_length()  # capacity bucket of a sequence holding ctx_len + 1 tokens
-    kc = rng.standard_normal(size=(batch, n_kv, cap, hd), dtype=F)
-    vc = rng.standard_normal(size=(batch, n_kv, cap, hd), dtype=F)
-    hidden = rng.standard_normal(size=(batch, d_model), dtype=F)
-    pos = np.full(batch, ctx_len, dtype=np.int32)
-    half = hd // 2
-    cos = np.ones((ctx_len + 1, half), F)
-    sin = np.zeros((ctx_len + 1, half), F)
-    # warm-up call packs the weights (the reference does this in its prepare entry)
-    lib.oracle_block_decode_step(ctypes.byref(L), _p(hidden), _p(kc), _p(vc), _p(pos), batch, cap, _p(cos), _p(sin))
+    if state is None:
+        lib.oracle_clear_caches()
+        rng = np.random.default_rng(seed)
+        cfg = SimpleNamespace(kind="ministral", d_model=d_model, n_q=n_q, n_kv=n_kv, hd=hd, d_mlp=d_mlp, rot=hd, eps=1e-5)
+        qkvw = (n_q + 2 * n_kv) * hd
+        block = rng.standard_normal(size=1 << 20, dtype=F) * F(0.02)
+        n = lambda *s: np.resize(block, s)  # noqa: E731  (values do not matter for timing; tiling is fast)
+        params = {"blocks.0.norm_1.gamma": np.ones(d_model, F), "blocks.0.norm_2.gamma": np.ones(d_model, F),
+                  "blocks.0.attention.w_qkv": n(d_model, qkvw), "blocks.0.attention.w_out": n(n_q * hd, d_model),
+                  "blocks.0.feed_forward.w_gate": n(d_model, d_mlp), "blocks.0.feed_forward.w_up": n(d_model, d_mlp),
+                  "blocks.0.feed_forward.w_down": n(d_mlp, d_model)}
+        L, keep = make_layer(cfg, params, 0)
+        cap = 1 << (ctx_len).bit_length()  # capacity bucket of a sequence holding ctx_len + 1 tokens
+        state = dict(L=L, keep=keep, cap=cap,
+                     kc=np.resize(block * F(50), (sample_rows, n_kv, cap, hd)),
+                     vc=np.resize(block * F(50), (sample_rows, n_kv, cap, hd)),
+                     hidden=rng.standard_normal(size=(sample_rows, d_model), dtype=F),
+                     pos=np.full(1, ctx_len, dtype=np.int32), cos=np.ones((ctx_len + 1, hd // 2), F),
+                     sin=np.zeros((ctx_len + 1, hd // 2), F), lm=n(d_model, vocab_sample), g=np.ones(d_model, F),
+                     logits=np.empty((1, vocab_sample), F), toks=np.empty(1, np.int32))
+        # first call packs the weights (the reference does this once in its prepare entry)
+        lib.oracle_block_decode_step(ctypes.byref(L), _p(state["hidden"]), _p(state["kc"]), _p(state["vc"]),
+                                     _p(state["pos"]), 1, cap, _p(state["cos"]), _p(state["sin"]))
+        lib.oracle_head_step(1, _p(state["hidden"]), _p(state["g"]), None, 1e-5, _p(state["lm"]), 1, d_model, vocab_sample,
+                             _p(state["logits"]), _p(state["toks"]))
+    st = state
+    cap = st["cap"]
+    seq_cache = n_kv * cap * hd * 4
     t0 = lib.oracle_now_seconds()
-    for _ in range(sample_layers):
-        rc = lib.oracle_block_decode_step(ctypes.byref(L), _p(hidden), _p(kc), _p(vc), _p(pos), batch, cap, _p(cos), _p(sin))
+    for r in range(sample_rows):
+        rc = lib.oracle_block_decode_step(ctypes.byref(st["L"]), st["hidden"].ctypes.data + r * d_model * 4,
+                                          st["kc"].ctypes.data + r * seq_cache, st["vc"].ctypes.data + r * seq_cache,
+                                          _p(st["pos"]), 1, cap, _p(st["cos"]), _p(st["sin"]))
         assert rc == 0
-    layer_s = (lib.oracle_now_seconds() - t0) / sample_layers
-    lm = n(d_model, vocab)
-    g = np.ones(d_model, F)
-    logits = np.empty((head_rows, vocab), F)
-    toks = np.empty(head_rows, np.int32)
-    lib.oracle_head_step(1, _p(hidden), _p(g), None, 1e-5, _p(lm), head_rows, d_model, vocab, _p(logits), _p(toks))
+    block_s = (lib.oracle_now_seconds() - t0) / sample_rows
     t0 = lib.oracle_now_seconds()
-    lib.oracle_head_step(1, _p(hidden), _p(g), None, 1e-5, _p(lm), head_rows, d_model, vocab, _p(logits), _p(toks))
-    head_s = (lib.oracle_now_seconds() - t0) * (batch / head_rows)
-    step_s = n_layers_total * layer_s + head_s
-    return dict(tokens_per_s=batch / step_s, step_seconds=step_s, layer_seconds=layer_s, head_seconds=head_s,
-                capacity=cap, kind=lib.oracle_kind().decode(), cores=1,
-                sample=f"{sample_layers} of {n_layers_total} decoder blocks + lm_head on {head_rows} of {batch} rows of one "
-                       f"f32 decode step (batch {batch}, context {ctx_len}, capacity bucket {cap}), single thread, "
-                       f"extrapolated to the full step")
+    lib.oracle_head_step(1, _p(st["hidden"]), _p(st["g"]), None, 1e-5, _p(st["lm"]), 1, d_model, vocab_sample,
+                         _p(st["logits"]), _p(st["toks"]))
+    head_s = (lib.oracle_now_seconds() - t0) * (vocab / vocab_sample)
+    seq_step_s = n_layers_total * block_s + head_s
+    return dict(tokens_per_s=1.0 / seq_step_s, step_seconds=batch * seq_step_s, block_seconds=block_s, head_seconds=head_s,
+                capacity=cap, kind=lib.oracle_kind().decode(), cores=1, state=st,
+                sample=f"1 of {n_layers_total} decoder blocks for {sample_rows} of {batch} sequences + final norm/lm_head/argmax "
+                       f"for 1 (lm_head on {vocab_sample} of {vocab} columns), f32, one sequence per call as the reference's model path has no batch dimension "
+                       f"(context {ctx_len}, capacity bucket {cap}), single thread, extrapolated linearly to the step")
