@@ -38,26 +38,28 @@ __device__ __forceinline__ void reduce_and_store_tile(const MatmulParams& p, flo
     } else {
         __syncthreads();
     }
-
-    // ---- cluster reduction + epilogue: CTA r owns batch rows m with m % S == r ---------------
     const uint32_t red_addr = smem_u32(red);
+    // Sum of one float4 of the tile over the cluster; all S remote loads are issued before any add.
+    auto gather = [&](uint32_t off) {
+        float4 u[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < S) u[r] = ld_dsmem_f4(map_to_cta(red_addr + off, r));
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < S) { v.x += u[r].x; v.y += u[r].y; v.z += u[r].z; v.w += u[r].w; }
+        return v;
+    };
+    const int rows_own = (MPAD - (int)my_rank + S - 1) / S;  // rows my_rank, my_rank + S, ...
     if (!p.swiglu) {
-        for (int idx = tid; idx < MPAD * 32; idx += n_threads) {
-            int row = idx >> 5, c4 = idx & 31;
-            if ((row % S) != (int)my_rank) continue;
-            int m = m0 + row, n = n_cta0 + c4 * 4;
+        for (int j = tid; j < rows_own * 32; j += n_threads) {
+            const int row = (int)my_rank + S * (j >> 5), c4 = j & 31;
+            const int m = m0 + row, n = n_cta0 + c4 * 4;
             if (m >= p.M || n >= p.N) continue;
-            uint32_t off = (row * kRedStride + c4 * 4) * 4;
             float4 v;
-            if (S > 1) {
-                v = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int r = 0; r < S; ++r) {
-                    float4 u = ld_dsmem_f4(map_to_cta(red_addr + off, r));
-                    v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
-                }
-            } else {
-                v = *reinterpret_cast<const float4*>(red + row * kRedStride + c4 * 4);
-            }
+            if (S > 1) v = gather((uint32_t)(row * kRedStride + c4 * 4) * 4);
+            else v = *reinterpret_cast<const float4*>(red + row * kRedStride + c4 * 4);
             if (p.bias) {
                 float4 b = *reinterpret_cast<const float4*>(p.bias + n);
                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
@@ -76,22 +78,16 @@ __device__ __forceinline__ void reduce_and_store_tile(const MatmulParams& p, flo
     } else {
         // Each 16-channel tile holds 8 gate rows followed by the 8 matching up rows.
         const int NO = p.N >> 1;
-        for (int idx = tid; idx < MPAD * 16; idx += n_threads) {
-            int row = idx >> 4, q = idx & 15;
-            if ((row % S) != (int)my_rank) continue;
-            int tile = q >> 1, half = q & 1;
-            int m = m0 + row, n_out = (n_cta0 >> 1) + tile * 8 + half * 4;
+        for (int j = tid; j < rows_own * 16; j += n_threads) {
+            const int row = (int)my_rank + S * (j >> 4), q = j & 15;
+            const int tile = q >> 1, half = q & 1;
+            const int m = m0 + row, n_out = (n_cta0 >> 1) + tile * 8 + half * 4;
             if (m >= p.M || n_out >= NO) continue;
-            int cg = tile * 16 + half * 4;
-            uint32_t off_g = (row * kRedStride + cg) * 4, off_u = off_g + 8 * 4;
-            float4 gt = make_float4(0.f, 0.f, 0.f, 0.f), up = gt;
+            const int cg = tile * 16 + half * 4;
+            float4 gt, up;
             if (S > 1) {
-                for (int r = 0; r < S; ++r) {
-                    float4 a = ld_dsmem_f4(map_to_cta(red_addr + off_g, r));
-                    float4 b = ld_dsmem_f4(map_to_cta(red_addr + off_u, r));
-                    gt.x += a.x; gt.y += a.y; gt.z += a.z; gt.w += a.w;
-                    up.x += b.x; up.y += b.y; up.z += b.z; up.w += b.w;
-                }
+                gt = gather((uint32_t)(row * kRedStride + cg) * 4);
+                up = gather((uint32_t)(row * kRedStride + cg + 8) * 4);
             } else {
                 gt = *reinterpret_cast<const float4*>(red + row * kRedStride + cg);
                 up = *reinterpret_cast<const float4*>(red + row * kRedStride + cg + 8);

@@ -19,6 +19,8 @@
 // running (max, sum, O) state for the GQA group's query heads and visits every 4th page of
 // the CTA's chunk; the warps' states are merged through shared memory at the end. No
 // CTA-wide synchronisation happens inside the streaming loop.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace gptrs {
@@ -29,7 +31,6 @@ constexpr int kPageTokens = 16;
 constexpr int kBlockBytes = kPageTokens * kHD * 2;  // 4096: one K or V block
 constexpr int kPageHeadBytes = 2 * kBlockBytes;     // 8192: K + V of one (page, head)
 constexpr int kAttnWarps = 4;
-constexpr int kDepth = 3;                           // stages per warp
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnParams {
@@ -48,7 +49,8 @@ struct AttnParams {
 
 __device__ __forceinline__ int swz(int tok, int chunk) { return tok * 256 + ((chunk ^ (tok & 7)) << 4); }
 
-__global__ void __launch_bounds__(kAttnWarps * 32, 2) paged_attention_kernel(const AttnParams p) {
+template <int kDepth>
+__global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_attention_kernel(const AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t full_bar[kAttnWarps][kDepth];
 
@@ -334,8 +336,15 @@ size_t gptrs_cuda_kv_pool_bytes(int64_t n_pages, int64_t n_kv_heads, int64_t hea
 }
 
 int gptrs_cuda_attention_chunk_pages(int64_t max_ctx_len, int64_t n_tokens, int64_t n_kv_heads) {
-    // Smallest power-of-two chunk (in pages, 4..128) that still yields >= 4 CTAs per SM.
-    const int64_t target = 4ll * sm_count();
+    // Largest power-of-two chunk (in pages, 4..128) that still yields enough CTAs for several
+    // waves (tail balance); GPTRS_ATTN_CTAS_PER_SM overrides the default of 16 CTAs per SM.
+    static int per_sm = 0;
+    if (per_sm == 0) {
+        const char* e = getenv("GPTRS_ATTN_CTAS_PER_SM");
+        per_sm = e ? atoi(e) : 16;
+        if (per_sm <= 0) per_sm = 16;
+    }
+    const int64_t target = (int64_t)per_sm * sm_count();
     int chunk = 128;
     while (chunk > 4) {
         int64_t splits = (max_ctx_len + chunk * kPageTokens - 1) / (chunk * kPageTokens);
@@ -403,12 +412,17 @@ int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, co
     p.T = (int)n_tokens; p.Hq = (int)n_q_heads; p.Hkv = (int)n_kv_heads;
     p.max_pages = (int)max_pages; p.chunk_pages = (int)chunk_pages; p.max_splits = (int)splits;
     p.scale_log2 = kLog2e / sqrtf((float)head_dim);
-    const size_t smem = (size_t)kAttnWarps * kDepth * kPageHeadBytes;
-    static bool attr_done = false;
-    if (!attr_done) {
-        GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_done = true;
+    static int depth = 0;
+    if (depth == 0) {
+        const char* e = getenv("GPTRS_ATTN_DEPTH");
+        depth = (e && atoi(e) == 3) ? 3 : 2;
+        GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kAttnWarps * 2 * kPageHeadBytes));
+        GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kAttnWarps * 3 * kPageHeadBytes));
     }
+    const size_t smem = (size_t)kAttnWarps * depth * kPageHeadBytes;
+    void (*attn_kernel)(AttnParams) = depth == 3 ? paged_attention_kernel<3> : paged_attention_kernel<2>;
     cudaStream_t st = as_stream(stream);
     // tokens beyond 65535 go through blockIdx.z in slabs
     for (int64_t t0 = 0; t0 < n_tokens; t0 += 65535) {
@@ -422,7 +436,7 @@ int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, co
             q.part_ml = p.part_ml + (size_t)t0 * n_q_heads * splits * 2;
         }
         q.T = (int)nt;
-        int rc = launch_kernel(paged_attention_kernel, dim3((unsigned)splits, (unsigned)n_kv_heads, (unsigned)nt),
+        int rc = launch_kernel(attn_kernel, dim3((unsigned)splits, (unsigned)n_kv_heads, (unsigned)nt),
                                dim3(kAttnWarps * 32), smem, st, 1, q);
         if (rc) return rc;
         if (splits > 1) {

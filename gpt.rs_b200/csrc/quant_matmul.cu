@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kWarps * 32, (MT >= 8) ? 1 : 2)
 quant_matmul_kernel(const MatmulParams p) {
     constexpr int MPAD = MT * 8;
     constexpr int kLoads = (BITS == 4) ? 2 : 4;   // 16-byte loads per lane per 128-k group
-    constexpr int kRing = (BITS == 4) ? 4 : 2;    // groups kept in flight per lane
+    constexpr int kRing = (BITS == 4) ? (MT <= 2 ? 6 : 4) : (MT <= 2 ? 3 : 2);  // groups kept in flight per lane
     constexpr int kStageBytes = MPAD * kGroupK * 2;
 
     extern __shared__ __align__(128) unsigned char smem[];
@@ -434,7 +434,9 @@ int launch_matmul(const MatmulParams& p, dim3 grid, size_t smem, cudaStream_t st
 }
 
 int pick_split(int n_blocks, int groups) {
-    const int target = 2 * sm_count();
+    // Smallest power-of-two K split that puts about 1.2 CTAs on every SM (each CTA should keep a
+    // long enough K range to stream); the largest valid split when even that is not enough.
+    const int target = sm_count() * 6 / 5;
     int best = 1;
     for (int s = 1; s <= 8; s *= 2) {
         if (groups % s != 0) break;

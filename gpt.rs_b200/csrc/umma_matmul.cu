@@ -5,13 +5,13 @@
 // crates/gpt-rs/src/ops/functional/linalg.rs:109-127, on quantised Linear weights).
 //
 // One CTA computes a 128 (output channels) x BN (batch rows) tile over its K range:
-//   warps 0-3  stream the packed int4 weights from HBM to registers (prefetch ring), dequantise
+//   warps 0-7  stream the packed int4 weights from HBM to registers (prefetch ring), dequantise
 //              them to bf16 (exact integer, then one bf16 multiply by the group scale) and store
 //              them into shared memory in the canonical K-major 128-byte-swizzled operand layout;
 //              afterwards they run the epilogue (TMEM -> registers -> shared tile),
-//   warp 4     issues one TMA tensor copy of the x tile [BN x 64] per stage (hardware swizzle,
+//   warp 8     issues one TMA tensor copy of the x tile [BN x 64] per stage (hardware swizzle,
 //              rows past M are zero-filled), and owns the TMEM allocation,
-//   warp 5     issues tcgen05.mma (M=128, N=BN, K=16, bf16 x bf16 -> f32 in TMEM), four per
+//   warp 9     issues tcgen05.mma (M=128, N=BN, K=16, bf16 x bf16 -> f32 in TMEM), four per
 //              64-wide stage, and releases stages with tcgen05.commit.
 // Split-K partials of a thread-block cluster meet through distributed shared memory (shared
 // with the mma.sync kernels). Every wait on an mbarrier is bounded; on a timeout the kernel
@@ -26,8 +26,9 @@ namespace {
 constexpr int kStages = 4;
 constexpr int kBlockK = 64;                 // bf16 elements per 128-byte swizzle span
 constexpr int kABytes = kCtaN * 128;        // 16 KB: 128 rows x 128 bytes
-constexpr int kUmmaThreads = 192;
-constexpr int kRing = 4;                    // stages of packed weights kept in flight per thread
+constexpr int kProducerWarps = 8;            // one 16-channel tile each
+constexpr int kUmmaThreads = (kProducerWarps + 2) * 32;
+constexpr int kRing = 8;                    // stages of packed weights kept in flight per thread
 
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     // K-major, SWIZZLE_128B: 8-row atoms of 1024 bytes (SBO = 1024), LBO unused (1), version 1.
@@ -81,7 +82,7 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t taddr, float (&v)[32]) {
 }
 
 template <int BN>
-__global__ void __launch_bounds__(kUmmaThreads, 1)
+__global__ void __launch_bounds__(kUmmaThreads, (BN <= 64) ? 2 : 1)
 umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_map, int* status) {
     constexpr int kBBytes = BN * 128;
     constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
@@ -106,13 +107,13 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full_bar[s], 128 + 1);
+            mbar_init(&full_bar[s], kProducerWarps * 32 + 1);
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(&done_bar, 1);
         mbar_fence_init();
     }
-    if (warp == 4) {
+    if (warp == kProducerWarps) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_holder)),
                      "r"(kTmemCols)
                      : "memory");
@@ -124,36 +125,29 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     const uint32_t tmem = tmem_holder;
     bool failed = false;
 
-    if (warp < 4) {
-        // ---------------- dequant producers: tiles 2*warp and 2*warp+1 of the CTA's 8 ------------
+    if (warp < kProducerWarps) {
+        // ---------------- dequant producers: warp w owns 16-channel tile w of the CTA's 8 --------
         const int g = lane >> 2, t = lane & 3;
         const int n_tiles_total = p.N >> 4;
-        const uint4* wp[2];
-        const uint32_t* sp[2];
-        bool tv[2];
+        const int tile = blockIdx.x * 8 + warp;
+        const bool tv = tile < n_tiles_total;
+        const size_t tl = tv ? tile : 0;
+        const uint4* wp = p.wq + (tl * chunks_total + chunk0) * 32 + lane;
+        const uint32_t* sp = reinterpret_cast<const uint32_t*>(p.scales) + (tl * (chunks_total / 2) + chunk0 / 2) * 8 + g;
+        uint4 ring[kRing];
+        uint32_t sring[kRing];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int tile = blockIdx.x * 8 + warp * 2 + j;
-            tv[j] = tile < n_tiles_total;
-            const size_t tl = tv[j] ? tile : 0;
-            wp[j] = p.wq + (tl * chunks_total + chunk0) * 32 + lane;
-            sp[j] = reinterpret_cast<const uint32_t*>(p.scales) + (tl * (chunks_total / 2) + chunk0 / 2) * 8 + g;
-        }
-        uint4 ring[kRing][2];
-        uint32_t sring[kRing][2];
-#pragma unroll
-        for (int r = 0; r < kRing; ++r)
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                ring[r][j] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // zeros after -8
-                sring[r][j] = 0;
-                if (tv[j] && r < n_it) {
-                    ring[r][j] = ldg_stream_16(wp[j] + (size_t)r * 32);
-                    sring[r][j] = __ldg(sp[j] + (r >> 1) * 8);
-                }
+        for (int r = 0; r < kRing; ++r) {
+            ring[r] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // zeros after -8
+            sring[r] = 0;
+            if (tv && r < n_it) {
+                ring[r] = ldg_stream_16(wp + (size_t)r * 32);
+                sring[r] = __ldg(sp + (r >> 1) * 8);
             }
+        }
         pdl_wait();
         const __nv_bfloat162 c136 = __floats2bfloat162_rn(136.f, 136.f);
+        const int row = warp * 16 + g;  // row & 7 == g for row and row + 8
         for (int it0 = 0; it0 < n_it && !failed; it0 += kRing) {
 #pragma unroll
             for (int r = 0; r < kRing; ++r) {
@@ -161,50 +155,41 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
                 if (it < n_it && !failed) {
                     const int s = it % kStages;
                     if (!mbar_wait_bounded(&empty_bar[s], ((it / kStages) & 1) ^ 1)) { failed = true; }
-                    uint4 cur[2] = {ring[r][0], ring[r][1]};
-                    uint32_t csc[2] = {sring[r][0], sring[r][1]};
-                    if (it + kRing < n_it) {
-#pragma unroll
-                        for (int j = 0; j < 2; ++j)
-                            if (tv[j]) {
-                                ring[r][j] = ldg_stream_16(wp[j] + (size_t)(it + kRing) * 32);
-                                sring[r][j] = __ldg(sp[j] + ((it + kRing) >> 1) * 8);
-                            }
+                    const uint4 cur = ring[r];
+                    const uint32_t csc = sring[r];
+                    if (tv && it + kRing < n_it) {
+                        ring[r] = ldg_stream_16(wp + (size_t)(it + kRing) * 32);
+                        sring[r] = __ldg(sp + ((it + kRing) >> 1) * 8);
                     }
-                    unsigned char* a_stage = sA + s * kABytes;
+                    const __half2 sc = *reinterpret_cast<const __half2*>(&csc);
+                    const __nv_bfloat162 s_lo = __float2bfloat162_rn(__low2float(sc));
+                    const __nv_bfloat162 s_hi = __float2bfloat162_rn(__high2float(sc));
+                    unsigned char* r_lo = sA + s * kABytes + row * 128 + 4 * t;
+                    unsigned char* r_hi = r_lo + 8 * 128;
+                    const uint32_t q4[4] = {cur.x, cur.y, cur.z, cur.w};
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const __half2 sc = *reinterpret_cast<const __half2*>(&csc[j]);
-                        const __nv_bfloat162 s_lo = __float2bfloat162_rn(__low2float(sc));
-                        const __nv_bfloat162 s_hi = __float2bfloat162_rn(__high2float(sc));
-                        const int row = (warp * 2 + j) * 16 + g;  // row & 7 == g for row and row + 8
-                        unsigned char* r_lo = a_stage + row * 128 + 4 * t;
-                        unsigned char* r_hi = r_lo + 8 * 128;
-                        const uint32_t q4[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint32_t q = q4[ks];
+                        uint32_t v[4];
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) {
-                            const uint32_t q = q4[ks];
-                            uint32_t v[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;
-                                __nv_bfloat162 d = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136);
-                                d = __hmul2(d, (i & 1) ? s_hi : s_lo);
-                                v[i] = *reinterpret_cast<uint32_t*>(&d);
-                            }
-                            const int c0 = ((2 * ks) ^ g) << 4, c1 = ((2 * ks + 1) ^ g) << 4;
-                            *reinterpret_cast<uint32_t*>(r_lo + c0) = v[0];  // row g,   k = 16ks + 2t, +1
-                            *reinterpret_cast<uint32_t*>(r_hi + c0) = v[1];  // row g+8, same k
-                            *reinterpret_cast<uint32_t*>(r_lo + c1) = v[2];  // row g,   k + 8
-                            *reinterpret_cast<uint32_t*>(r_hi + c1) = v[3];  // row g+8, k + 8
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;
+                            __nv_bfloat162 d = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136);
+                            d = __hmul2(d, (i & 1) ? s_hi : s_lo);
+                            v[i] = *reinterpret_cast<uint32_t*>(&d);
                         }
+                        const int c0 = ((2 * ks) ^ g) << 4, c1 = ((2 * ks + 1) ^ g) << 4;
+                        *reinterpret_cast<uint32_t*>(r_lo + c0) = v[0];  // row g,   k = 16ks + 2t, +1
+                        *reinterpret_cast<uint32_t*>(r_hi + c0) = v[1];  // row g+8, same k
+                        *reinterpret_cast<uint32_t*>(r_lo + c1) = v[2];  // row g,   k + 8
+                        *reinterpret_cast<uint32_t*>(r_hi + c1) = v[3];  // row g+8, k + 8
                     }
                     fence_proxy_async();
                     mbar_arrive(&full_bar[s]);
                 }
             }
         }
-    } else if (warp == 4) {
+    } else if (warp == kProducerWarps) {
         // ---------------- TMA producer for the activation tile -----------------------------------
         pdl_wait();
         if (lane == 0) {
@@ -240,14 +225,17 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
 
     // ---------------- epilogue: TMEM -> registers -> shared tile [BN][kRedStride] ----------------
     float* red = reinterpret_cast<float*>(smem);
-    if (warp < 4) {
+    if (warp < kProducerWarps) {
         if (!mbar_wait_bounded(&done_bar, 0)) failed = true;
         tc_fence_after();
-        const int col = warp * 32 + lane;  // output channel within the CTA tile == TMEM lane
+        // warp w reads TMEM lanes 32*(w % 4); warps 0-3 take the low half of the columns, 4-7 the high half
+        const int quarter = warp & 3;
+        const int col = quarter * 32 + lane;  // output channel within the CTA tile == TMEM lane
+        const int c_begin = (warp >> 2) * (BN / 2), c_end = c_begin + BN / 2;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = c_begin; c0 < c_end; c0 += 32) {
             float v[32];
-            tmem_ld_32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+            tmem_ld_32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
             for (int i = 0; i < 32; ++i) red[(c0 + i) * kRedStride + col] = v[i];
         }
@@ -255,7 +243,7 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     if (failed && lane == 0) atomicExch(status, 3);
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == kProducerWarps) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
     reduce_and_store_tile<BN>(p, red, tid, kUmmaThreads, m0, n_cta0);
@@ -340,7 +328,7 @@ int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
 int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
     const int groups = p.K / 128;
     const int n_blocks = ceil_div(p.N, kCtaN);
-    const int target = sm_count();
+    const int target = sm_count() * 6 / 5;
     int split = 1;
     for (int s = 1; s <= 8; s *= 2) {
         if (groups % s != 0) break;
