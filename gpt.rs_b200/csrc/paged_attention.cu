@@ -448,6 +448,54 @@ int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, co
     return GPTRS_OK;
 }
 
+// ---- allocation-free variant ---------------------------------------------------------------------
+// Some hosts of this library may not allocate device memory themselves: a plugin running inside a
+// serving process whose memory pool is owned (and fully reserved) by the host application, or code
+// running while a CUDA graph is being captured on another stream, where cudaMalloc is not allowed.
+// For them the split partials live in this fixed array instead of a caller-provided buffer. It is
+// part of the library image: every GPU that loads the library holds these bytes until the process
+// exits.
+constexpr size_t kNoAllocScratchBytes = 8u << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_noalloc_attention_scratch[kNoAllocScratchBytes];
+
+// In host code the array's name is only a handle; the device address comes from
+// cudaGetSymbolAddress, once per device, with that device current.
+static int noalloc_scratch_address(void** out) {
+    static void* per_device[64] = {nullptr};
+    int dev = 0;
+    GPTRS_CUDA_OK(cudaGetDevice(&dev));
+    GPTRS_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
+    if (!per_device[dev]) {
+        void* ptr = nullptr;
+        GPTRS_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_attention_scratch));
+        per_device[dev] = ptr;
+    }
+    *out = per_device[dev];
+    return GPTRS_OK;
+}
+
+size_t gptrs_cuda_paged_attention_noalloc_max_scratch_bytes(void) { return kNoAllocScratchBytes; }
+
+int gptrs_cuda_paged_attention_decode_noalloc(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                              int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                              void* d_out, int32_t* d_status, int64_t n_tokens, int64_t n_q_heads,
+                                              int64_t n_kv_heads, int64_t head_dim, int64_t max_ctx_len,
+                                              int64_t chunk_pages, void* stream) {
+    GPTRS_REQUIRE(chunk_pages >= 1, "chunk_pages must be positive");
+    const size_t need = gptrs_cuda_attention_scratch_bytes(n_tokens, n_q_heads, max_ctx_len, chunk_pages);
+    if (need > kNoAllocScratchBytes)
+        return fail(GPTRS_SPEC_VIOLATION,
+                    "paged_attention_decode_noalloc: this launch needs " + std::to_string(need) +
+                        " bytes of split scratch, the built-in array holds " + std::to_string(kNoAllocScratchBytes) +
+                        "; use fewer tokens per call, a larger chunk_pages, or gptrs_cuda_paged_attention_decode");
+    void* scratch = nullptr;
+    int rc = noalloc_scratch_address(&scratch);
+    if (rc) return rc;
+    return gptrs_cuda_paged_attention_decode(d_q, d_kv_pool, d_page_table, max_pages, d_slot, d_ctx_len, d_out, scratch,
+                                             kNoAllocScratchBytes, d_status, n_tokens, n_q_heads, n_kv_heads, head_dim,
+                                             max_ctx_len, chunk_pages, stream);
+}
+
 int gptrs_cuda_kv_gather(const void* d_kv_pool, const int32_t* d_page_row, int64_t n_tokens, int64_t n_kv_heads,
                          int64_t head_dim, void* d_k_out, void* d_v_out, void* stream) {
     GPTRS_REQUIRE(d_kv_pool && d_page_row && d_k_out && d_v_out, "null pointer");

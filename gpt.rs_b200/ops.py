@@ -159,6 +159,16 @@ def paged_attention_decode(q, kv_pool, page_table, slot, ctx_len, n_q, n_kv, max
     return out, status
 
 
+def paged_attention_decode_noalloc(q, kv_pool, page_table, slot, ctx_len, n_q, n_kv, max_ctx_len, out, status,
+                                   chunk_pages, head_dim=128):
+    """Allocation-free variant: the caller passes `out` and `status`; the split partials live in a fixed
+    array inside the library (see gptrs_cuda_paged_attention_decode_noalloc). Nothing is allocated here."""
+    check(lib().gptrs_cuda_paged_attention_decode_noalloc(_ptr(q), _ptr(kv_pool), _ptr(page_table), page_table.shape[1],
+                                                          _ptr(slot), _ptr(ctx_len), _ptr(out), _ptr(status), q.shape[0],
+                                                          n_q, n_kv, head_dim, max_ctx_len, chunk_pages, _stream()))
+    return out
+
+
 def kv_gather(kv_pool, page_row, n_tokens, n_kv, head_dim=128):
     k = torch.empty((n_tokens, n_kv, head_dim), dtype=torch.bfloat16, device=kv_pool.device)
     v = torch.empty_like(k)

@@ -145,6 +145,27 @@ int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, co
                                       int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
                                       int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
                                       void* stream);
+/* Allocation-free variant of gptrs_cuda_paged_attention_decode. It has no counterpart in gpt.rs.
+ * It exists for callers that cannot allocate device memory themselves: a plugin inside a serving
+ * process whose device memory pool belongs to the host application, or a caller that is in the
+ * middle of work during which cudaMalloc is not permitted. Instead of a caller-provided scratch
+ * buffer, the split partials go to a fixed array inside the library image
+ * (gptrs_cuda_paged_attention_noalloc_max_scratch_bytes() = 8 MiB, resident on every GPU that
+ * loads the library until the process exits). The call allocates nothing on host or device.
+ *  - A launch whose gptrs_cuda_attention_scratch_bytes(...) exceeds the array is rejected with
+ *    GPTRS_SPEC_VIOLATION and a message naming both sizes.
+ *  - The first call on a device looks up the array's device address (once per device, with that
+ *    device current); make that first call before starting any stream capture.
+ *  - All calls share the one array and it keeps the previous call's contents. Nothing in it has to
+ *    start at zero (every partial that is read was written by the same launch), but two calls that
+ *    run concurrently on one GPU (different streams) race on it: serialise them.
+ * Inputs, outputs and the status word are passed exactly as for gptrs_cuda_paged_attention_decode. */
+size_t gptrs_cuda_paged_attention_noalloc_max_scratch_bytes(void);
+int gptrs_cuda_paged_attention_decode_noalloc(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                              int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                              void* d_out, int32_t* d_status, int64_t n_tokens, int64_t n_q_heads,
+                                              int64_t n_kv_heads, int64_t head_dim, int64_t max_ctx_len,
+                                              int64_t chunk_pages, void* stream);
 /* Copies the first n_tokens of one page-table row out of the pool into dense bf16
  * K / V [n_tokens][n_kv_heads][128] (export and test helper). */
 int gptrs_cuda_kv_gather(const void* d_kv_pool, const int32_t* d_page_row, int64_t n_tokens, int64_t n_kv_heads,
