@@ -1,0 +1,115 @@
+"""CPU: the numpy PTIR interpreter (oracle/ptir_ref.py) on programs built by gptrs_b200.ptir.
+
+Pins: the reference's dynamic slice / update clamping known answers
+(crates/gpt-rs-backend-triton/tests/dynamic_ops_gpu.rs:35-104), and that the captured op sequences
+of the functionals, interpreted op by op, equal the closed-form functionals of
+oracle/functional_ref.py and whole decode steps equal oracle/models_ref.py."""
+import json
+
+import numpy as np
+import pytest
+
+from gptrs_b200 import ptir
+from oracle import functional_ref as fr
+from oracle import models_ref as mr
+from oracle import ptir_ref as pr
+
+F32, SI32 = ptir.F32, ptir.SI32
+
+
+def _run(b, inputs):
+    prog = json.loads(b.to_json())  # through the wire form
+    return pr.run_program(prog, inputs)
+
+
+def test_dynamic_slice_clamps_like_the_reference():
+    b = ptir.Builder()
+    x = b.parameter(F32, [5])
+    s = b.parameter(SI32, [1])
+    b.set_results([x.dynamic_slice(s, [2])])
+    data = np.array([1, 2, 3, 4, 5], np.float32)
+    assert _run(b, [data, np.array([-3], np.int32)])[0].tolist() == [1, 2]
+    assert _run(b, [data, np.array([9], np.int32)])[0].tolist() == [4, 5]
+    b = ptir.Builder()
+    xi = b.parameter(SI32, [5])
+    s = b.parameter(SI32, [1])
+    b.set_results([xi.dynamic_slice(s, [2])])
+    assert _run(b, [np.array([10, 20, 30, 40, 50], np.int32), np.array([7], np.int32)])[0].tolist() == [40, 50]
+
+
+def test_dynamic_update_slice_clamps_like_the_reference():
+    b = ptir.Builder()
+    x = b.parameter(F32, [5])
+    u = b.parameter(F32, [2])
+    s = b.parameter(SI32, [1])
+    b.set_results([x.dynamic_update_slice(u, s, [2])])
+    base = np.array([10, 11, 12, 13, 14], np.float32)
+    upd = np.array([99, 88], np.float32)
+    assert _run(b, [base, upd, np.array([-2], np.int32)])[0].tolist() == [99, 88, 12, 13, 14]
+    assert _run(b, [base, upd, np.array([8], np.int32)])[0].tolist() == [10, 11, 12, 99, 88]
+
+
+def test_functional_sequences_equal_closed_forms():
+    rng = np.random.default_rng(0)
+    x = rng.uniform(-1, 1, size=(3, 16)).astype(np.float32)
+    g = rng.uniform(-1, 1, size=16).astype(np.float32)
+    be = rng.uniform(-1, 1, size=16).astype(np.float32)
+    b = ptir.Builder()
+    px, pg, pb = b.parameter(F32, [3, 16]), b.parameter(F32, [16]), b.parameter(F32, [16])
+    b.set_results([ptir.layer_norm(px, pg, pb, 1e-5), ptir.rms_norm(px, pg, 1e-5), ptir.softmax_last_axis(px),
+                   ptir.gelu(px), ptir.silu(px), ptir.swiglu(px, px * 2.0)])
+    ln, rms, sm, ge, si, sw = _run(b, [x, g, be])
+    assert np.allclose(ln, fr.layer_norm(x, g, be, 1e-5)[0], atol=1e-6)
+    assert np.allclose(rms, fr.rms_norm(x, g, 1e-5)[0], atol=1e-6)
+    assert np.allclose(sm, fr.softmax_last_dim(x), atol=1e-7)
+    assert np.allclose(ge, fr.gelu(x), atol=1e-7)
+    assert np.allclose(si, fr.silu(x), atol=1e-7)
+    assert np.allclose(sw, fr.swiglu(x, x * 2), atol=1e-6)
+
+
+def test_rope_and_decode_attention_sequences():
+    rng = np.random.default_rng(1)
+    n_q, n_kv, hd, cap, pos = 4, 2, 8, 8, 5
+    width = (n_q + 2 * n_kv) * hd
+    qkv = rng.uniform(-1, 1, size=(1, width)).astype(np.float32)
+    ck = rng.uniform(-1, 1, size=(n_kv, cap, hd)).astype(np.float32)
+    cv = rng.uniform(-1, 1, size=(n_kv, cap, hd)).astype(np.float32)
+    cos, sin = fr.rotary_cos_sin(pos, 1, hd, 1e4)
+    b = ptir.Builder()
+    pq, pc, ps = b.parameter(F32, [1, width]), b.parameter(F32, [1, hd // 2]), b.parameter(F32, [1, hd // 2])
+    pk, pv = b.parameter(F32, [n_kv, cap, hd]), b.parameter(F32, [n_kv, cap, hd])
+    pu, pqs = b.parameter(SI32, [3]), b.parameter(SI32, [1])
+    roped = ptir.apply_rope_qkv_packed(pq, pc, ps, n_q, n_kv, hd)
+    ctx, nk, nv = ptir.attention_decode_cache(roped, pk, pv, pu, pqs, n_q, n_kv, hd)
+    b.set_results([roped, ctx, nk, nv])
+    got = _run(b, [qkv, cos, sin, ck, cv, np.array([0, pos, 0], np.int32), np.array([pos], np.int32)])
+    want_rope = fr.apply_rope_qkv_packed(qkv, cos, sin, n_q, n_kv, hd)
+    want_ctx, wk, wv = fr.attention_decode_cache(want_rope, n_q, n_kv, hd, ck, cv, pos)
+    assert np.allclose(got[0], want_rope, atol=1e-6)
+    assert np.allclose(got[1], want_ctx, atol=1e-5)
+    assert np.array_equal(got[2], wk) and np.array_equal(got[3], wv)
+
+
+@pytest.mark.parametrize("kind", ["gpt", "ministral"])
+def test_decode_step_program_equals_model_oracle(kind):
+    if kind == "gpt":
+        cfg = mr.Cfg("gpt", n_layers=2, d_model=32, n_q=4, n_kv=4, hd=8, d_mlp=64, vocab=48, ctx=16)
+    else:
+        cfg = mr.Cfg("ministral", n_layers=2, d_model=32, n_q=4, n_kv=2, hd=8, d_mlp=64, vocab=48, ctx=16, rot=8, theta=1e4)
+    params = mr.random_params(cfg, seed=2, std=0.3)
+    ref = mr.RefModel(cfg, params)
+    ref.forward([3, 1, 4, 1, 5])  # prefill 5 tokens -> capacity bucket 8
+    caches = [(k.copy(), v.copy()) for k, v in ref.caches]
+    want = ref.forward([9])[-1]
+    pos, cap = 5, 8
+    b, names = ptir.decode_step_program(cfg, cap)
+    cos, sin = fr.rotary_cos_sin(pos, 1, max(cfg.rot, 2), cfg.theta)
+    feed = {"@tokens": np.array([9], np.int32), "@positions": np.array([pos], np.int32), "@cos": cos, "@sin": sin,
+            "@update_starts": np.array([0, pos, 0], np.int32), "@query_start": np.array([pos], np.int32)}
+    for l in range(cfg.n_layers):
+        feed[f"@k{l}"], feed[f"@v{l}"] = caches[l]
+    inputs = [feed[n] if n in feed else params[n] for n in names]
+    out = _run(b, inputs)
+    assert np.allclose(out[0][0], want, rtol=1e-4, atol=1e-4)
+    for l in range(cfg.n_layers):
+        assert np.allclose(out[1 + 2 * l], ref.caches[l][0], atol=1e-6)
