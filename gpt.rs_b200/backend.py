@@ -1,0 +1,109 @@
+"""Host-side mirror of `PortableBackend` (crates/gpt-rs/src/backend/spec.rs:1287-1349) over the C ABI:
+tensor handles, materialize / to_literal, run_program on PTIR JSON, the parameter resolver and the
+decode sampler. numpy arrays stand in for `TensorLiteral` (row-major little-endian bytes)."""
+from __future__ import annotations
+
+import ctypes
+import json
+
+import numpy as np
+
+from . import check, lib
+
+_DT = {np.dtype(np.float32): 0, np.dtype(np.int32): 3, np.dtype(np.bool_): 4, np.dtype(np.int8): 5, np.dtype(np.uint8): 6}
+_NP = {0: np.float32, 3: np.int32, 4: np.bool_, 5: np.int8, 6: np.uint8}
+
+
+class TensorHandle:
+    """Reference-counted device tensor (`PortableBackend::TensorHandle`: Clone = retain, Drop = release)."""
+
+    def __init__(self, ptr: int):
+        self._p = ctypes.c_void_p(ptr)
+
+    def clone(self) -> "TensorHandle":
+        lib().gptrs_cuda_tensor_retain(self._p)
+        return TensorHandle(self._p.value)
+
+    def spec(self):
+        dt, rank = ctypes.c_int(), ctypes.c_int()
+        dims = (ctypes.c_int64 * 8)()
+        check(lib().gptrs_cuda_tensor_spec(self._p, ctypes.byref(dt), ctypes.byref(rank), dims, 8))
+        return dt.value, [dims[i] for i in range(rank.value)]
+
+    def data_ptr(self) -> int:
+        return lib().gptrs_cuda_tensor_data(self._p) or 0
+
+    def __del__(self):
+        try:
+            if self._p and self._p.value:
+                lib().gptrs_cuda_tensor_release(self._p)
+                self._p = ctypes.c_void_p()
+        except Exception:
+            pass
+
+
+class CudaBackend:
+    def backend_name(self) -> str:
+        return lib().gptrs_cuda_backend_name().decode()
+
+    def materialize(self, array: np.ndarray) -> TensorHandle:
+        """materialize(TensorInit::Literal)."""
+        a = np.ascontiguousarray(array)
+        if a.ndim == 0:
+            a = a.reshape(())
+        dims = (ctypes.c_int64 * max(a.ndim, 1))(*a.shape)
+        out = ctypes.c_void_p()
+        check(lib().gptrs_cuda_materialize_literal(_DT[a.dtype], a.ndim, dims, a.ctypes.data, a.nbytes, ctypes.byref(out)))
+        return TensorHandle(out.value)
+
+    def materialize_zeroed(self, dtype, dims) -> TensorHandle:
+        """materialize(TensorInit::Zeroed)."""
+        d = (ctypes.c_int64 * max(len(dims), 1))(*dims)
+        out = ctypes.c_void_p()
+        check(lib().gptrs_cuda_materialize_zeroed(_DT[np.dtype(dtype)], len(dims), d, ctypes.byref(out)))
+        return TensorHandle(out.value)
+
+    def to_literal(self, h: TensorHandle) -> np.ndarray:
+        dt, dims = h.spec()
+        out = np.empty(dims, dtype=_NP[dt])
+        written = ctypes.c_size_t()
+        check(lib().gptrs_cuda_to_literal(h._p, out.ctypes.data, out.nbytes, ctypes.byref(written)))
+        return out
+
+    def run_program(self, program, inputs: list[TensorHandle], stream: int | None = None) -> list[TensorHandle]:
+        text = (program if isinstance(program, str) else json.dumps(program, separators=(",", ":"))).encode()
+        ins = (ctypes.c_void_p * max(len(inputs), 1))(*[h._p.value for h in inputs])
+        cap = 1024
+        outs = (ctypes.c_void_p * cap)()
+        n = ctypes.c_size_t()
+        check(lib().gptrs_cuda_run_program(text, len(text), ins, len(inputs), outs, cap, ctypes.byref(n), stream))
+        return [TensorHandle(outs[i]) for i in range(n.value)]
+
+    def run_program_stats(self) -> dict:
+        v = [ctypes.c_int64() for _ in range(4)]
+        check(lib().gptrs_cuda_run_program_stats(*[ctypes.byref(x) for x in v]))
+        return dict(zip(("plan_builds", "plan_hits", "last_launches", "last_fused"), (x.value for x in v)))
+
+    def set_fusion(self, enabled: bool):
+        check(lib().gptrs_cuda_set_fusion(int(enabled)))
+
+    # ParamResolver::{get,set}
+    def param_set(self, stable_id: int, h: TensorHandle):
+        check(lib().gptrs_cuda_param_set(stable_id & (2 ** 64 - 1), stable_id >> 64, h._p))
+
+    def param_get(self, stable_id: int):
+        out = ctypes.c_void_p()
+        check(lib().gptrs_cuda_param_get(stable_id & (2 ** 64 - 1), stable_id >> 64, ctypes.byref(out)))
+        return TensorHandle(out.value) if out.value else None
+
+    def supports_decode_sampling(self, temperature: float, top_k=None) -> bool:
+        return bool(lib().gptrs_cuda_supports_decode_sampling(float(temperature), int(top_k is not None)))
+
+    def sample_decode_token(self, logits: TensorHandle, temperature: float = 0.0, random_u=None):
+        dt, dims = logits.spec()
+        assert dt == 0 and len(dims) == 2
+        has, tok = ctypes.c_int(0), ctypes.c_uint64(0)
+        check(lib().gptrs_cuda_sample_decode_token(logits.data_ptr(), dims[0], dims[1], float(temperature),
+                                                   int(random_u is not None), float(random_u or 0.0),
+                                                   ctypes.byref(has), ctypes.byref(tok), None))
+        return int(tok.value) if has.value else None

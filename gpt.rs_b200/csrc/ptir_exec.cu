@@ -1,0 +1,864 @@
+// PortableBackend::run_program for PTIR (ptir.v0.4) programs
+// (crates/gpt-rs/src/backend/spec.rs:1325-1329; callers: GraphArena::try_execute_plan,
+// crates/gpt-rs/src/ops/graph/arena.rs:1014).
+//
+// A program arrives as serde JSON (`Program::to_json_string`, spec.rs:799-817). It is parsed once,
+// rewritten (norm / softmax / matmul+bias subgraphs -> fused kernels, the C++ counterpart of the
+// `#[ptir_pattern]` rewrites a backend installs in its pipeline's `pre` phase,
+// crates/gpt-rs/src/backend/pipeline.rs:60-119) and cached by a hash of the text: the arena re-sends the
+// byte-identical program every decode step. Execution walks the instruction list; every operation
+// is one kernel launch on device tensors (f32 / si32 / i1), no host round trips:
+// DynamicSlice / DynamicUpdateSlice read their start indices on the device and clamp them there
+// (docs/backend.md:452-474).
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "ptir_json.h"
+#include "tensor.h"
+
+namespace gptrs {
+namespace ptir {
+namespace {
+
+constexpr int kMaxRank = 8;
+
+// ---- generic strided copy: out[o_off + idx . o_str] = in[i_off + idx . i_str] over `dims` -------
+struct CopyParams {
+    const void* in;
+    void* out;
+    int rank;
+    int64_t dims[kMaxRank], i_str[kMaxRank], o_str[kMaxRank];
+    int64_t i_off, o_off, n;
+    // dynamic offsets: starts[d] (si32, device) clamped into [0, limit[d]] scales dyn_str[d]
+    const int* starts;
+    int dyn_rank;
+    int64_t dyn_limit[kMaxRank], dyn_str[kMaxRank];
+    int dyn_on_out;
+};
+
+template <typename T>
+__global__ void strided_copy_kernel(const CopyParams p) {
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.n) return;
+    int64_t dyn = 0;
+    for (int d = 0; d < p.dyn_rank; ++d) {
+        int64_t s = p.starts[d];
+        s = s < 0 ? 0 : (s > p.dyn_limit[d] ? p.dyn_limit[d] : s);
+        dyn += s * p.dyn_str[d];
+    }
+    int64_t rem = i, io = p.i_off, oo = p.o_off;
+    for (int d = p.rank - 1; d >= 0; --d) {
+        int64_t c = rem % p.dims[d];
+        rem /= p.dims[d];
+        io += c * p.i_str[d];
+        oo += c * p.o_str[d];
+    }
+    if (p.dyn_on_out) oo += dyn; else io += dyn;
+    static_cast<T*>(p.out)[oo] = static_cast<const T*>(p.in)[io];
+}
+
+enum { U_NEG, U_ABS, U_EXP, U_LOG, U_TANH, U_ERF, U_RSQRT, U_RECIP };
+enum { B_ADD, B_SUB, B_MUL, B_DIV, B_MAX, B_MIN };
+enum { C_LT, C_LE, C_EQ, C_GE, C_GT, C_NE };
+
+struct EwParams { const void* a; const void* b; const void* c; void* out; int64_t n; int op; int is_int; };
+
+__global__ void unary_kernel(const EwParams p) {
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.n) return;
+    if (p.is_int) {
+        int x = static_cast<const int*>(p.a)[i];
+        static_cast<int*>(p.out)[i] = p.op == U_NEG ? -x : (x < 0 ? -x : x);
+        return;
+    }
+    float x = static_cast<const float*>(p.a)[i], y;
+    switch (p.op) {
+        case U_NEG: y = -x; break;
+        case U_ABS: y = fabsf(x); break;
+        case U_EXP: y = expf(x); break;
+        case U_LOG: y = logf(x); break;
+        case U_TANH: y = tanhf(x); break;
+        case U_ERF: y = erff(x); break;
+        case U_RSQRT: y = 1.0f / sqrtf(x); break;
+        default: y = 1.0f / x; break;
+    }
+    static_cast<float*>(p.out)[i] = y;
+}
+
+__global__ void binary_kernel(const EwParams p) {
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.n) return;
+    if (p.is_int) {
+        int a = static_cast<const int*>(p.a)[i], b = static_cast<const int*>(p.b)[i], y;
+        switch (p.op) {
+            case B_ADD: y = a + b; break;
+            case B_SUB: y = a - b; break;
+            case B_MUL: y = a * b; break;
+            case B_DIV: y = b == 0 ? 0 : a / b; break;
+            case B_MAX: y = a > b ? a : b; break;
+            default: y = a < b ? a : b; break;
+        }
+        static_cast<int*>(p.out)[i] = y;
+        return;
+    }
+    float a = static_cast<const float*>(p.a)[i], b = static_cast<const float*>(p.b)[i], y;
+    switch (p.op) {
+        case B_ADD: y = a + b; break;
+        case B_SUB: y = a - b; break;
+        case B_MUL: y = a * b; break;
+        case B_DIV: y = a / b; break;
+        case B_MAX: y = fmaxf(a, b); break;
+        default: y = fminf(a, b); break;
+    }
+    static_cast<float*>(p.out)[i] = y;
+}
+
+__global__ void compare_kernel(const EwParams p) {
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.n) return;
+    bool r;
+    if (p.is_int) {
+        int a = static_cast<const int*>(p.a)[i], b = static_cast<const int*>(p.b)[i];
+        r = p.op == C_LT ? a < b : p.op == C_LE ? a <= b : p.op == C_EQ ? a == b : p.op == C_GE ? a >= b : p.op == C_GT ? a > b : a != b;
+    } else {
+        float a = static_cast<const float*>(p.a)[i], b = static_cast<const float*>(p.b)[i];
+        r = p.op == C_LT ? a < b : p.op == C_LE ? a <= b : p.op == C_EQ ? a == b : p.op == C_GE ? a >= b : p.op == C_GT ? a > b : a != b;
+    }
+    static_cast<uint8_t*>(p.out)[i] = r ? 1 : 0;
+}
+
+__global__ void select_kernel(const EwParams p) {  // a: pred (u8), b / c: 4-byte values
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.n) return;
+    static_cast<uint32_t*>(p.out)[i] = static_cast<const uint8_t*>(p.a)[i] ? static_cast<const uint32_t*>(p.b)[i]
+                                                                           : static_cast<const uint32_t*>(p.c)[i];
+}
+
+// op: 0 f32->si32 (truncate, saturate, NaN -> 0), 1 si32->f32, 2 i1->f32, 3 i1->si32, 4 f32->i1, 5 si32->i1
+__global__ void cast_kernel(const EwParams p) {
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.n) return;
+    switch (p.op) {
+        case 0: {
+            float x = static_cast<const float*>(p.a)[i];
+            int y = isnan(x) ? 0 : (x >= 2147483648.f ? 2147483647 : (x <= -2147483648.f ? (-2147483647 - 1) : (int)truncf(x)));
+            static_cast<int*>(p.out)[i] = y;
+            break;
+        }
+        case 1: static_cast<float*>(p.out)[i] = (float)static_cast<const int*>(p.a)[i]; break;
+        case 2: static_cast<float*>(p.out)[i] = static_cast<const uint8_t*>(p.a)[i] ? 1.f : 0.f; break;
+        case 3: static_cast<int*>(p.out)[i] = static_cast<const uint8_t*>(p.a)[i] ? 1 : 0; break;
+        case 4: static_cast<uint8_t*>(p.out)[i] = static_cast<const float*>(p.a)[i] != 0.f; break;
+        default: static_cast<uint8_t*>(p.out)[i] = static_cast<const int*>(p.a)[i] != 0; break;
+    }
+}
+
+struct ReduceParams { const void* in; void* out; int64_t outer, axis, inner; int kind; int is_int; };
+// One warp per (outer, inner) pair; lanes stride over the reduced axis.
+__global__ void reduce_kernel(const ReduceParams p) {
+    int64_t w = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (w >= p.outer * p.inner) return;
+    const int64_t o = w / p.inner, in = w % p.inner;
+    if (p.is_int) {
+        const int* x = static_cast<const int*>(p.in) + o * p.axis * p.inner + in;
+        int acc = p.kind == 0 ? 0 : (p.kind == 1 ? (-2147483647 - 1) : 2147483647);
+        for (int64_t k = lane; k < p.axis; k += 32) {
+            int v = x[k * p.inner];
+            acc = p.kind == 0 ? acc + v : (p.kind == 1 ? max(acc, v) : min(acc, v));
+        }
+        for (int s = 16; s > 0; s >>= 1) {
+            int v = __shfl_xor_sync(0xffffffffu, acc, s);
+            acc = p.kind == 0 ? acc + v : (p.kind == 1 ? max(acc, v) : min(acc, v));
+        }
+        if (lane == 0) static_cast<int*>(p.out)[w] = acc;
+        return;
+    }
+    const float* x = static_cast<const float*>(p.in) + o * p.axis * p.inner + in;
+    float acc = p.kind == 0 ? 0.f : (p.kind == 1 ? -INFINITY : INFINITY);
+    for (int64_t k = lane; k < p.axis; k += 32) {
+        float v = x[k * p.inner];
+        acc = p.kind == 0 ? acc + v : (p.kind == 1 ? fmaxf(acc, v) : fminf(acc, v));
+    }
+    for (int s = 16; s > 0; s >>= 1) {
+        float v = __shfl_xor_sync(0xffffffffu, acc, s);
+        acc = p.kind == 0 ? acc + v : (p.kind == 1 ? fmaxf(acc, v) : fminf(acc, v));
+    }
+    if (lane == 0) static_cast<float*>(p.out)[w] = acc;
+}
+
+// out[b][m][n] = sum_k A[b, m, k] * B[b, k, n] with arbitrary strides (f32); one thread per output.
+struct DotParams {
+    const float* a; const float* b; float* out;
+    int64_t nb, m, k, n;
+    int64_t a_sb, a_sm, a_sk, b_sb, b_sk, b_sn;
+};
+__global__ void dot_kernel(const DotParams p) {
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.nb * p.m * p.n) return;
+    const int64_t n = i % p.n, m = (i / p.n) % p.m, b = i / (p.n * p.m);
+    const float* a = p.a + b * p.a_sb + m * p.a_sm;
+    const float* bb = p.b + b * p.b_sb + n * p.b_sn;
+    float acc = 0.f;
+    for (int64_t k = 0; k < p.k; ++k) acc = fmaf(a[k * p.a_sk], bb[k * p.b_sk], acc);
+    p.out[i] = acc;
+}
+
+struct IotaParams { int* out; int64_t n, inner, dim; };
+__global__ void iota_kernel(const IotaParams p) {
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i < p.n) p.out[i] = (int)((i / p.inner) % p.dim);
+}
+
+struct TakeParams { const uint32_t* w; const int* idx; uint32_t* out; int64_t n_idx, row, vocab; int* status; };
+__global__ void take_kernel(const TakeParams p) {
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.n_idx * p.row) return;
+    const int64_t r = i / p.row, c = i % p.row;
+    const int id = p.idx[r];
+    if (id < 0 || id >= p.vocab) { if (c == 0) atomicExch(p.status, 2); p.out[i] = 0; return; }
+    p.out[i] = p.w[(int64_t)id * p.row + c];
+}
+
+struct GatherParams { const uint32_t* in; const int* idx; uint32_t* out; int64_t outer, axis_in, axis_out, inner; int* status; };
+__global__ void gather_kernel(const GatherParams p) {  // take_along_axis
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.outer * p.axis_out * p.inner) return;
+    const int64_t in = i % p.inner, o = i / (p.inner * p.axis_out);
+    const int id = p.idx[i];
+    if (id < 0 || id >= p.axis_in) { atomicExch(p.status, 2); p.out[i] = 0; return; }
+    p.out[i] = p.in[(o * p.axis_in + id) * p.inner + in];
+}
+
+template <typename P>
+int launch_flat(void (*k)(P), int64_t n, const P& p, cudaStream_t st) {
+    if (n <= 0) return GPTRS_OK;
+    k<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p);
+    GPTRS_CUDA_OK(cudaGetLastError());
+    return GPTRS_OK;
+}
+
+std::vector<int64_t> row_major_strides(const std::vector<int64_t>& dims) {
+    std::vector<int64_t> s(dims.size(), 1);
+    for (int i = (int)dims.size() - 2; i >= 0; --i) s[i] = s[i + 1] * dims[i + 1];
+    return s;
+}
+
+// ---- the plan --------------------------------------------------------------------------------------
+struct Plan {
+    Function fn;
+    std::unordered_map<uint32_t, int> def;       // value id -> instruction index
+    std::unordered_map<uint32_t, int> uses;      // value id -> use count (operands + results)
+    int fused = 0;
+};
+
+const Inst* def_of(const Plan& pl, const Operand& o) {
+    if (o.is_literal) return nullptr;
+    auto it = pl.def.find(o.id);
+    return it == pl.def.end() ? nullptr : &pl.fn.body[it->second];
+}
+int uses_of(const Plan& pl, uint32_t id) { auto it = pl.uses.find(id); return it == pl.uses.end() ? 0 : it->second; }
+bool is_bin(const Inst* i, const char* k) { return i && !i->dead && i->op == Op::Binary && i->sub == k; }
+bool is_un(const Inst* i, const char* k) { return i && !i->dead && i->op == Op::Unary && i->sub == k; }
+bool is_red(const Inst* i, const char* k) {
+    return i && !i->dead && i->op == Op::Reduce && i->sub == k && i->keepdims && i->a.size() == 1 &&
+           !i->operands.empty() && !i->operands[0].is_literal;
+}
+bool same_val(const Operand& a, const Operand& b) { return !a.is_literal && !b.is_literal && a.id == b.id; }
+
+// BroadcastTo chain ending in a scalar f32 literal: returns true and the value.
+bool scalar_literal(const Plan& pl, const Operand& o, float* v) {
+    const Operand* cur = &o;
+    for (int depth = 0; depth < 4; ++depth) {
+        if (cur->is_literal) {
+            if (cur->lit.dtype != GPTRS_F32 || cur->lit.numel() != 1 || cur->bytes.size() != 4) return false;
+            memcpy(v, cur->bytes.data(), 4);
+            return true;
+        }
+        const Inst* d = def_of(pl, *cur);
+        if (!d || d->op != Op::BroadcastTo || d->operands.size() != 1) return false;
+        cur = &d->operands[0];
+    }
+    return false;
+}
+
+// BroadcastTo(x.shape) of a rank-1 [D] tensor (gamma / beta): returns the source operand.
+const Operand* row_broadcast(const Plan& pl, const Operand& o, int64_t d) {
+    const Inst* b = def_of(pl, o);
+    if (!b || b->dead || b->op != Op::BroadcastTo || b->operands[0].is_literal) return nullptr;
+    auto it = pl.def.find(b->operands[0].id);
+    const TSpec* src = nullptr;
+    if (it != pl.def.end()) src = &pl.fn.body[it->second].out;
+    else
+        for (size_t i = 0; i < pl.fn.param_ids.size(); ++i)
+            if (pl.fn.param_ids[i] == b->operands[0].id) src = &pl.fn.params[i];
+    if (!src || src->dims.size() != 1 || src->dims[0] != d) return nullptr;
+    return &b->operands[0];
+}
+
+// Matches inv = Rsqrt(Add(Mul(ReduceSum(sq_src . sq_src), c), eps)) broadcast back to x's shape, where the
+// squared operand is `sq_of`. Returns eps through *eps.
+bool match_inv_scale(const Plan& pl, const Operand& o, const Operand& sq_of, int64_t n, float* eps) {
+    const Inst* bc = def_of(pl, o);
+    if (!bc || bc->dead || bc->op != Op::BroadcastTo) return false;
+    const Inst* rs = def_of(pl, bc->operands[0]);
+    if (!is_un(rs, "Rsqrt")) return false;
+    const Inst* add = def_of(pl, rs->operands[0]);
+    if (!is_bin(add, "Add")) return false;
+    for (int sw = 0; sw < 2; ++sw) {
+        const Operand& var_o = add->operands[sw];
+        const Operand& eps_o = add->operands[1 - sw];
+        float e;
+        if (!scalar_literal(pl, eps_o, &e)) continue;
+        const Inst* mul = def_of(pl, var_o);
+        if (!is_bin(mul, "Mul")) continue;
+        for (int sw2 = 0; sw2 < 2; ++sw2) {
+            float c;
+            if (!scalar_literal(pl, mul->operands[1 - sw2], &c)) continue;
+            if (fabsf(c * (float)n - 1.f) > 1e-5f) continue;
+            const Inst* red = def_of(pl, mul->operands[sw2]);
+            if (!is_red(red, "Sum")) continue;
+            const Inst* sq = def_of(pl, red->operands[0]);
+            if (!is_bin(sq, "Mul") || !same_val(sq->operands[0], sq->operands[1]) || !same_val(sq->operands[0], sq_of)) continue;
+            if (red->a[0] != (int64_t)sq->out.dims.size() - 1) continue;
+            *eps = e;
+            return true;
+        }
+    }
+    return false;
+}
+
+void count_uses(Plan& pl) {
+    pl.uses.clear();
+    pl.def.clear();
+    for (size_t i = 0; i < pl.fn.body.size(); ++i) {
+        const Inst& in = pl.fn.body[i];
+        if (in.dead) continue;
+        pl.def[in.id] = (int)i;
+        for (auto& o : in.operands)
+            if (!o.is_literal) ++pl.uses[o.id];
+    }
+    for (uint32_t r : pl.fn.result_ids) ++pl.uses[r];
+}
+
+// Marks instructions whose values are no longer used as dead (repeat to a fixed point).
+void sweep_dead(Plan& pl) {
+    for (;;) {
+        count_uses(pl);
+        bool changed = false;
+        for (auto& in : pl.fn.body)
+            if (!in.dead && uses_of(pl, in.id) == 0) { in.dead = true; changed = true; }
+        if (!changed) return;
+    }
+}
+
+// Pattern rewrites. Each replaces the anchor instruction by a fused operation; the interior
+// instructions die in sweep_dead() when nothing else uses them (so values that escape stay).
+void rewrite_pass(Plan& pl, bool rms_pass) {
+    count_uses(pl);
+    for (auto& in : pl.fn.body) {
+        if (in.dead || in.out.dtype != GPTRS_F32 || in.out.dims.empty()) continue;
+        const int64_t d = in.out.dims.back();
+        // ---- rms_norm: Mul(Mul(x, bcast(inv)), bcast(gamma)) ------------------------------------
+        if (rms_pass && is_bin(&in, "Mul")) {
+            bool done = false;
+            for (int sw = 0; sw < 2 && !done; ++sw) {
+                const Operand* gamma = row_broadcast(pl, in.operands[1 - sw], d);
+                const Inst* nrm = def_of(pl, in.operands[sw]);
+                if (!gamma || !is_bin(nrm, "Mul")) continue;
+                for (int sw2 = 0; sw2 < 2 && !done; ++sw2) {
+                    const Operand& x = nrm->operands[sw2];
+                    float eps;
+                    if (x.is_literal || !match_inv_scale(pl, nrm->operands[1 - sw2], x, d, &eps)) continue;
+                    Inst f = in;
+                    f.op = Op::FusedRmsNorm; f.f0 = eps;
+                    f.operands = {x, *gamma};
+                    in = f; ++pl.fused; done = true;
+                }
+            }
+            if (done) continue;
+        }
+        if (rms_pass) continue;
+        // ---- layer_norm: Add(Mul(Mul(centered, bcast(inv)), bcast(gamma)), bcast(beta)) -----------
+        if (is_bin(&in, "Add")) {
+            bool done = false;
+            for (int sw = 0; sw < 2 && !done; ++sw) {
+                const Operand* beta = row_broadcast(pl, in.operands[1 - sw], d);
+                const Inst* ng = def_of(pl, in.operands[sw]);
+                if (!beta || !is_bin(ng, "Mul")) continue;
+                for (int sw2 = 0; sw2 < 2 && !done; ++sw2) {
+                    const Operand* gamma = row_broadcast(pl, ng->operands[1 - sw2], d);
+                    const Inst* nrm = def_of(pl, ng->operands[sw2]);
+                    if (!gamma || !is_bin(nrm, "Mul")) continue;
+                    for (int sw3 = 0; sw3 < 2 && !done; ++sw3) {
+                        const Operand& cen_o = nrm->operands[sw3];
+                        const Inst* cen = def_of(pl, cen_o);
+                        float eps;
+                        if (!is_bin(cen, "Sub") || !match_inv_scale(pl, nrm->operands[1 - sw3], cen_o, d, &eps)) continue;
+                        // centered = Sub(x, bcast(Mul(ReduceSum(x), 1/N)))
+                        const Operand& x = cen->operands[0];
+                        const Inst* mb = def_of(pl, cen->operands[1]);
+                        if (x.is_literal || !mb || mb->op != Op::BroadcastTo) continue;
+                        const Inst* mean = def_of(pl, mb->operands[0]);
+                        if (!is_bin(mean, "Mul")) continue;
+                        bool ok = false;
+                        for (int sw4 = 0; sw4 < 2; ++sw4) {
+                            float c;
+                            const Inst* red = def_of(pl, mean->operands[sw4]);
+                            if (scalar_literal(pl, mean->operands[1 - sw4], &c) && fabsf(c * (float)d - 1.f) <= 1e-5f &&
+                                is_red(red, "Sum") && same_val(red->operands[0], x) &&
+                                red->a[0] == (int64_t)in.out.dims.size() - 1)
+                                ok = true;
+                        }
+                        if (!ok) continue;
+                        Inst f = in;
+                        f.op = Op::FusedLayerNorm; f.f0 = eps;
+                        f.operands = {x, *gamma, *beta};
+                        in = f; ++pl.fused; done = true;
+                    }
+                }
+            }
+            if (done) continue;
+            // ---- matmul + add_bias: Add(DotGeneral[2-D](x, w), bcast(bias)) ---------------------
+            for (int sw = 0; sw < 2 && !done; ++sw) {
+                const Operand* bias = row_broadcast(pl, in.operands[1 - sw], d);
+                const Inst* dot = def_of(pl, in.operands[sw]);
+                if (!bias || !dot || dot->dead || dot->op != Op::DotGeneral || in.out.dims.size() != 2) continue;
+                if (!dot->a.empty() || dot->c != std::vector<int64_t>{1} || dot->d != std::vector<int64_t>{0}) continue;
+                if (uses_of(pl, dot->id) != 1) continue;
+                Inst f = in;
+                f.op = Op::FusedMatmulBias;
+                f.operands = {dot->operands[0], dot->operands[1], *bias};
+                in = f; ++pl.fused; done = true;
+            }
+            if (done) continue;
+        }
+        // ---- softmax over the last axis: Div(e, bcast(ReduceSum(e))), e = Exp(Sub(z, bcast(ReduceMax(z))))
+        if (is_bin(&in, "Div")) {
+            const Inst* e = def_of(pl, in.operands[0]);
+            const Inst* sb = def_of(pl, in.operands[1]);
+            if (!is_un(e, "Exp") || !sb || sb->op != Op::BroadcastTo) continue;
+            const Inst* rs = def_of(pl, sb->operands[0]);
+            if (!is_red(rs, "Sum") || !same_val(rs->operands[0], in.operands[0]) || rs->a[0] != (int64_t)in.out.dims.size() - 1) continue;
+            const Inst* sub = def_of(pl, e->operands[0]);
+            if (!is_bin(sub, "Sub")) continue;
+            const Inst* mb = def_of(pl, sub->operands[1]);
+            if (!mb || mb->op != Op::BroadcastTo) continue;
+            const Inst* rm = def_of(pl, mb->operands[0]);
+            if (!is_red(rm, "Max") || !same_val(rm->operands[0], sub->operands[0]) || rm->a[0] != (int64_t)in.out.dims.size() - 1) continue;
+            Inst f = in;
+            f.op = Op::FusedSoftmax;
+            f.operands = {sub->operands[0]};
+            in = f; ++pl.fused;
+        }
+    }
+    sweep_dead(pl);
+}
+
+// layer_norm / softmax / matmul+bias first: a layer_norm contains an rms_norm-shaped subgraph.
+void rewrite(Plan& pl) {
+    rewrite_pass(pl, false);
+    rewrite_pass(pl, true);
+}
+
+// Literal operands are uploaded once per plan.
+int upload_literals(Plan& pl) {
+    for (auto& in : pl.fn.body) {
+        if (in.dead) continue;
+        for (auto& o : in.operands) {
+            if (!o.is_literal || o.device) continue;
+            Tensor* t = nullptr;
+            int rc = tensor_alloc(o.lit.dtype, (int)o.lit.dims.size(), o.lit.dims.data(), false, &t);
+            if (rc) return rc;
+            if (o.bytes.size() != t->bytes) { tensor_release(t); return fail(GPTRS_SPEC_VIOLATION, "literal byte length mismatch"); }
+            if (t->bytes && cudaMemcpy(t->data, o.bytes.data(), t->bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+                tensor_release(t);
+                return fail(GPTRS_EXECUTION, "literal upload failed");
+            }
+            o.device = t;
+        }
+    }
+    return GPTRS_OK;
+}
+
+uint64_t fnv1a(const char* s, size_t n) {
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < n; ++i) { h ^= (unsigned char)s[i]; h *= 1099511628211ull; }
+    return h;
+}
+
+std::mutex g_plan_mu;
+std::unordered_map<uint64_t, std::shared_ptr<Plan>> g_plans;
+int64_t g_plan_hits = 0, g_plan_builds = 0, g_last_launches = 0, g_last_fused = 0;
+int g_fusion_enabled = 1;
+
+int* status_word() {
+    static int* d = nullptr;
+    if (!d) { if (cudaMalloc(&d, 4) != cudaSuccess) return nullptr; cudaMemset(d, 0, 4); }
+    return d;
+}
+
+// ---- execution -------------------------------------------------------------------------------------
+struct Exec {
+    cudaStream_t st;
+    std::unordered_map<uint32_t, Tensor*> env;  // retained
+    int64_t launches = 0;
+    ~Exec() { for (auto& kv : env) tensor_release(kv.second); }
+
+    int value(const Operand& o, Tensor** out) {  // returns a retained tensor
+        if (o.is_literal) {
+            Tensor* t = static_cast<Tensor*>(o.device);
+            if (!t) return fail(GPTRS_EXECUTION, "literal was not uploaded");
+            tensor_retain(t);
+            *out = t;
+            return GPTRS_OK;
+        }
+        auto it = env.find(o.id);
+        if (it == env.end()) return fail(GPTRS_SPEC_VIOLATION, "use of undefined value %" + std::to_string(o.id));
+        tensor_retain(it->second);
+        *out = it->second;
+        return GPTRS_OK;
+    }
+};
+
+int copy_generic(Exec& ex, const Tensor* in, Tensor* out, const std::vector<int64_t>& dims, const std::vector<int64_t>& i_str,
+                 const std::vector<int64_t>& o_str, int64_t i_off, int64_t o_off, const int* starts = nullptr,
+                 const std::vector<int64_t>& dyn_limit = {}, const std::vector<int64_t>& dyn_str = {}, bool dyn_on_out = false) {
+    if (dims.size() > (size_t)kMaxRank) return fail(GPTRS_UNIMPLEMENTED, "rank above 8");
+    CopyParams p = {};
+    p.in = in->data; p.out = out->data; p.rank = (int)dims.size();
+    p.n = 1;
+    for (size_t d = 0; d < dims.size(); ++d) { p.dims[d] = dims[d]; p.i_str[d] = i_str[d]; p.o_str[d] = o_str[d]; p.n *= dims[d]; }
+    p.i_off = i_off; p.o_off = o_off;
+    p.starts = starts; p.dyn_rank = (int)dyn_limit.size(); p.dyn_on_out = dyn_on_out;
+    for (size_t d = 0; d < dyn_limit.size(); ++d) { p.dyn_limit[d] = dyn_limit[d]; p.dyn_str[d] = dyn_str[d]; }
+    ++ex.launches;
+    return dtype_size(in->dtype) == 4 ? launch_flat(strided_copy_kernel<uint32_t>, p.n, p, ex.st)
+                                      : launch_flat(strided_copy_kernel<uint8_t>, p.n, p, ex.st);
+}
+
+int exec_inst(Exec& ex, const Inst& in, std::vector<Tensor*>& ops, Tensor** result) {
+    auto unimpl = [&](const std::string& why) { return fail(GPTRS_UNIMPLEMENTED, in.name + " is not implemented: " + why); };
+    auto spec = [&](const std::string& why) { return fail(GPTRS_SPEC_VIOLATION, in.name + " (%" + std::to_string(in.id) + "): " + why); };
+    Tensor* out = nullptr;
+    auto alloc_out = [&]() { return tensor_alloc(in.out.dtype, (int)in.out.dims.size(), in.out.dims.data(), false, &out); };
+    const int64_t n_out = in.out.numel();
+    int rc = GPTRS_OK;
+    switch (in.op) {
+        case Op::Constant:
+        case Op::StopGradient:
+            tensor_retain(ops[0]);
+            *result = ops[0];
+            return GPTRS_OK;
+        case Op::Reshape: {
+            if (ops[0]->numel() != n_out) return spec("element count changes");
+            Tensor* t = new Tensor();
+            t->dtype = ops[0]->dtype; t->dims = in.out.dims; t->data = ops[0]->data; t->bytes = ops[0]->bytes;
+            t->owns = false; t->base = ops[0];
+            tensor_retain(ops[0]);
+            *result = t;
+            return GPTRS_OK;
+        }
+        case Op::Unary: case Op::Binary: case Op::Compare: case Op::Select: case Op::Cast: {
+            if ((rc = alloc_out())) return rc;
+            EwParams p = {};
+            p.n = n_out; p.out = out->data; p.a = ops[0]->data;
+            ++ex.launches;
+            if (in.op == Op::Unary) {
+                static const char* names[] = {"Neg", "Abs", "Exp", "Log", "Tanh", "Erf", "Rsqrt", "Reciprocal"};
+                p.op = -1;
+                for (int i = 0; i < 8; ++i) if (in.sub == names[i]) p.op = i;
+                p.is_int = ops[0]->dtype == GPTRS_SI32;
+                if (p.op < 0 || (p.is_int && p.op > U_ABS) || ops[0]->dtype == GPTRS_I1) { tensor_release(out); return unimpl("unary " + in.sub + " on this dtype"); }
+                rc = launch_flat(unary_kernel, p.n, p, ex.st);
+            } else if (in.op == Op::Binary || in.op == Op::Compare) {
+                if (ops[0]->dims != ops[1]->dims || ops[0]->dtype != ops[1]->dtype) { tensor_release(out); return spec("operand shapes or dtypes differ"); }
+                p.b = ops[1]->data; p.is_int = ops[0]->dtype == GPTRS_SI32;
+                if (ops[0]->dtype == GPTRS_I1) { tensor_release(out); return unimpl("i1 operands"); }
+                if (in.op == Op::Binary) {
+                    static const char* names[] = {"Add", "Sub", "Mul", "Div", "Maximum", "Minimum"};
+                    p.op = -1;
+                    for (int i = 0; i < 6; ++i) if (in.sub == names[i]) p.op = i;
+                    if (p.op < 0) { tensor_release(out); return unimpl("binary " + in.sub); }
+                    rc = launch_flat(binary_kernel, p.n, p, ex.st);
+                } else {
+                    static const char* names[] = {"Less", "LessEqual", "Equal", "GreaterEqual", "Greater", "NotEqual"};
+                    p.op = -1;
+                    for (int i = 0; i < 6; ++i) if (in.sub == names[i]) p.op = i;
+                    if (p.op < 0) { tensor_release(out); return unimpl("compare " + in.sub); }
+                    rc = launch_flat(compare_kernel, p.n, p, ex.st);
+                }
+            } else if (in.op == Op::Select) {
+                if (ops[0]->dtype != GPTRS_I1 || dtype_size(ops[1]->dtype) != 4 || ops[1]->dims != ops[2]->dims || ops[0]->dims != ops[1]->dims) {
+                    tensor_release(out); return spec("select needs an i1 predicate and equal 4-byte branches");
+                }
+                p.b = ops[1]->data; p.c = ops[2]->data;
+                rc = launch_flat(select_kernel, p.n, p, ex.st);
+            } else {
+                const int from = ops[0]->dtype, to = in.out.dtype;
+                if (from == to) { tensor_release(out); tensor_retain(ops[0]); *result = ops[0]; --ex.launches; return GPTRS_OK; }
+                p.op = from == GPTRS_F32 && to == GPTRS_SI32 ? 0 : from == GPTRS_SI32 && to == GPTRS_F32 ? 1
+                       : from == GPTRS_I1 && to == GPTRS_F32 ? 2 : from == GPTRS_I1 && to == GPTRS_SI32 ? 3
+                       : from == GPTRS_F32 && to == GPTRS_I1 ? 4 : from == GPTRS_SI32 && to == GPTRS_I1 ? 5 : -1;
+                if (p.op < 0) { tensor_release(out); return unimpl("cast between these dtypes"); }
+                rc = launch_flat(cast_kernel, p.n, p, ex.st);
+            }
+            break;
+        }
+        case Op::Transpose: case Op::BroadcastTo: case Op::Slice: case Op::DynamicSlice: {
+            if ((rc = alloc_out())) return rc;
+            const auto& od = in.out.dims;
+            std::vector<int64_t> istr = row_major_strides(ops[0]->dims), ostr = row_major_strides(od), use(od.size(), 0);
+            int64_t off = 0;
+            if (in.op == Op::Transpose) {
+                if (in.a.size() != od.size()) { tensor_release(out); return spec("perm rank mismatch"); }
+                for (size_t d = 0; d < od.size(); ++d) use[d] = istr[in.a[d]];
+            } else if (in.op == Op::BroadcastTo) {
+                const size_t shift = od.size() - ops[0]->dims.size();
+                for (size_t d = 0; d < ops[0]->dims.size(); ++d) {
+                    if (ops[0]->dims[d] != 1 && ops[0]->dims[d] != od[d + shift]) { tensor_release(out); return spec("shapes are not broadcast compatible"); }
+                    use[d + shift] = ops[0]->dims[d] == 1 ? 0 : istr[d];
+                }
+            } else if (in.op == Op::Slice) {
+                for (size_t d = 0; d < od.size(); ++d) {
+                    if (in.a[d] + in.b[d] > ops[0]->dims[d]) { tensor_release(out); return spec("slice out of bounds"); }
+                    use[d] = istr[d]; off += in.a[d] * istr[d];
+                }
+            } else {
+                if (ops[1]->dtype != GPTRS_SI32 || ops[1]->numel() != (int64_t)od.size()) { tensor_release(out); return spec("starts must be si32[rank]"); }
+                std::vector<int64_t> lim(od.size());
+                for (size_t d = 0; d < od.size(); ++d) { use[d] = istr[d]; lim[d] = ops[0]->dims[d] - in.a[d]; if (lim[d] < 0) { tensor_release(out); return spec("slice larger than operand"); } }
+                rc = copy_generic(ex, ops[0], out, od, use, ostr, 0, 0, static_cast<const int*>(ops[1]->data), lim, istr, false);
+                break;
+            }
+            rc = copy_generic(ex, ops[0], out, od, use, ostr, off, 0);
+            break;
+        }
+        case Op::DynamicUpdateSlice: {
+            if ((rc = alloc_out())) return rc;
+            if (ops[0]->dims != in.out.dims || ops[1]->dims.size() != in.out.dims.size() || ops[2]->dtype != GPTRS_SI32) { tensor_release(out); return spec("operand mismatch"); }
+            GPTRS_CUDA_OK(cudaMemcpyAsync(out->data, ops[0]->data, out->bytes, cudaMemcpyDeviceToDevice, ex.st));
+            ++ex.launches;
+            std::vector<int64_t> ostr = row_major_strides(in.out.dims), ustr = row_major_strides(ops[1]->dims), lim(in.out.dims.size());
+            for (size_t d = 0; d < lim.size(); ++d) { lim[d] = in.out.dims[d] - ops[1]->dims[d]; if (lim[d] < 0) { tensor_release(out); return spec("update larger than operand"); } }
+            rc = copy_generic(ex, ops[1], out, ops[1]->dims, ustr, ostr, 0, 0, static_cast<const int*>(ops[2]->data), lim, ostr, true);
+            break;
+        }
+        case Op::Concat: {
+            if ((rc = alloc_out())) return rc;
+            const int64_t ax = in.axis < 0 ? in.axis + (int64_t)in.out.dims.size() : in.axis;
+            std::vector<int64_t> ostr = row_major_strides(in.out.dims);
+            int64_t pos = 0;
+            for (Tensor* t : ops) {
+                if ((rc = copy_generic(ex, t, out, t->dims, row_major_strides(t->dims), ostr, 0, pos * ostr[ax]))) break;
+                pos += t->dims[ax];
+            }
+            break;
+        }
+        case Op::Iota: {
+            if ((rc = alloc_out())) return rc;
+            if (in.out.dtype != GPTRS_SI32) { tensor_release(out); return unimpl("iota dtype other than si32"); }
+            int64_t inner = 1;
+            for (size_t d = in.axis + 1; d < in.out.dims.size(); ++d) inner *= in.out.dims[d];
+            IotaParams p = {static_cast<int*>(out->data), n_out, inner, in.out.dims[in.axis]};
+            ++ex.launches;
+            rc = launch_flat(iota_kernel, n_out, p, ex.st);
+            break;
+        }
+        case Op::Take: {
+            if ((rc = alloc_out())) return rc;
+            if (ops[1]->dtype != GPTRS_SI32 || dtype_size(ops[0]->dtype) != 4 || ops[0]->dims.empty()) { tensor_release(out); return spec("take needs si32 indices and a 4-byte table"); }
+            const int64_t row = ops[0]->numel() / ops[0]->dims[0];
+            TakeParams p = {static_cast<const uint32_t*>(ops[0]->data), static_cast<const int*>(ops[1]->data),
+                            static_cast<uint32_t*>(out->data), ops[1]->numel(), row, ops[0]->dims[0], status_word()};
+            ++ex.launches;
+            rc = launch_flat(take_kernel, p.n_idx * row, p, ex.st);
+            break;
+        }
+        case Op::Gather: {
+            if ((rc = alloc_out())) return rc;
+            const int64_t ax = in.axis < 0 ? in.axis + (int64_t)ops[0]->dims.size() : in.axis;
+            if (ops[1]->dtype != GPTRS_SI32 || ops[1]->dims != in.out.dims || dtype_size(ops[0]->dtype) != 4) { tensor_release(out); return spec("gather operands"); }
+            int64_t outer = 1, inner = 1;
+            for (int64_t d = 0; d < ax; ++d) outer *= ops[0]->dims[d];
+            for (size_t d = ax + 1; d < ops[0]->dims.size(); ++d) inner *= ops[0]->dims[d];
+            GatherParams p = {static_cast<const uint32_t*>(ops[0]->data), static_cast<const int*>(ops[1]->data),
+                              static_cast<uint32_t*>(out->data), outer, ops[0]->dims[ax], in.out.dims[ax], inner, status_word()};
+            ++ex.launches;
+            rc = launch_flat(gather_kernel, n_out, p, ex.st);
+            break;
+        }
+        case Op::Reduce: {
+            if ((rc = alloc_out())) return rc;
+            if (in.a.size() != 1 || ops[0]->dtype == GPTRS_I1) { tensor_release(out); return unimpl("multi-axis or i1 reduce"); }
+            const int64_t ax = in.a[0];
+            ReduceParams p = {ops[0]->data, out->data, 1, ops[0]->dims[ax], 1, in.sub == "Sum" ? 0 : in.sub == "Max" ? 1 : 2,
+                              ops[0]->dtype == GPTRS_SI32};
+            for (int64_t d = 0; d < ax; ++d) p.outer *= ops[0]->dims[d];
+            for (size_t d = ax + 1; d < ops[0]->dims.size(); ++d) p.inner *= ops[0]->dims[d];
+            ++ex.launches;
+            rc = launch_flat(reduce_kernel, p.outer * p.inner * 32, p, ex.st);
+            break;
+        }
+        case Op::DotGeneral: {
+            if ((rc = alloc_out())) return rc;
+            const Tensor *A = ops[0], *B = ops[1];
+            if (A->dtype != GPTRS_F32 || B->dtype != GPTRS_F32) { tensor_release(out); return unimpl("dot_general on non-f32 operands"); }
+            if (in.a.size() != in.b.size() || in.c.size() != 1 || in.d.size() != 1 || in.a.size() > 1) { tensor_release(out); return unimpl("dot_general with more than one batch or contracting axis"); }
+            std::vector<int64_t> as = row_major_strides(A->dims), bs = row_major_strides(B->dims);
+            DotParams p = {};
+            p.a = static_cast<const float*>(A->data); p.b = static_cast<const float*>(B->data); p.out = static_cast<float*>(out->data);
+            p.nb = 1;
+            if (!in.a.empty()) { p.nb = A->dims[in.a[0]]; p.a_sb = as[in.a[0]]; p.b_sb = bs[in.b[0]]; if (B->dims[in.b[0]] != p.nb) { tensor_release(out); return spec("batch sizes differ"); } }
+            p.k = A->dims[in.c[0]]; p.a_sk = as[in.c[0]]; p.b_sk = bs[in.d[0]];
+            if (B->dims[in.d[0]] != p.k) { tensor_release(out); return spec("contracting sizes differ"); }
+            std::vector<int> fa, fb;
+            for (int d = 0; d < (int)A->dims.size(); ++d) if ((in.a.empty() || d != in.a[0]) && d != in.c[0]) fa.push_back(d);
+            for (int d = 0; d < (int)B->dims.size(); ++d) if ((in.b.empty() || d != in.b[0]) && d != in.d[0]) fb.push_back(d);
+            if (fa.size() > 1 || fb.size() > 1) { tensor_release(out); return unimpl("dot_general with more than one free axis per side"); }
+            p.m = fa.empty() ? 1 : A->dims[fa[0]]; p.a_sm = fa.empty() ? 0 : as[fa[0]];
+            p.n = fb.empty() ? 1 : B->dims[fb[0]]; p.b_sn = fb.empty() ? 0 : bs[fb[0]];
+            ++ex.launches;
+            if (p.nb == 1 && p.a_sk == 1 && p.a_sm == p.k && p.b_sn == 1 && p.b_sk == p.n)
+                rc = gptrs_cuda_matmul_f32(p.a, p.b, p.out, p.m, p.n, p.k, nullptr, nullptr, 0, ex.st);  // [M,K].[K,N]
+            else
+                rc = launch_flat(dot_kernel, p.nb * p.m * p.n, p, ex.st);
+            break;
+        }
+        case Op::FusedLayerNorm: case Op::FusedRmsNorm: {
+            if ((rc = alloc_out())) return rc;
+            const int64_t d = in.out.dims.back(), rows = n_out / d;
+            ++ex.launches;
+            // the fused kernels take the row in `hidden` without modifying it when no delta is given
+            rc = in.op == Op::FusedLayerNorm
+                     ? gptrs_cuda_add_layer_norm(static_cast<float*>(ops[0]->data), nullptr, GPTRS_F32, nullptr, static_cast<const float*>(ops[1]->data),
+                                                 static_cast<const float*>(ops[2]->data), in.f0, out->data, GPTRS_F32, nullptr, nullptr, rows, d, ex.st)
+                     : gptrs_cuda_add_rms_norm(static_cast<float*>(ops[0]->data), nullptr, GPTRS_F32, static_cast<const float*>(ops[1]->data), in.f0,
+                                               out->data, GPTRS_F32, nullptr, rows, d, ex.st);
+            break;
+        }
+        case Op::FusedSoftmax: {
+            if ((rc = alloc_out())) return rc;
+            const int64_t d = in.out.dims.back();
+            ++ex.launches;
+            rc = gptrs_cuda_softmax_last_dim(static_cast<const float*>(ops[0]->data), static_cast<float*>(out->data), n_out / d, d, ex.st);
+            break;
+        }
+        case Op::FusedMatmulBias: {
+            if ((rc = alloc_out())) return rc;
+            ++ex.launches;
+            rc = gptrs_cuda_matmul_f32(static_cast<const float*>(ops[0]->data), static_cast<const float*>(ops[1]->data), static_cast<float*>(out->data),
+                                       ops[0]->dims[0], ops[1]->dims[1], ops[0]->dims[1], static_cast<const float*>(ops[2]->data), nullptr, 0, ex.st);
+            break;
+        }
+        case Op::CustomCall:
+            return fail(GPTRS_UNIMPLEMENTED, "custom_call target '" + in.sub + "' is not implemented by the cuda backend");
+        default:
+            return unimpl("operation outside the decode-path subset of this backend");
+    }
+    if (rc) { tensor_release(out); return rc; }
+    *result = out;
+    return GPTRS_OK;
+}
+
+}  // namespace
+}  // namespace ptir
+}  // namespace gptrs
+
+using namespace gptrs;
+using namespace gptrs::ptir;
+
+extern "C" {
+
+int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* const* inputs, size_t n_inputs,
+                           gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs, void* stream) {
+    GPTRS_REQUIRE(program_json && n_outputs && (n_inputs == 0 || inputs), "null pointer");
+    const uint64_t key = fnv1a(program_json, len) ^ (g_fusion_enabled ? 0 : 0x5bd1e995u);
+    std::shared_ptr<Plan> plan;
+    {
+        std::lock_guard<std::mutex> lk(g_plan_mu);
+        auto it = g_plans.find(key);
+        if (it != g_plans.end()) { plan = it->second; ++g_plan_hits; }
+    }
+    if (!plan) {
+        Json root;
+        std::string err;
+        if (!parse_json(program_json, len, &root, &err)) return fail(GPTRS_SPEC_VIOLATION, "program json: " + err);
+        auto p = std::make_shared<Plan>();
+        int st = build_function(root, &p->fn, &err);
+        if (st) return fail(st == 2 ? GPTRS_UNIMPLEMENTED : GPTRS_SPEC_VIOLATION, err);
+        if (g_fusion_enabled) rewrite(*p); else count_uses(*p);
+        if (int rc = upload_literals(*p)) return rc;
+        std::lock_guard<std::mutex> lk(g_plan_mu);
+        g_plans[key] = p;
+        ++g_plan_builds;
+        plan = p;
+    }
+    const Function& fn = plan->fn;
+    GPTRS_REQUIRE(n_inputs == fn.param_ids.size(), "entry input count does not match the function parameters");
+    GPTRS_REQUIRE(outputs_cap >= fn.result_ids.size() && (outputs || fn.result_ids.empty()), "output array too small");
+    Exec ex;
+    ex.st = as_stream(stream);
+    for (size_t i = 0; i < n_inputs; ++i) {
+        Tensor* t = reinterpret_cast<Tensor*>(inputs[i]);
+        GPTRS_REQUIRE(t, "null input handle");
+        if (t->dtype != fn.params[i].dtype || t->dims != fn.params[i].dims)
+            return fail(GPTRS_SPEC_VIOLATION, "input " + std::to_string(i) + " does not match the declared parameter type");
+        tensor_retain(t);
+        ex.env[fn.param_ids[i]] = t;
+    }
+    for (const Inst& in : fn.body) {
+        if (in.dead) continue;
+        std::vector<Tensor*> ops(in.operands.size(), nullptr);
+        int rc = GPTRS_OK;
+        for (size_t i = 0; i < ops.size() && !rc; ++i) rc = ex.value(in.operands[i], &ops[i]);
+        Tensor* res = nullptr;
+        if (!rc) rc = exec_inst(ex, in, ops, &res);
+        for (Tensor* t : ops) tensor_release(t);
+        if (rc) return rc;
+        if (res->dtype != in.out.dtype || res->dims != in.out.dims) {
+            tensor_release(res);
+            return fail(GPTRS_SPEC_VIOLATION, in.name + " (%" + std::to_string(in.id) + ") produced a value that does not match its declared type");
+        }
+        ex.env[in.id] = res;
+    }
+    for (size_t i = 0; i < fn.result_ids.size(); ++i) {
+        auto it = ex.env.find(fn.result_ids[i]);
+        if (it == ex.env.end()) return fail(GPTRS_SPEC_VIOLATION, "result value is undefined");
+        tensor_retain(it->second);
+        outputs[i] = reinterpret_cast<gptrs_tensor*>(it->second);
+    }
+    *n_outputs = fn.result_ids.size();
+    g_last_launches = ex.launches;
+    g_last_fused = plan->fused;
+    // report a device-side index error (take / gather) the way ref-cpu reports it: as an error
+    int* sw = status_word();
+    if (sw) {
+        int hs = 0;
+        GPTRS_CUDA_OK(cudaMemcpyAsync(&hs, sw, 4, cudaMemcpyDeviceToHost, ex.st));
+        GPTRS_CUDA_OK(cudaStreamSynchronize(ex.st));
+        if (hs) {
+            cudaMemsetAsync(sw, 0, 4, ex.st);
+            for (size_t i = 0; i < fn.result_ids.size(); ++i) tensor_release(reinterpret_cast<Tensor*>(outputs[i]));
+            *n_outputs = 0;
+            return fail(GPTRS_EXECUTION, "index out of range in take/gather");
+        }
+    }
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_run_program_stats(int64_t* plan_builds, int64_t* plan_hits, int64_t* last_launches, int64_t* last_fused) {
+    if (plan_builds) *plan_builds = g_plan_builds;
+    if (plan_hits) *plan_hits = g_plan_hits;
+    if (last_launches) *last_launches = g_last_launches;
+    if (last_fused) *last_fused = g_last_fused;
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_set_fusion(int enabled) {
+    g_fusion_enabled = enabled ? 1 : 0;
+    return GPTRS_OK;
+}
+
+}  // extern "C"

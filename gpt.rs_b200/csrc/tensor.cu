@@ -53,7 +53,9 @@ void tensor_retain(Tensor* t) { if (t) t->refs.fetch_add(1, std::memory_order_re
 void tensor_release(Tensor* t) {
     if (t && t->refs.fetch_sub(1, std::memory_order_acq_rel) == 1) {
         if (t->data && t->owns) cudaFree(t->data);
+        Tensor* base = t->base;
         delete t;
+        tensor_release(base);
     }
 }
 

@@ -16,6 +16,7 @@ struct Tensor {
     void* data = nullptr;
     size_t bytes = 0;
     bool owns = true;
+    Tensor* base = nullptr;  // a view (Reshape) keeps the tensor that owns the storage alive
     int64_t numel() const;
 };
 

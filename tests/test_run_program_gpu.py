@@ -1,0 +1,193 @@
+"""PortableBackend::run_program on the GPU against the numpy PTIR interpreter: known answers of the
+reference's own GPU tests, every functional's captured op sequence, and whole decode-step programs,
+with the fusion rewrites on and off. f32 tolerance 1e-4 (decode logits), integer / mask ops exact."""
+import json
+
+import numpy as np
+import pytest
+
+from gptrs_b200 import BackendError, ptir
+from gptrs_b200.backend import CudaBackend
+from oracle import functional_ref as fr
+from oracle import models_ref as mr
+from oracle import ptir_ref as pr
+
+pytestmark = pytest.mark.gpu
+F32, SI32 = ptir.F32, ptir.SI32
+
+
+@pytest.fixture(scope="module")
+def be(cuda):
+    b = CudaBackend()
+    assert b.backend_name() == "cuda"
+    yield b
+    b.set_fusion(True)
+
+
+def _both(be, builder, inputs, fusion=True):
+    prog = builder.to_json()
+    want = pr.run_program(json.loads(prog), inputs)
+    be.set_fusion(fusion)
+    hs = [be.materialize(a) for a in inputs]
+    got = [be.to_literal(h) for h in be.run_program(prog, hs)]
+    assert len(got) == len(want)
+    return got, want
+
+
+def test_smoke_matmul_and_handles(be):
+    b = ptir.Builder()
+    x, w = b.parameter(F32, [2, 2]), b.parameter(F32, [2, 2])
+    b.set_results([ptir.matmul(x, w)])
+    got, _ = _both(be, b, [np.array([[1, 2], [3, 4]], np.float32), np.array([[5, 6], [7, 8]], np.float32)])
+    assert got[0].ravel().tolist() == [19.0, 22.0, 43.0, 50.0]
+    h = be.materialize(np.arange(6, dtype=np.int32).reshape(2, 3))
+    h2 = h.clone()
+    del h
+    assert be.to_literal(h2).tolist() == [[0, 1, 2], [3, 4, 5]]
+    z = be.materialize_zeroed(np.float32, [2, 2])
+    assert not be.to_literal(z).any()
+
+
+def test_dynamic_slice_and_update_known_answers(be):
+    b = ptir.Builder()
+    x, s = b.parameter(F32, [5]), b.parameter(SI32, [1])
+    b.set_results([x.dynamic_slice(s, [2])])
+    data = np.array([1, 2, 3, 4, 5], np.float32)
+    for start, want in [(-3, [1, 2]), (9, [4, 5]), (2, [3, 4])]:
+        got, _ = _both(be, b, [data, np.array([start], np.int32)])
+        assert got[0].tolist() == want
+    b = ptir.Builder()
+    x, u, s = b.parameter(F32, [5]), b.parameter(F32, [2]), b.parameter(SI32, [1])
+    b.set_results([x.dynamic_update_slice(u, s, [2])])
+    base, upd = np.array([10, 11, 12, 13, 14], np.float32), np.array([99, 88], np.float32)
+    for start, want in [(-2, [99, 88, 12, 13, 14]), (8, [10, 11, 12, 99, 88])]:
+        got, _ = _both(be, b, [base, upd, np.array([start], np.int32)])
+        assert got[0].tolist() == want
+
+
+def test_sampler_on_program_output(be):
+    b = ptir.Builder()
+    x = b.parameter(F32, [1, 4])
+    b.set_results([x * 1.0])
+    out = be.run_program(b.to_json(), [be.materialize(np.array([[-1.0, 0.1, 2.5, 0.4]], np.float32))])
+    assert be.sample_decode_token(out[0], 0.0) == 2
+    assert be.supports_decode_sampling(0.0) and not be.supports_decode_sampling(0.5, top_k=5)
+
+
+@pytest.mark.parametrize("fusion", [True, False])
+def test_functional_sequences(be, fusion):
+    rng = np.random.default_rng(0)
+    x = rng.uniform(-1, 1, size=(5, 48)).astype(np.float32)
+    g = rng.uniform(-1, 1, size=48).astype(np.float32)
+    bt = rng.uniform(-1, 1, size=48).astype(np.float32)
+    w = rng.uniform(-1, 1, size=(48, 20)).astype(np.float32)
+    bias = rng.uniform(-1, 1, size=20).astype(np.float32)
+    b = ptir.Builder()
+    px, pg, pb, pw, pbias = (b.parameter(F32, list(a.shape)) for a in (x, g, bt, w, bias))
+    b.set_results([ptir.layer_norm(px, pg, pb, 1e-5), ptir.rms_norm(px, pg, 1e-5), ptir.softmax_last_axis(px),
+                   ptir.gelu(px), ptir.swiglu(px, px * 2.0), ptir.linear(px, pw, pbias),
+                   px.transpose([1, 0]).slice([3, 1], [7, 2])])
+    got, want = _both(be, b, [x, g, bt, w, bias], fusion)
+    for a, e in zip(got, want):
+        assert np.allclose(a, e, rtol=1e-4, atol=1e-5)
+    st = be.run_program_stats()
+    assert (st["last_fused"] == 4) if fusion else (st["last_fused"] == 0)
+
+
+def test_fusion_reduces_launches_and_keeps_escaping_values(be):
+    rng = np.random.default_rng(1)
+    x = rng.uniform(-1, 1, size=(3, 32)).astype(np.float32)
+    g = rng.uniform(-1, 1, size=32).astype(np.float32)
+    launches = {}
+    for fusion in (False, True):
+        b = ptir.Builder()
+        px, pg = b.parameter(F32, [3, 32]), b.parameter(F32, [32])
+        out = ptir.rms_norm(px, pg, 1e-5)
+        # the un-scaled `normalized` value (operand 0 of the last Mul) escapes as a second result
+        normalized_id = b.body[-1]["operands"][0]["Value"]
+        inner = next(v for v in [ptir.Value(b, normalized_id, F32, [3, 32])])
+        b.set_results([out, inner])
+        got, want = _both(be, b, [x, g], fusion)
+        assert np.allclose(got[0], want[0], atol=1e-5) and np.allclose(got[1], want[1], atol=1e-5)
+        launches[fusion] = be.run_program_stats()["last_launches"]
+    assert launches[True] < launches[False]
+
+
+def test_rope_attention_and_mask_ops(be):
+    rng = np.random.default_rng(2)
+    n_q, n_kv, hd, cap, pos = 4, 2, 8, 8, 5
+    width = (n_q + 2 * n_kv) * hd
+    qkv = rng.uniform(-1, 1, size=(1, width)).astype(np.float32)
+    ck = rng.uniform(-1, 1, size=(n_kv, cap, hd)).astype(np.float32)
+    cv = rng.uniform(-1, 1, size=(n_kv, cap, hd)).astype(np.float32)
+    cos, sin = fr.rotary_cos_sin(pos, 1, hd, 1e4)
+    b = ptir.Builder()
+    pq, pc, ps = b.parameter(F32, [1, width]), b.parameter(F32, [1, hd // 2]), b.parameter(F32, [1, hd // 2])
+    pk, pv = b.parameter(F32, [n_kv, cap, hd]), b.parameter(F32, [n_kv, cap, hd])
+    pu, pqs = b.parameter(SI32, [3]), b.parameter(SI32, [1])
+    roped = ptir.apply_rope_qkv_packed(pq, pc, ps, n_q, n_kv, hd)
+    ctx, nk, nv = ptir.attention_decode_cache(roped, pk, pv, pu, pqs, n_q, n_kv, hd)
+    b.set_results([roped, ctx, nk, nv])
+    inputs = [qkv, cos, sin, ck, cv, np.array([0, pos, 0], np.int32), np.array([pos], np.int32)]
+    for fusion in (True, False):
+        got, want = _both(be, b, inputs, fusion)
+        assert np.allclose(got[0], want[0], atol=1e-6) and np.allclose(got[1], want[1], atol=1e-5)
+        assert np.array_equal(got[2], want[2]) and np.array_equal(got[3], want[3])
+
+
+@pytest.mark.parametrize("kind", ["gpt", "ministral"])
+def test_decode_step_program_matches_oracles(be, kind):
+    if kind == "gpt":
+        cfg = mr.Cfg("gpt", n_layers=2, d_model=64, n_q=4, n_kv=4, hd=16, d_mlp=128, vocab=96, ctx=32)
+    else:
+        cfg = mr.Cfg("ministral", n_layers=2, d_model=64, n_q=4, n_kv=2, hd=16, d_mlp=128, vocab=96, ctx=32, rot=16, theta=1e4)
+    params = mr.random_params(cfg, seed=3, std=0.3)
+    ref = mr.RefModel(cfg, params)
+    ref.forward([3, 1, 4, 1, 5])
+    caches = [(k.copy(), v.copy()) for k, v in ref.caches]
+    want_logits = ref.forward([9])[-1]
+    pos, cap = 5, 8
+    b, names = ptir.decode_step_program(cfg, cap)
+    cos, sin = fr.rotary_cos_sin(pos, 1, max(cfg.rot, 2), cfg.theta)
+    feed = {"@tokens": np.array([9], np.int32), "@positions": np.array([pos], np.int32), "@cos": cos, "@sin": sin,
+            "@update_starts": np.array([0, pos, 0], np.int32), "@query_start": np.array([pos], np.int32)}
+    for l in range(cfg.n_layers):
+        feed[f"@k{l}"], feed[f"@v{l}"] = caches[l]
+    inputs = [feed[n] if n in feed else params[n] for n in names]
+    builds0 = be.run_program_stats()["plan_builds"]
+    for fusion in (True, False, True):
+        got, want = _both(be, b, inputs, fusion)
+        assert np.allclose(got[0][0], want_logits, rtol=1e-4, atol=1e-4)
+        for a, e in zip(got, want):
+            assert np.allclose(a, e, rtol=1e-4, atol=1e-4)
+    st = be.run_program_stats()
+    assert st["plan_builds"] == builds0 + 2 and st["plan_hits"] >= 1  # third run re-used the fused plan
+    assert st["last_fused"] >= 2 * cfg.n_layers + 1
+
+
+def test_errors_map_to_backend_error_kinds(be):
+    b = ptir.Builder()
+    x = b.parameter(F32, [4])
+    b.set_results([b.custom_call("gpt_rs.someone_else.op.v1", [x], F32, [4])])
+    with pytest.raises(BackendError) as e:
+        be.run_program(b.to_json(), [be.materialize(np.zeros(4, np.float32))])
+    assert e.value.kind == "Unimplemented"
+    prog = b.program()
+    prog["spec_version"] = "ptir.v9"
+    with pytest.raises(BackendError) as e:
+        be.run_program(prog, [be.materialize(np.zeros(4, np.float32))])
+    assert e.value.kind == "SpecViolation"
+    with pytest.raises(BackendError):
+        be.run_program("{not json", [])
+    b = ptir.Builder()
+    w, i = b.parameter(F32, [4, 2]), b.parameter(SI32, [2])
+    b.set_results([b.take(w, i)])
+    with pytest.raises(BackendError) as e:  # ref-cpu reports an out-of-range index as an error
+        be.run_program(b.to_json(), [be.materialize(np.zeros((4, 2), np.float32)), be.materialize(np.array([1, 4], np.int32))])
+    assert e.value.kind == "Execution"
+    with pytest.raises(BackendError):  # wrong input type
+        be.run_program(b.to_json(), [be.materialize(np.zeros((4, 3), np.float32)), be.materialize(np.array([1, 2], np.int32))])
+    pid = 0x1234_5678_9abc_def0_1122_3344_5566_7788
+    assert be.param_get(pid) is None
+    be.param_set(pid, be.materialize(np.arange(3, dtype=np.float32)))
+    assert be.to_literal(be.param_get(pid)).tolist() == [0.0, 1.0, 2.0]
