@@ -334,6 +334,17 @@ int gptrs_cuda_run_program_stats(int64_t* plan_builds, int64_t* plan_hits, int64
 /* Turns the fusion rewrites of run_program on (default) or off (GPTRS_OPT-style switch for tests). */
 int gptrs_cuda_set_fusion(int enabled);
 
+/* ==============================================================================================
+ * Multi-GPU: request-partitioned data parallelism (no counterpart in gpt.rs, whose model path is
+ * single-sequence: crates/gpt-rs/src/inference/mod.rs:14-21). Requests are independent; each rank
+ * (one process per GPU) runs its own engine on its shard and no activation crosses NVLink.
+ * assignment[i] = rank of request i (longest-processing-time-first on the KV traffic a request
+ * causes over `decode_steps` steps; deterministic, so every rank computes the same answer);
+ * rank_cost (optional, [n_ranks]) receives the per-rank totals. Host-only call.
+ * ============================================================================================ */
+int gptrs_cuda_partition_requests(const int64_t* prompt_lens, int64_t n_requests, int64_t decode_steps, int n_ranks,
+                                  int32_t* assignment, int64_t* rank_cost);
+
 #ifdef __cplusplus
 }
 #endif
