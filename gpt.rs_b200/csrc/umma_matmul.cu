@@ -81,9 +81,6 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-__device__ long long g_timeline[64];
-#define TL(i) do { if (blockIdx.x == 3 && blockIdx.y == 1 && lane == 0) g_timeline[(i)] = clock64(); } while (0)
-
 template <int BN>
 __global__ void __launch_bounds__(kUmmaThreads, (BN <= 64) ? 2 : 1)
 umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_map, int* status) {
@@ -108,7 +105,6 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     const int chunk0 = blockIdx.y * p.groups_per_cta * 2;   // first 64-k chunk of this CTA
     const int chunks_total = p.K / kBlockK;
 
-    if (warp == 0) TL(0);
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full_bar[s], kProducerWarps * 32 + 1);
@@ -128,7 +124,6 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     tc_fence_after();
     const uint32_t tmem = tmem_holder;
     bool failed = false;
-    if (warp == 0) TL(1);
 
     if (warp < kProducerWarps) {
         // ---------------- dequant producers: warp w owns 16-channel tile w of the CTA's 8 --------
@@ -150,7 +145,6 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
                 sring[r] = __ldg(sp + (r >> 1) * 8);
             }
         }
-        if (warp == 0) TL(2);
         pdl_wait();
         const __nv_bfloat162 c136 = __floats2bfloat162_rn(136.f, 136.f);
         const int row = warp * 16 + g;  // row & 7 == g for row and row + 8
@@ -161,7 +155,6 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
                 if (it < n_it && !failed) {
                     const int s = it % kStages;
                     if (!mbar_wait_bounded(&empty_bar[s], ((it / kStages) & 1) ^ 1)) { failed = true; }
-                    if (warp == 0 && it < 12) TL(8 + it);
                     const uint4 cur = ring[r];
                     const uint32_t csc = sring[r];
                     if (tv && it + kRing < n_it) {
@@ -193,7 +186,6 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
                     }
                     fence_proxy_async();
                     mbar_arrive(&full_bar[s]);
-                    if (warp == 0 && it < 12) TL(20 + it);
                 }
             }
         }
@@ -216,7 +208,6 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
             const int s = it % kStages;
             if (!mbar_wait_bounded(&full_bar[s], (it / kStages) & 1)) { failed = true; break; }
             tc_fence_after();
-            if (it < 12) TL(32 + it);
             if (lane == 0) {
                 const uint64_t a_desc = make_smem_desc(smem_u32(sA + s * kABytes));
                 const uint64_t b_desc = make_smem_desc(smem_u32(sB + s * kBBytes));
@@ -235,10 +226,8 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     // ---------------- epilogue: TMEM -> registers -> shared tile [BN][kRedStride] ----------------
     float* red = reinterpret_cast<float*>(smem);
     if (warp < kProducerWarps) {
-        if (warp == 0) TL(3);
         if (!mbar_wait_bounded(&done_bar, 0)) failed = true;
         tc_fence_after();
-        if (warp == 0) TL(4);
         // warp w reads TMEM lanes 32*(w % 4); warps 0-3 take the low half of the columns, 4-7 the high half
         const int quarter = warp & 3;
         const int col = quarter * 32 + lane;  // output channel within the CTA tile == TMEM lane
@@ -251,16 +240,13 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
             for (int i = 0; i < 32; ++i) red[(c0 + i) * kRedStride + col] = v[i];
         }
     }
-    if (warp == 0) TL(5);
     if (failed && lane == 0) atomicExch(status, 3);
     tc_fence_before();
     __syncthreads();
     if (warp == kProducerWarps) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
-    if (warp == 0) TL(6);
     reduce_and_store_tile<BN>(p, red, tid, kUmmaThreads, m0, n_cta0);
-    if (warp == 0) TL(7);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -354,10 +340,6 @@ int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
     if (p.M <= 64) return launch_umma<64>(p, dim3(n_blocks, split, 1), st);
     if (p.M <= 128) return launch_umma<128>(p, dim3(n_blocks, split, 1), st);
     return launch_umma<256>(p, dim3(n_blocks, split, ceil_div(p.M, 256)), st);
-}
-
-extern "C" int gptrs_debug_timeline(long long* out) {
-    return cudaMemcpyFromSymbol(out, g_timeline, sizeof(long long) * 64) == cudaSuccess ? 0 : 3;
 }
 
 int umma_status(int* out) {
