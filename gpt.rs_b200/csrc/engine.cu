@@ -21,9 +21,13 @@
 #include <tuple>
 #include <vector>
 
+#include "nccl_dl.h"
 #include "tensor.h"
 
 namespace gptrs {
+
+int sample_rows_with_values(const float* d_logits, int64_t rows, int64_t vocab, int32_t* d_tokens, float* d_values, cudaStream_t st);  // norm_embed_sample.cu
+
 namespace {
 
 enum { kKindGpt = 0, kKindMinistral = 1 };
@@ -99,6 +103,10 @@ struct Model {
     cudaStream_t stream = nullptr;
     struct GraphEntry { cudaGraphExec_t exec; int64_t kernels; };
     std::map<GraphKey, GraphEntry> graphs;
+    // tensor parallelism: cfg holds the LOCAL head / MLP sizes; the full sizes are kept here
+    int tp = 1, tp_rank = 0, full_q = 0, full_kv = 0, full_mlp = 0, vocab_l = 0;
+    NcclComm comm = nullptr;
+    DevBuf partial, tp_vals, tp_idx, tp_gvals, tp_gidx;  // row-parallel partial sums; (max, argmax) exchange
     int gen_batch = 0;  // slots 0..gen_batch-1 are driven by generator_step
     int64_t launches = 0;
     uint32_t sample_seed = 0;
@@ -120,6 +128,7 @@ struct Model {
         if (h_page_table) cudaFreeHost(h_page_table);
         if (h_stage) cudaFreeHost(h_stage);
         if (h_logits) cudaFreeHost(h_logits);
+        if (comm) { std::string e; if (const NcclApi* api = nccl_api(&e)) api->CommDestroy(comm); }
         if (stream) cudaStreamDestroy(stream);
     }
 };
@@ -148,19 +157,62 @@ int get_raw(Model& m, const std::string& name, std::vector<int64_t> want_dims, T
     return GPTRS_OK;
 }
 
+// Copies rows [row0, row0+rows) and the listed column ranges of an f32 leaf [R][C] into a new tensor.
+int slice_leaf(Model& m, Tensor* full, int64_t row0, int64_t rows, const std::vector<std::pair<int64_t, int64_t>>& cols,
+               Tensor** out) {
+    int64_t total = 0;
+    for (auto& c : cols) total += c.second;
+    const int64_t C = full->dims[1];
+    int64_t dims[2] = {rows, total};
+    int rc = tensor_alloc(GPTRS_F32, 2, dims, false, out);
+    if (rc) return rc;
+    int64_t o = 0;
+    for (auto& c : cols) {
+        GPTRS_CUDA_OK(cudaMemcpy2DAsync(static_cast<float*>((*out)->data) + o, total * 4,
+                                        static_cast<const float*>(full->data) + row0 * C + c.first, C * 4, c.second * 4, rows,
+                                        cudaMemcpyDeviceToDevice, m.stream));
+        o += c.second;
+    }
+    return GPTRS_OK;
+}
+
+enum TpSplit { kReplicated = 0, kColumnParallel = 1, kRowParallel = 2, kQkvColumns = 3 };
+
 // Builds a Linear from leaf weights `names` (each [in][out_i], concatenated along out) in the
 // model's weight mode. Quantised layouts are looked up / stored in the process-wide memo.
+// `in` / `outs` are the FULL sizes of the leaves; with tensor parallelism the rank's slice is cut
+// out first (column-parallel: output channels, row-parallel: input channels, qkv: its heads).
 int build_linear(Model& m, const std::vector<std::string>& names, const std::string& bias_name, int64_t in,
-                 const std::vector<int64_t>& outs, bool gate_up, Weight* w) {
-    int64_t out_total = 0;
-    for (int64_t o : outs) out_total += o;
-    w->in = in; w->out = out_total;
-    if (!bias_name.empty()) { int rc = get_raw(m, bias_name, {out_total}, &w->bias); if (rc) return rc; }
+                 std::vector<int64_t> outs, bool gate_up, Weight* w, int split = kReplicated) {
     std::vector<Tensor*> leaves(names.size(), nullptr);
     for (size_t i = 0; i < names.size(); ++i) {
         int rc = get_raw(m, names[i], {in, outs[i]}, &leaves[i]);
         if (rc) { for (Tensor* t : leaves) tensor_release(t); return rc; }
     }
+    if (m.tp > 1 && split != kReplicated) {
+        const int64_t r = m.tp_rank, n = m.tp;
+        for (size_t i = 0; i < leaves.size(); ++i) {
+            Tensor* cut = nullptr;
+            int rc;
+            if (split == kRowParallel) {
+                rc = slice_leaf(m, leaves[i], r * in / n, in / n, {{0, outs[i]}}, &cut);
+            } else if (split == kColumnParallel) {
+                rc = slice_leaf(m, leaves[i], 0, in, {{r * outs[i] / n, outs[i] / n}}, &cut);
+            } else {
+                const int64_t hd = m.cfg.head_dim, qd = (int64_t)m.full_q * hd, kd = (int64_t)m.full_kv * hd;
+                rc = slice_leaf(m, leaves[i], 0, in, {{r * qd / n, qd / n}, {qd + r * kd / n, kd / n}, {qd + kd + r * kd / n, kd / n}}, &cut);
+            }
+            if (rc) { for (Tensor* t : leaves) tensor_release(t); return rc; }
+            tensor_release(leaves[i]);
+            leaves[i] = cut;
+        }
+        if (split == kRowParallel) in /= n;
+        else for (auto& o : outs) o /= n;
+    }
+    int64_t out_total = 0;
+    for (int64_t o : outs) out_total += o;
+    w->in = in; w->out = out_total;
+    if (!bias_name.empty()) { int rc = get_raw(m, bias_name, {out_total}, &w->bias); if (rc) { for (Tensor* t : leaves) tensor_release(t); return rc; } }
     auto drop = [&]() { for (Tensor* t : leaves) tensor_release(t); };
     if (m.f32()) {
         if (names.size() != 1) { drop(); return fail(GPTRS_EXECUTION, "f32 mode keeps Linear weights separate"); }
@@ -169,6 +221,7 @@ int build_linear(Model& m, const std::vector<std::string>& names, const std::str
     }
     const bool w4 = m.cfg.weight_mode == kModeW4;
     std::string tag = std::string(w4 ? "w4g128" : "w8pc") + (gate_up ? ":gate_up" : "");
+    if (m.tp > 1 && split != kReplicated) tag += ":tp" + std::to_string(m.tp_rank) + "/" + std::to_string(m.tp) + ":" + std::to_string(split);
     std::pair<uint64_t, uint64_t> key = m.ids[names[0]];
     for (size_t i = 1; i < names.size(); ++i) { key.first ^= m.ids[names[i]].first * 31; key.second ^= m.ids[names[i]].second * 131; }
     auto did = derived_id(key, tag);
@@ -249,6 +302,20 @@ __global__ void gather_rows_kernel(const GatherParams p) {
         *reinterpret_cast<uint32_t*>(d + i) = *reinterpret_cast<const uint32_t*>(s + i);
 }
 
+struct TpPickParams { const float* vals; const int* idx; int* out; int rows, tp, vocab_l; };
+__global__ void tp_pick_kernel(const TpPickParams p) {
+    pdl_wait();
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= p.rows) return;
+    float best = p.vals[r];
+    int who = 0;
+    for (int k = 1; k < p.tp; ++k) {
+        float v = p.vals[k * p.rows + r];
+        if (v > best) { best = v; who = k; }
+    }
+    p.out[r] = p.idx[who * p.rows + r] + who * p.vocab_l;
+}
+
 struct AdvanceParams { int* pos; int* ctx; int n; };
 __global__ void advance_kernel(const AdvanceParams p) {
     pdl_wait();
@@ -272,15 +339,37 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
     ++m.launches;
     if (rc) return rc;
     const bool gpt = c.kind == kKindGpt;
+    const NcclApi* nccl = nullptr;
+    if (m.tp > 1) {
+        std::string err;
+        nccl = nccl_api(&err);
+        if (!nccl) return fail(GPTRS_EXECUTION, err);
+    }
+    // Row-parallel projections: without tensor parallelism the residual add is folded into the
+    // matmul epilogue (hidden += x.W in place). With it, each rank produces a partial [T, D] sum
+    // that is all-reduced over NVLink and then added to the residual stream by the next norm kernel.
+    const float* pending = nullptr;
+    auto row_parallel = [&](const Weight& w, const void* x) -> int {
+        if (m.tp == 1) return linear(m, w, x, hidden, T, true, hidden, false, false);
+        int r = linear(m, w, x, m.partial.p, T, true, nullptr, false, false);
+        if (r) return r;
+        ++m.launches;
+        int nr = nccl->AllReduce(m.partial.p, m.partial.p, (size_t)T * D, kNcclFloat32, kNcclSum, m.comm, st);
+        if (nr) return fail(GPTRS_EXECUTION, std::string("ncclAllReduce: ") + nccl->GetErrorString(nr));
+        pending = m.partial.as<float>();
+        return GPTRS_OK;
+    };
+    auto norm = [&](Tensor* g, Tensor* b) {
+        ++m.launches;
+        const float* delta = pending;
+        pending = nullptr;
+        return gpt ? gptrs_cuda_add_layer_norm(hidden, delta, GPTRS_F32, nullptr, (const float*)g->data, (const float*)b->data,
+                                               c.norm_eps, m.xn.p, act_dt, nullptr, nullptr, T, D, st)
+                   : gptrs_cuda_add_rms_norm(hidden, delta, GPTRS_F32, (const float*)g->data, c.norm_eps, m.xn.p, act_dt,
+                                             nullptr, T, D, st);
+    };
     for (int l = 0; l < c.n_layers; ++l) {
         Layer& L = m.layers[l];
-        auto norm = [&](Tensor* g, Tensor* b) {
-            ++m.launches;
-            return gpt ? gptrs_cuda_add_layer_norm(hidden, nullptr, GPTRS_F32, nullptr, (const float*)g->data, (const float*)b->data,
-                                                   c.norm_eps, m.xn.p, act_dt, nullptr, nullptr, T, D, st)
-                       : gptrs_cuda_add_rms_norm(hidden, nullptr, GPTRS_F32, (const float*)g->data, c.norm_eps, m.xn.p, act_dt,
-                                                 nullptr, T, D, st);
-        };
         if ((rc = norm(L.ln1_g, L.ln1_b))) return rc;
         if ((rc = linear(m, L.qkv, m.xn.p, m.qkv.p, T, false, nullptr, false, false))) return rc;
         if (m.f32()) {
@@ -313,8 +402,7 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
                                                         m.attn_scratch.p, m.attn_scratch.n, m.d_status.as<int32_t>(), T,
                                                         c.n_q_heads, c.n_kv_heads, c.head_dim, max_ctx, chunk_pages, st))) return rc;
         }
-        // hidden += attn . W_out (+ b)   (residual add folded into the epilogue, in place)
-        if ((rc = linear(m, L.attn_out, m.attn.p, hidden, T, true, hidden, false, false))) return rc;
+        if ((rc = row_parallel(L.attn_out, m.attn.p))) return rc;
         if ((rc = norm(L.ln2_g, L.ln2_b))) return rc;
         if (gpt) {
             if ((rc = linear(m, L.mlp_in, m.xn.p, m.mlp_h.p, T, false, nullptr, false, true))) return rc;
@@ -326,14 +414,9 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         } else {
             if ((rc = linear(m, L.mlp_gate_up, m.xn.p, m.mlp_h.p, T, false, nullptr, true, false))) return rc;
         }
-        if ((rc = linear(m, L.mlp_out, m.mlp_h.p, hidden, T, true, hidden, false, false))) return rc;
+        if ((rc = row_parallel(L.mlp_out, m.mlp_h.p))) return rc;
     }
-    ++m.launches;
-    rc = gpt ? gptrs_cuda_add_layer_norm(hidden, nullptr, GPTRS_F32, nullptr, (const float*)m.final_g->data,
-                                         (const float*)m.final_b->data, c.norm_eps, m.xn.p, act_dt, nullptr, nullptr, T, D, st)
-             : gptrs_cuda_add_rms_norm(hidden, nullptr, GPTRS_F32, (const float*)m.final_g->data, c.norm_eps, m.xn.p, act_dt,
-                                       nullptr, T, D, st);
-    if (rc) return rc;
+    if ((rc = norm(m.final_g, m.final_b))) return rc;
     const void* xr = m.xn.p;
     if (!rows_identity) {
         ++m.launches;
@@ -343,7 +426,18 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
     }
     if ((rc = linear(m, m.lm_head, xr, m.logits.p, n_rows, true, nullptr, false, false))) return rc;
     ++m.launches;
-    return gptrs_cuda_sample_rows(m.logits.as<float>(), n_rows, c.vocab, temperature, m.sample_seed, m.d_sampled.as<int32_t>(), st);
+    if (m.tp == 1)
+        return gptrs_cuda_sample_rows(m.logits.as<float>(), n_rows, c.vocab, temperature, m.sample_seed, m.d_sampled.as<int32_t>(), st);
+    // vocab-parallel head: every rank finds (max, argmax) of its shard, the pairs are all-gathered
+    // and each rank picks the global winner (ties -> smallest global index)
+    if (temperature > 0.f) return fail(GPTRS_UNIMPLEMENTED, "temperature sampling with a vocab-parallel head");
+    if ((rc = sample_rows_with_values(m.logits.as<float>(), n_rows, m.vocab_l, m.tp_idx.as<int32_t>(), m.tp_vals.as<float>(), st))) return rc;
+    int nr = nccl->AllGather(m.tp_vals.p, m.tp_gvals.p, (size_t)n_rows, kNcclFloat32, m.comm, st);
+    if (!nr) nr = nccl->AllGather(m.tp_idx.p, m.tp_gidx.p, (size_t)n_rows, kNcclInt32, m.comm, st);
+    if (nr) return fail(GPTRS_EXECUTION, std::string("ncclAllGather: ") + nccl->GetErrorString(nr));
+    m.launches += 3;
+    TpPickParams pp = {m.tp_gvals.as<float>(), m.tp_gidx.as<int32_t>(), m.d_sampled.as<int32_t>(), n_rows, m.tp, m.vocab_l};
+    return launch_kernel(tp_pick_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, st, 1, pp);
 }
 
 int ensure_pages(Model& m, int slot, int upto_pos) {
@@ -409,8 +503,22 @@ int gptrs_cuda_model_create(const gptrs_model_config* cfg, gptrs_model** out) {
         GPTRS_REQUIRE(c.kv_pages > 0 && c.max_pages_per_seq > 0, "kv_pages and max_pages_per_seq must be positive");
     }
     if (c.kind == kKindMinistral) GPTRS_REQUIRE(c.rotary_dim >= 0 && c.rotary_dim <= c.head_dim && c.rotary_dim % 2 == 0, "bad rotary_dim");
+    const int tp = c.tp_size > 1 ? c.tp_size : 1;
+    if (tp > 1) {
+        if (c.kind != kKindMinistral) return fail(GPTRS_UNIMPLEMENTED, "tensor parallelism is implemented for the ministral kind");
+        GPTRS_REQUIRE(c.tp_rank >= 0 && c.tp_rank < tp, "tp_rank out of range");
+        GPTRS_REQUIRE(c.n_kv_heads % tp == 0 && c.n_q_heads % tp == 0 && c.d_mlp % tp == 0 && c.vocab % tp == 0,
+                      "heads, d_mlp and vocab must be divisible by tp_size");
+        GPTRS_REQUIRE(c.weight_mode == kModeF32 || ((c.d_mlp / tp) % 128 == 0 && (c.n_q_heads / tp * c.head_dim) % 128 == 0 &&
+                                                     (c.vocab / tp) % 16 == 0),
+                      "quantised tensor-parallel slices need 128-aligned input sizes");
+    }
     auto m = std::make_unique<Model>();
     m->cfg = c;
+    m->tp = tp; m->tp_rank = tp > 1 ? c.tp_rank : 0;
+    m->full_q = c.n_q_heads; m->full_kv = c.n_kv_heads; m->full_mlp = c.d_mlp;
+    m->cfg.n_q_heads = c.n_q_heads / tp; m->cfg.n_kv_heads = c.n_kv_heads / tp; m->cfg.d_mlp = c.d_mlp / tp;
+    m->vocab_l = c.vocab / tp;
     GPTRS_CUDA_OK(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
     *out = reinterpret_cast<gptrs_model*>(m.release());
     return GPTRS_OK;
@@ -453,14 +561,43 @@ int gptrs_cuda_model_set_rope_tables(gptrs_model* h, const float* h_cos, const f
     return GPTRS_OK;
 }
 
+int gptrs_cuda_nccl_unique_id(uint8_t* out128) {
+    GPTRS_REQUIRE(out128, "null pointer");
+    std::string err;
+    const NcclApi* api = nccl_api(&err);
+    if (!api) return fail(GPTRS_EXECUTION, err);
+    NcclUniqueId id;
+    int nr = api->GetUniqueId(&id);
+    if (nr) return fail(GPTRS_EXECUTION, std::string("ncclGetUniqueId: ") + api->GetErrorString(nr));
+    memcpy(out128, id.internal, 128);
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_model_init_tensor_parallel(gptrs_model* h, const uint8_t* unique_id128) {
+    GPTRS_REQUIRE(h && unique_id128, "null pointer");
+    Model& m = *reinterpret_cast<Model*>(h);
+    GPTRS_REQUIRE(m.tp > 1, "model was created with tp_size <= 1");
+    GPTRS_REQUIRE(!m.comm, "tensor-parallel communicator already initialised");
+    std::string err;
+    const NcclApi* api = nccl_api(&err);
+    if (!api) return fail(GPTRS_EXECUTION, err);
+    NcclUniqueId id;
+    memcpy(id.internal, unique_id128, 128);
+    int nr = api->CommInitRank(&m.comm, m.tp, id, m.tp_rank);
+    if (nr) { m.comm = nullptr; return fail(GPTRS_EXECUTION, std::string("ncclCommInitRank: ") + api->GetErrorString(nr)); }
+    return GPTRS_OK;
+}
+
 int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
     GPTRS_REQUIRE(h, "null pointer");
     Model& m = *reinterpret_cast<Model*>(h);
     GPTRS_REQUIRE(!m.finalized, "model already finalized");
     const auto& c = m.cfg;
     const int64_t D = c.d_model, QKV = m.QKV(), QD = m.QD(), MLP = c.d_mlp;
+    const int64_t QKVf = (int64_t)(m.full_q + 2 * m.full_kv) * c.head_dim, QDf = (int64_t)m.full_q * c.head_dim, MLPf = m.full_mlp;
     const bool gpt = c.kind == kKindGpt;
     int rc;
+    if (m.tp > 1) GPTRS_REQUIRE(m.comm, "tensor-parallel model: call gptrs_cuda_model_init_tensor_parallel before finalize");
     if ((rc = get_raw(m, "tok_embeddings.weight", {c.vocab, D}, &m.tok_emb))) return rc;
     if (gpt && (rc = get_raw(m, "pos_embeddings", {c.context_length, D}, &m.pos_emb))) return rc;
     m.layers.resize(c.n_layers);
@@ -476,15 +613,15 @@ int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
             if ((rc = build_linear(m, {p + ".feed_forward.w_out"}, p + ".feed_forward.b_out", MLP, {D}, false, &L.mlp_out))) return rc;
         } else {
             if ((rc = get_raw(m, p + ".norm_1.gamma", {D}, &L.ln1_g)) || (rc = get_raw(m, p + ".norm_2.gamma", {D}, &L.ln2_g))) return rc;
-            if ((rc = build_linear(m, {p + ".attention.w_qkv"}, "", D, {QKV}, false, &L.qkv))) return rc;
-            if ((rc = build_linear(m, {p + ".attention.w_out"}, "", QD, {D}, false, &L.attn_out))) return rc;
+            if ((rc = build_linear(m, {p + ".attention.w_qkv"}, "", D, {QKVf}, false, &L.qkv, kQkvColumns))) return rc;
+            if ((rc = build_linear(m, {p + ".attention.w_out"}, "", QDf, {D}, false, &L.attn_out, kRowParallel))) return rc;
             if (m.f32()) {
-                if ((rc = build_linear(m, {p + ".feed_forward.w_gate"}, "", D, {MLP}, false, &L.mlp_gate))) return rc;
-                if ((rc = build_linear(m, {p + ".feed_forward.w_up"}, "", D, {MLP}, false, &L.mlp_up))) return rc;
+                if ((rc = build_linear(m, {p + ".feed_forward.w_gate"}, "", D, {MLPf}, false, &L.mlp_gate, kColumnParallel))) return rc;
+                if ((rc = build_linear(m, {p + ".feed_forward.w_up"}, "", D, {MLPf}, false, &L.mlp_up, kColumnParallel))) return rc;
             } else {
-                if ((rc = build_linear(m, {p + ".feed_forward.w_gate", p + ".feed_forward.w_up"}, "", D, {MLP, MLP}, true, &L.mlp_gate_up))) return rc;
+                if ((rc = build_linear(m, {p + ".feed_forward.w_gate", p + ".feed_forward.w_up"}, "", D, {MLPf, MLPf}, true, &L.mlp_gate_up, kColumnParallel))) return rc;
             }
-            if ((rc = build_linear(m, {p + ".feed_forward.w_down"}, "", MLP, {D}, false, &L.mlp_out))) return rc;
+            if ((rc = build_linear(m, {p + ".feed_forward.w_down"}, "", MLPf, {D}, false, &L.mlp_out, kRowParallel))) return rc;
         }
         if (drop_f32_leaves && !m.f32()) {
             // the f32 leaves of this layer's Linears are no longer needed once quantised
@@ -499,7 +636,7 @@ int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
     } else {
         if ((rc = get_raw(m, "final_norm.gamma", {D}, &m.final_g))) return rc;
     }
-    if ((rc = build_linear(m, {"lm_head"}, "", D, {c.vocab}, false, &m.lm_head))) return rc;
+    if ((rc = build_linear(m, {"lm_head"}, "", D, {c.vocab}, false, &m.lm_head, kColumnParallel))) return rc;
     if (drop_f32_leaves && !m.f32()) {
         auto it = m.raw.find("lm_head");
         if (it != m.raw.end()) { tensor_release(it->second); m.raw.erase(it); }
@@ -531,12 +668,14 @@ int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
     if (m.f32() && !gpt && ((rc = m.mlp_g.alloc((size_t)T * MLP * 4)) || (rc = m.mlp_u.alloc((size_t)T * MLP * 4)))) return rc;
     if (!m.f32() && (rc = m.q_rot.alloc((size_t)T * QD * 2))) return rc;
     const int max_rows = c.max_logit_rows > 0 ? c.max_logit_rows : c.max_seqs;
-    if ((rc = m.logits.alloc((size_t)max_rows * c.vocab * 4))) return rc;
+    if ((rc = m.logits.alloc((size_t)max_rows * m.vocab_l * 4))) return rc;
+    if (m.tp > 1 && ((rc = m.partial.alloc((size_t)T * D * 4)) || (rc = m.tp_vals.alloc((size_t)max_rows * 4)) || (rc = m.tp_idx.alloc((size_t)max_rows * 4)) ||
+                     (rc = m.tp_gvals.alloc((size_t)m.tp * max_rows * 4)) || (rc = m.tp_gidx.alloc((size_t)m.tp * max_rows * 4)))) return rc;
     for (DevBuf* b : {&m.d_tokens, &m.d_slot, &m.d_pos, &m.d_ctx, &m.d_rows, &m.d_sampled})
         if ((rc = b->alloc((size_t)std::max(T, max_rows) * 4, true))) return rc;
     if ((rc = m.d_status.alloc(4, true))) return rc;
     GPTRS_CUDA_OK(cudaMallocHost(&m.h_stage, (size_t)6 * std::max(T, max_rows) * 4));
-    GPTRS_CUDA_OK(cudaMallocHost(&m.h_logits, (size_t)max_rows * c.vocab * 4));
+    GPTRS_CUDA_OK(cudaMallocHost(&m.h_logits, (size_t)max_rows * m.vocab_l * 4));
 
     // KV storage
     m.seq_pages.assign(c.max_seqs, 0);
@@ -646,12 +785,12 @@ int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* h, const int32_t* h_
     rc = enqueue_forward(m, T, max_ctx, chunk, rows, false, temperature);
     if (rc) return rc;
     if (h_logits && n_logit_rows)
-        GPTRS_CUDA_OK(cudaMemcpyAsync(m.h_logits, m.logits.p, (size_t)n_logit_rows * c.vocab * 4, cudaMemcpyDeviceToHost, s));
+        GPTRS_CUDA_OK(cudaMemcpyAsync(m.h_logits, m.logits.p, (size_t)n_logit_rows * m.vocab_l * 4, cudaMemcpyDeviceToHost, s));
     if (h_sampled && n_logit_rows)
         GPTRS_CUDA_OK(cudaMemcpyAsync(st + 5 * stride, m.d_sampled.p, (size_t)n_logit_rows * 4, cudaMemcpyDeviceToHost, s));
     rc = check_status(m);  // synchronises the stream
     if (rc) return rc;
-    if (h_logits && n_logit_rows) memcpy(h_logits, m.h_logits, (size_t)n_logit_rows * c.vocab * 4);
+    if (h_logits && n_logit_rows) memcpy(h_logits, m.h_logits, (size_t)n_logit_rows * m.vocab_l * 4);
     if (h_sampled && n_logit_rows) memcpy(h_sampled, st + 5 * stride, (size_t)n_logit_rows * 4);
     return GPTRS_OK;
 }

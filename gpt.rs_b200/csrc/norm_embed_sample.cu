@@ -203,6 +203,7 @@ __global__ void __launch_bounds__(256) softmax_kernel(const SoftmaxParams p) {
 // ---- sampler ----------------------------------------------------------------------------------
 struct SampleParams {
     const float* logits;  // [rows][vocab]
+    float* values;        // optional [rows]: the winning (scaled) logit
     int* tokens;          // [rows]
     int rows, vocab;
     float temperature;    // <= 0: greedy
@@ -251,11 +252,21 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
             int oi = __shfl_xor_sync(0xffffffffu, besti, o);
             if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
         }
-        if (l == 0) p.tokens[row] = besti == 0x7fffffff ? 0 : besti;
+        if (l == 0) {
+            p.tokens[row] = besti == 0x7fffffff ? 0 : besti;
+            if (p.values) p.values[row] = best;
+        }
     }
 }
 
 }  // namespace
+
+// Greedy argmax per row that also reports the winning value (vocab-parallel heads exchange the pairs).
+int sample_rows_with_values(const float* d_logits, int64_t rows, int64_t vocab, int32_t* d_tokens, float* d_values, cudaStream_t st) {
+    SampleParams p = {d_logits, d_values, d_tokens, (int)rows, (int)vocab, 0.f, 0u};
+    return launch_kernel(sample_kernel, dim3((unsigned)rows), dim3(1024), 0, st, 1, p);
+}
+
 }  // namespace gptrs
 
 using namespace gptrs;
@@ -343,7 +354,7 @@ int gptrs_cuda_sample_rows(const float* d_logits, int64_t rows, int64_t vocab, f
     GPTRS_REQUIRE(d_logits && d_tokens, "null pointer");
     GPTRS_REQUIRE(rows >= 0 && vocab > 0 && vocab < (1ll << 31) && rows < (1ll << 31), "bad shape");
     if (rows == 0) return GPTRS_OK;
-    SampleParams p = {d_logits, d_tokens, (int)rows, (int)vocab, temperature, seed};
+    SampleParams p = {d_logits, nullptr, d_tokens, (int)rows, (int)vocab, temperature, seed};
     return launch_kernel(sample_kernel, dim3((unsigned)rows), dim3(1024), 0, as_stream(stream), 1, p);
 }
 

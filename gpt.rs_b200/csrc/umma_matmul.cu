@@ -18,6 +18,8 @@
 // records an error in *status, still frees its TMEM and leaves.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "matmul_common.cuh"
 
 namespace gptrs {
@@ -328,7 +330,9 @@ int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
 int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
     const int groups = p.K / 128;
     const int n_blocks = ceil_div(p.N, kCtaN);
-    const int target = sm_count() * 6 / 5;
+    static int pct = 0;  // CTAs per 100 SMs aimed at by the K split (GPTRS_UMMA_CTAS_PCT overrides)
+    if (pct == 0) { const char* e = getenv("GPTRS_UMMA_CTAS_PCT"); pct = e ? atoi(e) : 120; if (pct <= 0) pct = 120; }
+    const int target = sm_count() * pct / 100;
     int split = 1;
     for (int s = 1; s <= 8; s *= 2) {
         if (groups % s != 0) break;

@@ -30,6 +30,7 @@ class _ModelConfig(ctypes.Structure):
         ("norm_eps", ctypes.c_float), ("rope_theta", ctypes.c_float), ("rotary_dim", ctypes.c_int),
         ("max_seqs", ctypes.c_int), ("max_tokens", ctypes.c_int), ("max_logit_rows", ctypes.c_int),
         ("kv_pages", ctypes.c_int64), ("max_pages_per_seq", ctypes.c_int), ("use_pdl", ctypes.c_int),
+        ("tp_size", ctypes.c_int), ("tp_rank", ctypes.c_int),
     ]
 
 
@@ -54,6 +55,8 @@ class ModelConfig:
     kv_pages: int = 0
     max_pages_per_seq: int = 0
     use_pdl: int = 0
+    tp_size: int = 1
+    tp_rank: int = 0
 
     @staticmethod
     def gpt2_small(**kw):
@@ -166,6 +169,12 @@ class LoadedModel:
         sin = np.ascontiguousarray(sin, dtype=np.float32)
         check(lib().gptrs_cuda_model_set_rope_tables(self._h, cos.ctypes.data, sin.ctypes.data, cos.shape[0]))
 
+    def init_tensor_parallel(self, unique_id: bytes):
+        """Joins the NCCL communicator of the tensor-parallel group (call on every rank before finalize)."""
+        assert len(unique_id) == 128
+        buf = (ctypes.c_uint8 * 128).from_buffer_copy(unique_id)
+        check(lib().gptrs_cuda_model_init_tensor_parallel(self._h, buf))
+
     def finalize(self, drop_f32_leaves: bool = True):
         check(lib().gptrs_cuda_model_finalize(self._h, int(drop_f32_leaves)))
         self._finalized = True
@@ -192,7 +201,8 @@ class LoadedModel:
         pos = np.ascontiguousarray(positions, dtype=np.int32)
         rows = np.ascontiguousarray(logit_rows, dtype=np.int32)
         n, r = len(tok), len(rows)
-        logits = np.empty((r, self.config.vocab), dtype=np.float32) if (want_logits and r) else None
+        vocab_local = self.config.vocab // max(self.config.tp_size, 1)
+        logits = np.empty((r, vocab_local), dtype=np.float32) if (want_logits and r) else None
         sampled = np.empty(r, dtype=np.int32)
         check(lib().gptrs_cuda_model_forward_with_decode_cache(
             self._h, tok.ctypes.data, sl.ctypes.data, pos.ctypes.data, n, rows.ctypes.data if r else None, r,
@@ -223,6 +233,13 @@ class LoadedModel:
         n = len(tokens)
         lg, _ = self.forward_with_decode_cache(tokens, [0] * n, list(range(n)), list(range(n)))
         return lg
+
+
+def nccl_unique_id() -> bytes:
+    """128-byte NCCL id created on the calling rank (distribute it to the group yourself)."""
+    buf = (ctypes.c_uint8 * 128)()
+    check(lib().gptrs_cuda_nccl_unique_id(buf))
+    return bytes(buf)
 
 
 class Generator:

@@ -279,6 +279,8 @@ typedef struct {
     int64_t kv_pages;    /* pages per layer pool (quantised modes) */
     int max_pages_per_seq;
     int use_pdl;         /* record the decode graph with programmatic dependent launches */
+    int tp_size;         /* tensor-parallel ranks sharing this model (0 or 1 = none); sizes above are the FULL model's */
+    int tp_rank;
 } gptrs_model_config;
 
 int gptrs_cuda_model_create(const gptrs_model_config* cfg, gptrs_model** out);
@@ -292,6 +294,15 @@ int gptrs_cuda_model_load_param(gptrs_model* m, const char* name, uint64_t id_lo
  * the host and passes them as inputs, model/ministral.rs:253-261); otherwise finalize computes
  * them with the formula of ops/functional/rotary.rs:75-215 (no scaling). */
 int gptrs_cuda_model_set_rope_tables(gptrs_model* m, const float* h_cos, const float* h_sin, int64_t n_positions);
+/* Tensor-parallel variant (ministral kind; no counterpart in gpt.rs): w_qkv / w_gate / w_up / lm_head are
+ * column-parallel (each rank keeps n_q_heads/tp query heads, n_kv_heads/tp kv heads, d_mlp/tp columns,
+ * vocab/tp logits), w_out / w_down are row-parallel and followed by ONE ncclAllReduce(sum, f32) of the
+ * [rows, d_model] partial sums over NVLink; the greedy token is chosen from all-gathered (max, argmax)
+ * pairs. Every rank loads the FULL parameters and cuts its slice on the device. Rank 0 creates the id,
+ * the caller distributes the 128 bytes (e.g. with torch.distributed), every rank calls init before
+ * finalize. With tp_size > 1 forward_with_decode_cache returns the rank's logits shard [rows][vocab/tp]. */
+int gptrs_cuda_nccl_unique_id(uint8_t* out128);
+int gptrs_cuda_model_init_tensor_parallel(gptrs_model* m, const uint8_t* unique_id128);
 /* Checks that every parameter is present, quantises + repacks Linear weights (memoised process-wide
  * by stable id, see gptrs_cuda_param_get), allocates activations and KV storage. */
 int gptrs_cuda_model_finalize(gptrs_model* m, int drop_f32_leaves);
