@@ -88,12 +88,13 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def build_model(gm, torch, dev, steps_total: int, use_pdl: int, prefill_chunk: int):
+def build_model(gm, torch, dev, steps_total: int, use_pdl: int, prefill_chunk: int, tp_size: int = 1, tp_rank: int = 0, nccl_id=None):
     ctx = ((PROMPT_LEN + steps_total + 64 + 15) // 16) * 16
     pages_per_seq = ctx // 16
     cfg = gm.ModelConfig.ministral_3b(context_length=ctx, weight_mode=gm.MODE_W4A16, max_seqs=BATCH,
                                       max_tokens=prefill_chunk, max_logit_rows=BATCH,
-                                      kv_pages=BATCH * pages_per_seq + 8, max_pages_per_seq=pages_per_seq, use_pdl=use_pdl)
+                                      kv_pages=BATCH * pages_per_seq + 8, max_pages_per_seq=pages_per_seq, use_pdl=use_pdl,
+                                      tp_size=tp_size, tp_rank=tp_rank)
     model = gm.LoadedModel(cfg, namespace=0)
     gen = torch.Generator(device=dev)
     gen.manual_seed(0)
@@ -104,6 +105,8 @@ def build_model(gm, torch, dev, steps_total: int, use_pdl: int, prefill_chunk: i
             w = torch.empty(shape, dtype=torch.float32, device=dev).normal_(0.0, 0.02, generator=gen)
         model.load_param(name, w)
         del w
+    if tp_size > 1:
+        model.init_tensor_parallel(nccl_id)
     model.finalize(drop_f32_leaves=True)
     torch.cuda.empty_cache()
     return model, cfg
@@ -222,6 +225,17 @@ def run_reference_arm(args):
 
 
 def main():
+    # Libraries (NCCL banners, warnings) may write to stdout; the contract is ONE JSON line there.
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    try:
+        _main(real_stdout)
+    finally:
+        real_stdout.flush()
+
+
+def _main(out):
+    OUT[0] = out
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -234,6 +248,9 @@ def main():
     ap.add_argument("--microbench", default=None, choices=["attention", "gemv", "gemm64"],
                     help="run only one kernel microbenchmark (used for ncu captures) and print its JSON")
     ap.add_argument("--ctx", type=int, default=PROMPT_LEN + 20, help="context length for --microbench attention")
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                    help="dp: every rank decodes its own 64 requests (default); tp: all ranks share ONE batch of 64 "
+                         "(tensor parallel, NCCL all-reduce after the row-parallel projections)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -254,13 +271,13 @@ def main():
         if args.microbench == "attention":
             ms, nbytes, chunk = time_attention_kernel(ops, torch, dev, args.ctx, launches=5)
             print(json.dumps({"kernel": "paged_attention_kernel", "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
-                              "frac": nbytes / ms / 1e6 / peak, "chunk_pages": chunk, "ctx": args.ctx}))
+                              "frac": nbytes / ms / 1e6 / peak, "chunk_pages": chunk, "ctx": args.ctx}), file=out)
         elif args.microbench == "gemv":
             us, nbytes = time_gemv(ops, torch, dev, n_mats=16, iters=1)
-            print(json.dumps({"kernel": "quant_matmul_kernel<1,4>", "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3}))
+            print(json.dumps({"kernel": "quant_matmul_kernel<1,4>", "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3}), file=out)
         else:
             us, nbytes = time_gemv(ops, torch, dev, n=6144, k=3072, m=64, n_mats=16, iters=1)
-            print(json.dumps({"kernel": "umma_w4a16_kernel<64>", "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3}))
+            print(json.dumps({"kernel": "umma_w4a16_kernel<64>", "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3}), file=out)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -280,10 +297,16 @@ def main():
 
     steps_total = args.warmup + 2 * args.steps + 8  # device-resident loop, then the end-to-end loop
     t_setup = time.perf_counter()
-    model, cfg = build_model(gm, torch, dev, steps_total, args.pdl, args.prefill_chunk)
+    tp = args.parallelism == "tp" and world > 1
+    nccl_id = None
+    if tp:
+        box = [gm.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        nccl_id = box[0]
+    model, cfg = build_model(gm, torch, dev, steps_total, args.pdl, args.prefill_chunk, world if tp else 1, rank if tp else 0, nccl_id)
     t_weights = time.perf_counter() - t_setup
 
-    rng = np.random.default_rng(1000 + rank)
+    rng = np.random.default_rng(1000 + (0 if tp else rank))  # a tensor-parallel group shares ONE batch
     t0 = time.perf_counter()
     first = []
     for s in range(BATCH):
@@ -334,15 +357,16 @@ def main():
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
-    tokens = world * BATCH * args.steps
+    tokens = (1 if tp else world) * BATCH * args.steps
     value = tokens / (ms * 1e-3)
     e2e_value = tokens / (e2e_ms * 1e-3)
 
     line = {
         "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak",
         "vs_baseline": None, "dtype": "bf16 activations x int4 weights, f32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "parallelism": f"dp{world} (request-partitioned, no collective)",
+        "config": {"workload": WORKLOAD, "parallelism": (f"tp{world} (one batch of 64; NCCL all-reduce of [64,3072] f32 after o_proj and down_proj)" if tp
+                                   else f"dp{world} (request-partitioned, no collective)"),
                    "context_tokens_during_timing": [PROMPT_LEN + args.warmup, PROMPT_LEN + args.warmup + args.steps],
                    "l2": "inputs larger than L2 (1.8 GB weights + >14 GB KV streamed per step)",
                    "cuda_graph": True, "pdl": bool(args.pdl), "lm_head": "W4A16", "kv_cache": "paged bf16, 16-token pages",
@@ -358,8 +382,8 @@ def main():
         # whole-step roofline: weight + KV bytes per step
         w_bytes = model_weight_bytes(cfg)
         kv_bytes = cfg.n_layers * BATCH * ctx_mid * 4096
-        step_bytes = w_bytes + kv_bytes
-        line["step_roofline"] = {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms / args.steps * 1e-3) / 1e9,
+        step_bytes = (w_bytes + kv_bytes) // (world if tp else 1)  # per GPU
+        line["step_roofline"] = {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_bytes / (ms / args.steps * 1e-3) / 1e9,
                                  "peak_gbs": peak, "frac": step_bytes / (ms / args.steps * 1e-3) / 1e9 / peak,
                                  "peak_kind": peak_kind}
     if rank == 0 and not args.no_extras:
@@ -368,7 +392,8 @@ def main():
         a_ms, a_bytes, chunk = time_attention_kernel(ops, torch, dev, ctx_mid)
         ach = a_bytes / (a_ms * 1e-3) / 1e9
         line["roofline"] = {"kernel": "paged_attention_kernel", "bound": "hbm", "achieved": ach, "peak": peak,
-                            "unit": "GB/s", "frac": ach / peak, "traffic": NCU_TRAFFIC.get("paged_attention_kernel"),
+                            "unit": "GB/s", "frac": ach / peak, "traffic": int(NCU_TRAFFIC["paged_attention_kernel"]["bytes"] * ctx_mid / NCU_TRAFFIC["paged_attention_kernel"]["ctx"]),
+                            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at context 2068 (profiles/paged_attention_kernel_b64_ctx2068.md), scaled by the tokens of this launch",
                             "peak_kind": f"{peak_kind} copy bandwidth", "us_per_launch": a_ms * 1e3,
                             "algorithmic_bytes_per_launch": a_bytes, "chunk_pages": chunk,
                             "units": f"{BATCH} sequences x {ctx_mid} tokens x 4096 B KV (one layer)"}
@@ -391,15 +416,15 @@ def main():
         line["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": res["kind"],
                                 "sample": res["sample"], "host_cores_available": os.cpu_count()}
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), file=out)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
 
 
-# DRAM traffic per launch of the dominant kernel from the committed ncu capture (profiles/), scaled
-# to the bench launch by the tokens processed; None until a capture exists.
-NCU_TRAFFIC: dict = {}
+# DRAM traffic per launch of the dominant kernel from the committed ncu capture (profiles/): batch 64,
+# context 2068: 545,888,768 B read + 8,714,240 B written. It grows in proportion to the visible tokens.
+NCU_TRAFFIC: dict = {"paged_attention_kernel": {"bytes": 545888768 + 8714240, "ctx": 2068}}
 
 
 def lib_stream(model):
