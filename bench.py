@@ -27,6 +27,7 @@ sys.path.insert(0, str(ROOT))
 WORKLOAD = "ministral3b-shaped W4A16-g128 decode, batch 64/GPU, 2048-token prompts prefilled, greedy"
 PROMPT_LEN = 2048
 BATCH = 64
+OUT = [sys.stdout]  # the stream that receives the one JSON line (see main)
 
 
 def _peaks():
@@ -221,7 +222,7 @@ def run_reference_arm(args):
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    print(json.dumps(line), file=OUT[0])
 
 
 def main():
