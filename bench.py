@@ -167,8 +167,10 @@ def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3):
     """W4A16 decode GEMV over a rotating set of distinct weight matrices (working set >> L2)."""
     nbytes = ops.w4a16_packed_bytes(n, k)
     mats = [torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device=dev) for _ in range(n_mats)]
-    for mt in mats:  # fp16 scale bits must stay finite: overwrite the scale tail with 0x1c00-ish values
-        mt[n * k // 2:] = 0x1C
+    half = n * k // 2 + n * (k // 128) * 2  # the buffer holds two layouts, each weights then fp16 scales
+    for mt in mats:  # keep the fp16 scale bits finite
+        mt[n * k // 2:half] = 0x1C
+        mt[half + n * k // 2:] = 0x1C
     x = torch.randn((m, k), dtype=torch.bfloat16, device=dev)
     y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
     for mt in mats[:4]:
@@ -192,7 +194,7 @@ def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3):
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (iters * n_mats)
-    alg = nbytes + 2 * m * k + 2 * m * n
+    alg = nbytes // 2 + 2 * m * k + 2 * m * n  # a launch reads ONE of the two weight layouts
     return us, alg
 
 

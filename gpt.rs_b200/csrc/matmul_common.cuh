@@ -7,12 +7,27 @@
 namespace gptrs {
 
 constexpr int kCtaN = 128;            // output channels per CTA tile
+
+// W4 packed buffer = [A: mma.sync fragment layout][A scales][B: tensor-core row layout][B scales].
+//  A (M <= 16 kernel): 16-row tiles x 64-k chunks, lane-major A fragments; scales [tile][group][16].
+//  B (tcgen05 kernel): 128-row blocks x 64-k chunks x 256 threads x 16 bytes; thread (w, l) of a
+//    block-chunk holds row 16w + (l & 15), k in [32 (l >> 4), +32): four 32-bit words of 8 consecutive
+//    k each (nibble i = k 2i, nibble i+4 = k 2i+1, stored +8), i.e. one 16-byte shared-memory store per
+//    word after dequantisation; scales [block][group][128]. Rows past N are zero.
+__host__ __device__ inline size_t w4_layout_a_bytes(int64_t n, int64_t k) { return (size_t)n * k / 2 + (size_t)n * (k / 128) * 2; }
+__host__ __device__ inline int64_t w4_blocks(int64_t n) { return (n + kCtaN - 1) / kCtaN; }
+__host__ __device__ inline size_t w4_layout_b_weight_bytes(int64_t n, int64_t k) { return (size_t)w4_blocks(n) * kCtaN * k / 2; }
+__host__ __device__ inline size_t w4_layout_b_bytes(int64_t n, int64_t k) {
+    return w4_layout_b_weight_bytes(n, k) + (size_t)w4_blocks(n) * kCtaN * (k / 128) * 2;
+}
 constexpr int kRedStride = kCtaN + 4; // row stride (floats) of the partial tile in shared memory
 
 struct MatmulParams {
     const __nv_bfloat16* x;  // [M][K]
-    const uint4* wq;         // tile-interleaved weights
+    const uint4* wq;         // tile-interleaved weights (layout A)
     const __half* scales;    // W4: [n_tiles][K/128][16]; W8: [n_tiles][16]
+    const uint4* wq_rows;    // W4 layout B (tensor-core kernel)
+    const __half* scales_rows;
     void* y;
     const float* bias;
     const float* residual;

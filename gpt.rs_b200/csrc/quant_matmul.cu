@@ -24,8 +24,18 @@ namespace gptrs {
 
 int umma_w4a16_matmul(MatmulParams p, cudaStream_t st);  // umma_matmul.cu
 int umma_status(int* out);
+int w4_gemv(const MatmulParams& p, cudaStream_t st);  // quant_gemv.cu
 
 namespace {
+
+bool gemv_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("GPTRS_DISABLE_GEMV");
+        v = (e && e[0] == '1') ? 0 : 1;
+    }
+    return v == 1;
+}
 
 bool umma_enabled() {
     static int v = -1;
@@ -320,6 +330,56 @@ __global__ void w4_unpack_kernel(const uint32_t* in_w, const __half* in_s, int64
     }
 }
 
+// Layout B (tensor-core kernel). One thread per 32-bit word.
+__global__ void w4_repack_rows_kernel(const uint8_t* q, const __half* scales, int64_t N, int64_t K, int interleave,
+                                      uint32_t* out_w, __half* out_s) {
+    const int64_t chunks = K / 64, groups = K / 128, blocks = (N + 127) / 128;
+    const int64_t words = blocks * chunks * 256 * 4;
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i < words) {
+        const int j = i & 3, thr = (i >> 2) & 255;
+        const int64_t chunk = (i >> 10) % chunks, blk = (i >> 10) / chunks;
+        const int w = thr >> 5, l = thr & 31;
+        const int64_t row = blk * 128 + w * 16 + (l & 15);
+        const int64_t k0 = chunk * 64 + (l >> 4) * 32 + j * 8;
+        uint32_t v = 0x88888888u;  // zeros once the +8 bias is removed
+        if (row < N) {
+            const int64_t src = source_row(row, N, interleave);
+            v = 0;
+            for (int e = 0; e < 4; ++e) {
+                v |= nib_at(q, src, k0 + 2 * e, K) << (4 * e);
+                v |= nib_at(q, src, k0 + 2 * e + 1, K) << (4 * e + 16);
+            }
+        }
+        out_w[i] = v;
+    }
+    if (i < blocks * groups * 128) {
+        const int r = i & 127;
+        const int64_t grp = (i >> 7) % groups, blk = (i >> 7) / groups;
+        const int64_t row = blk * 128 + r;
+        out_s[i] = row < N ? scales[source_row(row, N, interleave) * groups + grp] : __float2half(0.f);
+    }
+}
+
+__global__ void w4_unpack_rows_kernel(const uint32_t* in_w, const __half* in_s, int64_t N, int64_t K, int interleave,
+                                      uint8_t* q, __half* scales) {
+    const int64_t chunks = K / 64, groups = K / 128;
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i < N * (K / 2)) {
+        const int64_t row = i / (K / 2), kp = i % (K / 2), k = kp * 2;
+        const int64_t blk = row >> 7, chunk = k / 64;
+        const int r = row & 127, w = r >> 4, kk = k & 63, half = kk >> 5, j = (kk & 31) >> 3, e = (kk & 7) >> 1;
+        const int thr = w * 32 + half * 16 + (r & 15);
+        const uint32_t v = in_w[((blk * chunks + chunk) * 256 + thr) * 4 + j];
+        const uint32_t v0 = (v >> (4 * e)) & 15, v1 = (v >> (4 * e + 16)) & 15;
+        q[source_row(row, N, interleave) * (K / 2) + kp] = (uint8_t)(((v0 + 8) & 15) | (((v1 + 8) & 15) << 4));
+    }
+    if (i < N * groups) {
+        const int64_t row = i / groups, grp = i % groups;
+        scales[source_row(row, N, interleave) * groups + grp] = in_s[((row >> 7) * groups + grp) * 128 + (row & 127)];
+    }
+}
+
 // Packed W8: [tile][K/32][lane][16 bytes]; byte order = A-fragment register order.
 __global__ void w8_repack_kernel(const int8_t* q, const __half* scales, int64_t N, int64_t K, int interleave,
                                  uint8_t* out_w, __half* out_s) {
@@ -460,6 +520,11 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
     p.wq = static_cast<const uint4*>(d_packed);
     size_t wbytes = (BITS == 4) ? (size_t)n * k / 2 : (size_t)n * k;
     p.scales = reinterpret_cast<const __half*>(static_cast<const unsigned char*>(d_packed) + wbytes);
+    if (BITS == 4) {
+        const unsigned char* base_b = static_cast<const unsigned char*>(d_packed) + w4_layout_a_bytes(n, k);
+        p.wq_rows = reinterpret_cast<const uint4*>(base_b);
+        p.scales_rows = reinterpret_cast<const __half*>(base_b + w4_layout_b_weight_bytes(n, k));
+    }
     p.y = d_y;
     p.M = (int)m; p.N = (int)n; p.K = (int)k;
     p.out_f32 = 0;
@@ -478,6 +543,10 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
     const int n_blocks = ceil_div(n, kCtaN);
     p.n_split = pick_split(n_blocks, groups);
     p.groups_per_cta = groups / p.n_split;
+    if (BITS == 4 && m <= 16 && gemv_enabled()) {
+        int rc = w4_gemv(p, st);
+        if (rc != GPTRS_UNIMPLEMENTED) return rc;
+    }
     dim3 grid(n_blocks, p.n_split, ceil_div(m, 64));
     const int64_t m_eff = m > 64 ? 64 : m;
     auto smem_for = [](int mt) {
@@ -500,7 +569,7 @@ extern "C" {
 
 size_t gptrs_cuda_w4a16_packed_bytes(int64_t n, int64_t k) {
     if (n <= 0 || k <= 0 || (n % 16) || (k % 128)) return 0;
-    return (size_t)n * k / 2 + (size_t)n * (k / 128) * 2;
+    return w4_layout_a_bytes(n, k) + w4_layout_b_bytes(n, k);
 }
 size_t gptrs_cuda_w8a16_packed_bytes(int64_t n, int64_t k) {
     if (n <= 0 || k <= 0 || (n % 16) || (k % 128)) return 0;
@@ -517,6 +586,24 @@ int gptrs_cuda_w4a16_repack(const uint8_t* d_q, const uint16_t* d_scales, int64_
     __half* os = reinterpret_cast<__half*>(static_cast<unsigned char*>(d_packed) + (size_t)n * k / 2);
     w4_repack_kernel<<<ceil_div(words, 256), 256, 0, as_stream(stream)>>>(
         d_q, reinterpret_cast<const __half*>(d_scales), n, k, interleave, ow, os);
+    GPTRS_CUDA_OK(cudaGetLastError());
+    unsigned char* base_b = static_cast<unsigned char*>(d_packed) + w4_layout_a_bytes(n, k);
+    const int64_t words_b = w4_blocks(n) * kCtaN * k / 8;
+    w4_repack_rows_kernel<<<ceil_div(words_b, 256), 256, 0, as_stream(stream)>>>(
+        d_q, reinterpret_cast<const __half*>(d_scales), n, k, interleave, reinterpret_cast<uint32_t*>(base_b),
+        reinterpret_cast<__half*>(base_b + w4_layout_b_weight_bytes(n, k)));
+    GPTRS_CUDA_OK(cudaGetLastError());
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_w4a16_unpack_rows(const void* d_packed, int64_t n, int64_t k, int interleave, uint8_t* d_q,
+                                 uint16_t* d_scales, void* stream) {
+    GPTRS_REQUIRE(d_q && d_scales && d_packed, "null pointer");
+    GPTRS_REQUIRE(n > 0 && k > 0 && n % 16 == 0 && k % 128 == 0, "N % 16 == 0 and K % 128 == 0 required");
+    const unsigned char* base_b = static_cast<const unsigned char*>(d_packed) + w4_layout_a_bytes(n, k);
+    w4_unpack_rows_kernel<<<ceil_div(n * k / 2, 256), 256, 0, as_stream(stream)>>>(
+        reinterpret_cast<const uint32_t*>(base_b), reinterpret_cast<const __half*>(base_b + w4_layout_b_weight_bytes(n, k)),
+        n, k, interleave, d_q, reinterpret_cast<__half*>(d_scales));
     GPTRS_CUDA_OK(cudaGetLastError());
     return GPTRS_OK;
 }

@@ -5,9 +5,10 @@
 // crates/gpt-rs/src/ops/functional/linalg.rs:109-127, on quantised Linear weights).
 //
 // One CTA computes a 128 (output channels) x BN (batch rows) tile over its K range:
-//   warps 0-7  stream the packed int4 weights from HBM to registers (prefetch ring), dequantise
-//              them to bf16 (exact integer, then one bf16 multiply by the group scale) and store
-//              them into shared memory in the canonical K-major 128-byte-swizzled operand layout;
+//   warps 0-7  stream the packed int4 weights (row-ordered layout B: 32 consecutive k of one row per
+//              thread and stage) from HBM to registers (prefetch ring), dequantise them to bf16 (exact
+//              integer, then one bf16 multiply by the group scale) and store them, 16 bytes at a time,
+//              into shared memory in the canonical K-major 128-byte-swizzled operand layout;
 //              afterwards they run the epilogue (TMEM -> registers -> shared tile),
 //   warp 8     issues one TMA tensor copy of the x tile [BN x 64] per stage (hardware swizzle,
 //              rows past M are zero-filled), and owns the TMEM allocation,
@@ -63,6 +64,14 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
                  : "memory");
 }
+// Bounded wait that backs off between polls (for waiters that are not on the critical path).
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(40);
+    }
+    return false;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
@@ -103,9 +112,13 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_cta0 = blockIdx.x * kCtaN;
     const int m0 = blockIdx.z * BN;
-    const int n_it = p.groups_per_cta * 2;                  // 64-wide stages of this CTA
-    const int chunk0 = blockIdx.y * p.groups_per_cta * 2;   // first 64-k chunk of this CTA
     const int chunks_total = p.K / kBlockK;
+    const int groups_total = p.K / 128;
+    // K range of this CTA in 128-k groups: [g0, g1) (split as evenly as the group count allows)
+    const int g0 = (int)(((int64_t)blockIdx.y * groups_total) / p.n_split);
+    const int g1 = (int)(((int64_t)(blockIdx.y + 1) * groups_total) / p.n_split);
+    const int n_it = (g1 - g0) * 2;   // 64-wide stages of this CTA
+    const int chunk0 = g0 * 2;        // first 64-k chunk of this CTA
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -128,63 +141,53 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     bool failed = false;
 
     if (warp < kProducerWarps) {
-        // ---------------- dequant producers: warp w owns 16-channel tile w of the CTA's 8 --------
-        const int g = lane >> 2, t = lane & 3;
-        const int n_tiles_total = p.N >> 4;
-        const int tile = blockIdx.x * 8 + warp;
-        const bool tv = tile < n_tiles_total;
-        const size_t tl = tv ? tile : 0;
-        const uint4* wp = p.wq + (tl * chunks_total + chunk0) * 32 + lane;
-        const uint32_t* sp = reinterpret_cast<const uint32_t*>(p.scales) + (tl * (chunks_total / 2) + chunk0 / 2) * 8 + g;
+        // ---------------- dequant producers: thread (warp, lane) owns row 16*warp + (lane & 15), ----
+        // ---------------- k half (lane >> 4) of every 64-wide stage (weight layout B) ---------------
+        const int row = warp * 16 + (lane & 15), half = lane >> 4;
+        const uint4* wp = p.wq_rows + ((size_t)blockIdx.x * chunks_total + chunk0) * 256 + tid;
+        const __half* sp = p.scales_rows + ((size_t)blockIdx.x * (chunks_total / 2) + chunk0 / 2) * kCtaN + row;
         uint4 ring[kRing];
-        uint32_t sring[kRing];
+        __half sring[kRing];
 #pragma unroll
         for (int r = 0; r < kRing; ++r) {
-            ring[r] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // zeros after -8
-            sring[r] = 0;
-            if (tv && r < n_it) {
-                ring[r] = ldg_stream_16(wp + (size_t)r * 32);
-                sring[r] = __ldg(sp + (r >> 1) * 8);
+            ring[r] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+            sring[r] = __float2half(0.f);
+            if (r < n_it) {
+                ring[r] = ldg_stream_16(wp + (size_t)r * 256);
+                sring[r] = __ldg(sp + (size_t)((chunk0 + r) / 2 - chunk0 / 2) * kCtaN);
             }
         }
         pdl_wait();
         const __nv_bfloat162 c136 = __floats2bfloat162_rn(136.f, 136.f);
-        const int row = warp * 16 + g;  // row & 7 == g for row and row + 8
+        unsigned char* const row_base = sA + row * 128;
+        const int sw = row & 7;
         for (int it0 = 0; it0 < n_it && !failed; it0 += kRing) {
 #pragma unroll
             for (int r = 0; r < kRing; ++r) {
                 const int it = it0 + r;
                 if (it < n_it && !failed) {
                     const int s = it % kStages;
-                    if (!mbar_wait_bounded(&empty_bar[s], ((it / kStages) & 1) ^ 1)) { failed = true; }
+                    if (!mbar_wait_relaxed(&empty_bar[s], ((it / kStages) & 1) ^ 1)) { failed = true; }
                     const uint4 cur = ring[r];
-                    const uint32_t csc = sring[r];
-                    if (tv && it + kRing < n_it) {
-                        ring[r] = ldg_stream_16(wp + (size_t)(it + kRing) * 32);
-                        sring[r] = __ldg(sp + ((it + kRing) >> 1) * 8);
+                    const __nv_bfloat162 sc = __float2bfloat162_rn(__half2float(sring[r]));
+                    if (it + kRing < n_it) {
+                        ring[r] = ldg_stream_16(wp + (size_t)(it + kRing) * 256);
+                        sring[r] = __ldg(sp + (size_t)((chunk0 + it + kRing) / 2 - chunk0 / 2) * kCtaN);
                     }
-                    const __half2 sc = *reinterpret_cast<const __half2*>(&csc);
-                    const __nv_bfloat162 s_lo = __float2bfloat162_rn(__low2float(sc));
-                    const __nv_bfloat162 s_hi = __float2bfloat162_rn(__high2float(sc));
-                    unsigned char* r_lo = sA + s * kABytes + row * 128 + 4 * t;
-                    unsigned char* r_hi = r_lo + 8 * 128;
+                    unsigned char* dst = row_base + s * kABytes;
                     const uint32_t q4[4] = {cur.x, cur.y, cur.z, cur.w};
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint32_t q = q4[ks];
-                        uint32_t v[4];
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t q = q4[j];
+                        uint4 v;
+                        uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;
-                            __nv_bfloat162 d = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136);
-                            d = __hmul2(d, (i & 1) ? s_hi : s_lo);
-                            v[i] = *reinterpret_cast<uint32_t*>(&d);
+                            uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;   // (k 2i, k 2i+1) + 128
+                            __nv_bfloat162 d = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136), sc);
+                            vv[i] = *reinterpret_cast<uint32_t*>(&d);
                         }
-                        const int c0 = ((2 * ks) ^ g) << 4, c1 = ((2 * ks + 1) ^ g) << 4;
-                        *reinterpret_cast<uint32_t*>(r_lo + c0) = v[0];  // row g,   k = 16ks + 2t, +1
-                        *reinterpret_cast<uint32_t*>(r_hi + c0) = v[1];  // row g+8, same k
-                        *reinterpret_cast<uint32_t*>(r_lo + c1) = v[2];  // row g,   k + 8
-                        *reinterpret_cast<uint32_t*>(r_hi + c1) = v[3];  // row g+8, k + 8
+                        *reinterpret_cast<uint4*>(dst + (((half * 4 + j) ^ sw) << 4)) = v;   // 8 consecutive k
                     }
                     fence_proxy_async();
                     mbar_arrive(&full_bar[s]);
@@ -197,7 +200,7 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
         if (lane == 0) {
             for (int it = 0; it < n_it; ++it) {
                 const int s = it % kStages;
-                if (!mbar_wait_bounded(&empty_bar[s], ((it / kStages) & 1) ^ 1)) { failed = true; break; }
+                if (!mbar_wait_relaxed(&empty_bar[s], ((it / kStages) & 1) ^ 1)) { failed = true; break; }
                 mbar_expect_tx(&full_bar[s], kBBytes);
                 tma_load_2d(sB + s * kBBytes, &x_map, (chunk0 + it) * kBlockK, m0, &full_bar[s]);
             }
@@ -228,7 +231,7 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     // ---------------- epilogue: TMEM -> registers -> shared tile [BN][kRedStride] ----------------
     float* red = reinterpret_cast<float*>(smem);
     if (warp < kProducerWarps) {
-        if (!mbar_wait_bounded(&done_bar, 0)) failed = true;
+        if (!mbar_wait_relaxed(&done_bar, 0)) failed = true;
         tc_fence_after();
         // warp w reads TMEM lanes 32*(w % 4); warps 0-3 take the low half of the columns, 4-7 the high half
         const int quarter = warp & 3;
@@ -330,17 +333,15 @@ int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
 int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
     const int groups = p.K / 128;
     const int n_blocks = ceil_div(p.N, kCtaN);
-    static int pct = 0;  // CTAs per 100 SMs aimed at by the K split (GPTRS_UMMA_CTAS_PCT overrides)
-    if (pct == 0) { const char* e = getenv("GPTRS_UMMA_CTAS_PCT"); pct = e ? atoi(e) : 120; if (pct <= 0) pct = 120; }
-    const int target = sm_count() * pct / 100;
-    int split = 1;
-    for (int s = 1; s <= 8; s *= 2) {
-        if (groups % s != 0) break;
-        split = s;
-        if (n_blocks * s >= target) break;
-    }
+    // K split (cluster size 1..8, any integer): about 2.5 CTAs per SM measured fastest on a decode step; the CTAs of a
+    // cluster are co-scheduled and meet at the reduction.
+    static int pct = 0;  // CTAs per 100 SMs (GPTRS_UMMA_CTAS_PCT overrides the default of 250)
+    if (pct == 0) { const char* e = getenv("GPTRS_UMMA_CTAS_PCT"); pct = e ? atoi(e) : 250; if (pct <= 0) pct = 250; }
+    int split = (sm_count() * pct / 100) / n_blocks;
+    split = split < 1 ? 1 : (split > 8 ? 8 : split);
+    if (split > groups) split = groups;
     p.n_split = split;
-    p.groups_per_cta = groups / split;
+    p.groups_per_cta = (groups + split - 1) / split;
     if (p.M <= 64) return launch_umma<64>(p, dim3(n_blocks, split, 1), st);
     if (p.M <= 128) return launch_umma<128>(p, dim3(n_blocks, split, 1), st);
     return launch_umma<256>(p, dim3(n_blocks, split, ceil_div(p.M, 256)), st);

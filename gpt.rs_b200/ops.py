@@ -50,6 +50,14 @@ def w4a16_unpack(packed: torch.Tensor, n: int, k: int, interleave_gate_up: bool 
     return q, s
 
 
+def w4a16_unpack_rows(packed: torch.Tensor, n: int, k: int, interleave_gate_up: bool = False):
+    """Reads the row-ordered (tensor-core) copy of a packed W4 buffer back to canonical form."""
+    q = torch.empty((n, k // 2), dtype=torch.uint8, device=packed.device)
+    s = torch.empty((n, k // 128), dtype=torch.float16, device=packed.device)
+    check(lib().gptrs_cuda_w4a16_unpack_rows(_ptr(packed), n, k, int(interleave_gate_up), _ptr(q), _ptr(s), _stream()))
+    return q, s
+
+
 def w8a16_repack(q: torch.Tensor, scales: torch.Tensor, n: int, k: int, interleave_gate_up: bool = False):
     nbytes = w8a16_packed_bytes(n, k)
     if nbytes == 0:

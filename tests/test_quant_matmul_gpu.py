@@ -30,9 +30,10 @@ def test_w4_repack_unpack_bit_exact(cuda, n, k):
     p, s = _w4_case(rng, n, k)
     for inter in (False, True) if n % 32 == 0 else (False,):
         packed = ops.w4a16_repack(_dev(p, cuda), _dev(s, cuda), n, k, inter)
-        q2, s2 = ops.w4a16_unpack(packed, n, k, inter)
-        assert np.array_equal(q2.cpu().numpy(), p)
-        assert np.array_equal(s2.cpu().numpy().view(np.uint16), s.view(np.uint16))
+        for unpack in (ops.w4a16_unpack, ops.w4a16_unpack_rows):  # both layouts held by the buffer
+            q2, s2 = unpack(packed, n, k, inter)
+            assert np.array_equal(q2.cpu().numpy(), p)
+            assert np.array_equal(s2.cpu().numpy().view(np.uint16), s.view(np.uint16))
 
 
 @pytest.mark.parametrize("n,k", [(16, 128), (48, 384), (3072, 3072)])
