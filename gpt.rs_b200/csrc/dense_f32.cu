@@ -41,6 +41,7 @@ __global__ void __launch_bounds__(kSgWarps * 32) sgemm_smallm_kernel(const Sgemm
     const int kn = min(p.k_per_cta, p.K - kb);
     const int m0 = blockIdx.z * MT;
 
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     for (int i = tid; i < MT * kn; i += kSgWarps * 32) {
         int m = i / kn, k = i % kn;
@@ -88,7 +89,6 @@ __global__ void __launch_bounds__(kSgWarps * 32) sgemm_smallm_kernel(const Sgemm
             for (int j = 0; j < 4; ++j) acc[m][j] = fmaf(xv, wv[j], acc[m][j]);
         }
     }
-    pdl_launch_dependents();
 #pragma unroll
     for (int m = 0; m < MT; ++m)
 #pragma unroll
@@ -144,6 +144,7 @@ struct KvAppendF32Params {
 };
 __global__ void kv_append_f32_kernel(const KvAppendF32Params p) {
     const int b = blockIdx.x;
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const int pos = min(max(p.positions[b], 0), p.capacity - 1);  // DynamicUpdateSlice clamps its start
     const int width = (p.Hq + 2 * p.Hkv) * p.hd;
@@ -175,6 +176,7 @@ __global__ void __launch_bounds__(128) attention_f32_kernel(const AttnF32Params 
     float* sc = at_smem + p.hd;       // [len]
     __shared__ float sh[32];
     const int hq = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const int pos = min(max(p.positions[b], 0), p.capacity - 1);
     const int len = pos + 1;
@@ -212,7 +214,6 @@ __global__ void __launch_bounds__(128) attention_f32_kernel(const AttnF32Params 
     if ((tid & 31) == 0) sh[8 + (tid >> 5)] = sum;
     __syncthreads();
     sum = sh[8] + sh[9] + sh[10] + sh[11];
-    pdl_launch_dependents();
     // out[c] = sum_j p_j V[j][c]: thread (part, c) walks tokens part, part+parts, ...
     const int parts = 128 / p.hd > 0 ? 128 / p.hd : 1;  // hd <= 128
     const int c = tid % p.hd, part = tid / p.hd;

@@ -281,6 +281,7 @@ __global__ void rope_f32_inplace_kernel(float* qkv, const int* positions, const 
                                         int n_rot_heads, int width, int hd, int half) {
     // one CTA per (head, token); rotates pairs (c, c + half), c < half
     const int head = blockIdx.x, b = blockIdx.y;
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const int pos = positions[b];
     float* x = qkv + (size_t)b * width + head * hd;
@@ -295,6 +296,7 @@ __global__ void rope_f32_inplace_kernel(float* qkv, const int* positions, const 
 
 struct GatherParams { const void* src; void* dst; const int* rows; int n_rows, row_bytes; };
 __global__ void gather_rows_kernel(const GatherParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const unsigned char* s = static_cast<const unsigned char*>(p.src) + (size_t)p.rows[blockIdx.x] * p.row_bytes;
     unsigned char* d = static_cast<unsigned char*>(p.dst) + (size_t)blockIdx.x * p.row_bytes;
@@ -304,6 +306,7 @@ __global__ void gather_rows_kernel(const GatherParams p) {
 
 struct TpPickParams { const float* vals; const int* idx; int* out; int rows, tp, vocab_l; };
 __global__ void tp_pick_kernel(const TpPickParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= p.rows) return;
@@ -318,6 +321,7 @@ __global__ void tp_pick_kernel(const TpPickParams p) {
 
 struct AdvanceParams { int* pos; int* ctx; int n; };
 __global__ void advance_kernel(const AdvanceParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < p.n) { p.pos[i] += 1; p.ctx[i] += 1; }

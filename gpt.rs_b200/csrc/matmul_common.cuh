@@ -38,43 +38,67 @@ struct MatmulParams {
     int swiglu;
 };
 
-// Every CTA of the cluster has written its partial tile red[MPAD][kRedStride] (row = batch row,
-// column = output channel of the CTA tile). CTA r of the cluster sums rows with row % S == r over
-// all peers through distributed shared memory, applies bias / residual / SwiGLU and stores.
-// Must be called by all `n_threads` threads of every CTA of the cluster.
-template <int MPAD>
-__device__ __forceinline__ void reduce_and_store_tile(const MatmulParams& p, float* red, int tid, int n_threads,
-                                                      int m0, int n_cta0) {
-    const int S = p.n_split;
-    uint32_t my_rank = 0;
-    if (S > 1) {
-        my_rank = cluster_ctarank();
-        cluster_sync_all();
-    } else {
-        __syncthreads();
+// ---- split-K reduction across the CTAs of a cluster: push, one barrier, local sum -------------------
+// Output row m of the CTA tile is owned by cluster rank m % S. Every CTA writes ("pushes") its partial
+// values straight into the owner's shared memory with st.shared::cluster (fire and forget, no remote
+// read latency); after ONE cluster barrier each owner sums the S contributions of its rows from local
+// shared memory, applies the epilogue and stores. The receive slots are a dedicated region
+// [S][rows_max][kRedStride] f32 (never aliased with pipeline stages: a fast peer may push while the
+// owner is still in its main loop). split_reduce_begin() must run at kernel start on every thread: it
+// arrives on the "everybody has started" barrier that remote writes have to wait for.
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+
+__host__ __device__ inline size_t split_slots_bytes(int mpad, int n_split) {
+    return (size_t)n_split * ((mpad + n_split - 1) / n_split) * kRedStride * sizeof(float);
+}
+
+struct SplitReduce {
+    uint32_t slots_addr;
+    int S, rank, rows_max;
+    __device__ __forceinline__ void begin(const MatmulParams& p) {
+        S = p.n_split;
+        rank = 0;
+        if (S > 1) { rank = (int)cluster_ctarank(); cluster_arrive(); }
     }
-    const uint32_t red_addr = smem_u32(red);
-    // Sum of one float4 of the tile over the cluster; all S remote loads are issued before any add.
-    auto gather = [&](uint32_t off) {
-        float4 u[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-            if (r < S) u[r] = ld_dsmem_f4(map_to_cta(red_addr + off, r));
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-            if (r < S) { v.x += u[r].x; v.y += u[r].y; v.z += u[r].z; v.w += u[r].w; }
+    // call once, by every thread, after the main loop and before the first push
+    __device__ __forceinline__ void ready(float* slots, int mpad) {
+        slots_addr = smem_u32(slots);
+        rows_max = (mpad + S - 1) / S;
+        if (S > 1) cluster_wait();
+    }
+    // element (m, c) of this CTA's partial tile; owner = m % S, local row = m / S (passed in)
+    __device__ __forceinline__ void push(int owner, int local_row, int c, float v) const {
+        const uint32_t a = slots_addr + (uint32_t)(((rank * rows_max + local_row) * kRedStride + c) * 4);
+        if (S > 1) st_cluster_f32(map_to_cta(a, (uint32_t)owner), v);
+        else asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(a), "f"(v) : "memory");
+    }
+};
+
+// Second half: barrier, local sum over the S slots, bias / residual / SwiGLU, store. All threads of the CTA.
+template <int MPAD>
+__device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const SplitReduce& sr, const float* slots, int tid,
+                                                    int n_threads, int m0, int n_cta0) {
+    const int S = sr.S, rank = sr.rank, rows_max = sr.rows_max;
+    if (S > 1) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+    auto gather = [&](int local_row, int c) {
+        float4 v = *reinterpret_cast<const float4*>(slots + (size_t)local_row * kRedStride + c);
+        for (int k = 1; k < S; ++k) {
+            const float4 u = *reinterpret_cast<const float4*>(slots + ((size_t)k * rows_max + local_row) * kRedStride + c);
+            v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+        }
         return v;
     };
-    const int rows_own = (MPAD - (int)my_rank + S - 1) / S;  // rows my_rank, my_rank + S, ...
+    const int rows_own = (MPAD - rank + S - 1) / S;  // rows rank, rank + S, ...
     if (!p.swiglu) {
         for (int j = tid; j < rows_own * 32; j += n_threads) {
-            const int row = (int)my_rank + S * (j >> 5), c4 = j & 31;
-            const int m = m0 + row, n = n_cta0 + c4 * 4;
+            const int lr = j >> 5, c4 = j & 31;
+            const int m = m0 + rank + S * lr, n = n_cta0 + c4 * 4;
             if (m >= p.M || n >= p.N) continue;
-            float4 v;
-            if (S > 1) v = gather((uint32_t)(row * kRedStride + c4 * 4) * 4);
-            else v = *reinterpret_cast<const float4*>(red + row * kRedStride + c4 * 4);
+            float4 v = gather(lr, c4 * 4);
             if (p.bias) {
                 float4 b = *reinterpret_cast<const float4*>(p.bias + n);
                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
@@ -94,19 +118,12 @@ __device__ __forceinline__ void reduce_and_store_tile(const MatmulParams& p, flo
         // Each 16-channel tile holds 8 gate rows followed by the 8 matching up rows.
         const int NO = p.N >> 1;
         for (int j = tid; j < rows_own * 16; j += n_threads) {
-            const int row = (int)my_rank + S * (j >> 4), q = j & 15;
+            const int lr = j >> 4, q = j & 15;
             const int tile = q >> 1, half = q & 1;
-            const int m = m0 + row, n_out = (n_cta0 >> 1) + tile * 8 + half * 4;
+            const int m = m0 + rank + S * lr, n_out = (n_cta0 >> 1) + tile * 8 + half * 4;
             if (m >= p.M || n_out >= NO) continue;
             const int cg = tile * 16 + half * 4;
-            float4 gt, up;
-            if (S > 1) {
-                gt = gather((uint32_t)(row * kRedStride + cg) * 4);
-                up = gather((uint32_t)(row * kRedStride + cg + 8) * 4);
-            } else {
-                gt = *reinterpret_cast<const float4*>(red + row * kRedStride + cg);
-                up = *reinterpret_cast<const float4*>(red + row * kRedStride + cg + 8);
-            }
+            const float4 gt = gather(lr, cg), up = gather(lr, cg + 8);
             float4 v;
             v.x = gt.x / (1.f + expf(-gt.x)) * up.x;
             v.y = gt.y / (1.f + expf(-gt.y)) * up.y;
@@ -120,7 +137,6 @@ __device__ __forceinline__ void reduce_and_store_tile(const MatmulParams& p, flo
             }
         }
     }
-    if (S > 1) cluster_sync_all();  // keep every CTA's tile alive until all peers have read it
 }
 
 }  // namespace gptrs

@@ -57,6 +57,7 @@ struct NormParams {
 __global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams p) {
     __shared__ float sh[32];
     const int row = blockIdx.x, tid = threadIdx.x;
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     float* h = p.hidden + (size_t)row * p.D;
     constexpr int kKeep = 16;
@@ -104,7 +105,6 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams
         const float ms = block_sum(sum, sh) * inv_n;
         inv = 1.f / sqrtf(ms + p.eps);
     }
-    pdl_launch_dependents();
     if (tid == 0) {
         if (p.stat0) p.stat0[row] = p.layer_norm ? mean : inv;
         if (p.stat1 && p.layer_norm) p.stat1[row] = inv;
@@ -135,6 +135,7 @@ struct EmbedParams {
 
 __global__ void __launch_bounds__(256) embedding_kernel(const EmbedParams p) {
     const int row = blockIdx.x;
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const int id = p.ids[row];
     const bool ok = id >= 0 && id < p.V;
@@ -145,7 +146,6 @@ __global__ void __launch_bounds__(256) embedding_kernel(const EmbedParams p) {
         pok = pid >= 0 && pid < p.P;
     }
     if ((!ok || !pok) && threadIdx.x == 0) atomicExch(p.status, 2);
-    pdl_launch_dependents();
     for (int i = threadIdx.x; i < p.D; i += blockDim.x) {
         float v = 0.f;
         if (ok)
@@ -167,6 +167,7 @@ struct EwParams {
     int op;
 };
 __global__ void elementwise_kernel(const EwParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n) return;
@@ -188,6 +189,7 @@ struct SoftmaxParams {
 };
 __global__ void __launch_bounds__(256) softmax_kernel(const SoftmaxParams p) {
     __shared__ float sh[32];
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const float* x = p.x + (size_t)blockIdx.x * p.n;
     float* o = p.out + (size_t)blockIdx.x * p.n;
@@ -218,6 +220,7 @@ __device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
 __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const int row = blockIdx.x;
     const float* x = p.logits + (size_t)row * p.vocab;

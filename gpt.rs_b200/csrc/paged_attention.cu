@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
     const int g = lane >> 2, t = lane & 3;
     const int group = p.Hq / p.Hkv;
 
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const int len = p.ctx_len[b];
     const int chunk_tokens = p.chunk_pages * kPageTokens;
@@ -181,7 +182,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
             issue(j + kDepth);
         }
     }
-    pdl_launch_dependents();
     if (failed && lane == 0) atomicExch(p.status, 1);
 
     // ---- merge the 4 warps (rows g < group live in lanes 0..15 when group <= 4, else all) ---
@@ -235,6 +235,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
 // One CTA per (token, query head): merges the splits written by paged_attention_kernel.
 __global__ void __launch_bounds__(128) attention_combine_kernel(const AttnParams p) {
     const int b = blockIdx.x, hq = blockIdx.y, c = threadIdx.x;
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const int len = p.ctx_len[b];
     const int chunk_tokens = p.chunk_pages * kPageTokens;
@@ -249,7 +250,6 @@ __global__ void __launch_bounds__(128) attention_combine_kernel(const AttnParams
         L += p.part_ml[(base + s) * 2 + 1] * f;
         acc += p.part_o[(base + s) * kHD + c] * f;
     }
-    pdl_launch_dependents();
     p.out[((size_t)b * p.Hq + hq) * kHD + c] = __float2bfloat16_rn(acc / L);
 }
 
@@ -269,6 +269,7 @@ struct RopeAppendParams {
 
 __global__ void __launch_bounds__(64) rope_append_kernel(const RopeAppendParams p) {
     const int head = blockIdx.x, b = blockIdx.y, i = threadIdx.x;  // i: channel pair (i, i + 64)
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const int pos = p.positions[b];
     const int width = (p.Hq + 2 * p.Hkv) * kHD;
@@ -295,7 +296,6 @@ __global__ void __launch_bounds__(64) rope_append_kernel(const RopeAppendParams 
             x2 = rot(i + 64, x2);
         }
     }
-    pdl_launch_dependents();
     const __nv_bfloat16 y1 = __float2bfloat16_rn(x1), y2 = __float2bfloat16_rn(x2);
     if (head < p.Hq) {
         __nv_bfloat16* dst = p.q_out + ((size_t)b * p.Hq + head) * kHD;

@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(kGvWarps * 32, 2) w4_gemv_kernel(const MatmulP
     extern __shared__ __align__(1024) unsigned char smem[];  // block addresses need zero bits 4..7 (XOR stepping)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    SplitReduce sr;
+    sr.begin(p);  // arrives on the cluster's "started" barrier; pushes wait for it
     const int g = lane >> 2, t = lane & 3;
     const int n_tile = blockIdx.x * kGvWarps + warp;
     const bool tile_valid = n_tile < (p.N >> 4);
@@ -53,6 +55,7 @@ __global__ void __launch_bounds__(kGvWarps * 32, 2) w4_gemv_kernel(const MatmulP
         }
     }
 
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     // ---- all activation rows of this CTA's K range -> shared memory -------------------------------
     for (int idx = tid; idx < G * MPAD * 16; idx += kGvWarps * 32) {
@@ -129,19 +132,22 @@ __global__ void __launch_bounds__(kGvWarps * 32, 2) w4_gemv_kernel(const MatmulP
             }
         }
     }
-    pdl_launch_dependents();
 
-    // ---- partial tile -> shared memory (behind the x blocks), cluster reduction, epilogue -------------
-    float* red = reinterpret_cast<float*>(smem + (size_t)G * kBlockBytes);
+    // ---- partial tile -> pushed to the owner CTA of each row (slots behind the x blocks) ---------------
+    float* slots = reinterpret_cast<float*>(smem + (size_t)G * kBlockBytes);
+    sr.ready(slots, MPAD);
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
-        const int m = i * 8 + 2 * t, c = warp * 16 + g;
-        red[m * kRedStride + c] = acc[i][0];
-        red[(m + 1) * kRedStride + c] = acc[i][1];
-        red[m * kRedStride + c + 8] = acc[i][2];
-        red[(m + 1) * kRedStride + c + 8] = acc[i][3];
+        const int c = warp * 16 + g;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int m = i * 8 + 2 * t + h;
+            const int owner = m % sr.S, lr = m / sr.S;
+            sr.push(owner, lr, c, acc[i][h]);
+            sr.push(owner, lr, c + 8, acc[i][2 + h]);
+        }
     }
-    reduce_and_store_tile<MPAD>(p, red, tid, kGvWarps * 32, 0, blockIdx.x * kCtaN);
+    split_reduce_finish<MPAD>(p, sr, slots, tid, kGvWarps * 32, 0, blockIdx.x * kCtaN);
 }
 
 template <int MT>
@@ -161,7 +167,7 @@ int launch_gemv(const MatmulParams& p, dim3 grid, size_t smem, cudaStream_t st) 
 // Returns GPTRS_UNIMPLEMENTED when the CTA's activation rows do not fit shared memory.
 int w4_gemv(const MatmulParams& p, cudaStream_t st) {
     const int mt = p.M <= 8 ? 1 : 2;
-    const size_t smem = (size_t)p.groups_per_cta * mt * 8 * 256 + (size_t)mt * 8 * kRedStride * 4;
+    const size_t smem = (size_t)p.groups_per_cta * mt * 8 * 256 + (size_t)(mt * 8 + 7) * kRedStride * 4;
     if (p.M > 16 || smem > 200 * 1024) return GPTRS_UNIMPLEMENTED;
     dim3 grid(ceil_div(p.N, kCtaN), p.n_split, 1);
     return mt == 1 ? launch_gemv<1>(p, grid, smem, st) : launch_gemv<2>(p, grid, smem, st);

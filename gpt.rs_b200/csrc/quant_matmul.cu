@@ -80,6 +80,8 @@ quant_matmul_kernel(const MatmulParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int tid = threadIdx.x;
+    SplitReduce sr;
+    sr.begin(p);  // arrives on the cluster's "started" barrier; pushes wait for it
     const int warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int m0 = blockIdx.z * 64;                      // batch rows handled by this CTA
@@ -129,6 +131,7 @@ quant_matmul_kernel(const MatmulParams p) {
         }
         cp_async_commit();
     };
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();  // x (and the residual) come from the previous kernel in the stream
 #pragma unroll
     for (int s = 0; s < kXStages - 1; ++s) issue_x(s);
@@ -223,7 +226,6 @@ quant_matmul_kernel(const MatmulParams p) {
             }
         }
     }
-    pdl_launch_dependents();
 
     if (BITS == 8) {
         float s_lo = 0.f, s_hi = 0.f;
@@ -237,19 +239,22 @@ quant_matmul_kernel(const MatmulParams p) {
         }
     }
 
-    // ---- partial tile -> shared memory (reusing the activation stages) ----------------------
+    // ---- partial tile -> pushed to the owner CTA of each row (slots behind the activation stages) ----
     cp_async_wait<0>();
-    __syncthreads();
-    float* red = reinterpret_cast<float*>(smem);
+    float* slots = reinterpret_cast<float*>(smem + kXStages * kStageBytes);
+    sr.ready(slots, MPAD);
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
-        int m = i * 8 + 2 * t, c = warp * 16 + g;
-        red[m * kRedStride + c] = acc[i][0];
-        red[(m + 1) * kRedStride + c] = acc[i][1];
-        red[m * kRedStride + c + 8] = acc[i][2];
-        red[(m + 1) * kRedStride + c + 8] = acc[i][3];
+        const int c = warp * 16 + g;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int m = i * 8 + 2 * t + h;
+            const int owner = m % sr.S, lr = m / sr.S;
+            sr.push(owner, lr, c, acc[i][h]);
+            sr.push(owner, lr, c + 8, acc[i][2 + h]);
+        }
     }
-    reduce_and_store_tile<MPAD>(p, red, tid, kWarps * 32, m0, blockIdx.x * kCtaN);
+    split_reduce_finish<MPAD>(p, sr, slots, tid, kWarps * 32, m0, blockIdx.x * kCtaN);
 }
 
 // ---- layout conversion kernels --------------------------------------------------------------
@@ -487,7 +492,7 @@ int launch_matmul(const MatmulParams& p, dim3 grid, size_t smem, cudaStream_t st
     void (*kern)(MatmulParams) = quant_matmul_kernel<MT, BITS>;
     static bool attr_done = false;  // per instantiation
     if (!attr_done) {
-        GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
         attr_done = true;
     }
     return launch_kernel(kern, grid, dim3(kWarps * 32), smem, stream, p.n_split, p);
@@ -551,8 +556,7 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
     const int64_t m_eff = m > 64 ? 64 : m;
     auto smem_for = [](int mt) {
         size_t stages = (size_t)kXStages * mt * 8 * kGroupK * 2;
-        size_t red = (size_t)mt * 8 * kRedStride * 4;
-        return stages > red ? stages : red;
+        return stages + (size_t)(mt * 8 + 7) * kRedStride * 4;  // + receive slots of the split-K reduction
     };
     if (m_eff <= 8) return launch_matmul<1, BITS>(p, grid, smem_for(1), st);
     if (m_eff <= 16) return launch_matmul<2, BITS>(p, grid, smem_for(2), st);

@@ -26,12 +26,11 @@
 namespace gptrs {
 namespace {
 
-constexpr int kStages = 4;
 constexpr int kBlockK = 64;                 // bf16 elements per 128-byte swizzle span
 constexpr int kABytes = kCtaN * 128;        // 16 KB: 128 rows x 128 bytes
 constexpr int kProducerWarps = 8;            // one 16-channel tile each
 constexpr int kUmmaThreads = (kProducerWarps + 2) * 32;
-constexpr int kRing = 8;                    // stages of packed weights kept in flight per thread
+constexpr int kRing = 8;                    // stages of packed weights in flight (per thread: kRing / G of its own)
 
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     // K-major, SWIZZLE_128B: 8-row atoms of 1024 bytes (SBO = 1024), LBO unused (1), version 1.
@@ -44,11 +43,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     return d;
 }
 
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint32_t bar_addr) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
             "r"(smem_u32(smem_dst)),
-        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        "l"(map), "r"(x), "r"(y), "r"(bar_addr)
         : "memory");
 }
 
@@ -64,14 +63,26 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
                  : "memory");
 }
-// Bounded wait that backs off between polls (for waiters that are not on the critical path).
-__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
+// Bounded wait that lets the hardware park the thread: try_wait with a suspend-time hint returns when the
+// phase completes or the hint (about a microsecond) runs out, so a waiting warp issues almost nothing.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar_addr, uint32_t parity) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(40);
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+            " selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(bar_addr), "r"(parity), "r"(1000u)
+            : "memory");
+        if (ok) return true;
     }
     return false;
 }
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) { return mbar_wait_parked(smem_u32(bar), parity); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__host__ __device__ constexpr int gcd_ce(int a, int b) { return b == 0 ? a : gcd_ce(b, a % b); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
@@ -92,8 +103,16 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-template <int BN>
-__global__ void __launch_bounds__(kUmmaThreads, (BN <= 64) ? 2 : 1)
+// smem of one CTA: stages, alignment slack, receive slots of the split-K reduction (tiles up to 128 rows)
+constexpr size_t umma_smem_max(int bn, int stages) {
+    return (size_t)stages * (kABytes + bn * 128) + 1024 + (bn <= 128 ? (size_t)(bn + 7) * kRedStride * 4 : 0);
+}
+
+// G = number of producer groups. Group g (256 / G threads) dequantises the stages it = g, g + G, ...; its
+// threads own G half-rows of such a stage each. The groups run out of phase, so that the fixed latencies of
+// one group (barrier wait, proxy fence) are covered by the arithmetic of the others.
+template <int BN, int G, int kStages>
+__global__ void __launch_bounds__(kUmmaThreads, (2 * (umma_smem_max(BN, kStages) + 1024) <= 227 * 1024) ? 2 : 1)
 umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_map, int* status) {
     constexpr int kBBytes = BN * 128;
     constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
@@ -110,6 +129,11 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     unsigned char* sB = smem + kStages * kABytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    SplitReduce sr;
+    sr.begin(p);  // arrives on the cluster's "started" barrier; pushes wait for it
+    // The next kernel may be scheduled as soon as every CTA of this one runs: its own wait for this grid's
+    // completion keeps the data dependence, and its set-up and weight prefetch overlap this kernel.
+    pdl_launch_dependents();
     const int n_cta0 = blockIdx.x * kCtaN;
     const int m0 = blockIdx.z * BN;
     const int chunks_total = p.K / kBlockK;
@@ -120,9 +144,54 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     const int n_it = (g1 - g0) * 2;   // 64-wide stages of this CTA
     const int chunk0 = g0 * 2;        // first 64-k chunk of this CTA
 
+    // ---------------- dequant producers (weight layout B: 256 x 16 bytes per 64-k stage; entry e holds ----
+    // ---------------- k half (e >> 4) & 1 of row 16 * (e >> 5) + (e & 15)) ---------------------------------
+    // The own-stage loop is unrolled over kOwn stages, a multiple of the period after which a group meets
+    // the same ring slot again, so slot offsets and barrier parities are per-thread constants.
+    constexpr int kGroupThreads = kProducerWarps * 32 / G;
+    constexpr int kPeriod = kStages / gcd_ce(G, kStages);
+    constexpr int kOwn = kPeriod * ((6 + G * kPeriod - 1) / (G * kPeriod));  // own stages kept in flight (>= 6 stages ahead)
+    constexpr int kLaps = G * kOwn / kStages;                               // trips round the ring per outer iteration
+    const int grp = tid / kGroupThreads, t = tid % kGroupThreads;
+    const uint4* wp = p.wq_rows + ((size_t)blockIdx.x * chunks_total + chunk0) * 256 + t;
+    const __half* sp = p.scales_rows + ((size_t)blockIdx.x * (chunks_total / 2) + chunk0 / 2) * kCtaN;
+    uint32_t st_addr[G][4];  // shared addresses (ring slot 0) of the four 16-byte chunks of unit j
+    int row[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+        const int e = t + j * kGroupThreads;
+        row[j] = 16 * (e >> 5) + (e & 15);
+        const uint32_t base = smem_u32(sA) + row[j] * 128 + (((((e >> 4) & 1) * 4) ^ (row[j] & 7)) << 4);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) st_addr[j][w] = base ^ (w << 4);
+    }
+    uint32_t slot[kOwn], par0[kOwn];
+#pragma unroll
+    for (int o = 0; o < kOwn; ++o) {
+        slot[o] = (grp + G * o) % kStages;
+        par0[o] = (((grp + G * o) / kStages) & 1) ^ 1;
+    }
+    const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+    // The first packed weights are requested before anything else, so that their DRAM latency covers the
+    // barrier and TMEM set-up below (weights are constants: no need to wait for the previous kernel).
+    uint4 ring[kOwn][G];
+    __half sring[kOwn][G];
+#pragma unroll
+    for (int o = 0; o < kOwn; ++o) {
+        const int it = warp < kProducerWarps ? grp + G * o : n_it;
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            ring[o][j] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+            sring[o][j] = __float2half(0.f);
+            if (it < n_it) {
+                ring[o][j] = ldg_stream_16(wp + (size_t)it * 256 + j * kGroupThreads);
+                sring[o][j] = __ldg(sp + (size_t)((chunk0 + it) / 2 - chunk0 / 2) * kCtaN + row[j]);
+            }
+        }
+    }
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full_bar[s], kProducerWarps * 32 + 1);
+            mbar_init(&full_bar[s], kProducerWarps * 32 / G + 1);
             mbar_init(&empty_bar[s], 1);
         }
         mbar_init(&done_bar, 1);
@@ -141,77 +210,57 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     bool failed = false;
 
     if (warp < kProducerWarps) {
-        // ---------------- dequant producers: thread (warp, lane) owns row 16*warp + (lane & 15), ----
-        // ---------------- k half (lane >> 4) of every 64-wide stage (weight layout B) ---------------
-        const int row = warp * 16 + (lane & 15), half = lane >> 4;
-        const uint4* wp = p.wq_rows + ((size_t)blockIdx.x * chunks_total + chunk0) * 256 + tid;
-        const __half* sp = p.scales_rows + ((size_t)blockIdx.x * (chunks_total / 2) + chunk0 / 2) * kCtaN + row;
-        uint4 ring[kRing];
-        __half sring[kRing];
-#pragma unroll
-        for (int r = 0; r < kRing; ++r) {
-            ring[r] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-            sring[r] = __float2half(0.f);
-            if (r < n_it) {
-                ring[r] = ldg_stream_16(wp + (size_t)r * 256);
-                sring[r] = __ldg(sp + (size_t)((chunk0 + r) / 2 - chunk0 / 2) * kCtaN);
-            }
-        }
-        pdl_wait();
+        pdl_wait();  // the activation tile comes from the previous kernel in the stream
         const __nv_bfloat162 c136 = __floats2bfloat162_rn(136.f, 136.f);
-        unsigned char* const row_base = sA + row * 128;
-        const int sw = row & 7;
-        for (int it0 = 0; it0 < n_it && !failed; it0 += kRing) {
+        uint32_t lap = 0;  // parity contribution of the outer iteration
+        for (int it_base = grp; it_base < n_it && !failed; it_base += G * kOwn, lap ^= (kLaps & 1)) {
 #pragma unroll
-            for (int r = 0; r < kRing; ++r) {
-                const int it = it0 + r;
+            for (int o = 0; o < kOwn; ++o) {
+                const int it = it_base + G * o;
                 if (it < n_it && !failed) {
-                    const int s = it % kStages;
-                    if (!mbar_wait_relaxed(&empty_bar[s], ((it / kStages) & 1) ^ 1)) { failed = true; }
-                    const uint4 cur = ring[r];
-                    const __nv_bfloat162 sc = __float2bfloat162_rn(__half2float(sring[r]));
-                    if (it + kRing < n_it) {
-                        ring[r] = ldg_stream_16(wp + (size_t)(it + kRing) * 256);
-                        sring[r] = __ldg(sp + (size_t)((chunk0 + it + kRing) / 2 - chunk0 / 2) * kCtaN);
+                    if (!mbar_wait_parked(empty0 + slot[o] * 8, par0[o] ^ lap)) failed = true;
+                    const uint32_t full = full0 + slot[o] * 8;
+                    if (t == 0) {  // the group leader also fetches the activation tile of this stage
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(full), "r"((uint32_t)kBBytes) : "memory");
+                        tma_load_2d(sB + slot[o] * kBBytes, &x_map, (chunk0 + it) * kBlockK, m0, full);
                     }
-                    unsigned char* dst = row_base + s * kABytes;
-                    const uint32_t q4[4] = {cur.x, cur.y, cur.z, cur.w};
+                    const uint32_t a_off = slot[o] * kABytes;
+                    const int nxt = it + G * kOwn;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t q = q4[j];
-                        uint4 v;
-                        uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;   // (k 2i, k 2i+1) + 128
-                            __nv_bfloat162 d = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136), sc);
-                            vv[i] = *reinterpret_cast<uint32_t*>(&d);
+                    for (int j = 0; j < G; ++j) {
+                        const uint4 cur = ring[o][j];
+                        const __nv_bfloat162 sc = __float2bfloat162_rn(__half2float(sring[o][j]));
+                        if (nxt < n_it) {
+                            ring[o][j] = ldg_stream_16(wp + (size_t)nxt * 256 + j * kGroupThreads);
+                            sring[o][j] = __ldg(sp + (size_t)((chunk0 + nxt) / 2 - chunk0 / 2) * kCtaN + row[j]);
                         }
-                        *reinterpret_cast<uint4*>(dst + (((half * 4 + j) ^ sw) << 4)) = v;   // 8 consecutive k
+                        const uint32_t q4[4] = {cur.x, cur.y, cur.z, cur.w};
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+                            const uint32_t q = q4[w];
+                            uint32_t vv[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;   // (k 2i, k 2i+1) + 128
+                                __nv_bfloat162 d = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136), sc);
+                                vv[i] = *reinterpret_cast<uint32_t*>(&d);
+                            }
+                            st_shared_v4(st_addr[j][w] + a_off, vv[0], vv[1], vv[2], vv[3]);   // 8 consecutive k
+                        }
                     }
                     fence_proxy_async();
-                    mbar_arrive(&full_bar[s]);
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(full) : "memory");
                 }
             }
         }
     } else if (warp == kProducerWarps) {
-        // ---------------- TMA producer for the activation tile -----------------------------------
-        pdl_wait();
-        if (lane == 0) {
-            for (int it = 0; it < n_it; ++it) {
-                const int s = it % kStages;
-                if (!mbar_wait_relaxed(&empty_bar[s], ((it / kStages) & 1) ^ 1)) { failed = true; break; }
-                mbar_expect_tx(&full_bar[s], kBBytes);
-                tma_load_2d(sB + s * kBBytes, &x_map, (chunk0 + it) * kBlockK, m0, &full_bar[s]);
-            }
-        }
-        __syncwarp();
+        pdl_wait();  // the TMEM owner idles during the main loop; it reads the residual in the epilogue
     } else {
         // ---------------- MMA issuer ---------------------------------------------------------------
         pdl_wait();  // this warp later reads the residual in the epilogue
         for (int it = 0; it < n_it; ++it) {
             const int s = it % kStages;
-            if (!mbar_wait_bounded(&full_bar[s], (it / kStages) & 1)) { failed = true; break; }
+            if (!mbar_wait_relaxed(&full_bar[s], (it / kStages) & 1)) { failed = true; break; }
             tc_fence_after();
             if (lane == 0) {
                 const uint64_t a_desc = make_smem_desc(smem_u32(sA + s * kABytes));
@@ -226,10 +275,11 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
         if (lane == 0) umma_commit(&done_bar);
         __syncwarp();
     }
-    pdl_launch_dependents();
-
-    // ---------------- epilogue: TMEM -> registers -> shared tile [BN][kRedStride] ----------------
-    float* red = reinterpret_cast<float*>(smem);
+    // ---------------- epilogue: TMEM -> registers -> pushed to the owner CTA of each output row ----
+    // Split launches receive into a region of their own behind the stages (a peer may push while this
+    // CTA is still in its main loop); an unsplit launch reuses the stage buffers.
+    float* slots = reinterpret_cast<float*>(p.n_split > 1 ? smem + kStages * (kABytes + kBBytes) : smem);
+    sr.ready(slots, BN);
     if (warp < kProducerWarps) {
         if (!mbar_wait_relaxed(&done_bar, 0)) failed = true;
         tc_fence_after();
@@ -241,8 +291,12 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
         for (int c0 = c_begin; c0 < c_end; c0 += 32) {
             float v[32];
             tmem_ld_32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+            int owner = c0 % sr.S, local_row = c0 / sr.S;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) red[(c0 + i) * kRedStride + col] = v[i];
+            for (int i = 0; i < 32; ++i) {
+                sr.push(owner, local_row, col, v[i]);
+                if (++owner == sr.S) { owner = 0; ++local_row; }
+            }
         }
     }
     if (failed && lane == 0) atomicExch(status, 3);
@@ -251,7 +305,7 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     if (warp == kProducerWarps) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
-    reduce_and_store_tile<BN>(p, red, tid, kUmmaThreads, m0, n_cta0);
+    split_reduce_finish<BN>(p, sr, slots, tid, kUmmaThreads, m0, n_cta0);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -279,7 +333,7 @@ int* umma_status_word() {
     return d;
 }
 
-template <int BN>
+template <int BN, int G, int kStages>
 int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(GPTRS_EXECUTION, "cuTensorMapEncodeTiled is not available");
@@ -294,11 +348,12 @@ int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
     if (r != CUDA_SUCCESS) return fail(GPTRS_EXECUTION, "cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
     int* status = umma_status_word();
     if (!status) return fail(GPTRS_EXECUTION, "cannot allocate the status word");
-    constexpr size_t smem = (size_t)kStages * (kABytes + BN * 128) + 1024;
-    auto kern = umma_w4a16_kernel<BN>;
+    const size_t smem = (size_t)kStages * (kABytes + BN * 128) + 1024 + (p.n_split > 1 ? split_slots_bytes(BN, p.n_split) : 0);
+    constexpr size_t smem_max = umma_smem_max(BN, kStages);
+    auto kern = umma_w4a16_kernel<BN, G, kStages>;
     static bool attr_done = false;
     if (!attr_done) {
-        GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
         attr_done = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -340,11 +395,21 @@ int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
     int split = (sm_count() * pct / 100) / n_blocks;
     split = split < 1 ? 1 : (split > 8 ? 8 : split);
     if (split > groups) split = groups;
+    if (p.M > 128) split = 1;  // the 256-row tile leaves no room for receive slots; it has M blocks to fill the GPU
     p.n_split = split;
     p.groups_per_cta = (groups + split - 1) / split;
-    if (p.M <= 64) return launch_umma<64>(p, dim3(n_blocks, split, 1), st);
-    if (p.M <= 128) return launch_umma<128>(p, dim3(n_blocks, split, 1), st);
-    return launch_umma<256>(p, dim3(n_blocks, split, ceil_div(p.M, 256)), st);
+    const dim3 grid(n_blocks, split, ceil_div(p.M, 256));
+    // decode-sized tiles: variant 0 = two groups, 3 stages, two CTAs per SM; 1 = four groups, 6 stages, one CTA per SM
+    static int variant = -1;
+    if (variant < 0) { const char* e = getenv("GPTRS_UMMA_VARIANT"); variant = e ? atoi(e) : 0; }
+    if (p.M <= 64) {
+        if (variant == 1) return launch_umma<64, 4, 6>(p, grid, st);
+        if (variant == 2) return launch_umma<64, 1, 3>(p, grid, st);
+        if (variant == 3) return launch_umma<64, 4, 4>(p, grid, st);
+        return launch_umma<64, 2, 3>(p, grid, st);
+    }
+    if (p.M <= 128) return launch_umma<128, 2, 4>(p, grid, st);
+    return launch_umma<256, 2, 4>(p, grid, st);
 }
 
 int umma_status(int* out) {
