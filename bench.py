@@ -113,17 +113,30 @@ def build_model(gm, torch, dev, steps_total: int, use_pdl: int, prefill_chunk: i
     return model, cfg
 
 
-def time_attention_kernel(ops, torch, dev, ctx_len: int, launches: int = 20):
+def _tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text()).get("bf16_tflops") or 0) or None
+    return 1590.0
+
+
+def time_attention_kernel(ops, torch, dev, ctx_len: int, launches: int = 20, ragged_seed=None):
     """CUDA-event time of the dominant kernel (paged decode attention of ONE layer) on a synthetic
-    pool of the bench geometry; every launch streams the whole pool (> L2)."""
+    pool of the bench geometry; every launch streams the whole pool (> L2). With `ragged_seed` the
+    context lengths are drawn uniformly from 512..ctx_len and the physical pages are a random permutation."""
     n_q, n_kv = 32, 8
     pages_per = (ctx_len + 15) // 16
+    if ragged_seed is None:
+        lens_host = [ctx_len] * BATCH
+    else:
+        import numpy as np
+        lens_host = [int(v) for v in np.random.default_rng(ragged_seed).integers(512, ctx_len + 1, size=BATCH)]
     total = BATCH * pages_per
     pool = torch.randn(total * n_kv * 2 * 16 * 128, dtype=torch.bfloat16, device=dev).view(torch.uint8)
     table = torch.randperm(total, device=dev, dtype=torch.int32).view(BATCH, pages_per).contiguous()
     q = torch.randn((BATCH, n_q, 128), dtype=torch.bfloat16, device=dev)
     slot = torch.arange(BATCH, dtype=torch.int32, device=dev)
-    lens = torch.full((BATCH,), ctx_len, dtype=torch.int32, device=dev)
+    lens = torch.tensor(lens_host, dtype=torch.int32, device=dev)
     bucket = ((ctx_len + 511) // 512) * 512
     from gptrs_b200 import lib
     chunk = lib().gptrs_cuda_attention_chunk_pages(bucket, BATCH, n_kv)
@@ -158,23 +171,33 @@ def time_attention_kernel(ops, torch, dev, ctx_len: int, launches: int = 20):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / launches
-    alg_bytes = BATCH * ctx_len * 4096 + 2 * BATCH * n_q * 128 * 2 + BATCH * pages_per * 4
+    alg_bytes = sum(lens_host) * 4096 + 2 * BATCH * n_q * 128 * 2 + sum((v + 15) // 16 for v in lens_host) * 4
     del pool
     return ms, alg_bytes, chunk
 
 
-def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3):
-    """W4A16 decode GEMV over a rotating set of distinct weight matrices (working set >> L2)."""
-    nbytes = ops.w4a16_packed_bytes(n, k)
-    mats = [torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device=dev) for _ in range(n_mats)]
-    half = n * k // 2 + n * (k // 128) * 2  # the buffer holds two layouts, each weights then fp16 scales
-    for mt in mats:  # keep the fp16 scale bits finite
-        mt[n * k // 2:half] = 0x1C
-        mt[half + n * k // 2:] = 0x1C
+def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3, bits=4):
+    """W4A16 / W8A16 matmul over a rotating set of distinct weight matrices (working set >> L2)."""
+    if bits == 4:
+        nbytes = ops.w4a16_packed_bytes(n, k)
+        mats = [torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device=dev) for _ in range(n_mats)]
+        half = n * k // 2 + n * (k // 128) * 2  # the buffer holds two layouts, each weights then fp16 scales
+        for mt in mats:  # keep the fp16 scale bits finite
+            mt[n * k // 2:half] = 0x1C
+            mt[half + n * k // 2:] = 0x1C
+        run = ops.quant_matmul_w4a16
+        weight_bytes = nbytes // 2  # a launch reads ONE of the two weight layouts
+    else:
+        nbytes = ops.w8a16_packed_bytes(n, k)
+        mats = [torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device=dev) for _ in range(n_mats)]
+        for mt in mats:
+            mt[n * k:] = 0x1C
+        run = ops.quant_matmul_w8a16
+        weight_bytes = nbytes
     x = torch.randn((m, k), dtype=torch.bfloat16, device=dev)
     y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
     for mt in mats[:4]:
-        ops.quant_matmul_w4a16(x, mt, m, n, k, out=y)
+        run(x, mt, m, n, k, out=y)
     torch.cuda.synchronize()
     # one CUDA graph over all matrices: the timing sees the device, not the Python launch rate
     graph = torch.cuda.CUDAGraph()
@@ -182,7 +205,7 @@ def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3):
     with torch.cuda.stream(side):
         graph.capture_begin()
         for mt in mats:
-            ops.quant_matmul_w4a16(x, mt, m, n, k, out=y)
+            run(x, mt, m, n, k, out=y)
         graph.capture_end()
     torch.cuda.synchronize()
     graph.replay()
@@ -194,7 +217,7 @@ def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3):
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / (iters * n_mats)
-    alg = nbytes // 2 + 2 * m * k + 2 * m * n  # a launch reads ONE of the two weight layouts
+    alg = weight_bytes + 2 * m * k + 2 * m * n
     return us, alg
 
 
@@ -206,6 +229,15 @@ def run_reference_arm(args):
         return
     from oracle import cbaseline as cb
     lib = cb.load(prefer_reference=True)
+    if args.workload == "gpt2-fp32":
+        res = cb.time_gpt2_decode(lib, n_tokens=max(4, min(args.steps, 32)))
+        v = res["tokens_per_s"]
+        print(json.dumps({"impl": "reference", "metric": "decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": GPT2_WORKLOAD},
+                          "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": res["cores"], "kind": res["kind"], "sample": res["sample"]},
+                          "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}), file=OUT[0])
+        return
     vals = []
     res, state = None, None
     for i in range(args.warmup + args.steps):
@@ -225,6 +257,75 @@ def run_reference_arm(args):
         "gpu_launches": 0,
     }
     print(json.dumps(line), file=OUT[0])
+
+
+GPT2_PUBLISHED_TOKENS_PER_S = 74.71  # the reference README's GPT-2 small row (C backend, single thread)
+GPT2_WORKLOAD = "gpt2-small fp32, one sequence, 32-token prompt, greedy decode with the dense-cache f32 kernels"
+
+
+def run_gpt2(args, out, gm, torch, np):
+    """The reference's CPU-runnable case on one GPU: GPT-2 small, f32 weights N(0, 0.02) seed 0, a 32-token
+    random prompt, greedy decode; a step is one generated token."""
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    cfg = gm.ModelConfig.gpt2_small(weight_mode=gm.MODE_F32, max_seqs=1, max_tokens=32, max_logit_rows=32, use_pdl=args.pdl)
+    model = gm.LoadedModel(cfg, namespace=7)
+    gen_t = torch.Generator(device=dev)
+    gen_t.manual_seed(0)
+    for name, shape in cfg.param_shapes().items():
+        if name.endswith("gamma"):
+            w = torch.ones(shape, dtype=torch.float32, device=dev)
+        elif name.endswith("beta") or ".b_" in name:
+            w = torch.zeros(shape, dtype=torch.float32, device=dev)
+        else:
+            w = torch.empty(shape, dtype=torch.float32, device=dev).normal_(0.0, 0.02, generator=gen_t)
+        model.load_param(name, w)
+    model.finalize()
+    prompt = np.random.default_rng(0).integers(0, cfg.vocab, size=32)
+    model.reset_sequence(0)
+    _, first = model.prefill(0, prompt)
+    gen = gm.Generator(model, [first], use_graph=True)
+    stream = torch.cuda.ExternalStream(lib_stream(model), device=dev)
+    for _ in range(args.warmup):
+        gen.step(read_back=False)
+    gen.sync()
+    sampler = ClockSampler(None)
+    launches0 = model.stats()["kernel_launches"]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    sampler.start()
+    e0.record(stream)
+    for _ in range(args.steps):
+        gen.step(read_back=False)
+    e1.record(stream)
+    gen.sync()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = model.stats()["kernel_launches"] - launches0
+    tok = int(gen.step()[0])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok = int(gen.step(tokens_in=[tok])[0])
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    weight_bytes = 4 * sum(int(np.prod(sh)) for n, sh in cfg.param_shapes().items() if "embeddings" not in n)
+    peak, peak_kind = _peaks()
+    line = {"metric": "decode_tokens_per_s", "value": args.steps / ms * 1e3, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": args.steps / ms * 1e3 / GPT2_PUBLISHED_TOKENS_PER_S,
+            "dtype": "f32", "data": "synthetic", "config": {"workload": GPT2_WORKLOAD, "cuda_graph": True, "pdl": bool(args.pdl),
+            "published_baseline": "74.71 tokens/s, gpt.rs C backend, one thread, Ryzen 9 9950X3D, pretrained weights (random weights of the same shapes here)",
+            "l2": "494 MB of f32 weights streamed per token (> L2)"},
+            "e2e": {"value": args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "clocks": clocks,
+            "roofline": {"kernel": "sgemm_smallm_kernel (all weight matrices of a step)", "bound": "hbm", "achieved": weight_bytes / (ms / args.steps) / 1e6,
+                         "peak": peak, "unit": "GB/s", "frac": weight_bytes / (ms / args.steps) / 1e6 / peak, "traffic": None,
+                         "peak_kind": peak_kind, "note": "whole-step figure: f32 weight bytes of one token over the step time"}}
+    if not args.no_cpu_baseline:
+        from oracle import cbaseline as cb
+        res = cb.time_gpt2_decode(cb.load(prefer_reference=True), n_tokens=8)
+        line["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": res["kind"], "sample": res["sample"]}
+    print(json.dumps(line), file=out)
 
 
 def main():
@@ -248,9 +349,11 @@ def _main(out):
     ap.add_argument("--pdl", type=int, default=int(os.environ.get("GPTRS_PDL", "1")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the kernel microbenchmarks")
-    ap.add_argument("--microbench", default=None, choices=["attention", "gemv", "gemm64"],
+    ap.add_argument("--microbench", default=None, choices=["attention", "attention-ragged", "gemv", "gemm64", "quant-linear"],
                     help="run only one kernel microbenchmark (used for ncu captures) and print its JSON")
     ap.add_argument("--ctx", type=int, default=PROMPT_LEN + 20, help="context length for --microbench attention")
+    ap.add_argument("--workload", default="ministral3b-w4", choices=["ministral3b-w4", "gpt2-fp32"],
+                    help="gpt2-fp32 = the reference's CPU-runnable case (one sequence, 32-token prompt, 64 greedy tokens)")
     ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
                     help="dp: every rank decodes its own 64 requests (default); tp: all ranks share ONE batch of 64 "
                          "(tensor parallel, NCCL all-reduce after the row-parallel projections)")
@@ -267,6 +370,9 @@ def _main(out):
     from gptrs_b200 import model as gm
     from gptrs_b200 import ops
 
+    if args.workload == "gpt2-fp32":
+        run_gpt2(args, out, gm, torch, np)
+        return
     if args.microbench:
         torch.cuda.set_device(0)
         dev = torch.device("cuda", 0)
@@ -275,6 +381,27 @@ def _main(out):
             ms, nbytes, chunk = time_attention_kernel(ops, torch, dev, args.ctx, launches=5)
             print(json.dumps({"kernel": "paged_attention_kernel", "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
                               "frac": nbytes / ms / 1e6 / peak, "chunk_pages": chunk, "ctx": args.ctx}), file=out)
+        elif args.microbench == "attention-ragged":
+            ms, nbytes, chunk = time_attention_kernel(ops, torch, dev, 8192, launches=5, ragged_seed=0)
+            print(json.dumps({"kernel": "paged_attention_kernel", "workload": "batch 64, context lengths U{512..8192} (seed 0), 32 q / 8 kv heads of 128, random page permutation",
+                              "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak,
+                              "chunk_pages": chunk}), file=out)
+        elif args.microbench == "quant-linear":
+            rows = []
+            tf_peak = _tensor_peak()
+            for bits in (4, 8):
+                for n in (3072, 9216):
+                    for m in (1, 16, 64, 256):
+                        per = n * 3072 * bits // 8
+                        n_mats = max(8, min(64, (400 << 20) // per))  # rotating working set of about 400 MB (> L2)
+                        us, alg = time_gemv(ops, torch, dev, n=n, k=3072, m=m, n_mats=n_mats, iters=3, bits=bits)
+                        tf = 2.0 * m * n * 3072 / us / 1e6
+                        rows.append({"bits": bits, "M": m, "N": n, "K": 3072, "us": round(us, 2), "algorithmic_bytes": alg,
+                                     "gbs": round(alg / us / 1e3, 1), "frac_of_hbm_peak": round(alg / us / 1e3 / peak, 3),
+                                     "tflops": round(tf, 1), "frac_of_bf16_peak": round(tf / tf_peak, 3) if tf_peak else None})
+            print(json.dumps({"microbench": "quant-linear", "hbm_peak_gbs": peak, "bf16_peak_tflops": tf_peak,
+                              "note": "rotating distinct weight matrices (> L2), back-to-back launches in one CUDA graph, CUDA events",
+                              "rows": rows}), file=out)
         elif args.microbench == "gemv":
             us, nbytes = time_gemv(ops, torch, dev, n_mats=16, iters=1)
             print(json.dumps({"kernel": "quant_matmul_kernel<1,4>", "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3}), file=out)

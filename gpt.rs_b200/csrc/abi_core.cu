@@ -8,6 +8,7 @@ namespace gptrs {
 
 static thread_local std::string g_last_error;
 int g_use_pdl = 0;
+int g_launch_priority = 0;
 
 void set_last_error(const std::string& msg) { g_last_error = msg; }
 

@@ -48,6 +48,7 @@ int sm_count();
 // programmatic stream serialisation (every kernel of this library executes
 // griddepcontrol.wait before it touches memory written by its predecessor).
 extern int g_use_pdl;
+extern int g_launch_priority;  // 0 = default; otherwise the stream priority value given to kernel launches
 
 #ifdef __CUDACC__
 // Launch through cudaLaunchKernelEx with the optional cluster (along grid.y) and
@@ -60,8 +61,13 @@ int launch_kernel(void (*kern)(P), dim3 grid, dim3 block, size_t smem, cudaStrea
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attrs[2];
+    cudaLaunchAttribute attrs[3];
     int na = 0;
+    if (g_launch_priority != 0) {
+        attrs[na].id = cudaLaunchAttributePriority;
+        attrs[na].val.priority = g_launch_priority;
+        ++na;
+    }
     if (cluster_y > 1) {
         attrs[na].id = cudaLaunchAttributeClusterDimension;
         attrs[na].val.clusterDim.x = 1;

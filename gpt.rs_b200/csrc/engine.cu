@@ -101,6 +101,16 @@ struct Model {
     int32_t* h_stage = nullptr;  // 6 * max_tokens int32
     float* h_logits = nullptr;
     cudaStream_t stream = nullptr;
+    // Optional (GPTRS_LANES=2): decode steps of >= 32 sequences run as two half-batches ("lanes") on two
+    // streams, meant to overlap the HBM-bound attention of one half with the latency-bound projections of
+    // the other. Off by default: on B200 the grids of both lanes fill every SM, the work distributor runs
+    // them back to back, and the doubled weight traffic made a batch-64 step 15 % slower.
+    cudaStream_t stream2 = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    std::vector<cudaEvent_t> ev_a, ev_b;  // per layer: attention of lane A / lane B finished
+    int n_lanes = 1;
+    bool lane_order = true;  // lanes take turns at the attention kernel
+    int lane_priority = 0;   // launch priority of everything but attention in a two-lane step (0 = off)
     struct GraphEntry { cudaGraphExec_t exec; int64_t kernels; };
     std::map<GraphKey, GraphEntry> graphs;
     // tensor parallelism: cfg holds the LOCAL head / MLP sizes; the full sizes are kept here
@@ -129,6 +139,11 @@ struct Model {
         if (h_stage) cudaFreeHost(h_stage);
         if (h_logits) cudaFreeHost(h_logits);
         if (comm) { std::string e; if (const NcclApi* api = nccl_api(&e)) api->CommDestroy(comm); }
+        for (cudaEvent_t e : ev_a) cudaEventDestroy(e);
+        for (cudaEvent_t e : ev_b) cudaEventDestroy(e);
+        if (ev_fork) cudaEventDestroy(ev_fork);
+        if (ev_join) cudaEventDestroy(ev_join);
+        if (stream2) cudaStreamDestroy(stream2);
         if (stream) cudaStreamDestroy(stream);
     }
 };
@@ -260,12 +275,12 @@ int build_linear(Model& m, const std::vector<std::string>& names, const std::str
 }
 
 int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool out_f32, const float* residual,
-           bool swiglu, bool gelu) {
+           bool swiglu, bool gelu, cudaStream_t st) {
     ++m.launches;
     if (m.f32()) {
         return gptrs_cuda_matmul_f32(static_cast<const float*>(x), static_cast<const float*>(w.f32->data),
                                      static_cast<float*>(y), rows, w.out, w.in,
-                                     w.bias ? static_cast<const float*>(w.bias->data) : nullptr, residual, gelu ? 1 : 0, m.stream);
+                                     w.bias ? static_cast<const float*>(w.bias->data) : nullptr, residual, gelu ? 1 : 0, st);
     }
     gptrs_matmul_epilogue ep = {};
     ep.out_dtype = out_f32 ? GPTRS_F32 : GPTRS_BF16;
@@ -273,8 +288,8 @@ int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool
     ep.d_residual = residual;
     ep.swiglu = swiglu ? 1 : 0;
     return m.cfg.weight_mode == kModeW4
-               ? gptrs_cuda_quant_matmul_w4a16(x, w.packed->data, y, rows, w.out, w.in, &ep, m.stream)
-               : gptrs_cuda_quant_matmul_w8a16(x, w.packed->data, y, rows, w.out, w.in, &ep, m.stream);
+               ? gptrs_cuda_quant_matmul_w4a16(x, w.packed->data, y, rows, w.out, w.in, &ep, st)
+               : gptrs_cuda_quant_matmul_w8a16(x, w.packed->data, y, rows, w.out, w.in, &ep, st);
 }
 
 __global__ void rope_f32_inplace_kernel(float* qkv, const int* positions, const float* cos_t, const float* sin_t,
@@ -327,6 +342,8 @@ __global__ void advance_kernel(const AdvanceParams p) {
     if (i < p.n) { p.pos[i] += 1; p.ctx[i] += 1; }
 }
 
+int attention_plan(const Model& m, int T, int max_ctx, size_t scratch_bytes, int* chunk_pages);
+
 // Enqueues one forward pass over T tokens whose ids / slots / positions / visible lengths are
 // already in the device arrays. `rows`: number of rows that get logits (row indices in d_rows,
 // or all T rows in order when rows_identity).
@@ -349,78 +366,143 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         nccl = nccl_api(&err);
         if (!nccl) return fail(GPTRS_EXECUTION, err);
     }
+    // A lane is a contiguous range of token rows with its own stream; every activation buffer is row-major,
+    // so a lane works on a row offset of the shared buffers.
+    struct Lane { cudaStream_t st; int r0, T, chunk; unsigned char* scratch; size_t scratch_n; };
+    const size_t act = m.f32() ? 4 : 2;
+    auto at = [](DevBuf& b, size_t row_bytes, const Lane& ln) { return static_cast<unsigned char*>(b.p) + (size_t)ln.r0 * row_bytes; };
+    auto ints = [](DevBuf& b, const Lane& ln) { return b.as<int32_t>() + ln.r0; };
     // Row-parallel projections: without tensor parallelism the residual add is folded into the
     // matmul epilogue (hidden += x.W in place). With it, each rank produces a partial [T, D] sum
-    // that is all-reduced over NVLink and then added to the residual stream by the next norm kernel.
+    // that is all-reduced over NVLink and then added to the residual stream by the next norm kernel
+    // (tensor-parallel steps always run as one lane).
     const float* pending = nullptr;
-    auto row_parallel = [&](const Weight& w, const void* x) -> int {
-        if (m.tp == 1) return linear(m, w, x, hidden, T, true, hidden, false, false);
-        int r = linear(m, w, x, m.partial.p, T, true, nullptr, false, false);
+    auto row_parallel = [&](const Lane& ln, const Weight& w, const void* x) -> int {
+        float* h = reinterpret_cast<float*>(at(m.hidden, (size_t)D * 4, ln));
+        if (m.tp == 1) return linear(m, w, x, h, ln.T, true, h, false, false, ln.st);
+        int r = linear(m, w, x, m.partial.p, ln.T, true, nullptr, false, false, ln.st);
         if (r) return r;
         ++m.launches;
-        int nr = nccl->AllReduce(m.partial.p, m.partial.p, (size_t)T * D, kNcclFloat32, kNcclSum, m.comm, st);
+        int nr = nccl->AllReduce(m.partial.p, m.partial.p, (size_t)ln.T * D, kNcclFloat32, kNcclSum, m.comm, ln.st);
         if (nr) return fail(GPTRS_EXECUTION, std::string("ncclAllReduce: ") + nccl->GetErrorString(nr));
         pending = m.partial.as<float>();
         return GPTRS_OK;
     };
-    auto norm = [&](Tensor* g, Tensor* b) {
+    auto norm = [&](const Lane& ln, Tensor* g, Tensor* b) {
         ++m.launches;
         const float* delta = pending;
         pending = nullptr;
-        return gpt ? gptrs_cuda_add_layer_norm(hidden, delta, GPTRS_F32, nullptr, (const float*)g->data, (const float*)b->data,
-                                               c.norm_eps, m.xn.p, act_dt, nullptr, nullptr, T, D, st)
-                   : gptrs_cuda_add_rms_norm(hidden, delta, GPTRS_F32, (const float*)g->data, c.norm_eps, m.xn.p, act_dt,
-                                             nullptr, T, D, st);
+        float* h = reinterpret_cast<float*>(at(m.hidden, (size_t)D * 4, ln));
+        void* xn = at(m.xn, (size_t)D * act, ln);
+        return gpt ? gptrs_cuda_add_layer_norm(h, delta, GPTRS_F32, nullptr, (const float*)g->data, (const float*)b->data,
+                                               c.norm_eps, xn, act_dt, nullptr, nullptr, ln.T, D, ln.st)
+                   : gptrs_cuda_add_rms_norm(h, delta, GPTRS_F32, (const float*)g->data, c.norm_eps, xn, act_dt,
+                                             nullptr, ln.T, D, ln.st);
     };
-    for (int l = 0; l < c.n_layers; ++l) {
+    // ---- the three parts of a decoder block ------------------------------------------------------
+    auto pre_attention = [&](const Lane& ln, int l) -> int {
         Layer& L = m.layers[l];
-        if ((rc = norm(L.ln1_g, L.ln1_b))) return rc;
-        if ((rc = linear(m, L.qkv, m.xn.p, m.qkv.p, T, false, nullptr, false, false))) return rc;
+        int r;
+        if ((r = norm(ln, L.ln1_g, L.ln1_b))) return r;
+        void* qkv = at(m.qkv, (size_t)m.QKV() * act, ln);
+        if ((r = linear(m, L.qkv, at(m.xn, (size_t)D * act, ln), qkv, ln.T, false, nullptr, false, false, ln.st))) return r;
         if (m.f32()) {
             if (!gpt && c.rotary_dim > 0) {
                 ++m.launches;
-                rope_f32_inplace_kernel<<<dim3(c.n_q_heads + c.n_kv_heads, T), 64, 0, st>>>(
-                    m.qkv.as<float>(), m.d_pos.as<int32_t>(), m.cos_tab.as<float>(), m.sin_tab.as<float>(),
+                rope_f32_inplace_kernel<<<dim3(c.n_q_heads + c.n_kv_heads, ln.T), 64, 0, ln.st>>>(
+                    static_cast<float*>(qkv), ints(m.d_pos, ln), m.cos_tab.as<float>(), m.sin_tab.as<float>(),
                     c.n_q_heads + c.n_kv_heads, m.QKV(), c.head_dim, c.rotary_dim / 2);
                 GPTRS_CUDA_OK(cudaGetLastError());
             }
             float* kc = m.k_cache.as<float>() + (size_t)l * m.cache_layer_elems;
             float* vc = m.v_cache.as<float>() + (size_t)l * m.cache_layer_elems;
-            m.launches += 2;
-            if ((rc = gptrs_cuda_kv_append_f32(m.qkv.as<float>(), m.d_pos.as<int32_t>(), m.d_slot.as<int32_t>(), kc, vc, T,
-                                               c.n_q_heads, c.n_kv_heads, c.head_dim, c.context_length, st))) return rc;
-            if ((rc = gptrs_cuda_attention_decode_f32(m.qkv.as<float>(), kc, vc, m.d_pos.as<int32_t>(), m.d_slot.as<int32_t>(),
-                                                      m.attn.as<float>(), T, c.n_q_heads, c.n_kv_heads, c.head_dim,
-                                                      c.context_length, st))) return rc;
-        } else {
-            unsigned char* pool = m.kv_pool.as<unsigned char>() + (size_t)l * m.pool_layer_bytes;
-            m.launches += 2;
-            if ((rc = gptrs_cuda_rope_kv_append(m.qkv.p, m.d_pos.as<int32_t>(), m.d_slot.as<int32_t>(),
-                                                m.d_page_table.as<int32_t>(), c.max_pages_per_seq, m.cos_tab.as<float>(),
-                                                m.sin_tab.as<float>(), c.rotary_dim, m.q_rot.p, pool, T, c.n_q_heads,
-                                                c.n_kv_heads, c.head_dim, st))) return rc;
-            const int splits = (max_ctx + chunk_pages * kPage - 1) / (chunk_pages * kPage);
-            if (splits > 1) ++m.launches;
-            if ((rc = gptrs_cuda_paged_attention_decode(m.q_rot.p, pool, m.d_page_table.as<int32_t>(), c.max_pages_per_seq,
-                                                        m.d_slot.as<int32_t>(), m.d_ctx.as<int32_t>(), m.attn.p,
-                                                        m.attn_scratch.p, m.attn_scratch.n, m.d_status.as<int32_t>(), T,
-                                                        c.n_q_heads, c.n_kv_heads, c.head_dim, max_ctx, chunk_pages, st))) return rc;
-        }
-        if ((rc = row_parallel(L.attn_out, m.attn.p))) return rc;
-        if ((rc = norm(L.ln2_g, L.ln2_b))) return rc;
-        if (gpt) {
-            if ((rc = linear(m, L.mlp_in, m.xn.p, m.mlp_h.p, T, false, nullptr, false, true))) return rc;
-        } else if (m.f32()) {
-            if ((rc = linear(m, L.mlp_gate, m.xn.p, m.mlp_g.p, T, false, nullptr, false, false))) return rc;
-            if ((rc = linear(m, L.mlp_up, m.xn.p, m.mlp_u.p, T, false, nullptr, false, false))) return rc;
             ++m.launches;
-            if ((rc = gptrs_cuda_swiglu(m.mlp_g.as<float>(), m.mlp_u.as<float>(), m.mlp_h.as<float>(), (int64_t)T * c.d_mlp, st))) return rc;
-        } else {
-            if ((rc = linear(m, L.mlp_gate_up, m.xn.p, m.mlp_h.p, T, false, nullptr, true, false))) return rc;
+            return gptrs_cuda_kv_append_f32(static_cast<float*>(qkv), ints(m.d_pos, ln), ints(m.d_slot, ln), kc, vc, ln.T,
+                                            c.n_q_heads, c.n_kv_heads, c.head_dim, c.context_length, ln.st);
         }
-        if ((rc = row_parallel(L.mlp_out, m.mlp_h.p))) return rc;
+        unsigned char* pool = m.kv_pool.as<unsigned char>() + (size_t)l * m.pool_layer_bytes;
+        ++m.launches;
+        return gptrs_cuda_rope_kv_append(qkv, ints(m.d_pos, ln), ints(m.d_slot, ln), m.d_page_table.as<int32_t>(),
+                                         c.max_pages_per_seq, m.cos_tab.as<float>(), m.sin_tab.as<float>(), c.rotary_dim,
+                                         at(m.q_rot, (size_t)m.QD() * 2, ln), pool, ln.T, c.n_q_heads, c.n_kv_heads, c.head_dim, ln.st);
+    };
+    auto attention = [&](const Lane& ln, int l) -> int {
+        void* out = at(m.attn, (size_t)m.QD() * act, ln);
+        ++m.launches;
+        if (m.f32()) {
+            float* kc = m.k_cache.as<float>() + (size_t)l * m.cache_layer_elems;
+            float* vc = m.v_cache.as<float>() + (size_t)l * m.cache_layer_elems;
+            return gptrs_cuda_attention_decode_f32(reinterpret_cast<float*>(at(m.qkv, (size_t)m.QKV() * 4, ln)), kc, vc,
+                                                   ints(m.d_pos, ln), ints(m.d_slot, ln), static_cast<float*>(out), ln.T,
+                                                   c.n_q_heads, c.n_kv_heads, c.head_dim, c.context_length, ln.st);
+        }
+        unsigned char* pool = m.kv_pool.as<unsigned char>() + (size_t)l * m.pool_layer_bytes;
+        const int splits = (max_ctx + ln.chunk * kPage - 1) / (ln.chunk * kPage);
+        if (splits > 1) ++m.launches;
+        // In a two-lane step the projections of the other lane outrank attention CTAs that wait for an SM.
+        struct PriorityGuard { int saved; PriorityGuard() : saved(g_launch_priority) { g_launch_priority = 0; } ~PriorityGuard() { g_launch_priority = saved; } } guard;
+        return gptrs_cuda_paged_attention_decode(at(m.q_rot, (size_t)m.QD() * 2, ln), pool, m.d_page_table.as<int32_t>(),
+                                                 c.max_pages_per_seq, ints(m.d_slot, ln), ints(m.d_ctx, ln), out, ln.scratch,
+                                                 ln.scratch_n, m.d_status.as<int32_t>(), ln.T, c.n_q_heads, c.n_kv_heads,
+                                                 c.head_dim, max_ctx, ln.chunk, ln.st);
+    };
+    auto post_attention = [&](const Lane& ln, int l) -> int {
+        Layer& L = m.layers[l];
+        int r;
+        if ((r = row_parallel(ln, L.attn_out, at(m.attn, (size_t)m.QD() * act, ln)))) return r;
+        if ((r = norm(ln, L.ln2_g, L.ln2_b))) return r;
+        void* xn = at(m.xn, (size_t)D * act, ln);
+        void* mlp_h = at(m.mlp_h, (size_t)c.d_mlp * act, ln);
+        if (gpt) {
+            if ((r = linear(m, L.mlp_in, xn, mlp_h, ln.T, false, nullptr, false, true, ln.st))) return r;
+        } else if (m.f32()) {
+            void* g = at(m.mlp_g, (size_t)c.d_mlp * 4, ln);
+            void* u = at(m.mlp_u, (size_t)c.d_mlp * 4, ln);
+            if ((r = linear(m, L.mlp_gate, xn, g, ln.T, false, nullptr, false, false, ln.st))) return r;
+            if ((r = linear(m, L.mlp_up, xn, u, ln.T, false, nullptr, false, false, ln.st))) return r;
+            ++m.launches;
+            if ((r = gptrs_cuda_swiglu(static_cast<float*>(g), static_cast<float*>(u), static_cast<float*>(mlp_h),
+                                       (int64_t)ln.T * c.d_mlp, ln.st))) return r;
+        } else {
+            if ((r = linear(m, L.mlp_gate_up, xn, mlp_h, ln.T, false, nullptr, true, false, ln.st))) return r;
+        }
+        return row_parallel(ln, L.mlp_out, mlp_h);
+    };
+    const bool two_lanes = rows_identity && m.n_lanes == 2 && !m.f32() && m.tp == 1 && T >= 32;
+    if (!two_lanes) {
+        const Lane all = {st, 0, T, chunk_pages, m.attn_scratch.as<unsigned char>(), m.attn_scratch.n};
+        for (int l = 0; l < c.n_layers; ++l) {
+            if ((rc = pre_attention(all, l))) return rc;
+            if ((rc = attention(all, l))) return rc;
+            if ((rc = post_attention(all, l))) return rc;
+        }
+    } else {
+        const int ta = (T + 1) / 2;
+        const size_t half = (m.attn_scratch.n / 2) & ~(size_t)255;
+        Lane a = {st, 0, ta, 1, m.attn_scratch.as<unsigned char>(), half};
+        Lane b = {m.stream2, ta, T - ta, 1, m.attn_scratch.as<unsigned char>() + half, half};
+        attention_plan(m, a.T, max_ctx, half, &a.chunk);
+        attention_plan(m, b.T, max_ctx, half, &b.chunk);
+        GPTRS_CUDA_OK(cudaEventRecord(m.ev_fork, st));
+        GPTRS_CUDA_OK(cudaStreamWaitEvent(b.st, m.ev_fork, 0));
+        struct PriorityScope { int saved; explicit PriorityScope(int p) : saved(g_launch_priority) { g_launch_priority = p; } ~PriorityScope() { g_launch_priority = saved; } } scope(m.lane_priority);
+        for (int l = 0; l < c.n_layers; ++l) {
+            if ((rc = pre_attention(a, l))) return rc;
+            if (m.lane_order && l > 0) GPTRS_CUDA_OK(cudaStreamWaitEvent(a.st, m.ev_b[l - 1], 0));
+            if ((rc = attention(a, l))) return rc;
+            if (m.lane_order) GPTRS_CUDA_OK(cudaEventRecord(m.ev_a[l], a.st));
+            if ((rc = pre_attention(b, l))) return rc;
+            if (m.lane_order) GPTRS_CUDA_OK(cudaStreamWaitEvent(b.st, m.ev_a[l], 0));
+            if ((rc = attention(b, l))) return rc;
+            if (m.lane_order) GPTRS_CUDA_OK(cudaEventRecord(m.ev_b[l], b.st));
+            if ((rc = post_attention(a, l))) return rc;
+            if ((rc = post_attention(b, l))) return rc;
+        }
+        GPTRS_CUDA_OK(cudaEventRecord(m.ev_join, b.st));
+        GPTRS_CUDA_OK(cudaStreamWaitEvent(st, m.ev_join, 0));
     }
-    if ((rc = norm(m.final_g, m.final_b))) return rc;
+    const Lane whole = {st, 0, T, chunk_pages, nullptr, 0};
+    if ((rc = norm(whole, m.final_g, m.final_b))) return rc;
     const void* xr = m.xn.p;
     if (!rows_identity) {
         ++m.launches;
@@ -428,7 +510,7 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         if ((rc = launch_kernel(gather_rows_kernel, dim3(n_rows), dim3(128), 0, st, 1, gp))) return rc;
         xr = m.xn_rows.p;
     }
-    if ((rc = linear(m, m.lm_head, xr, m.logits.p, n_rows, true, nullptr, false, false))) return rc;
+    if ((rc = linear(m, m.lm_head, xr, m.logits.p, n_rows, true, nullptr, false, false, st))) return rc;
     ++m.launches;
     if (m.tp == 1)
         return gptrs_cuda_sample_rows(m.logits.as<float>(), n_rows, c.vocab, temperature, m.sample_seed, m.d_sampled.as<int32_t>(), st);
@@ -476,11 +558,11 @@ int check_status(Model& m) {
     return GPTRS_OK;
 }
 
-int attention_plan(const Model& m, int T, int max_ctx, int* chunk_pages) {
+int attention_plan(const Model& m, int T, int max_ctx, size_t scratch_bytes, int* chunk_pages) {
     if (m.f32()) { *chunk_pages = 1; return GPTRS_OK; }
     int chunk = gptrs_cuda_attention_chunk_pages(max_ctx, T, m.cfg.n_kv_heads);
     // grow the chunk until the split partials fit the scratch buffer
-    while (chunk < 128 && gptrs_cuda_attention_scratch_bytes(T, m.cfg.n_q_heads, max_ctx, chunk) > m.attn_scratch.n) chunk *= 2;
+    while (chunk < 128 && gptrs_cuda_attention_scratch_bytes(T, m.cfg.n_q_heads, max_ctx, chunk) > scratch_bytes) chunk *= 2;
     *chunk_pages = chunk;
     return GPTRS_OK;
 }
@@ -524,6 +606,23 @@ int gptrs_cuda_model_create(const gptrs_model_config* cfg, gptrs_model** out) {
     m->cfg.n_q_heads = c.n_q_heads / tp; m->cfg.n_kv_heads = c.n_kv_heads / tp; m->cfg.d_mlp = c.d_mlp / tp;
     m->vocab_l = c.vocab / tp;
     GPTRS_CUDA_OK(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+    GPTRS_CUDA_OK(cudaStreamCreateWithFlags(&m->stream2, cudaStreamNonBlocking));
+    GPTRS_CUDA_OK(cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming));
+    GPTRS_CUDA_OK(cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming));
+    m->ev_a.resize(c.n_layers);
+    m->ev_b.resize(c.n_layers);
+    for (int l = 0; l < c.n_layers; ++l) {
+        GPTRS_CUDA_OK(cudaEventCreateWithFlags(&m->ev_a[l], cudaEventDisableTiming));
+        GPTRS_CUDA_OK(cudaEventCreateWithFlags(&m->ev_b[l], cudaEventDisableTiming));
+    }
+    if (const char* e = getenv("GPTRS_LANES")) m->n_lanes = atoi(e) >= 2 ? 2 : 1;
+    if (const char* e = getenv("GPTRS_LANE_ORDER")) m->lane_order = atoi(e) != 0;
+    {
+        int least = 0, greatest = 0;
+        GPTRS_CUDA_OK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+        m->lane_priority = greatest;  // numerically lower = more urgent
+        if (const char* e = getenv("GPTRS_LANE_PRIO")) if (atoi(e) == 0) m->lane_priority = 0;
+    }
     *out = reinterpret_cast<gptrs_model*>(m.release());
     return GPTRS_OK;
 }
@@ -781,7 +880,7 @@ int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* h, const int32_t* h_
     GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_ctx.p, st + 3 * stride, (size_t)T * 4, cudaMemcpyHostToDevice, s));
     if (n_logit_rows) GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_rows.p, st + 4 * stride, (size_t)n_logit_rows * 4, cudaMemcpyHostToDevice, s));
     int chunk = 1;
-    attention_plan(m, T, max_ctx, &chunk);
+    attention_plan(m, T, max_ctx, m.attn_scratch.n, &chunk);
     m.sample_seed = seed;
     // with no requested rows the pass still runs (it fills the KV cache); logits of row 0 are discarded
     const int rows = n_logit_rows > 0 ? n_logit_rows : 1;
@@ -847,7 +946,7 @@ int gptrs_cuda_generator_step(gptrs_model* h, const int32_t* h_tokens_in, int32_
     const int cap = m.f32() ? c.context_length : c.max_pages_per_seq * kPage;
     const int bucket = m.f32() ? c.context_length : std::min(cap, ((max_ctx + 511) / 512) * 512);
     int chunk = 1;
-    attention_plan(m, B, bucket, &chunk);
+    attention_plan(m, B, bucket, m.attn_scratch.n, &chunk);
     const int splits = m.f32() ? 1 : (bucket + chunk * kPage - 1) / (chunk * kPage);
     auto body = [&]() -> int {
         int r = enqueue_forward(m, B, bucket, chunk, B, true, 0.f);

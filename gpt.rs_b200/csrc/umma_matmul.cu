@@ -286,7 +286,8 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
         // warp w reads TMEM lanes 32*(w % 4); warps 0-3 take the low half of the columns, 4-7 the high half
         const int quarter = warp & 3;
         const int col = quarter * 32 + lane;  // output channel within the CTA tile == TMEM lane
-        const int c_begin = (warp >> 2) * (BN / 2), c_end = c_begin + BN / 2;
+        constexpr int kColHalves = BN >= 64 ? 2 : 1;  // a 32-column tile is read by warps 0-3 alone
+        const int c_begin = (warp >> 2) * (BN / kColHalves), c_end = (warp >> 2) < kColHalves ? c_begin + BN / kColHalves : c_begin;
 #pragma unroll 1
         for (int c0 = c_begin; c0 < c_end; c0 += 32) {
             float v[32];
@@ -361,8 +362,13 @@ int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
     cfg.blockDim = dim3(kUmmaThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attrs[2];
+    cudaLaunchAttribute attrs[3];
     int na = 0;
+    if (g_launch_priority != 0) {
+        attrs[na].id = cudaLaunchAttributePriority;
+        attrs[na].val.priority = g_launch_priority;
+        ++na;
+    }
     if (p.n_split > 1) {
         attrs[na].id = cudaLaunchAttributeClusterDimension;
         attrs[na].val.clusterDim.x = 1;
@@ -402,6 +408,7 @@ int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
     // decode-sized tiles: variant 0 = two groups, 3 stages, two CTAs per SM; 1 = four groups, 6 stages, one CTA per SM
     static int variant = -1;
     if (variant < 0) { const char* e = getenv("GPTRS_UMMA_VARIANT"); variant = e ? atoi(e) : 0; }
+    if (p.M <= 32 && variant == 0) return launch_umma<32, 2, 3>(p, grid, st);
     if (p.M <= 64) {
         if (variant == 1) return launch_umma<64, 4, 6>(p, grid, st);
         if (variant == 2) return launch_umma<64, 1, 3>(p, grid, st);

@@ -137,3 +137,55 @@ def time_ministral_step_sample(lib, batch=64, ctx_len=2048, n_layers_total=26, s
                 sample=f"1 of {n_layers_total} decoder blocks for {sample_rows} of {batch} sequences + final norm/lm_head/argmax "
                        f"for 1 (lm_head on {vocab_sample} of {vocab} columns), f32, one sequence per call as the reference's model path has no batch dimension "
                        f"(context {ctx_len}, capacity bucket {cap}), single thread, extrapolated linearly to the step")
+
+
+def time_gpt2_decode(lib, n_tokens: int = 4, ctx_start: int = 32, n_layers: int = 12, d_model: int = 768, n_heads: int = 12,
+                     d_mlp: int = 3072, vocab: int = 50257, seed: int = 0):
+    """Times `n_tokens` greedy decode steps of a GPT-2-small-shaped f32 model (the reference's README
+    workload: one sequence, dense KV cache, crates/gpt-rs/src/model/gpt.rs:459-545) on this host, single
+    thread, all 12 blocks and the full lm_head, through the reference's C kernels when they were built.
+    Weights are tiled from one random block (values do not matter for timing)."""
+    from types import SimpleNamespace
+    lib.oracle_clear_caches()
+    rng = np.random.default_rng(seed)
+    hd = d_model // n_heads
+    cfg = SimpleNamespace(kind="gpt", d_model=d_model, n_q=n_heads, n_kv=n_heads, hd=hd, d_mlp=d_mlp, rot=0, eps=1e-5)
+    block = rng.standard_normal(size=1 << 20, dtype=F) * F(0.02)
+    n = lambda *s: np.resize(block, s)  # noqa: E731
+    layers, keeps = [], []
+    for l in range(n_layers):
+        b = f"blocks.{l}"
+        params = {f"{b}.ln_1.gamma": np.ones(d_model, F), f"{b}.ln_1.beta": np.zeros(d_model, F),
+                  f"{b}.ln_2.gamma": np.ones(d_model, F), f"{b}.ln_2.beta": np.zeros(d_model, F),
+                  f"{b}.attention.w_qkv": np.roll(n(d_model, 3 * d_model), l), f"{b}.attention.b_qkv": np.zeros(3 * d_model, F),
+                  f"{b}.attention.w_out": np.roll(n(d_model, d_model), l), f"{b}.attention.b_out": np.zeros(d_model, F),
+                  f"{b}.feed_forward.w_in": np.roll(n(d_model, d_mlp), l), f"{b}.feed_forward.b_in": np.zeros(d_mlp, F),
+                  f"{b}.feed_forward.w_out": np.roll(n(d_mlp, d_model), l), f"{b}.feed_forward.b_out": np.zeros(d_model, F)}
+        L, keep = make_layer(cfg, params, l)
+        layers.append(L)
+        keeps.append(keep)
+    cap = 128  # capacity bucket of the dense cache for contexts up to 128 tokens
+    kc = [np.zeros((1, n_heads, cap, hd), F) for _ in range(n_layers)]
+    vc = [np.zeros((1, n_heads, cap, hd), F) for _ in range(n_layers)]
+    lm = n(d_model, vocab)
+    g, bta = np.ones(d_model, F), np.zeros(d_model, F)
+    logits = np.empty((1, vocab), F)
+    toks = np.empty(1, np.int32)
+    hidden = rng.standard_normal(size=(1, d_model), dtype=F)
+    pos = np.full(1, ctx_start, dtype=np.int32)
+
+    def step():
+        for l in range(n_layers):
+            rc = lib.oracle_block_decode_step(ctypes.byref(layers[l]), _p(hidden), _p(kc[l]), _p(vc[l]), _p(pos), 1, cap, None, None)
+            assert rc == 0
+        lib.oracle_head_step(0, _p(hidden), _p(g), _p(bta), 1e-5, _p(lm), 1, d_model, vocab, _p(logits), _p(toks))
+        pos[0] += 1
+
+    step()  # packs the weights (the reference's prepare step) and warms the caches
+    t0 = lib.oracle_now_seconds()
+    for _ in range(n_tokens):
+        step()
+        hidden[:] = rng.standard_normal(size=(1, d_model), dtype=F)
+    dt = lib.oracle_now_seconds() - t0
+    return dict(tokens_per_s=n_tokens / dt, kind=lib.oracle_kind().decode(), cores=1,
+                sample=f"{n_tokens} greedy decode steps of one sequence at context {ctx_start}+, all {n_layers} blocks + lm_head, f32, single thread")
