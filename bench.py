@@ -190,10 +190,11 @@ def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3, bits=4):
     else:
         nbytes = ops.w8a16_packed_bytes(n, k)
         mats = [torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device=dev) for _ in range(n_mats)]
-        for mt in mats:
-            mt[n * k:] = 0x1C
+        for mt in mats:  # per-channel fp16 scales of both layouts: finite bit patterns
+            mt[n * k:n * k + 2 * n] = 0x1C
+            mt[nbytes - 2 * ((n + 127) // 128) * 128:] = 0x1C
         run = ops.quant_matmul_w8a16
-        weight_bytes = nbytes
+        weight_bytes = n * k + 2 * n  # a launch reads ONE of the two weight layouts
     x = torch.randn((m, k), dtype=torch.bfloat16, device=dev)
     y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
     for mt in mats[:4]:

@@ -20,6 +20,15 @@ __host__ __device__ inline size_t w4_layout_b_weight_bytes(int64_t n, int64_t k)
 __host__ __device__ inline size_t w4_layout_b_bytes(int64_t n, int64_t k) {
     return w4_layout_b_weight_bytes(n, k) + (size_t)w4_blocks(n) * kCtaN * (k / 128) * 2;
 }
+// W8: layout A = tile-interleaved bytes + per-channel fp16 scales; layout B = row-ordered 16-byte entries for the
+// tensor-core kernel, [block][64-k chunk][512 entries], entry e = 16 consecutive k of row 16*(e>>6) + (e&15),
+// quarter (e>>4)&3 of the chunk, followed by [block][128] fp16 scales in tile-row order.
+__host__ __device__ inline size_t w8_layout_a_bytes(int64_t n, int64_t k) { return (size_t)n * k + (size_t)n * 2; }
+__host__ __device__ inline size_t w8_layout_b_weight_bytes(int64_t n, int64_t k) { return (size_t)w4_blocks(n) * kCtaN * k; }
+__host__ __device__ inline size_t w8_layout_b_bytes(int64_t n, int64_t k) {
+    return w8_layout_b_weight_bytes(n, k) + (size_t)w4_blocks(n) * kCtaN * 2;
+}
+
 constexpr int kRedStride = kCtaN + 4; // row stride (floats) of the partial tile in shared memory
 
 struct MatmulParams {

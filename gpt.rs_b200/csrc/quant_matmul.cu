@@ -23,6 +23,7 @@
 namespace gptrs {
 
 int umma_w4a16_matmul(MatmulParams p, cudaStream_t st);  // umma_matmul.cu
+int umma_w8a16_matmul(MatmulParams p, cudaStream_t st);  // umma_matmul.cu
 int umma_status(int* out);
 int w4_gemv(const MatmulParams& p, cudaStream_t st);  // quant_gemv.cu
 
@@ -428,6 +429,38 @@ __global__ void w8_unpack_kernel(const uint8_t* in_w, const __half* in_s, int64_
     }
 }
 
+// W8 layout B (tensor-core kernel): one thread per byte; bytes are stored as q + 128 like layout A.
+__global__ void w8_repack_rows_kernel(const int8_t* q, const __half* scales, int64_t N, int64_t K, int interleave,
+                                      uint8_t* out_w, __half* out_s) {
+    const int64_t chunks = K / 64, blocks = (N + 127) / 128;
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i < blocks * chunks * 8192) {
+        const int j = i & 15, e = (i >> 4) & 511;
+        const int64_t chunk = (i >> 13) % chunks, blk = (i >> 13) / chunks;
+        const int64_t row = blk * 128 + 16 * (e >> 6) + (e & 15);
+        const int64_t k = chunk * 64 + ((e >> 4) & 3) * 16 + j;
+        out_w[i] = row < N ? (uint8_t)(q[source_row(row, N, interleave) * K + k] + 128) : (uint8_t)128;
+    }
+    if (i < blocks * 128) {
+        const int64_t row = i;
+        out_s[i] = row < N ? scales[source_row(row, N, interleave)] : __float2half(0.f);
+    }
+}
+
+__global__ void w8_unpack_rows_kernel(const uint8_t* in_w, const __half* in_s, int64_t N, int64_t K, int interleave,
+                                      int8_t* q, __half* scales) {
+    const int64_t chunks = K / 64;
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i < N * K) {
+        const int64_t row = i / K, k = i % K;
+        const int64_t blk = row >> 7, chunk = k >> 6;
+        const int r = row & 127, kk = k & 63;
+        const int e = (r >> 4) * 64 + (kk >> 4) * 16 + (r & 15);
+        q[source_row(row, N, interleave) * K + k] = (int8_t)((int)in_w[((blk * chunks + chunk) * 512 + e) * 16 + (kk & 15)] - 128);
+    }
+    if (i < N) scales[source_row(i, N, interleave)] = in_s[i];
+}
+
 // Symmetric quantisation. One warp per (output channel n, 128-k group) for W4; one block per
 // channel for W8. Source is [K][N] (Linear layout) unless `transposed`.
 __device__ __forceinline__ float w_at(const float* w, int64_t n, int64_t k, int64_t N, int64_t K,
@@ -529,6 +562,10 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
         const unsigned char* base_b = static_cast<const unsigned char*>(d_packed) + w4_layout_a_bytes(n, k);
         p.wq_rows = reinterpret_cast<const uint4*>(base_b);
         p.scales_rows = reinterpret_cast<const __half*>(base_b + w4_layout_b_weight_bytes(n, k));
+    } else {
+        const unsigned char* base_b = static_cast<const unsigned char*>(d_packed) + w8_layout_a_bytes(n, k);
+        p.wq_rows = reinterpret_cast<const uint4*>(base_b);
+        p.scales_rows = reinterpret_cast<const __half*>(base_b + w8_layout_b_weight_bytes(n, k));
     }
     p.y = d_y;
     p.M = (int)m; p.N = (int)n; p.K = (int)k;
@@ -543,7 +580,7 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
         GPTRS_REQUIRE(!p.swiglu || n % 32 == 0, "swiglu needs N % 32 == 0");
     }
     cudaStream_t st = as_stream(stream);
-    if (BITS == 4 && m > 16 && umma_enabled()) return umma_w4a16_matmul(p, st);
+    if (m > 16 && umma_enabled()) return BITS == 4 ? umma_w4a16_matmul(p, st) : umma_w8a16_matmul(p, st);
     const int groups = (int)(k / 128);
     const int n_blocks = ceil_div(n, kCtaN);
     p.n_split = pick_split(n_blocks, groups);
@@ -577,7 +614,7 @@ size_t gptrs_cuda_w4a16_packed_bytes(int64_t n, int64_t k) {
 }
 size_t gptrs_cuda_w8a16_packed_bytes(int64_t n, int64_t k) {
     if (n <= 0 || k <= 0 || (n % 16) || (k % 128)) return 0;
-    return (size_t)n * k + (size_t)n * 2;
+    return w8_layout_a_bytes(n, k) + w8_layout_b_bytes(n, k);
 }
 
 int gptrs_cuda_w4a16_repack(const uint8_t* d_q, const uint16_t* d_scales, int64_t n, int64_t k,
@@ -633,6 +670,23 @@ int gptrs_cuda_w8a16_repack(const int8_t* d_q, const uint16_t* d_scales, int64_t
     __half* os = reinterpret_cast<__half*>(ow + (size_t)n * k);
     w8_repack_kernel<<<ceil_div(n * k, 256), 256, 0, as_stream(stream)>>>(
         d_q, reinterpret_cast<const __half*>(d_scales), n, k, interleave, ow, os);
+    GPTRS_CUDA_OK(cudaGetLastError());
+    uint8_t* base_b = ow + w8_layout_a_bytes(n, k);
+    w8_repack_rows_kernel<<<ceil_div((int64_t)w8_layout_b_weight_bytes(n, k), 256), 256, 0, as_stream(stream)>>>(
+        d_q, reinterpret_cast<const __half*>(d_scales), n, k, interleave, base_b,
+        reinterpret_cast<__half*>(base_b + w8_layout_b_weight_bytes(n, k)));
+    GPTRS_CUDA_OK(cudaGetLastError());
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_w8a16_unpack_rows(const void* d_packed, int64_t n, int64_t k, int interleave, int8_t* d_q,
+                                 uint16_t* d_scales, void* stream) {
+    GPTRS_REQUIRE(d_q && d_scales && d_packed, "null pointer");
+    GPTRS_REQUIRE(n > 0 && k > 0 && n % 16 == 0 && k % 128 == 0, "N % 16 == 0 and K % 128 == 0 required");
+    const uint8_t* base_b = static_cast<const uint8_t*>(d_packed) + w8_layout_a_bytes(n, k);
+    w8_unpack_rows_kernel<<<ceil_div(n * k, 256), 256, 0, as_stream(stream)>>>(
+        base_b, reinterpret_cast<const __half*>(base_b + w8_layout_b_weight_bytes(n, k)), n, k, interleave, d_q,
+        reinterpret_cast<__half*>(d_scales));
     GPTRS_CUDA_OK(cudaGetLastError());
     return GPTRS_OK;
 }

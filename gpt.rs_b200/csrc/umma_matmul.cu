@@ -111,8 +111,10 @@ constexpr size_t umma_smem_max(int bn, int stages) {
 // G = number of producer groups. Group g (256 / G threads) dequantises the stages it = g, g + G, ...; its
 // threads own G half-rows of such a stage each. The groups run out of phase, so that the fixed latencies of
 // one group (barrier wait, proxy fence) are covered by the arithmetic of the others.
-template <int BN, int G, int kStages>
-__global__ void __launch_bounds__(kUmmaThreads, (2 * (umma_smem_max(BN, kStages) + 1024) <= 227 * 1024) ? 2 : 1)
+// BITS = 8: per-channel scales are applied to the f32 accumulators in the epilogue, the producers only widen
+// int8 to bf16 (exact); a stage holds 512 sixteen-byte entries instead of 256.
+template <int BITS, int BN, int G, int kStages>
+__global__ void __launch_bounds__(kUmmaThreads, (BITS == 4 && 2 * (umma_smem_max(BN, kStages) + 1024) <= 227 * 1024) ? 2 : 1)
 umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_map, int* status) {
     constexpr int kBBytes = BN * 128;
     constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
@@ -153,17 +155,27 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     constexpr int kOwn = kPeriod * ((6 + G * kPeriod - 1) / (G * kPeriod));  // own stages kept in flight (>= 6 stages ahead)
     constexpr int kLaps = G * kOwn / kStages;                               // trips round the ring per outer iteration
     const int grp = tid / kGroupThreads, t = tid % kGroupThreads;
-    const uint4* wp = p.wq_rows + ((size_t)blockIdx.x * chunks_total + chunk0) * 256 + t;
-    const __half* sp = p.scales_rows + ((size_t)blockIdx.x * (chunks_total / 2) + chunk0 / 2) * kCtaN;
-    uint32_t st_addr[G][4];  // shared addresses (ring slot 0) of the four 16-byte chunks of unit j
-    int row[G];
+    constexpr int kEntries = BITS == 4 ? 256 : 512;  // 16-byte entries of one stage
+    constexpr int kUnits = kEntries / kGroupThreads;  // entries per thread and stage
+    constexpr int kOut = BITS == 4 ? 4 : 2;           // 16-byte shared chunks written per entry
+    const uint4* wp = p.wq_rows + ((size_t)blockIdx.x * chunks_total + chunk0) * kEntries + t;
+    const __half* sp = p.scales_rows + ((size_t)blockIdx.x * (chunks_total / 2) + chunk0 / 2) * kCtaN;  // W4 only
+    uint32_t st_addr[kUnits][kOut];  // shared addresses (ring slot 0) of the 16-byte chunks of unit j
+    int row[kUnits];
 #pragma unroll
-    for (int j = 0; j < G; ++j) {
+    for (int j = 0; j < kUnits; ++j) {
         const int e = t + j * kGroupThreads;
-        row[j] = 16 * (e >> 5) + (e & 15);
-        const uint32_t base = smem_u32(sA) + row[j] * 128 + (((((e >> 4) & 1) * 4) ^ (row[j] & 7)) << 4);
+        if (BITS == 4) {
+            row[j] = 16 * (e >> 5) + (e & 15);
+            const uint32_t base = smem_u32(sA) + row[j] * 128 + (((((e >> 4) & 1) * 4) ^ (row[j] & 7)) << 4);
 #pragma unroll
-        for (int w = 0; w < 4; ++w) st_addr[j][w] = base ^ (w << 4);
+            for (int w = 0; w < kOut; ++w) st_addr[j][w] = base ^ (w << 4);
+        } else {
+            row[j] = 16 * (e >> 6) + (e & 15);
+            const uint32_t base = smem_u32(sA) + row[j] * 128 + (((((e >> 4) & 3) * 2) ^ (row[j] & 7)) << 4);
+#pragma unroll
+            for (int w = 0; w < kOut; ++w) st_addr[j][w] = base ^ (w << 4);
+        }
     }
     uint32_t slot[kOwn], par0[kOwn];
 #pragma unroll
@@ -174,18 +186,18 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
     // The first packed weights are requested before anything else, so that their DRAM latency covers the
     // barrier and TMEM set-up below (weights are constants: no need to wait for the previous kernel).
-    uint4 ring[kOwn][G];
-    __half sring[kOwn][G];
+    uint4 ring[kOwn][kUnits];
+    __half sring[kOwn][BITS == 4 ? kUnits : 1];
 #pragma unroll
     for (int o = 0; o < kOwn; ++o) {
         const int it = warp < kProducerWarps ? grp + G * o : n_it;
 #pragma unroll
-        for (int j = 0; j < G; ++j) {
+        for (int j = 0; j < kUnits; ++j) {
             ring[o][j] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-            sring[o][j] = __float2half(0.f);
+            if (BITS == 4) sring[o][j] = __float2half(0.f);
             if (it < n_it) {
-                ring[o][j] = ldg_stream_16(wp + (size_t)it * 256 + j * kGroupThreads);
-                sring[o][j] = __ldg(sp + (size_t)((chunk0 + it) / 2 - chunk0 / 2) * kCtaN + row[j]);
+                ring[o][j] = ldg_stream_16(wp + (size_t)it * kEntries + j * kGroupThreads);
+                if (BITS == 4) sring[o][j] = __ldg(sp + (size_t)((chunk0 + it) / 2 - chunk0 / 2) * kCtaN + row[j]);
             }
         }
     }
@@ -227,25 +239,45 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
                     const uint32_t a_off = slot[o] * kABytes;
                     const int nxt = it + G * kOwn;
 #pragma unroll
-                    for (int j = 0; j < G; ++j) {
+                    for (int j = 0; j < kUnits; ++j) {
                         const uint4 cur = ring[o][j];
-                        const __nv_bfloat162 sc = __float2bfloat162_rn(__half2float(sring[o][j]));
+                        __nv_bfloat162 sc;
+                        if (BITS == 4) sc = __float2bfloat162_rn(__half2float(sring[o][j]));
                         if (nxt < n_it) {
-                            ring[o][j] = ldg_stream_16(wp + (size_t)nxt * 256 + j * kGroupThreads);
-                            sring[o][j] = __ldg(sp + (size_t)((chunk0 + nxt) / 2 - chunk0 / 2) * kCtaN + row[j]);
+                            ring[o][j] = ldg_stream_16(wp + (size_t)nxt * kEntries + j * kGroupThreads);
+                            if (BITS == 4) sring[o][j] = __ldg(sp + (size_t)((chunk0 + nxt) / 2 - chunk0 / 2) * kCtaN + row[j]);
                         }
                         const uint32_t q4[4] = {cur.x, cur.y, cur.z, cur.w};
+                        if (BITS == 4) {
 #pragma unroll
-                        for (int w = 0; w < 4; ++w) {
-                            const uint32_t q = q4[w];
-                            uint32_t vv[4];
+                            for (int w = 0; w < 4; ++w) {
+                                const uint32_t q = q4[w];
+                                uint32_t vv[4];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;   // (k 2i, k 2i+1) + 128
-                                __nv_bfloat162 d = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136), sc);
-                                vv[i] = *reinterpret_cast<uint32_t*>(&d);
+                                for (int i = 0; i < 4; ++i) {
+                                    uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;   // (k 2i, k 2i+1) + 128
+                                    __nv_bfloat162 d = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136), sc);
+                                    vv[i] = *reinterpret_cast<uint32_t*>(&d);
+                                }
+                                st_shared_v4(st_addr[j][w] + a_off, vv[0], vv[1], vv[2], vv[3]);   // 8 consecutive k
                             }
-                            st_shared_v4(st_addr[j][w] + a_off, vv[0], vv[1], vv[2], vv[3]);   // 8 consecutive k
+                        } else {
+                            // byte b = q + 128: the f32 with bit pattern 0x4B000000 | b is 2^23 + b, exactly
+#pragma unroll
+                            for (int w = 0; w < 2; ++w) {
+                                uint32_t vv[4];
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    const uint32_t q = q4[2 * w + h];
+                                    float f[4];
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i)
+                                        f[i] = __uint_as_float(__byte_perm(q, 0x4B000000u, 0x7650 + i)) - 8388736.f;
+                                    vv[2 * h] = pack_bf16x2(f[0], f[1]);
+                                    vv[2 * h + 1] = pack_bf16x2(f[2], f[3]);
+                                }
+                                st_shared_v4(st_addr[j][w] + a_off, vv[0], vv[1], vv[2], vv[3]);   // 8 consecutive k
+                            }
                         }
                     }
                     fence_proxy_async();
@@ -292,6 +324,11 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
         for (int c0 = c_begin; c0 < c_end; c0 += 32) {
             float v[32];
             tmem_ld_32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+            if (BITS == 8) {
+                const float ch_scale = __half2float(p.scales_rows[(size_t)blockIdx.x * kCtaN + col]);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] *= ch_scale;
+            }
             int owner = c0 % sr.S, local_row = c0 / sr.S;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -334,7 +371,7 @@ int* umma_status_word() {
     return d;
 }
 
-template <int BN, int G, int kStages>
+template <int BITS, int BN, int G, int kStages>
 int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return fail(GPTRS_EXECUTION, "cuTensorMapEncodeTiled is not available");
@@ -351,7 +388,7 @@ int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
     if (!status) return fail(GPTRS_EXECUTION, "cannot allocate the status word");
     const size_t smem = (size_t)kStages * (kABytes + BN * 128) + 1024 + (p.n_split > 1 ? split_slots_bytes(BN, p.n_split) : 0);
     constexpr size_t smem_max = umma_smem_max(BN, kStages);
-    auto kern = umma_w4a16_kernel<BN, G, kStages>;
+    auto kern = umma_w4a16_kernel<BITS, BN, G, kStages>;
     static bool attr_done = false;
     if (!attr_done) {
         GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
@@ -398,25 +435,48 @@ int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
     // cluster are co-scheduled and meet at the reduction.
     static int pct = 0;  // CTAs per 100 SMs (GPTRS_UMMA_CTAS_PCT overrides the default of 250)
     if (pct == 0) { const char* e = getenv("GPTRS_UMMA_CTAS_PCT"); pct = e ? atoi(e) : 250; if (pct <= 0) pct = 250; }
-    int split = (sm_count() * pct / 100) / n_blocks;
+    // Row tile: 256 rows when that alone fills the GPU (no K split: its shared memory has no room for receive
+    // slots), otherwise tiles of up to 128 rows with a K split over what is left of the SMs.
+    const bool big_tile = p.M > 128 && n_blocks * ceil_div(p.M, 256) >= sm_count();
+    const int m_blocks = big_tile ? ceil_div(p.M, 256) : ceil_div(p.M, 128);
+    // tiles of up to 64 rows fit two CTAs per SM, the 128-row tile one: never more CTAs than one wave of those
+    const int ctas = p.M <= 64 ? sm_count() * pct / 100 : sm_count();
+    int split = big_tile ? 1 : ctas / (n_blocks * m_blocks);
     split = split < 1 ? 1 : (split > 8 ? 8 : split);
     if (split > groups) split = groups;
-    if (p.M > 128) split = 1;  // the 256-row tile leaves no room for receive slots; it has M blocks to fill the GPU
     p.n_split = split;
     p.groups_per_cta = (groups + split - 1) / split;
-    const dim3 grid(n_blocks, split, ceil_div(p.M, 256));
+    const dim3 grid(n_blocks, split, m_blocks);
     // decode-sized tiles: variant 0 = two groups, 3 stages, two CTAs per SM; 1 = four groups, 6 stages, one CTA per SM
     static int variant = -1;
     if (variant < 0) { const char* e = getenv("GPTRS_UMMA_VARIANT"); variant = e ? atoi(e) : 0; }
-    if (p.M <= 32 && variant == 0) return launch_umma<32, 2, 3>(p, grid, st);
+    if (p.M <= 32 && variant == 0) return launch_umma<4, 32, 2, 3>(p, grid, st);
     if (p.M <= 64) {
-        if (variant == 1) return launch_umma<64, 4, 6>(p, grid, st);
-        if (variant == 2) return launch_umma<64, 1, 3>(p, grid, st);
-        if (variant == 3) return launch_umma<64, 4, 4>(p, grid, st);
-        return launch_umma<64, 2, 3>(p, grid, st);
+        if (variant == 1) return launch_umma<4, 64, 4, 6>(p, grid, st);
+        if (variant == 2) return launch_umma<4, 64, 1, 3>(p, grid, st);
+        if (variant == 3) return launch_umma<4, 64, 4, 4>(p, grid, st);
+        return launch_umma<4, 64, 2, 3>(p, grid, st);
     }
-    if (p.M <= 128) return launch_umma<128, 2, 4>(p, grid, st);
-    return launch_umma<256, 2, 4>(p, grid, st);
+    if (!big_tile) return launch_umma<4, 128, 2, 4>(p, grid, st);
+    return launch_umma<4, 256, 2, 4>(p, grid, st);
+}
+
+// W8A16 on the same kernel (M > 16).
+int umma_w8a16_matmul(MatmulParams p, cudaStream_t st) {
+    const int groups = p.K / 128;
+    const int n_blocks = ceil_div(p.N, kCtaN);
+    const bool big_tile = p.M > 128 && n_blocks * ceil_div(p.M, 256) >= sm_count();
+    const int m_blocks = big_tile ? ceil_div(p.M, 256) : ceil_div(p.M, 128);
+    // one CTA per SM: a W8 stage carries twice the bytes of a W4 stage
+    int split = big_tile ? 1 : sm_count() / (n_blocks * m_blocks);
+    split = split < 1 ? 1 : (split > 8 ? 8 : split);
+    if (split > groups) split = groups;
+    p.n_split = split;
+    p.groups_per_cta = (groups + split - 1) / split;
+    const dim3 grid(n_blocks, split, m_blocks);
+    if (p.M <= 64) return launch_umma<8, 64, 2, 4>(p, grid, st);
+    if (!big_tile) return launch_umma<8, 128, 2, 4>(p, grid, st);
+    return launch_umma<8, 256, 2, 4>(p, grid, st);
 }
 
 int umma_status(int* out) {

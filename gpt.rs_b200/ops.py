@@ -74,6 +74,14 @@ def w8a16_unpack(packed: torch.Tensor, n: int, k: int, interleave_gate_up: bool 
     return q, s
 
 
+def w8a16_unpack_rows(packed: torch.Tensor, n: int, k: int, interleave_gate_up: bool = False):
+    """Reads the row-ordered (tensor-core) copy of a packed W8 buffer back to canonical form."""
+    q = torch.empty((n, k), dtype=torch.int8, device=packed.device)
+    s = torch.empty((n,), dtype=torch.float16, device=packed.device)
+    check(lib().gptrs_cuda_w8a16_unpack_rows(_ptr(packed), n, k, int(interleave_gate_up), _ptr(q), _ptr(s), _stream()))
+    return q, s
+
+
 def quantize_w4(w: torch.Tensor, transposed: bool = False):
     """w: f32 [K][N] (Linear layout) or [N][K] when transposed -> (q uint8 [N][K/2], scales f16)."""
     k, n = (w.shape[1], w.shape[0]) if transposed else (w.shape[0], w.shape[1])

@@ -81,6 +81,8 @@ int gptrs_cuda_w4a16_unpack(const void* d_packed, int64_t n, int64_t k, int inte
                             uint8_t* d_q, uint16_t* d_scales, void* stream);
 int gptrs_cuda_w8a16_unpack(const void* d_packed, int64_t n, int64_t k, int interleave_gate_up, int8_t* d_q,
                             uint16_t* d_scales, void* stream);
+int gptrs_cuda_w8a16_unpack_rows(const void* d_packed, int64_t n, int64_t k, int interleave_gate_up, int8_t* d_q,
+                                 uint16_t* d_scales, void* stream);
 
 /* Quantise an f32 Linear weight stored [in=K][out=N] (nn/layers/linear.rs:14) to canonical
  * W4 group-128 symmetric (scale = fp16(max|w| / 7), q = clamp(rint(w / scale), -8, 7)) or W8

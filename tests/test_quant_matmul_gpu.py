@@ -43,9 +43,10 @@ def test_w8_repack_unpack_bit_exact(cuda, n, k):
     s = _scales(rng, (n,))
     for inter in (False, True) if n % 32 == 0 else (False,):
         packed = ops.w8a16_repack(_dev(q, cuda), _dev(s, cuda), n, k, inter)
-        q2, s2 = ops.w8a16_unpack(packed, n, k, inter)
-        assert np.array_equal(q2.cpu().numpy(), q)
-        assert np.array_equal(s2.cpu().numpy().view(np.uint16), s.view(np.uint16))
+        for unpack in (ops.w8a16_unpack, ops.w8a16_unpack_rows):  # both layouts held by the buffer
+            q2, s2 = unpack(packed, n, k, inter)
+            assert np.array_equal(q2.cpu().numpy(), q)
+            assert np.array_equal(s2.cpu().numpy().view(np.uint16), s.view(np.uint16))
 
 
 @pytest.mark.parametrize("transposed", [False, True])
