@@ -72,7 +72,7 @@ int gptrs_cuda_w4a16_repack(const uint8_t* d_q, const uint16_t* d_scales, int64_
                             int interleave_gate_up, void* d_packed, void* stream);
 int gptrs_cuda_w8a16_repack(const int8_t* d_q, const uint16_t* d_scales, int64_t n, int64_t k,
                             int interleave_gate_up, void* d_packed, void* stream);
-/* Kernel layout -> canonical q/scales (the bit-exact unpack check). The W4 buffer holds two layouts
+/* Kernel layout -> canonical q/scales (the bit-exact unpack check). A packed buffer holds two layouts
  * (fragment-ordered for the mma.sync kernel, row-ordered for the tcgen05 kernel); _unpack reads the
  * first, _unpack_rows the second. */
 int gptrs_cuda_w4a16_unpack_rows(const void* d_packed, int64_t n, int64_t k, int interleave_gate_up,

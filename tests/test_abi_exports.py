@@ -22,7 +22,7 @@ def test_every_declared_symbol_is_exported():
 def test_packed_sizes_and_argument_errors_without_gpu():
     lib = gptrs_b200.lib()
     assert lib.gptrs_cuda_w4a16_packed_bytes(3072, 3072) == 2 * (3072 * 3072 // 2 + 3072 * 24 * 2)  # two layouts
-    assert lib.gptrs_cuda_w8a16_packed_bytes(3072, 3072) == 3072 * 3072 + 3072 * 2
+    assert lib.gptrs_cuda_w8a16_packed_bytes(3072, 3072) == 2 * (3072 * 3072 + 3072 * 2)  # two layouts
     assert lib.gptrs_cuda_w4a16_packed_bytes(3072, 100) == 0
     # shape validation happens before any CUDA call
     st = lib.gptrs_cuda_quant_matmul_w4a16(1, 1, 1, 1, 3072, 100, None, None)
