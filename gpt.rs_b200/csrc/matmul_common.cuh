@@ -43,6 +43,7 @@ struct MatmulParams {
     int M, N, K;
     int groups_per_cta;  // K range of one CTA, in 128-k groups
     int n_split;         // cluster size along K
+    int k_intra;         // GEMV kernel: warps of a CTA that split the CTA's K range among themselves (1, 2, 4, 8)
     int out_f32;
     int swiglu;
 };
@@ -90,7 +91,7 @@ struct SplitReduce {
 // Second half: barrier, local sum over the S slots, bias / residual / SwiGLU, store. All threads of the CTA.
 template <int MPAD>
 __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const SplitReduce& sr, const float* slots, int tid,
-                                                    int n_threads, int m0, int n_cta0) {
+                                                    int n_threads, int m0, int n_cta0, int tile_cols = kCtaN) {
     const int S = sr.S, rank = sr.rank, rows_max = sr.rows_max;
     if (S > 1) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
     auto gather = [&](int local_row, int c) {
@@ -103,8 +104,10 @@ __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const
     };
     const int rows_own = (MPAD - rank + S - 1) / S;  // rows rank, rank + S, ...
     if (!p.swiglu) {
-        for (int j = tid; j < rows_own * 32; j += n_threads) {
-            const int lr = j >> 5, c4 = j & 31;
+        const int cols4 = tile_cols >> 2;  // float4 columns of the CTA tile (a power of two)
+        const int sh4 = 31 - __clz(cols4);
+        for (int j = tid; j < rows_own * cols4; j += n_threads) {
+            const int lr = j >> sh4, c4 = j & (cols4 - 1);
             const int m = m0 + rank + S * lr, n = n_cta0 + c4 * 4;
             if (m >= p.M || n >= p.N) continue;
             float4 v = gather(lr, c4 * 4);
@@ -126,8 +129,10 @@ __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const
     } else {
         // Each 16-channel tile holds 8 gate rows followed by the 8 matching up rows.
         const int NO = p.N >> 1;
-        for (int j = tid; j < rows_own * 16; j += n_threads) {
-            const int lr = j >> 4, q = j & 15;
+        const int cols8 = tile_cols >> 3;  // 4 gate + 4 up values per item
+        const int sh8 = 31 - __clz(cols8);
+        for (int j = tid; j < rows_own * cols8; j += n_threads) {
+            const int lr = j >> sh8, q = j & (cols8 - 1);
             const int tile = q >> 1, half = q & 1;
             const int m = m0 + rank + S * lr, n_out = (n_cta0 >> 1) + tile * 8 + half * 4;
             if (m >= p.M || n_out >= NO) continue;

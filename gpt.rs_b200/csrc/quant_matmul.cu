@@ -25,7 +25,7 @@ namespace gptrs {
 int umma_w4a16_matmul(MatmulParams p, cudaStream_t st);  // umma_matmul.cu
 int umma_w8a16_matmul(MatmulParams p, cudaStream_t st);  // umma_matmul.cu
 int umma_status(int* out);
-int w4_gemv(const MatmulParams& p, cudaStream_t st);  // quant_gemv.cu
+int w4_gemv(MatmulParams p, cudaStream_t st);  // quant_gemv.cu
 
 namespace {
 
