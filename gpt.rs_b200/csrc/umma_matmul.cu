@@ -241,8 +241,15 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
 #pragma unroll
                     for (int j = 0; j < kUnits; ++j) {
                         const uint4 cur = ring[o][j];
-                        __nv_bfloat162 sc;
-                        if (BITS == 4) sc = __float2bfloat162_rn(__half2float(sring[o][j]));
+                        // fp16 scale = hi + lo exactly (8 + 3 significant bits), so that fma(n, hi, n * lo) is the
+                        // product n * scale rounded ONCE to bf16: no error shared by the 128 weights of a group
+                        __nv_bfloat162 sc, sc_lo;
+                        if (BITS == 4) {
+                            const float sf = __half2float(sring[o][j]);
+                            const __nv_bfloat16 hi = __float2bfloat16_rn(sf);
+                            sc = __halves2bfloat162(hi, hi);
+                            sc_lo = __float2bfloat162_rn(sf - __bfloat162float(hi));
+                        }
                         if (nxt < n_it) {
                             ring[o][j] = ldg_stream_16(wp + (size_t)nxt * kEntries + j * kGroupThreads);
                             if (BITS == 4) sring[o][j] = __ldg(sp + (size_t)((chunk0 + nxt) / 2 - chunk0 / 2) * kCtaN + row[j]);
@@ -256,7 +263,8 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;   // (k 2i, k 2i+1) + 128
-                                    __nv_bfloat162 d = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136), sc);
+                                    const __nv_bfloat162 n = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136);
+                                    __nv_bfloat162 d = __hfma2(n, sc, __hmul2(n, sc_lo));
                                     vv[i] = *reinterpret_cast<uint32_t*>(&d);
                                 }
                                 st_shared_v4(st_addr[j][w] + a_off, vv[0], vv[1], vv[2], vv[3]);   // 8 consecutive k
