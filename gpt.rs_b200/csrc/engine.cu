@@ -347,7 +347,8 @@ int attention_plan(const Model& m, int T, int max_ctx, size_t scratch_bytes, int
 // Enqueues one forward pass over T tokens whose ids / slots / positions / visible lengths are
 // already in the device arrays. `rows`: number of rows that get logits (row indices in d_rows,
 // or all T rows in order when rows_identity).
-int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, bool rows_identity, float temperature) {
+int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, bool rows_identity, float temperature,
+                    bool prefill_groups = false) {
     const auto& c = m.cfg;
     const int D = c.d_model;
     cudaStream_t st = m.stream;
@@ -441,7 +442,9 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         if (splits > 1) ++m.launches;
         // In a two-lane step the projections of the other lane outrank attention CTAs that wait for an SM.
         struct PriorityGuard { int saved; PriorityGuard() : saved(g_launch_priority) { g_launch_priority = 0; } ~PriorityGuard() { g_launch_priority = saved; } } guard;
-        return gptrs_cuda_paged_attention_decode(at(m.q_rot, (size_t)m.QD() * 2, ln), pool, m.d_page_table.as<int32_t>(),
+        // token rows that come in per-sequence groups (a prompt chunk) share the K/V stream of their group
+        auto attention_fn = prefill_groups ? gptrs_cuda_paged_attention_prefill : gptrs_cuda_paged_attention_decode;
+        return attention_fn(at(m.q_rot, (size_t)m.QD() * 2, ln), pool, m.d_page_table.as<int32_t>(),
                                                  c.max_pages_per_seq, ints(m.d_slot, ln), ints(m.d_ctx, ln), out, ln.scratch,
                                                  ln.scratch_n, m.d_status.as<int32_t>(), ln.T, c.n_q_heads, c.n_kv_heads,
                                                  c.head_dim, max_ctx, ln.chunk, ln.st);
@@ -879,13 +882,28 @@ int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* h, const int32_t* h_
     GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_pos.p, st + 2 * stride, (size_t)T * 4, cudaMemcpyHostToDevice, s));
     GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_ctx.p, st + 3 * stride, (size_t)T * 4, cudaMemcpyHostToDevice, s));
     if (n_logit_rows) GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_rows.p, st + 4 * stride, (size_t)n_logit_rows * 4, cudaMemcpyHostToDevice, s));
+    // Prefill chunks: when every aligned group of 16 / (query heads per kv head) rows belongs to one sequence,
+    // the attention kernel streams the K/V pages once per group instead of once per row.
+    bool prefill_groups = false;
+    int attn_rows = T;
+    if (!m.f32() && T >= 2) {
+        const int grp = c.n_q_heads / c.n_kv_heads;
+        if (grp == 1 || grp == 2 || grp == 4 || grp == 8) {
+            const int tq = 16 / grp;
+            prefill_groups = tq > 1;
+            for (int i = 0; i < T && prefill_groups; ++i) prefill_groups = h_slots[i] == h_slots[i - i % tq];
+            if (prefill_groups) attn_rows = (T + tq - 1) / tq;
+        }
+    }
     int chunk = 1;
-    attention_plan(m, T, max_ctx, m.attn_scratch.n, &chunk);
+    attention_plan(m, attn_rows, max_ctx, m.attn_scratch.n, &chunk);
+    // the split partials are indexed by token row: the scratch must hold T rows at this chunk size
+    while (chunk < 128 && gptrs_cuda_attention_scratch_bytes(T, c.n_q_heads, max_ctx, chunk) > m.attn_scratch.n) chunk *= 2;
     m.sample_seed = seed;
     // with no requested rows the pass still runs (it fills the KV cache); logits of row 0 are discarded
     const int rows = n_logit_rows > 0 ? n_logit_rows : 1;
     if (n_logit_rows == 0) GPTRS_CUDA_OK(cudaMemsetAsync(m.d_rows.p, 0, 4, s));
-    rc = enqueue_forward(m, T, max_ctx, chunk, rows, false, temperature);
+    rc = enqueue_forward(m, T, max_ctx, chunk, rows, false, temperature, prefill_groups);
     if (rc) return rc;
     if (h_logits && n_logit_rows)
         GPTRS_CUDA_OK(cudaMemcpyAsync(m.h_logits, m.logits.p, (size_t)n_logit_rows * m.vocab_l * 4, cudaMemcpyDeviceToHost, s));

@@ -49,19 +49,31 @@ struct AttnParams {
 
 __device__ __forceinline__ int swz(int tok, int chunk) { return tok * 256 + ((chunk ^ (tok & 7)) << 4); }
 
-template <int kDepth>
+// kMulti = false: one query token per CTA (decode; the 4 or 8 query heads of the GQA group are rows 0..7 of the
+// 16-row MMA tile). kMulti = true: 16 / group consecutive rows of the token list per CTA, all of ONE sequence (a
+// prefill chunk): row r of the tile is query head r % group of token r / group, every row has its own visible
+// length, so the K/V pages are streamed once for 16 / group tokens instead of once per token.
+template <int kDepth, bool kMulti>
 __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_attention_kernel(const AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t full_bar[kAttnWarps][kDepth];
 
-    const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int split = blockIdx.x, h = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int group = p.Hq / p.Hkv;
+    const int tq = kMulti ? 16 / group : 1;  // query tokens of this CTA
+    const int b = blockIdx.z * tq;           // the first of them
 
     pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
-    const int len = p.ctx_len[b];
+    // rows g (lo) and g + 8 (hi) of the tile belong to this lane
+    const int tok_lo = kMulti ? b + g / group : b, tok_hi = kMulti ? b + (g + 8) / group : b;
+    const bool valid_lo = kMulti ? tok_lo < p.T : g < group, valid_hi = kMulti && tok_hi < p.T;
+    const int len_lo = valid_lo ? p.ctx_len[tok_lo] : 0, len_hi = valid_hi ? p.ctx_len[tok_hi] : 0;
+    int len = p.ctx_len[b];
+    if (kMulti)
+        for (int i = 1; i < tq && b + i < p.T; ++i) len = max(len, p.ctx_len[b + i]);
     const int chunk_tokens = p.chunk_pages * kPageTokens;
     const int first_tok = split * chunk_tokens;
     if (first_tok >= len) return;  // whole CTA leaves together, before any barrier
@@ -93,15 +105,24 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
     };
     for (int j = 0; j < kDepth && j < n_my; ++j) issue(j);
 
-    // Q fragments: row g of the A tile = query head h*group + g (rows >= group are zero).
-    uint32_t qf[8][2];
+    // Q fragments: row g of the A tile = query head h*group + g (rows >= group are zero); with kMulti rows g
+    // and g + 8 are (token, head) pairs as described above.
+    uint32_t qf[8][kMulti ? 4 : 2];
     {
-        const bool valid = g < group;
-        const __nv_bfloat16* qrow = p.q + ((size_t)b * p.Hq + h * group + (valid ? g : 0)) * kHD;
+        const int head_lo = h * group + (kMulti ? g % group : (valid_lo ? g : 0));
+        const __nv_bfloat16* qrow = p.q + ((size_t)(valid_lo ? tok_lo : b) * p.Hq + head_lo) * kHD;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-            qf[ks][0] = valid ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
-            qf[ks][1] = valid ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+            qf[ks][0] = valid_lo ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+            qf[ks][1] = valid_lo ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+        }
+        if (kMulti) {
+            const __nv_bfloat16* qhi = p.q + ((size_t)(valid_hi ? tok_hi : b) * p.Hq + h * group + (g + 8) % group) * kHD;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                qf[ks][2] = valid_hi ? *reinterpret_cast<const uint32_t*>(qhi + ks * 16 + 2 * t) : 0u;
+                qf[ks][3] = valid_hi ? *reinterpret_cast<const uint32_t*>(qhi + ks * 16 + 8 + 2 * t) : 0u;
+            }
         }
     }
 
@@ -110,7 +131,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
     for (int i = 0; i < 16; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;   // row g
+    float m_hi = -INFINITY, l_hi = 0.f;     // row g + 8 (kMulti)
     bool failed = false;
 
     const uint32_t ring_addr = smem_u32(my_ring);
@@ -129,7 +151,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
         for (int ks = 0; ks < 8; ++ks) {
             uint32_t bf[4];
             ldmatrix_x4(bf, kb + swz(k_tok, 2 * ks + k_half));
-            uint32_t a[4] = {qf[ks][0], 0u, qf[ks][1], 0u};
+            uint32_t a[4] = {qf[ks][0], kMulti ? qf[ks][kMulti ? 2 : 0] : 0u, qf[ks][1], kMulti ? qf[ks][kMulti ? 3 : 1] : 0u};
             mma_bf16_16816(s[0], a, bf[0], bf[1]);
             mma_bf16_16816(s[1], a, bf[2], bf[3]);
         }
@@ -142,33 +164,68 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
             for (int e = 0; e < 2; ++e) {
                 int tok = tok0 + nt * 8 + 2 * t + e;
                 float v = s[nt][e] * p.scale_log2;
-                v = tok < len ? v : -INFINITY;
+                v = tok < (kMulti ? len_lo : len) ? v : -INFINITY;
                 s[nt][e] = v;
                 mx = fmaxf(mx, v);
             }
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);  // finite: token tok0 is always visible
-        const float alpha = exp2f(m_run - m_new);
+        // decode: finite, token tok0 is always visible. kMulti: a shorter row may see nothing of this page (or of
+        // this split) yet; its maximum stays -inf and 0 stands in for it in the exponents.
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = (kMulti && m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = exp2f(m_run - m_use);
         float pr[2][2];
         float psum = 0.f;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                pr[nt][e] = exp2f(s[nt][e] - m_new);
+                pr[nt][e] = exp2f(s[nt][e] - m_use);
                 psum += pr[nt][e];
             }
         l_run = l_run * alpha + psum;
         m_run = m_new;
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+        float alpha_hi = 1.f;
+        float ph[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+        if (kMulti) {
+            float mxh = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    int tok = tok0 + nt * 8 + 2 * t + e;
+                    float v = s[nt][2 + e] * p.scale_log2;
+                    v = tok < len_hi ? v : -INFINITY;
+                    s[nt][2 + e] = v;
+                    mxh = fmaxf(mxh, v);
+                }
+            mxh = fmaxf(mxh, __shfl_xor_sync(0xffffffffu, mxh, 1));
+            mxh = fmaxf(mxh, __shfl_xor_sync(0xffffffffu, mxh, 2));
+            const float mh_new = fmaxf(m_hi, mxh);
+            const float mh_use = mh_new == -INFINITY ? 0.f : mh_new;
+            alpha_hi = exp2f(m_hi - mh_use);
+            float ps = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    ph[nt][e] = exp2f(s[nt][2 + e] - mh_use);
+                    ps += ph[nt][e];
+                }
+            l_hi = l_hi * alpha_hi + ps;
+            m_hi = mh_new;
+        }
+        if (__any_sync(0xffffffffu, alpha != 1.f || alpha_hi != 1.f)) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 o[i][0] *= alpha;
                 o[i][1] *= alpha;
+                if (kMulti) { o[i][2] *= alpha_hi; o[i][3] *= alpha_hi; }
             }
         }
-        uint32_t pa[4] = {pack_bf16x2(pr[0][0], pr[0][1]), 0u, pack_bf16x2(pr[1][0], pr[1][1]), 0u};
+        uint32_t pa[4] = {pack_bf16x2(pr[0][0], pr[0][1]), kMulti ? pack_bf16x2(ph[0][0], ph[0][1]) : 0u,
+                          pack_bf16x2(pr[1][0], pr[1][1]), kMulti ? pack_bf16x2(ph[1][0], ph[1][1]) : 0u};
 #pragma unroll
         for (int np = 0; np < 8; ++np) {
             uint32_t bf[4];
@@ -187,42 +244,65 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
     // ---- merge the 4 warps (rows g < group live in lanes 0..15 when group <= 4, else all) ---
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (kMulti) {
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    }
     __syncthreads();  // every stage has been consumed; the rings can be reused
-    float* mo = reinterpret_cast<float*>(smem);                       // [warp][8][128]
-    float* mml = mo + kAttnWarps * 8 * kHD;                           // [warp][8][2]
-    if (g < group) {
+    constexpr int kRows = kMulti ? 16 : 8;                            // tile rows kept per warp
+    float* mo = reinterpret_cast<float*>(smem);                       // [warp][kRows][128]
+    float* mml = mo + kAttnWarps * kRows * kHD;                       // [warp][kRows][2]
+    if (kMulti || g < group) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             float2 v = make_float2(o[i][0], o[i][1]);
-            *reinterpret_cast<float2*>(mo + (warp * 8 + g) * kHD + i * 8 + 2 * t) = v;
+            *reinterpret_cast<float2*>(mo + (warp * kRows + g) * kHD + i * 8 + 2 * t) = v;
+            if (kMulti) {
+                float2 u = make_float2(o[i][2], o[i][3]);
+                *reinterpret_cast<float2*>(mo + (warp * kRows + g + 8) * kHD + i * 8 + 2 * t) = u;
+            }
         }
         if (t == 0) {
-            mml[(warp * 8 + g) * 2] = m_run;
-            mml[(warp * 8 + g) * 2 + 1] = l_run;
+            mml[(warp * kRows + g) * 2] = m_run;
+            mml[(warp * kRows + g) * 2 + 1] = l_run;
+            if (kMulti) {
+                mml[(warp * kRows + g + 8) * 2] = m_hi;
+                mml[(warp * kRows + g + 8) * 2 + 1] = l_hi;
+            }
         }
     }
     __syncthreads();
-    for (int idx = tid; idx < group * (kHD / 4); idx += kAttnWarps * 32) {
+    const int n_rows = kMulti ? 16 : group;
+    for (int idx = tid; idx < n_rows * (kHD / 4); idx += kAttnWarps * 32) {
         const int r = idx / (kHD / 4), c4 = (idx % (kHD / 4)) * 4;
+        const int tok = kMulti ? b + r / group : b;
+        const int hq = h * group + (kMulti ? r % group : r);
+        int row_splits = n_splits;
+        if (kMulti) {
+            if (tok >= p.T) continue;
+            const int row_len = p.ctx_len[tok];
+            if (first_tok >= row_len) continue;  // this split holds nothing the row may see
+            row_splits = (row_len + chunk_tokens - 1) / chunk_tokens;
+        }
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, mml[(w * 8 + r) * 2]);
+        for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, mml[(w * kRows + r) * 2]);
         float L = 0.f;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) {
-            float f = exp2f(mml[(w * 8 + r) * 2] - M);
-            L += mml[(w * 8 + r) * 2 + 1] * f;
-            float4 v = *reinterpret_cast<const float4*>(mo + (w * 8 + r) * kHD + c4);
+            const float mw = mml[(w * kRows + r) * 2];
+            const float f = (kMulti && mw == -INFINITY) ? 0.f : exp2f(mw - M);  // a warp whose pages the row cannot see
+            L += mml[(w * kRows + r) * 2 + 1] * f;
+            float4 v = *reinterpret_cast<const float4*>(mo + (w * kRows + r) * kHD + c4);
             acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
         }
-        const int hq = h * group + r;
-        if (n_splits == 1) {
+        if (row_splits == 1) {
             const float inv = 1.f / L;
             uint2 ov = make_uint2(pack_bf16x2(acc.x * inv, acc.y * inv), pack_bf16x2(acc.z * inv, acc.w * inv));
-            *reinterpret_cast<uint2*>(p.out + ((size_t)b * p.Hq + hq) * kHD + c4) = ov;
+            *reinterpret_cast<uint2*>(p.out + ((size_t)tok * p.Hq + hq) * kHD + c4) = ov;
         } else {
-            const size_t pi = ((size_t)b * p.Hq + hq) * p.max_splits + split;
+            const size_t pi = ((size_t)tok * p.Hq + hq) * p.max_splits + split;
             *reinterpret_cast<float4*>(p.part_o + pi * kHD + c4) = acc;
             if (c4 == 0) {
                 p.part_ml[pi * 2] = M;
@@ -384,12 +464,12 @@ int gptrs_cuda_rope_kv_append(const void* d_qkv, const int32_t* d_positions, con
     return launch_kernel(rope_append_kernel, grid, dim3(64), 0, as_stream(stream), 1, p);
 }
 
-int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
-                                      int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
-                                      void* d_out, void* d_scratch, size_t scratch_bytes, int32_t* d_status,
-                                      int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
-                                      int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
-                                      void* stream) {
+static int paged_attention_launch(bool multi, const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                  int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                  void* d_out, void* d_scratch, size_t scratch_bytes, int32_t* d_status,
+                                  int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
+                                  int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
+                                  void* stream) {
     GPTRS_REQUIRE(d_q && d_kv_pool && d_page_table && d_slot && d_ctx_len && d_out && d_status, "null pointer");
     GPTRS_REQUIRE(head_dim == kHD, "paged bf16 attention supports head_dim 128 only");
     GPTRS_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "bad head counts");
@@ -416,13 +496,18 @@ int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, co
     if (depth == 0) {
         const char* e = getenv("GPTRS_ATTN_DEPTH");
         depth = (e && atoi(e) == 3) ? 3 : 2;
-        GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kAttnWarps * 2 * kPageHeadBytes));
-        GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kAttnWarps * 3 * kPageHeadBytes));
+        GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kAttnWarps * 2 * kPageHeadBytes));
     }
-    const size_t smem = (size_t)kAttnWarps * depth * kPageHeadBytes;
-    void (*attn_kernel)(AttnParams) = depth == 3 ? paged_attention_kernel<3> : paged_attention_kernel<2>;
+    const size_t smem = (size_t)kAttnWarps * (multi ? 2 : depth) * kPageHeadBytes;
+    void (*attn_kernel)(AttnParams) = multi ? paged_attention_kernel<2, true>
+                                            : (depth == 3 ? paged_attention_kernel<3, false> : paged_attention_kernel<2, false>);
+    const int group = (int)(n_q_heads / n_kv_heads);
+    const int tq = multi ? 16 / group : 1;  // token rows per CTA
     cudaStream_t st = as_stream(stream);
     // tokens beyond 65535 go through blockIdx.z in slabs
     for (int64_t t0 = 0; t0 < n_tokens; t0 += 65535) {
@@ -436,7 +521,7 @@ int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, co
             q.part_ml = p.part_ml + (size_t)t0 * n_q_heads * splits * 2;
         }
         q.T = (int)nt;
-        int rc = launch_kernel(attn_kernel, dim3((unsigned)splits, (unsigned)n_kv_heads, (unsigned)nt),
+        int rc = launch_kernel(attn_kernel, dim3((unsigned)splits, (unsigned)n_kv_heads, (unsigned)((nt + tq - 1) / tq)),
                                dim3(kAttnWarps * 32), smem, st, 1, q);
         if (rc) return rc;
         if (splits > 1) {
@@ -446,6 +531,34 @@ int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, co
         }
     }
     return GPTRS_OK;
+}
+
+int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                      int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                      void* d_out, void* d_scratch, size_t scratch_bytes, int32_t* d_status,
+                                      int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
+                                      int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
+                                      void* stream) {
+    return paged_attention_launch(false, d_q, d_kv_pool, d_page_table, max_pages, d_slot, d_ctx_len, d_out, d_scratch,
+                                  scratch_bytes, d_status, n_tokens, n_q_heads, n_kv_heads, head_dim, max_ctx_len,
+                                  chunk_pages, stream);
+}
+
+int gptrs_cuda_paged_attention_prefill(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                       int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                       void* d_out, void* d_scratch, size_t scratch_bytes, int32_t* d_status,
+                                       int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
+                                       int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
+                                       void* stream) {
+    GPTRS_REQUIRE(n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "bad head counts");
+    const int64_t group = n_q_heads / n_kv_heads;
+    if (group != 1 && group != 2 && group != 4 && group != 8)
+        return fail(GPTRS_UNIMPLEMENTED, "paged_attention_prefill needs a GQA group of 1, 2, 4 or 8 query heads");
+    // splits of a slab of 65535 CTAs along z would break the grouping of token rows
+    GPTRS_REQUIRE(n_tokens <= 65535, "at most 65535 token rows per call");
+    return paged_attention_launch(true, d_q, d_kv_pool, d_page_table, max_pages, d_slot, d_ctx_len, d_out, d_scratch,
+                                  scratch_bytes, d_status, n_tokens, n_q_heads, n_kv_heads, head_dim, max_ctx_len,
+                                  chunk_pages, stream);
 }
 
 // ---- allocation-free variant ---------------------------------------------------------------------

@@ -151,6 +151,19 @@ int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, co
                                       int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
                                       int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
                                       void* stream);
+/* The same attention for a PREFILL CHUNK: the rows are tokens of which every aligned group of
+ * 16 / (n_q_heads / n_kv_heads) consecutive rows belongs to ONE sequence (same d_slot value; a chunk of
+ * one prompt satisfies this trivially). The K/V pages are then streamed once per group instead of once per
+ * row; results are those of gptrs_cuda_paged_attention_decode. The GQA group must be 1, 2, 4 or 8
+ * (GPTRS_UNIMPLEMENTED otherwise). Replaces functional::attention on the prompt
+ * (crates/gpt-rs/src/ops/functional/attention.rs:337-541) together with gptrs_cuda_rope_kv_append. */
+int gptrs_cuda_paged_attention_prefill(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                       int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                       void* d_out, void* d_scratch, size_t scratch_bytes, int32_t* d_status,
+                                       int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
+                                       int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
+                                       void* stream);
+
 /* Allocation-free variant of gptrs_cuda_paged_attention_decode. It has no counterpart in gpt.rs.
  * It exists for callers that cannot allocate device memory themselves: a plugin inside a serving
  * process whose device memory pool belongs to the host application, or a caller that is in the

@@ -129,6 +129,48 @@ def test_prefill_rows_share_one_page_table_row(cuda):
         assert np.max(np.abs(got[t] - want[0])) <= 2e-2
 
 
+@pytest.mark.parametrize("l,n_q,n_kv,chunk", [(90, 8, 2, None), (131, 32, 8, 4), (70, 4, 4, None), (200, 16, 2, 4), (37, 8, 1, None)])
+def test_prefill_chunk_entry_point(cuda, l, n_q, n_kv, chunk):
+    """gptrs_cuda_paged_attention_prefill streams the pages once per group of 16 / (Hq / Hkv) token rows: same
+    results as the one-row-per-CTA entry point and the oracle, for row counts that are not a multiple of the group,
+    rows whose visible length ends in different splits (chunk of 4 pages = 64 tokens), and a second sequence whose
+    rows start in the middle of the row list at a group boundary."""
+    rng = np.random.default_rng(l * 7 + n_q)
+    l2 = 21
+    table, pool = _setup(rng, [l, l2], n_q, n_kv, cuda)
+    stored, q_rots, table_d = _fill(rng, [l, l2], n_q, n_kv, table, pool, cuda)
+    tq = 16 // (n_q // n_kv)
+    pad = (-l) % tq  # rows of sequence 1 must start a new group: repeat the last row of sequence 0
+    q = torch.cat([q_rots[0], q_rots[0][-1:].repeat(pad, 1, 1), q_rots[1]]).contiguous()
+    slot = torch.tensor([0] * (l + pad) + [1] * l2, dtype=torch.int32, device=cuda)
+    ctx = torch.tensor(list(range(1, l + 1)) + [l] * pad + list(range(1, l2 + 1)), dtype=torch.int32, device=cuda)
+    ref, st0 = ops.paged_attention_decode(q, pool, table_d, slot, ctx, n_q, n_kv, l, chunk_pages=chunk)
+    out, st1 = ops.paged_attention_decode(q, pool, table_d, slot, ctx, n_q, n_kv, l, chunk_pages=chunk, prefill=True)
+    torch.cuda.synchronize()
+    assert int(st0.item()) == 0 and int(st1.item()) == 0
+    got, base = out.float().cpu().numpy(), ref.float().cpu().numpy()
+    assert np.max(np.abs(got - base)) <= 8e-3, np.max(np.abs(got - base))  # both round to bf16 from slightly different sums
+    k_ref, v_ref, _ = stored[0]
+    for t in sorted({0, 1, tq - 1, tq, 15, 16, 63, 64, 65, l - 2, l - 1} & set(range(l))):
+        want = _oracle_decode([(k_ref[:t + 1], v_ref[:t + 1], None)], [t + 1], n_q, n_kv, [q[t].float().cpu().numpy()])
+        assert np.max(np.abs(got[t] - want[0])) <= 2e-2, t
+    k2, v2, _ = stored[1]
+    for t in (0, 5, l2 - 1):
+        want = _oracle_decode([(k2[:t + 1], v2[:t + 1], None)], [t + 1], n_q, n_kv, [q[l + pad + t].float().cpu().numpy()])
+        assert np.max(np.abs(got[l + pad + t] - want[0])) <= 2e-2, t
+
+
+def test_prefill_chunk_rejects_odd_group(cuda):
+    rng = np.random.default_rng(2)
+    table, pool = _setup(rng, [20], 6, 2, cuda)
+    stored, q_rots, table_d = _fill(rng, [20], 6, 2, table, pool, cuda)
+    from gptrs_b200 import BackendError
+    with pytest.raises(BackendError) as e:
+        ops.paged_attention_decode(q_rots[0], pool, table_d, torch.zeros(20, dtype=torch.int32, device=cuda),
+                                   torch.arange(1, 21, dtype=torch.int32, device=cuda), 6, 2, 20, prefill=True)
+    assert e.value.kind == "Unimplemented"
+
+
 def test_attention_rejects_unsupported_geometry(cuda):
     from gptrs_b200 import BackendError
     z = torch.zeros(16, dtype=torch.int32, device=cuda)
