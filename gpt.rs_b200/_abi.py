@@ -31,6 +31,13 @@ class MatmulEpilogue(ctypes.Structure):
         ("d_bias", ctypes.c_void_p),
         ("d_residual", ctypes.c_void_p),
         ("swiglu", ctypes.c_int),
+        ("d_norm_gamma", ctypes.c_void_p),
+        ("d_norm_x", ctypes.c_void_p),
+        ("d_sumsq_out", ctypes.c_void_p),
+        ("d_sumsq_in", ctypes.c_void_p),
+        ("sumsq_tiles", ctypes.c_int),
+        ("norm_dim", ctypes.c_int),
+        ("norm_eps", ctypes.c_float),
     ]
 
 

@@ -85,6 +85,8 @@ struct Model {
     // activations
     DevBuf hidden, xn, qkv, q_rot, attn, mlp_h, mlp_g, mlp_u, logits, xn_rows;
     DevBuf d_tokens, d_slot, d_pos, d_ctx, d_rows, d_sampled, d_status, attn_scratch;
+    DevBuf sumsq;  // [d_model / 128][max_tokens] row sums of squares of the folded RMSNorm
+    bool fold_norm = true;
     DevBuf cos_tab, sin_tab;
     int n_rope_pos = 0;
     // KV
@@ -274,8 +276,19 @@ int build_linear(Model& m, const std::vector<std::string>& names, const std::str
     return GPTRS_OK;
 }
 
+// Residual + RMSNorm folded into the projections around it (gptrs_matmul_epilogue): `produce` on the projection
+// that updates the residual stream, `consume` on the projection that reads the normed activations.
+struct NormFold {
+    const float* gamma = nullptr;  // produce: gain of the next norm
+    void* x_next = nullptr;        // produce: bf16(residual stream * gain)
+    float* sumsq = nullptr;        // [d_model / 128][rows] sums of squares
+    bool produce = false, consume = false;
+    int dim = 0;
+    float eps = 0.f;
+};
+
 int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool out_f32, const float* residual,
-           bool swiglu, bool gelu, cudaStream_t st) {
+           bool swiglu, bool gelu, cudaStream_t st, const NormFold* fold = nullptr) {
     ++m.launches;
     if (m.f32()) {
         return gptrs_cuda_matmul_f32(static_cast<const float*>(x), static_cast<const float*>(w.f32->data),
@@ -287,6 +300,8 @@ int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool
     ep.d_bias = w.bias ? static_cast<const float*>(w.bias->data) : nullptr;
     ep.d_residual = residual;
     ep.swiglu = swiglu ? 1 : 0;
+    if (fold && fold->produce) { ep.d_norm_gamma = fold->gamma; ep.d_norm_x = fold->x_next; ep.d_sumsq_out = fold->sumsq; }
+    if (fold && fold->consume) { ep.d_sumsq_in = fold->sumsq; ep.sumsq_tiles = fold->dim / 128; ep.norm_dim = fold->dim; ep.norm_eps = fold->eps; }
     return m.cfg.weight_mode == kModeW4
                ? gptrs_cuda_quant_matmul_w4a16(x, w.packed->data, y, rows, w.out, w.in, &ep, st)
                : gptrs_cuda_quant_matmul_w8a16(x, w.packed->data, y, rows, w.out, w.in, &ep, st);
@@ -378,9 +393,32 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
     // that is all-reduced over NVLink and then added to the residual stream by the next norm kernel
     // (tensor-parallel steps always run as one lane).
     const float* pending = nullptr;
-    auto row_parallel = [&](const Lane& ln, const Weight& w, const void* x) -> int {
+    // RMSNorm folded into the projections: quantised Ministral, one rank, more than 16 rows (tensor-core matmuls),
+    // d_model a multiple of 128. The sums of squares of a lane live at a row offset of the shared buffer: a lane's
+    // tile t is at sumsq + t * T_lane, so each lane gets a disjoint slab of [tiles][T_lane] floats.
+    const bool fold = m.fold_norm && !gpt && !m.f32() && m.tp == 1 && T > 16 && D % 128 == 0;
+    auto fold_for = [&](const Lane& ln, Tensor* next_gamma, bool produce) {
+        NormFold f;
+        f.sumsq = m.sumsq.as<float>() + (size_t)(D / 128) * ln.r0;
+        f.dim = D;
+        f.eps = c.norm_eps;
+        f.produce = produce;
+        f.consume = !produce;
+        if (produce) {
+            f.gamma = static_cast<const float*>(next_gamma->data);
+            f.x_next = at(m.xn, (size_t)D * act, ln);
+        }
+        return f;
+    };
+    auto row_parallel = [&](const Lane& ln, const Weight& w, const void* x, Tensor* next_gamma = nullptr) -> int {
         float* h = reinterpret_cast<float*>(at(m.hidden, (size_t)D * 4, ln));
-        if (m.tp == 1) return linear(m, w, x, h, ln.T, true, h, false, false, ln.st);
+        if (m.tp == 1) {
+            if (fold && next_gamma && ln.T > 16) {
+                const NormFold f = fold_for(ln, next_gamma, true);
+                return linear(m, w, x, h, ln.T, true, h, false, false, ln.st, &f);
+            }
+            return linear(m, w, x, h, ln.T, true, h, false, false, ln.st);
+        }
         int r = linear(m, w, x, m.partial.p, ln.T, true, nullptr, false, false, ln.st);
         if (r) return r;
         ++m.launches;
@@ -404,9 +442,15 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
     auto pre_attention = [&](const Lane& ln, int l) -> int {
         Layer& L = m.layers[l];
         int r;
-        if ((r = norm(ln, L.ln1_g, L.ln1_b))) return r;
+        const bool folded = fold && ln.T > 16;
         void* qkv = at(m.qkv, (size_t)m.QKV() * act, ln);
-        if ((r = linear(m, L.qkv, at(m.xn, (size_t)D * act, ln), qkv, ln.T, false, nullptr, false, false, ln.st))) return r;
+        if (folded && l > 0) {  // the previous block's last projection left bf16(hidden * gain) and the row sums
+            const NormFold f = fold_for(ln, nullptr, false);
+            if ((r = linear(m, L.qkv, at(m.xn, (size_t)D * act, ln), qkv, ln.T, false, nullptr, false, false, ln.st, &f))) return r;
+        } else {
+            if ((r = norm(ln, L.ln1_g, L.ln1_b))) return r;
+            if ((r = linear(m, L.qkv, at(m.xn, (size_t)D * act, ln), qkv, ln.T, false, nullptr, false, false, ln.st))) return r;
+        }
         if (m.f32()) {
             if (!gpt && c.rotary_dim > 0) {
                 ++m.launches;
@@ -452,8 +496,9 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
     auto post_attention = [&](const Lane& ln, int l) -> int {
         Layer& L = m.layers[l];
         int r;
-        if ((r = row_parallel(ln, L.attn_out, at(m.attn, (size_t)m.QD() * act, ln)))) return r;
-        if ((r = norm(ln, L.ln2_g, L.ln2_b))) return r;
+        const bool folded = fold && ln.T > 16;
+        if ((r = row_parallel(ln, L.attn_out, at(m.attn, (size_t)m.QD() * act, ln), folded ? L.ln2_g : nullptr))) return r;
+        if (!folded && (r = norm(ln, L.ln2_g, L.ln2_b))) return r;
         void* xn = at(m.xn, (size_t)D * act, ln);
         void* mlp_h = at(m.mlp_h, (size_t)c.d_mlp * act, ln);
         if (gpt) {
@@ -466,10 +511,14 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
             ++m.launches;
             if ((r = gptrs_cuda_swiglu(static_cast<float*>(g), static_cast<float*>(u), static_cast<float*>(mlp_h),
                                        (int64_t)ln.T * c.d_mlp, ln.st))) return r;
+        } else if (folded) {
+            const NormFold f = fold_for(ln, nullptr, false);
+            if ((r = linear(m, L.mlp_gate_up, xn, mlp_h, ln.T, false, nullptr, true, false, ln.st, &f))) return r;
         } else {
             if ((r = linear(m, L.mlp_gate_up, xn, mlp_h, ln.T, false, nullptr, true, false, ln.st))) return r;
         }
-        return row_parallel(ln, L.mlp_out, mlp_h);
+        // the last block leaves the final norm to its own kernel (its rows may be gathered first)
+        return row_parallel(ln, L.mlp_out, mlp_h, folded && l + 1 < c.n_layers ? m.layers[l + 1].ln1_g : nullptr);
     };
     const bool two_lanes = rows_identity && m.n_lanes == 2 && !m.f32() && m.tp == 1 && T >= 32;
     if (!two_lanes) {
@@ -619,6 +668,7 @@ int gptrs_cuda_model_create(const gptrs_model_config* cfg, gptrs_model** out) {
         GPTRS_CUDA_OK(cudaEventCreateWithFlags(&m->ev_b[l], cudaEventDisableTiming));
     }
     if (const char* e = getenv("GPTRS_LANES")) m->n_lanes = atoi(e) >= 2 ? 2 : 1;
+    if (const char* e = getenv("GPTRS_FOLD_NORM")) m->fold_norm = atoi(e) != 0;
     if (const char* e = getenv("GPTRS_LANE_ORDER")) m->lane_order = atoi(e) != 0;
     {
         int least = 0, greatest = 0;
@@ -768,6 +818,7 @@ int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
     // activations
     const int T = c.max_tokens;
     const size_t act = m.f32() ? 4 : 2;
+    if (!m.f32() && (rc = m.sumsq.alloc((size_t)((D + 127) / 128) * T * 4, true))) return rc;
     if ((rc = m.hidden.alloc((size_t)T * D * 4)) || (rc = m.xn.alloc((size_t)T * D * act)) || (rc = m.xn_rows.alloc((size_t)T * D * act)) ||
         (rc = m.qkv.alloc((size_t)T * QKV * act)) || (rc = m.attn.alloc((size_t)T * QD * act)) ||
         (rc = m.mlp_h.alloc((size_t)T * MLP * act))) return rc;

@@ -46,6 +46,13 @@ struct MatmulParams {
     int k_intra;         // GEMV kernel: warps of a CTA that split the CTA's K range among themselves (1, 2, 4, 8)
     int out_f32;
     int swiglu;
+    // residual + RMSNorm folded into the matmuls (see gptrs_matmul_epilogue)
+    const float* norm_gamma;      // producer: gain of the NEXT norm
+    __nv_bfloat16* norm_x;        // producer: bf16(y * gain)
+    float* sumsq_out;             // producer: [tile][M] sums of y^2
+    const float* sumsq_in;        // consumer: [sumsq_tiles][M]
+    int sumsq_tiles, norm_dim;
+    float norm_eps;
 };
 
 // ---- split-K reduction across the CTAs of a cluster: push, one barrier, local sum -------------------
@@ -93,7 +100,20 @@ template <int MPAD>
 __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const SplitReduce& sr, const float* slots, int tid,
                                                     int n_threads, int m0, int n_cta0, int tile_cols = kCtaN) {
     const int S = sr.S, rank = sr.rank, rows_max = sr.rows_max;
-    if (S > 1) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+    // consumer of a folded RMSNorm: 1 / rms of every row this CTA owns, from the producer's per-tile sums
+    __shared__ float row_scale[MPAD];
+    if (p.sumsq_in) {
+        const int rows_mine = (MPAD - rank + S - 1) / S;
+        for (int lr = tid; lr < rows_mine; lr += n_threads) {
+            const int m = m0 + rank + S * lr;
+            float ss = 0.f;
+            if (m < p.M)
+                for (int t = 0; t < p.sumsq_tiles; ++t) ss += p.sumsq_in[(size_t)t * p.M + m];
+            row_scale[lr] = rsqrtf(ss / (float)p.norm_dim + p.norm_eps);
+        }
+    }
+    if (S > 1) { cluster_arrive(); cluster_wait(); }
+    __syncthreads();
     auto gather = [&](int local_row, int c) {
         float4 v = *reinterpret_cast<const float4*>(slots + (size_t)local_row * kRedStride + c);
         for (int k = 1; k < S; ++k) {
@@ -109,21 +129,37 @@ __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const
         for (int j = tid; j < rows_own * cols4; j += n_threads) {
             const int lr = j >> sh4, c4 = j & (cols4 - 1);
             const int m = m0 + rank + S * lr, n = n_cta0 + c4 * 4;
-            if (m >= p.M || n >= p.N) continue;
-            float4 v = gather(lr, c4 * 4);
-            if (p.bias) {
+            const bool live = m < p.M && n < p.N;
+            if (!live && !p.sumsq_out) continue;
+            float4 v = live ? gather(lr, c4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.sumsq_in) { const float r = row_scale[lr]; v.x *= r; v.y *= r; v.z *= r; v.w *= r; }
+            if (live && p.bias) {
                 float4 b = *reinterpret_cast<const float4*>(p.bias + n);
                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
             }
-            if (p.residual) {
+            if (live && p.residual) {
                 float4 b = *reinterpret_cast<const float4*>(p.residual + (size_t)m * p.N + n);
                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
             }
-            if (p.out_f32) {
-                *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + (size_t)m * p.N + n) = v;
-            } else {
-                uint2 o = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
-                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)m * p.N + n) = o;
+            if (live) {
+                if (p.out_f32) {
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + (size_t)m * p.N + n) = v;
+                } else {
+                    uint2 o = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+                    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)m * p.N + n) = o;
+                }
+            }
+            if (p.sumsq_out) {
+                // producer of a folded RMSNorm: the 32 lanes of a warp hold one row of the 128-column tile
+                if (live) {
+                    const float4 g4 = *reinterpret_cast<const float4*>(p.norm_gamma + n);
+                    uint2 o = make_uint2(pack_bf16x2(v.x * g4.x, v.y * g4.y), pack_bf16x2(v.z * g4.z, v.w * g4.w));
+                    *reinterpret_cast<uint2*>(p.norm_x + (size_t)m * p.N + n) = o;
+                }
+                float ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+                if ((tid & 31) == 0 && m < p.M) p.sumsq_out[(size_t)(n_cta0 / kCtaN) * p.M + m] = ss;
             }
         }
     } else {
@@ -137,7 +173,12 @@ __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const
             const int m = m0 + rank + S * lr, n_out = (n_cta0 >> 1) + tile * 8 + half * 4;
             if (m >= p.M || n_out >= NO) continue;
             const int cg = tile * 16 + half * 4;
-            const float4 gt = gather(lr, cg), up = gather(lr, cg + 8);
+            float4 gt = gather(lr, cg), up = gather(lr, cg + 8);
+            if (p.sumsq_in) {
+                const float r = row_scale[lr];
+                gt.x *= r; gt.y *= r; gt.z *= r; gt.w *= r;
+                up.x *= r; up.y *= r; up.z *= r; up.w *= r;
+            }
             float4 v;
             v.x = gt.x / (1.f + expf(-gt.x)) * up.x;
             v.y = gt.y / (1.f + expf(-gt.y)) * up.y;

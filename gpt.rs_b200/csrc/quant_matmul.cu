@@ -578,9 +578,24 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
         p.swiglu = ep->swiglu != 0;
         GPTRS_REQUIRE(!(p.swiglu && (p.bias || p.residual)), "swiglu epilogue takes no bias/residual");
         GPTRS_REQUIRE(!p.swiglu || n % 32 == 0, "swiglu needs N % 32 == 0");
+        if (ep->d_sumsq_out || ep->d_norm_x || ep->d_norm_gamma) {
+            GPTRS_REQUIRE(ep->d_sumsq_out && ep->d_norm_x && ep->d_norm_gamma, "folded norm: gamma, x and sumsq_out go together");
+            GPTRS_REQUIRE(m > 16 && n % 128 == 0 && !p.swiglu, "folded norm producer: more than 16 rows, N % 128 == 0, no swiglu");
+            p.norm_gamma = ep->d_norm_gamma;
+            p.norm_x = static_cast<__nv_bfloat16*>(ep->d_norm_x);
+            p.sumsq_out = ep->d_sumsq_out;
+        }
+        if (ep->d_sumsq_in) {
+            GPTRS_REQUIRE(m > 16 && ep->sumsq_tiles > 0 && ep->norm_dim > 0, "folded norm consumer: more than 16 rows, tiles and norm_dim set");
+            p.sumsq_in = ep->d_sumsq_in;
+            p.sumsq_tiles = ep->sumsq_tiles;
+            p.norm_dim = ep->norm_dim;
+            p.norm_eps = ep->norm_eps;
+        }
     }
     cudaStream_t st = as_stream(stream);
     if (m > 16 && umma_enabled()) return BITS == 4 ? umma_w4a16_matmul(p, st) : umma_w8a16_matmul(p, st);
+    GPTRS_REQUIRE(!p.sumsq_in && !p.sumsq_out, "the folded norm needs the tensor-core matmul path");
     const int groups = (int)(k / 128);
     const int n_blocks = ceil_div(n, kCtaN);
     p.n_split = pick_split(n_blocks, groups);

@@ -108,22 +108,28 @@ def _epilogue(out_f32, bias, residual, swiglu):
     return ep
 
 
-def _quant_matmul(fn, x, packed, m, n, k, out, out_f32, bias, residual, swiglu):
+def _quant_matmul(fn, x, packed, m, n, k, out, out_f32, bias, residual, swiglu, norm_out=None, norm_in=None):
+    """norm_out = (gamma f32 [N], x_next bf16 [M][N], sumsq f32 [N/128][M]) makes this call the producer of a folded
+    RMSNorm; norm_in = (sumsq f32 [tiles][M], norm_dim, eps) makes it the consumer (see gptrs_matmul_epilogue)."""
     n_out = n // 2 if swiglu else n
     if out is None:
         out = torch.empty((m, n_out), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
     ep = _epilogue(out_f32, bias, residual, swiglu)
+    if norm_out is not None:
+        ep.d_norm_gamma, ep.d_norm_x, ep.d_sumsq_out = _ptr(norm_out[0]), _ptr(norm_out[1]), _ptr(norm_out[2])
+    if norm_in is not None:
+        ep.d_sumsq_in, ep.sumsq_tiles, ep.norm_dim, ep.norm_eps = _ptr(norm_in[0]), norm_in[0].shape[0], norm_in[1], norm_in[2]
     check(fn(_ptr(x), _ptr(packed), _ptr(out), m, n, k, ctypes.byref(ep), _stream()))
     return out
 
 
-def quant_matmul_w4a16(x, packed, m, n, k, out=None, out_f32=False, bias=None, residual=None, swiglu=False):
+def quant_matmul_w4a16(x, packed, m, n, k, out=None, out_f32=False, bias=None, residual=None, swiglu=False, **norm):
     """y = x . dequant(W4)^T (x bf16 [M][K]); see gptrs_cuda_quant_matmul_w4a16."""
-    return _quant_matmul(lib().gptrs_cuda_quant_matmul_w4a16, x, packed, m, n, k, out, out_f32, bias, residual, swiglu)
+    return _quant_matmul(lib().gptrs_cuda_quant_matmul_w4a16, x, packed, m, n, k, out, out_f32, bias, residual, swiglu, **norm)
 
 
-def quant_matmul_w8a16(x, packed, m, n, k, out=None, out_f32=False, bias=None, residual=None, swiglu=False):
-    return _quant_matmul(lib().gptrs_cuda_quant_matmul_w8a16, x, packed, m, n, k, out, out_f32, bias, residual, swiglu)
+def quant_matmul_w8a16(x, packed, m, n, k, out=None, out_f32=False, bias=None, residual=None, swiglu=False, **norm):
+    return _quant_matmul(lib().gptrs_cuda_quant_matmul_w8a16, x, packed, m, n, k, out, out_f32, bias, residual, swiglu, **norm)
 
 
 def matmul_status() -> int:

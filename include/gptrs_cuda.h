@@ -100,6 +100,21 @@ typedef struct {
     const float* d_residual;  /* optional [M][N] f32 added to the result (residual add) */
     int swiglu;               /* weight was repacked with interleave_gate_up: output is
                                  silu(gate)*up with N/2 columns (activation.rs:153-160) */
+    /* Residual + RMSNorm folded into two matmuls (functional::rms_norm, normalization.rs; all optional,
+     * zero = off; rows > 16 only, N a multiple of 128):
+     *   producer (the projection that updates the residual stream, out f32 + d_residual): also writes
+     *     d_norm_x[M][N] = bf16(y * d_norm_gamma[n]) and, per 128-column tile t, d_sumsq_out[t][M] = sum of y^2;
+     *   consumer (the next projection, fed with d_norm_x): scales every output row by
+     *     rsqrt(sum_t d_sumsq_in[t][m] / norm_dim + norm_eps) before bias / SwiGLU.
+     * Together: consumer(x) = W . (gamma * y / rms(y)), with bf16 rounding of gamma * y instead of
+     * gamma * y / rms(y). */
+    const float* d_norm_gamma;
+    void* d_norm_x;
+    float* d_sumsq_out;
+    const float* d_sumsq_in;
+    int sumsq_tiles;          /* tiles summed by the consumer (= norm_dim / 128) */
+    int norm_dim;
+    float norm_eps;
 } gptrs_matmul_epilogue;
 
 /* y[M][N] = x[M][K] (bf16) . dequant(W)^T, f32 accumulate. Up to 16 rows the group scale is

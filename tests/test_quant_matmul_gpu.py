@@ -144,6 +144,43 @@ def test_w4a16_epilogues(cuda):
     assert np.allclose(y8.cpu().numpy(), want8, rtol=1e-3, atol=1e-3 * max(1.0, np.abs(want8).max()))
 
 
+@pytest.mark.parametrize("m,swiglu", [(40, False), (64, True), (130, False)])
+def test_folded_residual_rmsnorm(cuda, m, swiglu):
+    """The projection that updates the residual stream also emits bf16(y * gamma) and per-tile sums of y^2; the next
+    projection scales its rows by 1 / rms(y). Together they equal matmul -> add -> rms_norm -> matmul."""
+    rng = np.random.default_rng(m)
+    d, k1, n2, eps = 384, 256, 512, 1e-5
+    p1, s1 = _w4_case(rng, d, k1)
+    p2, s2 = _w4_case(rng, n2, d)
+    x1 = qr.to_bf16(rng.normal(0, 1, size=(m, k1)).astype(np.float32))
+    hidden = rng.normal(0, 1, size=(m, d)).astype(np.float32)
+    gamma = (1 + 0.1 * rng.normal(size=d)).astype(np.float32)
+    w1 = ops.w4a16_repack(_dev(p1, cuda), _dev(s1, cuda), d, k1)
+    w2 = ops.w4a16_repack(_dev(p2, cuda), _dev(s2, cuda), n2, d, swiglu)
+    hid_d = _dev(hidden, cuda)
+    x_next = torch.empty((m, d), dtype=torch.bfloat16, device=cuda)
+    sumsq = torch.zeros((d // 128, m), dtype=torch.float32, device=cuda)
+    ops.quant_matmul_w4a16(_dev(x1, cuda).to(torch.bfloat16), w1, m, d, k1, out=hid_d, out_f32=True, residual=hid_d,
+                           norm_out=(_dev(gamma, cuda), x_next, sumsq))
+    y2 = ops.quant_matmul_w4a16(x_next, w2, m, n2, d, out_f32=True, swiglu=swiglu, norm_in=(sumsq, d, eps))
+    torch.cuda.synchronize()
+    h_gpu = hid_d.cpu().numpy()
+    h_ref = hidden + qr.quant_matmul(x1, qr.dequant_w4(p1, s1))
+    assert np.allclose(h_gpu, h_ref, rtol=0, atol=4e-3 * np.abs(h_ref).max())
+    # by-products are exact functions of the stored residual stream
+    assert np.array_equal(x_next.float().cpu().numpy(), qr.to_bf16(h_gpu * gamma))
+    assert np.allclose(sumsq.cpu().numpy().sum(axis=0), (h_gpu.astype(np.float64) ** 2).sum(axis=1), rtol=1e-5)
+    # the pair against norm-then-matmul on the same residual stream
+    rstd = 1.0 / np.sqrt((h_gpu.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + eps)
+    xn = qr.to_bf16((h_gpu * rstd * gamma).astype(np.float32))
+    want = qr.quant_matmul(xn, qr.dequant_w4(p2, s2))
+    if swiglu:
+        gate, up = want[:, :n2 // 2], want[:, n2 // 2:]
+        want = gate / (1 + np.exp(-gate)) * up
+    got = y2.cpu().numpy()
+    assert np.allclose(got, want, rtol=0, atol=8e-3 * np.abs(want).max()), np.abs(got - want).max() / np.abs(want).max()
+
+
 def test_matmul_rejects_bad_arguments(cuda):
     from gptrs_b200 import BackendError
     x = torch.zeros((1, 100), dtype=torch.bfloat16, device=cuda)
