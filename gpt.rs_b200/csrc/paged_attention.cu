@@ -44,8 +44,19 @@ struct AttnParams {
     float* part_ml;               // [T][Hq][max_splits][2]
     int* status;                  // device error word (0 = ok)
     int T, Hq, Hkv, max_pages, chunk_pages, max_splits;
+    int fixed_chunks;             // splits are chunk_pages long (prefill groups) instead of balanced per sequence
     float scale_log2;
 };
+
+// Split geometry of one sequence. The launch fixes the LARGEST chunk (chunk_pages); a sequence of `len` visible
+// tokens is cut into n = ceil(pages / chunk_pages) splits of equal size ceil(pages / n) pages, so a context just past
+// a multiple of the chunk does not leave a one-page straggler split.
+__device__ __forceinline__ void split_geometry(int len, int chunk_pages, int* n_splits, int* pages_per_split) {
+    const int pages = (len + kPageTokens - 1) / kPageTokens;
+    const int n = (pages + chunk_pages - 1) / chunk_pages;
+    *n_splits = n;
+    *pages_per_split = n > 0 ? (pages + n - 1) / n : chunk_pages;
+}
 
 __device__ __forceinline__ int swz(int tok, int chunk) { return tok * 256 + ((chunk ^ (tok & 7)) << 4); }
 
@@ -74,12 +85,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
     int len = p.ctx_len[b];
     if (kMulti)
         for (int i = 1; i < tq && b + i < p.T; ++i) len = max(len, p.ctx_len[b + i]);
-    const int chunk_tokens = p.chunk_pages * kPageTokens;
+    int n_splits, split_pages;
+    if (kMulti) { split_pages = p.chunk_pages; n_splits = (len + split_pages * kPageTokens - 1) / (split_pages * kPageTokens); }
+    else split_geometry(len, p.chunk_pages, &n_splits, &split_pages);  // rows of a prefill group keep one fixed grid
+    const int chunk_tokens = split_pages * kPageTokens;
     const int first_tok = split * chunk_tokens;
     if (first_tok >= len) return;  // whole CTA leaves together, before any barrier
     const int n_tok = min(chunk_tokens, len - first_tok);
     const int n_pages = (n_tok + kPageTokens - 1) / kPageTokens;
-    const int n_splits = (len + chunk_tokens - 1) / chunk_tokens;
     const int* pt = p.page_table + (size_t)p.slot[b] * p.max_pages + first_tok / kPageTokens;
 
     unsigned char* my_ring = smem + warp * (kDepth * kPageHeadBytes);
@@ -318,8 +331,9 @@ __global__ void __launch_bounds__(128) attention_combine_kernel(const AttnParams
     pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     const int len = p.ctx_len[b];
-    const int chunk_tokens = p.chunk_pages * kPageTokens;
-    const int n_splits = (len + chunk_tokens - 1) / chunk_tokens;
+    int n_splits, split_pages;
+    if (p.fixed_chunks) { split_pages = p.chunk_pages; n_splits = (len + split_pages * kPageTokens - 1) / (split_pages * kPageTokens); }
+    else split_geometry(len, p.chunk_pages, &n_splits, &split_pages);
     if (n_splits <= 1) return;
     const size_t base = ((size_t)b * p.Hq + hq) * p.max_splits;
     float M = -INFINITY;
@@ -508,6 +522,7 @@ static int paged_attention_launch(bool multi, const void* d_q, const void* d_kv_
                                             : (depth == 3 ? paged_attention_kernel<3, false> : paged_attention_kernel<2, false>);
     const int group = (int)(n_q_heads / n_kv_heads);
     const int tq = multi ? 16 / group : 1;  // token rows per CTA
+    p.fixed_chunks = multi ? 1 : 0;
     cudaStream_t st = as_stream(stream);
     // tokens beyond 65535 go through blockIdx.z in slabs
     for (int64_t t0 = 0; t0 < n_tokens; t0 += 65535) {
