@@ -452,6 +452,11 @@ int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
     int split = big_tile ? 1 : ctas / (n_blocks * m_blocks);
     split = split < 1 ? 1 : (split > 8 ? 8 : split);
     if (split > groups) split = groups;
+    // A cluster lives inside one GPC, so clusters of 5 or more CTAs do not pack into all 2 x SMs slots: a grid
+    // that needs more than about 85 % of them runs as two waves (measured: the 48-tile projection with 7-CTA
+    // clusters took twice the time of 5-CTA clusters). Pairs and triples pack well enough to ignore this.
+    if (p.M <= 64)
+        while (split > 3 && n_blocks * m_blocks * split > sm_count() * 2 * 85 / 100) --split;
     p.n_split = split;
     p.groups_per_cta = (groups + split - 1) / split;
     const dim3 grid(n_blocks, split, m_blocks);
