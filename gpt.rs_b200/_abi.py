@@ -38,6 +38,16 @@ class MatmulEpilogue(ctypes.Structure):
         ("sumsq_tiles", ctypes.c_int),
         ("norm_dim", ctypes.c_int),
         ("norm_eps", ctypes.c_float),
+        ("d_rope_positions", ctypes.c_void_p),
+        ("d_rope_slot", ctypes.c_void_p),
+        ("d_rope_page_table", ctypes.c_void_p),
+        ("rope_max_pages", ctypes.c_int64),
+        ("d_rope_cos", ctypes.c_void_p),
+        ("d_rope_sin", ctypes.c_void_p),
+        ("d_rope_q_out", ctypes.c_void_p),
+        ("d_rope_kv_pool", ctypes.c_void_p),
+        ("rope_q_heads", ctypes.c_int),
+        ("rope_kv_heads", ctypes.c_int),
     ]
 
 

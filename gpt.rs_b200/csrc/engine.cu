@@ -86,7 +86,7 @@ struct Model {
     DevBuf hidden, xn, qkv, q_rot, attn, mlp_h, mlp_g, mlp_u, logits, xn_rows;
     DevBuf d_tokens, d_slot, d_pos, d_ctx, d_rows, d_sampled, d_status, attn_scratch;
     DevBuf sumsq;  // [d_model / 128][max_tokens] row sums of squares of the folded RMSNorm
-    bool fold_norm = true;
+    bool fold_norm = true, fold_rope = true;
     DevBuf cos_tab, sin_tab;
     int n_rope_pos = 0;
     // KV
@@ -285,6 +285,11 @@ struct NormFold {
     bool produce = false, consume = false;
     int dim = 0;
     float eps = 0.f;
+    // RoPE + KV append folded into the qkv projection (positions non-null switches it on)
+    const int32_t* rope_positions = nullptr;
+    const int32_t* rope_slot = nullptr;
+    void* rope_q_out = nullptr;
+    void* rope_pool = nullptr;
 };
 
 int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool out_f32, const float* residual,
@@ -302,6 +307,13 @@ int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool
     ep.swiglu = swiglu ? 1 : 0;
     if (fold && fold->produce) { ep.d_norm_gamma = fold->gamma; ep.d_norm_x = fold->x_next; ep.d_sumsq_out = fold->sumsq; }
     if (fold && fold->consume) { ep.d_sumsq_in = fold->sumsq; ep.sumsq_tiles = fold->dim / 128; ep.norm_dim = fold->dim; ep.norm_eps = fold->eps; }
+    if (fold && fold->rope_positions) {
+        ep.d_rope_positions = fold->rope_positions; ep.d_rope_slot = fold->rope_slot;
+        ep.d_rope_page_table = m.d_page_table.as<int32_t>(); ep.rope_max_pages = m.cfg.max_pages_per_seq;
+        ep.d_rope_cos = m.cos_tab.as<float>(); ep.d_rope_sin = m.sin_tab.as<float>();
+        ep.d_rope_q_out = fold->rope_q_out; ep.d_rope_kv_pool = fold->rope_pool;
+        ep.rope_q_heads = m.cfg.n_q_heads; ep.rope_kv_heads = m.cfg.n_kv_heads;
+    }
     return m.cfg.weight_mode == kModeW4
                ? gptrs_cuda_quant_matmul_w4a16(x, w.packed->data, y, rows, w.out, w.in, &ep, st)
                : gptrs_cuda_quant_matmul_w8a16(x, w.packed->data, y, rows, w.out, w.in, &ep, st);
@@ -443,14 +455,20 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         Layer& L = m.layers[l];
         int r;
         const bool folded = fold && ln.T > 16;
+        // RoPE + KV append ride on the qkv projection's epilogue (tensor-core path, full rotary dimension)
+        const bool rope_folded = m.fold_rope && !m.f32() && !gpt && ln.T > 16 && c.rotary_dim == c.head_dim && c.head_dim == 128;
         void* qkv = at(m.qkv, (size_t)m.QKV() * act, ln);
-        if (folded && l > 0) {  // the previous block's last projection left bf16(hidden * gain) and the row sums
-            const NormFold f = fold_for(ln, nullptr, false);
-            if ((r = linear(m, L.qkv, at(m.xn, (size_t)D * act, ln), qkv, ln.T, false, nullptr, false, false, ln.st, &f))) return r;
-        } else {
-            if ((r = norm(ln, L.ln1_g, L.ln1_b))) return r;
-            if ((r = linear(m, L.qkv, at(m.xn, (size_t)D * act, ln), qkv, ln.T, false, nullptr, false, false, ln.st))) return r;
+        NormFold f;
+        if (folded && l > 0) f = fold_for(ln, nullptr, false);  // the previous block's last projection left bf16(hidden * gain) and the row sums
+        else if ((r = norm(ln, L.ln1_g, L.ln1_b))) return r;
+        if (rope_folded) {
+            f.rope_positions = ints(m.d_pos, ln);
+            f.rope_slot = ints(m.d_slot, ln);
+            f.rope_q_out = at(m.q_rot, (size_t)m.QD() * 2, ln);
+            f.rope_pool = m.kv_pool.as<unsigned char>() + (size_t)l * m.pool_layer_bytes;
         }
+        if ((r = linear(m, L.qkv, at(m.xn, (size_t)D * act, ln), qkv, ln.T, false, nullptr, false, false, ln.st, &f))) return r;
+        if (rope_folded) return GPTRS_OK;
         if (m.f32()) {
             if (!gpt && c.rotary_dim > 0) {
                 ++m.launches;
@@ -669,6 +687,7 @@ int gptrs_cuda_model_create(const gptrs_model_config* cfg, gptrs_model** out) {
     }
     if (const char* e = getenv("GPTRS_LANES")) m->n_lanes = atoi(e) >= 2 ? 2 : 1;
     if (const char* e = getenv("GPTRS_FOLD_NORM")) m->fold_norm = atoi(e) != 0;
+    if (const char* e = getenv("GPTRS_FOLD_ROPE")) m->fold_rope = atoi(e) != 0;
     if (const char* e = getenv("GPTRS_LANE_ORDER")) m->lane_order = atoi(e) != 0;
     {
         int least = 0, greatest = 0;

@@ -53,6 +53,15 @@ struct MatmulParams {
     const float* sumsq_in;        // consumer: [sumsq_tiles][M]
     int sumsq_tiles, norm_dim;
     float norm_eps;
+    // RoPE + KV append folded into the qkv projection (see gptrs_matmul_epilogue): a 128-column CTA tile is one head
+    const int* rope_pos;          // [M] positions; non-null switches the epilogue on
+    const int* rope_slot;         // [M] page-table row
+    const int* rope_page_table;   // [slots][rope_max_pages]
+    const float* rope_cos;        // [positions][64]
+    const float* rope_sin;
+    __nv_bfloat16* rope_q_out;    // [M][Hq][128]
+    unsigned char* rope_pool;     // paged KV pool of the layer
+    int rope_max_pages, rope_hq, rope_hkv;
 };
 
 // ---- split-K reduction across the CTAs of a cluster: push, one barrier, local sum -------------------
@@ -123,6 +132,51 @@ __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const
         return v;
     };
     const int rows_own = (MPAD - rank + S - 1) / S;  // rows rank, rank + S, ...
+    if (p.rope_pos) {
+        // The tile is one head of the packed qkv row. Values are rounded to bf16 first (what a separate RoPE kernel
+        // would read), Q and K heads rotate pairs (c, c + 64) in f32, then Q goes to rope_q_out and K / V into the
+        // token's page: pool[page][kv head][K|V][16 tokens][128], 16-byte chunk c of token t stored at c ^ (t & 7).
+        const int head = n_cta0 >> 7;
+        const bool is_q = head < p.rope_hq, is_v = head >= p.rope_hq + p.rope_hkv;
+        for (int j = tid; j < rows_own * 16; j += n_threads) {
+            const int lr = j >> 4, c4 = j & 15;
+            const int m = m0 + rank + S * lr;
+            if (m >= p.M || n_cta0 >= p.N) continue;
+            float4 lo = gather(lr, c4 * 4), hi = gather(lr, c4 * 4 + 64);
+            if (p.sumsq_in) {
+                const float r = row_scale[lr];
+                lo.x *= r; lo.y *= r; lo.z *= r; lo.w *= r;
+                hi.x *= r; hi.y *= r; hi.z *= r; hi.w *= r;
+            }
+            auto rb = [](float v) { return __bfloat162float(__float2bfloat16_rn(v)); };
+            lo = make_float4(rb(lo.x), rb(lo.y), rb(lo.z), rb(lo.w));
+            hi = make_float4(rb(hi.x), rb(hi.y), rb(hi.z), rb(hi.w));
+            const int pos = p.rope_pos[m];
+            if (!is_v) {
+                const float4 cs = *reinterpret_cast<const float4*>(p.rope_cos + (size_t)pos * 64 + c4 * 4);
+                const float4 sn = *reinterpret_cast<const float4*>(p.rope_sin + (size_t)pos * 64 + c4 * 4);
+                const float4 a = lo, b = hi;
+                lo = make_float4(a.x * cs.x - b.x * sn.x, a.y * cs.y - b.y * sn.y, a.z * cs.z - b.z * sn.z, a.w * cs.w - b.w * sn.w);
+                hi = make_float4(b.x * cs.x + a.x * sn.x, b.y * cs.y + a.y * sn.y, b.z * cs.z + a.z * sn.z, b.w * cs.w + a.w * sn.w);
+            }
+            const uint2 olo = make_uint2(pack_bf16x2(lo.x, lo.y), pack_bf16x2(lo.z, lo.w));
+            const uint2 ohi = make_uint2(pack_bf16x2(hi.x, hi.y), pack_bf16x2(hi.z, hi.w));
+            if (is_q) {
+                __nv_bfloat16* dst = p.rope_q_out + ((size_t)m * p.rope_hq + head) * 128 + c4 * 4;
+                *reinterpret_cast<uint2*>(dst) = olo;
+                *reinterpret_cast<uint2*>(dst + 64) = ohi;
+            } else {
+                const int kvh = is_v ? head - p.rope_hq - p.rope_hkv : head - p.rope_hq;
+                const int page = p.rope_page_table[(size_t)p.rope_slot[m] * p.rope_max_pages + (pos >> 4)];
+                const int tok = pos & 15;
+                unsigned char* blk = p.rope_pool + ((size_t)page * p.rope_hkv + kvh) * 8192 + (is_v ? 4096 : 0);
+                const int chunk = c4 >> 1, off = (c4 & 1) * 8;
+                *reinterpret_cast<uint2*>(blk + tok * 256 + ((chunk ^ (tok & 7)) << 4) + off) = olo;
+                *reinterpret_cast<uint2*>(blk + tok * 256 + (((chunk + 8) ^ (tok & 7)) << 4) + off) = ohi;
+            }
+        }
+        return;
+    }
     if (!p.swiglu) {
         const int cols4 = tile_cols >> 2;  // float4 columns of the CTA tile (a power of two)
         const int sh4 = 31 - __clz(cols4);

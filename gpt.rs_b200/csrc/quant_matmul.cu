@@ -585,6 +585,18 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
             p.norm_x = static_cast<__nv_bfloat16*>(ep->d_norm_x);
             p.sumsq_out = ep->d_sumsq_out;
         }
+        if (ep->d_rope_positions) {
+            GPTRS_REQUIRE(ep->d_rope_slot && ep->d_rope_page_table && ep->d_rope_cos && ep->d_rope_sin && ep->d_rope_q_out &&
+                              ep->d_rope_kv_pool, "folded RoPE: null pointer");
+            GPTRS_REQUIRE(m > 16 && !p.swiglu && !p.bias && !p.residual && ep->rope_q_heads > 0 && ep->rope_kv_heads > 0 &&
+                              n == (int64_t)(ep->rope_q_heads + 2 * ep->rope_kv_heads) * 128 && ep->rope_max_pages > 0,
+                          "folded RoPE: more than 16 rows, N = (q heads + 2 kv heads) * 128, no other epilogue");
+            p.rope_pos = ep->d_rope_positions; p.rope_slot = ep->d_rope_slot; p.rope_page_table = ep->d_rope_page_table;
+            p.rope_max_pages = (int)ep->rope_max_pages; p.rope_cos = ep->d_rope_cos; p.rope_sin = ep->d_rope_sin;
+            p.rope_q_out = static_cast<__nv_bfloat16*>(ep->d_rope_q_out);
+            p.rope_pool = static_cast<unsigned char*>(ep->d_rope_kv_pool);
+            p.rope_hq = ep->rope_q_heads; p.rope_hkv = ep->rope_kv_heads;
+        }
         if (ep->d_sumsq_in) {
             GPTRS_REQUIRE(m > 16 && ep->sumsq_tiles > 0 && ep->norm_dim > 0, "folded norm consumer: more than 16 rows, tiles and norm_dim set");
             p.sumsq_in = ep->d_sumsq_in;
@@ -595,7 +607,7 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
     }
     cudaStream_t st = as_stream(stream);
     if (m > 16 && umma_enabled()) return BITS == 4 ? umma_w4a16_matmul(p, st) : umma_w8a16_matmul(p, st);
-    GPTRS_REQUIRE(!p.sumsq_in && !p.sumsq_out, "the folded norm needs the tensor-core matmul path");
+    GPTRS_REQUIRE(!p.sumsq_in && !p.sumsq_out && !p.rope_pos, "the folded norm / RoPE epilogues need the tensor-core matmul path");
     const int groups = (int)(k / 128);
     const int n_blocks = ceil_div(n, kCtaN);
     p.n_split = pick_split(n_blocks, groups);

@@ -108,7 +108,7 @@ def _epilogue(out_f32, bias, residual, swiglu):
     return ep
 
 
-def _quant_matmul(fn, x, packed, m, n, k, out, out_f32, bias, residual, swiglu, norm_out=None, norm_in=None):
+def _quant_matmul(fn, x, packed, m, n, k, out, out_f32, bias, residual, swiglu, norm_out=None, norm_in=None, rope=None):
     """norm_out = (gamma f32 [N], x_next bf16 [M][N], sumsq f32 [N/128][M]) makes this call the producer of a folded
     RMSNorm; norm_in = (sumsq f32 [tiles][M], norm_dim, eps) makes it the consumer (see gptrs_matmul_epilogue)."""
     n_out = n // 2 if swiglu else n
@@ -119,6 +119,11 @@ def _quant_matmul(fn, x, packed, m, n, k, out, out_f32, bias, residual, swiglu, 
         ep.d_norm_gamma, ep.d_norm_x, ep.d_sumsq_out = _ptr(norm_out[0]), _ptr(norm_out[1]), _ptr(norm_out[2])
     if norm_in is not None:
         ep.d_sumsq_in, ep.sumsq_tiles, ep.norm_dim, ep.norm_eps = _ptr(norm_in[0]), norm_in[0].shape[0], norm_in[1], norm_in[2]
+    if rope is not None:  # (positions, slot, page_table, cos, sin, q_out, kv_pool, n_q_heads, n_kv_heads)
+        pos, slot, table, cos, sin, q_out, pool, n_q, n_kv = rope
+        ep.d_rope_positions, ep.d_rope_slot, ep.d_rope_page_table = _ptr(pos), _ptr(slot), _ptr(table)
+        ep.rope_max_pages, ep.d_rope_cos, ep.d_rope_sin = table.shape[1], _ptr(cos), _ptr(sin)
+        ep.d_rope_q_out, ep.d_rope_kv_pool, ep.rope_q_heads, ep.rope_kv_heads = _ptr(q_out), _ptr(pool), n_q, n_kv
     check(fn(_ptr(x), _ptr(packed), _ptr(out), m, n, k, ctypes.byref(ep), _stream()))
     return out
 

@@ -115,6 +115,19 @@ typedef struct {
     int sumsq_tiles;          /* tiles summed by the consumer (= norm_dim / 128) */
     int norm_dim;
     float norm_eps;
+    /* RoPE + KV append folded into the qkv projection (d_rope_positions non-null switches it on; rows > 16,
+     * head_dim 128, rotary_dim 128, N = (rope_q_heads + 2 rope_kv_heads) * 128): instead of storing y the
+     * epilogue does exactly what gptrs_cuda_rope_kv_append does on bf16(y): Q heads rotated to d_rope_q_out,
+     * K (rotated) and V scattered into the token's page of d_rope_kv_pool. d_y is not written. */
+    const int32_t* d_rope_positions;
+    const int32_t* d_rope_slot;
+    const int32_t* d_rope_page_table;
+    int64_t rope_max_pages;
+    const float* d_rope_cos;
+    const float* d_rope_sin;
+    void* d_rope_q_out;
+    void* d_rope_kv_pool;
+    int rope_q_heads, rope_kv_heads;
 } gptrs_matmul_epilogue;
 
 /* y[M][N] = x[M][K] (bf16) . dequant(W)^T, f32 accumulate. Up to 16 rows the group scale is

@@ -181,6 +181,40 @@ def test_folded_residual_rmsnorm(cuda, m, swiglu):
     assert np.allclose(got, want, rtol=0, atol=8e-3 * np.abs(want).max()), np.abs(got - want).max() / np.abs(want).max()
 
 
+def test_folded_rope_kv_append(cuda):
+    """The qkv projection with the RoPE + KV-append epilogue leaves the same rotated Q and the same pool bytes as
+    matmul -> gptrs_cuda_rope_kv_append (to one bf16 ulp: the two kernels may contract a*c - b*s differently)."""
+    from oracle import functional_ref as fr
+    rng = np.random.default_rng(21)
+    m, n_q, n_kv, k = 40, 4, 2, 256
+    n = (n_q + 2 * n_kv) * 128
+    p, s = _w4_case(rng, n, k)
+    w = ops.w4a16_repack(_dev(p, cuda), _dev(s, cuda), n, k)
+    x = _dev(qr.to_bf16(rng.normal(0, 1, size=(m, k)).astype(np.float32)), cuda).to(torch.bfloat16)
+    # two sequences: 25 tokens at positions 3..27 of slot 0 and 15 tokens at positions 0..14 of slot 1
+    pos = torch.tensor(list(range(3, 28)) + list(range(15)), dtype=torch.int32, device=cuda)
+    slot = torch.tensor([0] * 25 + [1] * 15, dtype=torch.int32, device=cuda)
+    table = torch.tensor([[5, 2, 0, 0], [1, 4, 0, 0]], dtype=torch.int32, device=cuda)
+    cos, sin = fr.rotary_cos_sin(0, 64, 128, 1e4)
+    cos_d, sin_d = _dev(cos, cuda), _dev(sin, cuda)
+    pool_a, pool_b = ops.new_kv_pool(6, n_kv, cuda), ops.new_kv_pool(6, n_kv, cuda)
+    qkv = ops.quant_matmul_w4a16(x, w, m, n, k)
+    q_a = ops.rope_kv_append(qkv, pos, slot, table, cos_d, sin_d, 128, pool_a, n_q, n_kv)
+    q_b = torch.zeros((m, n_q, 128), dtype=torch.bfloat16, device=cuda)
+    dummy = torch.empty((m, n), dtype=torch.bfloat16, device=cuda)
+    ops.quant_matmul_w4a16(x, w, m, n, k, out=dummy, rope=(pos, slot, table, cos_d, sin_d, q_b, pool_b, n_q, n_kv))
+    torch.cuda.synchronize()
+
+    def close(a, b):
+        a, b = a.float().cpu().numpy(), b.float().cpu().numpy()
+        assert np.mean(a == b) > 0.995
+        assert np.all(np.abs(a - b) <= 2.0 ** -7 * np.maximum(np.abs(a), 1e-3))
+
+    close(q_a, q_b)
+    close(pool_a.view(torch.bfloat16), pool_b.view(torch.bfloat16))
+    assert float(q_b.float().abs().sum()) > 0
+
+
 def test_matmul_rejects_bad_arguments(cuda):
     from gptrs_b200 import BackendError
     x = torch.zeros((1, 100), dtype=torch.bfloat16, device=cuda)
