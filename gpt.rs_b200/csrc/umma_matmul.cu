@@ -464,8 +464,8 @@ int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
     // per SM, and a single group, measured 15-40 % slower)
     if (p.M <= 32) return launch_umma<4, 32, 2, 3>(p, grid, st);
     if (p.M <= 64) return launch_umma<4, 64, 2, 3>(p, grid, st);
-    if (!big_tile) return launch_umma<4, 128, 2, 4>(p, grid, st);
-    return launch_umma<4, 256, 2, 4>(p, grid, st);
+    if (!big_tile) return launch_umma<4, 128, 4, 4>(p, grid, st);
+    return launch_umma<4, 256, 4, 4>(p, grid, st);
 }
 
 // W8A16 on the same kernel (M > 16).
