@@ -751,6 +751,8 @@ int gptrs_cuda_quantize_w8(const float* d_w, int64_t k, int64_t n, int transpose
     return GPTRS_OK;
 }
 
+size_t gptrs_cuda_matmul_epilogue_size(void) { return sizeof(gptrs_matmul_epilogue); }
+
 int gptrs_cuda_matmul_status(int32_t* h_status) {
     GPTRS_REQUIRE(h_status, "null pointer");
     int v = 0;

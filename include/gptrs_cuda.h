@@ -130,6 +130,10 @@ typedef struct {
     int rope_q_heads, rope_kv_heads;
 } gptrs_matmul_epilogue;
 
+/* sizeof(gptrs_matmul_epilogue) as the library was built: lets a foreign-language binding check its own
+ * declaration of the struct before the first call. */
+size_t gptrs_cuda_matmul_epilogue_size(void);
+
 /* y[M][N] = x[M][K] (bf16) . dequant(W)^T, f32 accumulate. Up to 16 rows the group scale is
  * applied to f32 partial sums (exact dequantisation); above 16 rows W4 weights run on the
  * tcgen05 tensor cores with weights dequantised to bf16 (one bf16 rounding per weight). */

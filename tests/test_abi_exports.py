@@ -28,3 +28,8 @@ def test_packed_sizes_and_argument_errors_without_gpu():
     st = lib.gptrs_cuda_quant_matmul_w4a16(1, 1, 1, 1, 3072, 100, None, None)
     assert st == 1
     assert b"multiple of 128" in lib.gptrs_cuda_last_error()
+
+
+def test_python_struct_mirrors_match_the_library():
+    lib = gptrs_b200.lib()
+    assert lib.gptrs_cuda_matmul_epilogue_size() == ctypes.sizeof(_abi.MatmulEpilogue)
