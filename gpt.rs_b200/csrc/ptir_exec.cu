@@ -353,12 +353,125 @@ void sweep_dead(Plan& pl) {
     }
 }
 
+// ---- decode attention over a dense cache (functional::attention_decode_cache, attention.rs:657-779) -------------
+// The captured graph is
+//   scores = DotGeneral(q[Hq,1,hd], KG[Hq,cap,hd])   KG = Reshape(BroadcastTo(Reshape(Slice?(k_cache[Hkv,cap,hd]))))
+//   z      = scores * (1/sqrt(hd)) + mask             mask = bcast(Select(bcast(DynamicSlice(iota, query_start)) >= iota, 0, -1e9))
+//   ctx    = DotGeneral(Softmax(z), VG[Hq,cap,hd])    VG built like KG from v_cache
+// It materialises two [Hq, cap, hd] copies of the caches and a [Hq, cap] score row per step. The helpers below
+// recognise it so that one kernel can read k_cache / v_cache in place.
+
+const TSpec* spec_of(const Plan& pl, const Operand& o) {
+    if (o.is_literal) return nullptr;
+    auto it = pl.def.find(o.id);
+    if (it != pl.def.end()) return &pl.fn.body[it->second].out;
+    for (size_t i = 0; i < pl.fn.param_ids.size(); ++i)
+        if (pl.fn.param_ids[i] == o.id) return &pl.fn.params[i];
+    return nullptr;
+}
+
+// KG / VG -> the [Hkv, cap, hd] cache it repeats per query-head group.
+const Operand* grouped_cache_source(const Plan& pl, const Operand& o, int64_t hq, int64_t cap, int64_t hd, int64_t* hkv) {
+    const Inst* r2 = def_of(pl, o);
+    if (!r2 || r2->dead || r2->op != Op::Reshape || r2->out.dims != std::vector<int64_t>{hq, cap, hd}) return nullptr;
+    const Inst* bc = def_of(pl, r2->operands[0]);
+    if (!bc || bc->dead || bc->op != Op::BroadcastTo || bc->out.dims.size() != 4) return nullptr;
+    const int64_t kv = bc->out.dims[0], grp = bc->out.dims[1];
+    if (kv * grp != hq || bc->out.dims[2] != cap || bc->out.dims[3] != hd) return nullptr;
+    const Inst* r1 = def_of(pl, bc->operands[0]);
+    if (!r1 || r1->dead || r1->op != Op::Reshape || r1->out.dims != std::vector<int64_t>{kv, 1, cap, hd}) return nullptr;
+    const Operand* src = &r1->operands[0];
+    const Inst* sl = def_of(pl, *src);
+    if (sl && !sl->dead && sl->op == Op::Slice) {  // a slice of the whole tensor
+        const TSpec* in_spec = spec_of(pl, sl->operands[0]);
+        if (!in_spec || in_spec->dims != sl->out.dims) return nullptr;
+        for (int64_t st : sl->a) if (st != 0) return nullptr;
+        src = &sl->operands[0];
+    }
+    const TSpec* cs = spec_of(pl, *src);
+    if (!cs || cs->dtype != GPTRS_F32 || cs->dims != std::vector<int64_t>{kv, cap, hd}) return nullptr;
+    *hkv = kv;
+    return src;
+}
+
+// The causal mask of one query row; returns the operand holding the query position (si32 [1]).
+const Operand* causal_mask_start(const Plan& pl, const Operand& o, int64_t cap) {
+    const Operand* cur = &o;
+    const Inst* sel = nullptr;
+    for (int depth = 0; depth < 4; ++depth) {
+        const Inst* d = def_of(pl, *cur);
+        if (!d || d->dead) return nullptr;
+        if (d->op == Op::BroadcastTo) { cur = &d->operands[0]; continue; }
+        if (d->op == Op::Select) sel = d;
+        break;
+    }
+    if (!sel || sel->operands.size() != 3 || sel->out.dims != std::vector<int64_t>{cap}) return nullptr;
+    float keep, drop;
+    if (!scalar_literal(pl, sel->operands[1], &keep) || !scalar_literal(pl, sel->operands[2], &drop)) return nullptr;
+    if (keep != 0.f || drop > -1e8f) return nullptr;
+    const Inst* cmp = def_of(pl, sel->operands[0]);
+    if (!cmp || cmp->dead || cmp->op != Op::Compare || cmp->sub != "GreaterEqual") return nullptr;
+    const Inst* keys = def_of(pl, cmp->operands[1]);
+    if (!keys || keys->dead || keys->op != Op::Iota || keys->out.dims != std::vector<int64_t>{cap}) return nullptr;
+    const Inst* qb = def_of(pl, cmp->operands[0]);
+    if (!qb || qb->dead || qb->op != Op::BroadcastTo) return nullptr;
+    const Inst* ds = def_of(pl, qb->operands[0]);
+    if (!ds || ds->dead || ds->op != Op::DynamicSlice || ds->operands.size() != 2 || ds->out.dims != std::vector<int64_t>{1}) return nullptr;
+    const Inst* src = def_of(pl, ds->operands[0]);
+    if (!src || src->dead || src->op != Op::Iota || src->out.dims != std::vector<int64_t>{cap}) return nullptr;
+    const TSpec* st = spec_of(pl, ds->operands[1]);
+    if (!st || st->dtype != GPTRS_SI32 || st->numel() != 1) return nullptr;
+    return &ds->operands[1];
+}
+
+bool is_batched_dot(const Inst* d, int64_t contract_rhs) {
+    return d && !d->dead && d->op == Op::DotGeneral && d->a == std::vector<int64_t>{0} && d->b == std::vector<int64_t>{0} &&
+           d->c == std::vector<int64_t>{2} && d->d == std::vector<int64_t>{contract_rhs};
+}
+
+// Anchor: ctx = DotGeneral(p, VG). On success `in` becomes FusedAttentionDecode(q, k_cache, v_cache, query_start).
+bool rewrite_attention_decode(Plan& pl, Inst& in) {
+    if (!is_batched_dot(&in, 1) || in.out.dims.size() != 3 || in.out.dims[1] != 1) return false;
+    const int64_t hq = in.out.dims[0], hd = in.out.dims[2];
+    const Inst* sm = def_of(pl, in.operands[0]);
+    if (!sm || sm->dead || sm->op != Op::FusedSoftmax || sm->out.dims.size() != 3 || sm->out.dims[0] != hq || sm->out.dims[1] != 1) return false;
+    const int64_t cap = sm->out.dims[2];
+    int64_t hkv_v = 0, hkv_k = 0;
+    const Operand* v_cache = grouped_cache_source(pl, in.operands[1], hq, cap, hd, &hkv_v);
+    const Inst* z = def_of(pl, sm->operands[0]);
+    if (!v_cache || !is_bin(z, "Add")) return false;
+    for (int sw = 0; sw < 2; ++sw) {
+        const Operand* start = causal_mask_start(pl, z->operands[1 - sw], cap);
+        const Inst* scaled = def_of(pl, z->operands[sw]);
+        if (!start || !is_bin(scaled, "Mul")) continue;
+        for (int sw2 = 0; sw2 < 2; ++sw2) {
+            float scale;
+            const Inst* scores = def_of(pl, scaled->operands[sw2]);
+            if (!scalar_literal(pl, scaled->operands[1 - sw2], &scale) || !is_batched_dot(scores, 2)) continue;
+            if (fabsf(scale * sqrtf((float)hd) - 1.f) > 1e-5f) continue;
+            const Operand& q = scores->operands[0];
+            const TSpec* qs = spec_of(pl, q);
+            const Operand* k_cache = grouped_cache_source(pl, scores->operands[1], hq, cap, hd, &hkv_k);
+            if (!qs || qs->dtype != GPTRS_F32 || qs->dims != std::vector<int64_t>{hq, 1, hd} || !k_cache || hkv_k != hkv_v) continue;
+            Inst f = in;
+            f.op = Op::FusedAttentionDecode;
+            f.operands = {q, *k_cache, *v_cache, *start};
+            f.a = {hq, hkv_k, hd, cap};
+            in = f;
+            ++pl.fused;
+            return true;
+        }
+    }
+    return false;
+}
+
 // Pattern rewrites. Each replaces the anchor instruction by a fused operation; the interior
 // instructions die in sweep_dead() when nothing else uses them (so values that escape stay).
 void rewrite_pass(Plan& pl, bool rms_pass) {
     count_uses(pl);
     for (auto& in : pl.fn.body) {
         if (in.dead || in.out.dtype != GPTRS_F32 || in.out.dims.empty()) continue;
+        if (!rms_pass && in.op == Op::DotGeneral && rewrite_attention_decode(pl, in)) continue;  // its softmax precedes it
         const int64_t d = in.out.dims.back();
         // ---- rms_norm: Mul(Mul(x, bcast(inv)), bcast(gamma)) ------------------------------------
         if (rms_pass && is_bin(&in, "Mul")) {
@@ -750,6 +863,21 @@ int exec_inst(Exec& ex, const Inst& in, std::vector<Tensor*>& ops, Tensor** resu
             ++ex.launches;
             rc = gptrs_cuda_matmul_f32(static_cast<const float*>(ops[0]->data), static_cast<const float*>(ops[1]->data), static_cast<float*>(out->data),
                                        ops[0]->dims[0], ops[1]->dims[1], ops[0]->dims[1], static_cast<const float*>(ops[2]->data), nullptr, 0, ex.st);
+            break;
+        }
+        case Op::FusedAttentionDecode: {
+            if ((rc = alloc_out())) return rc;
+            static int* zero_slot = nullptr;  // the cache operands hold ONE sequence: row 0
+            if (!zero_slot) {
+                if (cudaMalloc(&zero_slot, sizeof(int)) != cudaSuccess) { tensor_release(out); return fail(GPTRS_EXECUTION, "cudaMalloc failed"); }
+                cudaMemset(zero_slot, 0, sizeof(int));
+            }
+            ++ex.launches;
+            // q [Hq,1,hd] is read as the Q part of one packed row; the position is clamped on the device like the
+            // DynamicSlice it replaces
+            rc = gptrs_cuda_attention_decode_f32(static_cast<const float*>(ops[0]->data), static_cast<const float*>(ops[1]->data),
+                                                 static_cast<const float*>(ops[2]->data), static_cast<const int32_t*>(ops[3]->data), zero_slot,
+                                                 static_cast<float*>(out->data), 1, in.a[0], in.a[1], in.a[2], in.a[3], ex.st);
             break;
         }
         case Op::CustomCall:

@@ -34,7 +34,7 @@ enum class Op {
     Constant, Unary, Binary, DotGeneral, Reduce, Compare, Select, Cast, StopGradient, Reshape, Transpose, BroadcastTo,
     Slice, Concat, Iota, Take, Gather, DynamicSlice, DynamicUpdateSlice, CustomCall,
     // produced by the fusion rewrites of this backend
-    FusedLayerNorm, FusedRmsNorm, FusedSoftmax, FusedMatmulBias, Unsupported
+    FusedLayerNorm, FusedRmsNorm, FusedSoftmax, FusedMatmulBias, FusedAttentionDecode, Unsupported
 };
 
 struct TSpec {
