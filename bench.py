@@ -89,10 +89,11 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def build_model(gm, torch, dev, steps_total: int, use_pdl: int, prefill_chunk: int, tp_size: int = 1, tp_rank: int = 0, nccl_id=None):
+def build_model(gm, torch, dev, steps_total: int, use_pdl: int, prefill_chunk: int, tp_size: int = 1, tp_rank: int = 0, nccl_id=None,
+                weight_mode=None):
     ctx = ((PROMPT_LEN + steps_total + 64 + 15) // 16) * 16
     pages_per_seq = ctx // 16
-    cfg = gm.ModelConfig.ministral_3b(context_length=ctx, weight_mode=gm.MODE_W4A16, max_seqs=BATCH,
+    cfg = gm.ModelConfig.ministral_3b(context_length=ctx, weight_mode=weight_mode or gm.MODE_W4A16, max_seqs=BATCH,
                                       max_tokens=prefill_chunk, max_logit_rows=BATCH,
                                       kv_pages=BATCH * pages_per_seq + 8, max_pages_per_seq=pages_per_seq, use_pdl=use_pdl,
                                       tp_size=tp_size, tp_rank=tp_rank)
@@ -355,6 +356,8 @@ def _main(out):
     ap.add_argument("--ctx", type=int, default=PROMPT_LEN + 20, help="context length for --microbench attention")
     ap.add_argument("--workload", default="ministral3b-w4", choices=["ministral3b-w4", "gpt2-fp32"],
                     help="gpt2-fp32 = the reference's CPU-runnable case (one sequence, 32-token prompt, 64 greedy tokens)")
+    ap.add_argument("--weights", default="w4a16", choices=["w4a16", "w8a16"],
+                    help="w8a16 = the same workload with per-channel int8 weights (not the default line)")
     ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
                     help="dp: every rank decodes its own 64 requests (default); tp: all ranks share ONE batch of 64 "
                          "(tensor parallel, NCCL all-reduce after the row-parallel projections)")
@@ -434,7 +437,9 @@ def _main(out):
         box = [gm.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         nccl_id = box[0]
-    model, cfg = build_model(gm, torch, dev, steps_total, args.pdl, args.prefill_chunk, world if tp else 1, rank if tp else 0, nccl_id)
+    w8 = args.weights == "w8a16"
+    model, cfg = build_model(gm, torch, dev, steps_total, args.pdl, args.prefill_chunk, world if tp else 1, rank if tp else 0, nccl_id,
+                             gm.MODE_W8A16 if w8 else gm.MODE_W4A16)
     t_weights = time.perf_counter() - t_setup
 
     rng = np.random.default_rng(1000 + (0 if tp else rank))  # a tensor-parallel group shares ONE batch
@@ -495,12 +500,12 @@ def _main(out):
     line = {
         "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak",
-        "vs_baseline": None, "dtype": "bf16 activations x int4 weights, f32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "parallelism": (f"tp{world} (one batch of 64; NCCL all-reduce of [64,3072] f32 after o_proj and down_proj)" if tp
+        "vs_baseline": None, "dtype": f"bf16 activations x {'int8' if w8 else 'int4'} weights, f32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD.replace("W4A16-g128", "W8A16 per-channel") if w8 else WORKLOAD, "parallelism": (f"tp{world} (one batch of 64; NCCL all-reduce of [64,3072] f32 after o_proj and down_proj)" if tp
                                    else f"dp{world} (request-partitioned, no collective)"),
                    "context_tokens_during_timing": [PROMPT_LEN + args.warmup, PROMPT_LEN + args.warmup + args.steps],
                    "l2": "inputs larger than L2 (1.8 GB weights + >14 GB KV streamed per step)",
-                   "cuda_graph": True, "pdl": bool(args.pdl), "lm_head": "W4A16", "kv_cache": "paged bf16, 16-token pages",
+                   "cuda_graph": True, "pdl": bool(args.pdl), "lm_head": "W8A16" if w8 else "W4A16", "kv_cache": "paged bf16, 16-token pages",
                    "prefill_seconds": round(t_prefill, 2), "weight_setup_seconds": round(t_weights, 2)},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": BATCH * 4, "d2h_bytes_per_step": BATCH * 4,
                 "ms_per_step": e2e_ms / args.steps},
@@ -511,7 +516,7 @@ def _main(out):
     if rank == 0:
         peak, peak_kind = _peaks()
         # whole-step roofline: weight + KV bytes per step
-        w_bytes = model_weight_bytes(cfg)
+        w_bytes = model_weight_bytes(cfg, w8)
         kv_bytes = cfg.n_layers * BATCH * ctx_mid * 4096
         step_bytes = (w_bytes + kv_bytes) // (world if tp else 1)  # per GPU
         line["step_roofline"] = {"bytes_per_step_per_gpu": step_bytes, "achieved_gbs": step_bytes / (ms / args.steps * 1e-3) / 1e9,
@@ -563,10 +568,12 @@ def lib_stream(model):
     return lib().gptrs_cuda_model_stream(model._h)
 
 
-def model_weight_bytes(cfg) -> int:
+def model_weight_bytes(cfg, w8: bool = False) -> int:
     d, qkv, qd, mlp = cfg.d_model, (cfg.n_q_heads + 2 * cfg.n_kv_heads) * cfg.head_dim, cfg.n_q_heads * cfg.head_dim, cfg.d_mlp
     per_layer = d * qkv + qd * d + 2 * d * mlp + mlp * d
     elems = cfg.n_layers * per_layer + d * cfg.vocab
+    if w8:  # int8 + one fp16 scale per output channel
+        return elems + 2 * (cfg.n_layers * (qkv + d + 2 * mlp + d) + cfg.vocab)
     return elems // 2 + elems // 128 * 2
 
 

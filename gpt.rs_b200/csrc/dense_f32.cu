@@ -28,6 +28,11 @@ struct SgemmParams {
     int M, N, K;
     int k_per_cta, n_split;
     int act;  // 0 none, 1 gelu (erf)
+    // optional normalisation of the x rows while they are staged (functional::layer_norm / rms_norm over K)
+    int norm_kind;            // 0 none, 1 LayerNorm, 2 RMSNorm
+    const float* norm_gamma;  // [K]
+    const float* norm_beta;   // [K] (LayerNorm)
+    float norm_eps;
 };
 
 template <int MT>
@@ -43,9 +48,56 @@ __global__ void __launch_bounds__(kSgWarps * 32) sgemm_smallm_kernel(const Sgemm
 
     pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
-    for (int i = tid; i < MT * kn; i += kSgWarps * 32) {
-        int m = i / kn, k = i % kn;
-        xs[m * p.k_per_cta + k] = (m0 + m < p.M) ? p.x[(size_t)(m0 + m) * p.K + kb + k] : 0.f;
+    if (p.norm_kind == 0) {
+        for (int i = tid; i < MT * kn; i += kSgWarps * 32) {
+            int m = i / kn, k = i % kn;
+            xs[m * p.k_per_cta + k] = (m0 + m < p.M) ? p.x[(size_t)(m0 + m) * p.K + kb + k] : 0.f;
+        }
+    } else {
+        // Row statistics over the FULL K of every row of this CTA (a few KB per row, L2 resident), two passes as
+        // the row kernel does (mean, then centred variance), then the CTA's K slice is staged normalised.
+        __shared__ float stat[kSgWarps][MT];
+        __shared__ float mean_s[MT], inv_s[MT];
+        float part[MT];
+        for (int pass = 0; pass < 2; ++pass) {
+            if (pass == 0 && p.norm_kind == 2) {  // RMSNorm has no mean
+                if (tid < MT) mean_s[tid] = 0.f;
+                __syncthreads();
+                continue;
+            }
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                part[m] = 0.f;
+                if (m0 + m < p.M) {
+                    const float* row = p.x + (size_t)(m0 + m) * p.K;
+                    const float mu = pass ? mean_s[m] : 0.f;
+                    for (int k = tid; k < p.K; k += kSgWarps * 32) {
+                        const float v = row[k] - mu;
+                        part[m] += pass ? v * v : v;
+                    }
+                }
+                part[m] = warp_sum(part[m]);
+                if (lane == 0) stat[warp][m] = part[m];
+            }
+            __syncthreads();
+            if (tid < MT) {
+                float t = 0.f;
+#pragma unroll
+                for (int w = 0; w < kSgWarps; ++w) t += stat[w][tid];
+                t /= (float)p.K;
+                if (pass == 0) mean_s[tid] = t; else inv_s[tid] = 1.f / sqrtf(t + p.norm_eps);
+            }
+            __syncthreads();
+        }
+        for (int i = tid; i < MT * kn; i += kSgWarps * 32) {
+            int m = i / kn, k = i % kn;
+            float v = 0.f;
+            if (m0 + m < p.M) {
+                v = (p.x[(size_t)(m0 + m) * p.K + kb + k] - mean_s[m]) * inv_s[m] * p.norm_gamma[kb + k];
+                if (p.norm_beta) v += p.norm_beta[kb + k];
+            }
+            xs[m * p.k_per_cta + k] = v;
+        }
     }
     __syncthreads();
 
@@ -167,6 +219,8 @@ struct AttnF32Params {
     float* out;  // [T][Hq * hd]
     int T, Hq, Hkv, hd, capacity;
     float scale;
+    float* append_k;  // non-null: the CTA first stores the token's K / V row of its kv head at `pos` (decode steps of
+    float* append_v;  // distinct sequences only: no other token of the launch may read that row)
 };
 
 // One CTA (128 threads) per (query head, token); scores live in dynamic shared memory.
@@ -183,6 +237,15 @@ __global__ void __launch_bounds__(128) attention_f32_kernel(const AttnF32Params 
     const int group = p.Hq / p.Hkv, hk = hq / group;
     const int width = (p.Hq + 2 * p.Hkv) * p.hd;
     for (int i = tid; i < p.hd; i += 128) qs[i] = p.qkv[(size_t)b * width + hq * p.hd + i];
+    if (p.append_k) {
+        // the query heads of one group all store the same two rows: harmless
+        const size_t row = (((size_t)p.slot[b] * p.Hkv + hk) * p.capacity + pos) * p.hd;
+        const float* kv = p.qkv + (size_t)b * width + (size_t)(p.Hq + hk) * p.hd;
+        for (int i = tid; i < p.hd; i += 128) {
+            p.append_k[row + i] = kv[i];
+            p.append_v[row + i] = kv[(size_t)p.Hkv * p.hd + i];
+        }
+    }
     __syncthreads();
     const float* kc = p.k_cache + ((size_t)p.slot[b] * p.Hkv + hk) * p.capacity * p.hd;
     const float* vc = p.v_cache + ((size_t)p.slot[b] * p.Hkv + hk) * p.capacity * p.hd;
@@ -265,12 +328,21 @@ extern "C" {
 
 int gptrs_cuda_matmul_f32(const float* d_x, const float* d_w, float* d_y, int64_t m, int64_t n, int64_t k,
                           const float* d_bias, const float* d_residual, int gelu, void* stream) {
+    return gptrs_cuda_norm_matmul_f32(d_x, 0, nullptr, nullptr, 0.f, d_w, d_y, m, n, k, d_bias, d_residual, gelu, stream);
+}
+
+int gptrs_cuda_norm_matmul_f32(const float* d_x, int norm_kind, const float* d_gamma, const float* d_beta, float eps,
+                               const float* d_w, float* d_y, int64_t m, int64_t n, int64_t k, const float* d_bias,
+                               const float* d_residual, int gelu, void* stream) {
     GPTRS_REQUIRE(d_x && d_w && d_y, "null pointer");
     GPTRS_REQUIRE(m >= 0 && n > 0 && k > 0 && n < (1ll << 31) && k < (1ll << 31) && m < (1ll << 31), "bad shape");
+    GPTRS_REQUIRE(norm_kind >= 0 && norm_kind <= 2 && (norm_kind == 0 || d_gamma), "norm_kind 0 (none), 1 (layer norm) or 2 (rms norm) with a gain");
+    GPTRS_REQUIRE(!(norm_kind != 0 && d_residual == d_x), "a normalised input cannot also be the in-place residual target");
     if (m == 0) return GPTRS_OK;
     SgemmParams p = {};
     p.x = d_x; p.w = d_w; p.bias = d_bias; p.residual = d_residual; p.y = d_y;
     p.M = (int)m; p.N = (int)n; p.K = (int)k; p.act = gelu ? 1 : 0;
+    p.norm_kind = norm_kind; p.norm_gamma = d_gamma; p.norm_beta = norm_kind == 1 ? d_beta : nullptr; p.norm_eps = eps;
     cudaStream_t st = as_stream(stream);
     if (m == 1) return launch_sgemm<1>(p, st);
     if (m == 2) return launch_sgemm<2>(p, st);
@@ -300,7 +372,25 @@ int gptrs_cuda_attention_decode_f32(const float* d_qkv, const float* d_k_cache, 
     GPTRS_REQUIRE(capacity > 0 && capacity <= 32768, "capacity out of range");
     if (n_tokens == 0) return GPTRS_OK;
     AttnF32Params p = {d_qkv, d_k_cache, d_v_cache, d_positions, d_slot, d_out, (int)n_tokens, (int)n_q_heads,
-                       (int)n_kv_heads, (int)head_dim, (int)capacity, 1.0f / sqrtf((float)head_dim)};
+                       (int)n_kv_heads, (int)head_dim, (int)capacity, 1.0f / sqrtf((float)head_dim), nullptr, nullptr};
+    size_t smem = ((size_t)head_dim + (size_t)(capacity > 128 ? capacity : 128)) * sizeof(float);
+    GPTRS_CUDA_OK(cudaFuncSetAttribute(attention_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    return launch_kernel(attention_f32_kernel, dim3((unsigned)n_q_heads, (unsigned)n_tokens), dim3(128), smem,
+                         as_stream(stream), 1, p);
+}
+
+int gptrs_cuda_kv_append_attention_decode_f32(const float* d_qkv, float* d_k_cache, float* d_v_cache,
+                                              const int32_t* d_positions, const int32_t* d_slot, float* d_out,
+                                              int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
+                                              int64_t capacity, void* stream) {
+    GPTRS_REQUIRE(d_qkv && d_k_cache && d_v_cache && d_positions && d_slot && d_out, "null pointer");
+    GPTRS_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "bad head counts");
+    GPTRS_REQUIRE(head_dim > 0 && head_dim <= 128 && head_dim % 4 == 0 && 128 % head_dim == 0,
+                  "head_dim must divide 128 and be a multiple of 4");
+    GPTRS_REQUIRE(capacity > 0 && capacity <= 32768, "capacity out of range");
+    if (n_tokens == 0) return GPTRS_OK;
+    AttnF32Params p = {d_qkv, d_k_cache, d_v_cache, d_positions, d_slot, d_out, (int)n_tokens, (int)n_q_heads,
+                       (int)n_kv_heads, (int)head_dim, (int)capacity, 1.0f / sqrtf((float)head_dim), d_k_cache, d_v_cache};
     size_t smem = ((size_t)head_dim + (size_t)(capacity > 128 ? capacity : 128)) * sizeof(float);
     GPTRS_CUDA_OK(cudaFuncSetAttribute(attention_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     return launch_kernel(attention_f32_kernel, dim3((unsigned)n_q_heads, (unsigned)n_tokens), dim3(128), smem,

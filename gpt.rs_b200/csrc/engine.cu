@@ -290,15 +290,20 @@ struct NormFold {
     const int32_t* rope_slot = nullptr;
     void* rope_q_out = nullptr;
     void* rope_pool = nullptr;
+    // f32 path: normalise the x rows inside the matmul (1 = LayerNorm, 2 = RMSNorm)
+    int f32_norm = 0;
+    const float* f32_gamma = nullptr;
+    const float* f32_beta = nullptr;
 };
 
 int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool out_f32, const float* residual,
            bool swiglu, bool gelu, cudaStream_t st, const NormFold* fold = nullptr) {
     ++m.launches;
     if (m.f32()) {
-        return gptrs_cuda_matmul_f32(static_cast<const float*>(x), static_cast<const float*>(w.f32->data),
-                                     static_cast<float*>(y), rows, w.out, w.in,
-                                     w.bias ? static_cast<const float*>(w.bias->data) : nullptr, residual, gelu ? 1 : 0, st);
+        return gptrs_cuda_norm_matmul_f32(static_cast<const float*>(x), fold ? fold->f32_norm : 0, fold ? fold->f32_gamma : nullptr,
+                                          fold ? fold->f32_beta : nullptr, m.cfg.norm_eps, static_cast<const float*>(w.f32->data),
+                                          static_cast<float*>(y), rows, w.out, w.in,
+                                          w.bias ? static_cast<const float*>(w.bias->data) : nullptr, residual, gelu ? 1 : 0, st);
     }
     gptrs_matmul_epilogue ep = {};
     ep.out_dtype = out_f32 ? GPTRS_F32 : GPTRS_BF16;
@@ -422,6 +427,15 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         }
         return f;
     };
+    // f32 models on one rank: the norm before a projection is computed by the projection itself while it stages x
+    const bool fold32 = m.fold_norm && m.f32() && m.tp == 1;
+    auto fold32_for = [&](Tensor* g, Tensor* b) {
+        NormFold f;
+        f.f32_norm = gpt ? 1 : 2;
+        f.f32_gamma = static_cast<const float*>(g->data);
+        f.f32_beta = (gpt && b) ? static_cast<const float*>(b->data) : nullptr;
+        return f;
+    };
     auto row_parallel = [&](const Lane& ln, const Weight& w, const void* x, Tensor* next_gamma = nullptr) -> int {
         float* h = reinterpret_cast<float*>(at(m.hidden, (size_t)D * 4, ln));
         if (m.tp == 1) {
@@ -459,7 +473,10 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         const bool rope_folded = m.fold_rope && !m.f32() && !gpt && ln.T > 16 && c.rotary_dim == c.head_dim && c.head_dim == 128;
         void* qkv = at(m.qkv, (size_t)m.QKV() * act, ln);
         NormFold f;
-        if (folded && l > 0) f = fold_for(ln, nullptr, false);  // the previous block's last projection left bf16(hidden * gain) and the row sums
+        if (fold32) {
+            f = fold32_for(L.ln1_g, L.ln1_b);
+            if ((r = linear(m, L.qkv, at(m.hidden, (size_t)D * 4, ln), qkv, ln.T, false, nullptr, false, false, ln.st, &f))) return r;
+        } else if (folded && l > 0) f = fold_for(ln, nullptr, false);  // the previous block's last projection left bf16(hidden * gain) and the row sums
         else if ((r = norm(ln, L.ln1_g, L.ln1_b))) return r;
         if (rope_folded) {
             f.rope_positions = ints(m.d_pos, ln);
@@ -467,7 +484,7 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
             f.rope_q_out = at(m.q_rot, (size_t)m.QD() * 2, ln);
             f.rope_pool = m.kv_pool.as<unsigned char>() + (size_t)l * m.pool_layer_bytes;
         }
-        if ((r = linear(m, L.qkv, at(m.xn, (size_t)D * act, ln), qkv, ln.T, false, nullptr, false, false, ln.st, &f))) return r;
+        if (!fold32 && (r = linear(m, L.qkv, at(m.xn, (size_t)D * act, ln), qkv, ln.T, false, nullptr, false, false, ln.st, &f))) return r;
         if (rope_folded) return GPTRS_OK;
         if (m.f32()) {
             if (!gpt && c.rotary_dim > 0) {
@@ -479,6 +496,7 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
             }
             float* kc = m.k_cache.as<float>() + (size_t)l * m.cache_layer_elems;
             float* vc = m.v_cache.as<float>() + (size_t)l * m.cache_layer_elems;
+            if (rows_identity) return GPTRS_OK;  // decode step: the attention kernel appends the row itself
             ++m.launches;
             return gptrs_cuda_kv_append_f32(static_cast<float*>(qkv), ints(m.d_pos, ln), ints(m.d_slot, ln), kc, vc, ln.T,
                                             c.n_q_heads, c.n_kv_heads, c.head_dim, c.context_length, ln.st);
@@ -495,7 +513,12 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         if (m.f32()) {
             float* kc = m.k_cache.as<float>() + (size_t)l * m.cache_layer_elems;
             float* vc = m.v_cache.as<float>() + (size_t)l * m.cache_layer_elems;
-            return gptrs_cuda_attention_decode_f32(reinterpret_cast<float*>(at(m.qkv, (size_t)m.QKV() * 4, ln)), kc, vc,
+            auto attend = rows_identity ? gptrs_cuda_kv_append_attention_decode_f32
+                                        : [](const float* q, float* k, float* v, const int32_t* pos, const int32_t* sl, float* o, int64_t t,
+                                             int64_t hq, int64_t hkv, int64_t hd, int64_t cap, void* st) {
+                                              return gptrs_cuda_attention_decode_f32(q, k, v, pos, sl, o, t, hq, hkv, hd, cap, st);
+                                          };
+            return attend(reinterpret_cast<float*>(at(m.qkv, (size_t)m.QKV() * 4, ln)), kc, vc,
                                                    ints(m.d_pos, ln), ints(m.d_slot, ln), static_cast<float*>(out), ln.T,
                                                    c.n_q_heads, c.n_kv_heads, c.head_dim, c.context_length, ln.st);
         }
@@ -516,16 +539,19 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         int r;
         const bool folded = fold && ln.T > 16;
         if ((r = row_parallel(ln, L.attn_out, at(m.attn, (size_t)m.QD() * act, ln), folded ? L.ln2_g : nullptr))) return r;
-        if (!folded && (r = norm(ln, L.ln2_g, L.ln2_b))) return r;
-        void* xn = at(m.xn, (size_t)D * act, ln);
+        if (!folded && !fold32 && (r = norm(ln, L.ln2_g, L.ln2_b))) return r;
+        void* xn = fold32 ? at(m.hidden, (size_t)D * 4, ln) : at(m.xn, (size_t)D * act, ln);
         void* mlp_h = at(m.mlp_h, (size_t)c.d_mlp * act, ln);
+        NormFold f32n;
+        const NormFold* nf = nullptr;
+        if (fold32) { f32n = fold32_for(L.ln2_g, L.ln2_b); nf = &f32n; }
         if (gpt) {
-            if ((r = linear(m, L.mlp_in, xn, mlp_h, ln.T, false, nullptr, false, true, ln.st))) return r;
+            if ((r = linear(m, L.mlp_in, xn, mlp_h, ln.T, false, nullptr, false, true, ln.st, nf))) return r;
         } else if (m.f32()) {
             void* g = at(m.mlp_g, (size_t)c.d_mlp * 4, ln);
             void* u = at(m.mlp_u, (size_t)c.d_mlp * 4, ln);
-            if ((r = linear(m, L.mlp_gate, xn, g, ln.T, false, nullptr, false, false, ln.st))) return r;
-            if ((r = linear(m, L.mlp_up, xn, u, ln.T, false, nullptr, false, false, ln.st))) return r;
+            if ((r = linear(m, L.mlp_gate, xn, g, ln.T, false, nullptr, false, false, ln.st, nf))) return r;
+            if ((r = linear(m, L.mlp_up, xn, u, ln.T, false, nullptr, false, false, ln.st, nf))) return r;
             ++m.launches;
             if ((r = gptrs_cuda_swiglu(static_cast<float*>(g), static_cast<float*>(u), static_cast<float*>(mlp_h),
                                        (int64_t)ln.T * c.d_mlp, ln.st))) return r;
@@ -572,15 +598,17 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         GPTRS_CUDA_OK(cudaStreamWaitEvent(st, m.ev_join, 0));
     }
     const Lane whole = {st, 0, T, chunk_pages, nullptr, 0};
-    if ((rc = norm(whole, m.final_g, m.final_b))) return rc;
-    const void* xr = m.xn.p;
+    if (!fold32 && (rc = norm(whole, m.final_g, m.final_b))) return rc;
+    const void* xr = fold32 ? m.hidden.p : m.xn.p;  // f32: lm_head normalises its rows itself
     if (!rows_identity) {
         ++m.launches;
-        GatherParams gp = {m.xn.p, m.xn_rows.p, m.d_rows.as<int32_t>(), n_rows, D * (m.f32() ? 4 : 2)};
+        GatherParams gp = {xr, m.xn_rows.p, m.d_rows.as<int32_t>(), n_rows, D * (m.f32() ? 4 : 2)};
         if ((rc = launch_kernel(gather_rows_kernel, dim3(n_rows), dim3(128), 0, st, 1, gp))) return rc;
         xr = m.xn_rows.p;
     }
-    if ((rc = linear(m, m.lm_head, xr, m.logits.p, n_rows, true, nullptr, false, false, st))) return rc;
+    NormFold final_fold;
+    if (fold32) final_fold = fold32_for(m.final_g, m.final_b);
+    if ((rc = linear(m, m.lm_head, xr, m.logits.p, n_rows, true, nullptr, false, false, st, fold32 ? &final_fold : nullptr))) return rc;
     ++m.launches;
     if (m.tp == 1)
         return gptrs_cuda_sample_rows(m.logits.as<float>(), n_rows, c.vocab, temperature, m.sample_seed, m.d_sampled.as<int32_t>(), st);

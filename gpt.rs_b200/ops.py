@@ -305,9 +305,11 @@ def kv_append_f32(qkv, positions, slot, k_cache, v_cache, n_q, n_kv, head_dim):
                                          qkv.shape[0], n_q, n_kv, head_dim, k_cache.shape[2], _stream()))
 
 
-def attention_decode_f32(qkv, k_cache, v_cache, positions, slot, n_q, n_kv, head_dim):
+def attention_decode_f32(qkv, k_cache, v_cache, positions, slot, n_q, n_kv, head_dim, append=False):
+    """append=True: one launch that also stores the tokens' K / V rows first (tokens of distinct sequences only)."""
     t = qkv.shape[0]
     out = torch.empty((t, n_q * head_dim), dtype=torch.float32, device=qkv.device)
-    check(lib().gptrs_cuda_attention_decode_f32(_ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(slot),
-                                                _ptr(out), t, n_q, n_kv, head_dim, k_cache.shape[2], _stream()))
+    fn = lib().gptrs_cuda_kv_append_attention_decode_f32 if append else lib().gptrs_cuda_attention_decode_f32
+    check(fn(_ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(slot), _ptr(out), t, n_q, n_kv, head_dim,
+             k_cache.shape[2], _stream()))
     return out

@@ -272,6 +272,12 @@ int gptrs_cuda_sample_rows(const float* d_logits, int64_t rows, int64_t vocab, f
  * [in, out] (crates/gpt-rs/src/nn/layers/linear.rs:14, 50-71). */
 int gptrs_cuda_matmul_f32(const float* d_x, const float* d_w, float* d_y, int64_t m, int64_t n, int64_t k,
                           const float* d_bias, const float* d_residual, int gelu, void* stream);
+/* The same with the rows of x normalised over K while they are staged: norm_kind 1 = layer_norm(x, gamma, beta,
+ * eps), 2 = rms_norm(x, gamma, eps) (crates/gpt-rs/src/ops/functional/normalization.rs), 0 = none. Saves the
+ * separate norm launch of a decode step. */
+int gptrs_cuda_norm_matmul_f32(const float* d_x, int norm_kind, const float* d_gamma, const float* d_beta, float eps,
+                               const float* d_w, float* d_y, int64_t m, int64_t n, int64_t k, const float* d_bias,
+                               const float* d_residual, int gelu, void* stream);
 /* Dense f32 KV cache [slot][kv_head][capacity][head_dim] (attention.rs:35-39): append the K / V
  * part of packed f32 qkv rows at their positions (start clamped like DynamicUpdateSlice,
  * docs/backend.md:452-474), then attend over positions 0..pos. */
@@ -282,6 +288,12 @@ int gptrs_cuda_attention_decode_f32(const float* d_qkv, const float* d_k_cache, 
                                     const int32_t* d_positions, const int32_t* d_slot, float* d_out,
                                     int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
                                     int64_t capacity, void* stream);
+/* Both in one launch, for decode steps whose tokens belong to DISTINCT sequences (a token's row is written by
+ * the CTAs that read it; a second token of the same sequence in the launch would race with that write). */
+int gptrs_cuda_kv_append_attention_decode_f32(const float* d_qkv, float* d_k_cache, float* d_v_cache,
+                                              const int32_t* d_positions, const int32_t* d_slot, float* d_out,
+                                              int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
+                                              int64_t capacity, void* stream);
 
 /* ==============================================================================================
  * Backend object level: tensor handles and the parameter memo.

@@ -198,3 +198,7 @@ def test_attention_decode_f32_matches_oracle(cuda, n_q, n_kv, hd, cap, positions
         want, k_new, v_new = fr.attention_decode_cache(qkv[s:s + 1], n_q, n_kv, hd, ck[s], cv[s], p)
         assert np.allclose(got[s], want[0], rtol=1e-4, atol=1e-4)
         assert np.array_equal(kd[s].cpu().numpy(), k_new) and np.array_equal(vd[s].cpu().numpy(), v_new)
+    # the single-launch variant (append inside the attention kernel) leaves the same caches and outputs
+    kd2, vd2 = torch.from_numpy(ck).to(cuda), torch.from_numpy(cv).to(cuda)
+    out2 = ops.attention_decode_f32(qd, kd2, vd2, pos, slot, n_q, n_kv, hd, append=True)
+    assert torch.equal(out2, out) and torch.equal(kd2, kd) and torch.equal(vd2, vd)
