@@ -114,7 +114,7 @@ constexpr size_t umma_smem_max(int bn, int stages) {
 // BITS = 8: per-channel scales are applied to the f32 accumulators in the epilogue, the producers only widen
 // int8 to bf16 (exact); a stage holds 512 sixteen-byte entries instead of 256.
 template <int BITS, int BN, int G, int kStages>
-__global__ void __launch_bounds__(kUmmaThreads, (BITS == 4 && 2 * (umma_smem_max(BN, kStages) + 1024) <= 227 * 1024) ? 2 : 1)
+__global__ void __launch_bounds__(kUmmaThreads, (2 * (umma_smem_max(BN, kStages) + 1024) <= 227 * 1024) ? 2 : 1)
 umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_map, int* status) {
     constexpr int kBBytes = BN * 128;
     constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
@@ -434,55 +434,56 @@ int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
 
 }  // namespace
 
-// Called by quant_matmul.cu for W4 weights when M > 16. Returns GPTRS_UNIMPLEMENTED when the
-// tensor-core path does not apply, so that the caller falls back to the mma.sync kernel.
-int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
+// Grid geometry shared by both weight formats: row tile, cluster K split, CTA count.
+struct UmmaPlan { bool big_tile; int n_blocks, m_blocks, split; };
+
+UmmaPlan plan_umma(const MatmulParams& p) {
+    UmmaPlan pl;
     const int groups = p.K / 128;
-    const int n_blocks = ceil_div(p.N, kCtaN);
+    pl.n_blocks = ceil_div(p.N, kCtaN);
     // K split (cluster size 1..8, any integer): about 2.5 CTAs per SM measured fastest on a decode step; the CTAs of a
     // cluster are co-scheduled and meet at the reduction.
     static int pct = 0;  // CTAs per 100 SMs (GPTRS_UMMA_CTAS_PCT overrides the default of 250)
     if (pct == 0) { const char* e = getenv("GPTRS_UMMA_CTAS_PCT"); pct = e ? atoi(e) : 250; if (pct <= 0) pct = 250; }
     // Row tile: 256 rows when that alone fills the GPU (no K split: its shared memory has no room for receive
     // slots), otherwise tiles of up to 128 rows with a K split over what is left of the SMs.
-    const bool big_tile = p.M > 128 && n_blocks * ceil_div(p.M, 256) >= sm_count();
-    const int m_blocks = big_tile ? ceil_div(p.M, 256) : ceil_div(p.M, 128);
+    pl.big_tile = p.M > 128 && pl.n_blocks * ceil_div(p.M, 256) >= sm_count();
+    pl.m_blocks = pl.big_tile ? ceil_div(p.M, 256) : ceil_div(p.M, 128);
     // tiles of up to 64 rows fit two CTAs per SM, the 128-row tile one: never more CTAs than one wave of those
     const int ctas = p.M <= 64 ? sm_count() * pct / 100 : sm_count();
-    int split = big_tile ? 1 : ctas / (n_blocks * m_blocks);
+    int split = pl.big_tile ? 1 : ctas / (pl.n_blocks * pl.m_blocks);
     split = split < 1 ? 1 : (split > 8 ? 8 : split);
     if (split > groups) split = groups;
     // A cluster lives inside one GPC, so clusters of 5 or more CTAs do not pack into all 2 x SMs slots: a grid
     // that needs more than about 85 % of them runs as two waves (measured: the 48-tile projection with 7-CTA
     // clusters took twice the time of 5-CTA clusters). Pairs and triples pack well enough to ignore this.
     if (p.M <= 64)
-        while (split > 3 && n_blocks * m_blocks * split > sm_count() * 2 * 85 / 100) --split;
-    p.n_split = split;
-    p.groups_per_cta = (groups + split - 1) / split;
-    const dim3 grid(n_blocks, split, m_blocks);
+        while (split > 3 && pl.n_blocks * pl.m_blocks * split > sm_count() * 2 * 85 / 100) --split;
+    pl.split = split;
+    return pl;
+}
+
+// Called by quant_matmul.cu when M > 16.
+int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
+    const UmmaPlan pl = plan_umma(p);
+    p.n_split = pl.split;
+    p.groups_per_cta = (p.K / 128 + pl.split - 1) / pl.split;
+    const dim3 grid(pl.n_blocks, pl.split, pl.m_blocks);
     // decode-sized tiles: two producer groups, 3 stages, two CTAs per SM (four groups with 4-6 stages at one CTA
     // per SM, and a single group, measured 15-40 % slower)
     if (p.M <= 32) return launch_umma<4, 32, 2, 3>(p, grid, st);
     if (p.M <= 64) return launch_umma<4, 64, 2, 3>(p, grid, st);
-    if (!big_tile) return launch_umma<4, 128, 4, 4>(p, grid, st);
+    if (!pl.big_tile) return launch_umma<4, 128, 4, 4>(p, grid, st);
     return launch_umma<4, 256, 4, 4>(p, grid, st);
 }
 
-// W8A16 on the same kernel (M > 16).
 int umma_w8a16_matmul(MatmulParams p, cudaStream_t st) {
-    const int groups = p.K / 128;
-    const int n_blocks = ceil_div(p.N, kCtaN);
-    const bool big_tile = p.M > 128 && n_blocks * ceil_div(p.M, 256) >= sm_count();
-    const int m_blocks = big_tile ? ceil_div(p.M, 256) : ceil_div(p.M, 128);
-    // one CTA per SM: a W8 stage carries twice the bytes of a W4 stage
-    int split = big_tile ? 1 : sm_count() / (n_blocks * m_blocks);
-    split = split < 1 ? 1 : (split > 8 ? 8 : split);
-    if (split > groups) split = groups;
-    p.n_split = split;
-    p.groups_per_cta = (groups + split - 1) / split;
-    const dim3 grid(n_blocks, split, m_blocks);
-    if (p.M <= 64) return launch_umma<8, 64, 2, 4>(p, grid, st);
-    if (!big_tile) return launch_umma<8, 128, 2, 4>(p, grid, st);
+    const UmmaPlan pl = plan_umma(p);
+    p.n_split = pl.split;
+    p.groups_per_cta = (p.K / 128 + pl.split - 1) / pl.split;
+    const dim3 grid(pl.n_blocks, pl.split, pl.m_blocks);
+    if (p.M <= 64) return launch_umma<8, 64, 2, 3>(p, grid, st);
+    if (!pl.big_tile) return launch_umma<8, 128, 2, 4>(p, grid, st);
     return launch_umma<8, 256, 2, 4>(p, grid, st);
 }
 
