@@ -85,16 +85,25 @@ __host__ __device__ inline size_t split_slots_bytes(int mpad, int n_split) {
 struct SplitReduce {
     uint32_t slots_addr;
     int S, rank, rows_max;
-    __device__ __forceinline__ void begin(const MatmulParams& p) {
+    bool early;  // the "every CTA has started" barrier was armed at kernel start (dedicated receive slots)
+    // early_arrive = true: the receive slots are a region of their own, a peer may push as soon as this CTA has
+    // started; false: the slots alias buffers of the main loop and the caller runs barrier_all_done() after it.
+    __device__ __forceinline__ void begin(const MatmulParams& p, bool early_arrive = true) {
         S = p.n_split;
         rank = 0;
-        if (S > 1) { rank = (int)cluster_ctarank(); cluster_arrive(); }
+        early = early_arrive;
+        if (S > 1) { rank = (int)cluster_ctarank(); if (early) cluster_arrive(); }
+    }
+    // Slots that alias main-loop buffers: every thread of every CTA of the cluster calls this once its own CTA no
+    // longer touches those buffers; when it returns, no CTA of the cluster does.
+    __device__ __forceinline__ void barrier_all_done() const {
+        if (S > 1) { cluster_arrive(); cluster_wait(); }
     }
     // call once, by every thread, after the main loop and before the first push
     __device__ __forceinline__ void ready(float* slots, int mpad) {
         slots_addr = smem_u32(slots);
         rows_max = (mpad + S - 1) / S;
-        if (S > 1) cluster_wait();
+        if (S > 1 && early) cluster_wait();
     }
     // element (m, c) of this CTA's partial tile; owner = m % S, local row = m / S (passed in)
     __device__ __forceinline__ void push(int owner, int local_row, int c, float v) const {

@@ -103,10 +103,9 @@ __device__ __forceinline__ void tmem_ld_32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// smem of one CTA: stages, alignment slack, receive slots of the split-K reduction (tiles up to 128 rows)
-constexpr size_t umma_smem_max(int bn, int stages) {
-    return (size_t)stages * (kABytes + bn * 128) + 1024 + (bn <= 128 ? (size_t)(bn + 7) * kRedStride * 4 : 0);
-}
+// smem of one CTA: stages and alignment slack; the receive slots of the split-K reduction (and the output tile of
+// an unsplit launch) reuse the stage buffers once every CTA of the cluster has finished its main loop
+constexpr size_t umma_smem_max(int bn, int stages) { return (size_t)stages * (kABytes + bn * 128) + 1024; }
 
 // G = number of producer groups. Group g (256 / G threads) dequantises the stages it = g, g + G, ...; its
 // threads own G half-rows of such a stage each. The groups run out of phase, so that the fixed latencies of
@@ -132,7 +131,7 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     SplitReduce sr;
-    sr.begin(p);  // arrives on the cluster's "started" barrier; pushes wait for it
+    sr.begin(p, false);  // the receive slots alias the stages: see the barrier before the epilogue
     // The next kernel may be scheduled as soon as every CTA of this one runs: its own wait for this grid's
     // completion keeps the data dependence, and its set-up and weight prefetch overlap this kernel.
     pdl_launch_dependents();
@@ -316,13 +315,14 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
         __syncwarp();
     }
     // ---------------- epilogue: TMEM -> registers -> pushed to the owner CTA of each output row ----
-    // Split launches receive into a region of their own behind the stages (a peer may push while this
-    // CTA is still in its main loop); an unsplit launch reuses the stage buffers.
-    float* slots = reinterpret_cast<float*>(p.n_split > 1 ? smem + kStages * (kABytes + kBBytes) : smem);
+    // The partial tiles are received in the stage buffers. A CTA may be written to only when its own MMAs have
+    // read the last stage, so every thread first sees the MMA-done barrier and then meets the whole cluster.
+    if (!mbar_wait_relaxed(&done_bar, 0)) failed = true;
+    tc_fence_after();
+    sr.barrier_all_done();
+    float* slots = reinterpret_cast<float*>(smem);
     sr.ready(slots, BN);
     if (warp < kProducerWarps) {
-        if (!mbar_wait_relaxed(&done_bar, 0)) failed = true;
-        tc_fence_after();
         // warp w reads TMEM lanes 32*(w % 4); warps 0-3 take the low half of the columns, 4-7 the high half
         const int quarter = warp & 3;
         const int col = quarter * 32 + lane;  // output channel within the CTA tile == TMEM lane
@@ -394,7 +394,8 @@ int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
     if (r != CUDA_SUCCESS) return fail(GPTRS_EXECUTION, "cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
     int* status = umma_status_word();
     if (!status) return fail(GPTRS_EXECUTION, "cannot allocate the status word");
-    const size_t smem = (size_t)kStages * (kABytes + BN * 128) + 1024 + (p.n_split > 1 ? split_slots_bytes(BN, p.n_split) : 0);
+    const size_t smem = umma_smem_max(BN, kStages);
+    static_assert((size_t)kStages * (kABytes + BN * 128) >= (size_t)(BN + 7) * kRedStride * 4, "the receive slots must fit the stage buffers");
     constexpr size_t smem_max = umma_smem_max(BN, kStages);
     auto kern = umma_w4a16_kernel<BITS, BN, G, kStages>;
     static bool attr_done = false;
@@ -437,7 +438,7 @@ int launch_umma(const MatmulParams& p, dim3 grid, cudaStream_t st) {
 // Grid geometry shared by both weight formats: row tile, cluster K split, CTA count.
 struct UmmaPlan { bool big_tile; int n_blocks, m_blocks, split; };
 
-UmmaPlan plan_umma(const MatmulParams& p) {
+UmmaPlan plan_umma(const MatmulParams& p, int small_tile_ctas_per_sm) {
     UmmaPlan pl;
     const int groups = p.K / 128;
     pl.n_blocks = ceil_div(p.N, kCtaN);
@@ -445,8 +446,8 @@ UmmaPlan plan_umma(const MatmulParams& p) {
     // cluster are co-scheduled and meet at the reduction.
     static int pct = 0;  // CTAs per 100 SMs (GPTRS_UMMA_CTAS_PCT overrides the default of 250)
     if (pct == 0) { const char* e = getenv("GPTRS_UMMA_CTAS_PCT"); pct = e ? atoi(e) : 250; if (pct <= 0) pct = 250; }
-    // Row tile: 256 rows when that alone fills the GPU (no K split: its shared memory has no room for receive
-    // slots), otherwise tiles of up to 128 rows with a K split over what is left of the SMs.
+    // Row tile: 256 rows when that alone fills the GPU, otherwise tiles of up to 128 rows with a K split over what
+    // is left of the SMs.
     pl.big_tile = p.M > 128 && pl.n_blocks * ceil_div(p.M, 256) >= sm_count();
     pl.m_blocks = pl.big_tile ? ceil_div(p.M, 256) : ceil_div(p.M, 128);
     // tiles of up to 64 rows fit two CTAs per SM, the 128-row tile one: never more CTAs than one wave of those
@@ -458,18 +459,18 @@ UmmaPlan plan_umma(const MatmulParams& p) {
     // that needs more than about 85 % of them runs as two waves (measured: the 48-tile projection with 7-CTA
     // clusters took twice the time of 5-CTA clusters). Pairs and triples pack well enough to ignore this.
     if (p.M <= 64)
-        while (split > 3 && pl.n_blocks * pl.m_blocks * split > sm_count() * 2 * 85 / 100) --split;
+        while (split > 3 && pl.n_blocks * pl.m_blocks * split > sm_count() * small_tile_ctas_per_sm * 85 / 100) --split;
     pl.split = split;
     return pl;
 }
 
 // Called by quant_matmul.cu when M > 16.
 int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
-    const UmmaPlan pl = plan_umma(p);
+    const UmmaPlan pl = plan_umma(p, 2);
     p.n_split = pl.split;
     p.groups_per_cta = (p.K / 128 + pl.split - 1) / pl.split;
     const dim3 grid(pl.n_blocks, pl.split, pl.m_blocks);
-    // decode-sized tiles: two producer groups, 3 stages, two CTAs per SM (four groups with 4-6 stages at one CTA
+    // decode-sized tiles: two producer groups, 3 stages, three CTAs per SM (four groups with 4-6 stages at one CTA
     // per SM, and a single group, measured 15-40 % slower)
     if (p.M <= 32) return launch_umma<4, 32, 2, 3>(p, grid, st);
     if (p.M <= 64) return launch_umma<4, 64, 2, 3>(p, grid, st);
@@ -478,7 +479,7 @@ int umma_w4a16_matmul(MatmulParams p, cudaStream_t st) {
 }
 
 int umma_w8a16_matmul(MatmulParams p, cudaStream_t st) {
-    const UmmaPlan pl = plan_umma(p);
+    const UmmaPlan pl = plan_umma(p, 2);
     p.n_split = pl.split;
     p.groups_per_cta = (p.K / 128 + pl.split - 1) / pl.split;
     const dim3 grid(pl.n_blocks, pl.split, pl.m_blocks);

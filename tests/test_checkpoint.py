@@ -131,3 +131,25 @@ def test_rope_tables():
         ck.rope_tables(63, 1e4, 4)
     with pytest.raises(BackendError):
         ck.rope_tables(64, 1e4, 4, {"kind": "yarn", "factor": 2.0})  # no original length, no context length
+
+
+def test_cli_export_random_and_inspect_need_no_gpu(tmp_path, capsys):
+    spec = importlib.util.spec_from_file_location("gptrs_cli", ROOT / "gpt.rs_b200" / "cli.py")
+    cli = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(cli)
+    import json
+    conf = {"vocab_size": 96, "context_length": 64, "embed_dim": 128, "num_layers": 2, "num_heads": 2, "num_kv_heads": 1,
+            "head_dim": 64, "mlp_hidden_dim": 256, "rms_norm_eps": 1e-5, "rope_theta": 1e4, "rotary_dim": 64,
+            "rope_scaling": {"kind": "linear", "factor": 2.0}}
+    out = tmp_path / "m.gptrschk"
+    assert cli.main(["export-random", "--out", str(out), "--kind", "ministral", "--config", json.dumps(conf), "--seed", "5"]) == 0
+    r = ck.CheckpointReader(out)
+    cfg, scaling = ck.engine_config(r.model_config)
+    assert scaling == {"kind": "linear", "factor": 2.0}
+    assert cfg.n_kv_heads == 1 and cfg.head_dim == 64 and cfg.d_mlp == 256
+    assert set(cfg.param_shapes()) == {e.name for e in r.entries}
+    assert np.array_equal(r.get("final_norm.gamma"), np.ones(128, np.float32))
+    capsys.readouterr()
+    assert cli.main(["inspect", "--checkpoint", str(out)]) == 0
+    text = capsys.readouterr().out
+    assert "blocks.1.feed_forward.w_down" in text and '"kind": "ministral"' in text
