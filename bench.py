@@ -9,6 +9,10 @@ GPU, prompts of 2048 random token ids prefilled through the engine, then greedy 
 is one decode step of the whole batch (64 tokens per GPU). Requests are independent, so ranks
 share nothing on the data path (request-partitioned, weak scaling).
 Prints ONE JSON line on rank 0.
+
+Other modes (none of them the default line): --workload gpt2-fp32 (the reference's CPU-runnable case: one sequence,
+f32 weights), --weights w8a16, --parallelism tp (one batch over a tensor-parallel group), --microbench
+attention | attention-ragged | gemv | gemm64 | quant-linear (single kernels, CUDA-graph timed; used for ncu captures).
 """
 from __future__ import annotations
 
