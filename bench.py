@@ -563,8 +563,8 @@ def _main(out):
 
 
 # DRAM traffic per launch of the dominant kernel from the committed ncu capture (profiles/): batch 64,
-# context 2068: 545,888,768 B read + 8,714,240 B written. It grows in proportion to the visible tokens.
-NCU_TRAFFIC: dict = {"paged_attention_kernel": {"bytes": 545888768 + 8714240, "ctx": 2068}}
+# context 2068: 545,838,080 B read + 4,967,936 B written. It grows in proportion to the visible tokens.
+NCU_TRAFFIC: dict = {"paged_attention_kernel": {"bytes": 545838080 + 4967936, "ctx": 2068}}
 
 
 def lib_stream(model):
