@@ -1,21 +1,23 @@
-// W4A16 dequant-fused matmul on the 5th-generation tensor cores (tcgen05 / TMEM) for batches
+// W4A16 / W8A16 dequant-fused matmul on the 5th-generation tensor cores (tcgen05 / TMEM) for batches
 // above 16 rows: y[M][N] = x[M][K] . dequant(W)^T.
 //
-// Same contract, weight layout and epilogues as quant_matmul.cu (functional::matmul,
-// crates/gpt-rs/src/ops/functional/linalg.rs:109-127, on quantised Linear weights).
+// Same contract and epilogues as quant_matmul.cu (functional::matmul,
+// crates/gpt-rs/src/ops/functional/linalg.rs:109-127, on quantised Linear weights); the weights come from the
+// row-ordered copy of the packed buffer (layout B).
 //
 // One CTA computes a 128 (output channels) x BN (batch rows) tile over its K range:
-//   warps 0-7  stream the packed int4 weights (row-ordered layout B: 32 consecutive k of one row per
-//              thread and stage) from HBM to registers (prefetch ring), dequantise them to bf16 (exact
-//              integer, then one bf16 multiply by the group scale) and store them, 16 bytes at a time,
-//              into shared memory in the canonical K-major 128-byte-swizzled operand layout;
-//              afterwards they run the epilogue (TMEM -> registers -> shared tile),
-//   warp 8     issues one TMA tensor copy of the x tile [BN x 64] per stage (hardware swizzle,
-//              rows past M are zero-filled), and owns the TMEM allocation,
+//   warps 0-7  form G producer groups that take the 64-k stages in turn. A thread requests its 16-byte
+//              entries of the next stages before anything else (register ring), widens them to bf16 (W4:
+//              exact integer, then the product with the fp16 group scale rounded once to bf16; W8: exact, the
+//              channel scale multiplies the accumulator later) and stores them, 16 bytes at a time, into
+//              shared memory in the canonical K-major 128-byte-swizzled operand layout. The leader of a
+//              group issues the TMA tensor copy of the x tile [BN x 64] of its stage (hardware swizzle, rows
+//              past M zero-filled). Afterwards these warps run the epilogue (TMEM -> registers -> owner CTA),
+//   warp 8     owns the TMEM allocation,
 //   warp 9     issues tcgen05.mma (M=128, N=BN, K=16, bf16 x bf16 -> f32 in TMEM), four per
 //              64-wide stage, and releases stages with tcgen05.commit.
-// Split-K partials of a thread-block cluster meet through distributed shared memory (shared
-// with the mma.sync kernels). Every wait on an mbarrier is bounded; on a timeout the kernel
+// Split-K partials of a thread-block cluster are pushed into the stage buffers of the CTA that owns the
+// output row (matmul_common.cuh). Every wait on an mbarrier is bounded; on a timeout the kernel
 // records an error in *status, still frees its TMEM and leaves.
 #include <cuda.h>
 
