@@ -94,8 +94,8 @@ class ClockSampler:
 
 
 def build_model(gm, torch, dev, steps_total: int, use_pdl: int, prefill_chunk: int, tp_size: int = 1, tp_rank: int = 0, nccl_id=None,
-                weight_mode=None):
-    ctx = ((PROMPT_LEN + steps_total + 64 + 15) // 16) * 16
+                weight_mode=None, max_context=None):
+    ctx = (((max_context or PROMPT_LEN + steps_total + 64) + 15) // 16) * 16
     pages_per_seq = ctx // 16
     cfg = gm.ModelConfig.ministral_3b(context_length=ctx, weight_mode=weight_mode or gm.MODE_W4A16, max_seqs=BATCH,
                                       max_tokens=prefill_chunk, max_logit_rows=BATCH,
@@ -334,6 +334,95 @@ def run_gpt2(args, out, gm, torch, np):
     print(json.dumps(line), file=out)
 
 
+def run_dp512(args, out, gm, torch, np):
+    """512 requests with prompt lengths U{256..4096} (seed 0), 256 greedy decode steps each: the requests are
+    bin-packed over the ranks by token count, every rank serves its shard in waves of 64 on its own engine and
+    KV pool, and the only exchange is the host-side gather of the generated ids. Times are CUDA events on each
+    engine's stream around every phase, summed per rank, max over ranks."""
+    from gptrs_b200 import parallel
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    lo, hi = 256, 4096
+    lens = np.random.default_rng(0).integers(lo, hi + 1, size=args.requests)
+    assign, cost = parallel.partition_requests(lens, args.decode_steps, world)
+    mine = parallel.shard_of(assign, rank)
+    model, cfg = build_model(gm, torch, dev, 0, args.pdl, args.prefill_chunk, max_context=hi + args.decode_steps + 16)
+    rng = np.random.default_rng(2000)
+    all_prompts = [rng.integers(0, cfg.vocab, size=int(n)) for n in lens]  # same arrays on every rank
+    prompts = {int(i): all_prompts[int(i)] for i in mine}
+    stream = torch.cuda.ExternalStream(lib_stream(model), device=dev)
+    # warm-up: one short wave, so that graph capture and first-launch costs stay outside the timed region
+    parallel.run_requests(model, {int(i): all_prompts[int(i)][:64] for i in mine[:BATCH]}, max(args.warmup, 3), BATCH, args.prefill_chunk)
+    spans = {"prefill": [], "decode": []}
+    wall = {"prefill": 0.0, "decode": 0.0}
+
+    def timed(name, wave, fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        e0.record(stream)
+        fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        wall[name] += time.perf_counter() - t0
+        spans[name].append(e0.elapsed_time(e1))
+
+    uuid = None
+    try:
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(dev).uuid)
+    except Exception:
+        pass
+    sampler = ClockSampler(uuid)
+    launches0 = model.stats()["kernel_launches"]
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    ids = parallel.run_requests(model, prompts, args.decode_steps, BATCH, args.prefill_chunk, on_phase=timed)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    clocks = sampler.stop()
+    launches = model.stats()["kernel_launches"] - launches0
+    merged = parallel.gather_generated(ids, world)
+    t = torch.tensor([sum(spans["decode"]), sum(spans["prefill"]), wall["decode"] * 1e3, (wall["decode"] + wall["prefill"]) * 1e3],
+                     dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dec_ms, pre_ms, dec_wall_ms, job_ms = (float(x) for x in t)
+    tokens = args.requests * args.decode_steps
+    waves = len(spans["decode"])
+    if rank == 0:
+        assert sorted(merged) == list(range(args.requests)) and all(len(v) == args.decode_steps + 1 for v in merged.values())
+        line = {"metric": "decode_tokens_per_s", "value": tokens / (dec_ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                "steps": waves * args.decode_steps, "warmup": max(args.warmup, 3), "ms_per_step": dec_ms / max(waves * args.decode_steps, 1),
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "bf16 activations x int4 weights, f32 accumulate", "data": "synthetic",
+                "config": {"workload": f"Ministral-3B-shaped W4A16-g128, {args.requests} requests, prompt lengths U{{{lo}..{hi}}} (seed 0), "
+                                       f"{args.decode_steps} greedy decode steps each, waves of {BATCH} per GPU",
+                           "parallelism": f"dp{world} (requests bin-packed by token count, no collective)",
+                           "rank_token_cost": [int(c) for c in cost], "waves_on_rank0": waves,
+                           "l2": "inputs larger than L2 (1.8 GB weights + KV of the wave streamed per step)",
+                           "cuda_graph": True, "pdl": bool(args.pdl), "kv_cache": "paged bf16, 16-token pages",
+                           "prefill_seconds": round(pre_ms * 1e-3, 2), "prefill_tokens": int(lens.sum()),
+                           "prefill_tokens_per_s": float(lens.sum()) / (pre_ms * 1e-3),
+                           "job_seconds": round(job_ms * 1e-3, 2), "requests_per_s": args.requests / (job_ms * 1e-3)},
+                "e2e": {"value": tokens / (dec_wall_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": BATCH * 4,
+                        "d2h_bytes_per_step": BATCH * 4, "note": "host ids in and sampled ids out on every step; value is the same loop timed with CUDA events"},
+                "gpu_launches": int(launches), "clocks": clocks}
+        print(json.dumps(line), file=out)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     # Libraries (NCCL banners, warnings) may write to stdout; the contract is ONE JSON line there.
     real_stdout = os.fdopen(os.dup(1), "w")
@@ -358,8 +447,12 @@ def _main(out):
     ap.add_argument("--microbench", default=None, choices=["attention", "attention-ragged", "gemv", "gemm64", "quant-linear"],
                     help="run only one kernel microbenchmark (used for ncu captures) and print its JSON")
     ap.add_argument("--ctx", type=int, default=PROMPT_LEN + 20, help="context length for --microbench attention")
-    ap.add_argument("--workload", default="ministral3b-w4", choices=["ministral3b-w4", "gpt2-fp32"],
-                    help="gpt2-fp32 = the reference's CPU-runnable case (one sequence, 32-token prompt, 64 greedy tokens)")
+    ap.add_argument("--workload", default="ministral3b-w4", choices=["ministral3b-w4", "gpt2-fp32", "dp512"],
+                    help="gpt2-fp32 = the reference's CPU-runnable case (one sequence, 32-token prompt, 64 greedy tokens); "
+                         "dp512 = 512 requests with prompt lengths U{256..4096}, 256 decode steps each, partitioned over the ranks "
+                         "(total work fixed: strong scaling; not the default line)")
+    ap.add_argument("--requests", type=int, default=512, help="dp512: number of requests")
+    ap.add_argument("--decode-steps", type=int, default=256, help="dp512: decode steps per request")
     ap.add_argument("--weights", default="w4a16", choices=["w4a16", "w8a16"],
                     help="w8a16 = the same workload with per-channel int8 weights (not the default line)")
     ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
@@ -380,6 +473,9 @@ def _main(out):
 
     if args.workload == "gpt2-fp32":
         run_gpt2(args, out, gm, torch, np)
+        return
+    if args.workload == "dp512":
+        run_dp512(args, out, gm, torch, np)
         return
     if args.microbench:
         torch.cuda.set_device(0)

@@ -99,11 +99,11 @@ class CudaBackend:
     def supports_decode_sampling(self, temperature: float, top_k=None) -> bool:
         return bool(lib().gptrs_cuda_supports_decode_sampling(float(temperature), int(top_k is not None)))
 
-    def sample_decode_token(self, logits: TensorHandle, temperature: float = 0.0, random_u=None):
+    def sample_decode_token(self, logits: TensorHandle, temperature: float = 0.0, random_u=None, top_k=None):
         dt, dims = logits.spec()
         assert dt == 0 and len(dims) == 2
         has, tok = ctypes.c_int(0), ctypes.c_uint64(0)
-        check(lib().gptrs_cuda_sample_decode_token(logits.data_ptr(), dims[0], dims[1], float(temperature),
-                                                   int(random_u is not None), float(random_u or 0.0),
-                                                   ctypes.byref(has), ctypes.byref(tok), None))
+        check(lib().gptrs_cuda_sample_decode_token_top_k(logits.data_ptr(), dims[0], dims[1], float(temperature), int(top_k or 0),
+                                                         int(random_u is not None), float(random_u or 0.0),
+                                                         ctypes.byref(has), ctypes.byref(tok), None))
         return int(tok.value) if has.value else None

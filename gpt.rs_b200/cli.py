@@ -44,9 +44,8 @@ def cmd_generate(args) -> int:
     from gptrs_b200 import model as gm
     prompt = _ids(args)
     mode = {"f32": gm.MODE_F32, "w4a16": gm.MODE_W4A16, "w8a16": gm.MODE_W8A16}[args.weight_mode]
-    if args.top_k is not None:
-        # the device sampler refuses top-k exactly as the reference's does (inference/sampler.rs:74-81)
-        raise SystemExit("Unimplemented: top-k sampling is not available on the device sampler")
+    if args.top_k is not None and args.top_k < 1:
+        raise SystemExit("--top-k must be at least 1")
     reader = ck.CheckpointReader(args.checkpoint)
     ctx_cap = int(reader.model_config["config"]["context_length"])
     need = len(prompt) + args.max_tokens
@@ -64,6 +63,7 @@ def cmd_generate(args) -> int:
     t0 = time.perf_counter()
     out: list[int] = []
     if args.temperature > 0:
+        model.set_top_k(args.top_k)  # kept on the device, unlike the reference's host-only top-k (inference/sampler.rs:74-81)
         n = len(prompt)
         _, first = model.forward_with_decode_cache(prompt, [0] * n, list(range(n)), [n - 1], want_logits=False,
                                                    temperature=args.temperature, seed=args.seed)

@@ -122,6 +122,7 @@ struct Model {
     int gen_batch = 0;  // slots 0..gen_batch-1 are driven by generator_step
     int64_t launches = 0;
     uint32_t sample_seed = 0;
+    int64_t top_k = 0;  // 0 = no top-k filter in temperature sampling
 
     int QKV() const { return (cfg.n_q_heads + 2 * cfg.n_kv_heads) * cfg.head_dim; }
     int QD() const { return cfg.n_q_heads * cfg.head_dim; }
@@ -611,7 +612,7 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
     if ((rc = linear(m, m.lm_head, xr, m.logits.p, n_rows, true, nullptr, false, false, st, fold32 ? &final_fold : nullptr))) return rc;
     ++m.launches;
     if (m.tp == 1)
-        return gptrs_cuda_sample_rows(m.logits.as<float>(), n_rows, c.vocab, temperature, m.sample_seed, m.d_sampled.as<int32_t>(), st);
+        return gptrs_cuda_sample_rows_top_k(m.logits.as<float>(), n_rows, c.vocab, temperature, m.top_k, m.sample_seed, m.d_sampled.as<int32_t>(), st);
     // vocab-parallel head: every rank finds (max, argmax) of its shard, the pairs are all-gathered
     // and each rank picks the global winner (ties -> smallest global index)
     if (temperature > 0.f) return fail(GPTRS_UNIMPLEMENTED, "temperature sampling with a vocab-parallel head");
@@ -919,6 +920,13 @@ int gptrs_cuda_model_stats(gptrs_model* h, int64_t* quantised_now, int64_t* memo
     if (memo_hits) *memo_hits = m.memo_hits;
     if (free_pages) *free_pages = (int64_t)m.free_pages.size();
     if (kernel_launches) *kernel_launches = m.launches;
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_model_set_top_k(gptrs_model* h, int64_t top_k) {
+    GPTRS_REQUIRE(h, "null pointer");
+    GPTRS_REQUIRE(top_k >= 0, "top_k must not be negative");
+    reinterpret_cast<Model*>(h)->top_k = top_k;
     return GPTRS_OK;
 }
 

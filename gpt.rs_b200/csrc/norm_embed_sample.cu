@@ -262,6 +262,116 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
     }
 }
 
+
+// ---- top-k sampler ----------------------------------------------------------------------------
+// inference/sampler.rs:35-52 keeps every logit >= the k-th largest (ties at the threshold stay),
+// then samples from the softmax of what is left. Here: an exact radix select of the k-th largest
+// value (four passes over 8 bits of an order-preserving integer key), then Gumbel-max over the
+// kept logits with the hash of sample_kernel, so top_k >= vocab reproduces its draw bit for bit.
+struct TopKParams {
+    const float* logits;
+    int* tokens;
+    int rows, vocab, top_k;
+    float temperature;
+    uint32_t seed;
+};
+
+__device__ __forceinline__ uint32_t ordered_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);  // larger float <=> larger key
+}
+
+constexpr int kTopKThreads = 1024;
+
+__global__ void __launch_bounds__(kTopKThreads) sample_top_k_kernel(const TopKParams p) {
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t sel_prefix, sel_remaining;
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const float* x = p.logits + (size_t)row * p.vocab;
+    const int tid = threadIdx.x, lane = tid & 31;
+    uint32_t prefix = 0, remaining = (uint32_t)p.top_k;  // the threshold is the `remaining`-th largest key under `prefix`
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        const uint32_t mask = pass == 0 ? 0u : 0xffffffffu << (shift + 8);
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        for (int i0 = 0; i0 < p.vocab; i0 += kTopKThreads) {  // whole warps iterate together (match_any needs them converged)
+            const int i = i0 + tid;
+            const bool in = i < p.vocab;
+            const uint32_t key = in ? ordered_key(x[i]) : 0u;
+            const bool take = in && (key & mask) == prefix;
+            const uint32_t bin = take ? (key >> shift) & 255u : 256u;
+            const uint32_t peers = __match_any_sync(0xffffffffu, bin);  // one atomic per distinct bin of the warp
+            if (take && lane == __ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
+        }
+        __syncthreads();
+        if (tid < 32) {  // walk the bins from the top: 8 per lane, then a scan across the lanes
+            uint32_t mine = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mine += hist[255 - (tid * 8 + j)];
+            uint32_t incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t;
+            }
+            const uint32_t before = incl - mine;
+            if (before < remaining && remaining <= incl) {  // exactly one lane
+                uint32_t acc = before;
+                for (int j = 0; j < 8; ++j) {
+                    const int b = 255 - (tid * 8 + j);
+                    const uint32_t c = hist[b];
+                    if (acc + c >= remaining) {
+                        sel_prefix = prefix | ((uint32_t)b << shift);
+                        sel_remaining = remaining - acc;
+                        break;
+                    }
+                    acc += c;
+                }
+            }
+        }
+        __syncthreads();
+        prefix = sel_prefix;
+        remaining = sel_remaining;
+        __syncthreads();
+    }
+    const uint32_t threshold = prefix;  // key of the k-th largest logit
+    float best = -INFINITY;
+    int besti = 0x7fffffff;
+    for (int i = tid; i < p.vocab; i += kTopKThreads) {
+        float v = x[i];
+        if (ordered_key(v) < threshold) continue;
+        const uint32_t hsh = hash_u32(p.seed ^ hash_u32((uint32_t)i + 0x9e3779b9u * (uint32_t)(row + 1)));
+        const float u = ((float)(hsh >> 8) + 0.5f) * (1.f / 16777216.f);
+        v = v / p.temperature - logf(-logf(u));
+        if (v > best || (v == best && i < besti)) { best = v; besti = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+        if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+    }
+    const int w = tid >> 5;
+    if (lane == 0) { sv[w] = best; si[w] = besti; }
+    __syncthreads();
+    if (w == 0) {
+        best = sv[lane];
+        besti = si[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+            if (ov > best || (ov == best && oi < besti)) { best = ov; besti = oi; }
+        }
+        if (lane == 0) p.tokens[row] = besti == 0x7fffffff ? 0 : besti;
+    }
+}
+
 }  // namespace
 
 // Greedy argmax per row that also reports the winning value (vocab-parallel heads exchange the pairs).
@@ -349,7 +459,20 @@ int gptrs_cuda_softmax_last_dim(const float* d_x, float* d_out, int64_t rows, in
 
 int gptrs_cuda_supports_decode_sampling(float temperature, int has_top_k) {
     (void)temperature;
-    return has_top_k ? 0 : 1;  // top-k is left to the host sampler, as in the reference
+    (void)has_top_k;  // greedy, temperature and temperature + top-k all run on the device
+    return 1;
+}
+
+int gptrs_cuda_sample_rows_top_k(const float* d_logits, int64_t rows, int64_t vocab, float temperature, int64_t top_k,
+                                 uint32_t seed, int32_t* d_tokens, void* stream) {
+    GPTRS_REQUIRE(top_k >= 0, "top_k must not be negative");
+    // greedy ignores top-k, and k = 0 or k >= vocab filters nothing (inference/sampler.rs:30-36)
+    if (temperature <= 0.f || top_k == 0 || top_k >= vocab) return gptrs_cuda_sample_rows(d_logits, rows, vocab, temperature, seed, d_tokens, stream);
+    GPTRS_REQUIRE(d_logits && d_tokens, "null pointer");
+    GPTRS_REQUIRE(rows >= 0 && vocab > 0 && vocab < (1ll << 31) && rows < (1ll << 31), "bad shape");
+    if (rows == 0) return GPTRS_OK;
+    TopKParams p = {d_logits, d_tokens, (int)rows, (int)vocab, (int)top_k, temperature, seed};
+    return launch_kernel(sample_top_k_kernel, dim3((unsigned)rows), dim3(kTopKThreads), 0, as_stream(stream), 1, p);
 }
 
 int gptrs_cuda_sample_rows(const float* d_logits, int64_t rows, int64_t vocab, float temperature, uint32_t seed,
@@ -363,6 +486,11 @@ int gptrs_cuda_sample_rows(const float* d_logits, int64_t rows, int64_t vocab, f
 
 int gptrs_cuda_sample_decode_token(const float* d_logits, int64_t rows, int64_t vocab, float temperature,
                                    int has_random_u, float random_u, int* has_token, uint64_t* token, void* stream) {
+    return gptrs_cuda_sample_decode_token_top_k(d_logits, rows, vocab, temperature, 0, has_random_u, random_u, has_token, token, stream);
+}
+
+int gptrs_cuda_sample_decode_token_top_k(const float* d_logits, int64_t rows, int64_t vocab, float temperature, int64_t top_k,
+                                         int has_random_u, float random_u, int* has_token, uint64_t* token, void* stream) {
     GPTRS_REQUIRE(d_logits && has_token && token, "null pointer");
     GPTRS_REQUIRE(rows >= 1 && vocab > 0, "bad shape");
     *has_token = 0;
@@ -370,7 +498,7 @@ int gptrs_cuda_sample_decode_token(const float* d_logits, int64_t rows, int64_t 
     GPTRS_CUDA_OK(cudaMalloc(&d_tok, sizeof(int32_t)));
     uint32_t seed = 0;
     if (has_random_u) { float u = random_u; seed = *reinterpret_cast<uint32_t*>(&u); }
-    int rc = gptrs_cuda_sample_rows(d_logits + (size_t)(rows - 1) * vocab, 1, vocab, temperature, seed, d_tok, stream);
+    int rc = gptrs_cuda_sample_rows_top_k(d_logits + (size_t)(rows - 1) * vocab, 1, vocab, temperature, top_k, seed, d_tok, stream);
     int32_t h = 0;
     cudaError_t e = cudaSuccess;
     if (rc == GPTRS_OK) e = cudaMemcpyAsync(&h, d_tok, sizeof(h), cudaMemcpyDeviceToHost, as_stream(stream));

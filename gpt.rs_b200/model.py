@@ -188,6 +188,10 @@ class LoadedModel:
     def reset_sequence(self, slot: int = 0):
         check(lib().gptrs_cuda_model_reset_sequence(self._h, slot))
 
+    def set_top_k(self, top_k: int | None):
+        """Sampler::with_top_k for temperature draws (None or 0 = keep every logit)."""
+        check(lib().gptrs_cuda_model_set_top_k(self._h, int(top_k or 0)))
+
     def sequence_length(self, slot: int = 0) -> int:
         n = ctypes.c_int()
         check(lib().gptrs_cuda_model_sequence_length(self._h, slot, ctypes.byref(n)))

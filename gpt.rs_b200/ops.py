@@ -274,20 +274,23 @@ def softmax_last_dim(x):
     return out
 
 
-def sample_rows(logits, temperature=0.0, seed=0):
+def sample_rows(logits, temperature=0.0, seed=0, top_k=None):
     rows, vocab = logits.shape
     tok = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    check(lib().gptrs_cuda_sample_rows(_ptr(logits), rows, vocab, temperature, seed, _ptr(tok), _stream()))
+    if top_k is None:
+        check(lib().gptrs_cuda_sample_rows(_ptr(logits), rows, vocab, temperature, seed, _ptr(tok), _stream()))
+    else:
+        check(lib().gptrs_cuda_sample_rows_top_k(_ptr(logits), rows, vocab, temperature, int(top_k), seed, _ptr(tok), _stream()))
     return tok
 
 
-def sample_decode_token(logits, temperature=0.0, random_u=None):
+def sample_decode_token(logits, temperature=0.0, random_u=None, top_k=None):
     """PortableBackend::sample_decode_token: token of the LAST row, or None when unsupported."""
     rows, vocab = logits.shape
     has = ctypes.c_int(0)
     tok = ctypes.c_uint64(0)
-    check(lib().gptrs_cuda_sample_decode_token(_ptr(logits), rows, vocab, temperature, int(random_u is not None),
-                                               float(random_u or 0.0), ctypes.byref(has), ctypes.byref(tok), _stream()))
+    check(lib().gptrs_cuda_sample_decode_token_top_k(_ptr(logits), rows, vocab, temperature, int(top_k or 0), int(random_u is not None),
+                                                     float(random_u or 0.0), ctypes.byref(has), ctypes.byref(tok), _stream()))
     return int(tok.value) if has.value else None
 
 

@@ -36,3 +36,50 @@ def gather_generated(local_ids: dict, world_size: int):
     for p in parts:
         out.update(p)
     return out
+
+
+def plan_waves(request_ids, prompt_lens, max_batch: int):
+    """Cuts one rank's shard into waves of at most `max_batch` requests, longest prompts first, so the KV
+    pages a wave needs shrink from wave to wave and the first one shows whether the pool is large enough.
+    Every request decodes the same number of steps, so a wave's slots finish together and no slot idles."""
+    if max_batch <= 0:
+        raise ValueError("max_batch must be positive")
+    ids = [int(r) for r in request_ids]
+    ids.sort(key=lambda r: (-int(prompt_lens[r]), r))
+    return [ids[i:i + max_batch] for i in range(0, len(ids), max_batch)]
+
+
+def run_requests(model, prompts: dict, decode_steps: int, max_batch: int, prefill_chunk: int | None = None, on_phase=None,
+                 generator=None):
+    """Serves {request index: prompt ids} on one engine in waves (see plan_waves): prefill every request of a
+    wave into its slot, then `decode_steps` greedy steps over the wave's slots. Returns {request index:
+    [first id from the prompt's last row, then the decode_steps generated ids]}. `on_phase(name, wave, fn)`,
+    when given, runs each phase through the caller (the bench wraps it in timers); `generator` replaces the
+    engine's Generator class (host-logic tests pass a stand-in)."""
+    if generator is None:
+        from .model import Generator as generator
+    lens = {r: len(p) for r, p in prompts.items()}
+    call = on_phase or (lambda name, wave, fn: fn())
+    out = {}
+    for wave in plan_waves(prompts.keys(), lens, max_batch):
+        first = []
+
+        def prefill():
+            for slot, r in enumerate(wave):
+                model.reset_sequence(slot)
+                first.append(model.prefill(slot, prompts[r], chunk=prefill_chunk)[1])
+
+        steps = []
+
+        def decode():
+            gen = generator(model, first, use_graph=True)
+            cur = None
+            for _ in range(decode_steps):
+                cur = gen.step(tokens_in=cur)
+                steps.append(cur)
+
+        call("prefill", wave, prefill)
+        call("decode", wave, decode)
+        for slot, r in enumerate(wave):
+            out[r] = [int(first[slot])] + [int(s[slot]) for s in steps]
+    return out

@@ -255,15 +255,22 @@ int gptrs_cuda_softmax_last_dim(const float* d_x, float* d_out, int64_t rows, in
 
 /* PortableBackend::supports_decode_sampling / sample_decode_token
  * (crates/gpt-rs/src/backend/spec.rs:1331-1348): greedy (temperature <= 0; ties -> smallest
- * index) or Gumbel-max temperature sampling; top-k is refused (has_top_k -> 0), as the reference's
- * device sampler does. sample_decode_token samples the LAST row of logits[rows][vocab]
- * (crates/gpt-rs-backend-triton/src/runtime/sampling.rs:61-87) and synchronises the stream. */
+ * index) or Gumbel-max temperature sampling. sample_decode_token samples the LAST row of
+ * logits[rows][vocab] (crates/gpt-rs-backend-triton/src/runtime/sampling.rs:61-87) and synchronises
+ * the stream. The *_top_k forms serve DecodeSampleRequest.top_k (spec.rs, a field the reference's
+ * own device sampler refuses): every logit >= the k-th largest is kept, ties included, then the
+ * draw is from the softmax of the kept ones (crates/gpt-rs/src/inference/sampler.rs:35-52);
+ * top_k = 0 or >= vocab filters nothing and gives the draw of the plain form for the same seed. */
 int gptrs_cuda_supports_decode_sampling(float temperature, int has_top_k);
 int gptrs_cuda_sample_decode_token(const float* d_logits, int64_t rows, int64_t vocab, float temperature,
                                    int has_random_u, float random_u, int* has_token, uint64_t* token, void* stream);
 /* Batched form: one token per row, written to d_tokens[rows] (asynchronous). */
 int gptrs_cuda_sample_rows(const float* d_logits, int64_t rows, int64_t vocab, float temperature, uint32_t seed,
                            int32_t* d_tokens, void* stream);
+int gptrs_cuda_sample_rows_top_k(const float* d_logits, int64_t rows, int64_t vocab, float temperature, int64_t top_k,
+                                 uint32_t seed, int32_t* d_tokens, void* stream);
+int gptrs_cuda_sample_decode_token_top_k(const float* d_logits, int64_t rows, int64_t vocab, float temperature, int64_t top_k,
+                                         int has_random_u, float random_u, int* has_token, uint64_t* token, void* stream);
 
 /* ==============================================================================================
  * f32 path (unquantised models, e.g. GPT-2 small).
@@ -371,6 +378,9 @@ int gptrs_cuda_model_init_tensor_parallel(gptrs_model* m, const uint8_t* unique_
 int gptrs_cuda_model_finalize(gptrs_model* m, int drop_f32_leaves);
 int gptrs_cuda_model_stats(gptrs_model* m, int64_t* quantised_now, int64_t* memo_hits, int64_t* free_pages,
                            int64_t* kernel_launches);
+/* Sampler::with_top_k (crates/gpt-rs/src/inference/sampler.rs:20-23) for the temperature draws of
+ * forward_with_decode_cache: 0 (the default) keeps every logit. */
+int gptrs_cuda_model_set_top_k(gptrs_model* m, int64_t top_k);
 int gptrs_cuda_model_reset_sequence(gptrs_model* m, int slot);
 int gptrs_cuda_model_sequence_length(gptrs_model* m, int slot, int* len);
 /* One forward pass over n_tokens rows (token id, slot, position each; host arrays). K/V of every

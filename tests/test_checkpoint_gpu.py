@@ -64,7 +64,12 @@ def test_cli_generate_and_inspect(cuda, capsys):
     text = capsys.readouterr().out
     assert "tok_embeddings.weight" in text and '"kind": "gpt"' in text
     with pytest.raises(SystemExit):
-        cli.main(["generate", "--checkpoint", str(FIXTURE), "--prompt-ids", "1", "--top-k", "5"])
+        cli.main(["generate", "--checkpoint", str(FIXTURE), "--prompt-ids", "1", "--top-k", "0"])
+    capsys.readouterr()
+    # top-k 1 leaves only the largest logit, so a temperature draw is the greedy id
+    assert cli.main(["generate", "--checkpoint", str(FIXTURE), "--prompt-ids", "7,8,9", "--max-tokens", "10",
+                     "--temperature", "0.8", "--top-k", "1", "--seed", "3"]) == 0
+    assert [int(t) for t in capsys.readouterr().out.strip().split(",")] == want_ids
 
 
 def test_cli_random_ministral_checkpoint_quantised(cuda, tmp_path, capsys):

@@ -239,3 +239,18 @@ def test_gpt2_small_fp32_64_greedy_tokens_match_oracle(cuda):
         lgs, _ = m.forward_with_decode_cache([want_ids[i]], [0], [32 + i], [0])
         worst = max(worst, float(np.max(np.abs(lgs[0] - want_logits[i + 1]))))
     assert worst <= 1e-4, worst
+
+
+def test_requests_served_in_waves_match_the_oracle(cuda):
+    """Seven ragged requests on a three-slot engine (waves of 3, 3, 1): every request's ids equal the
+    oracle's single-sequence greedy decode, whatever wave and slot it ran in."""
+    from gptrs_b200 import parallel
+    cfg = mr.Cfg("ministral", n_layers=2, d_model=32, n_q=4, n_kv=2, hd=8, d_mlp=64, vocab=96, ctx=64, rot=8, theta=1e4)
+    params = mr.random_params(cfg, seed=11, std=0.4)
+    rng = np.random.default_rng(3)
+    prompts = {r: rng.integers(0, cfg.vocab, size=int(n)).tolist() for r, n in enumerate((9, 2, 17, 5, 30, 1, 12))}
+    m = _load(cfg, params, max_seqs=3, max_tokens=8)
+    got = parallel.run_requests(m, prompts, decode_steps=10, max_batch=3, prefill_chunk=8)
+    assert sorted(got) == list(range(7))
+    for r, p in prompts.items():
+        assert got[r] == mr.RefModel(cfg, params).generate_greedy(p, 11), r

@@ -122,7 +122,45 @@ def test_sampler_known_answers(cuda):
     assert np.array_equal(got, np.argmax(big, axis=1))
     lib = __import__("gptrs_b200").lib()
     assert lib.gptrs_cuda_supports_decode_sampling(0.0, 0) == 1
-    assert lib.gptrs_cuda_supports_decode_sampling(0.7, 1) == 0
+    assert lib.gptrs_cuda_supports_decode_sampling(0.7, 1) == 1
+
+
+def test_top_k_sampler(cuda):
+    """inference/sampler.rs:35-52: logits below the k-th largest are dropped (ties at the threshold stay), the
+    draw is from the softmax of the rest. The draw itself is random in the reference, so parity is the kept
+    set (exact) and the distribution (statistical)."""
+    rng = np.random.default_rng(4)
+    big = rng.normal(0, 2, size=(48, 131072)).astype(np.float32)
+    big[1] = -np.abs(big[1]) - 5.0          # every logit negative
+    big[2] = np.round(big[2])               # heavy ties, also at the threshold
+    big[3, :] = 0.0                         # all equal: everything is kept
+    big[3, 77] = 1.0
+    d = _d(big, cuda)
+    for k in (1, 2, 50, 1000):
+        for seed in (0, 9):
+            got = ops.sample_rows(d, temperature=1.3, seed=seed, top_k=k).cpu().numpy()
+            kth = np.partition(big, big.shape[1] - k, axis=1)[:, big.shape[1] - k]
+            assert (big[np.arange(48), got] >= kth).all(), (k, seed)
+            if k == 1:
+                assert np.array_equal(big[np.arange(48), got], big.max(axis=1))
+    # k = 0 and k >= vocab filter nothing: the draw of the plain sampler for the same seed
+    plain = ops.sample_rows(d, temperature=0.9, seed=5).cpu().numpy()
+    for k in (0, 131072, 10 ** 6):
+        assert np.array_equal(ops.sample_rows(d, temperature=0.9, seed=5, top_k=k).cpu().numpy(), plain)
+    assert np.array_equal(ops.sample_rows(d, temperature=0.0, seed=5, top_k=7).cpu().numpy(), np.argmax(big, axis=1))  # greedy ignores k
+    # distribution over the kept set: 8192 rows with the same logits draw independently (the hash mixes the row)
+    base = np.array([2.0, -1.0, 0.5, 1.5, 1.5, -3.0, 0.0, 1.0] + [-4.0] * 56, np.float32)
+    rows = np.tile(base, (8192, 1))
+    temp, k = 0.7, 4
+    got = ops.sample_rows(_d(rows, cuda), temperature=temp, seed=123, top_k=k).cpu().numpy()
+    keep = base >= np.sort(base)[-k]
+    assert keep.sum() == 4 and keep[got].all()
+    want = np.where(keep, np.exp((base - base.max()) / temp), 0.0)
+    want /= want.sum()
+    freq = np.bincount(got, minlength=64) / len(got)
+    assert np.abs(freq - want).max() < 0.02, (freq[:8], want[:8])
+    tok = ops.sample_decode_token(_d(np.array([[0.0, 5.0, 4.9, -1.0]], np.float32), cuda), 1.0, random_u=0.5, top_k=2)
+    assert tok in (1, 2)
 
 
 MATMUL_SHAPES = [(1, 1, 1), (1, 5, 3), (4, 5, 1), (7, 13, 9), (33, 65, 31), (8, 1, 8), (1, 16, 17), (64, 128, 32),

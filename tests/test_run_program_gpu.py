@@ -71,7 +71,8 @@ def test_sampler_on_program_output(be):
     b.set_results([x * 1.0])
     out = be.run_program(b.to_json(), [be.materialize(np.array([[-1.0, 0.1, 2.5, 0.4]], np.float32))])
     assert be.sample_decode_token(out[0], 0.0) == 2
-    assert be.supports_decode_sampling(0.0) and not be.supports_decode_sampling(0.5, top_k=5)
+    assert be.supports_decode_sampling(0.0) and be.supports_decode_sampling(0.5, top_k=5)
+    assert be.sample_decode_token(out[0], 0.9, random_u=0.25, top_k=1) == 2
 
 
 @pytest.mark.parametrize("fusion", [True, False])
