@@ -11,7 +11,9 @@ share nothing on the data path (request-partitioned, weak scaling).
 Prints ONE JSON line on rank 0.
 
 Other modes (none of them the default line): --workload gpt2-fp32 (the reference's CPU-runnable case: one sequence,
-f32 weights), --weights w8a16, --parallelism tp (one batch over a tensor-parallel group), --microbench
+f32 weights), --workload dp512 (512 requests with prompt lengths U{256..4096}, 256 decode steps each, bin-packed over the
+ranks and served in waves of 64: total work fixed, strong scaling), --weights w8a16, --parallelism tp (one batch over a
+tensor-parallel group), --microbench
 attention | attention-ragged | gemv | gemm64 | quant-linear (single kernels, CUDA-graph timed; used for ncu captures).
 """
 from __future__ import annotations
