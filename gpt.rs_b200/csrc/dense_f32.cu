@@ -250,13 +250,18 @@ __global__ void __launch_bounds__(128) attention_f32_kernel(const AttnF32Params 
     const float* kc = p.k_cache + ((size_t)p.slot[b] * p.Hkv + hk) * p.capacity * p.hd;
     const float* vc = p.v_cache + ((size_t)p.slot[b] * p.Hkv + hk) * p.capacity * p.hd;
     float mx = -INFINITY;
+    const bool vec4 = (p.hd & 3) == 0;
     for (int j = tid; j < len; j += 128) {
         const float* kr = kc + (size_t)j * p.hd;
         float s = 0.f;
-        for (int c = 0; c < p.hd; c += 4) {
-            float4 kv = *reinterpret_cast<const float4*>(kr + c);
-            s = fmaf(qs[c], kv.x, s); s = fmaf(qs[c + 1], kv.y, s);
-            s = fmaf(qs[c + 2], kv.z, s); s = fmaf(qs[c + 3], kv.w, s);
+        if (vec4) {
+            for (int c = 0; c < p.hd; c += 4) {
+                float4 kv = *reinterpret_cast<const float4*>(kr + c);
+                s = fmaf(qs[c], kv.x, s); s = fmaf(qs[c + 1], kv.y, s);
+                s = fmaf(qs[c + 2], kv.z, s); s = fmaf(qs[c + 3], kv.w, s);
+            }
+        } else {  // head sizes that are not a multiple of 4 (rows are then not 16-byte aligned)
+            for (int c = 0; c < p.hd; ++c) s = fmaf(qs[c], kr[c], s);
         }
         s *= p.scale;
         sc[j] = s;
@@ -367,8 +372,7 @@ int gptrs_cuda_attention_decode_f32(const float* d_qkv, const float* d_k_cache, 
                                     int64_t capacity, void* stream) {
     GPTRS_REQUIRE(d_qkv && d_k_cache && d_v_cache && d_positions && d_slot && d_out, "null pointer");
     GPTRS_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "bad head counts");
-    GPTRS_REQUIRE(head_dim > 0 && head_dim <= 128 && head_dim % 4 == 0 && 128 % head_dim == 0,
-                  "head_dim must divide 128 and be a multiple of 4");
+    GPTRS_REQUIRE(head_dim > 0 && head_dim <= 128, "head_dim must be 1..128");
     GPTRS_REQUIRE(capacity > 0 && capacity <= 32768, "capacity out of range");
     if (n_tokens == 0) return GPTRS_OK;
     AttnF32Params p = {d_qkv, d_k_cache, d_v_cache, d_positions, d_slot, d_out, (int)n_tokens, (int)n_q_heads,
@@ -385,8 +389,7 @@ int gptrs_cuda_kv_append_attention_decode_f32(const float* d_qkv, float* d_k_cac
                                               int64_t capacity, void* stream) {
     GPTRS_REQUIRE(d_qkv && d_k_cache && d_v_cache && d_positions && d_slot && d_out, "null pointer");
     GPTRS_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "bad head counts");
-    GPTRS_REQUIRE(head_dim > 0 && head_dim <= 128 && head_dim % 4 == 0 && 128 % head_dim == 0,
-                  "head_dim must divide 128 and be a multiple of 4");
+    GPTRS_REQUIRE(head_dim > 0 && head_dim <= 128, "head_dim must be 1..128");
     GPTRS_REQUIRE(capacity > 0 && capacity <= 32768, "capacity out of range");
     if (n_tokens == 0) return GPTRS_OK;
     AttnF32Params p = {d_qkv, d_k_cache, d_v_cache, d_positions, d_slot, d_out, (int)n_tokens, (int)n_q_heads,

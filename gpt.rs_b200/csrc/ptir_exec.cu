@@ -433,9 +433,12 @@ bool is_batched_dot(const Inst* d, int64_t contract_rhs) {
 bool rewrite_attention_decode(Plan& pl, Inst& in) {
     if (!is_batched_dot(&in, 1) || in.out.dims.size() != 3 || in.out.dims[1] != 1) return false;
     const int64_t hq = in.out.dims[0], hd = in.out.dims[2];
+    // geometries the dense-cache attention kernel does not take stay on the op-by-op path
+    if (hd > 128) return false;
     const Inst* sm = def_of(pl, in.operands[0]);
     if (!sm || sm->dead || sm->op != Op::FusedSoftmax || sm->out.dims.size() != 3 || sm->out.dims[0] != hq || sm->out.dims[1] != 1) return false;
     const int64_t cap = sm->out.dims[2];
+    if (cap > 32768) return false;
     int64_t hkv_v = 0, hkv_k = 0;
     const Operand* v_cache = grouped_cache_source(pl, in.operands[1], hq, cap, hd, &hkv_v);
     const Inst* z = def_of(pl, sm->operands[0]);

@@ -179,7 +179,8 @@ def test_attention_rejects_unsupported_geometry(cuda):
         ops.paged_attention_decode(q, q, z.view(1, 16), z[:1], z[:1], 4, 1, 16, head_dim=64)
 
 
-@pytest.mark.parametrize("n_q,n_kv,hd,cap,positions", [(12, 12, 64, 64, [0, 5, 63]), (4, 2, 16, 32, [31]), (8, 1, 128, 128, [7, 100])])
+@pytest.mark.parametrize("n_q,n_kv,hd,cap,positions", [(12, 12, 64, 64, [0, 5, 63]), (4, 2, 16, 32, [31]), (8, 1, 128, 128, [7, 100]),
+                                                       (4, 4, 1, 8, [0, 7]), (3, 3, 24, 16, [5, 15]), (2, 1, 6, 300, [299]), (2, 2, 127, 9, [4])])
 def test_attention_decode_f32_matches_oracle(cuda, n_q, n_kv, hd, cap, positions):
     rng = np.random.default_rng(n_q * 10 + hd)
     n_slots = len(positions)

@@ -193,3 +193,24 @@ def test_errors_map_to_backend_error_kinds(be):
     assert be.param_get(pid) is None
     be.param_set(pid, be.materialize(np.arange(3, dtype=np.float32)))
     assert be.to_literal(be.param_get(pid)).tolist() == [0.0, 1.0, 2.0]
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd", [(4, 4, 1), (3, 3, 24), (2, 1, 6), (2, 2, 127), (2, 1, 160)])
+def test_decode_attention_odd_head_sizes(be, n_q, n_kv, hd):
+    """head_dim 1 (torch_parity/attention.rs:433-453), sizes that are no multiple of 4 or do not divide 128, and one above the
+    fused kernel's limit of 128 (left on the op-by-op path by the rewrite): fused and unfused results agree with the interpreter."""
+    rng = np.random.default_rng(n_q * 100 + hd)
+    cap, pos = 8, 3
+    width = (n_q + 2 * n_kv) * hd
+    qkv = rng.uniform(-1, 1, size=(1, width)).astype(np.float32)
+    ck = rng.uniform(-1, 1, size=(n_kv, cap, hd)).astype(np.float32)
+    cv = rng.uniform(-1, 1, size=(n_kv, cap, hd)).astype(np.float32)
+    b = ptir.Builder()
+    pq, pk, pv = b.parameter(F32, [1, width]), b.parameter(F32, [n_kv, cap, hd]), b.parameter(F32, [n_kv, cap, hd])
+    pu, pqs = b.parameter(SI32, [3]), b.parameter(SI32, [1])
+    ctx, nk, nv = ptir.attention_decode_cache(pq, pk, pv, pu, pqs, n_q, n_kv, hd)
+    b.set_results([ctx, nk, nv])
+    inputs = [qkv, ck, cv, np.array([0, pos, 0], np.int32), np.array([pos], np.int32)]
+    for fusion in (True, False):
+        got, want = _both(be, b, inputs, fusion)
+        assert np.allclose(got[0], want[0], atol=1e-5) and np.array_equal(got[1], want[1]) and np.array_equal(got[2], want[2])
