@@ -231,6 +231,48 @@ __global__ void gather_kernel(const GatherParams p) {  // take_along_axis
     p.out[i] = p.in[(o * p.axis_in + id) * p.inner + in];
 }
 
+// ReduceWindow over a rank-4 f32 tensor (crates/gpt-rs-backend-ref-cpu/src/cpu.rs:1944-2108): one thread per output
+// element walks its window; a window position counts when it lands on a base-dilated input element inside the tensor.
+struct ReduceWindowParams {
+    const float* in; float* out;
+    int64_t n_out;
+    int in_dims[4], out_dims[4], window[4], stride[4], pad_lo[4], base_dil[4], win_dil[4];
+    int kind;  // 0 sum, 1 max, 2 min
+};
+__global__ void reduce_window_kernel(const ReduceWindowParams p) {
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.n_out) return;
+    int o[4];
+    int64_t r = i;
+#pragma unroll
+    for (int d = 3; d >= 0; --d) { o[d] = (int)(r % p.out_dims[d]); r /= p.out_dims[d]; }
+    int start[4];
+#pragma unroll
+    for (int d = 0; d < 4; ++d) start[d] = o[d] * p.stride[d] - p.pad_lo[d];
+    float acc = p.kind == 0 ? 0.f : (p.kind == 1 ? -INFINITY : INFINITY);
+    for (int w0 = 0; w0 < p.window[0]; ++w0) {
+        const int p0 = start[0] + w0 * p.win_dil[0];
+        if (p0 < 0 || p0 % p.base_dil[0] != 0 || p0 / p.base_dil[0] >= p.in_dims[0]) continue;
+        for (int w1 = 0; w1 < p.window[1]; ++w1) {
+            const int p1 = start[1] + w1 * p.win_dil[1];
+            if (p1 < 0 || p1 % p.base_dil[1] != 0 || p1 / p.base_dil[1] >= p.in_dims[1]) continue;
+            for (int w2 = 0; w2 < p.window[2]; ++w2) {
+                const int p2 = start[2] + w2 * p.win_dil[2];
+                if (p2 < 0 || p2 % p.base_dil[2] != 0 || p2 / p.base_dil[2] >= p.in_dims[2]) continue;
+                for (int w3 = 0; w3 < p.window[3]; ++w3) {
+                    const int p3 = start[3] + w3 * p.win_dil[3];
+                    if (p3 < 0 || p3 % p.base_dil[3] != 0 || p3 / p.base_dil[3] >= p.in_dims[3]) continue;
+                    const int64_t lin = (((int64_t)(p0 / p.base_dil[0]) * p.in_dims[1] + p1 / p.base_dil[1]) * p.in_dims[2] +
+                                         p2 / p.base_dil[2]) * p.in_dims[3] + p3 / p.base_dil[3];
+                    const float v = p.in[lin];
+                    acc = p.kind == 0 ? acc + v : (p.kind == 1 ? fmaxf(acc, v) : fminf(acc, v));
+                }
+            }
+        }
+    }
+    p.out[i] = acc;
+}
+
 template <typename P>
 int launch_flat(void (*k)(P), int64_t n, const P& p, cudaStream_t st) {
     if (n <= 0) return GPTRS_OK;
@@ -815,6 +857,30 @@ int exec_inst(Exec& ex, const Inst& in, std::vector<Tensor*>& ops, Tensor** resu
             for (size_t d = ax + 1; d < ops[0]->dims.size(); ++d) p.inner *= ops[0]->dims[d];
             ++ex.launches;
             rc = launch_flat(reduce_kernel, p.outer * p.inner * 32, p, ex.st);
+            break;
+        }
+        case Op::ReduceWindow: {
+            const Tensor* X = ops[0];
+            if (X->dtype != GPTRS_F32 || in.out.dtype != GPTRS_F32) return fail(GPTRS_EXECUTION, "reduce_window only supports f32 tensors");
+            if (in.f0 != 0.f) return unimpl("reduce_window: accum_dtype override not supported");
+            if (X->dims.size() != 4) return unimpl("reduce_window: only rank-4 tensors are supported");
+            if (in.a.size() != 4 || in.b.size() != 4 || in.c.size() != 4 || in.d.size() != 4 || in.e.size() != 4)
+                return fail(GPTRS_EXECUTION, "reduce_window expects window/stride/padding/dilation rank 4");
+            if (in.out.dims.size() != 4) return fail(GPTRS_EXECUTION, "reduce_window output must have rank 4");
+            if (in.out.dims[3] != X->dims[3]) return fail(GPTRS_EXECUTION, "reduce_window expects channels dimension preserved");
+            if (in.sub != "Sum" && in.sub != "Max" && in.sub != "Min") return spec("reduce_window: unknown reduce kind");
+            ReduceWindowParams p = {};
+            for (int d = 0; d < 4; ++d) {
+                if (in.d[d] < 1 || in.e[d] < 1 || in.b[d] < 0 || in.a[d] < 0 || X->dims[d] >= (1ll << 31) || in.out.dims[d] >= (1ll << 31))
+                    return spec("reduce_window: bad window attributes");
+                p.in_dims[d] = (int)X->dims[d]; p.out_dims[d] = (int)in.out.dims[d]; p.window[d] = (int)in.a[d];
+                p.stride[d] = (int)in.b[d]; p.pad_lo[d] = (int)in.c[d]; p.base_dil[d] = (int)in.d[d]; p.win_dil[d] = (int)in.e[d];
+            }
+            if ((rc = alloc_out())) return rc;
+            p.in = static_cast<const float*>(X->data); p.out = static_cast<float*>(out->data); p.n_out = in.out.numel();
+            p.kind = in.sub == "Sum" ? 0 : in.sub == "Max" ? 1 : 2;
+            ++ex.launches;
+            rc = launch_flat(reduce_window_kernel, p.n_out, p, ex.st);
             break;
         }
         case Op::DotGeneral: {

@@ -241,6 +241,17 @@ int build_function(const Json& program, Function* fn, std::string* err) {
         else if (n == "Gather") { in.op = Op::Gather; in.axis = attr->get("axis") ? attr->get("axis")->as_int() : 0; }
         else if (n == "DynamicSlice") { in.op = Op::DynamicSlice; read_ints(attr->get("sizes"), &in.a); }
         else if (n == "DynamicUpdateSlice") { in.op = Op::DynamicUpdateSlice; read_ints(attr->get("sizes"), &in.a); }
+        else if (n == "ReduceWindow") {
+            // ReduceWindowSpec (spec.rs:532-543): a = window, b = strides, c = low padding, d = base dilation, e = window dilation
+            in.op = Op::ReduceWindow;
+            in.sub = attr->get("reduce") ? attr->get("reduce")->str : "";
+            read_ints(attr->get("window_dims"), &in.a); read_ints(attr->get("strides"), &in.b);
+            if (const Json* pad = attr->get("padding"))
+                for (auto& pr : pad->arr) in.c.push_back(pr.arr.empty() ? 0 : pr.arr[0].as_int());
+            read_ints(attr->get("base_dilation"), &in.d); read_ints(attr->get("window_dilation"), &in.e);
+            const Json* acc = attr->get("accum_dtype");
+            if (acc && acc->kind == Json::String && acc->str != "F32") in.f0 = 1.f;  // refused at run time like the reference
+        }
         else if (n == "CustomCall") { in.op = Op::CustomCall; in.sub = attr->get("target") ? attr->get("target")->str : ""; }
         else in.op = Op::Unsupported;
         fn->body.push_back(std::move(in));

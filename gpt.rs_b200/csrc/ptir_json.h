@@ -32,7 +32,7 @@ bool parse_json(const char* text, size_t len, Json* out, std::string* err);
 
 enum class Op {
     Constant, Unary, Binary, DotGeneral, Reduce, Compare, Select, Cast, StopGradient, Reshape, Transpose, BroadcastTo,
-    Slice, Concat, Iota, Take, Gather, DynamicSlice, DynamicUpdateSlice, CustomCall,
+    Slice, Concat, Iota, Take, Gather, DynamicSlice, DynamicUpdateSlice, ReduceWindow, CustomCall,
     // produced by the fusion rewrites of this backend
     FusedLayerNorm, FusedRmsNorm, FusedSoftmax, FusedMatmulBias, FusedAttentionDecode, Unsupported
 };
@@ -56,7 +56,7 @@ struct Inst {
     Op op = Op::Unsupported;
     std::string name;             // operation name as written (for error messages)
     std::string sub;              // unary / binary / compare / reduce kind, cast dtype, custom target
-    std::vector<int64_t> a, b, c, d;  // attribute vectors (meaning depends on op)
+    std::vector<int64_t> a, b, c, d, e;  // attribute vectors (meaning depends on op)
     int64_t axis = 0;
     bool keepdims = false;
     float f0 = 0.f;               // fused ops: eps

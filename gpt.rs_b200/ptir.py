@@ -83,6 +83,19 @@ class Value:
                 "contract_rhs": list(contract_r), "accum_dtype": None, "out_dtype": None}
         return self.b.emit({"DotGeneral": spec}, [self, other], F32, dims)
 
+    def reduce_window(self, kind, window, strides, padding, base_dilation=None, window_dilation=None):
+        """ReduceWindowSpec (spec.rs:532-543); output extents follow the usual pooling arithmetic."""
+        n = len(self.dims)
+        bd, wd = list(base_dilation or [1] * n), list(window_dilation or [1] * n)
+        dims = []
+        for d in range(n):
+            dilated_in = (self.dims[d] - 1) * bd[d] + 1 if self.dims[d] > 0 else 0
+            span = (window[d] - 1) * wd[d] + 1
+            dims.append((dilated_in + padding[d][0] + padding[d][1] - span) // strides[d] + 1)
+        spec = {"window_dims": list(window), "strides": list(strides), "padding": [list(p) for p in padding],
+                "base_dilation": bd, "window_dilation": wd, "reduce": kind, "accum_dtype": None}
+        return self.b.emit({"ReduceWindow": spec}, [self], self.dtype, dims)
+
     def dynamic_slice(self, starts, sizes):
         return self.b.emit({"DynamicSlice": {"sizes": list(sizes)}}, [self, starts], self.dtype, sizes)
 

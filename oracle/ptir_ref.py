@@ -96,6 +96,50 @@ _CMP = {"Less": np.less, "LessEqual": np.less_equal, "Equal": np.equal, "Greater
         "Greater": np.greater, "NotEqual": np.not_equal}
 
 
+def _reduce_window(x, attr, out_dims):
+    """crates/gpt-rs-backend-ref-cpu/src/cpu.rs:1944-2108: rank-4 f32 only; a window position counts when it is
+    non-negative, lands on a multiple of the base dilation and the divided index is inside the input."""
+    if x.dtype != np.float32:
+        raise PtirError("reduce_window only supports f32 tensors")
+    if attr.get("accum_dtype") not in (None, "F32"):
+        raise PtirError("reduce_window: accum_dtype override not supported")
+    if x.ndim != 4 or len(out_dims) != 4:
+        raise PtirError("reduce_window: only rank-4 tensors are supported")
+    win, strides, pad = attr["window_dims"], attr["strides"], attr["padding"]
+    bdil, wdil = attr["base_dilation"], attr["window_dilation"]
+    if not all(len(v) == 4 for v in (win, strides, pad, bdil, wdil)):
+        raise PtirError("reduce_window expects window/stride/padding/dilation rank 4")
+    if out_dims[3] != x.shape[3]:
+        raise PtirError("reduce_window expects channels dimension preserved")
+    kind = attr["reduce"]
+    ident = {"Sum": np.float32(0.0), "Max": np.float32(-np.inf), "Min": np.float32(np.inf)}[kind]
+    out = np.full(out_dims, ident, dtype=np.float32)
+    # per axis: for every output index, the input indices its window touches (in window order)
+    taps = []
+    for d in range(4):
+        per_out = []
+        for o in range(out_dims[d]):
+            start = o * strides[d] - pad[d][0]
+            hit = []
+            for w in range(win[d]):
+                pos = start + w * wdil[d]
+                if pos < 0 or pos % bdil[d] != 0 or pos // bdil[d] >= x.shape[d]:
+                    continue
+                hit.append(pos // bdil[d])
+            per_out.append(hit)
+        taps.append(per_out)
+    for idx in np.ndindex(*out_dims):
+        acc = ident
+        for a in taps[0][idx[0]]:
+            for b in taps[1][idx[1]]:
+                for c in taps[2][idx[2]]:
+                    for e in taps[3][idx[3]]:
+                        v = x[a, b, c, e]
+                        acc = np.float32(acc + v) if kind == "Sum" else (max(acc, v) if kind == "Max" else min(acc, v))
+        out[idx] = acc
+    return out
+
+
 def _dot_general(a, b, s):
     bl, br, cl, cr = s["batch_lhs"], s["batch_rhs"], s["contract_lhs"], s["contract_rhs"]
     fl = [i for i in range(a.ndim) if i not in bl and i not in cl]
@@ -135,6 +179,8 @@ def execute_instruction(op, ins, out_spec):
             raise PtirError("reduce: single axis only")
         fn = {"Sum": np.sum, "Max": np.max, "Min": np.min}[attr["kind"]]
         return fn(ins[0], axis=attr["axes"][0], keepdims=attr["keepdims"]).astype(ins[0].dtype)
+    if kind == "ReduceWindow":
+        return _reduce_window(ins[0], attr, out_dims)
     if kind == "Compare":
         return _CMP[attr["op"]](ins[0], ins[1])
     if kind == "Select":

@@ -113,3 +113,53 @@ def test_decode_step_program_equals_model_oracle(kind):
     assert np.allclose(out[0][0], want, rtol=1e-4, atol=1e-4)
     for l in range(cfg.n_layers):
         assert np.allclose(out[1 + 2 * l], ref.caches[l][0], atol=1e-6)
+
+
+def _pool_program(shape, kind, window, strides, padding, base_dilation=None, window_dilation=None):
+    b = ptir.Builder()
+    x = b.parameter(ptir.F32, list(shape))
+    b.set_results([x.reduce_window(kind, window, strides, padding, base_dilation, window_dilation)])
+    return b
+
+
+@pytest.mark.parametrize("n,h,w,c,window,stride,pad,seed", [(1, 7, 8, 3, (3, 3), (2, 2), 1, 107), (1, 8, 8, 3, (2, 2), (2, 2), 0, 309),
+                                                             (2, 5, 6, 4, (2, 3), (1, 2), 1, 1)])
+def test_reduce_window_max_pool_matches_torch(n, h, w, c, window, stride, pad, seed):
+    # torch_parity/vision_ops.rs:619-660 (7x8x3, window 3, stride 2, padding 1) and :870-872 (8x8x3, window 2, stride 2)
+    import torch
+    x = np.random.default_rng(seed).uniform(-1, 1, size=(n, h, w, c)).astype(np.float32)
+    b = _pool_program(x.shape, "Max", [1, *window, 1], [1, *stride, 1], [(0, 0), (pad, pad), (pad, pad), (0, 0)])
+    got = _run(b, [x])[0]
+    want = torch.nn.functional.max_pool2d(torch.from_numpy(x).permute(0, 3, 1, 2), window, stride, pad).permute(0, 2, 3, 1).numpy()
+    assert got.shape == want.shape and np.array_equal(got, want)
+
+
+def test_reduce_window_sum_min_and_dilations():
+    import torch
+    x = np.random.default_rng(3).uniform(-1, 1, size=(2, 6, 7, 3)).astype(np.float32)
+    b = _pool_program(x.shape, "Sum", [1, 2, 2, 1], [1, 2, 2, 1], [(0, 0), (0, 0), (1, 0), (0, 0)])
+    want = torch.nn.functional.avg_pool2d(torch.nn.functional.pad(torch.from_numpy(x).permute(0, 3, 1, 2), (1, 0, 0, 0)), 2, 2).permute(0, 2, 3, 1).numpy() * 4
+    assert np.allclose(_run(b, [x])[0], want, atol=1e-6)
+    b = _pool_program(x.shape, "Min", [1, 3, 1, 1], [1, 1, 1, 1], [(0, 0), (1, 1), (0, 0), (0, 0)])
+    want = -torch.nn.functional.max_pool2d(torch.from_numpy(-x).permute(0, 3, 1, 2), (3, 1), 1, (1, 0)).permute(0, 2, 3, 1).numpy()
+    assert np.array_equal(_run(b, [x])[0], want)
+    # window dilation 2 = torch's dilation argument
+    b = _pool_program(x.shape, "Max", [1, 2, 2, 1], [1, 1, 1, 1], [(0, 0)] * 4, window_dilation=[1, 2, 2, 1])
+    want = torch.nn.functional.max_pool2d(torch.from_numpy(x).permute(0, 3, 1, 2), 2, 1, 0, dilation=2).permute(0, 2, 3, 1).numpy()
+    assert np.array_equal(_run(b, [x])[0], want)
+    # base dilation 2 spreads the input over a grid with holes that contribute nothing: a 1x1 sum window reads x or 0
+    b = _pool_program(x.shape, "Sum", [1, 1, 1, 1], [1, 1, 1, 1], [(0, 0)] * 4, base_dilation=[1, 2, 2, 1])
+    got = _run(b, [x])[0]
+    assert got.shape == (2, 11, 13, 3) and np.array_equal(got[:, ::2, ::2], x) and not got[:, 1::2].any() and not got[:, :, 1::2].any()
+    # a window that lies wholly in the padding keeps the identity of the reduction
+    b = _pool_program((1, 2, 2, 1), "Max", [1, 1, 1, 1], [1, 1, 1, 1], [(0, 0), (1, 1), (1, 1), (0, 0)])
+    got = _run(b, [np.ones((1, 2, 2, 1), np.float32)])[0]
+    assert got.shape == (1, 4, 4, 1) and np.isneginf(got[0, 0, 0, 0]) and got[0, 1, 1, 0] == 1.0
+
+
+def test_reduce_window_refusals():
+    b = ptir.Builder()
+    x = b.parameter(ptir.F32, [4, 4, 2])
+    b.set_results([x.reduce_window("Max", [2, 2, 1], [2, 2, 1], [(0, 0)] * 3)])
+    with pytest.raises(pr.PtirError):  # only rank-4 tensors (cpu.rs:1970-1975)
+        _run(b, [np.zeros((4, 4, 2), np.float32)])

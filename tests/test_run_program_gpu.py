@@ -214,3 +214,44 @@ def test_decode_attention_odd_head_sizes(be, n_q, n_kv, hd):
     for fusion in (True, False):
         got, want = _both(be, b, inputs, fusion)
         assert np.allclose(got[0], want[0], atol=1e-5) and np.array_equal(got[1], want[1]) and np.array_equal(got[2], want[2])
+
+
+@pytest.mark.parametrize("shape,kind,window,strides,padding,bdil,wdil", [
+    ((1, 7, 8, 3), "Max", [1, 3, 3, 1], [1, 2, 2, 1], [(0, 0), (1, 1), (1, 1), (0, 0)], None, None),   # vision_ops.rs:619-660
+    ((1, 8, 8, 3), "Max", [1, 2, 2, 1], [1, 2, 2, 1], [(0, 0)] * 4, None, None),                        # vision_ops.rs:870-872
+    ((2, 6, 7, 3), "Sum", [1, 2, 2, 1], [1, 2, 2, 1], [(0, 0), (0, 0), (1, 0), (0, 0)], None, None),
+    ((2, 6, 7, 3), "Min", [1, 3, 1, 1], [1, 1, 1, 1], [(0, 0), (1, 1), (0, 0), (0, 0)], None, None),
+    ((2, 6, 7, 3), "Max", [1, 2, 2, 1], [1, 1, 1, 1], [(0, 0)] * 4, None, [1, 2, 2, 1]),
+    ((2, 6, 7, 3), "Sum", [1, 1, 1, 1], [1, 1, 1, 1], [(0, 0)] * 4, [1, 2, 2, 1], None),
+    ((1, 2, 2, 1), "Max", [1, 1, 1, 1], [1, 1, 1, 1], [(0, 0), (1, 1), (1, 1), (0, 0)], None, None),    # windows wholly in the padding
+    ((3, 4, 5, 6), "Sum", [2, 2, 2, 1], [1, 2, 1, 1], [(1, 0), (0, 1), (1, 1), (0, 0)], None, [1, 1, 2, 1]),
+    ((4, 64, 64, 16), "Max", [1, 3, 3, 1], [1, 2, 2, 1], [(0, 0), (1, 1), (1, 1), (0, 0)], None, None),
+])
+def test_reduce_window(be, shape, kind, window, strides, padding, bdil, wdil):
+    """ReduceWindow (crates/gpt-rs-backend-ref-cpu/src/cpu.rs:1944-2108): max / sum / min results are exact copies or
+    sums in window order of at most a few terms, so the comparison with the interpreter is 1e-6."""
+    x = np.random.default_rng(len(shape) + shape[1]).uniform(-1, 1, size=shape).astype(np.float32)
+    b = ptir.Builder()
+    px = b.parameter(F32, list(shape))
+    b.set_results([px.reduce_window(kind, window, strides, padding, bdil, wdil)])
+    got, want = _both(be, b, [x])
+    assert got[0].shape == want[0].shape
+    if kind == "Sum":
+        assert np.allclose(got[0], want[0], atol=1e-6)
+    else:
+        assert np.array_equal(got[0], want[0])
+
+
+def test_reduce_window_refusals(be):
+    b = ptir.Builder()
+    x = b.parameter(F32, [4, 4, 2])
+    b.set_results([x.reduce_window("Max", [2, 2, 1], [2, 2, 1], [(0, 0)] * 3)])
+    with pytest.raises(BackendError) as e:  # only rank-4 tensors, as in the reference
+        be.run_program(b.to_json(), [be.materialize(np.zeros((4, 4, 2), np.float32))])
+    assert e.value.kind == "Unimplemented"
+    b = ptir.Builder()
+    x = b.parameter(SI32, [1, 4, 4, 2])
+    b.set_results([x.reduce_window("Max", [1, 2, 2, 1], [1, 2, 2, 1], [(0, 0)] * 4)])
+    with pytest.raises(BackendError) as e:
+        be.run_program(b.to_json(), [be.materialize(np.zeros((1, 4, 4, 2), np.int32))])
+    assert e.value.kind == "Execution"
