@@ -79,6 +79,15 @@ class CudaBackend:
         check(lib().gptrs_cuda_run_program(text, len(text), ins, len(inputs), outs, cap, ctypes.byref(n), stream))
         return [TensorHandle(outs[i]) for i in range(n.value)]
 
+    def execute_instruction(self, instruction, inputs: list, stream: int | None = None) -> list[TensorHandle]:
+        """PortableBackend::execute_instruction: one handle per operand (None for a Literal operand)."""
+        text = (instruction if isinstance(instruction, str) else json.dumps(instruction, separators=(",", ":"))).encode()
+        ins = (ctypes.c_void_p * max(len(inputs), 1))(*[(h._p.value if h is not None else None) for h in inputs])
+        outs = (ctypes.c_void_p * 8)()
+        n = ctypes.c_size_t()
+        check(lib().gptrs_cuda_execute_instruction(text, len(text), ins, len(inputs), outs, 8, ctypes.byref(n), stream))
+        return [TensorHandle(outs[i]) for i in range(n.value)]
+
     def run_program_stats(self) -> dict:
         v = [ctypes.c_int64() for _ in range(4)]
         check(lib().gptrs_cuda_run_program_stats(*[ctypes.byref(x) for x in v]))

@@ -1045,6 +1045,46 @@ int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* c
     return GPTRS_OK;
 }
 
+int gptrs_cuda_execute_instruction(const char* instruction_json, size_t len, gptrs_tensor* const* inputs, size_t n_inputs,
+                                   gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs, void* stream) {
+    GPTRS_REQUIRE(instruction_json && n_outputs && (n_inputs == 0 || inputs), "null pointer");
+    Json inst;
+    std::string err;
+    if (!parse_json(instruction_json, len, &inst, &err)) return fail(GPTRS_SPEC_VIOLATION, "instruction json: " + err);
+    const Json *id = inst.get("id"), *operands = inst.get("operands");
+    if (!id || !operands || operands->kind != Json::Array) return fail(GPTRS_SPEC_VIOLATION, "malformed instruction");
+    GPTRS_REQUIRE(n_inputs == operands->arr.size(), "one input handle per operand is expected");
+    // A one-instruction function around the text as given: each distinct operand value becomes a parameter typed by
+    // the handle passed for it; literal operands stay literals (their handle is not read).
+    static const char* const kNames[] = {"F32", "F16", "Bf16", "Si32", "I1", "Si8", "Ui8"};  // gptrs_dtype order
+    std::string params, pids;
+    std::vector<gptrs_tensor*> args;
+    std::vector<int64_t> seen;
+    for (size_t i = 0; i < operands->arr.size(); ++i) {
+        const Json* v = operands->arr[i].get("Value");
+        if (!v) continue;
+        const int64_t vid = v->as_int();
+        bool dup = false;
+        for (int64_t s2 : seen) dup = dup || s2 == vid;
+        if (dup) continue;
+        const Tensor* t = reinterpret_cast<const Tensor*>(inputs[i]);
+        GPTRS_REQUIRE(t, "null input handle");
+        GPTRS_REQUIRE(t->dtype >= 0 && t->dtype < 7, "input handle of an unknown dtype");
+        seen.push_back(vid);
+        args.push_back(inputs[i]);
+        if (!params.empty()) { params += ","; pids += ","; }
+        params += std::string("{\"Tensor\":{\"dtype\":\"") + kNames[t->dtype] + "\",\"shape\":{\"dims\":[";
+        for (size_t d = 0; d < t->dims.size(); ++d) params += (d ? ",{\"Static\":" : "{\"Static\":") + std::to_string(t->dims[d]) + "}";
+        params += "]}}}";
+        pids += std::to_string(vid);
+    }
+    std::string text = "{\"spec_version\":\"ptir.v0.4\",\"entry\":\"instruction\",\"functions\":[{\"name\":\"instruction\",\"parameters\":[" +
+                       params + "],\"parameter_ids\":[" + pids + "],\"results\":[],\"body\":[";
+    text.append(instruction_json, len);
+    text += "],\"hints\":[],\"result_ids\":[" + std::to_string(id->as_int()) + "]}],\"regions\":[]}";
+    return gptrs_cuda_run_program(text.data(), text.size(), args.data(), args.size(), outputs, outputs_cap, n_outputs, stream);
+}
+
 int gptrs_cuda_run_program_stats(int64_t* plan_builds, int64_t* plan_hits, int64_t* last_launches, int64_t* last_fused) {
     if (plan_builds) *plan_builds = g_plan_builds;
     if (plan_hits) *plan_hits = g_plan_hits;

@@ -408,12 +408,17 @@ void* gptrs_cuda_model_stream(gptrs_model* m); /* cudaStream_t of the model */
  * `outputs` as new retained handles. Supported operations: the decode-path subset Constant, Reshape,
  * Slice, Transpose, BroadcastTo, DotGeneral, ElementwiseUnary/Binary, Reduce (one axis), Compare,
  * Select, Cast, Concat, Take, Gather, Iota, DynamicSlice, DynamicUpdateSlice, StopGradient on f32 /
- * si32 / i1; anything else, and every unknown CustomCall target, returns GPTRS_UNIMPLEMENTED
+ * si32 / i1, ReduceWindow on rank-4 f32; anything else, and every unknown CustomCall target, returns GPTRS_UNIMPLEMENTED
  * (docs/backend.md:581-582). The parsed and rewritten plan is cached by a hash of the text.
  * The rewrite fuses layer_norm, rms_norm, softmax and matmul+bias subgraphs (the op sequences of
  * ops/functional/normalization.rs:133-206, common.rs:22-31, tensor_ops.rs:50-55) into single kernels. */
 int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* const* inputs, size_t n_inputs,
                            gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs, void* stream);
+/* execute_instruction (spec.rs:1318-1323): one Instruction as serde JSON ({"id", "op", "operands", "output"}) with one
+ * handle per operand, in operand order (the handle of a Literal operand is not read and may be NULL). Runs through the
+ * same executor as run_program, so the supported operations and the error kinds are the same. */
+int gptrs_cuda_execute_instruction(const char* instruction_json, size_t len, gptrs_tensor* const* inputs, size_t n_inputs,
+                                   gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs, void* stream);
 int gptrs_cuda_run_program_stats(int64_t* plan_builds, int64_t* plan_hits, int64_t* last_launches, int64_t* last_fused);
 /* Turns the fusion rewrites of run_program on (default) or off (GPTRS_OPT-style switch for tests). */
 int gptrs_cuda_set_fusion(int enabled);

@@ -255,3 +255,35 @@ def test_reduce_window_refusals(be):
     with pytest.raises(BackendError) as e:
         be.run_program(b.to_json(), [be.materialize(np.zeros((1, 4, 4, 2), np.int32))])
     assert e.value.kind == "Execution"
+
+
+def test_execute_instruction(be):
+    """PortableBackend::execute_instruction (spec.rs:1318-1323): single instructions through the same executor."""
+    rng = np.random.default_rng(8)
+    a, w = rng.uniform(-1, 1, size=(3, 5)).astype(np.float32), rng.uniform(-1, 1, size=(5, 4)).astype(np.float32)
+    b = ptir.Builder()
+    pa, pw = b.parameter(F32, [3, 5]), b.parameter(F32, [5, 4])
+    dot = ptir.matmul(pa, pw)
+    sq = pa * pa            # the same value twice among the operands
+    plus1 = pa + 1.0        # emits BroadcastTo(literal 1.0) and the Add
+    ha, hw = be.materialize(a), be.materialize(w)
+    by_id = {i["id"]: i for i in b.body}
+    got = be.execute_instruction(by_id[dot.id], [ha, hw])
+    assert len(got) == 1 and np.allclose(be.to_literal(got[0]), a @ w, atol=1e-5)
+    got = be.execute_instruction(by_id[sq.id], [ha, ha])
+    assert np.array_equal(be.to_literal(got[0]), a * a)
+    lit = next(i for i in b.body if any("Literal" in o for o in i["operands"]))  # BroadcastTo of the scalar literal 1.0
+    got = be.execute_instruction(lit, [None])                                   # the handle of a literal operand is not read
+    assert np.array_equal(be.to_literal(got[0]), np.ones((3, 5), np.float32))
+    got = be.execute_instruction(by_id[plus1.id], [ha, got[0]])
+    assert np.array_equal(be.to_literal(got[0]), a + 1.0)
+    # errors keep their kinds: unknown operation, operand count, operand type
+    with pytest.raises(BackendError) as e:
+        be.execute_instruction({"id": 9, "op": {"RngUniform": {}}, "operands": [], "output": by_id[dot.id]["output"]}, [])
+    assert e.value.kind == "Unimplemented"
+    with pytest.raises(BackendError):
+        be.execute_instruction(by_id[dot.id], [ha])
+    with pytest.raises(BackendError):
+        be.execute_instruction(by_id[dot.id], [hw, ha])  # contracting sizes differ
+    with pytest.raises(BackendError):
+        be.execute_instruction("{broken", [])
