@@ -88,6 +88,10 @@ class CudaBackend:
         check(lib().gptrs_cuda_execute_instruction(text, len(text), ins, len(inputs), outs, 8, ctypes.byref(n), stream))
         return [TensorHandle(outs[i]) for i in range(n.value)]
 
+    def pipeline_fuse(self, program) -> tuple[str, int]:
+        """The backend's fuse phase on a program: (rewritten program JSON, number of rewrites)."""
+        return pipeline_fuse(program)
+
     def run_program_stats(self) -> dict:
         v = [ctypes.c_int64() for _ in range(4)]
         check(lib().gptrs_cuda_run_program_stats(*[ctypes.byref(x) for x in v]))
@@ -116,3 +120,13 @@ class CudaBackend:
                                                          int(random_u is not None), float(random_u or 0.0),
                                                          ctypes.byref(has), ctypes.byref(tok), None))
         return int(tok.value) if has.value else None
+
+
+def pipeline_fuse(program) -> tuple[str, int]:
+    """gptrs_cuda_pipeline_fuse: host-only text-to-text rewrite (needs no GPU)."""
+    text = (program if isinstance(program, str) else json.dumps(program, separators=(",", ":"))).encode()
+    n, fused = ctypes.c_size_t(), ctypes.c_int64()
+    check(lib().gptrs_cuda_pipeline_fuse(text, len(text), None, 0, ctypes.byref(n), ctypes.byref(fused)))
+    buf = ctypes.create_string_buffer(n.value)
+    check(lib().gptrs_cuda_pipeline_fuse(text, len(text), buf, n.value, ctypes.byref(n), ctypes.byref(fused)))
+    return buf.raw[:n.value].decode(), int(fused.value)

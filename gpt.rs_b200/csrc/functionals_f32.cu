@@ -1,0 +1,136 @@
+// Stand-alone f32 functionals of the override boundary that the engine itself reaches only fused into
+// other kernels: RoPE on [heads, seq, head_dim] and on packed qkv rows, prefill attention with an
+// optional cache in front, and dequantisation of the canonical W4 / W8 weight formats.
+//
+//   apply_rope, apply_rope_qkv_packed   crates/gpt-rs/src/ops/functional/rotary.rs:289-336, 430-536
+//   functional::attention               crates/gpt-rs/src/ops/functional/attention.rs:337-541
+//   Dequantize                          crates/gpt-rs/src/backend/spec.rs:577-596 (scheme backend-defined)
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace gptrs {
+namespace {
+
+// Half-split rotation of the first 2 * half channels of every head row; the rest passes through.
+// `x_row(head, t)` / `o_row(head, t)` give the row starts, so one kernel serves both layouts.
+struct RopeParams {
+    const float* x; float* out;
+    const float* cos_t; const float* sin_t;  // [seq][half]
+    int heads, seq, hd, half;
+    int64_t head_stride, tok_stride;          // element strides of x and out
+};
+__global__ void rope_f32_kernel(const RopeParams p) {
+    const int head = blockIdx.x, t = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* x = p.x + head * p.head_stride + t * p.tok_stride;
+    float* o = p.out + head * p.head_stride + t * p.tok_stride;
+    for (int c = threadIdx.x; c < p.hd; c += blockDim.x) {
+        float v;
+        if (c < p.half) {
+            v = x[c] * p.cos_t[(size_t)t * p.half + c] - x[c + p.half] * p.sin_t[(size_t)t * p.half + c];
+        } else if (c < 2 * p.half) {
+            const int i = c - p.half;
+            v = x[c] * p.cos_t[(size_t)t * p.half + i] + x[i] * p.sin_t[(size_t)t * p.half + i];
+        } else {
+            v = x[c];
+        }
+        o[c] = v;
+    }
+}
+
+struct CopyColsParams { const float* src; float* dst; int64_t rows, cols, src_stride, dst_stride; };
+__global__ void copy_cols_kernel(const CopyColsParams p) {
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= p.rows * p.cols) return;
+    const int64_t r = i / p.cols, c = i % p.cols;
+    p.dst[r * p.dst_stride + c] = p.src[r * p.src_stride + c];
+}
+
+// present K / V [Hkv][l0 + T][hd]: the cache rows first, then the K / V parts of the packed rows
+struct PresentParams {
+    const float* qkv; const float* cache_k; const float* cache_v; float* k_out; float* v_out;
+    int T, Hq, Hkv, hd, l0;
+};
+__global__ void present_kv_kernel(const PresentParams p) {
+    const int64_t total = p.l0 + p.T;
+    const int64_t n = (int64_t)p.Hkv * total * p.hd;
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int c = (int)(i % p.hd);
+    const int64_t j = (i / p.hd) % total;
+    const int h = (int)(i / (p.hd * total));
+    if (j < p.l0) {
+        const size_t s = ((size_t)h * p.l0 + j) * p.hd + c;
+        p.k_out[i] = p.cache_k[s];
+        p.v_out[i] = p.cache_v[s];
+    } else {
+        const size_t width = (size_t)(p.Hq + 2 * p.Hkv) * p.hd;
+        const float* row = p.qkv + (size_t)(j - p.l0) * width + (size_t)(p.Hq + h) * p.hd;
+        p.k_out[i] = row[c];
+        p.v_out[i] = row[(size_t)p.Hkv * p.hd + c];
+    }
+}
+
+// One CTA per (query head, token): the token at position l0 + t attends to positions 0..l0+t of its KV head.
+struct PrefillAttnParams {
+    const float* qkv; const float* k; const float* v; float* out;
+    int T, Hq, Hkv, hd, l0;
+    float scale;
+};
+__global__ void __launch_bounds__(128) attention_prefill_f32_kernel(const PrefillAttnParams p) {
+    extern __shared__ float pf_smem[];
+    float* qs = pf_smem;          // [hd]
+    float* sc = pf_smem + p.hd;   // [max(total, 128)]
+    __shared__ float sh[8];
+    const int hq = blockIdx.x, t = blockIdx.y, tid = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int total = p.l0 + p.T, len = p.l0 + t + 1;
+    const int hk = hq / (p.Hq / p.Hkv);
+    const size_t width = (size_t)(p.Hq + 2 * p.Hkv) * p.hd;
+    for (int i = tid; i < p.hd; i += 128) qs[i] = p.qkv[(size_t)t * width + (size_t)hq * p.hd + i];
+    __syncthreads();
+    const float* kc = p.k + (size_t)hk * total * p.hd;
+    const float* vc = p.v + (size_t)hk * total * p.hd;
+    float mx = -INFINITY;
+    for (int j = tid; j < len; j += 128) {
+        float s = 0.f;
+        for (int c = 0; c < p.hd; ++c) s = fmaf(qs[c], kc[(size_t)j * p.hd + c], s);
+        s *= p.scale;
+        sc[j] = s;
+        mx = fmaxf(mx, s);
+    }
+    mx = warp_max(mx);
+    if ((tid & 31) == 0) sh[tid >> 5] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(sh[0], sh[1]), fmaxf(sh[2], sh[3]));
+    float sum = 0.f;
+    for (int j = tid; j < len; j += 128) {
+        const float e = expf(sc[j] - mx);
+        sc[j] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    if ((tid & 31) == 0) sh[4 + (tid >> 5)] = sum;
+    __syncthreads();
+    sum = sh[4] + sh[5] + sh[6] + sh[7];
+    // out[c] = sum_j p_j V[j][c]: thread (part, c) walks tokens part, part + parts, ...
+    const int parts = 128 / p.hd > 0 ? 128 / p.hd : 1;
+    const int c = tid % p.hd, part = tid / p.hd;
+    float acc = 0.f;
+    if (part < parts)
+        for (int j = part; j < len; j += parts) acc = fmaf(sc[j], vc[(size_t)j * p.hd + c], acc);
+    __syncthreads();  // every read of the probabilities is done: the row is reused for the partial sums
+    if (part < parts) sc[part * p.hd + c] = acc;
+    __syncthreads();
+    if (tid < p.hd) {
+        float v = 0.f;
+        for (int q = 0; q < parts; ++q) v += sc[q * p.hd + tid];
+        p.out[(size_t)t * p.Hq * p.hd + (size_t)hq * p.hd + tid] = v / sum;
+    }
+}
+
+}  // namespace
+}  // namespace gptrs

@@ -1085,6 +1085,79 @@ int gptrs_cuda_execute_instruction(const char* instruction_json, size_t len, gpt
     return gptrs_cuda_run_program(text.data(), text.size(), args.data(), args.size(), outputs, outputs_cap, n_outputs, stream);
 }
 
+namespace {
+
+Json jnum(double v) { Json j; j.kind = Json::Number; j.num = v; return j; }
+Json jstr(const std::string& v) { Json j; j.kind = Json::String; j.str = v; return j; }
+Json jobj(std::vector<std::pair<std::string, Json>> kv) { Json j; j.kind = Json::Object; j.obj = std::move(kv); return j; }
+Json jarr(std::vector<Json> v) { Json j; j.kind = Json::Array; j.arr = std::move(v); return j; }
+
+Json tensor_spec_json(const TSpec& t) {
+    static const char* const kNames[] = {"F32", "F16", "Bf16", "Si32", "I1", "Si8", "Ui8"};  // gptrs_dtype order
+    std::vector<Json> dims;
+    for (int64_t d : t.dims) dims.push_back(jobj({{"Static", jnum((double)d)}}));
+    return jobj({{"dtype", jstr(kNames[t.dtype])}, {"shape", jobj({{"dims", jarr(std::move(dims))}})}});
+}
+
+// A fused operation as the CustomCall instruction the reference's rewriters would insert (docs/backend.md:568-592).
+Json fused_instruction_json(const Inst& in) {
+    std::vector<Json> operands;
+    for (const Operand& o : in.operands) {
+        if (!o.is_literal) { operands.push_back(jobj({{"Value", jnum(o.id)}})); continue; }
+        std::vector<Json> bytes;
+        for (uint8_t b : o.bytes) bytes.push_back(jnum(b));
+        operands.push_back(jobj({{"Literal", jobj({{"spec", tensor_spec_json(o.lit)}, {"bytes", jarr(std::move(bytes))}})}}));
+    }
+    std::vector<std::pair<std::string, Json>> attrs;
+    if (in.op == Op::FusedLayerNorm || in.op == Op::FusedRmsNorm) attrs.push_back({"eps", jobj({{"F64", jnum((double)in.f0)}})});
+    if (in.op == Op::FusedAttentionDecode) {
+        std::vector<Json> g;
+        for (int64_t v : in.a) g.push_back(jnum((double)v));
+        attrs.push_back({"geometry", jobj({{"I64Array", jarr(std::move(g))}})});
+    }
+    Json call = jobj({{"CustomCall", jobj({{"target", jstr(fused_target(in.op))}, {"attrs", jobj(std::move(attrs))}})}});
+    return jobj({{"id", jnum(in.id)}, {"op", std::move(call)}, {"operands", jarr(std::move(operands))},
+                 {"output", jobj({{"Tensor", tensor_spec_json(in.out)}})}});
+}
+
+}  // namespace
+
+int gptrs_cuda_pipeline_fuse(const char* program_json, size_t len, char* out, size_t out_cap, size_t* written, int64_t* n_fused) {
+    GPTRS_REQUIRE(program_json && written, "null pointer");
+    Json root;
+    std::string err;
+    if (!parse_json(program_json, len, &root, &err)) return fail(GPTRS_SPEC_VIOLATION, "program json: " + err);
+    Plan plan;
+    int st = build_function(root, &plan.fn, &err);
+    if (st) return fail(st == 2 ? GPTRS_UNIMPLEMENTED : GPTRS_SPEC_VIOLATION, err);
+    rewrite(plan);
+    // the entry function's body: surviving instructions as they were, fused ones as CustomCalls, in the old order
+    const std::string entry = root.get("entry")->str;
+    for (auto& kv : root.obj) {
+        if (kv.first != "functions") continue;
+        for (Json& f : kv.second.arr) {
+            const Json* name = f.get("name");
+            if (!name || name->str != entry) continue;
+            for (auto& fkv : f.obj) {
+                if (fkv.first != "body") continue;
+                std::vector<Json> body;
+                for (const Inst& in : plan.fn.body) {
+                    if (in.dead) continue;
+                    if (fused_target(in.op)) body.push_back(fused_instruction_json(in));
+                    else body.push_back(fkv.second.arr[in.src]);
+                }
+                fkv.second.arr = std::move(body);
+            }
+        }
+    }
+    std::string text;
+    write_json(root, &text);
+    *written = text.size();
+    if (n_fused) *n_fused = plan.fused;
+    if (out && out_cap >= text.size()) memcpy(out, text.data(), text.size());
+    return GPTRS_OK;
+}
+
 int gptrs_cuda_run_program_stats(int64_t* plan_builds, int64_t* plan_hits, int64_t* last_launches, int64_t* last_fused) {
     if (plan_builds) *plan_builds = g_plan_builds;
     if (plan_hits) *plan_hits = g_plan_hits;

@@ -1,6 +1,8 @@
 // JSON reader + PTIR program model (see ptir_json.h).
 #include "ptir_json.h"
 
+#include <cstdio>
+
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -155,6 +157,57 @@ bool parse_json(const char* text, size_t len, Json* out, std::string* err) {
     return true;
 }
 
+void write_json(const Json& j, std::string* out) {
+    switch (j.kind) {
+        case Json::Null: *out += "null"; break;
+        case Json::Bool: *out += j.b ? "true" : "false"; break;
+        case Json::Number: {
+            char buf[40];
+            if (j.num == (double)(int64_t)j.num && j.num > -9.0e15 && j.num < 9.0e15) snprintf(buf, sizeof buf, "%lld", (long long)j.num);
+            else snprintf(buf, sizeof buf, "%.17g", j.num);
+            *out += buf;
+            break;
+        }
+        case Json::String: {
+            *out += '"';
+            for (unsigned char c : j.str) {
+                if (c == '"' || c == '\\') { *out += '\\'; *out += (char)c; }
+                else if (c < 0x20) { char buf[8]; snprintf(buf, sizeof buf, "\\u%04x", c); *out += buf; }
+                else *out += (char)c;
+            }
+            *out += '"';
+            break;
+        }
+        case Json::Array:
+            *out += '[';
+            for (size_t i = 0; i < j.arr.size(); ++i) { if (i) *out += ','; write_json(j.arr[i], out); }
+            *out += ']';
+            break;
+        case Json::Object:
+            *out += '{';
+            for (size_t i = 0; i < j.obj.size(); ++i) {
+                if (i) *out += ',';
+                Json k; k.kind = Json::String; k.str = j.obj[i].first;
+                write_json(k, out);
+                *out += ':';
+                write_json(j.obj[i].second, out);
+            }
+            *out += '}';
+            break;
+    }
+}
+
+const char* fused_target(Op op) {
+    switch (op) {
+        case Op::FusedLayerNorm: return "gpt_rs.cuda.layer_norm.f32.v1";
+        case Op::FusedRmsNorm: return "gpt_rs.cuda.rms_norm.f32.v1";
+        case Op::FusedSoftmax: return "gpt_rs.cuda.softmax_last_axis.f32.v1";
+        case Op::FusedMatmulBias: return "gpt_rs.cuda.matmul_bias.f32.v1";
+        case Op::FusedAttentionDecode: return "gpt_rs.cuda.attention_decode.f32.v1";
+        default: return nullptr;
+    }
+}
+
 int build_function(const Json& program, Function* fn, std::string* err) {
     const Json* ver = program.get("spec_version");
     if (ver && ver->str != "ptir.v0.4") { *err = "unsupported PTIR spec version '" + ver->str + "'"; return 1; }
@@ -252,8 +305,31 @@ int build_function(const Json& program, Function* fn, std::string* err) {
             const Json* acc = attr->get("accum_dtype");
             if (acc && acc->kind == Json::String && acc->str != "F32") in.f0 = 1.f;  // refused at run time like the reference
         }
-        else if (n == "CustomCall") { in.op = Op::CustomCall; in.sub = attr->get("target") ? attr->get("target")->str : ""; }
+        else if (n == "CustomCall") {
+            in.op = Op::CustomCall;
+            in.sub = attr->get("target") ? attr->get("target")->str : "";
+            // the targets written by this backend's own fusion pipeline come back as the fused operations
+            const Json* attrs = attr->get("attrs");
+            for (Op f : {Op::FusedLayerNorm, Op::FusedRmsNorm, Op::FusedSoftmax, Op::FusedMatmulBias, Op::FusedAttentionDecode}) {
+                if (in.sub != fused_target(f)) continue;
+                const size_t want = f == Op::FusedLayerNorm || f == Op::FusedMatmulBias ? 3 : f == Op::FusedRmsNorm ? 2 : f == Op::FusedSoftmax ? 1 : 4;
+                if (in.operands.size() != want) { *err = in.sub + ": wrong operand count"; return 1; }
+                in.op = f;
+                if (f == Op::FusedLayerNorm || f == Op::FusedRmsNorm) {
+                    const Json* e = attrs ? attrs->get("eps") : nullptr;
+                    const Json* v = e ? e->get("F64") : nullptr;
+                    if (!v || v->kind != Json::Number) { *err = in.sub + ": attribute eps (F64) is required"; return 1; }
+                    in.f0 = (float)v->num;
+                }
+                if (f == Op::FusedAttentionDecode) {
+                    const Json* g = attrs ? attrs->get("geometry") : nullptr;
+                    read_ints(g ? g->get("I64Array") : nullptr, &in.a);
+                    if (in.a.size() != 4) { *err = in.sub + ": attribute geometry (I64Array of q heads, kv heads, head_dim, capacity) is required"; return 1; }
+                }
+            }
+        }
         else in.op = Op::Unsupported;
+        in.src = (int)fn->body.size();
         fn->body.push_back(std::move(in));
     }
     return 0;

@@ -29,6 +29,8 @@ struct Json {
 
 // Returns false and fills `err` on malformed input.
 bool parse_json(const char* text, size_t len, Json* out, std::string* err);
+// Compact text of a tree (numbers that hold an integer are written without a fraction).
+void write_json(const Json& j, std::string* out);
 
 enum class Op {
     Constant, Unary, Binary, DotGeneral, Reduce, Compare, Select, Cast, StopGradient, Reshape, Transpose, BroadcastTo,
@@ -63,6 +65,7 @@ struct Inst {
     std::vector<Operand> operands;
     TSpec out;
     bool dead = false;            // removed by a rewrite
+    int src = -1;                 // index of the instruction in the function body it was read from
 };
 
 struct Function {
@@ -73,6 +76,10 @@ struct Function {
 
 // Builds the entry function. status: 0 ok, 1 spec violation, 2 unimplemented.
 int build_function(const Json& program, Function* fn, std::string* err);
+
+// CustomCall targets the fusion pipeline of this backend emits and run_program accepts (docs/backend.md:568-592:
+// namespaced and versioned).
+const char* fused_target(Op op);
 
 }  // namespace ptir
 }  // namespace gptrs

@@ -419,6 +419,15 @@ int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* c
  * same executor as run_program, so the supported operations and the error kinds are the same. */
 int gptrs_cuda_execute_instruction(const char* instruction_json, size_t len, gptrs_tensor* const* inputs, size_t n_inputs,
                                    gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs, void* stream);
+/* The fuse phase of PortableBackend::pipeline() (crates/gpt-rs/src/backend/pipeline.rs:60-65, hooks of
+ * BackendPipeline::populate_fuse) as a text-to-text pass: the entry function of `program_json` comes back with the
+ * layer_norm, rms_norm, softmax, matmul+bias and decode-attention subgraphs replaced by CustomCall instructions whose
+ * targets are gpt_rs.cuda.{layer_norm,rms_norm,softmax_last_axis,matmul_bias,attention_decode}.f32.v1 (attrs: eps as
+ * F64; geometry as I64Array of q heads, kv heads, head_dim, capacity); instructions nothing uses any more are dropped,
+ * values that escape a subgraph keep their producers. run_program accepts these targets. Host only, no CUDA call.
+ * *written is the length of the result; it is copied to `out` only when out_cap is large enough (call once with
+ * out = NULL to size the buffer). n_fused (optional) receives the number of rewrites. */
+int gptrs_cuda_pipeline_fuse(const char* program_json, size_t len, char* out, size_t out_cap, size_t* written, int64_t* n_fused);
 int gptrs_cuda_run_program_stats(int64_t* plan_builds, int64_t* plan_hits, int64_t* last_launches, int64_t* last_fused);
 /* Turns the fusion rewrites of run_program on (default) or off (GPTRS_OPT-style switch for tests). */
 int gptrs_cuda_set_fusion(int enabled);

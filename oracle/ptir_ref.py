@@ -230,7 +230,35 @@ def execute_instruction(op, ins, out_spec):
         return base
     if kind == "StopGradient":
         return ins[0]
+    if kind == "CustomCall":
+        return _cuda_custom_call(attr, ins, out_dims)
     raise PtirError(f"unsupported operation {kind}")
+
+
+def _cuda_custom_call(attr, ins, out_dims):
+    """The CustomCall targets written by the cuda backend's fuse phase, by their closed forms (the functionals the
+    replaced subgraphs were captured from: normalization.rs:123-217, activation.rs:77-89, linear.rs:50-71,
+    attention.rs:657-779). Any other target is unknown, as docs/backend.md:581-582 requires."""
+    from . import functional_ref as fr
+    target, attrs = attr["target"], attr.get("attrs", {})
+    if target == "gpt_rs.cuda.layer_norm.f32.v1":
+        return fr.layer_norm(ins[0], ins[1], ins[2], np.float32(attrs["eps"]["F64"]))[0]
+    if target == "gpt_rs.cuda.rms_norm.f32.v1":
+        return fr.rms_norm(ins[0], ins[1], np.float32(attrs["eps"]["F64"]))[0]
+    if target == "gpt_rs.cuda.softmax_last_axis.f32.v1":
+        return fr.softmax_last_dim(ins[0])
+    if target == "gpt_rs.cuda.matmul_bias.f32.v1":
+        return fr.linear(ins[0], ins[1], ins[2])
+    if target == "gpt_rs.cuda.attention_decode.f32.v1":
+        hq, hkv, hd, cap = attrs["geometry"]["I64Array"]
+        q, k, v = ins[0].reshape(hq, 1, hd), ins[1], ins[2]
+        qpos = min(max(int(ins[3][0]), 0), cap - 1)   # DynamicSlice start clamping of the mask it replaces
+        kg, vg = np.repeat(k, hq // hkv, axis=0), np.repeat(v, hq // hkv, axis=0)
+        scores = np.einsum("hqd,hkd->hqk", q, kg).astype(np.float32) * np.float32(1.0 / math.sqrt(hd))
+        mask = np.where(qpos >= np.arange(cap), np.float32(0.0), np.float32(-1e9)).astype(np.float32)
+        p = fr.softmax_last_dim((scores + mask[None, None, :]).astype(np.float32))
+        return np.einsum("hqk,hkd->hqd", p, vg).astype(np.float32).reshape(out_dims)
+    raise PtirError(f"unknown custom_call target {target}")
 
 
 def run_program(program: dict, inputs: list[np.ndarray]) -> list[np.ndarray]:

@@ -163,3 +163,80 @@ def test_reduce_window_refusals():
     b.set_results([x.reduce_window("Max", [2, 2, 1], [2, 2, 1], [(0, 0)] * 3)])
     with pytest.raises(pr.PtirError):  # only rank-4 tensors (cpu.rs:1970-1975)
         _run(b, [np.zeros((4, 4, 2), np.float32)])
+
+
+def _decode_program(kind):
+    if kind == "gpt":
+        cfg = mr.Cfg("gpt", n_layers=2, d_model=64, n_q=4, n_kv=4, hd=16, d_mlp=128, vocab=96, ctx=32)
+    else:
+        cfg = mr.Cfg("ministral", n_layers=2, d_model=64, n_q=4, n_kv=2, hd=16, d_mlp=128, vocab=96, ctx=32, rot=16, theta=1e4)
+    params = mr.random_params(cfg, seed=3, std=0.3)
+    pos, cap = 5, 8
+    b, names = ptir.decode_step_program(cfg, cap)
+    rng = np.random.default_rng(0)
+    cos, sin = fr.rotary_cos_sin(pos, 1, max(cfg.rot, 2), cfg.theta)
+    feed = {"@tokens": np.array([9], np.int32), "@positions": np.array([pos], np.int32), "@cos": cos, "@sin": sin,
+            "@update_starts": np.array([0, pos, 0], np.int32), "@query_start": np.array([pos], np.int32)}
+    for l in range(cfg.n_layers):
+        feed[f"@k{l}"] = rng.uniform(-1, 1, size=(cfg.n_kv, cap, cfg.hd)).astype(np.float32)
+        feed[f"@v{l}"] = rng.uniform(-1, 1, size=(cfg.n_kv, cap, cfg.hd)).astype(np.float32)
+    return cfg, b, [feed[n] if n in feed else params[n] for n in names]
+
+
+@pytest.mark.parametrize("kind", ["gpt", "ministral"])
+def test_pipeline_fuse_rewrites_to_custom_calls(kind):
+    """The backend's fuse phase as a text-to-text pass (host only): the rewritten decode-step program holds namespaced,
+    versioned CustomCalls in place of the norm / softmax / bias / decode-attention subgraphs, is much shorter, and the
+    interpreter gives the same results for both texts."""
+    from gptrs_b200 import backend
+    cfg, b, inputs = _decode_program(kind)
+    text = b.to_json()
+    fused_text, n_fused = backend.pipeline_fuse(text)
+    before, after = json.loads(text), json.loads(fused_text)
+    assert n_fused >= 4 * cfg.n_layers + 1
+    body0, body1 = before["functions"][0]["body"], after["functions"][0]["body"]
+    assert len(body1) < len(body0) * 6 // 10  # 257 -> 135 instructions for the two-layer Ministral step (RoPE stays op by op)
+    targets = [i["op"]["CustomCall"]["target"] for i in body1 if isinstance(i["op"], dict) and "CustomCall" in i["op"]]
+    # each layer's softmax rewrite is absorbed by the attention rewrite that follows it
+    assert len(targets) == n_fused - cfg.n_layers and all(t.startswith("gpt_rs.cuda.") and t.endswith(".f32.v1") for t in targets)
+    assert targets.count("gpt_rs.cuda.attention_decode.f32.v1") == cfg.n_layers
+    norm = "gpt_rs.cuda.layer_norm.f32.v1" if kind == "gpt" else "gpt_rs.cuda.rms_norm.f32.v1"
+    assert targets.count(norm) == 2 * cfg.n_layers + 1
+    for k in ("spec_version", "entry", "regions"):
+        assert after[k] == before[k]
+    f0, f1 = before["functions"][0], after["functions"][0]
+    assert all(f1[k] == f0[k] for k in f0 if k != "body")
+    # surviving instructions are the original ones, in the original order
+    ids0 = [i["id"] for i in body0]
+    kept = [i for i in body1 if not (isinstance(i["op"], dict) and "CustomCall" in i["op"])]
+    assert all(i in body0 for i in kept) and [i["id"] for i in body1] == [x for x in ids0 if x in {i["id"] for i in body1}]
+    want, got = pr.run_program(before, inputs), pr.run_program(after, inputs)
+    assert len(want) == len(got)
+    for w, g in zip(want, got):
+        assert np.allclose(w, g, rtol=1e-5, atol=1e-5)
+    # a second pass finds nothing left to fuse and keeps the text
+    again, n2 = backend.pipeline_fuse(fused_text)
+    assert n2 == 0 and json.loads(again) == after
+
+
+def test_pipeline_fuse_keeps_escaping_values_and_rejects_bad_input():
+    from gptrs_b200 import BackendError, backend
+    b = ptir.Builder()
+    px, pg = b.parameter(F32, [3, 32]), b.parameter(F32, [32])
+    out = ptir.rms_norm(px, pg, 1e-5)
+    inner = ptir.Value(b, b.body[-1]["operands"][0]["Value"], F32, [3, 32])  # the un-scaled normalized value escapes
+    b.set_results([out, inner])
+    fused_text, n = backend.pipeline_fuse(b.to_json())
+    after = json.loads(fused_text)
+    assert n == 1 and any(i["id"] == inner.id for i in after["functions"][0]["body"])
+    x = np.random.default_rng(1).uniform(-1, 1, size=(3, 32)).astype(np.float32)
+    g = np.random.default_rng(2).uniform(-1, 1, size=32).astype(np.float32)
+    for w, gt in zip(_run(b, [x, g]), pr.run_program(after, [x, g])):
+        assert np.allclose(w, gt, atol=1e-6)
+    with pytest.raises(BackendError):
+        backend.pipeline_fuse("{not json")
+    with pytest.raises(pr.PtirError):
+        bb = ptir.Builder()
+        p = bb.parameter(F32, [4])
+        bb.set_results([bb.custom_call("gpt_rs.someone_else.op.v1", [p], F32, [4])])
+        _run(bb, [np.zeros(4, np.float32)])

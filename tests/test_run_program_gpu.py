@@ -287,3 +287,43 @@ def test_execute_instruction(be):
         be.execute_instruction(by_id[dot.id], [hw, ha])  # contracting sizes differ
     with pytest.raises(BackendError):
         be.execute_instruction("{broken", [])
+
+
+@pytest.mark.parametrize("kind", ["gpt", "ministral"])
+def test_run_program_accepts_the_fuse_phase_output(be, kind):
+    """pipeline() hook form: the program rewritten by gptrs_cuda_pipeline_fuse (CustomCall targets gpt_rs.cuda.*.f32.v1)
+    runs with fusion off (nothing left to match) and gives the logits of the original program within 1e-4."""
+    if kind == "gpt":
+        cfg = mr.Cfg("gpt", n_layers=2, d_model=64, n_q=4, n_kv=4, hd=16, d_mlp=128, vocab=96, ctx=32)
+    else:
+        cfg = mr.Cfg("ministral", n_layers=2, d_model=64, n_q=4, n_kv=2, hd=16, d_mlp=128, vocab=96, ctx=32, rot=16, theta=1e4)
+    params = mr.random_params(cfg, seed=5, std=0.3)
+    pos, cap = 6, 8
+    b, names = ptir.decode_step_program(cfg, cap)
+    rng = np.random.default_rng(4)
+    cos, sin = fr.rotary_cos_sin(pos, 1, max(cfg.rot, 2), cfg.theta)
+    feed = {"@tokens": np.array([11], np.int32), "@positions": np.array([pos], np.int32), "@cos": cos, "@sin": sin,
+            "@update_starts": np.array([0, pos, 0], np.int32), "@query_start": np.array([pos], np.int32)}
+    for l in range(cfg.n_layers):
+        feed[f"@k{l}"] = rng.uniform(-1, 1, size=(cfg.n_kv, cap, cfg.hd)).astype(np.float32)
+        feed[f"@v{l}"] = rng.uniform(-1, 1, size=(cfg.n_kv, cap, cfg.hd)).astype(np.float32)
+    inputs = [feed[n] if n in feed else params[n] for n in names]
+    text = b.to_json()
+    fused_text, n_fused = be.pipeline_fuse(text)
+    assert n_fused >= 4 * cfg.n_layers + 1
+    want = pr.run_program(json.loads(text), inputs)
+    hs = [be.materialize(a) for a in inputs]
+    for fusion in (False, True):
+        be.set_fusion(fusion)
+        got = [be.to_literal(h) for h in be.run_program(fused_text, hs)]
+        st = be.run_program_stats()
+        assert st["last_fused"] == 0  # the text already holds the fused operations
+        assert len(got) == len(want)
+        for a, e in zip(got, want):
+            assert np.allclose(a, e, rtol=1e-4, atol=1e-4)
+    launches_fused = be.run_program_stats()["last_launches"]
+    be.set_fusion(False)
+    be.run_program(text, hs)
+    launches_plain = be.run_program_stats()["last_launches"]
+    assert launches_fused < launches_plain * 7 // 10, (launches_fused, launches_plain)
+    be.set_fusion(True)
