@@ -316,3 +316,43 @@ def attention_decode_f32(qkv, k_cache, v_cache, positions, slot, n_q, n_kv, head
     check(fn(_ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(slot), _ptr(out), t, n_q, n_kv, head_dim,
              k_cache.shape[2], _stream()))
     return out
+
+
+def apply_rope(x, cos, sin):
+    """functional::apply_rope on x[heads, seq, head_dim] with cos / sin [seq, rotary_dim / 2]."""
+    heads, seq, hd = x.shape
+    out = torch.empty_like(x)
+    check(lib().gptrs_cuda_apply_rope_f32(_ptr(x), _ptr(cos), _ptr(sin), _ptr(out), heads, seq, hd, cos.shape[1], _stream()))
+    return out
+
+
+def apply_rope_qkv_packed(qkv, cos, sin, n_q, n_kv, head_dim):
+    out = torch.empty_like(qkv)
+    check(lib().gptrs_cuda_apply_rope_qkv_packed_f32(_ptr(qkv), _ptr(cos), _ptr(sin), _ptr(out), qkv.shape[0], n_q, n_kv, head_dim,
+                                                     cos.shape[1], _stream()))
+    return out
+
+
+def attention_f32(qkv, n_q, n_kv, head_dim, cache_k=None, cache_v=None):
+    """functional::attention: returns (out [seq, n_q*head_dim], present K, present V [n_kv, cache_len+seq, head_dim])."""
+    seq = qkv.shape[0]
+    l0 = 0 if cache_k is None else cache_k.shape[1]
+    out = torch.empty(seq, n_q * head_dim, dtype=torch.float32, device=qkv.device)
+    k = torch.empty(n_kv, l0 + seq, head_dim, dtype=torch.float32, device=qkv.device)
+    v = torch.empty_like(k)
+    check(lib().gptrs_cuda_attention_f32(_ptr(qkv), _ptr(cache_k), _ptr(cache_v), l0, _ptr(out), _ptr(k), _ptr(v), seq, n_q, n_kv,
+                                         head_dim, _stream()))
+    return out, k, v
+
+
+def dequantize_w4(q, scales, n, k, transposed=False):
+    """Canonical W4 (q uint8 [n, k/2], scales fp16 [n, k/128]) -> f32 [k, n] (Linear layout) or [n, k]."""
+    w = torch.empty((n, k) if transposed else (k, n), dtype=torch.float32, device=q.device)
+    check(lib().gptrs_cuda_dequantize_w4(_ptr(q), _ptr(scales), k, n, int(transposed), _ptr(w), _stream()))
+    return w
+
+
+def dequantize_w8(q, scales, n, k, transposed=False):
+    w = torch.empty((n, k) if transposed else (k, n), dtype=torch.float32, device=q.device)
+    check(lib().gptrs_cuda_dequantize_w8(_ptr(q), _ptr(scales), k, n, int(transposed), _ptr(w), _stream()))
+    return w

@@ -93,6 +93,14 @@ int gptrs_cuda_quantize_w4(const float* d_w, int64_t k, int64_t n, int transpose
 int gptrs_cuda_quantize_w8(const float* d_w, int64_t k, int64_t n, int transposed, int8_t* d_q,
                            uint16_t* d_scales, void* stream);
 
+/* Dequantize (spec.rs:577-596; the scheme is the backend's): canonical W4 / W8 back to f32, q * scale, written
+ * in the Linear layout [K][N] or, with `transposed` != 0, as [N][K]. Exact (an int4 / int8 times an fp16 scale is
+ * representable in f32). */
+int gptrs_cuda_dequantize_w4(const uint8_t* d_q, const uint16_t* d_scales, int64_t k, int64_t n, int transposed, float* d_w,
+                             void* stream);
+int gptrs_cuda_dequantize_w8(const int8_t* d_q, const uint16_t* d_scales, int64_t k, int64_t n, int transposed, float* d_w,
+                             void* stream);
+
 /* Epilogue selector for the quantised matmuls. */
 typedef struct {
     int out_dtype;            /* GPTRS_BF16 or GPTRS_F32 */
@@ -295,6 +303,20 @@ int gptrs_cuda_attention_decode_f32(const float* d_qkv, const float* d_k_cache, 
                                     const int32_t* d_positions, const int32_t* d_slot, float* d_out,
                                     int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
                                     int64_t capacity, void* stream);
+/* functional::apply_rope (crates/gpt-rs/src/ops/functional/rotary.rs:289-336) on x[heads][seq][head_dim] and
+ * apply_rope_qkv_packed (rotary.rs:430-536) on packed rows [seq][q|k|v]: half-split rotation of the first
+ * 2 * rotary_half channels of every Q and K head with cos / sin [seq][rotary_half]; other channels and V pass
+ * through. d_out may equal the input. */
+int gptrs_cuda_apply_rope_f32(const float* d_x, const float* d_cos, const float* d_sin, float* d_out, int64_t heads, int64_t seq,
+                              int64_t head_dim, int64_t rotary_half, void* stream);
+int gptrs_cuda_apply_rope_qkv_packed_f32(const float* d_qkv, const float* d_cos, const float* d_sin, float* d_out, int64_t seq,
+                                         int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim, int64_t rotary_half, void* stream);
+/* functional::attention (crates/gpt-rs/src/ops/functional/attention.rs:337-541): packed rows [seq][q|k|v], an optional
+ * cache [kv_heads][cache_len][head_dim] in front, causal attention of row t over positions 0..cache_len+t; writes
+ * d_out [seq][q_heads*head_dim] and the present K / V [kv_heads][cache_len+seq][head_dim]. cache_len + seq <= 32768. */
+int gptrs_cuda_attention_f32(const float* d_qkv, const float* d_cache_k, const float* d_cache_v, int64_t cache_len, float* d_out,
+                             float* d_k_out, float* d_v_out, int64_t seq, int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim,
+                             void* stream);
 /* Both in one launch, for decode steps whose tokens belong to DISTINCT sequences (a token's row is written by
  * the CTAs that read it; a second token of the same sequence in the launch would race with that write). */
 int gptrs_cuda_kv_append_attention_decode_f32(const float* d_qkv, float* d_k_cache, float* d_v_cache,

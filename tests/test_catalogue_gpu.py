@@ -129,3 +129,87 @@ def test_attention_layer_prefill_then_decode_equals_full(cuda, kind, embed, head
     for i in range(4, 7):
         lg, _ = m.forward_with_decode_cache([tokens[i]], [0], [i], [0])
         assert np.allclose(lg[0], full[i], rtol=RTOL, atol=ATOL)
+
+
+def _t(a, cuda):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+@pytest.mark.parametrize("seq,embed,heads,kv,seed", [(4, 6, 3, 3, 555), (3, 8, 4, 2, 777), (1, 8, 2, 2, 600), (8, 32, 4, 4, 601),
+                                                     (4, 4, 4, 4, 602), (8, 32, 8, 1, 603), (8, 32, 8, 2, 604), (40, 256, 2, 1, 9)])
+def test_attention_functional(cuda, seq, embed, heads, kv, seed):
+    """functional::attention against the oracle for the torch-parity geometries (attention.rs:189-278, 433-453: head_dim 1,
+    MQA, GQA), no cache: out and the exported K / V."""
+    from gptrs_b200 import ops
+    from oracle import functional_ref as fr
+    hd = embed // heads
+    qkv = _u(np.random.default_rng(seed), seq, (heads + 2 * kv) * hd)
+    out, k, v = ops.attention_f32(_t(qkv, cuda), heads, kv, hd)
+    want, wk, wv = fr.attention_prefill(qkv, heads, kv, hd)
+    assert np.allclose(out.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    assert np.array_equal(k.cpu().numpy(), wk) and np.array_equal(v.cpu().numpy(), wv)
+
+
+@pytest.mark.parametrize("heads,kv,seed", [(4, 4, 605), (8, 2, 606)])
+def test_attention_functional_cache_append_equals_full(cuda, heads, kv, seed):
+    """attention.rs:280-431, 455-465: a 4-token prefill, then three single-token calls that extend the returned cache,
+    give the rows of one 7-token call; the cache grows by one row per step."""
+    from gptrs_b200 import ops
+    from oracle import functional_ref as fr
+    embed = 32
+    hd = embed // heads
+    qkv = _u(np.random.default_rng(seed), 7, (heads + 2 * kv) * hd)
+    full, fk, fv = fr.attention_prefill(qkv, heads, kv, hd)
+    d = _t(qkv, cuda)
+    out, k, v = ops.attention_f32(d[:4].contiguous(), heads, kv, hd)
+    rows = [out.cpu().numpy()]
+    for t in range(4, 7):
+        out, k, v = ops.attention_f32(d[t:t + 1].contiguous(), heads, kv, hd, cache_k=k, cache_v=v)
+        assert tuple(k.shape) == (kv, t + 1, hd)
+        rows.append(out.cpu().numpy())
+    assert np.allclose(np.concatenate(rows), full, rtol=RTOL, atol=ATOL)
+    assert np.array_equal(k.cpu().numpy(), fk) and np.array_equal(v.cpu().numpy(), fv)
+    # a multi-token extension in one call
+    out2, k2, _ = ops.attention_f32(d[4:].contiguous(), heads, kv, hd, cache_k=_t(fk[:, :4], cuda), cache_v=_t(fv[:, :4], cuda))
+    assert np.allclose(out2.cpu().numpy(), full[4:], rtol=RTOL, atol=ATOL) and np.array_equal(k2.cpu().numpy(), fk)
+
+
+@pytest.mark.parametrize("heads,seq,hd,rot,seed", [(4, 9, 16, 16, 0x7010), (3, 7, 24, 16, 0x7011), (2, 5, 8, 4, 1)])
+def test_rope_functionals(cuda, heads, seq, hd, rot, seed):
+    """rotary_ops.rs:82-88: full and partial rotary width, theta 1e4; the packed form rotates Q and K heads and leaves V."""
+    from gptrs_b200 import ops
+    from oracle import functional_ref as fr
+    rng = np.random.default_rng(seed)
+    x = _u(rng, heads, seq, hd)
+    cos, sin = fr.rotary_cos_sin(0, seq, rot, 1e4)
+    got = ops.apply_rope(_t(x, cuda), _t(cos, cuda), _t(sin, cuda)).cpu().numpy()
+    assert np.allclose(got, fr.apply_rope(x, cos, sin), rtol=RTOL, atol=1e-6)
+    n_kv = 1 if heads % 2 else 2
+    qkv = _u(rng, seq, (heads + 2 * n_kv) * hd)
+    got = ops.apply_rope_qkv_packed(_t(qkv, cuda), _t(cos, cuda), _t(sin, cuda), heads, n_kv, hd).cpu().numpy()
+    want = fr.apply_rope_qkv_packed(qkv, cos, sin, heads, n_kv, hd)
+    assert np.allclose(got, want, rtol=RTOL, atol=1e-6)
+    assert np.array_equal(got[:, (heads + n_kv) * hd:], qkv[:, (heads + n_kv) * hd:])
+
+
+def test_dequantize_is_exact(cuda):
+    """Dequantize of the backend-defined W4 group-128 / W8 per-channel formats: bit-equal to the oracle, both layouts."""
+    from gptrs_b200 import ops
+    from oracle import quant_ref as qr
+    rng = np.random.default_rng(12)
+    n, k = 48, 384
+    w = rng.normal(0, 0.05, size=(n, k)).astype(np.float32)
+    q4, s4 = qr.quantize_w4(w)
+    q8, s8 = qr.quantize_w8(w)
+    for transposed in (False, True):
+        got4 = ops.dequantize_w4(_t(q4, cuda), _t(s4, cuda), n, k, transposed).cpu().numpy()
+        got8 = ops.dequantize_w8(_t(q8, cuda), _t(s8, cuda), n, k, transposed).cpu().numpy()
+        w4, w8 = qr.dequant_w4(q4, s4), qr.dequant_w8(q8, s8)
+        assert np.array_equal(got4, w4 if transposed else w4.T) and np.array_equal(got8, w8 if transposed else w8.T)
+    # quantise on the device, dequantise on the device: the round trip stays within half a step of every group
+    import torch
+    dq, ds = ops.quantize_w4(_t(w.T.copy(), cuda))
+    back = ops.dequantize_w4(dq, ds, n, k, transposed=True).cpu().numpy()
+    step = np.repeat(ds.cpu().numpy().view(np.float16).astype(np.float32).reshape(n, k // 128), 128, axis=1)
+    assert (np.abs(back - w) <= 0.5 * step + 1e-7).all()
