@@ -139,6 +139,63 @@ def time_ministral_step_sample(lib, batch=64, ctx_len=2048, n_layers_total=26, s
                        f"(context {ctx_len}, capacity bucket {cap}), single thread, extrapolated linearly to the step")
 
 
+def _parallel_worker(lib, state, kw, reps, start, out_q):
+    """Child of time_ministral_step_parallel: the inherited state is shared copy-on-write; only the activations and
+    the cache rows this process writes become private pages. A barrier before every repetition keeps the
+    processes in step, so that each repetition is measured with all of them running."""
+    vals = []
+    for _ in range(reps):
+        start.wait(timeout=300)  # a broken barrier ends the child instead of leaving it waiting
+        r = time_ministral_step_sample(lib, state=state, **kw)
+        vals.append(1.0 / r["tokens_per_s"])  # seconds per sequence-step
+    out_q.put(vals)
+
+
+def host_processes(limit: int = 64) -> int:
+    """Processes the CPU arm runs at once: the cores this process may use, at most `limit`."""
+    import os
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(1, min(n, limit))
+
+
+def time_ministral_step_parallel(lib, procs: int, reps: int = 3, **kw):
+    """The same bounded sample as time_ministral_step_sample, run by `procs` processes at once: requests are
+    independent, so the host's cores are used the way the GPUs are, one share of the batch each, every process
+    running the reference's single-threaded kernels. The weights (and the library's packed copies) are built once
+    and inherited by fork. `rep_tokens_per_s[i]` is the whole host's tokens/s in repetition i = sum over processes
+    of 1 / (seconds per sequence-step); the first repetition also pays the page faults of a fresh child.
+    `tokens_per_s` is the mean over the repetitions after the first."""
+    import multiprocessing as mp
+    first = time_ministral_step_sample(lib, **kw)  # builds and packs the weights in this process (or reuses kw['state'])
+    if procs <= 1:
+        res = dict(first)
+        res["rep_tokens_per_s"] = [first["tokens_per_s"]] + [time_ministral_step_sample(lib, **{**kw, "state": first["state"]})["tokens_per_s"]
+                                                               for _ in range(reps - 1)]
+        return res
+    ctx = mp.get_context("fork")
+    start, q = ctx.Barrier(procs), ctx.Queue()
+    child_kw = {k: v for k, v in kw.items() if k != "state"}
+    ps = [ctx.Process(target=_parallel_worker, args=(lib, first["state"], child_kw, reps, start, q)) for _ in range(procs)]
+    for p in ps:
+        p.start()
+    try:
+        per_proc = [q.get(timeout=600) for _ in ps]
+    finally:
+        for p in ps:
+            p.join(timeout=5)
+            if p.is_alive():
+                p.terminate()
+    per_rep = [float(sum(1.0 / v[i] for v in per_proc)) for i in range(reps)]
+    steady = per_rep[1:] or per_rep
+    res = dict(first)
+    res.update(tokens_per_s=sum(steady) / len(steady), rep_tokens_per_s=per_rep, cores=procs,
+               sample=first["sample"].replace("single thread", f"{procs} processes at once (one share of the batch each, the reference's kernels are single-threaded)"))
+    return res
+
+
 def time_gpt2_decode(lib, n_tokens: int = 4, ctx_start: int = 32, n_layers: int = 12, d_model: int = 768, n_heads: int = 12,
                      d_mlp: int = 3072, vocab: int = 50257, seed: int = 0):
     """Times `n_tokens` greedy decode steps of a GPT-2-small-shaped f32 model (the reference's README
