@@ -444,7 +444,7 @@ def _main(out):
     ap.add_argument("--pdl", type=int, default=int(os.environ.get("GPTRS_PDL", "1")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the kernel microbenchmarks")
-    ap.add_argument("--microbench", default=None, choices=["attention", "attention-ragged", "gemv", "gemm64", "quant-linear"],
+    ap.add_argument("--microbench", default=None, choices=["attention", "attention-ragged", "gemv", "gemm64", "quant-linear", "prefill"],
                     help="run only one kernel microbenchmark (used for ncu captures) and print its JSON")
     ap.add_argument("--ctx", type=int, default=PROMPT_LEN + 20, help="context length for --microbench attention")
     ap.add_argument("--workload", default="ministral3b-w4", choices=["ministral3b-w4", "gpt2-fp32", "dp512"],
@@ -477,6 +477,30 @@ def _main(out):
     if args.workload == "dp512":
         run_dp512(args, out, gm, torch, np)
         return
+    if args.microbench == "prefill":
+        # chunked prefill of a few 2048-token prompts through the engine (used for the ncu launch list of the prefill path)
+        torch.cuda.set_device(0)
+        dev = torch.device("cuda", 0)
+        model, cfg = build_model(gm, torch, dev, 0, args.pdl, args.prefill_chunk)
+        stream = torch.cuda.ExternalStream(lib_stream(model), device=dev)
+        rng = np.random.default_rng(1000)
+        n_seq = max(args.steps, 1) if args.steps != 64 else 4
+        model.prefill(0, rng.integers(0, cfg.vocab, size=PROMPT_LEN), chunk=args.prefill_chunk)  # warm-up
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for s_ in range(1, 1 + n_seq):
+            model.prefill(s_, rng.integers(0, cfg.vocab, size=PROMPT_LEN), chunk=args.prefill_chunk)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        qkv_w = (cfg.n_q_heads + 2 * cfg.n_kv_heads) * cfg.head_dim
+        per_layer = cfg.d_model * qkv_w + cfg.n_q_heads * cfg.head_dim * cfg.d_model + 3 * cfg.d_model * cfg.d_mlp
+        flops = 2.0 * cfg.n_layers * per_layer * PROMPT_LEN * n_seq  # projections only (attention and the one lm_head row left out)
+        print(json.dumps({"microbench": "prefill", "sequences": n_seq, "prompt_tokens": PROMPT_LEN, "chunk": args.prefill_chunk,
+                          "ms": ms, "tokens_per_s": n_seq * PROMPT_LEN / ms * 1e3, "matmul_tflops": flops / ms / 1e9}), file=out)
+        return
+
     if args.microbench:
         torch.cuda.set_device(0)
         dev = torch.device("cuda", 0)
@@ -544,11 +568,8 @@ def _main(out):
 
     rng = np.random.default_rng(1000 + (0 if tp else rank))  # a tensor-parallel group shares ONE batch
     t0 = time.perf_counter()
-    first = []
-    for s in range(BATCH):
-        prompt = rng.integers(0, cfg.vocab, size=PROMPT_LEN)
-        _, tok = model.prefill(s, prompt, chunk=args.prefill_chunk)
-        first.append(tok)
+    prompts = [rng.integers(0, cfg.vocab, size=PROMPT_LEN) for _ in range(BATCH)]
+    first = model.prefill_many(list(range(BATCH)), prompts, chunk=args.prefill_chunk)  # rows packed across prompts
     t_prefill = time.perf_counter() - t0
 
     gen = gm.Generator(model, first, use_graph=True)

@@ -231,6 +231,46 @@ class LoadedModel:
                 logits, sampled = lg, sm
         return (logits[0] if logits is not None else None), int(sampled[0])
 
+    def prefill_many(self, slots, prompts, chunk: int | None = None):
+        """Appends one prompt to each of `slots` with the rows of all prompts packed into forward passes of up to
+        `chunk` rows, so a pass may hold the tail of one sequence and the head of the next: the matmuls then see
+        full row tiles whatever the prompt lengths are. A pass is cut early where the next sequence would start
+        off the row alignment that lets the attention kernel share one K/V stream between the rows of a group.
+        Returns the greedy id that follows each prompt, in the order given."""
+        cfg = self.config
+        chunk = min(chunk or cfg.max_tokens, cfg.max_tokens)
+        group = max(cfg.n_q_heads // max(cfg.n_kv_heads, 1), 1)
+        align = max(16 // group, 1)
+        max_rows = cfg.max_logit_rows if cfg.max_logit_rows > 0 else cfg.max_seqs
+        first = [None] * len(prompts)
+        tok, sl, pos, rows, owners = [], [], [], [], []
+
+        def flush():
+            if not tok:
+                return
+            _, sampled = self.forward_with_decode_cache(tok, sl, pos, rows, want_logits=False)
+            for r, o in enumerate(owners):
+                first[o] = int(sampled[r])
+            tok.clear(), sl.clear(), pos.clear(), rows.clear(), owners.clear()
+
+        for i, (slot, prompt) in enumerate(zip(slots, prompts)):
+            prompt = np.asarray(prompt, dtype=np.int32)
+            start = self.sequence_length(slot)
+            done = 0
+            while done < len(prompt):
+                n = min(len(prompt) - done, chunk - len(tok))
+                tok.extend(prompt[done:done + n].tolist())
+                sl.extend([slot] * n)
+                pos.extend(range(start + done, start + done + n))
+                done += n
+                if done == len(prompt):
+                    rows.append(len(tok) - 1)
+                    owners.append(i)
+                if len(tok) == chunk or (done == len(prompt) and (len(tok) % align != 0 or len(rows) == max_rows)):
+                    flush()
+        flush()
+        return first
+
     def logits(self, tokens) -> np.ndarray:
         """LoadedModel.logits of the py bindings: logits of every row of one fresh sequence."""
         self.reset_sequence(0)

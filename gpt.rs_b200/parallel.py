@@ -65,9 +65,12 @@ def run_requests(model, prompts: dict, decode_steps: int, max_batch: int, prefil
         first = []
 
         def prefill():
-            for slot, r in enumerate(wave):
+            for slot in range(len(wave)):
                 model.reset_sequence(slot)
-                first.append(model.prefill(slot, prompts[r], chunk=prefill_chunk)[1])
+            if hasattr(model, "prefill_many"):  # rows of several prompts packed into full passes
+                first.extend(model.prefill_many(list(range(len(wave))), [prompts[r] for r in wave], chunk=prefill_chunk))
+            else:
+                first.extend(model.prefill(slot, prompts[r], chunk=prefill_chunk)[1] for slot, r in enumerate(wave))
 
         steps = []
 

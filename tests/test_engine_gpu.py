@@ -254,3 +254,29 @@ def test_requests_served_in_waves_match_the_oracle(cuda):
     assert sorted(got) == list(range(7))
     for r, p in prompts.items():
         assert got[r] == mr.RefModel(cfg, params).generate_greedy(p, 11), r
+
+
+@pytest.mark.parametrize("lens,chunk", [((5, 33, 17, 64, 8, 40), 32), ((32, 32, 32, 32), 48), ((3, 70), 64)])
+def test_packed_prefill_of_several_prompts_matches_oracle(cuda, lens, chunk):
+    """prefill_many: the rows of several prompts in one pass (the tail of one sequence and the head of the next),
+    aligned and unaligned boundaries; afterwards every sequence's next-token logits match the oracle at 2e-2."""
+    cfg = TINY_Q
+    params = mr.random_params(cfg, seed=21, std=0.05)
+    qparams = mr.quantised_params(cfg, params, "w4")
+    rng = np.random.default_rng(len(lens) + chunk)
+    prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in lens]
+    n = len(prompts)
+    m = _load(cfg, params, mode=gm.MODE_W4A16, max_seqs=n, max_tokens=64, max_logit_rows=n, kv_pages=n * 6 + 4, max_pages_per_seq=6)
+    first = m.prefill_many(list(range(n)), prompts, chunk=chunk)
+    assert [m.sequence_length(s) for s in range(n)] == list(lens)
+    refs = [mr.RefModel(cfg, qparams) for _ in prompts]
+    for s, p in enumerate(prompts):
+        want = refs[s].forward(p)[-1]
+        gap = np.sort(want)
+        if gap[-1] - gap[-2] > 4e-2:
+            assert first[s] == int(np.argmax(want)), s
+    # one decode step for all sequences: logits against the oracle teacher-forced with the engine's first tokens
+    lg, _ = m.forward_with_decode_cache(first, list(range(n)), list(lens), list(range(n)))
+    for s in range(n):
+        want = refs[s].forward([first[s]])[-1]
+        assert float(np.max(np.abs(lg[s] - want))) <= 2e-2, s
