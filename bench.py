@@ -440,7 +440,8 @@ def _main(out):
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--prefill-chunk", type=int, default=1024)
+    ap.add_argument("--prefill-chunk", type=int, default=1536,
+                    help="rows per prefill pass: 1536 = 6 tiles of 256 rows, so the 24-column-tile projections launch 144 CTAs (one wave of 148 SMs)")
     ap.add_argument("--pdl", type=int, default=int(os.environ.get("GPTRS_PDL", "1")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the kernel microbenchmarks")
