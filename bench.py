@@ -14,7 +14,8 @@ Other modes (none of them the default line): --workload gpt2-fp32 (the reference
 f32 weights), --workload dp512 (512 requests with prompt lengths U{256..4096}, 256 decode steps each, bin-packed over the
 ranks and served in waves of 64: total work fixed, strong scaling), --weights w8a16, --parallelism tp (one batch over a
 tensor-parallel group), --microbench
-attention | attention-ragged | gemv | gemm64 | quant-linear (single kernels, CUDA-graph timed; used for ncu captures).
+attention | attention-ragged | gemv | gemm64 | quant-linear (single kernels, CUDA-graph timed; used for ncu captures)
+| prefill (a few 2048-token prompts through the engine's chunked prefill; --steps = number of prompts).
 """
 from __future__ import annotations
 
