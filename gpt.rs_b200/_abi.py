@@ -48,6 +48,7 @@ class MatmulEpilogue(ctypes.Structure):
         ("d_rope_kv_pool", ctypes.c_void_p),
         ("rope_q_heads", ctypes.c_int),
         ("rope_kv_heads", ctypes.c_int),
+        ("d_status", ctypes.c_void_p),
     ]
 
 

@@ -2,13 +2,16 @@
 // crates/gpt-rs/src/backend/spec.rs:1224-1266, 1291).
 #include "common.cuh"
 
+#include <cstdlib>
 #include <string>
 
 namespace gptrs {
 
 static thread_local std::string g_last_error;
-int g_use_pdl = 0;
-int g_launch_priority = 0;
+// GPTRS_FORCE_PDL=1 launches every kernel with programmatic stream serialisation, also outside the engine's
+// recorded step (used to time chains of functional-level calls the way the engine runs them)
+thread_local int g_use_pdl = [] { const char* e = getenv("GPTRS_FORCE_PDL"); return (e && e[0] == '1') ? 1 : 0; }();
+thread_local int g_launch_priority = 0;
 
 void set_last_error(const std::string& msg) { g_last_error = msg; }
 
@@ -17,17 +20,21 @@ int fail(int status, const std::string& msg) {
     return status;
 }
 
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return 0;
+    return dev;
+}
+
 int sm_count() {
-    static int cached = 0;
-    if (cached == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-            cached = n;
-        else
-            cached = 148;
+    static std::atomic<int> cached[kMaxDevices];
+    const int dev = current_device() & (kMaxDevices - 1);
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached;
+    return n;
 }
 
 }  // namespace gptrs

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <string>
 
 #include "../../include/gptrs_cuda.h"
@@ -41,14 +42,29 @@ inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s
 
 static inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
-// Number of SMs of the current device (cached per process; B200 = 148).
+// Ordinal of the calling thread's current device (0 when the runtime cannot tell).
+int current_device();
+constexpr int kMaxDevices = 64;
+
+// Number of SMs of the current device (cached per device; B200 = 148).
 int sm_count();
 
-// Non-zero while the decode engine records a step: kernels are then launched with
-// programmatic stream serialisation (every kernel of this library executes
-// griddepcontrol.wait before it touches memory written by its predecessor).
-extern int g_use_pdl;
-extern int g_launch_priority;  // 0 = default; otherwise the stream priority value given to kernel launches
+// "Done once per device" flag for state that the runtime keeps per device (function attributes):
+// first_time() answers true exactly once for each device ordinal, from whichever thread comes first.
+struct PerDeviceOnce {
+    std::atomic<uint64_t> mask{0};
+    bool first_time() {
+        const uint64_t bit = 1ull << (current_device() & (kMaxDevices - 1));
+        return (mask.fetch_or(bit) & bit) == 0;
+    }
+};
+
+// Launch options of the calling thread. g_use_pdl is non-zero while that thread records a decode step:
+// kernels are then launched with programmatic stream serialisation (every kernel of this library
+// executes griddepcontrol.wait before it touches memory written by its predecessor). Thread-local, so
+// that two host threads driving two models do not see each other's setting.
+extern thread_local int g_use_pdl;
+extern thread_local int g_launch_priority;  // 0 = default; otherwise the stream priority value given to kernel launches
 
 #ifdef __CUDACC__
 // Launch through cudaLaunchKernelEx with the optional cluster (along grid.y) and

@@ -311,6 +311,7 @@ int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool
     ep.d_bias = w.bias ? static_cast<const float*>(w.bias->data) : nullptr;
     ep.d_residual = residual;
     ep.swiglu = swiglu ? 1 : 0;
+    ep.d_status = m.d_status.as<int32_t>();  // a matmul wait that gives up reports through the model's word
     if (fold && fold->produce) { ep.d_norm_gamma = fold->gamma; ep.d_norm_x = fold->x_next; ep.d_sumsq_out = fold->sumsq; }
     if (fold && fold->consume) { ep.d_sumsq_in = fold->sumsq; ep.sumsq_tiles = fold->dim / 128; ep.norm_dim = fold->dim; ep.norm_eps = fold->eps; }
     if (fold && fold->rope_positions) {
@@ -652,7 +653,9 @@ int check_status(Model& m) {
     GPTRS_CUDA_OK(cudaStreamSynchronize(m.stream));
     if (st != 0) {
         cudaMemsetAsync(m.d_status.p, 0, 4, m.stream);
-        return fail(GPTRS_EXECUTION, st == 2 ? "token or position id out of range" : "a bounded device wait gave up");
+        return fail(GPTRS_EXECUTION, st == 2   ? "token or position id out of range"
+                                     : st == 3 ? "a bounded wait inside a tensor-core matmul kernel gave up"
+                                               : "a bounded wait inside the attention kernel gave up");
     }
     return GPTRS_OK;
 }
@@ -1088,9 +1091,10 @@ int gptrs_cuda_generator_step(gptrs_model* h, const int32_t* h_tokens_in, int32_
             const int64_t launches_before = m.launches;
             cudaGraph_t graph = nullptr;
             GPTRS_CUDA_OK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+            const int pdl_before = g_use_pdl;
             g_use_pdl = c.use_pdl ? 1 : 0;
             int r = body();
-            g_use_pdl = 0;
+            g_use_pdl = pdl_before;
             cudaError_t e = cudaStreamEndCapture(s, &graph);
             const int64_t recorded = m.launches - launches_before;
             m.launches = launches_before;  // capturing launches nothing

@@ -62,6 +62,13 @@ struct MatmulParams {
     __nv_bfloat16* rope_q_out;    // [M][Hq][128]
     unsigned char* rope_pool;     // paged KV pool of the layer
     int rope_max_pages, rope_hq, rope_hkv;
+    // tensor-core kernels: where a bounded wait that gave up records code 3 (the caller's word, else the
+    // library's per-device word), how many polls a wait may take, and the test switch that withholds the first
+    // activation tile so that a wait runs out (gptrs_cuda_debug_matmul_fault)
+    int* status;
+    uint32_t spin_limit;
+    int debug_starve;
+    int stage_rotation;  // streaming kernel: column tiles start their K walk at different stages
 };
 
 // ---- split-K reduction across the CTAs of a cluster: push, one barrier, local sum -------------------
@@ -116,7 +123,8 @@ struct SplitReduce {
 // Second half: barrier, local sum over the S slots, bias / residual / SwiGLU, store. All threads of the CTA.
 template <int MPAD>
 __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const SplitReduce& sr, const float* slots, int tid,
-                                                    int n_threads, int m0, int n_cta0, int tile_cols = kCtaN) {
+                                                    int n_threads, int m0, int n_cta0, int tile_cols = kCtaN,
+                                                    bool cluster_barrier = true) {
     const int S = sr.S, rank = sr.rank, rows_max = sr.rows_max;
     // consumer of a folded RMSNorm: 1 / rms of every row this CTA owns, from the producer's per-tile sums
     __shared__ float row_scale[MPAD];
@@ -130,7 +138,9 @@ __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const
             row_scale[lr] = rsqrtf(ss / (float)p.norm_dim + p.norm_eps);
         }
     }
-    if (S > 1) { cluster_arrive(); cluster_wait(); }
+    // the barrier after which every push of the cluster has landed (a CTA with several tiles pushes them all first
+    // and passes the barrier once)
+    if (S > 1 && cluster_barrier) { cluster_arrive(); cluster_wait(); }
     __syncthreads();
     auto gather = [&](int local_row, int c) {
         float4 v = *reinterpret_cast<const float4*>(slots + (size_t)local_row * kRedStride + c);

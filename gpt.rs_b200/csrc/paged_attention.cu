@@ -44,9 +44,21 @@ struct AttnParams {
     float* part_ml;               // [T][Hq][max_splits][2]
     int* status;                  // device error word (0 = ok)
     int T, Hq, Hkv, max_pages, chunk_pages, max_splits;
+    int max_len;                  // lengths above min(launch bound, page-table row) are clamped to it and flagged
     int fixed_chunks;             // splits are chunk_pages long (prefill groups) instead of balanced per sequence
     float scale_log2;
 };
+
+// A visible length read from device memory, held to what the launch was sized for: a larger value would walk off the
+// page-table row and the split partials. The caller's status word gets code 2 (argument out of range).
+__device__ __forceinline__ int clamped_len(const AttnParams& p, int tok) {
+    int len = p.ctx_len[tok];
+    if (len > p.max_len || len < 0) {
+        if (p.status) atomicExch(p.status, 2);
+        len = len < 0 ? 0 : p.max_len;
+    }
+    return len;
+}
 
 // Split geometry of one sequence. The launch fixes the LARGEST chunk (chunk_pages); a sequence of `len` visible
 // tokens is cut into n = ceil(pages / chunk_pages) splits of equal size ceil(pages / n) pages, so a context just past
@@ -81,10 +93,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
     // rows g (lo) and g + 8 (hi) of the tile belong to this lane
     const int tok_lo = kMulti ? b + g / group : b, tok_hi = kMulti ? b + (g + 8) / group : b;
     const bool valid_lo = kMulti ? tok_lo < p.T : g < group, valid_hi = kMulti && tok_hi < p.T;
-    const int len_lo = valid_lo ? p.ctx_len[tok_lo] : 0, len_hi = valid_hi ? p.ctx_len[tok_hi] : 0;
-    int len = p.ctx_len[b];
+    const int len_lo = valid_lo ? clamped_len(p, tok_lo) : 0, len_hi = valid_hi ? clamped_len(p, tok_hi) : 0;
+    int len = clamped_len(p, b);
     if (kMulti)
-        for (int i = 1; i < tq && b + i < p.T; ++i) len = max(len, p.ctx_len[b + i]);
+        for (int i = 1; i < tq && b + i < p.T; ++i) len = max(len, clamped_len(p, b + i));
     int n_splits, split_pages;
     if (kMulti) { split_pages = p.chunk_pages; n_splits = (len + split_pages * kPageTokens - 1) / (split_pages * kPageTokens); }
     else split_geometry(len, p.chunk_pages, &n_splits, &split_pages);  // rows of a prefill group keep one fixed grid
@@ -293,7 +305,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
         int row_splits = n_splits;
         if (kMulti) {
             if (tok >= p.T) continue;
-            const int row_len = p.ctx_len[tok];
+            const int row_len = clamped_len(p, tok);
             if (first_tok >= row_len) continue;  // this split holds nothing the row may see
             row_splits = (row_len + chunk_tokens - 1) / chunk_tokens;
         }
@@ -330,7 +342,7 @@ __global__ void __launch_bounds__(128) attention_combine_kernel(const AttnParams
     const int b = blockIdx.x, hq = blockIdx.y, c = threadIdx.x;
     pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
-    const int len = p.ctx_len[b];
+    const int len = clamped_len(p, b);
     int n_splits, split_pages;
     if (p.fixed_chunks) { split_pages = p.chunk_pages; n_splits = (len + split_pages * kPageTokens - 1) / (split_pages * kPageTokens); }
     else split_geometry(len, p.chunk_pages, &n_splits, &split_pages);
@@ -506,11 +518,11 @@ static int paged_attention_launch(bool multi, const void* d_q, const void* d_kv_
     p.status = d_status;
     p.T = (int)n_tokens; p.Hq = (int)n_q_heads; p.Hkv = (int)n_kv_heads;
     p.max_pages = (int)max_pages; p.chunk_pages = (int)chunk_pages; p.max_splits = (int)splits;
+    p.max_len = (int)std::min<int64_t>(max_ctx_len, max_pages * kPageTokens);
     p.scale_log2 = kLog2e / sqrtf((float)head_dim);
-    static int depth = 0;
-    if (depth == 0) {
-        const char* e = getenv("GPTRS_ATTN_DEPTH");
-        depth = (e && atoi(e) == 3) ? 3 : 2;
+    static const int depth = [] { const char* e = getenv("GPTRS_ATTN_DEPTH"); return (e && atoi(e) == 3) ? 3 : 2; }();
+    static PerDeviceOnce attr_once;
+    if (attr_once.first_time()) {
         GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kAttnWarps * 2 * kPageHeadBytes));
         GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -590,16 +602,18 @@ static __device__ __align__(256) unsigned char g_noalloc_attention_scratch[kNoAl
 // In host code the array's name is only a handle; the device address comes from
 // cudaGetSymbolAddress, once per device, with that device current.
 static int noalloc_scratch_address(void** out) {
-    static void* per_device[64] = {nullptr};
+    // one slot per device ordinal; two host threads that make the first call together both look the address up
+    // and store the same value
+    static std::atomic<void*> per_device[64];
     int dev = 0;
     GPTRS_CUDA_OK(cudaGetDevice(&dev));
     GPTRS_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
-    if (!per_device[dev]) {
-        void* ptr = nullptr;
+    void* ptr = per_device[dev].load(std::memory_order_acquire);
+    if (!ptr) {
         GPTRS_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_attention_scratch));
-        per_device[dev] = ptr;
+        per_device[dev].store(ptr, std::memory_order_release);
     }
-    *out = per_device[dev];
+    *out = ptr;
     return GPTRS_OK;
 }
 

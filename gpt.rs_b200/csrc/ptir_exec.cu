@@ -984,6 +984,7 @@ int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* c
         if (!parse_json(program_json, len, &root, &err)) return fail(GPTRS_SPEC_VIOLATION, "program json: " + err);
         auto p = std::make_shared<Plan>();
         int st = build_function(root, &p->fn, &err);
+        if (!st) st = verify_function(p->fn, &err);   // before any launch: arity, attribute ranges, declared result types
         if (st) return fail(st == 2 ? GPTRS_UNIMPLEMENTED : GPTRS_SPEC_VIOLATION, err);
         if (g_fusion_enabled) rewrite(*p); else count_uses(*p);
         if (int rc = upload_literals(*p)) return rc;
@@ -1109,11 +1110,13 @@ Json fused_instruction_json(const Inst& in) {
         operands.push_back(jobj({{"Literal", jobj({{"spec", tensor_spec_json(o.lit)}, {"bytes", jarr(std::move(bytes))}})}}));
     }
     std::vector<std::pair<std::string, Json>> attrs;
-    if (in.op == Op::FusedLayerNorm || in.op == Op::FusedRmsNorm) attrs.push_back({"eps", jobj({{"F64", jnum((double)in.f0)}})});
+    // CustomCallAttr is adjacently tagged (#[serde(tag = "kind", content = "value")], spec.rs:602-613)
+    if (in.op == Op::FusedLayerNorm || in.op == Op::FusedRmsNorm || in.op == Op::FusedAddRmsNorm || in.op == Op::FusedAddLayerNorm)
+        attrs.push_back({"eps", jobj({{"kind", jstr("F64")}, {"value", jnum((double)in.f0)}})});
     if (in.op == Op::FusedAttentionDecode) {
         std::vector<Json> g;
         for (int64_t v : in.a) g.push_back(jnum((double)v));
-        attrs.push_back({"geometry", jobj({{"I64Array", jarr(std::move(g))}})});
+        attrs.push_back({"geometry", jobj({{"kind", jstr("I64Array")}, {"value", jarr(std::move(g))}})});
     }
     Json call = jobj({{"CustomCall", jobj({{"target", jstr(fused_target(in.op))}, {"attrs", jobj(std::move(attrs))}})}});
     return jobj({{"id", jnum(in.id)}, {"op", std::move(call)}, {"operands", jarr(std::move(operands))},
@@ -1129,6 +1132,7 @@ int gptrs_cuda_pipeline_fuse(const char* program_json, size_t len, char* out, si
     if (!parse_json(program_json, len, &root, &err)) return fail(GPTRS_SPEC_VIOLATION, "program json: " + err);
     Plan plan;
     int st = build_function(root, &plan.fn, &err);
+    if (!st) st = verify_function(plan.fn, &err);
     if (st) return fail(st == 2 ? GPTRS_UNIMPLEMENTED : GPTRS_SPEC_VIOLATION, err);
     rewrite(plan);
     // the entry function's body: surviving instructions as they were, fused ones as CustomCalls, in the old order
@@ -1155,6 +1159,18 @@ int gptrs_cuda_pipeline_fuse(const char* program_json, size_t len, char* out, si
     *written = text.size();
     if (n_fused) *n_fused = plan.fused;
     if (out && out_cap >= text.size()) memcpy(out, text.data(), text.size());
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_verify_program(const char* program_json, size_t len) {
+    GPTRS_REQUIRE(program_json, "null pointer");
+    Json root;
+    std::string err;
+    if (!parse_json(program_json, len, &root, &err)) return fail(GPTRS_SPEC_VIOLATION, "program json: " + err);
+    Function fn;
+    int st = build_function(root, &fn, &err);
+    if (!st) st = verify_function(fn, &err);
+    if (st) return fail(st == 2 ? GPTRS_UNIMPLEMENTED : GPTRS_SPEC_VIOLATION, err);
     return GPTRS_OK;
 }
 

@@ -142,6 +142,15 @@ bool read_value_type(const Json& vt, TSpec* out, std::string* err) {
     return read_tspec(t, out, err);
 }
 
+// CustomCallAttr is adjacently tagged by serde: {"kind": "F64", "value": 1e-5} (spec.rs:602-613). The externally
+// tagged form {"F64": 1e-5} is accepted as well.
+const Json* attr_value(const Json* a, const char* kind) {
+    if (!a || a->kind != Json::Object) return nullptr;
+    const Json* k = a->get("kind");
+    if (k && k->kind == Json::String && k->str == kind) return a->get("value");
+    return a->get(kind);
+}
+
 void read_ints(const Json* a, std::vector<int64_t>* out) {
     if (!a) return;
     for (auto& e : a->arr) out->push_back(e.as_int());
@@ -263,6 +272,13 @@ int build_function(const Json& program, Function* fn, std::string* err) {
             return 1;
         }
         const std::string& n = in.name;
+        static const char* const kNeedsAttr[] = {"Constant", "ElementwiseUnary", "ElementwiseBinary", "DotGeneral", "Reduce", "Compare", "Cast",
+                                                 "Transpose", "Slice", "Concat", "Iota", "Gather", "DynamicSlice", "DynamicUpdateSlice",
+                                                 "ReduceWindow", "CustomCall", "Dequantize"};
+        for (const char* k : kNeedsAttr)
+            if (n == k && !attr) { *err = n + " (%" + std::to_string(in.id) + ") without its attributes"; return 1; }
+        if ((n == "ElementwiseUnary" || n == "ElementwiseBinary") && attr->kind != Json::String) { *err = n + ": the operation kind must be a string"; return 1; }
+        if (n != "ElementwiseUnary" && n != "ElementwiseBinary" && attr && attr->kind != Json::Object) { *err = n + ": attributes must be an object"; return 1; }
         if (n == "Constant") {
             in.op = Op::Constant;
             Operand o; o.is_literal = true;
@@ -305,6 +321,12 @@ int build_function(const Json& program, Function* fn, std::string* err) {
             const Json* acc = attr->get("accum_dtype");
             if (acc && acc->kind == Json::String && acc->str != "F32") in.f0 = 1.f;  // refused at run time like the reference
         }
+        else if (n == "Dequantize") {
+            // DequantizeSpec { axis, output_dtype } (spec.rs:585-589). The scheme is backend-defined (docs/backend.md:620-632);
+            // this backend's: (q si8 [N][K], fp16 scales [N]) or (q ui8 [N][K/2] = two si4 per byte, low nibble first,
+            // fp16 scales [N][K/128]) -> f32 [N][K], w = q * scale.
+            in.op = Op::Dequantize;
+        }
         else if (n == "CustomCall") {
             in.op = Op::CustomCall;
             in.sub = attr->get("target") ? attr->get("target")->str : "";
@@ -317,13 +339,13 @@ int build_function(const Json& program, Function* fn, std::string* err) {
                 in.op = f;
                 if (f == Op::FusedLayerNorm || f == Op::FusedRmsNorm) {
                     const Json* e = attrs ? attrs->get("eps") : nullptr;
-                    const Json* v = e ? e->get("F64") : nullptr;
+                    const Json* v = attr_value(e, "F64");
                     if (!v || v->kind != Json::Number) { *err = in.sub + ": attribute eps (F64) is required"; return 1; }
                     in.f0 = (float)v->num;
                 }
                 if (f == Op::FusedAttentionDecode) {
                     const Json* g = attrs ? attrs->get("geometry") : nullptr;
-                    read_ints(g ? g->get("I64Array") : nullptr, &in.a);
+                    read_ints(attr_value(g, "I64Array"), &in.a);
                     if (in.a.size() != 4) { *err = in.sub + ": attribute geometry (I64Array of q heads, kv heads, head_dim, capacity) is required"; return 1; }
                 }
             }

@@ -34,9 +34,10 @@ void write_json(const Json& j, std::string* out);
 
 enum class Op {
     Constant, Unary, Binary, DotGeneral, Reduce, Compare, Select, Cast, StopGradient, Reshape, Transpose, BroadcastTo,
-    Slice, Concat, Iota, Take, Gather, DynamicSlice, DynamicUpdateSlice, ReduceWindow, CustomCall,
+    Slice, Concat, Iota, Take, Gather, DynamicSlice, DynamicUpdateSlice, ReduceWindow, Dequantize, CustomCall,
     // produced by the fusion rewrites of this backend
-    FusedLayerNorm, FusedRmsNorm, FusedSoftmax, FusedMatmulBias, FusedAttentionDecode, Unsupported
+    FusedLayerNorm, FusedRmsNorm, FusedSoftmax, FusedMatmulBias, FusedAttentionDecode, FusedAddRmsNorm, FusedAddLayerNorm,
+    FusedQuantMatmul, Unsupported
 };
 
 struct TSpec {
@@ -76,6 +77,10 @@ struct Function {
 
 // Builds the entry function. status: 0 ok, 1 spec violation, 2 unimplemented.
 int build_function(const Json& program, Function* fn, std::string* err);
+
+// Checks operand counts, attribute ranges and every declared result type against the operand types
+// (ptir_verify.cpp). status: 0 ok, 1 spec violation.
+int verify_function(const Function& fn, std::string* err);
 
 // CustomCall targets the fusion pipeline of this backend emits and run_program accepts (docs/backend.md:568-592:
 // namespaced and versioned).

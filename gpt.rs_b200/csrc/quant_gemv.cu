@@ -172,10 +172,9 @@ __global__ void __launch_bounds__(kGvWarps * 32, 2) w4_gemv_kernel(const MatmulP
 template <int MT>
 int launch_gemv(const MatmulParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     void (*kern)(MatmulParams) = w4_gemv_kernel<MT>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.first_time()) {
         GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_done = true;
     }
     return launch_kernel(kern, grid, dim3(kGvWarps * 32), smem, st, p.n_split, p);
 }

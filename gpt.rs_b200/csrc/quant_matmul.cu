@@ -25,6 +25,7 @@ namespace gptrs {
 int umma_w4a16_matmul(MatmulParams p, cudaStream_t st);  // umma_matmul.cu
 int umma_w8a16_matmul(MatmulParams p, cudaStream_t st);  // umma_matmul.cu
 int umma_status(int* out);
+void umma_debug_fault(int starve, uint32_t spin_limit);
 int w4_gemv(MatmulParams p, cudaStream_t st);  // quant_gemv.cu
 
 namespace {
@@ -523,10 +524,9 @@ __global__ void quantize_w8_kernel(const float* w, int64_t K, int64_t N, int tra
 template <int MT, int BITS>
 int launch_matmul(const MatmulParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
     void (*kern)(MatmulParams) = quant_matmul_kernel<MT, BITS>;
-    static bool attr_done = false;  // per instantiation
-    if (!attr_done) {
+    static PerDeviceOnce attr_once;  // per instantiation
+    if (attr_once.first_time()) {
         GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024));
-        attr_done = true;
     }
     return launch_kernel(kern, grid, dim3(kWarps * 32), smem, stream, p.n_split, p);
 }
@@ -570,6 +570,7 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
     p.y = d_y;
     p.M = (int)m; p.N = (int)n; p.K = (int)k;
     p.out_f32 = 0;
+    p.status = ep ? ep->d_status : nullptr;
     if (ep) {
         GPTRS_REQUIRE(ep->out_dtype == GPTRS_BF16 || ep->out_dtype == GPTRS_F32, "out_dtype must be bf16 or f32");
         p.out_f32 = ep->out_dtype == GPTRS_F32;
@@ -759,6 +760,11 @@ int gptrs_cuda_matmul_status(int32_t* h_status) {
     int rc = umma_status(&v);
     *h_status = v;
     return rc;
+}
+
+int gptrs_cuda_debug_matmul_fault(int starve, uint32_t spin_limit) {
+    umma_debug_fault(starve, spin_limit);
+    return GPTRS_OK;
 }
 
 int gptrs_cuda_quant_matmul_w4a16(const void* d_x, const void* d_packed, void* d_y, int64_t m,

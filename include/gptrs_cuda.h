@@ -136,6 +136,9 @@ typedef struct {
     void* d_rope_q_out;
     void* d_rope_kv_pool;
     int rope_q_heads, rope_kv_heads;
+    /* Optional device word that receives code 3 when a bounded wait inside a tensor-core matmul kernel gives up
+     * (rows > 16). Null = the library's own per-device word, read with gptrs_cuda_matmul_status. */
+    int32_t* d_status;
 } gptrs_matmul_epilogue;
 
 /* sizeof(gptrs_matmul_epilogue) as the library was built: lets a foreign-language binding check its own
@@ -155,6 +158,14 @@ int gptrs_cuda_quant_matmul_w8a16(const void* d_x_bf16, const void* d_packed, vo
 /* Synchronises the device and returns (then clears) the error word of the tensor-core matmul
  * kernels: 0 = ok, 3 = a bounded wait inside a kernel gave up. */
 int gptrs_cuda_matmul_status(int32_t* h_status);
+
+/* Test switch for the failure path of the tensor-core matmuls (no counterpart in the reference; its GPU backend
+ * has no device-side waits). While `starve` is non-zero every decode-sized launch (17..64 rows) withholds the
+ * first activation tile, so the waits that depend on it run out after `spin_limit` polls (0 = the built-in
+ * limit of 2^20); the kernel then records code 3 in its status word, frees its tensor memory and returns with
+ * an unspecified result. Nothing faults and nothing waits without a bound. Process-wide; call with (0, 0) to
+ * switch it off again. */
+int gptrs_cuda_debug_matmul_fault(int starve, uint32_t spin_limit);
 
 /* ==============================================================================================
  * Paged bf16 KV cache and decode attention (split-K flash decoding).
@@ -450,6 +461,11 @@ int gptrs_cuda_execute_instruction(const char* instruction_json, size_t len, gpt
  * *written is the length of the result; it is copied to `out` only when out_cap is large enough (call once with
  * out = NULL to size the buffer). n_fused (optional) receives the number of rewrites. */
 int gptrs_cuda_pipeline_fuse(const char* program_json, size_t len, char* out, size_t out_cap, size_t* written, int64_t* n_fused);
+/* Parses a program and checks it the way run_program does before its first launch: operand counts, attribute ranges
+ * (axes, permutations, slice bounds), every declared result type against the type its operands imply, and that every
+ * value is defined before it is used. Returns GPTRS_SPEC_VIOLATION with the offending instruction in the message, as
+ * the reference interpreter does for a malformed program (crates/gpt-rs-backend-ref-cpu/src/cpu.rs). Host only. */
+int gptrs_cuda_verify_program(const char* program_json, size_t len);
 int gptrs_cuda_run_program_stats(int64_t* plan_builds, int64_t* plan_hits, int64_t* last_launches, int64_t* last_fused);
 /* Turns the fusion rewrites of run_program on (default) or off (GPTRS_OPT-style switch for tests). */
 int gptrs_cuda_set_fusion(int enabled);

@@ -241,16 +241,33 @@ def _cuda_custom_call(attr, ins, out_dims):
     attention.rs:657-779). Any other target is unknown, as docs/backend.md:581-582 requires."""
     from . import functional_ref as fr
     target, attrs = attr["target"], attr.get("attrs", {})
+
+    def val(name, kind):
+        """CustomCallAttr is adjacently tagged by serde: {"kind": "F64", "value": 1e-5} (spec.rs:602-613)."""
+        a = attrs[name]
+        if a.get("kind") != kind:
+            raise PtirError(f"attribute {name} of {target} must be {kind}")
+        return a["value"]
+
     if target == "gpt_rs.cuda.layer_norm.f32.v1":
-        return fr.layer_norm(ins[0], ins[1], ins[2], np.float32(attrs["eps"]["F64"]))[0]
+        return fr.layer_norm(ins[0], ins[1], ins[2], np.float32(val("eps", "F64")))[0]
     if target == "gpt_rs.cuda.rms_norm.f32.v1":
-        return fr.rms_norm(ins[0], ins[1], np.float32(attrs["eps"]["F64"]))[0]
+        return fr.rms_norm(ins[0], ins[1], np.float32(val("eps", "F64")))[0]
+    if target == "gpt_rs.cuda.add_rms_norm.f32.v1":      # rms_norm(residual + update): common.rs:58-65 then normalization.rs:192-206
+        return fr.rms_norm((ins[0] + ins[1]).astype(np.float32), ins[2], np.float32(val("eps", "F64")))[0]
+    if target == "gpt_rs.cuda.add_layer_norm.f32.v1":
+        return fr.layer_norm((ins[0] + ins[1]).astype(np.float32), ins[2], ins[3], np.float32(val("eps", "F64")))[0]
+    if target in ("gpt_rs.cuda.quant_matmul_w4a16.v1", "gpt_rs.cuda.quant_matmul_w8a16.v1"):
+        # x [M][K] . dequant(q, scales)^T with x rounded to bf16 (the kernel's activation type), f32 accumulate
+        from . import quant_ref as qr
+        w = qr.dequant_w4(ins[1], ins[2]) if target.endswith("w4a16.v1") else qr.dequant_w8(ins[1], ins[2])
+        return qr.quant_matmul(qr.to_bf16(ins[0]), w)
     if target == "gpt_rs.cuda.softmax_last_axis.f32.v1":
         return fr.softmax_last_dim(ins[0])
     if target == "gpt_rs.cuda.matmul_bias.f32.v1":
         return fr.linear(ins[0], ins[1], ins[2])
     if target == "gpt_rs.cuda.attention_decode.f32.v1":
-        hq, hkv, hd, cap = attrs["geometry"]["I64Array"]
+        hq, hkv, hd, cap = val("geometry", "I64Array")
         q, k, v = ins[0].reshape(hq, 1, hd), ins[1], ins[2]
         qpos = min(max(int(ins[3][0]), 0), cap - 1)   # DynamicSlice start clamping of the mask it replaces
         kg, vg = np.repeat(k, hq // hkv, axis=0), np.repeat(v, hq // hkv, axis=0)

@@ -203,3 +203,21 @@ def test_attention_decode_f32_matches_oracle(cuda, n_q, n_kv, hd, cap, positions
     kd2, vd2 = torch.from_numpy(ck).to(cuda), torch.from_numpy(cv).to(cuda)
     out2 = ops.attention_decode_f32(qd, kd2, vd2, pos, slot, n_q, n_kv, hd, append=True)
     assert torch.equal(out2, out) and torch.equal(kd2, kd) and torch.equal(vd2, vd)
+
+
+def test_context_length_above_the_launch_bound_is_clamped_and_flagged(cuda):
+    """A visible length in device memory that exceeds what the launch was sized for must not walk off the page table
+    or the split partials: the kernel clamps it and sets code 2 in the status word."""
+    rng = np.random.default_rng(12)
+    lens, n_q, n_kv = [100, 40], 8, 2
+    table, pool = _setup(rng, lens, n_q, n_kv, cuda)
+    stored, q_rots, table_d = _fill(rng, lens, n_q, n_kv, table, pool, cuda)
+    q = torch.stack([q_rots[s][lens[s] - 1] for s in range(2)]).contiguous()
+    slot = torch.arange(2, dtype=torch.int32, device=cuda)
+    bad = torch.tensor([100, 5000], dtype=torch.int32, device=cuda)   # second sequence claims 5000 visible tokens
+    out, status = ops.paged_attention_decode(q, pool, table_d, slot, bad, n_q, n_kv, 100, chunk_pages=4)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 2
+    want = _oracle_decode(stored[:1], lens[:1], n_q, n_kv, [q[0].float().cpu().numpy()])
+    assert np.max(np.abs(out[0].float().cpu().numpy() - want[0])) <= 2e-2   # the well-formed row is unaffected
+    assert torch.isfinite(out.float()).all()

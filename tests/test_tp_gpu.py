@@ -18,6 +18,19 @@ if str(ROOT) not in sys.path:
 
 
 def _worker(rank, world, port, mode, q):
+    """A rank that fails tells the parent through the queue and leaves with os._exit, so that the parent can end the
+    other rank instead of waiting for a collective that will never complete."""
+    try:
+        _worker_body(rank, world, port, mode, q)
+    except BaseException as e:  # noqa: BLE001
+        import traceback
+        q.put(("error", rank, "".join(traceback.format_exception(type(e), e, e.__traceback__))))
+        q.close()
+        q.join_thread()
+        os._exit(1)
+
+
+def _worker_body(rank, world, port, mode, q):
     sys.path.insert(0, str(ROOT))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -73,10 +86,22 @@ def test_tp2_matches_single_gpu_oracle(mode):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, q)) for r in range(2)]
     for p in procs:
         p.start()
-    gathered = q.get(timeout=300)
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    try:
+        gathered = q.get(timeout=300)
+        if gathered and gathered[0] == "error":
+            raise AssertionError(f"rank {gathered[1]} failed:\n{gathered[2]}")
+        for p in procs:
+            p.join(timeout=120)
+        assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    finally:
+        # never leave a rank behind that spins inside a collective on a shared GPU
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=20)
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=20)
     cfg = mr.Cfg("ministral", n_layers=2, d_model=256, n_q=4, n_kv=2, hd=128, d_mlp=512, vocab=512, ctx=128, rot=128)
     params = mr.random_params(cfg, seed=11, std=0.05)
     if mode == 1:
