@@ -196,9 +196,13 @@ constexpr size_t umma_smem_max(int bn, int stages) { return (size_t)stages * (kA
 // one group (barrier wait, proxy fence) are covered by the arithmetic of the others.
 // BITS = 8: per-channel scales are applied to the f32 accumulators in the epilogue, the producers only widen
 // int8 to bf16 (exact); a stage holds 512 sixteen-byte entries instead of 256.
-template <int BITS, int BN, int G, int kStages>
+// kDebug = the instantiation the test switch of gptrs_cuda_debug_matmul_fault launches: poll limit from the launch
+// parameters and the first activation tile withheld on request. The regular instantiation keeps the compile-time
+// limit (a run-time limit and the extra test in the stage loop cost 5 % of a decode-sized launch).
+template <int BITS, int BN, int G, int kStages, bool kDebug>
 __global__ void __launch_bounds__(kUmmaThreads, (2 * (umma_smem_max(BN, kStages) + 1024) <= 227 * 1024) ? 2 : 1)
 umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_map) {
+    const uint32_t limit = kDebug ? p.spin_limit : kSpinLimit;
     constexpr int kBBytes = BN * 128;
     constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
     constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -313,11 +317,11 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
             for (int o = 0; o < kOwn; ++o) {
                 const int it = it_base + G * o;
                 if (it < n_it && !failed) {
-                    if (!mbar_wait_parked(empty0 + slot[o] * 8, par0[o] ^ lap, p.spin_limit)) failed = true;
+                    if (!mbar_wait_parked(empty0 + slot[o] * 8, par0[o] ^ lap, limit)) failed = true;
                     const uint32_t full = full0 + slot[o] * 8;
                     if (t == 0) {  // the group leader also fetches the activation tile of this stage
                         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(full), "r"((uint32_t)kBBytes) : "memory");
-                        if (!(p.debug_starve && it == 0)) tma_load_2d(sB + slot[o] * kBBytes, &x_map, (chunk0 + it) * kBlockK, m0, full);
+                        if (!(kDebug && p.debug_starve && it == 0)) tma_load_2d(sB + slot[o] * kBBytes, &x_map, (chunk0 + it) * kBlockK, m0, full);
                     }
                     const uint32_t a_off = slot[o] * kABytes;
                     const int nxt = it + G * kOwn;
@@ -383,7 +387,7 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
         pdl_wait();  // this warp later reads the residual in the epilogue
         for (int it = 0; it < n_it; ++it) {
             const int s = it % kStages;
-            if (!mbar_wait_relaxed(&full_bar[s], (it / kStages) & 1, p.spin_limit)) { failed = true; break; }
+            if (!mbar_wait_relaxed(&full_bar[s], (it / kStages) & 1, limit)) { failed = true; break; }
             tc_fence_after();
             if (lane == 0) {
                 const uint64_t a_desc = make_smem_desc(smem_u32(sA + s * kABytes));
@@ -401,7 +405,7 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
     // ---------------- epilogue: TMEM -> registers -> pushed to the owner CTA of each output row ----
     // The partial tiles are received in the stage buffers. A CTA may be written to only when its own MMAs have
     // read the last stage, so every thread first sees the MMA-done barrier and then meets the whole cluster.
-    if (!mbar_wait_relaxed(&done_bar, 0, p.spin_limit)) failed = true;
+    if (!mbar_wait_relaxed(&done_bar, 0, limit)) failed = true;
     tc_fence_after();
     sr.barrier_all_done();
     float* slots = reinterpret_cast<float*>(smem);
@@ -836,7 +840,13 @@ int launch_umma(MatmulParams p, dim3 grid, cudaStream_t st) {
     if (rc) return rc;
     static_assert((size_t)kStages * (kABytes + BN * 128) >= (size_t)(BN + 7) * kRedStride * 4, "the receive slots must fit the stage buffers");
     constexpr size_t smem_max = umma_smem_max(BN, kStages);
-    auto kern = umma_w4a16_kernel<BITS, BN, G, kStages>;
+    if (p.debug_starve || p.spin_limit != kSpinLimit) {
+        auto kern = umma_w4a16_kernel<BITS, BN, G, kStages, true>;
+        static PerDeviceOnce attr_once;
+        if (attr_once.first_time()) GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
+        return launch_tc(kern, p, map, grid, kUmmaThreads, smem_max, st);
+    }
+    auto kern = umma_w4a16_kernel<BITS, BN, G, kStages, false>;
     static PerDeviceOnce attr_once;
     if (attr_once.first_time()) GPTRS_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
     return launch_tc(kern, p, map, grid, kUmmaThreads, smem_max, st);
