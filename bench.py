@@ -10,6 +10,11 @@ is one decode step of the whole batch (64 tokens per GPU). Requests are independ
 share nothing on the data path (request-partitioned, weak scaling).
 Prints ONE JSON line on rank 0.
 
+The default line also carries sub-records measured after it in the same process (switch them off with --no-extras):
+"gpt2_fp32" (N = 1: the reference's CPU-runnable case, one sequence), "dp512" (512 ragged requests bin-packed over the
+ranks and served in waves: total work fixed, so its figures scale strongly with N) and, for N > 1, "tp" (one batch of 64
+over a tensor-parallel group of all ranks, with a check that its greedy ids equal a single-rank engine's).
+
 Other modes (none of them the default line): --workload gpt2-fp32 (the reference's CPU-runnable case: one sequence,
 f32 weights), --workload dp512 (512 requests with prompt lengths U{256..4096}, 256 decode steps each, bin-packed over the
 ranks and served in waves of 64: total work fixed, strong scaling), --weights w8a16, --parallelism tp (one batch over a
@@ -271,10 +276,14 @@ GPT2_WORKLOAD = "gpt2-small fp32, one sequence, 32-token prompt, greedy decode w
 
 
 def run_gpt2(args, out, gm, torch, np):
+    print(json.dumps(measure_gpt2(args, gm, torch, np, cpu_baseline=not args.no_cpu_baseline)), file=out)
+
+
+def measure_gpt2(args, gm, torch, np, cpu_baseline: bool, device_index: int = 0):
     """The reference's CPU-runnable case on one GPU: GPT-2 small, f32 weights N(0, 0.02) seed 0, a 32-token
     random prompt, greedy decode; a step is one generated token."""
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(device_index)
+    dev = torch.device("cuda", device_index)
     cfg = gm.ModelConfig.gpt2_small(weight_mode=gm.MODE_F32, max_seqs=1, max_tokens=32, max_logit_rows=32, use_pdl=args.pdl)
     model = gm.LoadedModel(cfg, namespace=7)
     gen_t = torch.Generator(device=dev)
@@ -328,19 +337,16 @@ def run_gpt2(args, out, gm, torch, np):
             "roofline": {"kernel": "sgemm_smallm_kernel (all weight matrices of a step)", "bound": "hbm", "achieved": weight_bytes / (ms / args.steps) / 1e6,
                          "peak": peak, "unit": "GB/s", "frac": weight_bytes / (ms / args.steps) / 1e6 / peak, "traffic": None,
                          "peak_kind": peak_kind, "note": "whole-step figure: f32 weight bytes of one token over the step time"}}
-    if not args.no_cpu_baseline:
+    line["launches_per_token"] = launches / max(args.steps, 1)
+    if cpu_baseline:
         from oracle import cbaseline as cb
         res = cb.time_gpt2_decode(cb.load(prefer_reference=True), n_tokens=8)
         line["cpu_baseline"] = {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": res["kind"], "sample": res["sample"]}
-    print(json.dumps(line), file=out)
+    model.close()
+    return line
 
 
 def run_dp512(args, out, gm, torch, np):
-    """512 requests with prompt lengths U{256..4096} (seed 0), 256 greedy decode steps each: the requests are
-    bin-packed over the ranks by token count, every rank serves its shard in waves of 64 on its own engine and
-    KV pool, and the only exchange is the host-side gather of the generated ids. Times are CUDA events on each
-    engine's stream around every phase, summed per rank, max over ranks."""
-    from gptrs_b200 import parallel
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -350,6 +356,21 @@ def run_dp512(args, out, gm, torch, np):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+    line = measure_dp512(args, gm, torch, np, dist, world, rank, dev)
+    if rank == 0:
+        print(json.dumps(line), file=out)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def measure_dp512(args, gm, torch, np, dist, world, rank, dev):
+    """512 requests with prompt lengths U{256..4096} (seed 0), 256 greedy decode steps each: the requests are
+    bin-packed over the ranks by token count, every rank serves its shard in waves of 64 on its own engine and
+    KV pool, and the only exchange is the host-side gather of the generated ids. Times are CUDA events on each
+    engine's stream around every phase, summed per rank, max over ranks (and the mean, for the imbalance).
+    Returns the JSON line (every rank computes it; rank 0's is the one to print)."""
+    from gptrs_b200 import parallel
     lo, hi = 256, 4096
     lens = np.random.default_rng(0).integers(lo, hi + 1, size=args.requests)
     assign, cost = parallel.partition_requests(lens, args.decode_steps, world)
@@ -395,33 +416,91 @@ def run_dp512(args, out, gm, torch, np):
     merged = parallel.gather_generated(ids, world)
     t = torch.tensor([sum(spans["decode"]), sum(spans["prefill"]), wall["decode"] * 1e3, (wall["decode"] + wall["prefill"]) * 1e3],
                      dtype=torch.float64, device=dev)
+    t_sum = t.clone()
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t_sum, op=dist.ReduceOp.SUM)
     dec_ms, pre_ms, dec_wall_ms, job_ms = (float(x) for x in t)
+    job_mean_ms = float(t_sum[3]) / world
     tokens = args.requests * args.decode_steps
     waves = len(spans["decode"])
-    if rank == 0:
-        assert sorted(merged) == list(range(args.requests)) and all(len(v) == args.decode_steps + 1 for v in merged.values())
-        line = {"metric": "decode_tokens_per_s", "value": tokens / (dec_ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-                "steps": waves * args.decode_steps, "warmup": max(args.warmup, 3), "ms_per_step": dec_ms / max(waves * args.decode_steps, 1),
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "bf16 activations x int4 weights, f32 accumulate", "data": "synthetic",
-                "config": {"workload": f"Ministral-3B-shaped W4A16-g128, {args.requests} requests, prompt lengths U{{{lo}..{hi}}} (seed 0), "
-                                       f"{args.decode_steps} greedy decode steps each, waves of {BATCH} per GPU",
-                           "parallelism": f"dp{world} (requests bin-packed by token count, no collective)",
-                           "rank_token_cost": [int(c) for c in cost], "waves_on_rank0": waves,
-                           "l2": "inputs larger than L2 (1.8 GB weights + KV of the wave streamed per step)",
-                           "cuda_graph": True, "pdl": bool(args.pdl), "kv_cache": "paged bf16, 16-token pages",
-                           "prefill_seconds": round(pre_ms * 1e-3, 2), "prefill_tokens": int(lens.sum()),
-                           "prefill_tokens_per_s": float(lens.sum()) / (pre_ms * 1e-3),
-                           "job_seconds": round(job_ms * 1e-3, 2), "requests_per_s": args.requests / (job_ms * 1e-3)},
-                "e2e": {"value": tokens / (dec_wall_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": BATCH * 4,
-                        "d2h_bytes_per_step": BATCH * 4, "note": "host ids in and sampled ids out on every step; value is the same loop timed with CUDA events"},
-                "gpu_launches": int(launches), "clocks": clocks}
-        print(json.dumps(line), file=out)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    model.close()
+    assert sorted(merged) == list(range(args.requests)) and all(len(v) == args.decode_steps + 1 for v in merged.values())
+    line = {"metric": "decode_tokens_per_s", "value": tokens / (dec_ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": waves * args.decode_steps, "warmup": max(args.warmup, 3), "ms_per_step": dec_ms / max(waves * args.decode_steps, 1),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 activations x int4 weights, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"Ministral-3B-shaped W4A16-g128, {args.requests} requests, prompt lengths U{{{lo}..{hi}}} (seed 0), "
+                                   f"{args.decode_steps} greedy decode steps each, waves of {BATCH} per GPU",
+                       "parallelism": f"dp{world} (requests bin-packed by token count, no collective)",
+                       "rank_token_cost": [int(c) for c in cost], "waves_on_rank0": waves,
+                       "l2": "inputs larger than L2 (1.8 GB weights + KV of the wave streamed per step)",
+                       "cuda_graph": True, "pdl": bool(args.pdl), "kv_cache": "paged bf16, 16-token pages",
+                       "prefill_seconds": round(pre_ms * 1e-3, 2), "prefill_tokens": int(lens.sum()),
+                       "prefill_tokens_per_s": float(lens.sum()) / (pre_ms * 1e-3),
+                       "job_seconds": round(job_ms * 1e-3, 2), "requests_per_s": args.requests / (job_ms * 1e-3),
+                       "rank_time_max_over_mean": job_ms / max(job_mean_ms, 1e-9),
+                       "token_step_cost_per_rank": [int(c) for c in cost]},
+            "e2e": {"value": tokens / (dec_wall_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": BATCH * 4,
+                    "d2h_bytes_per_step": BATCH * 4, "note": "host ids in and sampled ids out on every step; value is the same loop timed with CUDA events"},
+            "gpu_launches": int(launches), "clocks": clocks}
+    return line
+
+
+def measure_tp(args, gm, torch, np, dist, world, rank, dev, single_rank_model, single_cfg):
+    """One batch of 64 requests (2048-token prompts) over a tensor-parallel group of all ranks: ms per decode step and
+    tokens/s, CUDA events, max over ranks. `check`: the tensor-parallel engine and the single-rank engine of rank 0
+    prefill the same eight 48-token prompts and decode eight greedy steps; every id must be the same."""
+    box = [gm.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    steps_total = args.warmup + args.steps + 32
+    model, cfg = build_model(gm, torch, dev, steps_total, args.pdl, args.prefill_chunk, world, rank, box[0])
+    rng = np.random.default_rng(1000)
+    # correctness first, on fresh slots
+    short = [np.random.default_rng(77 + i).integers(0, cfg.vocab, size=48) for i in range(8)]
+
+    def greedy(m):
+        for s_ in range(8):
+            m.reset_sequence(s_)
+        first = m.prefill_many(list(range(8)), short, chunk=args.prefill_chunk)
+        g = gm.Generator(m, first, use_graph=True)
+        ids = [list(first)] + [g.step().tolist() for _ in range(8)]
+        for s_ in range(8):
+            m.reset_sequence(s_)
+        return ids
+
+    tp_ids = greedy(model)
+    ref_box = [greedy(single_rank_model) if rank == 0 else None]
+    dist.broadcast_object_list(ref_box, src=0)
+    differ = sum(int(a != b) for ra, rb in zip(tp_ids, ref_box[0]) for a, b in zip(ra, rb))
+    flags = torch.tensor([differ], dtype=torch.int32, device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+    # timing
+    prompts = [rng.integers(0, cfg.vocab, size=PROMPT_LEN) for _ in range(BATCH)]
+    first = model.prefill_many(list(range(BATCH)), prompts, chunk=args.prefill_chunk)
+    gen = gm.Generator(model, first, use_graph=True)
+    stream = torch.cuda.ExternalStream(lib_stream(model), device=dev)
+    for _ in range(args.warmup):
+        gen.step(read_back=False)
+    gen.sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(args.steps):
+        gen.step(read_back=False)
+    e1.record(stream)
+    gen.sync()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0]) / args.steps
+    del gen
+    model.close()
+    return {"parallelism": f"tp{world}", "batch": BATCH, "ms_per_step": ms, "tokens_per_s": BATCH / (ms * 1e-3),
+            "collective": "ncclAllReduce(sum, f32 [64, 3072]) after o_proj and down_proj, recorded in the decode graph",
+            "check": {"same_greedy_ids_as_single_rank": int(flags[0]) == 0, "ids_that_differ": int(flags[0]), "ids_compared": 72,
+                      "prompts": 8, "steps": 8}}
 
 
 def main():
@@ -650,9 +729,11 @@ def _main(out):
         del gen
         a_ms, a_bytes, chunk = time_attention_kernel(ops, torch, dev, ctx_mid)
         ach = a_bytes / (a_ms * 1e-3) / 1e9
+        cap = ncu_traffic("paged_attention_kernel")
         line["roofline"] = {"kernel": "paged_attention_kernel", "bound": "hbm", "achieved": ach, "peak": peak,
-                            "unit": "GB/s", "frac": ach / peak, "traffic": int(NCU_TRAFFIC["paged_attention_kernel"]["bytes"] * ctx_mid / NCU_TRAFFIC["paged_attention_kernel"]["ctx"]),
-                            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at context 2068 (profiles/paged_attention_kernel_b64_ctx2068.md), scaled by the tokens of this launch",
+                            "unit": "GB/s", "frac": ach / peak, "traffic": int(cap["bytes"] * ctx_mid / cap["ctx"]) if cap else None,
+                            "traffic_source": (f"dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture at context {cap['ctx']} "
+                                               f"({cap['source']}), scaled by the tokens of this launch") if cap else None,
                             "peak_kind": f"{peak_kind} copy bandwidth", "us_per_launch": a_ms * 1e3,
                             "algorithmic_bytes_per_launch": a_bytes, "chunk_pages": chunk,
                             "units": f"{BATCH} sequences x {ctx_mid} tokens x 4096 B KV (one layer)"}
@@ -663,6 +744,20 @@ def _main(out):
         g_us, g_bytes = time_gemv(ops, torch, dev, n=131072, k=3072, n_mats=4, iters=3)
         line["gemv_w4a16_lm_head"] = {"shape": "M=1 N=131072 K=3072", "us_per_launch": g_us,
                                       "achieved_gbs": g_bytes / (g_us * 1e-6) / 1e9, "frac_of_peak": g_bytes / (g_us * 1e-6) / 1e9 / peak}
+    if not args.no_extras and not tp:
+        # sub-records: measured after the headline figures, in the same process group
+        if world > 1:
+            line["tp"] = measure_tp(args, gm, torch, np, dist, world, rank, dev, model, cfg)
+        model.close()
+        del model
+        torch.cuda.empty_cache()
+        sub = argparse.Namespace(**vars(args))
+        sub.warmup = 3
+        line["dp512"] = strip_sub(measure_dp512(sub, gm, torch, np, dist, world, rank, dev))
+        if rank == 0 and world == 1:
+            g2 = argparse.Namespace(**vars(args))
+            g2.steps, g2.warmup = 64, 4
+            line["gpt2_fp32"] = strip_sub(measure_gpt2(g2, gm, torch, np, cpu_baseline=not args.no_cpu_baseline, device_index=local))
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import cbaseline as cb
         # the CPU arm forks one process per host core: run it as its own interpreter, apart from this CUDA process
@@ -685,9 +780,27 @@ def _main(out):
         dist.destroy_process_group()
 
 
-# DRAM traffic per launch of the dominant kernel from the committed ncu capture (profiles/): batch 64,
-# context 2068: 545,838,080 B read + 4,967,936 B written. It grows in proportion to the visible tokens.
-NCU_TRAFFIC: dict = {"paged_attention_kernel": {"bytes": 545838080 + 4967936, "ctx": 2068}}
+def ncu_traffic(kernel: str):
+    """DRAM traffic per launch of a kernel as one committed ncu capture recorded it: reads the summary under profiles/
+    (the lines `dram__bytes_read.sum` / `dram__bytes_write.sum` of its first captured launch and the context length in
+    its file name). Returns {"bytes", "ctx", "source"} or None when the summary is missing."""
+    import re
+    for path in sorted((ROOT / "profiles").glob(f"{kernel}_*ctx*.md")):
+        text = path.read_text()
+        m_ctx = re.search(r"ctx(\d+)", path.name)
+        rd = re.search(r"dram__bytes_read\.sum\s*\|\s*([0-9.]+)\s*\|\s*(\w+)", text)
+        wr = re.search(r"dram__bytes_write\.sum\s*\|\s*([0-9.]+)\s*\|\s*(\w+)", text)
+        if not (m_ctx and rd and wr):
+            continue
+        unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+        total = float(rd.group(1)) * unit.get(rd.group(2), 1.0) + float(wr.group(1)) * unit.get(wr.group(2), 1.0)
+        return {"bytes": total, "ctx": int(m_ctx.group(1)), "source": f"profiles/{path.name}"}
+    return None
+
+
+def strip_sub(rec: dict) -> dict:
+    """A sub-record keeps its figures and drops what only a top-level line needs."""
+    return {k: v for k, v in rec.items() if k not in ("n_gpus", "higher_is_better", "vs_baseline", "data", "warmup")}
 
 
 def lib_stream(model):

@@ -38,3 +38,6 @@ def test_gpu_arm_line(cuda):
     rf = d["roofline"]
     assert rf["bound"] == "hbm" and rf["unit"] == "GB/s" and abs(rf["frac"] - rf["achieved"] / rf["peak"]) < 1e-9 and rf["traffic"] > 0
     assert set(d["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons"}
+    # sub-records of the default line: the 512-request job (strong scaling) and the reference's CPU-runnable case
+    assert d["dp512"]["scaling"] == "strong" and d["dp512"]["value"] > 1000 and d["dp512"]["config"]["job_seconds"] > 0
+    assert d["gpt2_fp32"]["value"] > 100 and d["gpt2_fp32"]["launches_per_token"] > 0 and d["gpt2_fp32"]["roofline"]["frac"] > 0
