@@ -86,6 +86,7 @@ struct Model {
     DevBuf hidden, xn, qkv, q_rot, attn, mlp_h, mlp_g, mlp_u, logits, xn_rows;
     DevBuf d_tokens, d_slot, d_pos, d_ctx, d_rows, d_sampled, d_status, attn_scratch;
     DevBuf sumsq;  // [d_model / 128][max_tokens] row sums of squares of the folded RMSNorm
+    DevBuf history;  // [max_seqs][context_length] token ids by position (the generator re-windows from it)
     bool fold_norm = true, fold_rope = true;
     DevBuf cos_tab, sin_tab;
     int n_rope_pos = 0;
@@ -368,12 +369,29 @@ __global__ void tp_pick_kernel(const TpPickParams p) {
     p.out[r] = p.idx[who * p.rows + r] + who * p.vocab_l;
 }
 
-struct AdvanceParams { int* pos; int* ctx; int n; };
+// End of a generator step: the token a slot consumed goes into its history at the position it had, the sampled id
+// becomes the slot's next input, position and visible length advance.
+struct AdvanceParams { int* tokens; const int* sampled; int* pos; int* ctx; int* history; int n, context_length; };
 __global__ void advance_kernel(const AdvanceParams p) {
     pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < p.n) { p.pos[i] += 1; p.ctx[i] += 1; }
+    if (i < p.n) {
+        const int at = p.pos[i];
+        if (at >= 0 && at < p.context_length) p.history[(size_t)i * p.context_length + at] = p.tokens[i];
+        p.tokens[i] = p.sampled[i];
+        p.pos[i] = at + 1;
+        p.ctx[i] += 1;
+    }
+}
+
+// A forward pass over host-given rows: every (token, slot, position) goes into the slot's history.
+struct HistoryParams { const int* tokens; const int* slot; const int* pos; int* history; int n, context_length; };
+__global__ void record_history_kernel(const HistoryParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < p.n && p.pos[i] >= 0 && p.pos[i] < p.context_length) p.history[(size_t)p.slot[i] * p.context_length + p.pos[i]] = p.tokens[i];
 }
 
 int attention_plan(const Model& m, int T, int max_ctx, size_t scratch_bytes, int* chunk_pages);
@@ -879,6 +897,7 @@ int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
     if ((rc = m.logits.alloc((size_t)max_rows * m.vocab_l * 4))) return rc;
     if (m.tp > 1 && ((rc = m.partial.alloc((size_t)T * D * 4)) || (rc = m.tp_vals.alloc((size_t)max_rows * 4)) || (rc = m.tp_idx.alloc((size_t)max_rows * 4)) ||
                      (rc = m.tp_gvals.alloc((size_t)m.tp * max_rows * 4)) || (rc = m.tp_gidx.alloc((size_t)m.tp * max_rows * 4)))) return rc;
+    if ((rc = m.history.alloc((size_t)c.max_seqs * c.context_length * 4, true))) return rc;
     for (DevBuf* b : {&m.d_tokens, &m.d_slot, &m.d_pos, &m.d_ctx, &m.d_rows, &m.d_sampled})
         if ((rc = b->alloc((size_t)std::max(T, max_rows) * 4, true))) return rc;
     if ((rc = m.d_status.alloc(4, true))) return rc;
@@ -1012,6 +1031,11 @@ int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* h, const int32_t* h_
     // with no requested rows the pass still runs (it fills the KV cache); logits of row 0 are discarded
     const int rows = n_logit_rows > 0 ? n_logit_rows : 1;
     if (n_logit_rows == 0) GPTRS_CUDA_OK(cudaMemsetAsync(m.d_rows.p, 0, 4, s));
+    {
+        HistoryParams hp = {m.d_tokens.as<int>(), m.d_slot.as<int>(), m.d_pos.as<int>(), m.history.as<int>(), T, c.context_length};
+        ++m.launches;
+        if ((rc = launch_kernel(record_history_kernel, dim3((T + 127) / 128), dim3(128), 0, s, 1, hp))) return rc;
+    }
     rc = enqueue_forward(m, T, max_ctx, chunk, rows, false, temperature, prefill_groups);
     if (rc) return rc;
     if (h_logits && n_logit_rows)
@@ -1047,12 +1071,65 @@ int gptrs_cuda_generator_begin(gptrs_model* h, int batch, const int32_t* h_first
     return GPTRS_OK;
 }
 
+namespace {
+
+// See the call in gptrs_cuda_generator_step. The generator's device state (input ids, positions, visible lengths of
+// slots 0 .. B-1) shares its buffers with the forward pass used for the re-prefill, so it is read back first and written
+// again afterwards.
+int slide_windows(Model& m, gptrs_model* h, int B, const int32_t* h_tokens_in) {
+    const auto& c = m.cfg;
+    const int C = c.context_length;
+    cudaStream_t s = m.stream;
+    std::vector<int32_t> cur(B);
+    if (h_tokens_in) memcpy(cur.data(), h_tokens_in, (size_t)B * 4);
+    else GPTRS_CUDA_OK(cudaMemcpyAsync(cur.data(), m.d_tokens.p, (size_t)B * 4, cudaMemcpyDeviceToHost, s));
+    GPTRS_CUDA_OK(cudaStreamSynchronize(s));
+    std::vector<int32_t> window(C), slots, pos;
+    for (int b = 0; b < B; ++b) {
+        if (m.seq_len[b] < C) continue;
+        if (C < 2) return fail(GPTRS_SPEC_VIOLATION, "context_length 1 leaves no window to slide");
+        // tokens at positions 1 .. C-1 of the old window become positions 0 .. C-2 of the new one
+        GPTRS_CUDA_OK(cudaMemcpy(window.data(), m.history.as<int32_t>() + (size_t)b * C + 1, (size_t)(C - 1) * 4, cudaMemcpyDeviceToHost));
+        int rc = gptrs_cuda_model_reset_sequence(h, b);
+        if (rc) return rc;
+        for (int o = 0; o < C - 1; o += c.max_tokens) {
+            const int n = std::min(c.max_tokens, C - 1 - o);
+            slots.assign(n, b);
+            pos.resize(n);
+            for (int i = 0; i < n; ++i) pos[i] = o + i;
+            rc = gptrs_cuda_model_forward_with_decode_cache(h, window.data() + o, slots.data(), pos.data(), n, nullptr, 0, nullptr, nullptr, 0.f, 0);
+            if (rc) return rc;
+        }
+    }
+    // the generator's rows again: slot b at its (new) length
+    const int stride = std::max(c.max_tokens, c.max_logit_rows > 0 ? c.max_logit_rows : c.max_seqs);
+    int32_t* st = m.h_stage;
+    for (int b = 0; b < B; ++b) { st[b] = cur[b]; st[stride + b] = b; st[2 * stride + b] = m.seq_len[b]; st[3 * stride + b] = m.seq_len[b] + 1; }
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_tokens.p, st, (size_t)B * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_slot.p, st + stride, (size_t)B * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_pos.p, st + 2 * stride, (size_t)B * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_ctx.p, st + 3 * stride, (size_t)B * 4, cudaMemcpyHostToDevice, s));
+    GPTRS_CUDA_OK(cudaStreamSynchronize(s));
+    return GPTRS_OK;
+}
+
+}  // namespace
+
 int gptrs_cuda_generator_step(gptrs_model* h, const int32_t* h_tokens_in, int32_t* h_tokens_out, int use_graph) {
     GPTRS_REQUIRE(h, "null pointer");
     Model& m = *reinterpret_cast<Model*>(h);
     const auto& c = m.cfg;
     const int B = m.gen_batch;
     GPTRS_REQUIRE(m.finalized && B > 0, "generator_begin has not been called");
+    // Context-window slide (Generator::step, crates/gpt-rs/src/inference/generate.rs:127-134): a sequence whose next
+    // token would not fit drops its caches and is processed again from its last context_length tokens, at positions
+    // restarting from 0. Here the window without its last token is prefilled again (positions 0 .. context_length - 2)
+    // and the step below then runs the last token at position context_length - 1 like any other decode row.
+    {
+        bool any = false;
+        for (int b = 0; b < B; ++b) any = any || m.seq_len[b] >= c.context_length;
+        if (any) { int rc = slide_windows(m, h, B, h_tokens_in); if (rc) return rc; }
+    }
     int max_ctx = 1;
     for (int b = 0; b < B; ++b) {
         GPTRS_REQUIRE(m.seq_len[b] < c.context_length, "sequence reached context_length");
@@ -1078,9 +1155,9 @@ int gptrs_cuda_generator_step(gptrs_model* h, const int32_t* h_tokens_in, int32_
     auto body = [&]() -> int {
         int r = enqueue_forward(m, B, bucket, chunk, B, true, 0.f);
         if (r) return r;
-        // next step: the sampled ids become the inputs, positions advance
-        GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_tokens.p, m.d_sampled.p, (size_t)B * 4, cudaMemcpyDeviceToDevice, s));
-        AdvanceParams ap = {m.d_pos.as<int>(), m.d_ctx.as<int>(), B};
+        // next step: the consumed ids go into the history, the sampled ids become the inputs, positions advance
+        AdvanceParams ap = {m.d_tokens.as<int>(), m.d_sampled.as<int>(), m.d_pos.as<int>(), m.d_ctx.as<int>(), m.history.as<int>(), B,
+                            c.context_length};
         ++m.launches;
         return launch_kernel(advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s, 1, ap);
     };

@@ -518,7 +518,9 @@ static int paged_attention_launch(bool multi, const void* d_q, const void* d_kv_
     p.status = d_status;
     p.T = (int)n_tokens; p.Hq = (int)n_q_heads; p.Hkv = (int)n_kv_heads;
     p.max_pages = (int)max_pages; p.chunk_pages = (int)chunk_pages; p.max_splits = (int)splits;
-    p.max_len = (int)std::min<int64_t>(max_ctx_len, max_pages * kPageTokens);
+    // what the launch geometry covers: `splits` chunks of chunk_pages pages, within one page-table row (a recorded
+    // launch may be replayed for any length up to that, not only up to the max_ctx_len it was planned with)
+    p.max_len = (int)std::min<int64_t>(splits * chunk_pages * kPageTokens, max_pages * kPageTokens);
     p.scale_log2 = kLog2e / sqrtf((float)head_dim);
     static const int depth = [] { const char* e = getenv("GPTRS_ATTN_DEPTH"); return (e && atoi(e) == 3) ? 3 : 2; }();
     static PerDeviceOnce attr_once;

@@ -4,9 +4,11 @@
 // (crates/gpt-rs/src/backend/param_resolver.rs:11-50).
 #include "tensor.h"
 
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
+#include <vector>
 
 namespace gptrs {
 
@@ -16,6 +18,91 @@ size_t dtype_size(int dtype) {
         case GPTRS_F16: case GPTRS_BF16: return 2;
         case GPTRS_I1: case GPTRS_SI8: case GPTRS_UI8: return 1;
         default: return 0;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Device memory of tensor handles comes from a pool of freed blocks, per device and by (rounded) size, as the
+// reference's own GPU backend keeps one (crates/gpt-rs-backend-triton/src/device.rs:719-759): a decode step hands
+// back the previous step's K/V handles and asks for the same sizes again, so in the steady state no call reaches
+// cudaMalloc, and no release reaches cudaFree (which would synchronise the device). The pool keeps at most
+// GPTRS_POOL_MAX_MB (default 8192) of freed blocks per device; beyond that a block is returned to the driver.
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+
+struct DevicePool {
+    std::mutex mu;
+    std::map<size_t, std::vector<void*>> free_blocks;
+    size_t cached_bytes = 0;
+};
+DevicePool g_pools[kMaxDevices];
+std::atomic<int64_t> g_driver_allocs{0}, g_pool_hits{0}, g_driver_frees{0};
+
+size_t pool_round(size_t bytes) { return (bytes + 255) & ~(size_t)255; }
+size_t pool_cap() {
+    static const size_t cap = [] { const char* e = getenv("GPTRS_POOL_MAX_MB"); const long v = e ? atol(e) : 8192; return (size_t)(v < 0 ? 0 : v) << 20; }();
+    return cap;
+}
+
+}  // namespace
+
+cudaError_t pool_alloc(void** out, size_t bytes, int* device) {
+    const int dev = current_device() & (kMaxDevices - 1);
+    const size_t need = pool_round(bytes);
+    *device = dev;
+    DevicePool& pool = g_pools[dev];
+    {
+        std::lock_guard<std::mutex> lk(pool.mu);
+        auto it = pool.free_blocks.find(need);
+        if (it != pool.free_blocks.end() && !it->second.empty()) {
+            *out = it->second.back();
+            it->second.pop_back();
+            pool.cached_bytes -= need;
+            g_pool_hits.fetch_add(1, std::memory_order_relaxed);
+            return cudaSuccess;
+        }
+    }
+    g_driver_allocs.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaMalloc(out, need);
+    if (e != cudaSuccess) {
+        // give the driver what the pool holds and try once more
+        std::vector<void*> drop;
+        {
+            std::lock_guard<std::mutex> lk(pool.mu);
+            for (auto& kv : pool.free_blocks) { drop.insert(drop.end(), kv.second.begin(), kv.second.end()); kv.second.clear(); }
+            pool.cached_bytes = 0;
+        }
+        for (void* p : drop) { cudaFree(p); g_driver_frees.fetch_add(1, std::memory_order_relaxed); }
+        cudaGetLastError();
+        e = cudaMalloc(out, need);
+    }
+    return e;
+}
+
+void pool_free(void* ptr, size_t bytes, int device) {
+    if (!ptr) return;
+    const size_t need = pool_round(bytes);
+    DevicePool& pool = g_pools[device & (kMaxDevices - 1)];
+    {
+        std::lock_guard<std::mutex> lk(pool.mu);
+        if (pool.cached_bytes + need <= pool_cap()) {
+            pool.free_blocks[need].push_back(ptr);
+            pool.cached_bytes += need;
+            return;
+        }
+    }
+    g_driver_frees.fetch_add(1, std::memory_order_relaxed);
+    cudaFree(ptr);
+}
+
+void pool_stats(int64_t* driver_allocs, int64_t* pool_hits, int64_t* driver_frees, int64_t* cached_bytes) {
+    if (driver_allocs) *driver_allocs = g_driver_allocs.load();
+    if (pool_hits) *pool_hits = g_pool_hits.load();
+    if (driver_frees) *driver_frees = g_driver_frees.load();
+    if (cached_bytes) {
+        int64_t total = 0;
+        for (auto& p : g_pools) { std::lock_guard<std::mutex> lk(p.mu); total += (int64_t)p.cached_bytes; }
+        *cached_bytes = total;
     }
 }
 
@@ -37,11 +124,11 @@ int tensor_alloc(int dtype, int rank, const int64_t* dims, bool zero, Tensor** o
     }
     t->bytes = (size_t)t->numel() * dtype_size(dtype);
     if (t->bytes) {
-        cudaError_t e = cudaMalloc(&t->data, t->bytes);
+        cudaError_t e = pool_alloc(&t->data, t->bytes, &t->device);
         if (e != cudaSuccess) { delete t; return fail(GPTRS_EXECUTION, std::string("cudaMalloc: ") + cudaGetErrorString(e)); }
         if (zero) {
             e = cudaMemset(t->data, 0, t->bytes);
-            if (e != cudaSuccess) { cudaFree(t->data); delete t; return fail(GPTRS_EXECUTION, "cudaMemset failed"); }
+            if (e != cudaSuccess) { pool_free(t->data, t->bytes, t->device); delete t; return fail(GPTRS_EXECUTION, "cudaMemset failed"); }
         }
     }
     *out = t;
@@ -52,10 +139,12 @@ void tensor_retain(Tensor* t) { if (t) t->refs.fetch_add(1, std::memory_order_re
 
 void tensor_release(Tensor* t) {
     if (t && t->refs.fetch_sub(1, std::memory_order_acq_rel) == 1) {
-        if (t->data && t->owns) cudaFree(t->data);
+        if (t->data && t->owns) pool_free(t->data, t->bytes, t->device);
         Tensor* base = t->base;
+        Tensor* derived = t->derived;
         delete t;
         tensor_release(base);
+        tensor_release(derived);
     }
 }
 
@@ -138,6 +227,11 @@ int gptrs_cuda_to_literal(const gptrs_tensor* h, void* h_dst, size_t cap, size_t
 
 void gptrs_cuda_tensor_retain(gptrs_tensor* h) { tensor_retain(reinterpret_cast<Tensor*>(h)); }
 void gptrs_cuda_tensor_release(gptrs_tensor* h) { tensor_release(reinterpret_cast<Tensor*>(h)); }
+
+int gptrs_cuda_alloc_stats(int64_t* driver_allocs, int64_t* pool_hits, int64_t* driver_frees, int64_t* cached_bytes) {
+    pool_stats(driver_allocs, pool_hits, driver_frees, cached_bytes);
+    return GPTRS_OK;
+}
 
 int gptrs_cuda_param_get(uint64_t id_lo, uint64_t id_hi, gptrs_tensor** out) {
     GPTRS_REQUIRE(out, "null pointer");

@@ -16,7 +16,12 @@ struct Tensor {
     void* data = nullptr;
     size_t bytes = 0;
     bool owns = true;
+    int device = 0;          // ordinal the storage was allocated on (its pool)
     Tensor* base = nullptr;  // a view (Reshape) keeps the tensor that owns the storage alive
+    // A layout derived from this tensor and memoised with it (retained): the repacked kernel layout of a quantised
+    // weight, built the first time a fused matmul meets the handle (run_program's derived-parameter memo).
+    Tensor* derived = nullptr;
+    const void* derived_with = nullptr;  // the second operand the layout was derived with (the scales' storage)
     int64_t numel() const;
 };
 
@@ -24,6 +29,11 @@ size_t dtype_size(int dtype);
 int tensor_alloc(int dtype, int rank, const int64_t* dims, bool zero, Tensor** out);
 void tensor_retain(Tensor* t);
 void tensor_release(Tensor* t);
+
+// Pooled device memory of tensor handles (tensor.cu) and its counters.
+cudaError_t pool_alloc(void** out, size_t bytes, int* device);
+void pool_free(void* ptr, size_t bytes, int device);
+void pool_stats(int64_t* driver_allocs, int64_t* pool_hits, int64_t* driver_frees, int64_t* cached_bytes);
 
 // ParamResolver memo (process-wide): returns a retained tensor or nullptr.
 Tensor* param_lookup(uint64_t lo, uint64_t hi);

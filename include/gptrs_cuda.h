@@ -350,6 +350,10 @@ int gptrs_cuda_materialize_zeroed(int dtype, int rank, const int64_t* dims, gptr
 int gptrs_cuda_to_literal(const gptrs_tensor* h, void* h_dst, size_t cap, size_t* written);
 int gptrs_cuda_tensor_spec(const gptrs_tensor* h, int* dtype, int* rank, int64_t* dims, int dims_cap);
 void* gptrs_cuda_tensor_data(const gptrs_tensor* h); /* device pointer */
+/* Counters of the pooled allocator behind tensor handles (materialize, run_program results and temporaries): calls
+ * that reached cudaMalloc, requests served from freed blocks, blocks returned to the driver, bytes held for reuse.
+ * The reference's GPU backend pools device memory the same way (crates/gpt-rs-backend-triton/src/device.rs:719-759). */
+int gptrs_cuda_alloc_stats(int64_t* driver_allocs, int64_t* pool_hits, int64_t* driver_frees, int64_t* cached_bytes);
 void gptrs_cuda_tensor_retain(gptrs_tensor* h);
 void gptrs_cuda_tensor_release(gptrs_tensor* h);
 /* ParamResolver::{get,set} (crates/gpt-rs/src/backend/param_resolver.rs:11-17): memo of leaf and

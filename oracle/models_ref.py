@@ -192,6 +192,35 @@ class RefModel:
         return (out, np.stack(rows)) if return_logits else out
 
 
+def generate_greedy_windowed(model: RefModel, prompt, n_new: int):
+    """Generator::{new, step} with a KV cache, including the context-window slide
+    (crates/gpt-rs/src/inference/generate.rs:59-169): when the tokens since `window_start` outnumber the model's
+    context length, the window start moves up, every cache is dropped and the whole window is processed again from
+    position 0. Greedy sampling. Returns the n_new generated ids."""
+    cfg = model.cfg
+    model.reset()
+    tokens = list(prompt)
+    window_start, processed = 0, 0
+    logits = model.forward(tokens)[-1]
+    processed = len(tokens)
+    out = []
+    for step in range(n_new):
+        nxt = fr.argmax_host_sampler(logits)
+        out.append(nxt)
+        tokens.append(nxt)
+        if step + 1 == n_new:
+            break   # step_final: no forward pass for a token nobody will sample from
+        if len(tokens) - window_start > cfg.ctx:
+            window_start = len(tokens) - cfg.ctx
+            model.reset()
+            processed = 0
+        context = tokens[window_start:]
+        chunk = context[min(processed, len(context)):]
+        logits = model.forward(chunk)[-1]
+        processed = len(context)
+    return out
+
+
 def quantised_params(cfg: Cfg, params, mode: str):
     """Replaces every Linear weight (and lm_head) by its exactly dequantised W4 / W8 version."""
     from . import quant_ref as qr

@@ -281,3 +281,29 @@ def test_packed_prefill_of_several_prompts_matches_oracle(cuda, lens, chunk):
     for s in range(n):
         want = refs[s].forward([first[s]])[-1]
         assert float(np.max(np.abs(lg[s] - want))) / max(1.0, float(np.max(np.abs(want)))) <= 1.5e-2, s
+
+
+@pytest.mark.parametrize("kind", ["gpt", "ministral"])
+def test_generator_slides_the_context_window(cuda, kind):
+    """Generating past context_length: the reference drops the caches and runs its last context_length tokens again from
+    position 0 on every further step (generate.rs:127-134). Same ids as the oracle's restatement, f32, with and
+    without a CUDA graph, ids fed back on the device or through the host."""
+    if kind == "gpt":
+        cfg = mr.Cfg("gpt", n_layers=2, d_model=32, n_q=4, n_kv=4, hd=8, d_mlp=64, vocab=50, ctx=12)
+    else:
+        cfg = mr.Cfg("ministral", n_layers=2, d_model=16, n_q=4, n_kv=2, hd=4, d_mlp=32, vocab=48, ctx=10, rot=4, theta=1e4)
+    params = mr.random_params(cfg, seed=3, std=0.4)
+    prompt, n_new = [5, 9, 2, 7], 24
+    want = mr.generate_greedy_windowed(mr.RefModel(cfg, params), prompt, n_new)
+    m = _load(cfg, params, max_seqs=2, max_tokens=8)   # re-prefill in chunks of 8 rows
+    for use_graph, host_fed in ((True, False), (False, True)):
+        m.reset_sequence(0)
+        _, first = m.prefill(0, prompt)
+        got = [first]
+        gen = gm.Generator(m, [first], use_graph=use_graph)
+        cur = None
+        for _ in range(n_new - 1):
+            cur = gen.step(tokens_in=cur if host_fed else None)
+            got.append(int(cur[0]))
+        assert got == want, (use_graph, host_fed)
+        assert m.sequence_length(0) == cfg.ctx   # the window is full and stays full
