@@ -276,7 +276,94 @@ GPT2_WORKLOAD = "gpt2-small fp32, one sequence, 32-token prompt, greedy decode w
 
 
 def run_gpt2(args, out, gm, torch, np):
+    if args.path == "run_program":
+        print(json.dumps(measure_gpt2_run_program(args, torch, np)), file=out)
+        return
     print(json.dumps(measure_gpt2(args, gm, torch, np, cpu_baseline=not args.no_cpu_baseline)), file=out)
+
+
+def measure_gpt2_run_program(args, torch, np):
+    """GPT-2 small decode driven ONLY through PortableBackend::run_program: the captured one-token decode program (the
+    op sequence gpt.rs' functionals emit, capacity bucket 128), its weights as parameter handles, the previous step's
+    K/V handles in and fresh ones out every step, the next id picked by the backend's decode sampler. Timed on the host
+    clock around the loop (every step ends with the synchronous read of the sampled id)."""
+    from types import SimpleNamespace
+    from gptrs_b200 import ptir
+    from gptrs_b200.backend import CudaBackend
+    torch.cuda.set_device(0)
+    cfg = SimpleNamespace(kind="gpt", n_layers=12, d_model=768, n_q=12, n_kv=12, hd=64, d_mlp=3072, vocab=50257, ctx=1024, eps=1e-5, rot=0)
+    cap = 128
+    be = CudaBackend()
+    builder, names = ptir.decode_step_program(cfg, cap)
+    prog = be.prepare(builder.to_json())
+    rng = np.random.default_rng(0)
+    weights = {}
+    shapes = {p.id: p.dims for p in builder.params}
+    for n, p in zip(names, builder.params):
+        if n.startswith("@"):
+            continue
+        if n.endswith("gamma"):
+            w = np.ones(p.dims, np.float32)
+        elif n.endswith("beta") or ".b_" in n:
+            w = np.zeros(p.dims, np.float32)
+        else:
+            w = rng.normal(0.0, 0.02, size=p.dims).astype(np.float32)
+        weights[n] = be.materialize(w)
+    caches = [(be.materialize_zeroed(np.float32, [cfg.n_kv, cap, cfg.hd]), be.materialize_zeroed(np.float32, [cfg.n_kv, cap, cfg.hd]))
+              for _ in range(cfg.n_layers)]
+    state = {"tok": 0, "pos": 0}
+
+    def step():
+        tok, pos = state["tok"], state["pos"]
+        small = {"@tokens": np.array([tok], np.int32), "@positions": np.array([pos], np.int32),
+                 "@update_starts": np.array([0, pos, 0], np.int32), "@query_start": np.array([pos], np.int32)}
+        hs = []
+        for n in names:
+            if n in small:
+                hs.append(be.materialize(small[n]))
+            elif n.startswith("@k"):
+                hs.append(caches[int(n[2:])][0])
+            elif n.startswith("@v"):
+                hs.append(caches[int(n[2:])][1])
+            else:
+                hs.append(weights[n])
+        res = prog.run(hs)
+        for l in range(cfg.n_layers):
+            caches[l] = (res[1 + 2 * l], res[2 + 2 * l])
+        state["tok"] = be.sample_decode_token(res[0], 0.0)
+        state["pos"] = pos + 1
+
+    prompt = np.random.default_rng(0).integers(0, cfg.vocab, size=32)
+    for t in prompt[:-1]:    # the prompt, one token per call (set-up, not timed)
+        state["tok"] = int(t)
+        step()
+    state["tok"] = int(prompt[-1])
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    allocs0 = be.alloc_stats()["driver_allocs"]
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    st, al = be.run_program_stats(), be.alloc_stats()
+    weight_bytes = 4 * sum(int(np.prod(p.dims)) for n, p in zip(names, builder.params) if not n.startswith("@") and "embeddings" not in n)
+    peak, peak_kind = _peaks()
+    return {"metric": "decode_tokens_per_s", "value": args.steps / dt, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": args.steps / dt / GPT2_PUBLISHED_TOKENS_PER_S, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": GPT2_WORKLOAD.replace("the dense-cache f32 kernels", "every step one PortableBackend::run_program call"),
+                       "path": "run_program", "capacity_bucket": cap, "l2": "494 MB of f32 weights streamed per token (> L2)",
+                       "program_instructions": len(builder.body)},
+            "e2e": {"value": args.steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": 32, "d2h_bytes_per_step": 8,
+                    "note": "the timed loop is the end-to-end loop: host arguments in, sampled id out, every step"},
+            "gpu_launches": int(st["last_launches"]) * args.steps, "launches_per_token": int(st["last_launches"]),
+            "fused_rewrites": int(st["last_fused"]), "driver_allocs_in_timed_region": int(al["driver_allocs"] - allocs0),
+            "pool_hits": int(al["pool_hits"]),
+            "roofline": {"kernel": "all weight matrices of a step", "bound": "hbm", "achieved": weight_bytes / dt * args.steps / 1e9,
+                         "peak": peak, "unit": "GB/s", "frac": weight_bytes / dt * args.steps / 1e9 / peak, "traffic": None,
+                         "peak_kind": peak_kind}}
 
 
 def measure_gpt2(args, gm, torch, np, cpu_baseline: bool, device_index: int = 0):
@@ -538,6 +625,9 @@ def _main(out):
                     help="gpt2-fp32 = the reference's CPU-runnable case (one sequence, 32-token prompt, 64 greedy tokens); "
                          "dp512 = 512 requests with prompt lengths U{256..4096}, 256 decode steps each, partitioned over the ranks "
                          "(total work fixed: strong scaling; not the default line)")
+    ap.add_argument("--path", default="engine", choices=["engine", "run_program"],
+                    help="gpt2-fp32 only: engine = the model-level ABI (default); run_program = every decode step one "
+                         "PortableBackend::run_program call on the captured decode program")
     ap.add_argument("--requests", type=int, default=512, help="dp512: number of requests")
     ap.add_argument("--decode-steps", type=int, default=256, help="dp512: decode steps per request")
     ap.add_argument("--weights", default="w4a16", choices=["w4a16", "w8a16"],
@@ -764,6 +854,9 @@ def _main(out):
             g2 = argparse.Namespace(**vars(args))
             g2.steps, g2.warmup = 64, 4
             line["gpt2_fp32"] = strip_sub(measure_gpt2(g2, gm, torch, np, cpu_baseline=not args.no_cpu_baseline, device_index=local))
+            rp = measure_gpt2_run_program(g2, torch, np)
+            line["gpt2_fp32"]["run_program_path"] = {k: rp[k] for k in ("value", "ms_per_step", "launches_per_token", "fused_rewrites",
+                                                                        "driver_allocs_in_timed_region")}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import cbaseline as cb
         # the CPU arm forks one process per host core: run it as its own interpreter, apart from this CUDA process

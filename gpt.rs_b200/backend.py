@@ -10,8 +10,9 @@ import numpy as np
 
 from . import check, lib
 
-_DT = {np.dtype(np.float32): 0, np.dtype(np.int32): 3, np.dtype(np.bool_): 4, np.dtype(np.int8): 5, np.dtype(np.uint8): 6}
-_NP = {0: np.float32, 3: np.int32, 4: np.bool_, 5: np.int8, 6: np.uint8}
+_DT = {np.dtype(np.float32): 0, np.dtype(np.float16): 1, np.dtype(np.int32): 3, np.dtype(np.bool_): 4, np.dtype(np.int8): 5,
+       np.dtype(np.uint8): 6}
+_NP = {0: np.float32, 1: np.float16, 2: np.uint16, 3: np.int32, 4: np.bool_, 5: np.int8, 6: np.uint8}   # bf16 comes back as its bit patterns
 
 
 class TensorHandle:
@@ -38,6 +39,28 @@ class TensorHandle:
             if self._p and self._p.value:
                 lib().gptrs_cuda_tensor_release(self._p)
                 self._p = ctypes.c_void_p()
+        except Exception:
+            pass
+
+
+class PreparedProgram:
+    """Handle of a prepared program (see CudaBackend.prepare)."""
+
+    def __init__(self, h):
+        self._h = h
+        self._outs = (ctypes.c_void_p * 1024)()
+        self._n = ctypes.c_size_t()
+
+    def run(self, inputs: list, stream: int | None = None) -> list:
+        ins = (ctypes.c_void_p * max(len(inputs), 1))(*[h._p.value for h in inputs])
+        check(lib().gptrs_cuda_program_run(self._h, ins, len(inputs), self._outs, 1024, ctypes.byref(self._n), stream))
+        return [TensorHandle(self._outs[i]) for i in range(self._n.value)]
+
+    def __del__(self):
+        try:
+            if self._h and self._h.value:
+                lib().gptrs_cuda_program_release(self._h)
+                self._h = ctypes.c_void_p()
         except Exception:
             pass
 
@@ -79,6 +102,13 @@ class CudaBackend:
         check(lib().gptrs_cuda_run_program(text, len(text), ins, len(inputs), outs, cap, ctypes.byref(n), stream))
         return [TensorHandle(outs[i]) for i in range(n.value)]
 
+    def prepare(self, program) -> "PreparedProgram":
+        """gptrs_cuda_program_prepare: parse / verify / rewrite / plan once, run many times."""
+        text = (program if isinstance(program, str) else json.dumps(program, separators=(",", ":"))).encode()
+        h = ctypes.c_void_p()
+        check(lib().gptrs_cuda_program_prepare(text, len(text), ctypes.byref(h)))
+        return PreparedProgram(h)
+
     def execute_instruction(self, instruction, inputs: list, stream: int | None = None) -> list[TensorHandle]:
         """PortableBackend::execute_instruction: one handle per operand (None for a Literal operand)."""
         text = (instruction if isinstance(instruction, str) else json.dumps(instruction, separators=(",", ":"))).encode()
@@ -100,6 +130,14 @@ class CudaBackend:
     def set_fusion(self, enabled: bool):
         check(lib().gptrs_cuda_set_fusion(int(enabled)))
 
+    def set_buffer_plan(self, enabled: bool):
+        check(lib().gptrs_cuda_set_buffer_plan(int(enabled)))
+
+    def alloc_stats(self) -> dict:
+        v = [ctypes.c_int64() for _ in range(4)]
+        check(lib().gptrs_cuda_alloc_stats(*[ctypes.byref(x) for x in v]))
+        return dict(zip(("driver_allocs", "pool_hits", "driver_frees", "cached_bytes"), (x.value for x in v)))
+
     # ParamResolver::{get,set}
     def param_set(self, stable_id: int, h: TensorHandle):
         check(lib().gptrs_cuda_param_set(stable_id & (2 ** 64 - 1), stable_id >> 64, h._p))
@@ -120,6 +158,17 @@ class CudaBackend:
                                                          int(random_u is not None), float(random_u or 0.0),
                                                          ctypes.byref(has), ctypes.byref(tok), None))
         return int(tok.value) if has.value else None
+
+
+def pipeline(phase: str, program) -> tuple[str, int]:
+    """gptrs_cuda_pipeline: one of the four BackendPipeline hooks (pre, legalize, fuse, cleanup) as a host-only
+    text-to-text pass. Returns (program JSON, number of rewrites)."""
+    text = (program if isinstance(program, str) else json.dumps(program, separators=(",", ":"))).encode()
+    n, fused = ctypes.c_size_t(), ctypes.c_int64()
+    check(lib().gptrs_cuda_pipeline(phase.encode(), text, len(text), None, 0, ctypes.byref(n), ctypes.byref(fused)))
+    buf = ctypes.create_string_buffer(n.value)
+    check(lib().gptrs_cuda_pipeline(phase.encode(), text, len(text), buf, n.value, ctypes.byref(n), ctypes.byref(fused)))
+    return buf.raw[:n.value].decode(), int(fused.value)
 
 
 def pipeline_fuse(program) -> tuple[str, int]:

@@ -40,6 +40,7 @@ __device__ __forceinline__ float block_max(float v, float* sh) {
 
 struct NormParams {
     float* hidden;             // [T][D] f32 residual stream (updated in place when delta != null)
+    const float* hidden_in;    // when set: the rows are read from here and `hidden` (may be null) receives the sums
     const void* delta;         // optional [T][D] to add first (f32 or bf16)
     const float* delta_bias;   // optional [D] f32 added together with delta
     const float* gamma;        // [D]
@@ -59,21 +60,29 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams
     const int row = blockIdx.x, tid = threadIdx.x;
     pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
     pdl_wait();
-    float* h = p.hidden + (size_t)row * p.D;
+    const float* hin = (p.hidden_in ? p.hidden_in : p.hidden) + (size_t)row * p.D;
+    float* hst = p.hidden ? p.hidden + (size_t)row * p.D : nullptr;
     constexpr int kKeep = 16;
     constexpr int kKeepSpan = kKeep * kNormThreads;  // elements held in registers
     float keep[kKeep];
-    auto load = [&](int i) {
-        float v = h[i];
+    auto value = [&](int i) {   // the row element with the update added (the same value every time it is asked for)
+        float v = hin[i];
         if (p.delta) {
             float d = p.delta_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.delta)[(size_t)row * p.D + i])
                                    : static_cast<const float*>(p.delta)[(size_t)row * p.D + i];
             if (p.delta_bias) d += p.delta_bias[i];
             v += d;
-            h[i] = v;
         }
         return v;
     };
+    auto load = [&](int i) {
+        const float v = value(i);
+        if (p.delta && hst) hst[i] = v;
+        return v;
+    };
+    // elements beyond the register span are read a second time: from where this thread stored the sum (in place, the
+    // input itself no longer holds the addend-free value), else recomputed
+    auto again = [&](int i) { return (p.delta && hst) ? hst[i] : value(i); };
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < kKeep; ++j) {
@@ -98,7 +107,7 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams
             const int i = tid + j * kNormThreads;
             if (i < p.D) { float c = keep[j] - mean; sq += c * c; }
         }
-        for (int i = kKeepSpan + tid; i < p.D; i += kNormThreads) { float c = h[i] - mean; sq += c * c; }
+        for (int i = kKeepSpan + tid; i < p.D; i += kNormThreads) { float c = again(i) - mean; sq += c * c; }
         const float var = block_sum(sq, sh) * inv_n;
         inv = 1.f / sqrtf(var + p.eps);
     } else {
@@ -120,7 +129,7 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams
         const int i = tid + j * kNormThreads;
         if (i < p.D) store(i, keep[j]);
     }
-    for (int i = kKeepSpan + tid; i < p.D; i += kNormThreads) store(i, h[i]);
+    for (int i = kKeepSpan + tid; i < p.D; i += kNormThreads) store(i, again(i));
 }
 
 struct EmbedParams {
@@ -402,6 +411,24 @@ static int norm_common(float* d_hidden, const void* d_delta, int delta_dtype, co
     p.delta_bf16 = delta_dtype == GPTRS_BF16; p.out_f32 = out_dtype == GPTRS_F32; p.layer_norm = layer_norm;
     return launch_kernel(add_norm_kernel, dim3((unsigned)rows), dim3(kNormThreads), 0, as_stream(stream), 1, p);
 }
+
+}  // extern "C"
+
+namespace gptrs {
+int add_norm_out_of_place(const float* hidden_in, const float* delta, float* sum_out, const float* gamma, const float* beta, float eps,
+                          float* out, int64_t rows, int64_t dim, bool layer_norm, cudaStream_t st) {
+    GPTRS_REQUIRE(hidden_in && delta && gamma && out, "null pointer");
+    GPTRS_REQUIRE(rows >= 0 && dim > 0 && dim < (1ll << 31) && rows < (1ll << 31), "bad shape");
+    if (rows == 0) return GPTRS_OK;
+    NormParams p = {};
+    p.hidden = sum_out; p.hidden_in = hidden_in; p.delta = delta; p.gamma = gamma; p.beta = beta; p.out = out;
+    p.T = (int)rows; p.D = (int)dim; p.eps = eps;
+    p.delta_bf16 = 0; p.out_f32 = 1; p.layer_norm = layer_norm ? 1 : 0;
+    return launch_kernel(add_norm_kernel, dim3((unsigned)rows), dim3(kNormThreads), 0, st, 1, p);
+}
+}  // namespace gptrs
+
+extern "C" {
 
 int gptrs_cuda_add_rms_norm(float* d_hidden, const void* d_delta, int delta_dtype, const float* d_gamma,
                             float eps, void* d_out, int out_dtype, float* d_inv_rms, int64_t rows, int64_t dim,

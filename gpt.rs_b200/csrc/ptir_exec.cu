@@ -18,6 +18,12 @@
 #include "tensor.h"
 
 namespace gptrs {
+
+// norm_embed_sample.cu: out = norm(hidden_in + delta) with the sum optionally written to sum_out (any of the three row
+// buffers may be the same memory); layer_norm selects LayerNorm (beta may be null) or RMSNorm.
+int add_norm_out_of_place(const float* hidden_in, const float* delta, float* sum_out, const float* gamma, const float* beta, float eps,
+                          float* out, int64_t rows, int64_t dim, bool layer_norm, cudaStream_t st);
+
 namespace ptir {
 namespace {
 
@@ -135,7 +141,8 @@ __global__ void select_kernel(const EwParams p) {  // a: pred (u8), b / c: 4-byt
                                                                            : static_cast<const uint32_t*>(p.c)[i];
 }
 
-// op: 0 f32->si32 (truncate, saturate, NaN -> 0), 1 si32->f32, 2 i1->f32, 3 i1->si32, 4 f32->i1, 5 si32->i1
+// op: 0 f32->si32 (truncate, saturate, NaN -> 0), 1 si32->f32, 2 i1->f32, 3 i1->si32, 4 f32->i1, 5 si32->i1,
+//     6 f32->bf16, 7 bf16->f32, 8 f32->f16, 9 f16->f32 (round to nearest even)
 __global__ void cast_kernel(const EwParams p) {
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n) return;
@@ -150,6 +157,10 @@ __global__ void cast_kernel(const EwParams p) {
         case 2: static_cast<float*>(p.out)[i] = static_cast<const uint8_t*>(p.a)[i] ? 1.f : 0.f; break;
         case 3: static_cast<int*>(p.out)[i] = static_cast<const uint8_t*>(p.a)[i] ? 1 : 0; break;
         case 4: static_cast<uint8_t*>(p.out)[i] = static_cast<const float*>(p.a)[i] != 0.f; break;
+        case 6: static_cast<__nv_bfloat16*>(p.out)[i] = __float2bfloat16_rn(static_cast<const float*>(p.a)[i]); break;
+        case 7: static_cast<float*>(p.out)[i] = __bfloat162float(static_cast<const __nv_bfloat16*>(p.a)[i]); break;
+        case 8: static_cast<__half*>(p.out)[i] = __float2half_rn(static_cast<const float*>(p.a)[i]); break;
+        case 9: static_cast<float*>(p.out)[i] = __half2float(static_cast<const __half*>(p.a)[i]); break;
         default: static_cast<uint8_t*>(p.out)[i] = static_cast<const int*>(p.a)[i] != 0; break;
     }
 }
@@ -293,6 +304,16 @@ struct Plan {
     std::unordered_map<uint32_t, int> def;       // value id -> instruction index
     std::unordered_map<uint32_t, int> uses;      // value id -> use count (operands + results)
     int fused = 0;
+    // Buffer plan (the counterpart of the reference's liveness-based bufferisation,
+    // crates/gpt-rs/src/backend/conversion/bufferize.rs): every temporary of the function gets a fixed offset in ONE
+    // arena that is allocated when the plan first runs; two values share bytes when their lifetimes do not overlap.
+    // Values that leave the function (results, and what they are views of) are allocated per call.
+    std::vector<int64_t> arena_offset;           // per instruction: offset of its value, -1 = allocated per call / a view
+    int64_t arena_bytes = 0;
+    Tensor* arena = nullptr;                     // retained; one per plan (and so per device)
+    int device = 0;
+    std::mutex run_mu;                           // the arena serves one execution at a time
+    ~Plan() { tensor_release(arena); }
 };
 
 const Inst* def_of(const Plan& pl, const Operand& o) {
@@ -378,6 +399,7 @@ void count_uses(Plan& pl) {
         const Inst& in = pl.fn.body[i];
         if (in.dead) continue;
         pl.def[in.id] = (int)i;
+        if (in.side_id) pl.def[in.side_id] = (int)i;
         for (auto& o : in.operands)
             if (!o.is_literal) ++pl.uses[o.id];
     }
@@ -614,10 +636,123 @@ void rewrite_pass(Plan& pl, bool rms_pass) {
     sweep_dead(pl);
 }
 
+// dequant + dot_general: DotGeneral(x[M,K], W) with W = Dequantize(q, scales)[N,K] contracted over K, directly or
+// through Transpose([1,0]) (the Linear layout [K,N]) -> FusedQuantMatmul(x, q, scales): the f32 weight is never built.
+void rewrite_quant_dots(Plan& pl) {
+    count_uses(pl);
+    for (auto& in : pl.fn.body) {
+        if (in.dead || in.op != Op::DotGeneral || in.out.dtype != GPTRS_F32 || in.out.dims.size() != 2) continue;
+        if (!in.a.empty() || in.c != std::vector<int64_t>{1} || in.d.size() != 1) continue;
+        const TSpec* xs = spec_of(pl, in.operands[0]);
+        if (!xs || xs->dtype != GPTRS_F32 || xs->dims.size() != 2) continue;
+        const Inst* w = def_of(pl, in.operands[1]);
+        int64_t contract = in.d[0];
+        if (w && !w->dead && w->op == Op::Transpose && w->a == std::vector<int64_t>{1, 0}) { w = def_of(pl, w->operands[0]); contract = 1 - contract; }
+        if (!w || w->dead || w->op != Op::Dequantize || contract != 1 || w->operands.size() != 2) continue;
+        const int64_t n = w->out.dims[0], k = w->out.dims[1];
+        if (k % 128 != 0 || n % 16 != 0 || xs->dims[1] != k) continue;
+        Inst f = in;
+        f.op = Op::FusedQuantMatmul;
+        f.sub = spec_of(pl, w->operands[0])->dtype == GPTRS_SI8 ? "w8" : "w4";
+        f.operands = {in.operands[0], w->operands[0], w->operands[1]};
+        in = f;
+        ++pl.fused;
+    }
+    sweep_dead(pl);
+}
+
+// norm + residual: FusedRmsNorm / FusedLayerNorm whose input is Add(residual, update) -> one kernel that adds and
+// normalises. When the sum has other readers (it is the new residual stream) the kernel writes it as a second result,
+// provided none of those readers comes before the norm in the instruction order.
+void rewrite_add_norms(Plan& pl, bool allow_second_result) {
+    count_uses(pl);
+    for (size_t i = 0; i < pl.fn.body.size(); ++i) {
+        Inst& in = pl.fn.body[i];
+        if (in.dead || (in.op != Op::FusedRmsNorm && in.op != Op::FusedLayerNorm) || in.operands[0].is_literal) continue;
+        auto it = pl.def.find(in.operands[0].id);
+        if (it == pl.def.end()) continue;
+        Inst& add = pl.fn.body[it->second];
+        if (!is_bin(&add, "Add") || add.out.dtype != GPTRS_F32 || add.operands[0].is_literal || add.operands[1].is_literal) continue;
+        bool early_reader = false, is_result = false;
+        for (size_t j = 0; j < i; ++j)
+            for (const Operand& o : pl.fn.body[j].operands)
+                if (!pl.fn.body[j].dead && !o.is_literal && o.id == add.id) early_reader = true;
+        for (uint32_t r : pl.fn.result_ids) is_result = is_result || r == add.id;
+        if (early_reader) continue;
+        const bool shared = uses_of(pl, add.id) > 1 || is_result;
+        if (shared && !allow_second_result) continue;   // the text form of a CustomCall has one result
+        Inst f = in;
+        f.op = in.op == Op::FusedRmsNorm ? Op::FusedAddRmsNorm : Op::FusedAddLayerNorm;
+        f.operands = {add.operands[0], add.operands[1]};
+        for (size_t k = 1; k < in.operands.size(); ++k) f.operands.push_back(in.operands[k]);
+        if (shared) { f.side_id = add.id; f.side_out = add.out; }
+        add.dead = true;
+        in = f;
+        ++pl.fused;
+        count_uses(pl);
+    }
+    sweep_dead(pl);
+}
+
 // layer_norm / softmax / matmul+bias first: a layer_norm contains an rms_norm-shaped subgraph.
-void rewrite(Plan& pl) {
+void rewrite(Plan& pl, bool in_process = true) {
     rewrite_pass(pl, false);
     rewrite_pass(pl, true);
+    rewrite_quant_dots(pl);
+    rewrite_add_norms(pl, in_process);
+}
+
+// True for operations whose result is (or may be) the storage of an operand: their source must live as long as they do.
+bool may_alias_operand(const Inst& in) {
+    return in.op == Op::Reshape || in.op == Op::Constant || in.op == Op::StopGradient || in.op == Op::Cast;
+}
+
+// Assigns arena offsets (see Plan). Lifetimes are instruction indices; a value that an aliasing operation forwards
+// lives as long as the alias. First-fit over the blocks free at the defining instruction.
+void plan_buffers(Plan& pl) {
+    const auto& body = pl.fn.body;
+    const int n = (int)body.size();
+    pl.arena_offset.assign(n, -1);
+    std::vector<int> last(n, -1);          // last instruction index that reads the value of instruction i
+    std::vector<char> escapes(n, 0);
+    auto idx_of = [&](uint32_t id) { auto it = pl.def.find(id); return it == pl.def.end() ? -1 : it->second; };
+    for (uint32_t r : pl.fn.result_ids) { int i = idx_of(r); if (i >= 0) escapes[i] = 1; }
+    for (int i = n - 1; i >= 0; --i) {
+        const Inst& in = body[i];
+        if (in.dead) continue;
+        for (const Operand& o : in.operands) {
+            if (o.is_literal) continue;
+            const int src = idx_of(o.id);
+            if (src < 0) continue;
+            last[src] = std::max(last[src], i);
+            if (may_alias_operand(in)) {   // the alias keeps its source alive and passes an escape on
+                last[src] = std::max(last[src], last[i]);
+                if (escapes[i]) escapes[src] = 1;
+            }
+        }
+    }
+    struct Block { int64_t off, bytes; int free_at; };
+    std::vector<Block> blocks;
+    int64_t top = 0;
+    for (int i = 0; i < n; ++i) {
+        const Inst& in = body[i];
+        if (in.dead || escapes[i] || may_alias_operand(in) || in.side_id) continue;
+        const int64_t bytes = (((int64_t)in.out.numel() * (int64_t)dtype_size(in.out.dtype)) + 255) & ~(int64_t)255;
+        if (bytes == 0) continue;
+        const int free_at = last[i] < 0 ? i : last[i];
+        int best = -1;
+        for (int b = 0; b < (int)blocks.size(); ++b)
+            if (blocks[b].free_at < i && blocks[b].bytes >= bytes && (best < 0 || blocks[b].bytes < blocks[best].bytes)) best = b;
+        if (best >= 0) {
+            pl.arena_offset[i] = blocks[best].off;
+            blocks[best].free_at = free_at;
+        } else {
+            pl.arena_offset[i] = top;
+            blocks.push_back({top, bytes, free_at});
+            top += bytes;
+        }
+    }
+    pl.arena_bytes = top;
 }
 
 // Literal operands are uploaded once per plan.
@@ -650,6 +785,7 @@ std::mutex g_plan_mu;
 std::unordered_map<uint64_t, std::shared_ptr<Plan>> g_plans;
 int64_t g_plan_hits = 0, g_plan_builds = 0, g_last_launches = 0, g_last_fused = 0;
 int g_fusion_enabled = 1;
+int g_arena_enabled = 1;   // GPTRS_PTIR_ARENA=0 allocates every temporary by itself (for comparison)
 
 int* status_word() {
     static int* d = nullptr;
@@ -662,6 +798,9 @@ struct Exec {
     cudaStream_t st;
     std::unordered_map<uint32_t, Tensor*> env;  // retained
     int64_t launches = 0;
+    Tensor* arena = nullptr;      // the plan's arena (not retained here: the plan outlives the execution)
+    int64_t arena_off = -1;       // offset of the value of the instruction being executed, -1 = allocate
+    Tensor* side = nullptr;       // second result of the instruction being executed (retained), if it has one
     ~Exec() { for (auto& kv : env) tensor_release(kv.second); }
 
     int value(const Operand& o, Tensor** out) {  // returns a retained tensor
@@ -692,15 +831,28 @@ int copy_generic(Exec& ex, const Tensor* in, Tensor* out, const std::vector<int6
     p.starts = starts; p.dyn_rank = (int)dyn_limit.size(); p.dyn_on_out = dyn_on_out;
     for (size_t d = 0; d < dyn_limit.size(); ++d) { p.dyn_limit[d] = dyn_limit[d]; p.dyn_str[d] = dyn_str[d]; }
     ++ex.launches;
-    return dtype_size(in->dtype) == 4 ? launch_flat(strided_copy_kernel<uint32_t>, p.n, p, ex.st)
-                                      : launch_flat(strided_copy_kernel<uint8_t>, p.n, p, ex.st);
+    const size_t es = dtype_size(in->dtype);
+    return es == 4 ? launch_flat(strided_copy_kernel<uint32_t>, p.n, p, ex.st)
+           : es == 2 ? launch_flat(strided_copy_kernel<uint16_t>, p.n, p, ex.st)
+                     : launch_flat(strided_copy_kernel<uint8_t>, p.n, p, ex.st);
 }
 
 int exec_inst(Exec& ex, const Inst& in, std::vector<Tensor*>& ops, Tensor** result) {
     auto unimpl = [&](const std::string& why) { return fail(GPTRS_UNIMPLEMENTED, in.name + " is not implemented: " + why); };
     auto spec = [&](const std::string& why) { return fail(GPTRS_SPEC_VIOLATION, in.name + " (%" + std::to_string(in.id) + "): " + why); };
     Tensor* out = nullptr;
-    auto alloc_out = [&]() { return tensor_alloc(in.out.dtype, (int)in.out.dims.size(), in.out.dims.data(), false, &out); };
+    auto alloc_out = [&]() {
+        if (ex.arena && ex.arena_off >= 0) {   // a temporary with a planned place in the arena
+            out = new Tensor();
+            out->dtype = in.out.dtype; out->dims = in.out.dims;
+            out->bytes = (size_t)in.out.numel() * dtype_size(in.out.dtype);
+            out->data = static_cast<unsigned char*>(ex.arena->data) + ex.arena_off;
+            out->owns = false; out->base = ex.arena; out->device = ex.arena->device;
+            tensor_retain(ex.arena);
+            return (int)GPTRS_OK;
+        }
+        return tensor_alloc(in.out.dtype, (int)in.out.dims.size(), in.out.dims.data(), false, &out);
+    };
     const int64_t n_out = in.out.numel();
     int rc = GPTRS_OK;
     switch (in.op) {
@@ -758,7 +910,9 @@ int exec_inst(Exec& ex, const Inst& in, std::vector<Tensor*>& ops, Tensor** resu
                 if (from == to) { tensor_release(out); tensor_retain(ops[0]); *result = ops[0]; --ex.launches; return GPTRS_OK; }
                 p.op = from == GPTRS_F32 && to == GPTRS_SI32 ? 0 : from == GPTRS_SI32 && to == GPTRS_F32 ? 1
                        : from == GPTRS_I1 && to == GPTRS_F32 ? 2 : from == GPTRS_I1 && to == GPTRS_SI32 ? 3
-                       : from == GPTRS_F32 && to == GPTRS_I1 ? 4 : from == GPTRS_SI32 && to == GPTRS_I1 ? 5 : -1;
+                       : from == GPTRS_F32 && to == GPTRS_I1 ? 4 : from == GPTRS_SI32 && to == GPTRS_I1 ? 5
+                       : from == GPTRS_F32 && to == GPTRS_BF16 ? 6 : from == GPTRS_BF16 && to == GPTRS_F32 ? 7
+                       : from == GPTRS_F32 && to == GPTRS_F16 ? 8 : from == GPTRS_F16 && to == GPTRS_F32 ? 9 : -1;
                 if (p.op < 0) { tensor_release(out); return unimpl("cast between these dtypes"); }
                 rc = launch_flat(cast_kernel, p.n, p, ex.st);
             }
@@ -949,6 +1103,79 @@ int exec_inst(Exec& ex, const Inst& in, std::vector<Tensor*>& ops, Tensor** resu
                                                  static_cast<float*>(out->data), 1, in.a[0], in.a[1], in.a[2], in.a[3], ex.st);
             break;
         }
+        case Op::Dequantize: {
+            // canonical W8 (si8 [N][K], fp16 scales [N]) or W4 (two si4 per byte [N][K/2], fp16 scales [N][K/128]) -> f32 [N][K]
+            if ((rc = alloc_out())) return rc;
+            const int64_t N = in.out.dims[0], K = in.out.dims[1];
+            ++ex.launches;
+            rc = ops[0]->dtype == GPTRS_SI8
+                     ? gptrs_cuda_dequantize_w8(static_cast<const int8_t*>(ops[0]->data), static_cast<const uint16_t*>(ops[1]->data), K, N, 1,
+                                                static_cast<float*>(out->data), ex.st)
+                     : gptrs_cuda_dequantize_w4(static_cast<const uint8_t*>(ops[0]->data), static_cast<const uint16_t*>(ops[1]->data), K, N, 1,
+                                                static_cast<float*>(out->data), ex.st);
+            break;
+        }
+        case Op::FusedQuantMatmul: {
+            // x f32 [M][K] . dequant(q, scales)^T -> f32 [M][N] on the quantised matmul kernels. The kernel layout of the
+            // weight is derived once per weight handle and kept with it (the derived-parameter memo of the reference's
+            // resolver, crates/gpt-rs/src/backend/param_resolver.rs:11-50, keyed here by the handle itself).
+            Tensor *X = ops[0], *Q = ops[1], *S = ops[2];
+            const bool w8 = Q->dtype == GPTRS_SI8;
+            const int64_t M = X->dims[0], K = X->dims[1], N = Q->dims[0];
+            const size_t need = w8 ? gptrs_cuda_w8a16_packed_bytes(N, K) : gptrs_cuda_w4a16_packed_bytes(N, K);
+            if (need == 0) return spec("quantised matmul needs K % 128 == 0 and N % 16 == 0");
+            static std::mutex derive_mu;
+            Tensor* packed = nullptr;
+            {
+                std::lock_guard<std::mutex> lk(derive_mu);
+                if (!Q->derived || Q->derived_with != S->data || Q->derived->bytes != need) {
+                    Tensor* fresh = nullptr;
+                    int64_t pd[1] = {(int64_t)need};
+                    if ((rc = tensor_alloc(GPTRS_UI8, 1, pd, false, &fresh))) return rc;
+                    rc = w8 ? gptrs_cuda_w8a16_repack(static_cast<const int8_t*>(Q->data), static_cast<const uint16_t*>(S->data), N, K, 0, fresh->data, ex.st)
+                            : gptrs_cuda_w4a16_repack(static_cast<const uint8_t*>(Q->data), static_cast<const uint16_t*>(S->data), N, K, 0, fresh->data, ex.st);
+                    if (rc) { tensor_release(fresh); return rc; }
+                    ex.launches += 2;
+                    tensor_release(Q->derived);
+                    Q->derived = fresh;
+                    Q->derived_with = S->data;
+                }
+                packed = Q->derived;
+                tensor_retain(packed);
+            }
+            Tensor* xb = nullptr;   // the kernels take bf16 activations
+            if ((rc = tensor_alloc(GPTRS_BF16, 2, X->dims.data(), false, &xb))) { tensor_release(packed); return rc; }
+            EwParams cp = {};
+            cp.a = X->data; cp.out = xb->data; cp.n = X->numel(); cp.op = 6;
+            rc = launch_flat(cast_kernel, cp.n, cp, ex.st);
+            if (!rc) rc = alloc_out();
+            if (!rc) {
+                gptrs_matmul_epilogue ep = {};
+                ep.out_dtype = GPTRS_F32;
+                rc = w8 ? gptrs_cuda_quant_matmul_w8a16(xb->data, packed->data, out->data, M, N, K, &ep, ex.st)
+                        : gptrs_cuda_quant_matmul_w4a16(xb->data, packed->data, out->data, M, N, K, &ep, ex.st);
+            }
+            ex.launches += 2;
+            // the temporaries are read by kernels already enqueued on this stream; their memory is pooled and handed out
+            // again only to work enqueued later on a stream (run_program is synchronous at its end)
+            tensor_release(xb);
+            tensor_release(packed);
+            break;
+        }
+        case Op::FusedAddRmsNorm: case Op::FusedAddLayerNorm: {
+            // (residual, update, gamma[, beta]) -> norm(residual + update); with a second result the sum is written too
+            if ((rc = alloc_out())) return rc;
+            const bool ln = in.op == Op::FusedAddLayerNorm;
+            const int64_t d = in.out.dims.back(), rows = n_out / d;
+            Tensor* sum = nullptr;
+            if (in.side_id && (rc = tensor_alloc(in.side_out.dtype, (int)in.side_out.dims.size(), in.side_out.dims.data(), false, &sum))) break;
+            ++ex.launches;
+            rc = add_norm_out_of_place(static_cast<const float*>(ops[0]->data), static_cast<const float*>(ops[1]->data),
+                                       sum ? static_cast<float*>(sum->data) : nullptr, static_cast<const float*>(ops[2]->data),
+                                       ln ? static_cast<const float*>(ops[3]->data) : nullptr, in.f0, static_cast<float*>(out->data), rows, d, ln, ex.st);
+            if (rc) tensor_release(sum); else ex.side = sum;
+            break;
+        }
         case Op::CustomCall:
             return fail(GPTRS_UNIMPLEMENTED, "custom_call target '" + in.sub + "' is not implemented by the cuda backend");
         default:
@@ -968,10 +1195,12 @@ using namespace gptrs::ptir;
 
 extern "C" {
 
-int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* const* inputs, size_t n_inputs,
-                           gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs, void* stream) {
-    GPTRS_REQUIRE(program_json && n_outputs && (n_inputs == 0 || inputs), "null pointer");
-    const uint64_t key = fnv1a(program_json, len) ^ (g_fusion_enabled ? 0 : 0x5bd1e995u);
+namespace {
+
+// The cached plan of a program text on the current device (parsed, verified, rewritten, buffers planned).
+int plan_for(const char* program_json, size_t len, std::shared_ptr<Plan>* out) {
+    const int device = current_device();
+    const uint64_t key = fnv1a(program_json, len) ^ (g_fusion_enabled ? 0 : 0x5bd1e995u) ^ ((uint64_t)(device + 1) * 0x9e3779b97f4a7c15ull);
     std::shared_ptr<Plan> plan;
     {
         std::lock_guard<std::mutex> lk(g_plan_mu);
@@ -988,16 +1217,33 @@ int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* c
         if (st) return fail(st == 2 ? GPTRS_UNIMPLEMENTED : GPTRS_SPEC_VIOLATION, err);
         if (g_fusion_enabled) rewrite(*p); else count_uses(*p);
         if (int rc = upload_literals(*p)) return rc;
+        p->device = device;
+        count_uses(*p);
+        if (g_arena_enabled) plan_buffers(*p);
         std::lock_guard<std::mutex> lk(g_plan_mu);
         g_plans[key] = p;
         ++g_plan_builds;
         plan = p;
     }
+    *out = plan;
+    return GPTRS_OK;
+}
+
+int execute_plan(const std::shared_ptr<Plan>& plan, gptrs_tensor* const* inputs, size_t n_inputs, gptrs_tensor** outputs,
+                 size_t outputs_cap, size_t* n_outputs, void* stream) {
     const Function& fn = plan->fn;
+    if (plan->device != current_device()) return fail(GPTRS_SPEC_VIOLATION, "the program was prepared on another device");
     GPTRS_REQUIRE(n_inputs == fn.param_ids.size(), "entry input count does not match the function parameters");
-    GPTRS_REQUIRE(outputs_cap >= fn.result_ids.size() && (outputs || fn.result_ids.empty()), "output array too small");
+    GPTRS_REQUIRE(n_outputs && outputs_cap >= fn.result_ids.size() && (outputs || fn.result_ids.empty()), "output array too small");
+    // one execution at a time per plan: the temporaries of the function live at fixed offsets of the plan's arena
+    std::lock_guard<std::mutex> run_lock(plan->run_mu);
+    if (plan->arena_bytes > 0 && !plan->arena) {
+        int64_t ad[1] = {plan->arena_bytes};
+        if (int rc = tensor_alloc(GPTRS_UI8, 1, ad, false, &plan->arena)) return rc;
+    }
     Exec ex;
     ex.st = as_stream(stream);
+    ex.arena = plan->arena;
     for (size_t i = 0; i < n_inputs; ++i) {
         Tensor* t = reinterpret_cast<Tensor*>(inputs[i]);
         GPTRS_REQUIRE(t, "null input handle");
@@ -1006,15 +1252,19 @@ int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* c
         tensor_retain(t);
         ex.env[fn.param_ids[i]] = t;
     }
-    for (const Inst& in : fn.body) {
+    for (size_t ii = 0; ii < fn.body.size(); ++ii) {
+        const Inst& in = fn.body[ii];
         if (in.dead) continue;
         std::vector<Tensor*> ops(in.operands.size(), nullptr);
         int rc = GPTRS_OK;
         for (size_t i = 0; i < ops.size() && !rc; ++i) rc = ex.value(in.operands[i], &ops[i]);
         Tensor* res = nullptr;
+        ex.arena_off = ii < plan->arena_offset.size() ? plan->arena_offset[ii] : -1;
+        ex.side = nullptr;
         if (!rc) rc = exec_inst(ex, in, ops, &res);
         for (Tensor* t : ops) tensor_release(t);
         if (rc) return rc;
+        if (ex.side) { ex.env[in.side_id] = ex.side; ex.side = nullptr; }
         if (res->dtype != in.out.dtype || res->dims != in.out.dims) {
             tensor_release(res);
             return fail(GPTRS_SPEC_VIOLATION, in.name + " (%" + std::to_string(in.id) + ") produced a value that does not match its declared type");
@@ -1045,6 +1295,36 @@ int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* c
     }
     return GPTRS_OK;
 }
+
+}  // namespace
+
+int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* const* inputs, size_t n_inputs,
+                           gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs, void* stream) {
+    GPTRS_REQUIRE(program_json && n_outputs && (n_inputs == 0 || inputs), "null pointer");
+    std::shared_ptr<Plan> plan;
+    if (int rc = plan_for(program_json, len, &plan)) return rc;
+    return execute_plan(plan, inputs, n_inputs, outputs, outputs_cap, n_outputs, stream);
+}
+
+int gptrs_cuda_program_prepare(const char* program_json, size_t len, gptrs_program** out) {
+    GPTRS_REQUIRE(program_json && out, "null pointer");
+    std::shared_ptr<Plan> plan;
+    if (int rc = plan_for(program_json, len, &plan)) return rc;
+    *out = reinterpret_cast<gptrs_program*>(new std::shared_ptr<Plan>(plan));
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_program_run(gptrs_program* program, gptrs_tensor* const* inputs, size_t n_inputs, gptrs_tensor** outputs,
+                           size_t outputs_cap, size_t* n_outputs, void* stream) {
+    GPTRS_REQUIRE(program && n_outputs && (n_inputs == 0 || inputs), "null pointer");
+    {
+        std::lock_guard<std::mutex> lk(g_plan_mu);
+        ++g_plan_hits;
+    }
+    return execute_plan(*reinterpret_cast<std::shared_ptr<Plan>*>(program), inputs, n_inputs, outputs, outputs_cap, n_outputs, stream);
+}
+
+void gptrs_cuda_program_release(gptrs_program* program) { delete reinterpret_cast<std::shared_ptr<Plan>*>(program); }
 
 int gptrs_cuda_execute_instruction(const char* instruction_json, size_t len, gptrs_tensor* const* inputs, size_t n_inputs,
                                    gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs, void* stream) {
@@ -1113,12 +1393,15 @@ Json fused_instruction_json(const Inst& in) {
     // CustomCallAttr is adjacently tagged (#[serde(tag = "kind", content = "value")], spec.rs:602-613)
     if (in.op == Op::FusedLayerNorm || in.op == Op::FusedRmsNorm || in.op == Op::FusedAddRmsNorm || in.op == Op::FusedAddLayerNorm)
         attrs.push_back({"eps", jobj({{"kind", jstr("F64")}, {"value", jnum((double)in.f0)}})});
+    if (in.op == Op::FusedQuantMatmul) attrs.push_back({"group_size", jobj({{"kind", jstr("I64")}, {"value", jnum(in.sub == "w4" ? 128 : 0)}})});
     if (in.op == Op::FusedAttentionDecode) {
         std::vector<Json> g;
         for (int64_t v : in.a) g.push_back(jnum((double)v));
         attrs.push_back({"geometry", jobj({{"kind", jstr("I64Array")}, {"value", jarr(std::move(g))}})});
     }
-    Json call = jobj({{"CustomCall", jobj({{"target", jstr(fused_target(in.op))}, {"attrs", jobj(std::move(attrs))}})}});
+    const std::string target = in.op == Op::FusedQuantMatmul ? (in.sub == "w8" ? "gpt_rs.cuda.quant_matmul_w8a16.v1" : "gpt_rs.cuda.quant_matmul_w4a16.v1")
+                                                             : std::string(fused_target(in.op));
+    Json call = jobj({{"CustomCall", jobj({{"target", jstr(target)}, {"attrs", jobj(std::move(attrs))}})}});
     return jobj({{"id", jnum(in.id)}, {"op", std::move(call)}, {"operands", jarr(std::move(operands))},
                  {"output", jobj({{"Tensor", tensor_spec_json(in.out)}})}});
 }
@@ -1134,7 +1417,7 @@ int gptrs_cuda_pipeline_fuse(const char* program_json, size_t len, char* out, si
     int st = build_function(root, &plan.fn, &err);
     if (!st) st = verify_function(plan.fn, &err);
     if (st) return fail(st == 2 ? GPTRS_UNIMPLEMENTED : GPTRS_SPEC_VIOLATION, err);
-    rewrite(plan);
+    rewrite(plan, false);
     // the entry function's body: surviving instructions as they were, fused ones as CustomCalls, in the old order
     const std::string entry = root.get("entry")->str;
     for (auto& kv : root.obj) {
@@ -1147,7 +1430,7 @@ int gptrs_cuda_pipeline_fuse(const char* program_json, size_t len, char* out, si
                 std::vector<Json> body;
                 for (const Inst& in : plan.fn.body) {
                     if (in.dead) continue;
-                    if (fused_target(in.op)) body.push_back(fused_instruction_json(in));
+                    if (fused_target(in.op) || in.op == Op::FusedQuantMatmul) body.push_back(fused_instruction_json(in));
                     else body.push_back(fkv.second.arr[in.src]);
                 }
                 fkv.second.arr = std::move(body);
@@ -1184,6 +1467,29 @@ int gptrs_cuda_run_program_stats(int64_t* plan_builds, int64_t* plan_hits, int64
 
 int gptrs_cuda_set_fusion(int enabled) {
     g_fusion_enabled = enabled ? 1 : 0;
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_set_buffer_plan(int enabled) {
+    g_arena_enabled = enabled ? 1 : 0;
+    std::lock_guard<std::mutex> lk(g_plan_mu);
+    g_plans.clear();   // plans are built with or without an arena
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_pipeline(const char* phase, const char* program_json, size_t len, char* out, size_t out_cap, size_t* written,
+                        int64_t* n_rewrites) {
+    GPTRS_REQUIRE(phase && program_json && written, "null pointer");
+    const std::string ph = phase;
+    if (ph == "pre" || ph == "fuse") return gptrs_cuda_pipeline_fuse(program_json, len, out, out_cap, written, n_rewrites);
+    if (ph != "legalize" && ph != "cleanup") return fail(GPTRS_SPEC_VIOLATION, "unknown pipeline phase '" + ph + "' (pre, legalize, fuse, cleanup)");
+    // legalize: every operation of the decode-path subset runs as written, nothing to lower. cleanup: the rewrites
+    // sweep their own dead instructions. Both return the program unchanged (after checking that it parses and verifies).
+    int rc = gptrs_cuda_verify_program(program_json, len);
+    if (rc) return rc;
+    *written = len;
+    if (n_rewrites) *n_rewrites = 0;
+    if (out && out_cap >= len) memcpy(out, program_json, len);
     return GPTRS_OK;
 }
 

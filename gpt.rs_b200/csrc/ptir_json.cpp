@@ -213,6 +213,8 @@ const char* fused_target(Op op) {
         case Op::FusedSoftmax: return "gpt_rs.cuda.softmax_last_axis.f32.v1";
         case Op::FusedMatmulBias: return "gpt_rs.cuda.matmul_bias.f32.v1";
         case Op::FusedAttentionDecode: return "gpt_rs.cuda.attention_decode.f32.v1";
+        case Op::FusedAddRmsNorm: return "gpt_rs.cuda.add_rms_norm.f32.v1";
+        case Op::FusedAddLayerNorm: return "gpt_rs.cuda.add_layer_norm.f32.v1";
         default: return nullptr;
     }
 }
@@ -332,12 +334,19 @@ int build_function(const Json& program, Function* fn, std::string* err) {
             in.sub = attr->get("target") ? attr->get("target")->str : "";
             // the targets written by this backend's own fusion pipeline come back as the fused operations
             const Json* attrs = attr->get("attrs");
-            for (Op f : {Op::FusedLayerNorm, Op::FusedRmsNorm, Op::FusedSoftmax, Op::FusedMatmulBias, Op::FusedAttentionDecode}) {
-                if (in.sub != fused_target(f)) continue;
-                const size_t want = f == Op::FusedLayerNorm || f == Op::FusedMatmulBias ? 3 : f == Op::FusedRmsNorm ? 2 : f == Op::FusedSoftmax ? 1 : 4;
+            if (in.sub == "gpt_rs.cuda.quant_matmul_w4a16.v1" || in.sub == "gpt_rs.cuda.quant_matmul_w8a16.v1") {
+                if (in.operands.size() != 3) { *err = in.sub + ": wrong operand count"; return 1; }
+                in.op = Op::FusedQuantMatmul;
+                in.sub = in.sub == "gpt_rs.cuda.quant_matmul_w8a16.v1" ? "w8" : "w4";
+            }
+            for (Op f : {Op::FusedLayerNorm, Op::FusedRmsNorm, Op::FusedSoftmax, Op::FusedMatmulBias, Op::FusedAttentionDecode, Op::FusedAddRmsNorm,
+                         Op::FusedAddLayerNorm}) {
+                if (in.op != Op::CustomCall || in.sub != fused_target(f)) continue;
+                const size_t want = f == Op::FusedLayerNorm || f == Op::FusedMatmulBias || f == Op::FusedAddRmsNorm ? 3
+                                    : f == Op::FusedRmsNorm ? 2 : f == Op::FusedSoftmax ? 1 : 4;
                 if (in.operands.size() != want) { *err = in.sub + ": wrong operand count"; return 1; }
                 in.op = f;
-                if (f == Op::FusedLayerNorm || f == Op::FusedRmsNorm) {
+                if (f == Op::FusedLayerNorm || f == Op::FusedRmsNorm || f == Op::FusedAddRmsNorm || f == Op::FusedAddLayerNorm) {
                     const Json* e = attrs ? attrs->get("eps") : nullptr;
                     const Json* v = attr_value(e, "F64");
                     if (!v || v->kind != Json::Number) { *err = in.sub + ": attribute eps (F64) is required"; return 1; }

@@ -67,6 +67,10 @@ struct Inst {
     TSpec out;
     bool dead = false;            // removed by a rewrite
     int src = -1;                 // index of the instruction in the function body it was read from
+    // A fused residual-add + norm also produces the sum itself when other instructions read it: the value id and type
+    // of that second result (0 = none). Only the in-process rewrite uses it; the CustomCall text form has one result.
+    uint32_t side_id = 0;
+    TSpec side_out;
 };
 
 struct Function {

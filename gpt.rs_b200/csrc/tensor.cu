@@ -35,7 +35,8 @@ struct DevicePool {
     std::map<size_t, std::vector<void*>> free_blocks;
     size_t cached_bytes = 0;
 };
-DevicePool g_pools[kMaxDevices];
+// never destroyed: tensors released by other static objects at process exit still find their pool
+DevicePool* const g_pools = new DevicePool[kMaxDevices];
 std::atomic<int64_t> g_driver_allocs{0}, g_pool_hits{0}, g_driver_frees{0};
 
 size_t pool_round(size_t bytes) { return (bytes + 255) & ~(size_t)255; }
@@ -101,7 +102,7 @@ void pool_stats(int64_t* driver_allocs, int64_t* pool_hits, int64_t* driver_free
     if (driver_frees) *driver_frees = g_driver_frees.load();
     if (cached_bytes) {
         int64_t total = 0;
-        for (auto& p : g_pools) { std::lock_guard<std::mutex> lk(p.mu); total += (int64_t)p.cached_bytes; }
+        for (int d = 0; d < kMaxDevices; ++d) { std::lock_guard<std::mutex> lk(g_pools[d].mu); total += (int64_t)g_pools[d].cached_bytes; }
         *cached_bytes = total;
     }
 }

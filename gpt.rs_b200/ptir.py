@@ -22,6 +22,7 @@ import math
 import struct
 
 F32, SI32, I1 = "F32", "Si32", "I1"
+SI8, UI8, F16, BF16 = "Si8", "Ui8", "F16", "Bf16"   # quantised weights (Ui8 = two packed si4), their scales, 16-bit activations
 _PACK = {F32: "<f", SI32: "<i"}
 
 
@@ -101,6 +102,17 @@ class Value:
 
     def dynamic_update_slice(self, update, starts, sizes):
         return self.b.emit({"DynamicUpdateSlice": {"sizes": list(sizes)}}, [self, update, starts], self.dtype, self.dims)
+
+    def dequantize(self, scales):
+        """Operation::Dequantize(DequantizeSpec { axis, output_dtype }) (spec.rs:585-589) in this backend's scheme: self =
+        si8 [N][K] with fp16 scales [N], or ui8 [N][K/2] (two si4 per byte, low nibble first) with fp16 scales [N][K/128];
+        the result is f32 [N][K] = q * scale."""
+        n = self.dims[0]
+        k = self.dims[1] * (2 if self.dtype == UI8 else 1)
+        return self.b.emit({"Dequantize": {"axis": 0, "output_dtype": F32}}, [self, scales], F32, [n, k])
+
+    def cast(self, dtype):
+        return self.b.emit({"Cast": {"dtype": dtype}}, [self], dtype, self.dims)
 
     def compare(self, op, other):
         return self.b.emit({"Compare": {"op": op}}, [self, other], I1, self.dims)

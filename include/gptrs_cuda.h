@@ -451,6 +451,15 @@ void* gptrs_cuda_model_stream(gptrs_model* m); /* cudaStream_t of the model */
  * ops/functional/normalization.rs:133-206, common.rs:22-31, tensor_ops.rs:50-55) into single kernels. */
 int gptrs_cuda_run_program(const char* program_json, size_t len, gptrs_tensor* const* inputs, size_t n_inputs,
                            gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs, void* stream);
+/* The same in two steps, for a caller that keeps its own cache of compiled programs (the reference's graph arena does:
+ * global program cache by structural compile key, crates/gpt-rs/src/ops/graph/arena.rs:756-779): prepare parses,
+ * verifies, rewrites and plans the buffers of a program once (on the current device) and returns a handle;
+ * program_run executes it without touching the text again. */
+typedef struct gptrs_program gptrs_program;
+int gptrs_cuda_program_prepare(const char* program_json, size_t len, gptrs_program** out);
+int gptrs_cuda_program_run(gptrs_program* program, gptrs_tensor* const* inputs, size_t n_inputs, gptrs_tensor** outputs,
+                           size_t outputs_cap, size_t* n_outputs, void* stream);
+void gptrs_cuda_program_release(gptrs_program* program);
 /* execute_instruction (spec.rs:1318-1323): one Instruction as serde JSON ({"id", "op", "operands", "output"}) with one
  * handle per operand, in operand order (the handle of a Literal operand is not read and may be NULL). Runs through the
  * same executor as run_program, so the supported operations and the error kinds are the same. */
@@ -473,6 +482,21 @@ int gptrs_cuda_verify_program(const char* program_json, size_t len);
 int gptrs_cuda_run_program_stats(int64_t* plan_builds, int64_t* plan_hits, int64_t* last_launches, int64_t* last_fused);
 /* Turns the fusion rewrites of run_program on (default) or off (GPTRS_OPT-style switch for tests). */
 int gptrs_cuda_set_fusion(int enabled);
+/* Turns the per-plan buffer plan of run_program on (default) or off: with it the temporaries of a function live at
+ * fixed offsets of one arena per cached plan (lifetime analysis, the counterpart of the reference's bufferisation,
+ * crates/gpt-rs/src/backend/conversion/bufferize.rs); without it each is a pooled allocation of its own. Drops the
+ * cached plans. */
+int gptrs_cuda_set_buffer_plan(int enabled);
+/* The four hooks of BackendPipeline (crates/gpt-rs/src/backend/pipeline.rs:60-65, default order :74-119) as text-to-text
+ * passes over a program: phase = "pre" | "legalize" | "fuse" | "cleanup". The rewrites of this backend (norms, softmax,
+ * matmul + bias, decode attention, dequant + dot_general, norm + residual) belong in "pre", before the reference's
+ * ParamOnlyFoldToParam erases the broadcast structure the norm patterns rely on, exactly where its Triton backend
+ * installs its own (crates/gpt-rs-backend-triton/src/optimizer/pipeline.rs:73-78); "fuse" runs the same rewrites on
+ * whatever reaches it; "legalize" and "cleanup" verify the program and return it unchanged (every operation of the
+ * subset runs as written, and the rewrites remove their own dead instructions). Same out / written convention as
+ * gptrs_cuda_pipeline_fuse. */
+int gptrs_cuda_pipeline(const char* phase, const char* program_json, size_t len, char* out, size_t out_cap, size_t* written,
+                        int64_t* n_rewrites);
 
 /* ==============================================================================================
  * Multi-GPU: request-partitioned data parallelism (no counterpart in gpt.rs, whose model path is

@@ -20,7 +20,7 @@ import math
 
 import numpy as np
 
-DTYPES = {"F32": np.float32, "Si32": np.int32, "I1": np.bool_}
+DTYPES = {"F32": np.float32, "Si32": np.int32, "I1": np.bool_, "Si8": np.int8, "Ui8": np.uint8, "F16": np.float16}
 
 
 class PtirError(Exception):
@@ -230,6 +230,14 @@ def execute_instruction(op, ins, out_spec):
         return base
     if kind == "StopGradient":
         return ins[0]
+    if kind == "Dequantize":
+        # backend-defined scheme (docs/backend.md:620-632): si8 [N][K] x fp16 [N], or two si4 per byte [N][K/2] x fp16 [N][K/128]
+        from . import quant_ref as qr
+        if ins[0].dtype == np.int8:
+            return qr.dequant_w8(ins[0], ins[1])
+        if ins[0].dtype == np.uint8:
+            return qr.dequant_w4(ins[0], ins[1])
+        raise PtirError("dequantize of an unsupported dtype")
     if kind == "CustomCall":
         return _cuda_custom_call(attr, ins, out_dims)
     raise PtirError(f"unsupported operation {kind}")

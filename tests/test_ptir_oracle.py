@@ -197,11 +197,14 @@ def test_pipeline_fuse_rewrites_to_custom_calls(kind):
     body0, body1 = before["functions"][0]["body"], after["functions"][0]["body"]
     assert len(body1) < len(body0) * 6 // 10  # 257 -> 135 instructions for the two-layer Ministral step (RoPE stays op by op)
     targets = [i["op"]["CustomCall"]["target"] for i in body1 if isinstance(i["op"], dict) and "CustomCall" in i["op"]]
-    # each layer's softmax rewrite is absorbed by the attention rewrite that follows it
-    assert len(targets) == n_fused - cfg.n_layers and all(t.startswith("gpt_rs.cuda.") and t.endswith(".f32.v1") for t in targets)
+    # each layer's softmax rewrite is absorbed by the attention rewrite that follows it, and the last block's residual add
+    # is folded into the final norm (a rewrite of an already rewritten norm; the other sums stay: they are read again)
+    folded = sum(t.startswith("gpt_rs.cuda.add_") for t in targets)
+    assert folded == 1 and len(targets) == n_fused - cfg.n_layers - folded
+    assert all(t.startswith("gpt_rs.cuda.") and t.endswith(".f32.v1") for t in targets)
     assert targets.count("gpt_rs.cuda.attention_decode.f32.v1") == cfg.n_layers
     norm = "gpt_rs.cuda.layer_norm.f32.v1" if kind == "gpt" else "gpt_rs.cuda.rms_norm.f32.v1"
-    assert targets.count(norm) == 2 * cfg.n_layers + 1
+    assert targets.count(norm) + targets.count(norm.replace("cuda.", "cuda.add_")) == 2 * cfg.n_layers + 1
     for k in ("spec_version", "entry", "regions"):
         assert after[k] == before[k]
     f0, f1 = before["functions"][0], after["functions"][0]
@@ -240,3 +243,44 @@ def test_pipeline_fuse_keeps_escaping_values_and_rejects_bad_input():
         p = bb.parameter(F32, [4])
         bb.set_results([bb.custom_call("gpt_rs.someone_else.op.v1", [p], F32, [4])])
         _run(bb, [np.zeros(4, np.float32)])
+
+
+def test_pipeline_phases_and_quantised_rewrites_in_text_form():
+    """The four BackendPipeline hooks as text-to-text passes (host only): "pre" / "fuse" write the CustomCalls,
+    "legalize" / "cleanup" hand a verified program back unchanged. The dequant + dot_general and norm + residual
+    rewrites appear under their own versioned targets, with serde's adjacently tagged attributes."""
+    from gptrs_b200 import BackendError
+    from gptrs_b200.backend import pipeline
+    b = ptir.Builder()
+    x = b.parameter(ptir.F32, [4, 256])
+    r = b.parameter(ptir.F32, [4, 64])
+    g = b.parameter(ptir.F32, [64])
+    q = b.parameter(ptir.UI8, [64, 128])
+    s = b.parameter(ptir.F16, [64, 2])
+    y = x.dot_general(q.dequantize(s).transpose([1, 0]), [], [1], [0])    # [4, 64]
+    n = ptir.rms_norm(r + y, g, 1e-5)                                      # the sum has no other reader: one CustomCall
+    b.set_results([n])
+    text = b.to_json()
+    out, n_rw = pipeline("pre", text)
+    body = json.loads(out)["functions"][0]["body"]
+    targets = [i["op"]["CustomCall"]["target"] for i in body if isinstance(i["op"], dict) and "CustomCall" in i["op"]]
+    assert targets == ["gpt_rs.cuda.quant_matmul_w4a16.v1", "gpt_rs.cuda.add_rms_norm.f32.v1"] and n_rw == 3
+    norm = [i for i in body if isinstance(i["op"], dict) and "CustomCall" in i["op"]][1]
+    assert norm["op"]["CustomCall"]["attrs"]["eps"]["kind"] == "F64" and abs(norm["op"]["CustomCall"]["attrs"]["eps"]["value"] - 1e-5) < 1e-12
+    assert not any(isinstance(i["op"], dict) and ("Dequantize" in i["op"] or "Transpose" in i["op"]) for i in body)
+    again, n2 = pipeline("fuse", out)                                       # nothing left to rewrite
+    assert n2 == 0 and json.loads(again) == json.loads(out)
+    for phase in ("legalize", "cleanup"):
+        same, n0 = pipeline(phase, out)
+        assert n0 == 0 and json.loads(same) == json.loads(out)
+    with pytest.raises(BackendError) as e:
+        pipeline("lower", text)
+    assert e.value.kind == "SpecViolation"
+    # the rewritten program means the same: the oracle runs both
+    rng = np.random.default_rng(0)
+    ins = [rng.normal(0, 1, size=(4, 256)).astype(np.float32), rng.normal(0, 1, size=(4, 64)).astype(np.float32),
+           (1 + 0.1 * rng.normal(size=64)).astype(np.float32), rng.integers(0, 256, size=(64, 128), dtype=np.uint8),
+           np.exp(rng.normal(-5, 0.5, size=(64, 2))).astype(np.float16)]
+    a = pr.run_program(json.loads(text), ins)[0]
+    c = pr.run_program(json.loads(out), ins)[0]
+    assert np.abs(a - c).max() <= 2e-2 * max(1.0, float(np.abs(a).max()))   # the fused matmul rounds its activations to bf16

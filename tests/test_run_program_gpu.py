@@ -317,7 +317,11 @@ def test_run_program_accepts_the_fuse_phase_output(be, kind):
         be.set_fusion(fusion)
         got = [be.to_literal(h) for h in be.run_program(fused_text, hs)]
         st = be.run_program_stats()
-        assert st["last_fused"] == 0  # the text already holds the fused operations
+        # the text already holds the fused operations; in process, the residual adds whose sums are read again are
+        # folded into their norms as well (a second result the text form of a CustomCall cannot carry)
+        # (per block the attention and the MLP residual; the last one is already folded in the text; GPT-2 adds the
+        # token + position embedding sum in front of the first norm)
+        assert st["last_fused"] == ((2 * cfg.n_layers - (0 if kind == "gpt" else 1)) if fusion else 0)
         assert len(got) == len(want)
         for a, e in zip(got, want):
             assert np.allclose(a, e, rtol=1e-4, atol=1e-4)
