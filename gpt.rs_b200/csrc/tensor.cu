@@ -247,3 +247,65 @@ int gptrs_cuda_param_set(uint64_t id_lo, uint64_t id_hi, gptrs_tensor* h) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// Backend object (PortableBackend is `Send + Sync` and a process may hold one per GPU,
+// crates/gpt-rs/src/backend/spec.rs:1287-1349): a device ordinal and a stream of its own. Every call made through
+// the object first makes its device current on the calling thread, so two threads can drive two backends (or two
+// models of one backend) without sharing any per-thread launch state. What the library keeps per device (pools,
+// function attributes, status words, SM counts, cached plans) is keyed by the ordinal.
+// ---------------------------------------------------------------------------------------------------------------
+struct gptrs_backend {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+};
+
+extern "C" {
+
+int gptrs_cuda_create(int device, gptrs_backend** out) {
+    GPTRS_REQUIRE(out, "null pointer");
+    int n = 0;
+    GPTRS_CUDA_OK(cudaGetDeviceCount(&n));
+    GPTRS_REQUIRE(device >= 0 && device < n && device < gptrs::kMaxDevices, "no such CUDA device");
+    GPTRS_CUDA_OK(cudaSetDevice(device));
+    int major = 0;
+    GPTRS_CUDA_OK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10) return gptrs::fail(GPTRS_UNIMPLEMENTED, "this backend is built for sm_100a (B200) only");
+    auto* b = new gptrs_backend();
+    b->device = device;
+    cudaError_t e = cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { delete b; return gptrs::fail(GPTRS_EXECUTION, std::string("cudaStreamCreate: ") + cudaGetErrorString(e)); }
+    *out = b;
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_destroy(gptrs_backend* b) {
+    if (!b) return GPTRS_OK;
+    cudaSetDevice(b->device);
+    if (b->stream) { cudaStreamSynchronize(b->stream); cudaStreamDestroy(b->stream); }
+    delete b;
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_backend_make_current(gptrs_backend* b) {
+    GPTRS_REQUIRE(b, "null backend");
+    GPTRS_CUDA_OK(cudaSetDevice(b->device));
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_backend_device(const gptrs_backend* b) { return b ? b->device : -1; }
+void* gptrs_cuda_backend_stream(gptrs_backend* b) { return b ? b->stream : nullptr; }
+
+int gptrs_cuda_backend_materialize_literal(gptrs_backend* b, int dtype, int rank, const int64_t* dims, const void* h_bytes, size_t n_bytes,
+                                           gptrs_tensor** out) {
+    int rc = gptrs_cuda_backend_make_current(b);
+    return rc ? rc : gptrs_cuda_materialize_literal(dtype, rank, dims, h_bytes, n_bytes, out);
+}
+
+int gptrs_cuda_backend_run_program(gptrs_backend* b, const char* program_json, size_t len, gptrs_tensor* const* inputs, size_t n_inputs,
+                                   gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs) {
+    int rc = gptrs_cuda_backend_make_current(b);
+    return rc ? rc : gptrs_cuda_run_program(program_json, len, inputs, n_inputs, outputs, outputs_cap, n_outputs, b->stream);
+}
+
+}  // extern "C"

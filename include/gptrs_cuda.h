@@ -341,6 +341,24 @@ int gptrs_cuda_kv_append_attention_decode_f32(const float* d_qkv, float* d_k_cac
  * reference counted (retain = Clone, release = Drop), thread safe, immutable once produced.
  * ============================================================================================ */
 typedef struct gptrs_tensor gptrs_tensor;
+/* A backend object: one device and one stream of its own (the trait is Send + Sync, spec.rs:1287-1349, and a process
+ * may hold one backend per GPU). create() checks the device (sm_100 only) and makes it current; the calls below make
+ * it current on the calling thread and then do what their process-level namesakes do, on the object's stream. All
+ * other entry points of this header act on the calling thread's current device and may be used after
+ * gptrs_cuda_backend_make_current(b). Launch options (programmatic launch, priorities) are per thread and what the
+ * library caches (memory pools, function attributes, status words, plans) is per device, so two threads may drive two
+ * backends, or two models of one, at the same time. */
+typedef struct gptrs_backend gptrs_backend;
+int gptrs_cuda_create(int device, gptrs_backend** out);
+int gptrs_cuda_destroy(gptrs_backend* b);
+int gptrs_cuda_backend_make_current(gptrs_backend* b);
+int gptrs_cuda_backend_device(const gptrs_backend* b);
+void* gptrs_cuda_backend_stream(gptrs_backend* b);
+int gptrs_cuda_backend_materialize_literal(gptrs_backend* b, int dtype, int rank, const int64_t* dims, const void* h_bytes,
+                                           size_t n_bytes, gptrs_tensor** out);
+int gptrs_cuda_backend_run_program(gptrs_backend* b, const char* program_json, size_t len, gptrs_tensor* const* inputs,
+                                   size_t n_inputs, gptrs_tensor** outputs, size_t outputs_cap, size_t* n_outputs);
+
 /* materialize(TensorInit::Literal | Zeroed) (spec.rs:295-300, 1312-1313): bytes are row-major
  * little-endian, n_bytes must equal numel * sizeof(dtype). Synchronous. */
 int gptrs_cuda_materialize_literal(int dtype, int rank, const int64_t* dims, const void* h_bytes, size_t n_bytes,
