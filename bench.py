@@ -19,7 +19,7 @@ Other modes (none of them the default line): --workload gpt2-fp32 (the reference
 f32 weights), --workload dp512 (512 requests with prompt lengths U{256..4096}, 256 decode steps each, bin-packed over the
 ranks and served in waves of 64: total work fixed, strong scaling), --weights w8a16, --parallelism tp (one batch over a
 tensor-parallel group), --microbench
-attention | attention-ragged | gemv | gemm64 | quant-linear (single kernels, CUDA-graph timed; used for ncu captures)
+attention | attention-ragged | gemv | gemv-lm-head | gemm64 | quant-linear (single kernels, CUDA-graph timed; used for ncu captures)
 | prefill (a few 2048-token prompts through the engine's chunked prefill; --steps = number of prompts).
 """
 from __future__ import annotations
@@ -618,7 +618,7 @@ def _main(out):
     ap.add_argument("--pdl", type=int, default=int(os.environ.get("GPTRS_PDL", "1")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the kernel microbenchmarks")
-    ap.add_argument("--microbench", default=None, choices=["attention", "attention-ragged", "gemv", "gemm64", "quant-linear", "prefill"],
+    ap.add_argument("--microbench", default=None, choices=["attention", "attention-ragged", "gemv", "gemv-lm-head", "gemm64", "quant-linear", "prefill"],
                     help="run only one kernel microbenchmark (used for ncu captures) and print its JSON")
     ap.add_argument("--ctx", type=int, default=PROMPT_LEN + 20, help="context length for --microbench attention")
     ap.add_argument("--workload", default="ministral3b-w4", choices=["ministral3b-w4", "gpt2-fp32", "dp512"],
@@ -709,7 +709,10 @@ def _main(out):
                               "rows": rows}), file=out)
         elif args.microbench == "gemv":
             us, nbytes = time_gemv(ops, torch, dev, n_mats=16, iters=1)
-            print(json.dumps({"kernel": "quant_matmul_kernel<1,4>", "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3}), file=out)
+            print(json.dumps({"kernel": "w4_gemv_kernel<1,2> M=1 N=9216 K=3072", "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3}), file=out)
+        elif args.microbench == "gemv-lm-head":
+            us, nbytes = time_gemv(ops, torch, dev, n=131072, k=3072, n_mats=4, iters=1)
+            print(json.dumps({"kernel": "w4_gemv_kernel<1,4> M=1 N=131072 K=3072", "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3}), file=out)
         else:
             us, nbytes = time_gemv(ops, torch, dev, n=6144, k=3072, m=64, n_mats=16, iters=1)
             print(json.dumps({"kernel": "umma_w4a16_kernel<64>", "us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3}), file=out)

@@ -44,6 +44,7 @@ struct MatmulParams {
     int groups_per_cta;  // K range of one CTA, in 128-k groups
     int n_split;         // cluster size along K
     int k_intra;         // GEMV kernel: warps of a CTA that split the CTA's K range among themselves (1, 2, 4, 8)
+    int gemv_stages;     // GEMV kernel: depth of every warp's ring of weight stages in shared memory
     int out_f32;
     int swiglu;
     // residual + RMSNorm folded into the matmuls (see gptrs_matmul_epilogue)

@@ -107,6 +107,24 @@ __device__ __forceinline__ void mbar_expect_tx_addr(uint32_t bar_addr, uint32_t 
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar_addr), "r"(bytes) : "memory");
 }
 
+// Eight packed nibbles of one word -> four bf16 pairs 128 + (q + 8): nibbles i and i + 4 land in the mantissas of pair i.
+// PTX keeps the shape (three shifts, four three-input logic ops); the optimiser would move the mask in front of the shift
+// and make the OR an instruction of its own, and the logic pipe runs at half rate.
+__device__ __forceinline__ void nibbles_to_bf16_biased(uint32_t q, uint32_t (&u)[4]) {
+    asm("{\n"
+        ".reg .b32 t1, t2, t3;\n"
+        "shr.u32 t1, %4, 4;\n"
+        "shr.u32 t2, %4, 8;\n"
+        "shr.u32 t3, %4, 12;\n"
+        "lop3.b32 %0, %4, 0x000f000f, 0x43004300, 0xEA;\n"
+        "lop3.b32 %1, t1, 0x000f000f, 0x43004300, 0xEA;\n"
+        "lop3.b32 %2, t2, 0x000f000f, 0x43004300, 0xEA;\n"
+        "lop3.b32 %3, t3, 0x000f000f, 0x43004300, 0xEA;\n"
+        "}\n"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3])
+        : "r"(q));
+}
+
 // One 16-byte entry of packed weights -> bf16, stored as 16-byte chunks of the 128-byte-swizzled K-major operand
 // tile. W4: a word holds 8 consecutive k (nibble i = k 2i, nibble i + 4 = k 2i + 1, stored + 8); the fp16 group
 // scale is hi + lo exactly (8 + 3 significant bits), so that fma(n, hi, n * lo) is the product n * scale rounded
@@ -124,10 +142,11 @@ __device__ __forceinline__ void dequant_cols(const uint4 cur, const __half scale
         const __nv_bfloat162 sc_lo = __float2bfloat162_rn(sf - __bfloat162float(hi));
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const uint32_t q = q4[w];
+            uint32_t u4[4];
+            nibbles_to_bf16_biased(q4[w], u4);   // (k 2i, k 2i+1) + 128
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;   // (k 2i, k 2i+1) + 128
+                uint32_t u = u4[i];
                 const __nv_bfloat162 n = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136);
                 __nv_bfloat162 d = __hfma2(n, sc, __hmul2(n, sc_lo));
                 out[w * 4 + i] = *reinterpret_cast<uint32_t*>(&d);
@@ -345,11 +364,11 @@ umma_w4a16_kernel(const MatmulParams p, const __grid_constant__ CUtensorMap x_ma
                         if (BITS == 4) {
 #pragma unroll
                             for (int w = 0; w < 4; ++w) {
-                                const uint32_t q = q4[w];
-                                uint32_t vv[4];
+                                uint32_t vv[4], u4[4];
+                                nibbles_to_bf16_biased(q4[w], u4);   // (k 2i, k 2i+1) + 128
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
-                                    uint32_t u = ((q >> (4 * i)) & 0x000f000fu) | 0x43004300u;   // (k 2i, k 2i+1) + 128
+                                    uint32_t u = u4[i];
                                     const __nv_bfloat162 n = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), c136);
                                     __nv_bfloat162 d = __hfma2(n, sc, __hmul2(n, sc_lo));
                                     vv[i] = *reinterpret_cast<uint32_t*>(&d);
@@ -868,6 +887,8 @@ int launch_stream(MatmulParams p, dim3 grid, cudaStream_t st) {
 }
 
 }  // namespace
+
+int* matmul_status_word() { return umma_status_word(); }
 
 // Grid geometry shared by both weight formats: row tile, cluster K split, CTA count.
 struct UmmaPlan { bool big_tile; int n_blocks, m_blocks, split; };
