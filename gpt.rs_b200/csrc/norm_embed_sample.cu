@@ -13,6 +13,10 @@
 //                       index, docs/backend.md:270; Gumbel-max for temperature > 0 as in
 //                       crates/gpt-rs-backend-triton/src/kernels/sample_temperature_last_axis_f32.triton:45-69)
 #include "common.cuh"
+#include "tensor.h"
+
+#include <cmath>
+#include <cstring>
 
 namespace gptrs {
 namespace {
@@ -521,16 +525,24 @@ int gptrs_cuda_sample_decode_token_top_k(const float* d_logits, int64_t rows, in
     GPTRS_REQUIRE(d_logits && has_token && token, "null pointer");
     GPTRS_REQUIRE(rows >= 1 && vocab > 0, "bad shape");
     *has_token = 0;
-    int32_t* d_tok = nullptr;
-    GPTRS_CUDA_OK(cudaMalloc(&d_tok, sizeof(int32_t)));
     uint32_t seed = 0;
-    if (has_random_u) { float u = random_u; seed = *reinterpret_cast<uint32_t*>(&u); }
+    if (temperature > 0.f) {
+        // no usable draw from the caller: the host sampler decides (runtime/sampling.rs:94-97 of the triton backend)
+        if (!has_random_u || !std::isfinite(random_u)) return GPTRS_OK;
+        uint32_t bits;
+        memcpy(&bits, &random_u, sizeof(bits));
+        seed = bits * 747796405u + 2891336453u;   // the same seed mix (runtime/sampling.rs:98-101)
+    }
+    void* buf = nullptr;
+    int dev = 0;
+    GPTRS_CUDA_OK(pool_alloc(&buf, 256, &dev));
+    int32_t* d_tok = static_cast<int32_t*>(buf);
     int rc = gptrs_cuda_sample_rows_top_k(d_logits + (size_t)(rows - 1) * vocab, 1, vocab, temperature, top_k, seed, d_tok, stream);
     int32_t h = 0;
     cudaError_t e = cudaSuccess;
     if (rc == GPTRS_OK) e = cudaMemcpyAsync(&h, d_tok, sizeof(h), cudaMemcpyDeviceToHost, as_stream(stream));
     if (rc == GPTRS_OK && e == cudaSuccess) e = cudaStreamSynchronize(as_stream(stream));
-    cudaFree(d_tok);
+    pool_free(buf, 256, dev);
     if (rc != GPTRS_OK) return rc;
     GPTRS_CUDA_OK(e);
     *has_token = 1;

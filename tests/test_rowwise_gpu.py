@@ -116,6 +116,9 @@ def test_sampler_known_answers(cuda):
     assert ops.sample_decode_token(l2, 0.0) == 1
     tok = ops.sample_decode_token(logits, 0.8, random_u=0.37)
     assert 0 <= tok < 4
+    # a temperature without a draw from the caller is left to the host sampler (runtime/sampling.rs:94-97)
+    assert ops.sample_decode_token(logits, 0.8) is None
+    assert ops.sample_decode_token(logits, 0.8, random_u=float("nan")) is None
     rng = np.random.default_rng(0)
     big = rng.normal(0, 1, size=(64, 131072)).astype(np.float32)
     got = ops.sample_rows(_d(big, cuda)).cpu().numpy()
