@@ -450,7 +450,11 @@ int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* m, const int32_t* h_
  * step() runs one greedy decode step for the whole batch. h_tokens_in (optional) overrides the
  * device-resident inputs, h_tokens_out (optional) receives the sampled ids and makes the call
  * synchronous; with both NULL the ids stay on the device and feed the next step. use_graph != 0
- * replays a CUDA graph of the step (recorded on first use per launch geometry). */
+ * replays a CUDA graph of the step (recorded on first use per launch geometry).
+ * A sequence whose length has reached the model's context_length slides its window first, as Generator::step does
+ * (crates/gpt-rs/src/inference/generate.rs:127-134: the window start moves up, the caches are dropped and the window
+ * is processed again from position 0): the oldest token leaves, the remaining context_length - 1 tokens of the
+ * device-side history are prefilled at positions 0.., then the step runs at the last position. */
 int gptrs_cuda_generator_begin(gptrs_model* m, int batch, const int32_t* h_first_tokens);
 int gptrs_cuda_generator_step(gptrs_model* m, const int32_t* h_tokens_in, int32_t* h_tokens_out, int use_graph);
 /* Waits for the model's stream and reports a device-side error recorded by any step. */
