@@ -540,13 +540,8 @@ def measure_tp(args, gm, torch, np, dist, world, rank, dev, single_rank_model, s
     decodes eight greedy steps; the tensor-parallel engine does the same, fed the single-rank ids at every step; the
     72 ids are compared one by one (the weights are random, so a few exact near-ties between the two summation orders
     are possible: the count is reported)."""
-    box = [gm.nccl_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(box, src=0)
     steps_total = args.warmup + args.steps + 32
-    model, cfg = build_model(gm, torch, dev, steps_total, args.pdl, args.prefill_chunk, world, rank, box[0])
-    rng = np.random.default_rng(1000)
-    # correctness first, on fresh slots
-    short = [np.random.default_rng(77 + i).integers(0, cfg.vocab, size=48) for i in range(8)]
+    short = [np.random.default_rng(77 + i).integers(0, 131072, size=48) for i in range(8)]
 
     def greedy(m, forced=None):
         """First id from every prompt, then eight decode steps. With `forced` (the ids of another engine) every step is
@@ -564,35 +559,53 @@ def measure_tp(args, gm, torch, np, dist, world, rank, dev, single_rank_model, s
 
     ref_box = [greedy(single_rank_model) if rank == 0 else None]
     dist.broadcast_object_list(ref_box, src=0)
-    tp_ids = greedy(model, forced=ref_box[0])
-    differ = sum(int(a != b) for ra, rb in zip(tp_ids, ref_box[0]) for a, b in zip(ra, rb))
-    flags = torch.tensor([differ], dtype=torch.int32, device=dev)
-    dist.all_reduce(flags, op=dist.ReduceOp.MAX)
-    # timing
-    prompts = [rng.integers(0, cfg.vocab, size=PROMPT_LEN) for _ in range(BATCH)]
-    first = model.prefill_many(list(range(BATCH)), prompts, chunk=args.prefill_chunk)
-    gen = gm.Generator(model, first, use_graph=True)
-    stream = torch.cuda.ExternalStream(lib_stream(model), device=dev)
-    for _ in range(args.warmup):
-        gen.step(read_back=False)
-    gen.sync()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    dist.barrier()
-    torch.cuda.synchronize()
-    e0.record(stream)
-    for _ in range(args.steps):
-        gen.step(read_back=False)
-    e1.record(stream)
-    gen.sync()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t[0]) / args.steps
-    del gen
-    model.close()
+
+    def one(collective):
+        """Builds the tensor-parallel engine with the given collective, checks it, times it."""
+        if collective == "nccl":
+            os.environ["GPTRS_TP_ALLREDUCE"] = "nccl"
+        else:
+            os.environ.pop("GPTRS_TP_ALLREDUCE", None)
+        box = [gm.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        model, cfg = build_model(gm, torch, dev, steps_total, args.pdl, args.prefill_chunk, world, rank, box[0])
+        kind = model.tp_allreduce_kind()
+        tp_ids = greedy(model, forced=ref_box[0])
+        differ = sum(int(a != b) for ra, rb in zip(tp_ids, ref_box[0]) for a, b in zip(ra, rb))
+        flags = torch.tensor([differ], dtype=torch.int32, device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+        rng = np.random.default_rng(1000)
+        prompts = [rng.integers(0, cfg.vocab, size=PROMPT_LEN) for _ in range(BATCH)]
+        first = model.prefill_many(list(range(BATCH)), prompts, chunk=args.prefill_chunk)
+        gen = gm.Generator(model, first, use_graph=True)
+        stream = torch.cuda.ExternalStream(lib_stream(model), device=dev)
+        for _ in range(args.warmup):
+            gen.step(read_back=False)
+        gen.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(args.steps):
+            gen.step(read_back=False)
+        e1.record(stream)
+        gen.sync()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        del gen
+        model.close()
+        os.environ.pop("GPTRS_TP_ALLREDUCE", None)
+        return float(t[0]) / args.steps, int(flags[0]), kind
+
+    ms, differ, kind = one("peer")
+    ms_nccl, differ_nccl, kind_nccl = one("nccl")
+    n_collectives = 2 * 26
     return {"parallelism": f"tp{world}", "batch": BATCH, "ms_per_step": ms, "tokens_per_s": BATCH / (ms * 1e-3),
-            "collective": "ncclAllReduce(sum, f32 [64, 3072]) after o_proj and down_proj, recorded in the decode graph",
-            "check": {"same_greedy_ids_as_single_rank": int(flags[0]) == 0, "ids_that_differ": int(flags[0]), "ids_compared": 72,
+            "collective": f"{kind}: all-reduce(sum, f32 [64, 3072]) after o_proj and down_proj, {n_collectives} per step, inside the decode graph",
+            "with_nccl_allreduce": {"collective": kind_nccl, "ms_per_step": ms_nccl, "ids_that_differ": differ_nccl,
+                                    "us_per_collective_saved": (ms_nccl - ms) * 1e3 / n_collectives},
+            "check": {"same_greedy_ids_as_single_rank": differ == 0, "ids_that_differ": differ, "ids_compared": 72,
                       "prompts": 8, "steps": 8}}
 
 

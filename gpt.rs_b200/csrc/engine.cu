@@ -22,6 +22,7 @@
 #include <vector>
 
 #include "nccl_dl.h"
+#include "peer_allreduce.h"
 #include "tensor.h"
 
 namespace gptrs {
@@ -119,6 +120,11 @@ struct Model {
     // tensor parallelism: cfg holds the LOCAL head / MLP sizes; the full sizes are kept here
     int tp = 1, tp_rank = 0, full_q = 0, full_kv = 0, full_mlp = 0, vocab_l = 0;
     NcclComm comm = nullptr;
+    // one-shot all-reduce over peer memory (decode-sized messages); the regions of the peers are IPC mappings
+    void* peer_region = nullptr;
+    void* peer_maps[kMaxPeers] = {};
+    PeerView peer = {};
+    bool peer_on = false;
     DevBuf partial, tp_vals, tp_idx, tp_gvals, tp_gidx;  // row-parallel partial sums; (max, argmax) exchange
     int gen_batch = 0;  // slots 0..gen_batch-1 are driven by generator_step
     int64_t launches = 0;
@@ -142,6 +148,8 @@ struct Model {
         if (h_page_table) cudaFreeHost(h_page_table);
         if (h_stage) cudaFreeHost(h_stage);
         if (h_logits) cudaFreeHost(h_logits);
+        for (void* p : peer_maps) if (p) cudaIpcCloseMemHandle(p);
+        if (peer_region) cudaFree(peer_region);
         if (comm) { std::string e; if (const NcclApi* api = nccl_api(&e)) api->CommDestroy(comm); }
         for (cudaEvent_t e : ev_a) cudaEventDestroy(e);
         for (cudaEvent_t e : ev_b) cudaEventDestroy(e);
@@ -467,10 +475,16 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         }
         int r = linear(m, w, x, m.partial.p, ln.T, true, nullptr, false, false, ln.st);
         if (r) return r;
+        pending = m.partial.as<float>();
+        if (m.peer_on && (size_t)ln.T * D <= m.peer.cap_floats) {
+            // every rank stores its partial tile into the peers' receive slots, then adds up what it received
+            m.launches += 2;
+            if ((r = peer_push(m.peer, m.partial.as<float>(), (size_t)ln.T * D, ln.st))) return r;
+            return peer_wait_sum(m.peer, m.partial.as<float>(), (size_t)ln.T * D, m.d_status.as<int32_t>(), kPeerSpinLimit, ln.st);
+        }
         ++m.launches;
         int nr = nccl->AllReduce(m.partial.p, m.partial.p, (size_t)ln.T * D, kNcclFloat32, kNcclSum, m.comm, ln.st);
         if (nr) return fail(GPTRS_EXECUTION, std::string("ncclAllReduce: ") + nccl->GetErrorString(nr));
-        pending = m.partial.as<float>();
         return GPTRS_OK;
     };
     auto norm = [&](const Lane& ln, Tensor* g, Tensor* b) {
@@ -665,6 +679,57 @@ int sync_page_table(Model& m) {
     return GPTRS_OK;
 }
 
+// Maps every peer's receive region into this process (CUDA IPC) so that the row-parallel partial sums of a decode
+// step travel as plain stores over NVLink. The 64-byte handles are exchanged with the communicator that already
+// exists; if any rank cannot map any peer, every rank stays on ncclAllReduce (the ranks agree through one more
+// all-reduce). GPTRS_TP_ALLREDUCE=nccl keeps the library collective.
+int setup_peer_allreduce(Model& m, int max_rows_peer) {
+    if (const char* e = getenv("GPTRS_TP_ALLREDUCE")) if (!strcmp(e, "nccl")) return GPTRS_OK;
+    std::string err;
+    const NcclApi* api = nccl_api(&err);
+    if (!api) return fail(GPTRS_EXECUTION, err);
+    const size_t cap = (size_t)max_rows_peer * m.cfg.d_model;
+    if (cap % 4) return GPTRS_OK;
+    const size_t bytes = peer_region_bytes(m.tp, cap);
+    int failures = 0;
+    cudaIpcMemHandle_t mine;
+    memset(&mine, 0, sizeof(mine));
+    if (cudaMalloc(&m.peer_region, bytes) != cudaSuccess) { m.peer_region = nullptr; failures = 1; cudaGetLastError(); }
+    if (!failures && (cudaMemset(m.peer_region, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+                      cudaIpcGetMemHandle(&mine, m.peer_region) != cudaSuccess)) { failures = 1; cudaGetLastError(); }
+    DevBuf send, all, flag;
+    int rc;
+    if ((rc = send.alloc(sizeof(mine))) || (rc = all.alloc(sizeof(mine) * m.tp)) || (rc = flag.alloc(4))) return rc;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 16 int32");
+    GPTRS_CUDA_OK(cudaMemcpyAsync(send.p, &mine, sizeof(mine), cudaMemcpyHostToDevice, m.stream));
+    int nr = api->AllGather(send.p, all.p, 16, kNcclInt32, m.comm, m.stream);
+    if (nr) return fail(GPTRS_EXECUTION, std::string("ncclAllGather: ") + api->GetErrorString(nr));
+    std::vector<cudaIpcMemHandle_t> handles(m.tp);
+    GPTRS_CUDA_OK(cudaMemcpyAsync(handles.data(), all.p, sizeof(mine) * m.tp, cudaMemcpyDeviceToHost, m.stream));
+    GPTRS_CUDA_OK(cudaStreamSynchronize(m.stream));
+    for (int p = 0; p < m.tp && !failures; ++p) {
+        if (p == m.tp_rank) continue;
+        if (cudaIpcOpenMemHandle(&m.peer_maps[p], handles[p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            m.peer_maps[p] = nullptr;
+            failures = 1;
+            cudaGetLastError();
+        }
+    }
+    // agreement: the sum of the failure counts of all ranks
+    GPTRS_CUDA_OK(cudaMemcpyAsync(flag.p, &failures, 4, cudaMemcpyHostToDevice, m.stream));
+    nr = api->AllReduce(flag.p, flag.p, 1, kNcclInt32, kNcclSum, m.comm, m.stream);
+    if (nr) return fail(GPTRS_EXECUTION, std::string("ncclAllReduce: ") + api->GetErrorString(nr));
+    int total = 0;
+    GPTRS_CUDA_OK(cudaMemcpyAsync(&total, flag.p, 4, cudaMemcpyDeviceToHost, m.stream));
+    GPTRS_CUDA_OK(cudaStreamSynchronize(m.stream));
+    if (total != 0) return GPTRS_OK;   // some rank could not map a peer: everyone keeps the library collective
+    peer_view_local(&m.peer, m.peer_region, m.tp, m.tp_rank, cap);
+    for (int p = 0; p < m.tp; ++p)
+        if (p != m.tp_rank) peer_view_connect(&m.peer, p, m.peer_maps[p]);
+    m.peer_on = true;
+    return GPTRS_OK;
+}
+
 int check_status(Model& m) {
     int32_t st = 0;
     GPTRS_CUDA_OK(cudaMemcpyAsync(&st, m.d_status.p, 4, cudaMemcpyDeviceToHost, m.stream));
@@ -673,6 +738,7 @@ int check_status(Model& m) {
         cudaMemsetAsync(m.d_status.p, 0, 4, m.stream);
         return fail(GPTRS_EXECUTION, st == 2   ? "token or position id out of range"
                                      : st == 3 ? "a bounded wait inside a tensor-core matmul kernel gave up"
+                                     : st == 4 ? "a tensor-parallel peer did not deliver its partial sums in time"
                                                : "a bounded wait inside the attention kernel gave up");
     }
     return GPTRS_OK;
@@ -813,6 +879,12 @@ int gptrs_cuda_model_init_tensor_parallel(gptrs_model* h, const uint8_t* unique_
     return GPTRS_OK;
 }
 
+int gptrs_cuda_model_tp_allreduce_kind(gptrs_model* h) {
+    if (!h) return 0;
+    const Model& m = *reinterpret_cast<Model*>(h);
+    return m.tp <= 1 ? 0 : (m.peer_on ? 2 : 1);
+}
+
 int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
     GPTRS_REQUIRE(h, "null pointer");
     Model& m = *reinterpret_cast<Model*>(h);
@@ -898,6 +970,7 @@ int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
     if (m.tp > 1 && ((rc = m.partial.alloc((size_t)T * D * 4)) || (rc = m.tp_vals.alloc((size_t)max_rows * 4)) || (rc = m.tp_idx.alloc((size_t)max_rows * 4)) ||
                      (rc = m.tp_gvals.alloc((size_t)m.tp * max_rows * 4)) || (rc = m.tp_gidx.alloc((size_t)m.tp * max_rows * 4)))) return rc;
     if ((rc = m.history.alloc((size_t)c.max_seqs * c.context_length * 4, true))) return rc;
+    if (m.tp > 1 && (rc = setup_peer_allreduce(m, std::min(T, 256)))) return rc;
     for (DevBuf* b : {&m.d_tokens, &m.d_slot, &m.d_pos, &m.d_ctx, &m.d_rows, &m.d_sampled})
         if ((rc = b->alloc((size_t)std::max(T, max_rows) * 4, true))) return rc;
     if ((rc = m.d_status.alloc(4, true))) return rc;

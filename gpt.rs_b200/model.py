@@ -175,6 +175,10 @@ class LoadedModel:
         buf = (ctypes.c_uint8 * 128).from_buffer_copy(unique_id)
         check(lib().gptrs_cuda_model_init_tensor_parallel(self._h, buf))
 
+    def tp_allreduce_kind(self) -> str:
+        """The collective behind the row-parallel projections of decode-sized steps (after finalize)."""
+        return {0: "none", 1: "nccl", 2: "peer-store one-shot"}[int(lib().gptrs_cuda_model_tp_allreduce_kind(self._h))]
+
     def finalize(self, drop_f32_leaves: bool = True):
         check(lib().gptrs_cuda_model_finalize(self._h, int(drop_f32_leaves)))
         self._finalized = True

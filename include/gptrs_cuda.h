@@ -428,6 +428,19 @@ int gptrs_cuda_model_set_rope_tables(gptrs_model* m, const float* h_cos, const f
  * finalize. With tp_size > 1 forward_with_decode_cache returns the rank's logits shard [rows][vocab/tp]. */
 int gptrs_cuda_nccl_unique_id(uint8_t* out128);
 int gptrs_cuda_model_init_tensor_parallel(gptrs_model* m, const uint8_t* unique_id128);
+/* Which collective adds up the row-parallel partial sums of decode-sized steps (valid after finalize): 0 = none
+ * (tp_size 1), 1 = ncclAllReduce, 2 = the library's one-shot all-reduce over NVLink peer memory — every rank stores its
+ * [rows, d_model] partial tile into a receive slot in every peer's memory (CUDA IPC mappings, plain peer stores), raises
+ * a flag there, and adds up what it received after a BOUNDED wait for the peers' flags (a wait that runs out records
+ * status 4, reported by the next synchronising call). Used for up to 256 rows; larger steps (prefill) stay on NCCL.
+ * GPTRS_TP_ALLREDUCE=nccl in the environment keeps the library collective everywhere. No counterpart in gpt.rs. */
+int gptrs_cuda_model_tp_allreduce_kind(gptrs_model* m);
+/* Test entry of that all-reduce: `tp` ranks emulated on ONE device (regions = tp * gptrs_cuda_peer_region_bytes(tp,
+ * cap_floats) zeroed bytes, partials [tp][n] f32, updated in place to the sum over ranks, `calls` times in a row). All
+ * pushes of a call are launched before its first wait, so no launch polls for a later one. */
+size_t gptrs_cuda_peer_region_bytes(int tp, int64_t cap_floats);
+int gptrs_cuda_debug_peer_allreduce(void* d_regions, float* d_partials, int tp, int64_t n, int64_t cap_floats, int calls,
+                                    int32_t* d_status, void* stream);
 /* Checks that every parameter is present, quantises + repacks Linear weights (memoised process-wide
  * by stable id, see gptrs_cuda_param_get), allocates activations and KV storage. */
 int gptrs_cuda_model_finalize(gptrs_model* m, int drop_f32_leaves);
