@@ -645,6 +645,7 @@ def _main(out):
     ap.add_argument("--decode-steps", type=int, default=256, help="dp512: decode steps per request")
     ap.add_argument("--weights", default="w4a16", choices=["w4a16", "w8a16"],
                     help="w8a16 = the same workload with per-channel int8 weights (not the default line)")
+    ap.add_argument("--sub", default="tp,dp512,gpt2", help="sub-records measured after the default line (comma list of tp, dp512, gpt2)")
     ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
                     help="dp: every rank decodes its own 64 requests (default); tp: all ranks share ONE batch of 64 "
                          "(tensor parallel, NCCL all-reduce after the row-parallel projections)")
@@ -858,15 +859,17 @@ def _main(out):
                                       "achieved_gbs": g_bytes / (g_us * 1e-6) / 1e9, "frac_of_peak": g_bytes / (g_us * 1e-6) / 1e9 / peak}
     if not args.no_extras and not tp:
         # sub-records: measured after the headline figures, in the same process group
-        if world > 1:
+        subs = set(args.sub.split(","))
+        if world > 1 and "tp" in subs:
             line["tp"] = measure_tp(args, gm, torch, np, dist, world, rank, dev, model, cfg)
         model.close()
         del model
         torch.cuda.empty_cache()
         sub = argparse.Namespace(**vars(args))
         sub.warmup = 3
-        line["dp512"] = strip_sub(measure_dp512(sub, gm, torch, np, dist, world, rank, dev))
-        if rank == 0 and world == 1:
+        if "dp512" in subs:
+            line["dp512"] = strip_sub(measure_dp512(sub, gm, torch, np, dist, world, rank, dev))
+        if rank == 0 and world == 1 and "gpt2" in subs:
             g2 = argparse.Namespace(**vars(args))
             g2.steps, g2.warmup = 64, 4
             line["gpt2_fp32"] = strip_sub(measure_gpt2(g2, gm, torch, np, cpu_baseline=not args.no_cpu_baseline, device_index=local))

@@ -1,5 +1,6 @@
 """Tensor-parallel decode (TP = 2) on two GPUs: column-parallel qkv / gate / up / lm_head, row-parallel
-w_out / w_down with one NCCL all-reduce each. Every rank must produce the same greedy ids as the
+w_out / w_down with one all-reduce each — the library's one-shot all-reduce over NVLink peer memory (plain peer
+stores, bounded waits, NVLS off) or ncclAllReduce. Every rank must produce the same greedy ids as the
 single-GPU oracle, and the logits shards, concatenated, the oracle's logits (f32 mode 1e-4, W4A16 2e-2).
 Skipped unless two CUDA devices are visible. Ranks are child processes; the NCCL id travels over gloo."""
 import os
@@ -17,11 +18,11 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 
-def _worker(rank, world, port, mode, q):
+def _worker(rank, world, port, mode, collective, q):
     """A rank that fails tells the parent through the queue and leaves with os._exit, so that the parent can end the
     other rank instead of waiting for a collective that will never complete."""
     try:
-        _worker_body(rank, world, port, mode, q)
+        _worker_body(rank, world, port, mode, collective, q)
     except BaseException as e:  # noqa: BLE001
         import traceback
         q.put(("error", rank, "".join(traceback.format_exception(type(e), e, e.__traceback__))))
@@ -30,11 +31,15 @@ def _worker(rank, world, port, mode, q):
         os._exit(1)
 
 
-def _worker_body(rank, world, port, mode, q):
+def _worker_body(rank, world, port, mode, collective, q):
     sys.path.insert(0, str(ROOT))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    if collective == "nccl":
+        os.environ["GPTRS_TP_ALLREDUCE"] = "nccl"
+    else:
+        os.environ.pop("GPTRS_TP_ALLREDUCE", None)
     import torch.distributed as dist
     import __graft_entry__ as entry
     entry.load_package()
@@ -54,6 +59,7 @@ def _worker_body(rank, world, port, mode, q):
         m.load_param(name, w)
     m.init_tensor_parallel(ids[0])
     m.finalize()
+    kind = m.tp_allreduce_kind()
     prompts = [[5, 17, 300, 41, 8, 99, 250], [77, 3]]
     shards, firsts = [], []
     for s, p in enumerate(prompts):
@@ -63,7 +69,7 @@ def _worker_body(rank, world, port, mode, q):
     gen = gm.Generator(m, firsts, use_graph=True)
     steps = [gen.step().tolist() for _ in range(5)]
     gathered = [None] * world
-    dist.all_gather_object(gathered, (rank, shards, firsts, steps))
+    dist.all_gather_object(gathered, (rank, shards, firsts, steps, kind))
     dist.barrier()
     m.close()
     dist.destroy_process_group()
@@ -71,8 +77,9 @@ def _worker_body(rank, world, port, mode, q):
         q.put(gathered)
 
 
+@pytest.mark.parametrize("collective", ["peer", "nccl"])
 @pytest.mark.parametrize("mode", [0, 1], ids=["f32", "w4a16"])
-def test_tp2_matches_single_gpu_oracle(mode):
+def test_tp2_matches_single_gpu_oracle(mode, collective):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
     import torch.multiprocessing as mp
@@ -83,7 +90,7 @@ def test_tp2_matches_single_gpu_oracle(mode):
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, collective, q)) for r in range(2)]
     for p in procs:
         p.start()
     try:
@@ -109,6 +116,8 @@ def test_tp2_matches_single_gpu_oracle(mode):
     tol = 1e-4 if mode == 0 else 2e-2
     gathered.sort(key=lambda t: t[0])
     assert gathered[0][2] == gathered[1][2] and gathered[0][3] == gathered[1][3]  # both ranks agree on every id
+    want_kind = "nccl" if collective == "nccl" else "peer-store one-shot"
+    assert gathered[0][4] == gathered[1][4] == want_kind, (gathered[0][4], gathered[1][4])
     prompts = [[5, 17, 300, 41, 8, 99, 250], [77, 3]]
     refs = [mr.RefModel(cfg, params) for _ in prompts]
     for s, p in enumerate(prompts):
