@@ -438,6 +438,7 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
     // that is all-reduced over NVLink and then added to the residual stream by the next norm kernel
     // (tensor-parallel steps always run as one lane).
     const float* pending = nullptr;
+    bool pending_peer = false;   // the pending tile still has to be summed over the ranks (by the norm kernel)
     // RMSNorm folded into the projections: quantised Ministral, one rank, more than 16 rows (tensor-core matmuls),
     // d_model a multiple of 128. The sums of squares of a lane live at a row offset of the shared buffer: a lane's
     // tile t is at sumsq + t * T_lane, so each lane gets a disjoint slab of [tiles][T_lane] floats.
@@ -477,10 +478,11 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         if (r) return r;
         pending = m.partial.as<float>();
         if (m.peer_on && (size_t)ln.T * D <= m.peer.cap_floats) {
-            // every rank stores its partial tile into the peers' receive slots, then adds up what it received
-            m.launches += 2;
-            if ((r = peer_push(m.peer, m.partial.as<float>(), (size_t)ln.T * D, ln.st))) return r;
-            return peer_wait_sum(m.peer, m.partial.as<float>(), (size_t)ln.T * D, m.d_status.as<int32_t>(), kPeerSpinLimit, ln.st);
+            // every rank stores its partial tile into the peers' receive slots; the norm that follows waits for the
+            // peers' flags and adds up the tiles
+            ++m.launches;
+            pending_peer = true;
+            return peer_push(m.peer, m.partial.as<float>(), (size_t)ln.T * D, ln.st);
         }
         ++m.launches;
         int nr = nccl->AllReduce(m.partial.p, m.partial.p, (size_t)ln.T * D, kNcclFloat32, kNcclSum, m.comm, ln.st);
@@ -493,6 +495,11 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         pending = nullptr;
         float* h = reinterpret_cast<float*>(at(m.hidden, (size_t)D * 4, ln));
         void* xn = at(m.xn, (size_t)D * act, ln);
+        if (pending_peer) {
+            pending_peer = false;
+            return add_norm_peer(h, delta, m.peer, m.d_status.as<int32_t>(), kPeerSpinLimit, (const float*)g->data,
+                                 gpt ? (const float*)b->data : nullptr, c.norm_eps, xn, act_dt, ln.T, D, gpt, ln.st);
+        }
         return gpt ? gptrs_cuda_add_layer_norm(h, delta, GPTRS_F32, nullptr, (const float*)g->data, (const float*)b->data,
                                                c.norm_eps, xn, act_dt, nullptr, nullptr, ln.T, D, ln.st)
                    : gptrs_cuda_add_rms_norm(h, delta, GPTRS_F32, (const float*)g->data, c.norm_eps, xn, act_dt,

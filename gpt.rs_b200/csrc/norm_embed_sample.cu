@@ -13,6 +13,7 @@
 //                       index, docs/backend.md:270; Gumbel-max for temperature > 0 as in
 //                       crates/gpt-rs-backend-triton/src/kernels/sample_temperature_last_axis_f32.triton:45-69)
 #include "common.cuh"
+#include "peer_allreduce.h"
 #include "tensor.h"
 
 #include <cmath>
@@ -55,6 +56,12 @@ struct NormParams {
     int T, D;
     float eps;
     int delta_bf16, out_f32, layer_norm;
+    // tensor-parallel step: delta is this rank's partial tile and the peers' tiles wait in the receive slots of the
+    // one-shot all-reduce (peer_allreduce.cu); the kernel polls the peers' flags (bounded) and adds the tiles in rank order
+    int peer_on;
+    PeerView peer;
+    int* peer_status;
+    uint32_t peer_limit;
 };
 
 // One CTA per row. The row is kept in registers between the statistics and the output pass
@@ -69,8 +76,37 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams
     constexpr int kKeep = 16;
     constexpr int kKeepSpan = kKeep * kNormThreads;  // elements held in registers
     float keep[kKeep];
+    uint32_t peer_slot = 0;
+    if (p.peer_on) {
+        const uint32_t call = *reinterpret_cast<volatile uint32_t*>(p.peer.calls);   // this rank's push has advanced it
+        peer_slot = (call - 1u) & 1u;
+        if (tid < p.peer.tp && tid != p.peer.rank) {
+            const uint32_t* flag = p.peer.flags + peer_slot * p.peer.tp + tid;
+            bool seen = false;
+            for (uint32_t it = 0; it < p.peer_limit; ++it) {
+                uint32_t f;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(f) : "l"(flag) : "memory");
+                if ((int32_t)(f - call) >= 0) { seen = true; break; }
+                __nanosleep(20);
+            }
+            if (!seen && p.peer_status) atomicExch(p.peer_status, 4);
+        }
+        __syncthreads();
+    }
     auto value = [&](int i) {   // the row element with the update added (the same value every time it is asked for)
         float v = hin[i];
+        if (p.peer_on) {
+            // the tiles of all ranks in rank order (every rank ends up with the same bits), read past L1
+            const float* recv = p.peer.recv + (size_t)peer_slot * p.peer.tp * p.peer.cap_floats + (size_t)row * p.D + i;
+            float d = 0.f;
+            for (int r = 0; r < p.peer.tp; ++r) {
+                float t;
+                if (r == p.peer.rank) t = static_cast<const float*>(p.delta)[(size_t)row * p.D + i];
+                else asm volatile("ld.global.cg.f32 %0, [%1];\n" : "=f"(t) : "l"(recv + (size_t)r * p.peer.cap_floats));
+                d = r == 0 ? t : d + t;
+            }
+            return v + d;
+        }
         if (p.delta) {
             float d = p.delta_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.delta)[(size_t)row * p.D + i])
                                    : static_cast<const float*>(p.delta)[(size_t)row * p.D + i];
@@ -419,6 +455,20 @@ static int norm_common(float* d_hidden, const void* d_delta, int delta_dtype, co
 }  // extern "C"
 
 namespace gptrs {
+// The norm after a row-parallel projection of a tensor-parallel step: hidden += sum over ranks of the partial tiles
+// (own tile from `partial`, the peers' tiles from the receive slots, after a bounded wait for their flags), then the norm.
+int add_norm_peer(float* hidden, const float* partial, const PeerView& peer, int* status, uint32_t limit, const float* gamma,
+                  const float* beta, float eps, void* out, int out_dtype, int64_t rows, int64_t dim, bool layer_norm, cudaStream_t st) {
+    GPTRS_REQUIRE(hidden && partial && gamma && out, "null pointer");
+    GPTRS_REQUIRE(rows > 0 && dim > 0 && (size_t)rows * dim <= peer.cap_floats, "the tile must fit the receive slot");
+    NormParams p = {};
+    p.hidden = hidden; p.delta = partial; p.gamma = gamma; p.beta = beta; p.out = out;
+    p.T = (int)rows; p.D = (int)dim; p.eps = eps;
+    p.delta_bf16 = 0; p.out_f32 = out_dtype == GPTRS_F32; p.layer_norm = layer_norm ? 1 : 0;
+    p.peer_on = 1; p.peer = peer; p.peer_status = status; p.peer_limit = limit;
+    return launch_kernel(add_norm_kernel, dim3((unsigned)rows), dim3(kNormThreads), 0, st, 1, p);
+}
+
 int add_norm_out_of_place(const float* hidden_in, const float* delta, float* sum_out, const float* gamma, const float* beta, float eps,
                           float* out, int64_t rows, int64_t dim, bool layer_norm, cudaStream_t st) {
     GPTRS_REQUIRE(hidden_in && delta && gamma && out, "null pointer");

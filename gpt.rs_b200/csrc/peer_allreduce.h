@@ -25,6 +25,9 @@ size_t peer_region_bytes(int tp, size_t cap_floats);
 void peer_view_local(PeerView* v, void* region, int tp, int rank, size_t cap_floats);   // region must be zeroed
 void peer_view_connect(PeerView* v, int p, void* peer_region);
 int peer_push(const PeerView& v, const float* partial, size_t n_floats, cudaStream_t st);
+// norm_embed_sample.cu: residual add of the all-reduced tile + norm in one kernel (the wait and the sum of the all-reduce ride on it)
+int add_norm_peer(float* hidden, const float* partial, const PeerView& peer, int* status, uint32_t limit, const float* gamma,
+                  const float* beta, float eps, void* out, int out_dtype, int64_t rows, int64_t dim, bool layer_norm, cudaStream_t st);
 int peer_wait_sum(const PeerView& v, float* partial, size_t n_floats, int* status, uint32_t limit, cudaStream_t st);
 
 }  // namespace gptrs
