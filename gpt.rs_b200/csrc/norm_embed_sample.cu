@@ -76,33 +76,22 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams
     constexpr int kKeep = 16;
     constexpr int kKeepSpan = kKeep * kNormThreads;  // elements held in registers
     float keep[kKeep];
-    uint32_t peer_slot = 0;
+    uint32_t peer_call = 0;
+    const uint2* peer_recv = nullptr;
+    bool peer_late = false;
     if (p.peer_on) {
-        const uint32_t call = *reinterpret_cast<volatile uint32_t*>(p.peer.calls);   // this rank's push has advanced it
-        peer_slot = (call - 1u) & 1u;
-        if (tid < p.peer.tp && tid != p.peer.rank) {
-            const uint32_t* flag = p.peer.flags + peer_slot * p.peer.tp + tid;
-            bool seen = false;
-            for (uint32_t it = 0; it < p.peer_limit; ++it) {
-                uint32_t f;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(f) : "l"(flag) : "memory");
-                if ((int32_t)(f - call) >= 0) { seen = true; break; }
-                __nanosleep(20);
-            }
-            if (!seen && p.peer_status) atomicExch(p.peer_status, 4);
-        }
-        __syncthreads();
+        peer_call = *reinterpret_cast<volatile uint32_t*>(p.peer.calls) + 1u;   // the same number this rank's push used
+        peer_recv = p.peer.recv + (size_t)((peer_call - 1u) & 1u) * p.peer.tp * p.peer.cap_floats + (size_t)row * p.D;
     }
     auto value = [&](int i) {   // the row element with the update added (the same value every time it is asked for)
         float v = hin[i];
         if (p.peer_on) {
-            // the tiles of all ranks in rank order (every rank ends up with the same bits), read past L1
-            const float* recv = p.peer.recv + (size_t)peer_slot * p.peer.tp * p.peer.cap_floats + (size_t)row * p.D + i;
+            // the tiles of all ranks in rank order (every rank ends up with the same bits); a peer's value is read
+            // until it carries this call's mark
             float d = 0.f;
             for (int r = 0; r < p.peer.tp; ++r) {
-                float t;
-                if (r == p.peer.rank) t = static_cast<const float*>(p.delta)[(size_t)row * p.D + i];
-                else asm volatile("ld.global.cg.f32 %0, [%1];\n" : "=f"(t) : "l"(recv + (size_t)r * p.peer.cap_floats));
+                const float t = r == p.peer.rank ? static_cast<const float*>(p.delta)[(size_t)row * p.D + i]
+                                                 : peer_unit_wait(peer_recv + (size_t)r * p.peer.cap_floats + i, peer_call, p.peer_limit, &peer_late);
                 d = r == 0 ? t : d + t;
             }
             return v + d;
@@ -170,6 +159,10 @@ __global__ void __launch_bounds__(kNormThreads) add_norm_kernel(const NormParams
         if (i < p.D) store(i, keep[j]);
     }
     for (int i = kKeepSpan + tid; i < p.D; i += kNormThreads) store(i, again(i));
+    if (p.peer_on) {
+        if (peer_late && p.peer_status) atomicExch(p.peer_status, 4);
+        peer_call_done(p.peer, peer_call);
+    }
 }
 
 struct EmbedParams {

@@ -430,10 +430,12 @@ int gptrs_cuda_nccl_unique_id(uint8_t* out128);
 int gptrs_cuda_model_init_tensor_parallel(gptrs_model* m, const uint8_t* unique_id128);
 /* Which collective adds up the row-parallel partial sums of decode-sized steps (valid after finalize): 0 = none
  * (tp_size 1), 1 = ncclAllReduce, 2 = the library's one-shot all-reduce over NVLink peer memory — every rank stores its
- * [rows, d_model] partial tile into a receive slot in every peer's memory (CUDA IPC mappings, plain peer stores), raises
- * a flag there, and adds up what it received after a BOUNDED wait for the peers' flags (a wait that runs out records
- * status 4, reported by the next synchronising call). Used for up to 256 rows; larger steps (prefill) stay on NCCL.
- * GPTRS_TP_ALLREDUCE=nccl in the environment keeps the library collective everywhere. No counterpart in gpt.rs. */
+ * [rows, d_model] partial tile into a receive slot in every peer's memory (CUDA IPC mappings, plain peer stores, every
+ * float as an 8-byte {value, call number} unit so that no fence or flag round trip is needed), and the residual-add +
+ * norm kernel that follows reads the peers' units until they carry the current call number (a BOUNDED wait: one that
+ * runs out records status 4, reported by the next synchronising call) and adds the tiles in rank order. Used for up to
+ * 256 rows; larger steps (prefill) stay on NCCL. GPTRS_TP_ALLREDUCE=nccl in the environment keeps the library
+ * collective everywhere. No counterpart in gpt.rs. */
 int gptrs_cuda_model_tp_allreduce_kind(gptrs_model* m);
 /* Test entry of that all-reduce: `tp` ranks emulated on ONE device (regions = tp * gptrs_cuda_peer_region_bytes(tp,
  * cap_floats) zeroed bytes, partials [tp][n] f32, updated in place to the sum over ranks, `calls` times in a row). All
