@@ -536,43 +536,44 @@ def measure_dp512(args, gm, torch, np, dist, world, rank, dev):
 
 def measure_tp(args, gm, torch, np, dist, world, rank, dev, single_rank_model, single_cfg):
     """One batch of 64 requests (2048-token prompts) over a tensor-parallel group of all ranks: ms per decode step and
-    tokens/s, CUDA events, max over ranks. `check`: the single-rank engine of rank 0 prefills eight 48-token prompts and
+    tokens/s, CUDA events, max over ranks. `check`: the single-rank engine of rank 0 prefills 24 48-token prompts and
     decodes eight greedy steps; the tensor-parallel engine does the same, fed the single-rank ids at every step; the
-    72 ids are compared one by one (the weights are random, so a few exact near-ties between the two summation orders
+    216 ids are compared one by one (the weights are random, so a few exact near-ties between the two summation orders
     are possible: the count is reported)."""
     steps_total = args.warmup + args.steps + 32
-    short = [np.random.default_rng(77 + i).integers(0, 131072, size=48) for i in range(8)]
+    NP = 24   # more than 16 rows: the decode steps of the check run the tensor-core matmuls, like the timed batch
+    short = [np.random.default_rng(77 + i).integers(0, 131072, size=48) for i in range(NP)]
 
     GAP = 0.1   # logits of this model have a standard deviation of about 1.1; two engines agree to a few hundredths
 
     def reference_run(m):
         """The single-rank engine: first id from every prompt, then eight eager decode steps with the logits read back.
         Returns the ids per step and, per id, whether the top-2 gap of its logits row makes it a decided choice."""
-        for s_ in range(8):
+        for s_ in range(NP):
             m.reset_sequence(s_)
-        cur = list(m.prefill_many(list(range(8)), short, chunk=args.prefill_chunk))
-        ids, sure = [cur], [[False] * 8]   # the first ids come without logits: compared but reported apart
+        cur = list(m.prefill_many(list(range(NP)), short, chunk=args.prefill_chunk))
+        ids, sure = [cur], [[False] * NP]   # the first ids come without logits: compared but reported apart
         for k in range(8):
-            pos = [48 + k] * 8
-            lg, tok = m.forward_with_decode_cache(cur, list(range(8)), pos, list(range(8)))
+            pos = [48 + k] * NP
+            lg, tok = m.forward_with_decode_cache(cur, list(range(NP)), pos, list(range(NP)))
             top = np.sort(lg, axis=1)
             ids.append([int(t) for t in tok])
             sure.append([bool(g) for g in (top[:, -1] - top[:, -2]) > GAP])
             cur = ids[-1]
-        for s_ in range(8):
+        for s_ in range(NP):
             m.reset_sequence(s_)
         return ids, sure
 
     def forced_run(m, ref_ids):
         """The tensor-parallel engine, fed the reference's ids at every step (one near-tie cannot change what follows)."""
-        for s_ in range(8):
+        for s_ in range(NP):
             m.reset_sequence(s_)
-        first = m.prefill_many(list(range(8)), short, chunk=args.prefill_chunk)
+        first = m.prefill_many(list(range(NP)), short, chunk=args.prefill_chunk)
         g = gm.Generator(m, ref_ids[0], use_graph=True)
         ids = [[int(t) for t in first]]
         for k in range(8):
             ids.append(g.step(tokens_in=ref_ids[k]).tolist())
-        for s_ in range(8):
+        for s_ in range(NP):
             m.reset_sequence(s_)
         return ids
 
@@ -630,8 +631,8 @@ def measure_tp(args, gm, torch, np, dist, world, rank, dev, single_rank_model, s
             "with_nccl_allreduce": {"collective": kind_nccl, "ms_per_step": ms_nccl, "ids_that_differ": differ_nccl,
                                     "decided_ids_that_differ": decided_nccl, "us_per_collective_saved": (ms_nccl - ms) * 1e3 / n_collectives},
             "check": {"same_greedy_ids_as_single_rank": decided == 0, "decided_ids_compared": n_sure, "decided_ids_that_differ": decided,
-                      "ids_compared": 72, "ids_that_differ": differ,
-                      "rule": f"teacher-forced; an id is decided when the single-rank logits' top-2 gap exceeds {GAP}", "prompts": 8, "steps": 8}}
+                      "ids_compared": 9 * NP, "ids_that_differ": differ,
+                      "rule": f"teacher-forced; an id is decided when the single-rank logits' top-2 gap exceeds {GAP}", "prompts": NP, "steps": 8}}
 
 
 def main():

@@ -49,6 +49,7 @@ class MatmulEpilogue(ctypes.Structure):
         ("rope_q_heads", ctypes.c_int),
         ("rope_kv_heads", ctypes.c_int),
         ("d_status", ctypes.c_void_p),
+        ("peer_push", ctypes.c_void_p),
     ]
 
 

@@ -125,6 +125,7 @@ struct Model {
     void* peer_maps[kMaxPeers] = {};
     PeerView peer = {};
     bool peer_on = false;
+    bool fuse_peer_push = true;   // GPTRS_TP_FUSED_PUSH=0: a copy kernel pushes the tile instead of the matmul epilogue
     DevBuf partial, tp_vals, tp_idx, tp_gvals, tp_gidx;  // row-parallel partial sums; (max, argmax) exchange
     int gen_batch = 0;  // slots 0..gen_batch-1 are driven by generator_step
     int64_t launches = 0;
@@ -307,7 +308,7 @@ struct NormFold {
 };
 
 int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool out_f32, const float* residual,
-           bool swiglu, bool gelu, cudaStream_t st, const NormFold* fold = nullptr) {
+           bool swiglu, bool gelu, cudaStream_t st, const NormFold* fold = nullptr, const PeerView* push = nullptr) {
     ++m.launches;
     if (m.f32()) {
         return gptrs_cuda_norm_matmul_f32(static_cast<const float*>(x), fold ? fold->f32_norm : 0, fold ? fold->f32_gamma : nullptr,
@@ -321,6 +322,7 @@ int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool
     ep.d_residual = residual;
     ep.swiglu = swiglu ? 1 : 0;
     ep.d_status = m.d_status.as<int32_t>();  // a matmul wait that gives up reports through the model's word
+    ep.peer_push = push;
     if (fold && fold->produce) { ep.d_norm_gamma = fold->gamma; ep.d_norm_x = fold->x_next; ep.d_sumsq_out = fold->sumsq; }
     if (fold && fold->consume) { ep.d_sumsq_in = fold->sumsq; ep.sumsq_tiles = fold->dim / 128; ep.norm_dim = fold->dim; ep.norm_eps = fold->eps; }
     if (fold && fold->rope_positions) {
@@ -474,14 +476,17 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
             }
             return linear(m, w, x, h, ln.T, true, h, false, false, ln.st);
         }
-        int r = linear(m, w, x, m.partial.p, ln.T, true, nullptr, false, false, ln.st);
+        // One-shot all-reduce over peer memory: the projection's epilogue stores its tile into the peers' receive slots
+        // as it is produced (f32 weights: a copy kernel does), the norm that follows is the consumer.
+        const bool peer = m.peer_on && (size_t)ln.T * D <= m.peer.cap_floats;
+        const bool fused_push = peer && !m.f32() && m.fuse_peer_push;
+        int r = linear(m, w, x, m.partial.p, ln.T, true, nullptr, false, false, ln.st, nullptr, fused_push ? &m.peer : nullptr);
         if (r) return r;
         pending = m.partial.as<float>();
-        if (m.peer_on && (size_t)ln.T * D <= m.peer.cap_floats) {
-            // every rank stores its partial tile into the peers' receive slots; the norm that follows waits for the
-            // peers' flags and adds up the tiles
-            ++m.launches;
+        if (peer) {
             pending_peer = true;
+            if (fused_push) return GPTRS_OK;
+            ++m.launches;
             return peer_push(m.peer, m.partial.as<float>(), (size_t)ln.T * D, ln.st);
         }
         ++m.launches;
@@ -730,6 +735,7 @@ int setup_peer_allreduce(Model& m, int max_rows_peer) {
     GPTRS_CUDA_OK(cudaMemcpyAsync(&total, flag.p, 4, cudaMemcpyDeviceToHost, m.stream));
     GPTRS_CUDA_OK(cudaStreamSynchronize(m.stream));
     if (total != 0) return GPTRS_OK;   // some rank could not map a peer: everyone keeps the library collective
+    if (const char* e = getenv("GPTRS_TP_FUSED_PUSH")) m.fuse_peer_push = atoi(e) != 0;
     peer_view_local(&m.peer, m.peer_region, m.tp, m.tp_rank, cap);
     for (int p = 0; p < m.tp; ++p)
         if (p != m.tp_rank) peer_view_connect(&m.peer, p, m.peer_maps[p]);

@@ -3,6 +3,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "peer_allreduce.h"
 
 namespace gptrs {
 
@@ -70,6 +71,10 @@ struct MatmulParams {
     uint32_t spin_limit;
     int debug_starve;
     int stage_rotation;  // streaming kernel: column tiles start their K walk at different stages
+    // tensor-parallel row-parallel projection: the f32 output tile also goes, as {value, call number} units, into the
+    // receive slots of the one-shot all-reduce in every peer's memory (peer_allreduce.cu)
+    int peer_on;
+    PeerView peer;
 };
 
 // ---- split-K reduction across the CTAs of a cluster: push, one barrier, local sum -------------------
@@ -218,6 +223,17 @@ __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const
             if (live) {
                 if (p.out_f32) {
                     *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + (size_t)m * p.N + n) = v;
+                    if (p.peer_on) {
+                        const uint32_t call = *reinterpret_cast<volatile uint32_t*>(p.peer.calls) + 1u;   // advanced by the consumer of the previous call
+                        const size_t unit = ((size_t)((call - 1u) & 1u) * p.peer.tp + p.peer.rank) * p.peer.cap_floats + (size_t)m * p.N + n;
+                        const uint4 lo = make_uint4(__float_as_uint(v.x), call, __float_as_uint(v.y), call);
+                        const uint4 hi = make_uint4(__float_as_uint(v.z), call, __float_as_uint(v.w), call);
+                        for (int q = 0; q < p.peer.tp; ++q) {
+                            if (q == p.peer.rank) continue;
+                            peer_store_16(p.peer.peer_recv[q] + unit, lo);
+                            peer_store_16(p.peer.peer_recv[q] + unit + 2, hi);
+                        }
+                    }
                 } else {
                     uint2 o = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
                     *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)m * p.N + n) = o;

@@ -598,6 +598,14 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
             p.rope_pool = static_cast<unsigned char*>(ep->d_rope_kv_pool);
             p.rope_hq = ep->rope_q_heads; p.rope_hkv = ep->rope_kv_heads;
         }
+        if (ep->peer_push) {
+            const PeerView* pv = static_cast<const PeerView*>(ep->peer_push);
+            GPTRS_REQUIRE(p.out_f32 && !p.swiglu && !p.sumsq_out && !p.rope_pos && !ep->d_sumsq_in && n % 4 == 0 &&
+                              (size_t)m * (size_t)n <= pv->cap_floats && pv->tp >= 2 && pv->tp <= kMaxPeers,
+                          "peer push: f32 output, no other epilogue, the tile within the receive slot");
+            p.peer_on = 1;
+            p.peer = *pv;
+        }
         if (ep->d_sumsq_in) {
             GPTRS_REQUIRE(m > 16 && ep->sumsq_tiles > 0 && ep->norm_dim > 0, "folded norm consumer: more than 16 rows, tiles and norm_dim set");
             p.sumsq_in = ep->d_sumsq_in;

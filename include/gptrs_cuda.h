@@ -139,6 +139,11 @@ typedef struct {
     /* Optional device word that receives code 3 when a bounded wait inside a tensor-core matmul kernel gives up
      * (rows > 16). Null = the library's own per-device word, read with gptrs_cuda_matmul_status. */
     int32_t* d_status;
+    /* Tensor-parallel engine only (null otherwise): the row-parallel projection also stores its f32 output tile, as it is
+     * produced, into the receive slots of the one-shot all-reduce in every peer's memory (see
+     * gptrs_cuda_model_tp_allreduce_kind): the GEMM and the push of the collective are one kernel. Points to the engine's
+     * description of the peers (opaque to callers); needs out_dtype f32 and no other epilogue. */
+    const void* peer_push;
 } gptrs_matmul_epilogue;
 
 /* sizeof(gptrs_matmul_epilogue) as the library was built: lets a foreign-language binding check its own
