@@ -842,7 +842,7 @@ def _main(out):
         "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if tp else "weak",
         "vs_baseline": None, "dtype": f"bf16 activations x {'int8' if w8 else 'int4'} weights, f32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD.replace("W4A16-g128", "W8A16 per-channel") if w8 else WORKLOAD, "parallelism": (f"tp{world} (one batch of 64; NCCL all-reduce of [64,3072] f32 after o_proj and down_proj)" if tp
+        "config": {"workload": WORKLOAD.replace("W4A16-g128", "W8A16 per-channel") if w8 else WORKLOAD, "parallelism": (f"tp{world} (one batch of 64; all-reduce of [64,3072] f32 after o_proj and down_proj: {model.tp_allreduce_kind()})" if tp
                                    else f"dp{world} (request-partitioned, no collective)"),
                    "context_tokens_during_timing": [PROMPT_LEN + args.warmup, PROMPT_LEN + args.warmup + args.steps],
                    "l2": "inputs larger than L2 (1.8 GB weights + >14 GB KV streamed per step)",

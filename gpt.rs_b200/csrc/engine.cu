@@ -23,6 +23,7 @@
 
 #include "nccl_dl.h"
 #include "peer_allreduce.h"
+#include "gpt_decode_mega.h"
 #include "tensor.h"
 
 namespace gptrs {
@@ -127,6 +128,10 @@ struct Model {
     bool peer_on = false;
     bool fuse_peer_push = true;   // GPTRS_TP_FUSED_PUSH=0: a copy kernel pushes the tile instead of the matmul epilogue
     DevBuf partial, tp_vals, tp_idx, tp_gvals, tp_gidx;  // row-parallel partial sums; (max, argmax) exchange
+    // f32 GPT kind, one sequence: the whole decode step as one cooperative kernel (gpt_decode_mega.cu)
+    bool mega_on = false;
+    DevBuf mega_wt, mega_scratch;   // transposed weights [out][in]; vectors + barrier word
+    MegaParams mega = {};
     int gen_batch = 0;  // slots 0..gen_batch-1 are driven by generator_step
     int64_t launches = 0;
     uint32_t sample_seed = 0;
@@ -416,6 +421,16 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
     cudaStream_t st = m.stream;
     float* hidden = m.hidden.as<float>();
     const int act_dt = m.f32() ? GPTRS_F32 : GPTRS_BF16;
+    if (m.mega_on && T == 1 && n_rows == 1 && rows_identity && !prefill_groups) {
+        // one sequence, one token: the whole step is one cooperative kernel (+ the memset of its barrier word)
+        MegaParams P = m.mega;
+        P.greedy = temperature <= 0.f ? 1 : 0;
+        m.launches += 1;
+        int r = mega_launch(P, st);
+        if (r || P.greedy) return r;
+        ++m.launches;
+        return gptrs_cuda_sample_rows_top_k(m.logits.as<float>(), 1, c.vocab, temperature, m.top_k, m.sample_seed, m.d_sampled.as<int32_t>(), st);
+    }
     int rc = gptrs_cuda_embedding_lookup(m.tok_emb->data, GPTRS_F32, c.vocab, D, m.d_tokens.as<int32_t>(), T,
                                          m.pos_emb ? static_cast<const float*>(m.pos_emb->data) : nullptr,
                                          m.pos_emb ? c.context_length : 0, m.d_pos.as<int32_t>(), hidden,
@@ -688,6 +703,68 @@ int sync_page_table(Model& m) {
     if (m.f32() || !m.table_dirty) return GPTRS_OK;
     GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_page_table.p, m.h_page_table, m.d_page_table.n, cudaMemcpyHostToDevice, m.stream));
     m.table_dirty = false;
+    return GPTRS_OK;
+}
+
+// Transposed copies of the projection weights and the scratch vectors of the single-kernel decode step (f32 GPT kind,
+// one sequence). GPTRS_GPT_MEGA=0 keeps the kernel-per-projection path.
+int setup_mega(Model& m) {
+    const auto& c = m.cfg;
+    if (const char* e = getenv("GPTRS_GPT_MEGA")) if (atoi(e) == 0) return GPTRS_OK;
+    if (!m.f32() || c.kind != kKindGpt || m.tp != 1 || c.n_q_heads != c.n_kv_heads || !m.pos_emb) return GPTRS_OK;
+    if (!mega_supported(c.d_model, c.n_q_heads, c.head_dim, c.d_mlp, c.context_length, c.n_layers)) return GPTRS_OK;
+    const size_t D = c.d_model, MLP = c.d_mlp, V = c.vocab;
+    const size_t per_layer = 3 * D * D + D * D + MLP * D + D * MLP;
+    int rc = m.mega_wt.alloc((per_layer * c.n_layers + V * D) * 4);
+    if (rc) return rc;
+    MegaLayer* host = m.mega.layers;
+    float* w = m.mega_wt.as<float>();
+    auto tr = [&](const Weight& src, const float** dst) -> int {
+        *dst = w;
+        int r = mega_transpose(static_cast<const float*>(src.f32->data), w, src.in, src.out, m.stream);
+        w += (size_t)src.in * src.out;
+        return r;
+    };
+    auto fp = [](Tensor* t) { return t ? static_cast<const float*>(t->data) : nullptr; };
+    for (int l = 0; l < c.n_layers; ++l) {
+        Layer& L = m.layers[l];
+        MegaLayer& M = host[l];
+        if (!L.qkv.bias || !L.attn_out.bias || !L.mlp_in.bias || !L.mlp_out.bias) return GPTRS_OK;   // the kernel adds all four
+        if ((rc = tr(L.qkv, &M.w_qkv_t)) || (rc = tr(L.attn_out, &M.w_out_t)) || (rc = tr(L.mlp_in, &M.w_mlp_in_t)) ||
+            (rc = tr(L.mlp_out, &M.w_mlp_out_t))) return rc;
+        M.ln1_g = fp(L.ln1_g); M.ln1_b = fp(L.ln1_b); M.ln2_g = fp(L.ln2_g); M.ln2_b = fp(L.ln2_b);
+        M.b_qkv = fp(L.qkv.bias); M.b_out = fp(L.attn_out.bias); M.b_mlp_in = fp(L.mlp_in.bias); M.b_mlp_out = fp(L.mlp_out.bias);
+        M.k_cache = m.k_cache.as<float>() + (size_t)l * m.cache_layer_elems;
+        M.v_cache = m.v_cache.as<float>() + (size_t)l * m.cache_layer_elems;
+    }
+    const float* lm_t = nullptr;
+    if ((rc = tr(m.lm_head, &lm_t))) return rc;
+    const size_t n_sm = (size_t)sm_count();
+    auto pad = [](size_t n) { return (n + 63) & ~(size_t)63; };   // every vector starts on a 256-byte boundary
+    const size_t n_part = pad(n_sm * (c.head_dim + 2));
+    const size_t floats = pad(3 * D) + n_part + pad(D) + pad(MLP) + pad(4 * D) + 2 * pad(n_sm) + 64 + 512;
+    if ((rc = m.mega_scratch.alloc(floats * 4, true))) return rc;
+    float* s = m.mega_scratch.as<float>();
+    MegaParams& P = m.mega;
+    P.n_layers = c.n_layers;
+    P.tok_emb = fp(m.tok_emb); P.pos_emb = fp(m.pos_emb); P.lnf_g = fp(m.final_g); P.lnf_b = fp(m.final_b); P.lm_head_t = lm_t;
+    P.token = m.d_tokens.as<int>(); P.pos = m.d_pos.as<int>(); P.slot = m.d_slot.as<int>();
+    P.qkv = s; s += pad(3 * D);
+    P.att_part = s; s += n_part;
+    P.pc = s; s += pad(D);
+    P.mh = s; s += pad(MLP);
+    P.pe = s; s += pad(4 * D);
+    P.cand_val = s; s += pad(n_sm);
+    P.cand_idx = reinterpret_cast<int*>(s); s += pad(n_sm);
+    P.barrier = reinterpret_cast<unsigned*>(s); s += 64;
+    P.timing = nullptr;
+    if (const char* e = getenv("GPTRS_MEGA_TIMING")) if (atoi(e)) P.timing = reinterpret_cast<unsigned long long*>(s);
+    P.logits = m.logits.as<float>();
+    P.sampled = m.d_sampled.as<int>();
+    P.status = m.d_status.as<int32_t>();
+    P.D = (int)D; P.H = c.n_q_heads; P.hd = c.head_dim; P.MLP = (int)MLP; P.vocab = c.vocab; P.ctx_cap = c.context_length;
+    P.n_pos = c.context_length; P.eps = c.norm_eps; P.greedy = 1;
+    m.mega_on = true;
     return GPTRS_OK;
 }
 
@@ -1015,6 +1092,7 @@ int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
         worst = std::min<size_t>(worst, (size_t)1 << 30);
         if ((rc = m.attn_scratch.alloc(worst))) return rc;
     }
+    if ((rc = setup_mega(m))) return rc;
     GPTRS_CUDA_OK(cudaStreamSynchronize(m.stream));
     m.finalized = true;
     return GPTRS_OK;
@@ -1247,7 +1325,7 @@ int gptrs_cuda_generator_step(gptrs_model* h, const int32_t* h_tokens_in, int32_
         ++m.launches;
         return launch_kernel(advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s, 1, ap);
     };
-    if (use_graph) {
+    if (use_graph && !(m.mega_on && B == 1)) {   // the single-kernel step needs no graph
         GraphKey key{B, chunk, splits};
         auto it = m.graphs.find(key);
         if (it == m.graphs.end()) {
@@ -1288,6 +1366,15 @@ int gptrs_cuda_generator_step(gptrs_model* h, const int32_t* h_tokens_in, int32_
 int gptrs_cuda_generator_sync(gptrs_model* h) {
     GPTRS_REQUIRE(h, "null pointer");
     return check_status(*reinterpret_cast<Model*>(h));
+}
+
+int gptrs_cuda_debug_mega_timing(gptrs_model* h, uint64_t* out, int n) {
+    GPTRS_REQUIRE(h && out && n > 0 && n <= 256, "bad arguments");
+    Model& m = *reinterpret_cast<Model*>(h);
+    GPTRS_REQUIRE(m.mega_on && m.mega.timing, "the single-kernel step is off or was built without GPTRS_MEGA_TIMING=1");
+    GPTRS_CUDA_OK(cudaStreamSynchronize(m.stream));
+    GPTRS_CUDA_OK(cudaMemcpy(out, m.mega.timing, (size_t)n * 8, cudaMemcpyDeviceToHost));
+    return GPTRS_OK;
 }
 
 void* gptrs_cuda_model_stream(gptrs_model* h) { return h ? reinterpret_cast<Model*>(h)->stream : nullptr; }

@@ -475,6 +475,9 @@ int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* m, const int32_t* h_
  * (crates/gpt-rs/src/inference/generate.rs:127-134: the window start moves up, the caches are dropped and the window
  * is processed again from position 0): the oldest token leaves, the remaining context_length - 1 tokens of the
  * device-side history are prefilled at positions 0.., then the step runs at the last position. */
+/* Debug: the timestamps (ns, globaltimer) that CTA 0 of the single-kernel GPT decode step took at its start and around
+ * each of its grid barriers during the last step; only with GPTRS_MEGA_TIMING=1 in the environment at finalize. */
+int gptrs_cuda_debug_mega_timing(gptrs_model* m, uint64_t* out, int n);
 int gptrs_cuda_generator_begin(gptrs_model* m, int batch, const int32_t* h_first_tokens);
 int gptrs_cuda_generator_step(gptrs_model* m, const int32_t* h_tokens_in, int32_t* h_tokens_out, int use_graph);
 /* Waits for the model's stream and reports a device-side error recorded by any step. */
