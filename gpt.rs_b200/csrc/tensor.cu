@@ -84,16 +84,33 @@ void pool_free(void* ptr, size_t bytes, int device) {
     if (!ptr) return;
     const size_t need = pool_round(bytes);
     DevicePool& pool = g_pools[device & (kMaxDevices - 1)];
+    // The block that was just in use is the one most likely to be asked for again: it stays, and when the cache is over
+    // its cap the LARGEST cached blocks go back to the driver instead (a closed model leaves gigabytes of weight buffers
+    // behind; without this every later free of a small result was a synchronising cudaFree).
+    std::vector<void*> victims;
+    bool keep = need <= pool_cap();
     {
         std::lock_guard<std::mutex> lk(pool.mu);
-        if (pool.cached_bytes + need <= pool_cap()) {
-            pool.free_blocks[need].push_back(ptr);
-            pool.cached_bytes += need;
-            return;
+        if (keep) {
+            for (auto it = pool.free_blocks.rbegin(); it != pool.free_blocks.rend() && pool.cached_bytes + need > pool_cap(); ++it) {
+                while (!it->second.empty() && pool.cached_bytes + need > pool_cap()) {
+                    victims.push_back(it->second.back());
+                    it->second.pop_back();
+                    pool.cached_bytes -= it->first;
+                }
+            }
+            keep = pool.cached_bytes + need <= pool_cap();
+            if (keep) {
+                pool.free_blocks[need].push_back(ptr);
+                pool.cached_bytes += need;
+            }
         }
     }
-    g_driver_frees.fetch_add(1, std::memory_order_relaxed);
-    cudaFree(ptr);
+    if (!keep) victims.push_back(ptr);
+    for (void* v : victims) {
+        g_driver_frees.fetch_add(1, std::memory_order_relaxed);
+        cudaFree(v);
+    }
 }
 
 void pool_stats(int64_t* driver_allocs, int64_t* pool_hits, int64_t* driver_frees, int64_t* cached_bytes) {
