@@ -887,7 +887,10 @@ def _main(out):
         # sub-records: measured after the headline figures, in the same process group
         subs = set(args.sub.split(","))
         if world > 1 and "tp" in subs:
-            line["tp"] = measure_tp(args, gm, torch, np, dist, world, rank, dev, model, cfg)
+            try:
+                line["tp"] = measure_tp(args, gm, torch, np, dist, world, rank, dev, model, cfg)
+            except Exception as e:  # noqa: BLE001  (every rank runs the same shapes, so a refusal is raised on all of them alike)
+                line["tp"] = {"parallelism": f"tp{world}", "error": f"{type(e).__name__}: {e}"[:400]}
         model.close()
         del model
         torch.cuda.empty_cache()
