@@ -773,7 +773,11 @@ int setup_mega(Model& m) {
 // exists; if any rank cannot map any peer, every rank stays on ncclAllReduce (the ranks agree through one more
 // all-reduce). GPTRS_TP_ALLREDUCE=nccl keeps the library collective.
 int setup_peer_allreduce(Model& m, int max_rows_peer) {
-    if (const char* e = getenv("GPTRS_TP_ALLREDUCE")) if (!strcmp(e, "nccl")) return GPTRS_OK;
+    // Default: the peer-memory all-reduce for two ranks, the library collective beyond (measured at batch 64: 3.63 against
+    // 3.97 ms per step at two ranks, 3.89 against 3.56 ms at four: a one-shot exchange sends the whole tile to every peer).
+    // GPTRS_TP_ALLREDUCE=peer / nccl forces either.
+    const char* choice = getenv("GPTRS_TP_ALLREDUCE");
+    if (choice ? !strcmp(choice, "nccl") : m.tp > 2) return GPTRS_OK;
     std::string err;
     const NcclApi* api = nccl_api(&err);
     if (!api) return fail(GPTRS_EXECUTION, err);

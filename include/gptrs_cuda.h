@@ -439,8 +439,8 @@ int gptrs_cuda_model_init_tensor_parallel(gptrs_model* m, const uint8_t* unique_
  * float as an 8-byte {value, call number} unit so that no fence or flag round trip is needed), and the residual-add +
  * norm kernel that follows reads the peers' units until they carry the current call number (a BOUNDED wait: one that
  * runs out records status 4, reported by the next synchronising call) and adds the tiles in rank order. Used for up to
- * 256 rows; larger steps (prefill) stay on NCCL. GPTRS_TP_ALLREDUCE=nccl in the environment keeps the library
- * collective everywhere. No counterpart in gpt.rs. */
+ * 256 rows; larger steps (prefill) stay on NCCL. It is the default for two ranks (where it was measured faster); larger
+ * groups default to NCCL, GPTRS_TP_ALLREDUCE=peer or =nccl in the environment forces either. No counterpart in gpt.rs. */
 int gptrs_cuda_model_tp_allreduce_kind(gptrs_model* m);
 /* Test entry of that all-reduce: `tp` ranks emulated on ONE device (regions = tp * gptrs_cuda_peer_region_bytes(tp,
  * cap_floats) zeroed bytes, partials [tp][n] f32, updated in place to the sum over ranks, `calls` times in a row). All

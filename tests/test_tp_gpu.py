@@ -36,10 +36,7 @@ def _worker_body(rank, world, port, mode, collective, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    if collective == "nccl":
-        os.environ["GPTRS_TP_ALLREDUCE"] = "nccl"
-    else:
-        os.environ.pop("GPTRS_TP_ALLREDUCE", None)
+    os.environ["GPTRS_TP_ALLREDUCE"] = collective
     import torch.distributed as dist
     import __graft_entry__ as entry
     entry.load_package()
