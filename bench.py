@@ -289,6 +289,7 @@ def measure_gpt2_run_program(args, torch, np):
     clock around the loop (every step ends with the synchronous read of the sampled id)."""
     from types import SimpleNamespace
     from gptrs_b200 import ptir
+    from gptrs_b200 import lib as _lib
     from gptrs_b200.backend import CudaBackend
     torch.cuda.set_device(0)
     cfg = SimpleNamespace(kind="gpt", n_layers=12, d_model=768, n_q=12, n_kv=12, hd=64, d_mlp=3072, vocab=50257, ctx=1024, eps=1e-5, rot=0)
@@ -328,6 +329,7 @@ def measure_gpt2_run_program(args, torch, np):
             else:
                 hs.append(weights[n])
         res = prog.run(hs)
+        state["replays"] = state.get("replays", 0) + int(_lib().gptrs_cuda_last_run_replayed_graph())
         for l in range(cfg.n_layers):
             caches[l] = (res[1 + 2 * l], res[2 + 2 * l])
         state["tok"] = be.sample_decode_token(res[0], 0.0)
@@ -342,6 +344,7 @@ def measure_gpt2_run_program(args, torch, np):
         step()
     torch.cuda.synchronize()
     allocs0 = be.alloc_stats()["driver_allocs"]
+    state["replays"] = 0
     t0 = time.perf_counter()
     for _ in range(args.steps):
         step()
@@ -360,7 +363,7 @@ def measure_gpt2_run_program(args, torch, np):
                     "note": "the timed loop is the end-to-end loop: host arguments in, sampled id out, every step"},
             "gpu_launches": int(st["last_launches"]) * args.steps, "launches_per_token": int(st["last_launches"]),
             "fused_rewrites": int(st["last_fused"]), "driver_allocs_in_timed_region": int(al["driver_allocs"] - allocs0),
-            "pool_hits": int(al["pool_hits"]),
+            "pool_hits": int(al["pool_hits"]), "graph_replays_in_timed_region": int(state["replays"]),
             "roofline": {"kernel": "all weight matrices of a step", "bound": "hbm", "achieved": weight_bytes / dt * args.steps / 1e9,
                          "peak": peak, "unit": "GB/s", "frac": weight_bytes / dt * args.steps / 1e9 / peak, "traffic": None,
                          "peak_kind": peak_kind}}
@@ -904,7 +907,7 @@ def _main(out):
             line["gpt2_fp32"] = strip_sub(measure_gpt2(g2, gm, torch, np, cpu_baseline=not args.no_cpu_baseline, device_index=local))
             rp = measure_gpt2_run_program(g2, torch, np)
             line["gpt2_fp32"]["run_program_path"] = {k: rp[k] for k in ("value", "ms_per_step", "launches_per_token", "fused_rewrites",
-                                                                        "driver_allocs_in_timed_region")}
+                                                                        "driver_allocs_in_timed_region", "graph_replays_in_timed_region")}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import cbaseline as cb
         # the CPU arm forks one process per host core: run it as its own interpreter, apart from this CUDA process

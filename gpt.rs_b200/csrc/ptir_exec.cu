@@ -313,7 +313,32 @@ struct Plan {
     Tensor* arena = nullptr;                     // retained; one per plan (and so per device)
     int device = 0;
     std::mutex run_mu;                           // the arena serves one execution at a time
-    ~Plan() { tensor_release(arena); }
+    // CUDA graphs of the whole execution. A graph bakes in every pointer, so it is valid for one set of input buffers and
+    // one set of result buffers: a replay first asks the pool for the results in the order the recorded run took them and
+    // launches the graph only if the pool hands back the very same blocks (in a decode loop the caches ping-pong between
+    // two sets of blocks, so two graphs serve every step); otherwise the call runs kernel by kernel as before.
+    struct RunGraph {
+        std::vector<const void*> in_ptrs;        // data pointers of the inputs
+        std::vector<TSpec> allocs;               // the pool allocations of the run, in order
+        std::vector<void*> alloc_ptrs;           // ... and the blocks they received
+        std::vector<int> result_of;              // result i = allocation result_of[i]
+        cudaGraphExec_t exec = nullptr;
+        int64_t launches = 0;
+    };
+    std::vector<RunGraph> graphs;
+    // The legacy default stream cannot be captured: graphs are recorded and launched on a stream of the plan's own,
+    // ordered after and before the caller's stream with two events.
+    cudaStream_t side_stream = nullptr;
+    cudaEvent_t ev_in = nullptr, ev_out = nullptr;
+    int runs = 0, graph_failures = 0;
+    bool graph_ok = true;                        // false once an execution turned out not to fit the scheme
+    ~Plan() {
+        for (auto& g : graphs) if (g.exec) cudaGraphExecDestroy(g.exec);
+        if (ev_in) cudaEventDestroy(ev_in);
+        if (ev_out) cudaEventDestroy(ev_out);
+        if (side_stream) cudaStreamDestroy(side_stream);
+        tensor_release(arena);
+    }
 };
 
 const Inst* def_of(const Plan& pl, const Operand& o) {
@@ -736,8 +761,11 @@ void plan_buffers(Plan& pl) {
     int64_t top = 0;
     for (int i = 0; i < n; ++i) {
         const Inst& in = body[i];
-        if (in.dead || escapes[i] || may_alias_operand(in) || in.side_id) continue;
-        const int64_t bytes = (((int64_t)in.out.numel() * (int64_t)dtype_size(in.out.dtype)) + 255) & ~(int64_t)255;
+        if (in.dead || escapes[i] || may_alias_operand(in)) continue;
+        int64_t bytes = (((int64_t)in.out.numel() * (int64_t)dtype_size(in.out.dtype)) + 255) & ~(int64_t)255;
+        // a second result (the sum of a fused residual-add + norm) lives right behind the first, for the same lifetime
+        // (value ids of both map to this instruction, so `last` already covers the readers of either)
+        if (in.side_id) bytes += (((int64_t)in.side_out.numel() * (int64_t)dtype_size(in.side_out.dtype)) + 255) & ~(int64_t)255;
         if (bytes == 0) continue;
         const int free_at = last[i] < 0 ? i : last[i];
         int best = -1;
@@ -1168,7 +1196,15 @@ int exec_inst(Exec& ex, const Inst& in, std::vector<Tensor*>& ops, Tensor** resu
             const bool ln = in.op == Op::FusedAddLayerNorm;
             const int64_t d = in.out.dims.back(), rows = n_out / d;
             Tensor* sum = nullptr;
-            if (in.side_id && (rc = tensor_alloc(in.side_out.dtype, (int)in.side_out.dims.size(), in.side_out.dims.data(), false, &sum))) break;
+            if (in.side_id && ex.arena && ex.arena_off >= 0) {   // planned: right behind the first result
+                const int64_t main_bytes = (((int64_t)in.out.numel() * (int64_t)dtype_size(in.out.dtype)) + 255) & ~(int64_t)255;
+                sum = new Tensor();
+                sum->dtype = in.side_out.dtype; sum->dims = in.side_out.dims;
+                sum->bytes = (size_t)in.side_out.numel() * dtype_size(in.side_out.dtype);
+                sum->data = static_cast<unsigned char*>(ex.arena->data) + ex.arena_off + main_bytes;
+                sum->owns = false; sum->base = ex.arena; sum->device = ex.arena->device;
+                tensor_retain(ex.arena);
+            } else if (in.side_id && (rc = tensor_alloc(in.side_out.dtype, (int)in.side_out.dims.size(), in.side_out.dims.data(), false, &sum))) break;
             ++ex.launches;
             rc = add_norm_out_of_place(static_cast<const float*>(ops[0]->data), static_cast<const float*>(ops[1]->data),
                                        sum ? static_cast<float*>(sum->data) : nullptr, static_cast<const float*>(ops[2]->data),
@@ -1229,26 +1265,14 @@ int plan_for(const char* program_json, size_t len, std::shared_ptr<Plan>* out) {
     return GPTRS_OK;
 }
 
-int execute_plan(const std::shared_ptr<Plan>& plan, gptrs_tensor* const* inputs, size_t n_inputs, gptrs_tensor** outputs,
-                 size_t outputs_cap, size_t* n_outputs, void* stream) {
-    const Function& fn = plan->fn;
-    if (plan->device != current_device()) return fail(GPTRS_SPEC_VIOLATION, "the program was prepared on another device");
-    GPTRS_REQUIRE(n_inputs == fn.param_ids.size(), "entry input count does not match the function parameters");
-    GPTRS_REQUIRE(n_outputs && outputs_cap >= fn.result_ids.size() && (outputs || fn.result_ids.empty()), "output array too small");
-    // one execution at a time per plan: the temporaries of the function live at fixed offsets of the plan's arena
-    std::lock_guard<std::mutex> run_lock(plan->run_mu);
-    if (plan->arena_bytes > 0 && !plan->arena) {
-        int64_t ad[1] = {plan->arena_bytes};
-        if (int rc = tensor_alloc(GPTRS_UI8, 1, ad, false, &plan->arena)) return rc;
-    }
+// The instructions of the plan, launched on `st` (directly or into a stream capture). Fills outputs (retained).
+int run_instructions(Plan& pl, gptrs_tensor* const* inputs, size_t n_inputs, gptrs_tensor** outputs, cudaStream_t st, int64_t* launches) {
+    const Function& fn = pl.fn;
     Exec ex;
-    ex.st = as_stream(stream);
-    ex.arena = plan->arena;
+    ex.st = st;
+    ex.arena = pl.arena;
     for (size_t i = 0; i < n_inputs; ++i) {
         Tensor* t = reinterpret_cast<Tensor*>(inputs[i]);
-        GPTRS_REQUIRE(t, "null input handle");
-        if (t->dtype != fn.params[i].dtype || t->dims != fn.params[i].dims)
-            return fail(GPTRS_SPEC_VIOLATION, "input " + std::to_string(i) + " does not match the declared parameter type");
         tensor_retain(t);
         ex.env[fn.param_ids[i]] = t;
     }
@@ -1259,7 +1283,7 @@ int execute_plan(const std::shared_ptr<Plan>& plan, gptrs_tensor* const* inputs,
         int rc = GPTRS_OK;
         for (size_t i = 0; i < ops.size() && !rc; ++i) rc = ex.value(in.operands[i], &ops[i]);
         Tensor* res = nullptr;
-        ex.arena_off = ii < plan->arena_offset.size() ? plan->arena_offset[ii] : -1;
+        ex.arena_off = ii < pl.arena_offset.size() ? pl.arena_offset[ii] : -1;
         ex.side = nullptr;
         if (!rc) rc = exec_inst(ex, in, ops, &res);
         for (Tensor* t : ops) tensor_release(t);
@@ -1277,6 +1301,160 @@ int execute_plan(const std::shared_ptr<Plan>& plan, gptrs_tensor* const* inputs,
         tensor_retain(it->second);
         outputs[i] = reinterpret_cast<gptrs_tensor*>(it->second);
     }
+    *launches = ex.launches;
+    return GPTRS_OK;
+}
+
+std::atomic<int> g_plan_graphs{1};   // gptrs_cuda_set_plan_graphs
+thread_local int64_t g_last_graph_replays = 0;
+
+// Replay: take the results from the pool in the recorded order; launch the graph whose blocks they are.
+bool try_replay(Plan& pl, gptrs_tensor* const* inputs, size_t n_inputs, gptrs_tensor** outputs, cudaStream_t st, int64_t* launches) {
+    for (auto& g : pl.graphs) {
+        bool same = g.in_ptrs.size() == n_inputs;
+        for (size_t i = 0; i < n_inputs && same; ++i) same = reinterpret_cast<Tensor*>(inputs[i])->data == g.in_ptrs[i];
+        if (!same) continue;
+        std::vector<Tensor*> got;
+        bool ok = true;
+        for (size_t k = 0; k < g.allocs.size() && ok; ++k) {
+            Tensor* t = nullptr;
+            if (tensor_alloc(g.allocs[k].dtype, (int)g.allocs[k].dims.size(), g.allocs[k].dims.data(), false, &t) != GPTRS_OK) { ok = false; break; }
+            got.push_back(t);
+            ok = t->data == g.alloc_ptrs[k];
+        }
+        if (ok && cudaGraphLaunch(g.exec, st) == cudaSuccess) {
+            for (size_t i = 0; i < g.result_of.size(); ++i) outputs[i] = reinterpret_cast<gptrs_tensor*>(got[g.result_of[i]]);
+            *launches = g.launches;
+            return true;
+        }
+        // the pool handed out other blocks: give them back in reverse order, so that the pool's stacks are as before
+        for (size_t k = got.size(); k-- > 0;) tensor_release(got[k]);
+        cudaGetLastError();
+    }
+    return false;
+}
+
+// One execution recorded into a graph. Returns false (with nothing launched and nothing kept) when the execution does
+// not fit the scheme: then the caller runs it kernel by kernel.
+bool capture_run(Plan& pl, gptrs_tensor* const* inputs, size_t n_inputs, gptrs_tensor** outputs, cudaStream_t st, int64_t* launches, int* rc_out) {
+    const size_t n_res = pl.fn.result_ids.size();
+    std::vector<Tensor*> record;
+    if (cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed) != cudaSuccess) { cudaGetLastError(); return false; }
+    g_alloc_record = &record;
+    int rc = run_instructions(pl, inputs, n_inputs, outputs, st, launches);
+    g_alloc_record = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(st, &graph);
+    auto drop_outputs = [&]() { if (!rc) for (size_t i = 0; i < n_res; ++i) tensor_release(reinterpret_cast<Tensor*>(outputs[i])); };
+    if (getenv("GPTRS_DEBUG_GRAPH") && (rc || e != cudaSuccess)) fprintf(stderr, "plan graph: capture failed rc=%d cuda=%s\n", rc, cudaGetErrorString(e));
+    if (rc || e != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        drop_outputs();
+        if (rc) { *rc_out = rc; return true; }   // a real error of the program: report it
+        return false;
+    }
+    // fits only if every allocation of the run is exactly one result and no result is an input or a view
+    Plan::RunGraph g;
+    bool fits = record.size() == n_res;
+    g.result_of.assign(n_res, -1);
+    for (size_t i = 0; i < n_res && fits; ++i) {
+        Tensor* t = reinterpret_cast<Tensor*>(outputs[i]);
+        for (size_t k = 0; k < record.size(); ++k) if (record[k] == t) g.result_of[i] = (int)k;
+        fits = g.result_of[i] >= 0;
+        for (size_t j = 0; j < i && fits; ++j) fits = g.result_of[j] != g.result_of[i];
+    }
+    if (getenv("GPTRS_DEBUG_GRAPH")) {
+        fprintf(stderr, "plan graph: %zu allocations for %zu results, fits=%d\n", record.size(), n_res, (int)fits);
+        if (!fits) for (Tensor* t : record) {
+            bool is_res = false;
+            for (size_t i = 0; i < n_res; ++i) is_res = is_res || reinterpret_cast<Tensor*>(outputs[i]) == t;
+            if (!is_res) fprintf(stderr, "  extra allocation: dtype %d, %zu bytes, rank %zu\n", t->dtype, t->bytes, t->dims.size());
+        }
+    }
+    if (fits) {
+        e = cudaGraphInstantiate(&g.exec, graph, 0);
+        fits = e == cudaSuccess;
+    }
+    cudaGraphDestroy(graph);
+    if (fits) fits = cudaGraphLaunch(g.exec, st) == cudaSuccess;
+    if (!fits) {
+        if (g.exec) cudaGraphExecDestroy(g.exec);
+        cudaGetLastError();
+        drop_outputs();
+        return false;
+    }
+    for (size_t i = 0; i < n_inputs; ++i) g.in_ptrs.push_back(reinterpret_cast<Tensor*>(inputs[i])->data);
+    for (Tensor* t : record) {
+        TSpec sp;
+        sp.dtype = t->dtype;
+        sp.dims = t->dims;
+        g.allocs.push_back(sp);
+        g.alloc_ptrs.push_back(t->data);
+    }
+    g.launches = *launches;
+    pl.graphs.push_back(std::move(g));
+    return true;
+}
+
+int execute_plan(const std::shared_ptr<Plan>& plan, gptrs_tensor* const* inputs, size_t n_inputs, gptrs_tensor** outputs,
+                 size_t outputs_cap, size_t* n_outputs, void* stream) {
+    const Function& fn = plan->fn;
+    if (plan->device != current_device()) return fail(GPTRS_SPEC_VIOLATION, "the program was prepared on another device");
+    GPTRS_REQUIRE(n_inputs == fn.param_ids.size(), "entry input count does not match the function parameters");
+    GPTRS_REQUIRE(n_outputs && outputs_cap >= fn.result_ids.size() && (outputs || fn.result_ids.empty()), "output array too small");
+    // one execution at a time per plan: the temporaries of the function live at fixed offsets of the plan's arena
+    std::lock_guard<std::mutex> run_lock(plan->run_mu);
+    if (plan->arena_bytes > 0 && !plan->arena) {
+        int64_t ad[1] = {plan->arena_bytes};
+        if (int rc = tensor_alloc(GPTRS_UI8, 1, ad, false, &plan->arena)) return rc;
+    }
+    for (size_t i = 0; i < n_inputs; ++i) {
+        Tensor* t = reinterpret_cast<Tensor*>(inputs[i]);
+        GPTRS_REQUIRE(t, "null input handle");
+        if (t->dtype != fn.params[i].dtype || t->dims != fn.params[i].dims)
+            return fail(GPTRS_SPEC_VIOLATION, "input " + std::to_string(i) + " does not match the declared parameter type");
+    }
+    cudaStream_t st = as_stream(stream);
+    struct { int64_t launches = 0; } ex;
+    bool done = false;
+    g_last_graph_replays = 0;
+    // The first two executions run kernel by kernel (they fill the memos of derived weight layouts); later ones replay a
+    // graph when one fits, and record one (at most four per plan) when none does.
+    const bool graphs_on = g_plan_graphs.load(std::memory_order_relaxed) != 0 && plan->graph_ok && plan->arena && !fn.result_ids.empty();
+    ++plan->runs;
+    if (graphs_on && plan->runs > 2) {
+        if (!plan->side_stream) {
+            if (cudaStreamCreateWithFlags(&plan->side_stream, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&plan->ev_in, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&plan->ev_out, cudaEventDisableTiming) != cudaSuccess) {
+                cudaGetLastError();
+                plan->graph_ok = false;
+            }
+        }
+        if (plan->graph_ok) {
+            cudaStream_t gs = plan->side_stream;
+            GPTRS_CUDA_OK(cudaEventRecord(plan->ev_in, st));
+            GPTRS_CUDA_OK(cudaStreamWaitEvent(gs, plan->ev_in, 0));
+            done = try_replay(*plan, inputs, n_inputs, outputs, gs, &ex.launches);
+            if (done) g_last_graph_replays = 1;
+            if (!done && plan->graphs.size() < 4) {
+                int rc = GPTRS_OK;
+                done = capture_run(*plan, inputs, n_inputs, outputs, gs, &ex.launches, &rc);
+                if (done && rc) return rc;
+                if (!done && ++plan->graph_failures >= 2) plan->graph_ok = false;
+            }
+            if (done) {
+                GPTRS_CUDA_OK(cudaEventRecord(plan->ev_out, gs));
+                GPTRS_CUDA_OK(cudaStreamWaitEvent(st, plan->ev_out, 0));
+            }
+        }
+    }
+    if (!done) {
+        int rc = run_instructions(*plan, inputs, n_inputs, outputs, st, &ex.launches);
+        if (rc) return rc;
+    }
+    cudaStream_t ex_st = st;
     *n_outputs = fn.result_ids.size();
     g_last_launches = ex.launches;
     g_last_fused = plan->fused;
@@ -1284,10 +1462,10 @@ int execute_plan(const std::shared_ptr<Plan>& plan, gptrs_tensor* const* inputs,
     int* sw = status_word();
     if (sw) {
         int hs = 0;
-        GPTRS_CUDA_OK(cudaMemcpyAsync(&hs, sw, 4, cudaMemcpyDeviceToHost, ex.st));
-        GPTRS_CUDA_OK(cudaStreamSynchronize(ex.st));
+        GPTRS_CUDA_OK(cudaMemcpyAsync(&hs, sw, 4, cudaMemcpyDeviceToHost, ex_st));
+        GPTRS_CUDA_OK(cudaStreamSynchronize(ex_st));
         if (hs) {
-            cudaMemsetAsync(sw, 0, 4, ex.st);
+            cudaMemsetAsync(sw, 0, 4, ex_st);
             for (size_t i = 0; i < fn.result_ids.size(); ++i) tensor_release(reinterpret_cast<Tensor*>(outputs[i]));
             *n_outputs = 0;
             return fail(GPTRS_EXECUTION, "index out of range in take/gather");
@@ -1469,6 +1647,13 @@ int gptrs_cuda_set_fusion(int enabled) {
     g_fusion_enabled = enabled ? 1 : 0;
     return GPTRS_OK;
 }
+
+int gptrs_cuda_set_plan_graphs(int enabled) {
+    g_plan_graphs.store(enabled ? 1 : 0);
+    return GPTRS_OK;
+}
+
+int gptrs_cuda_last_run_replayed_graph(void) { return (int)g_last_graph_replays; }
 
 int gptrs_cuda_set_buffer_plan(int enabled) {
     g_arena_enabled = enabled ? 1 : 0;

@@ -130,6 +130,8 @@ int64_t Tensor::numel() const {
     return n;
 }
 
+thread_local std::vector<Tensor*>* g_alloc_record = nullptr;
+
 int tensor_alloc(int dtype, int rank, const int64_t* dims, bool zero, Tensor** out) {
     GPTRS_REQUIRE(out, "null output");
     GPTRS_REQUIRE(dtype_size(dtype) > 0, "unsupported dtype");
@@ -149,6 +151,7 @@ int tensor_alloc(int dtype, int rank, const int64_t* dims, bool zero, Tensor** o
             if (e != cudaSuccess) { pool_free(t->data, t->bytes, t->device); delete t; return fail(GPTRS_EXECUTION, "cudaMemset failed"); }
         }
     }
+    if (g_alloc_record) g_alloc_record->push_back(t);
     *out = t;
     return GPTRS_OK;
 }

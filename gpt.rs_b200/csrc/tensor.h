@@ -27,6 +27,9 @@ struct Tensor {
 
 size_t dtype_size(int dtype);
 int tensor_alloc(int dtype, int rank, const int64_t* dims, bool zero, Tensor** out);
+// While non-null on the calling thread, every tensor that tensor_alloc creates is appended (run_program records which
+// pool blocks an execution took, so that a replay can ask for the same ones).
+extern thread_local std::vector<Tensor*>* g_alloc_record;
 void tensor_retain(Tensor* t);
 void tensor_release(Tensor* t);
 

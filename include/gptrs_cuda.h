@@ -527,6 +527,14 @@ int gptrs_cuda_verify_program(const char* program_json, size_t len);
 int gptrs_cuda_run_program_stats(int64_t* plan_builds, int64_t* plan_hits, int64_t* last_launches, int64_t* last_fused);
 /* Turns the fusion rewrites of run_program on (default) or off (GPTRS_OPT-style switch for tests). */
 int gptrs_cuda_set_fusion(int enabled);
+/* CUDA graph per cached plan (on by default, needs the buffer plan): from its third execution on, a program whose every
+ * result is a freshly allocated buffer is recorded into a graph and later executions replay it with one launch. A graph is
+ * tied to the input buffers and to the pool blocks of its results, so a replay first takes the results from the pool in the
+ * recorded order and falls back to kernel-by-kernel execution (or records one more graph, at most four per plan) when the
+ * pool hands out other blocks. set_plan_graphs(0) turns it off; last_run_replayed_graph() tells whether the calling thread's
+ * last run_program was a replay. No counterpart in gpt.rs. */
+int gptrs_cuda_set_plan_graphs(int enabled);
+int gptrs_cuda_last_run_replayed_graph(void);
 /* Turns the per-plan buffer plan of run_program on (default) or off: with it the temporaries of a function live at
  * fixed offsets of one arena per cached plan (lifetime analysis, the counterpart of the reference's bufferisation,
  * crates/gpt-rs/src/backend/conversion/bufferize.rs); without it each is a pooled allocation of its own. Drops the

@@ -331,3 +331,56 @@ def test_run_program_accepts_the_fuse_phase_output(be, kind):
     launches_plain = be.run_program_stats()["last_launches"]
     assert launches_fused < launches_plain * 7 // 10, (launches_fused, launches_plain)
     be.set_fusion(True)
+
+
+@pytest.mark.parametrize("graphs", [True, False], ids=["plan-graphs", "kernel-by-kernel"])
+def test_decode_loop_through_a_prepared_program_replays_graphs(be, graphs):
+    """Ten greedy decode steps of a tiny GPT, every step ONE call of a prepared program with the previous step's K/V
+    handles in and fresh ones out, the way gpt.rs drives a backend. From the third call on the plan records CUDA graphs
+    (the result buffers ping-pong between two sets of pool blocks) and later calls replay them: the logits of every
+    step must equal the oracle's whether a step ran kernel by kernel, was recorded, or was a replay."""
+    from gptrs_b200 import lib
+    cfg = mr.Cfg("gpt", n_layers=2, d_model=64, n_q=4, n_kv=4, hd=16, d_mlp=128, vocab=96, ctx=32)
+    params = mr.random_params(cfg, seed=5, std=0.3)
+    ref = mr.RefModel(cfg, params)
+    prompt = [3, 1, 4, 1, 5]
+    logits = ref.forward(prompt)[-1]
+    cap = 32
+    b, names = ptir.decode_step_program(cfg, cap)
+    lib().gptrs_cuda_set_plan_graphs(1 if graphs else 0)
+    be.set_fusion(True)
+    try:
+        prog = be.prepare(b.to_json())
+        weights = {n: be.materialize(params[n]) for n in names if not n.startswith("@")}
+        caches = []
+        for k, v in ref.caches:   # the oracle's caches after the prompt, padded to the program's capacity
+            kp = np.zeros((cfg.n_kv, cap, cfg.hd), np.float32)
+            vp = np.zeros_like(kp)
+            kp[:, :k.shape[1]] = k
+            vp[:, :v.shape[1]] = v
+            caches.append((be.materialize(kp), be.materialize(vp)))
+        tok, pos, replays = int(np.argmax(logits)), len(prompt), 0
+        for step in range(10):
+            want = ref.forward([tok])[-1]
+            small = {"@tokens": np.array([tok], np.int32), "@positions": np.array([pos], np.int32),
+                     "@update_starts": np.array([0, pos, 0], np.int32), "@query_start": np.array([pos], np.int32)}
+            hs = []
+            for n in names:
+                if n in small:
+                    hs.append(be.materialize(small[n]))
+                elif n.startswith("@k"):
+                    hs.append(caches[int(n[2:])][0])
+                elif n.startswith("@v"):
+                    hs.append(caches[int(n[2:])][1])
+                else:
+                    hs.append(weights[n])
+            res = prog.run(hs)
+            replays += int(lib().gptrs_cuda_last_run_replayed_graph())
+            got = be.to_literal(res[0])[0]
+            assert np.allclose(got, want, rtol=1e-4, atol=1e-4), step
+            caches = [(res[1 + 2 * l], res[2 + 2 * l]) for l in range(cfg.n_layers)]
+            del res, hs
+            tok, pos = int(np.argmax(want)), pos + 1
+        assert (replays >= 4) if graphs else (replays == 0), replays
+    finally:
+        lib().gptrs_cuda_set_plan_graphs(1)
