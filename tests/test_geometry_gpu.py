@@ -38,6 +38,10 @@ def _rows_to_check(rng, n, want=768):
 SHAPES = [
     (64, 3072, 4096), (64, 3072, 9216), (16, 3072, 9216), (1, 3072, 9216), (16, 9216, 3072), (256, 9216, 3072),
     (64, 6144, 3072), (64, 18432, 3072), (1, 131072, 3072), (64, 131072, 3072), (256, 3072, 9216), (33, 3072, 4096),
+    # the per-rank shapes of the tensor-parallel engine at 2, 4 and 8 ranks (heads, MLP columns and vocabulary split)
+    (64, 3072, 2048), (64, 9216, 3072), (64, 3072, 4608), (64, 65536, 3072),
+    (64, 1536, 3072), (64, 3072, 1024), (64, 4608, 3072), (64, 3072, 2304), (64, 32768, 3072),
+    (64, 768, 3072), (64, 3072, 512), (64, 2304, 3072), (64, 3072, 1152), (64, 16384, 3072), (8, 3072, 1152), (8, 768, 3072),
 ]
 
 
@@ -130,11 +134,13 @@ def test_folded_epilogues_full_width(cuda):
     assert float(np.abs(b).sum()) > 0 and ops.matmul_status() == 0
 
 
-def test_attention_batch64_ragged_contexts(cuda):
-    """Batch 64, context lengths U{512..8192} (seed 0), 32 query / 8 KV heads, random page table: every sequence
-    goes through the kernel, the oracle checks eight of them, the longest and the shortest among them."""
-    n_q, n_kv, hd, b = 32, 8, 128, 64
-    lens = [int(v) for v in np.random.default_rng(0).integers(512, 8193, size=b)]
+@pytest.mark.parametrize("n_q,n_kv,hi", [(32, 8, 8192), (4, 1, 4096)], ids=["32q-8kv", "one-rank-of-tp8"])
+def test_attention_batch64_ragged_contexts(cuda, n_q, n_kv, hi):
+    """Batch 64, context lengths U{512..8192} (seed 0), 32 query / 8 KV heads (and the 4 / 1 heads a rank of an 8-way
+    tensor-parallel group holds), random page table: every sequence goes through the kernel, the oracle checks eight
+    of them, the longest and the shortest among them."""
+    hd, b = 128, 64
+    lens = [int(v) for v in np.random.default_rng(0).integers(512, hi + 1, size=b)]
     rng = np.random.default_rng(1)
     pages_per = [(l + 15) // 16 for l in lens]
     max_pages = max(pages_per)
