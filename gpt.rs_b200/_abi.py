@@ -50,6 +50,9 @@ class MatmulEpilogue(ctypes.Structure):
         ("rope_kv_heads", ctypes.c_int),
         ("d_status", ctypes.c_void_p),
         ("peer_push", ctypes.c_void_p),
+        ("d_best_val", ctypes.c_void_p),
+        ("d_best_idx", ctypes.c_void_p),
+        ("skip_store", ctypes.c_int),
     ]
 
 

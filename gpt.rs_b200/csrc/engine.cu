@@ -128,6 +128,9 @@ struct Model {
     bool peer_on = false;
     bool fuse_peer_push = true;   // GPTRS_TP_FUSED_PUSH=0: a copy kernel pushes the tile instead of the matmul epilogue
     DevBuf partial, tp_vals, tp_idx, tp_gvals, tp_gidx;  // row-parallel partial sums; (max, argmax) exchange
+    // greedy head of the quantised engine: per-tile (max, argmax) candidates from the lm_head epilogue
+    DevBuf best_val, best_idx;
+    bool fuse_pick = true;   // GPTRS_FUSE_PICK=0: logits + sampling kernel
     // f32 GPT kind, one sequence: the whole decode step as one cooperative kernel (gpt_decode_mega.cu)
     bool mega_on = false;
     DevBuf mega_wt, mega_scratch;   // transposed weights [out][in]; vectors + barrier word
@@ -313,7 +316,8 @@ struct NormFold {
 };
 
 int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool out_f32, const float* residual,
-           bool swiglu, bool gelu, cudaStream_t st, const NormFold* fold = nullptr, const PeerView* push = nullptr) {
+           bool swiglu, bool gelu, cudaStream_t st, const NormFold* fold = nullptr, const PeerView* push = nullptr,
+           bool pick = false) {
     ++m.launches;
     if (m.f32()) {
         return gptrs_cuda_norm_matmul_f32(static_cast<const float*>(x), fold ? fold->f32_norm : 0, fold ? fold->f32_gamma : nullptr,
@@ -328,6 +332,7 @@ int linear(Model& m, const Weight& w, const void* x, void* y, int64_t rows, bool
     ep.swiglu = swiglu ? 1 : 0;
     ep.d_status = m.d_status.as<int32_t>();  // a matmul wait that gives up reports through the model's word
     ep.peer_push = push;
+    if (pick) { ep.d_best_val = m.best_val.as<float>(); ep.d_best_idx = m.best_idx.as<int32_t>(); ep.skip_store = 1; }
     if (fold && fold->produce) { ep.d_norm_gamma = fold->gamma; ep.d_norm_x = fold->x_next; ep.d_sumsq_out = fold->sumsq; }
     if (fold && fold->consume) { ep.d_sumsq_in = fold->sumsq; ep.sumsq_tiles = fold->dim / 128; ep.norm_dim = fold->dim; ep.norm_eps = fold->eps; }
     if (fold && fold->rope_positions) {
@@ -415,7 +420,7 @@ int attention_plan(const Model& m, int T, int max_ctx, size_t scratch_bytes, int
 // already in the device arrays. `rows`: number of rows that get logits (row indices in d_rows,
 // or all T rows in order when rows_identity).
 int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, bool rows_identity, float temperature,
-                    bool prefill_groups = false) {
+                    bool prefill_groups = false, bool skip_logits = false) {
     const auto& c = m.cfg;
     const int D = c.d_model;
     cudaStream_t st = m.stream;
@@ -669,8 +674,13 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
     }
     NormFold final_fold;
     if (fold32) final_fold = fold32_for(m.final_g, m.final_b);
-    if ((rc = linear(m, m.lm_head, xr, m.logits.p, n_rows, true, nullptr, false, false, st, fold32 ? &final_fold : nullptr))) return rc;
+    // Greedy ids that nobody wants the logits of (generator steps): the lm_head epilogue leaves per-tile candidates and a
+    // small kernel picks among them; the [rows, vocab] logits are neither written nor read.
+    const bool pick = skip_logits && m.fuse_pick && temperature <= 0.f && m.tp == 1 && !m.f32() && n_rows > 16 && m.best_val.p;
+    if ((rc = linear(m, m.lm_head, xr, m.logits.p, n_rows, true, nullptr, false, false, st, fold32 ? &final_fold : nullptr, nullptr, pick))) return rc;
     ++m.launches;
+    if (pick)
+        return gptrs_cuda_pick_best(m.best_val.as<float>(), m.best_idx.as<int32_t>(), (c.vocab + 127) / 128, n_rows, m.d_sampled.as<int32_t>(), st);
     if (m.tp == 1)
         return gptrs_cuda_sample_rows_top_k(m.logits.as<float>(), n_rows, c.vocab, temperature, m.top_k, m.sample_seed, m.d_sampled.as<int32_t>(), st);
     // vocab-parallel head: every rank finds (max, argmax) of its shard, the pairs are all-gathered
@@ -1061,6 +1071,11 @@ int gptrs_cuda_model_finalize(gptrs_model* h, int drop_f32_leaves) {
     if (!m.f32() && (rc = m.q_rot.alloc((size_t)T * QD * 2))) return rc;
     const int max_rows = c.max_logit_rows > 0 ? c.max_logit_rows : c.max_seqs;
     if ((rc = m.logits.alloc((size_t)max_rows * m.vocab_l * 4))) return rc;
+    if (!m.f32() && m.tp == 1) {
+        const size_t tiles = (size_t)(m.vocab_l + 127) / 128;
+        if ((rc = m.best_val.alloc(tiles * max_rows * 4)) || (rc = m.best_idx.alloc(tiles * max_rows * 4))) return rc;
+        if (const char* e = getenv("GPTRS_FUSE_PICK")) m.fuse_pick = atoi(e) != 0;
+    }
     if (m.tp > 1 && ((rc = m.partial.alloc((size_t)T * D * 4)) || (rc = m.tp_vals.alloc((size_t)max_rows * 4)) || (rc = m.tp_idx.alloc((size_t)max_rows * 4)) ||
                      (rc = m.tp_gvals.alloc((size_t)m.tp * max_rows * 4)) || (rc = m.tp_gidx.alloc((size_t)m.tp * max_rows * 4)))) return rc;
     if ((rc = m.history.alloc((size_t)c.max_seqs * c.context_length * 4, true))) return rc;
@@ -1321,7 +1336,7 @@ int gptrs_cuda_generator_step(gptrs_model* h, const int32_t* h_tokens_in, int32_
     attention_plan(m, B, bucket, m.attn_scratch.n, &chunk);
     const int splits = m.f32() ? 1 : (bucket + chunk * kPage - 1) / (chunk * kPage);
     auto body = [&]() -> int {
-        int r = enqueue_forward(m, B, bucket, chunk, B, true, 0.f);
+        int r = enqueue_forward(m, B, bucket, chunk, B, true, 0.f, false, true);
         if (r) return r;
         // next step: the consumed ids go into the history, the sampled ids become the inputs, positions advance
         AdvanceParams ap = {m.d_tokens.as<int>(), m.d_sampled.as<int>(), m.d_pos.as<int>(), m.d_ctx.as<int>(), m.history.as<int>(), B,

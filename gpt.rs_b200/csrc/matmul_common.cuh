@@ -75,6 +75,11 @@ struct MatmulParams {
     // receive slots of the one-shot all-reduce in every peer's memory (peer_allreduce.cu)
     int peer_on;
     PeerView peer;
+    // greedy head: per (column tile, row) the largest output and its column (ties: the smaller column), for a pick kernel
+    // that then reads rows x tiles candidates instead of rows x N logits; 128-column tiles only
+    float* best_val;   // [N / 128][M]
+    int* best_idx;
+    int skip_store;    // with best_val: the outputs themselves are not written
 };
 
 // ---- split-K reduction across the CTAs of a cluster: push, one barrier, local sum -------------------
@@ -209,7 +214,7 @@ __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const
             const int lr = j >> sh4, c4 = j & (cols4 - 1);
             const int m = m0 + rank + S * lr, n = n_cta0 + c4 * 4;
             const bool live = m < p.M && n < p.N;
-            if (!live && !p.sumsq_out) continue;
+            if (!live && !p.sumsq_out && !p.best_val) continue;
             float4 v = live ? gather(lr, c4 * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (p.sumsq_in) { const float r = row_scale[lr]; v.x *= r; v.y *= r; v.z *= r; v.w *= r; }
             if (live && p.bias) {
@@ -220,7 +225,28 @@ __device__ __forceinline__ void split_reduce_finish(const MatmulParams& p, const
                 float4 b = *reinterpret_cast<const float4*>(p.residual + (size_t)m * p.N + n);
                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
             }
-            if (live) {
+            if (p.best_val) {
+                // the 32 lanes of a warp hold one row of the 128-column tile
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+                if (live) {
+                    bv = v.x; bi = n;
+                    if (v.y > bv) { bv = v.y; bi = n + 1; }
+                    if (v.z > bv) { bv = v.z; bi = n + 2; }
+                    if (v.w > bv) { bv = v.w; bi = n + 3; }
+                }
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+                    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+                }
+                if ((tid & 31) == 0 && m < p.M) {
+                    p.best_val[(size_t)(n_cta0 / kCtaN) * p.M + m] = bv;
+                    p.best_idx[(size_t)(n_cta0 / kCtaN) * p.M + m] = bi;
+                }
+            }
+            if (live && !(p.best_val && p.skip_store)) {
                 if (p.out_f32) {
                     *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.y) + (size_t)m * p.N + n) = v;
                     if (p.peer_on) {

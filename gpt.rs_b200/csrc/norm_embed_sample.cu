@@ -245,6 +245,36 @@ __global__ void __launch_bounds__(256) softmax_kernel(const SoftmaxParams p) {
 }
 
 // ---- sampler ----------------------------------------------------------------------------------
+// Greedy pick among per-tile candidates (see gptrs_matmul_epilogue.d_best_val): one CTA per row.
+struct PickParams { const float* val; const int* idx; int* tokens; int n_tiles, rows; };
+__global__ void __launch_bounds__(128) pick_best_kernel(const PickParams p) {
+    __shared__ float sv[4];
+    __shared__ int si[4];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int t = tid; t < p.n_tiles; t += 128) {
+        const float v = p.val[(size_t)t * p.rows + row];
+        const int i = p.idx[(size_t)t * p.rows + row];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((tid & 31) == 0) { sv[tid >> 5] = bv; si[tid >> 5] = bi; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < 4; ++w)
+            if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+        p.tokens[row] = bi;
+    }
+}
+
 struct SampleParams {
     const float* logits;  // [rows][vocab]
     float* values;        // optional [rows]: the winning (scaled) logit
@@ -547,6 +577,15 @@ int gptrs_cuda_sample_rows_top_k(const float* d_logits, int64_t rows, int64_t vo
     if (rows == 0) return GPTRS_OK;
     TopKParams p = {d_logits, d_tokens, (int)rows, (int)vocab, (int)top_k, temperature, seed};
     return launch_kernel(sample_top_k_kernel, dim3((unsigned)rows), dim3(kTopKThreads), 0, as_stream(stream), 1, p);
+}
+
+int gptrs_cuda_pick_best(const float* d_best_val, const int32_t* d_best_idx, int64_t n_tiles, int64_t rows, int32_t* d_tokens,
+                         void* stream) {
+    GPTRS_REQUIRE(d_best_val && d_best_idx && d_tokens, "null pointer");
+    GPTRS_REQUIRE(n_tiles > 0 && rows >= 0 && n_tiles < (1ll << 24) && rows < (1ll << 24), "bad shape");
+    if (rows == 0) return GPTRS_OK;
+    PickParams p = {d_best_val, d_best_idx, d_tokens, (int)n_tiles, (int)rows};
+    return launch_kernel(pick_best_kernel, dim3((unsigned)rows), dim3(128), 0, as_stream(stream), 1, p);
 }
 
 int gptrs_cuda_sample_rows(const float* d_logits, int64_t rows, int64_t vocab, float temperature, uint32_t seed,

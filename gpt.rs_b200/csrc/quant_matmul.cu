@@ -598,6 +598,14 @@ int quant_matmul(const void* d_x, const void* d_packed, void* d_y, int64_t m, in
             p.rope_pool = static_cast<unsigned char*>(ep->d_rope_kv_pool);
             p.rope_hq = ep->rope_q_heads; p.rope_hkv = ep->rope_kv_heads;
         }
+        if (ep->d_best_val || ep->d_best_idx) {
+            GPTRS_REQUIRE(ep->d_best_val && ep->d_best_idx && m > 16 && p.out_f32 && !p.swiglu && !p.sumsq_out && !p.rope_pos && !ep->peer_push &&
+                              !ep->d_sumsq_in && n % 4 == 0,
+                          "greedy-head candidates: more than 16 rows, f32 output, no other epilogue");
+            p.best_val = ep->d_best_val;
+            p.best_idx = ep->d_best_idx;
+            p.skip_store = ep->skip_store ? 1 : 0;
+        }
         if (ep->peer_push) {
             const PeerView* pv = static_cast<const PeerView*>(ep->peer_push);
             GPTRS_REQUIRE(p.out_f32 && !p.swiglu && !p.sumsq_out && !p.rope_pos && !ep->d_sumsq_in && n % 4 == 0 &&

@@ -108,7 +108,7 @@ def _epilogue(out_f32, bias, residual, swiglu):
     return ep
 
 
-def _quant_matmul(fn, x, packed, m, n, k, out, out_f32, bias, residual, swiglu, norm_out=None, norm_in=None, rope=None):
+def _quant_matmul(fn, x, packed, m, n, k, out, out_f32, bias, residual, swiglu, norm_out=None, norm_in=None, rope=None, best=None):
     """norm_out = (gamma f32 [N], x_next bf16 [M][N], sumsq f32 [N/128][M]) makes this call the producer of a folded
     RMSNorm; norm_in = (sumsq f32 [tiles][M], norm_dim, eps) makes it the consumer (see gptrs_matmul_epilogue)."""
     n_out = n // 2 if swiglu else n
@@ -124,8 +124,18 @@ def _quant_matmul(fn, x, packed, m, n, k, out, out_f32, bias, residual, swiglu, 
         ep.d_rope_positions, ep.d_rope_slot, ep.d_rope_page_table = _ptr(pos), _ptr(slot), _ptr(table)
         ep.rope_max_pages, ep.d_rope_cos, ep.d_rope_sin = table.shape[1], _ptr(cos), _ptr(sin)
         ep.d_rope_q_out, ep.d_rope_kv_pool, ep.rope_q_heads, ep.rope_kv_heads = _ptr(q_out), _ptr(pool), n_q, n_kv
+    if best is not None:   # (best_val f32 [tiles][M], best_idx int32 [tiles][M], skip_store)
+        ep.d_best_val, ep.d_best_idx, ep.skip_store = _ptr(best[0]), _ptr(best[1]), int(bool(best[2]))
     check(fn(_ptr(x), _ptr(packed), _ptr(out), m, n, k, ctypes.byref(ep), _stream()))
     return out
+
+
+def pick_best(best_val, best_idx):
+    """gptrs_cuda_pick_best: per row the column of the largest per-tile candidate."""
+    tiles, rows = best_val.shape
+    tokens = torch.empty(rows, dtype=torch.int32, device=best_val.device)
+    check(lib().gptrs_cuda_pick_best(_ptr(best_val), _ptr(best_idx), tiles, rows, _ptr(tokens), _stream()))
+    return tokens
 
 
 def quant_matmul_w4a16(x, packed, m, n, k, out=None, out_f32=False, bias=None, residual=None, swiglu=False, **norm):

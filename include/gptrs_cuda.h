@@ -144,7 +144,18 @@ typedef struct {
      * gptrs_cuda_model_tp_allreduce_kind): the GEMM and the push of the collective are one kernel. Points to the engine's
      * description of the peers (opaque to callers); needs out_dtype f32 and no other epilogue. */
     const void* peer_push;
+    /* Greedy head (rows > 16, f32 output, no other epilogue): besides (or, with skip_store != 0, instead of) the outputs the
+     * kernel writes per 128-column tile and row the largest output and its column (ties: the smaller column) to
+     * d_best_val / d_best_idx [ceil(N / 128)][rows]; gptrs_cuda_pick_best then chooses per row among the tiles. The
+     * result equals the argmax of the f32 logits (what Sampler::argmax / sample_decode_token return). */
+    float* d_best_val;
+    int32_t* d_best_idx;
+    int skip_store;
 } gptrs_matmul_epilogue;
+
+/* tokens[r] = column of the largest candidate of row r among n_tiles per-tile candidates (see d_best_val). */
+int gptrs_cuda_pick_best(const float* d_best_val, const int32_t* d_best_idx, int64_t n_tiles, int64_t rows, int32_t* d_tokens,
+                         void* stream);
 
 /* sizeof(gptrs_matmul_epilogue) as the library was built: lets a foreign-language binding check its own
  * declaration of the struct before the first call. */

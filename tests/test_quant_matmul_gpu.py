@@ -221,3 +221,34 @@ def test_matmul_rejects_bad_arguments(cuda):
     with pytest.raises(BackendError) as e:
         ops.quant_matmul_w4a16(x, x, 1, 16, 100)
     assert e.value.kind == "SpecViolation"
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("m,n,k", [(64, 4096, 512), (33, 1000 * 4, 256), (17, 128, 128)])
+def test_greedy_head_candidates_equal_the_argmax_of_the_logits(cuda, bits, m, n, k):
+    """The lm_head epilogue that leaves per-tile (max, argmax) candidates, and the pick among them: the ids equal the
+    argmax of the kernel's own f32 outputs (ties to the smaller column), with and without the outputs being stored."""
+    rng = np.random.default_rng(bits * 1000 + m + n)
+    x = torch.from_numpy(rng.normal(0, 1, size=(m, k)).astype(np.float32)).to(cuda).to(torch.bfloat16)
+    if bits == 4:
+        p = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+        s = (rng.uniform(0.5, 1.5, size=(n, k // 128)) * 0.01).astype(np.float16)
+        packed = ops.w4a16_repack(torch.from_numpy(p).to(cuda), torch.from_numpy(s).to(cuda), n, k)
+        run = ops.quant_matmul_w4a16
+    else:
+        q = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+        s = (rng.uniform(0.5, 1.5, size=(n,)) * 0.01).astype(np.float16)
+        packed = ops.w8a16_repack(torch.from_numpy(q).to(cuda), torch.from_numpy(s).to(cuda), n, k)
+        run = ops.quant_matmul_w8a16
+    tiles = (n + 127) // 128
+    logits = run(x, packed, m, n, k, out_f32=True)
+    want = torch.argmax(logits, dim=1).to(torch.int32)   # torch returns the first maximum: the smaller column
+    for skip in (False, True):
+        bv = torch.full((tiles, m), float("nan"), dtype=torch.float32, device=cuda)
+        bi = torch.full((tiles, m), -1, dtype=torch.int32, device=cuda)
+        out = torch.zeros((m, n), dtype=torch.float32, device=cuda)
+        run(x, packed, m, n, k, out=out, out_f32=True, best=(bv, bi, skip))
+        got = ops.pick_best(bv, bi)
+        assert torch.equal(got, want), skip
+        assert torch.equal(out, logits) if not skip else float(out.abs().max()) == 0.0
+    assert ops.matmul_status() == 0
