@@ -153,4 +153,6 @@ def main(root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_lit_fixtures.py <root of a gpt.rs source tree>")
+    main(sys.argv[1])
