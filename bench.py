@@ -189,7 +189,7 @@ def time_attention_kernel(ops, torch, dev, ctx_len: int, launches: int = 20, rag
     return ms, alg_bytes, chunk
 
 
-def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3, bits=4):
+def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3, bits=4, pdl=True):
     """W4A16 / W8A16 matmul over a rotating set of distinct weight matrices (working set >> L2)."""
     if bits == 4:
         nbytes = ops.w4a16_packed_bytes(n, k)
@@ -214,13 +214,19 @@ def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3, bits=4):
         run(x, mt, m, n, k, out=y)
     torch.cuda.synchronize()
     # one CUDA graph over all matrices: the timing sees the device, not the Python launch rate
+    # ... and the launches carry programmatic dependent launch edges, as in the engine's recorded decode step
+    from gptrs_b200 import lib as _lib
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
-    with torch.cuda.stream(side):
-        graph.capture_begin()
-        for mt in mats:
-            run(x, mt, m, n, k, out=y)
-        graph.capture_end()
+    before = _lib().gptrs_cuda_set_thread_pdl(1 if pdl else 0)
+    try:
+        with torch.cuda.stream(side):
+            graph.capture_begin()
+            for mt in mats:
+                run(x, mt, m, n, k, out=y)
+            graph.capture_end()
+    finally:
+        _lib().gptrs_cuda_set_thread_pdl(before)
     torch.cuda.synchronize()
     graph.replay()
     torch.cuda.synchronize()
@@ -882,7 +888,7 @@ def _main(out):
         g_us, g_bytes = time_gemv(ops, torch, dev)
         line["gemv_w4a16"] = {"shape": "M=1 N=9216 K=3072", "us_per_launch": g_us, "achieved_gbs": g_bytes / (g_us * 1e-6) / 1e9,
                               "frac_of_peak": g_bytes / (g_us * 1e-6) / 1e9 / peak, "frac_of_nominal_8tbs": g_bytes / (g_us * 1e-6) / 8e12,
-                              "note": "64 distinct weight matrices in rotation (0.94 GB working set), back-to-back launches in one CUDA graph"}
+                              "note": "64 distinct weight matrices in rotation (0.94 GB working set), back-to-back launches in one CUDA graph with programmatic dependent launch edges, as in the engine's recorded step"}
         g_us, g_bytes = time_gemv(ops, torch, dev, n=131072, k=3072, n_mats=4, iters=3)
         line["gemv_w4a16_lm_head"] = {"shape": "M=1 N=131072 K=3072", "us_per_launch": g_us,
                                       "achieved_gbs": g_bytes / (g_us * 1e-6) / 1e9, "frac_of_peak": g_bytes / (g_us * 1e-6) / 1e9 / peak}

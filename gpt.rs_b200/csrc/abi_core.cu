@@ -44,5 +44,10 @@ extern "C" {
 const char* gptrs_cuda_last_error(void) { return gptrs::g_last_error.c_str(); }
 const char* gptrs_cuda_backend_name(void) { return "cuda"; }
 int gptrs_cuda_abi_version(void) { return 1; }
+int gptrs_cuda_set_thread_pdl(int enabled) {
+    const int before = gptrs::g_use_pdl;
+    gptrs::g_use_pdl = enabled ? 1 : 0;
+    return before;
+}
 
 }  // extern "C"

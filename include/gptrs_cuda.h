@@ -41,6 +41,11 @@ typedef enum {
 } gptrs_dtype;
 
 /* Message of the last failing call on this thread ("" if none). */
+/* Launch option of the calling thread: with a non-zero value every kernel this thread launches through the library carries
+ * the programmatic-stream-serialisation attribute (each kernel of the library executes griddepcontrol.wait before it reads
+ * what its predecessor wrote), the way the engine records its decode step; used to time chains of functional-level calls as
+ * the engine runs them. Returns the previous value. No counterpart in gpt.rs. */
+int gptrs_cuda_set_thread_pdl(int enabled);
 const char* gptrs_cuda_last_error(void);
 /* backend_name(): always "cuda" (spec.rs:1291). */
 const char* gptrs_cuda_backend_name(void);
