@@ -766,6 +766,11 @@ void plan_buffers(Plan& pl) {
         // a second result (the sum of a fused residual-add + norm) lives right behind the first, for the same lifetime
         // (value ids of both map to this instruction, so `last` already covers the readers of either)
         if (in.side_id) bytes += (((int64_t)in.side_out.numel() * (int64_t)dtype_size(in.side_out.dtype)) + 255) & ~(int64_t)255;
+        // the bf16 copy of the activations that a quantised matmul reads lives right behind its result
+        if (in.op == Op::FusedQuantMatmul && !in.operands.empty()) {
+            const TSpec* xs = spec_of(pl, in.operands[0]);
+            if (xs) bytes += ((xs->numel() * 2) + 255) & ~(int64_t)255;
+        }
         if (bytes == 0) continue;
         const int free_at = last[i] < 0 ? i : last[i];
         int best = -1;
@@ -1172,7 +1177,15 @@ int exec_inst(Exec& ex, const Inst& in, std::vector<Tensor*>& ops, Tensor** resu
                 tensor_retain(packed);
             }
             Tensor* xb = nullptr;   // the kernels take bf16 activations
-            if ((rc = tensor_alloc(GPTRS_BF16, 2, X->dims.data(), false, &xb))) { tensor_release(packed); return rc; }
+            if (ex.arena && ex.arena_off >= 0) {   // planned: right behind the result
+                const int64_t main_bytes = (((int64_t)in.out.numel() * (int64_t)dtype_size(in.out.dtype)) + 255) & ~(int64_t)255;
+                xb = new Tensor();
+                xb->dtype = GPTRS_BF16; xb->dims = X->dims;
+                xb->bytes = (size_t)X->numel() * 2;
+                xb->data = static_cast<unsigned char*>(ex.arena->data) + ex.arena_off + main_bytes;
+                xb->owns = false; xb->base = ex.arena; xb->device = ex.arena->device;
+                tensor_retain(ex.arena);
+            } else if ((rc = tensor_alloc(GPTRS_BF16, 2, X->dims.data(), false, &xb))) { tensor_release(packed); return rc; }
             EwParams cp = {};
             cp.a = X->data; cp.out = xb->data; cp.n = X->numel(); cp.op = 6;
             rc = launch_flat(cast_kernel, cp.n, cp, ex.st);

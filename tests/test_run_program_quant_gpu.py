@@ -177,3 +177,38 @@ def test_buffer_plan_and_pool_reach_a_steady_state(be):
         assert allocs[-1] == allocs[2], allocs   # steps 3 .. 5 allocate nothing from the driver
     assert outs[True] == outs[False]
     be.set_buffer_plan(True)
+
+
+def test_a_program_with_quantised_matmuls_replays_its_graph(be):
+    """x -> rms_norm -> W4 projection -> residual add, run ten times with fresh activations: the bf16 copy of the
+    activations lives in the plan's arena, so the execution fits the graph scheme; every run equals the interpreter
+    (bf16 activations against an f32 oracle: 2e-2 of the output scale) and the later runs are replays."""
+    from gptrs_b200 import lib
+    rng = np.random.default_rng(21)
+    m, d = 24, 256
+    q = rng.integers(0, 256, size=(d, d // 2), dtype=np.uint8)
+    s = _scales(rng, (d, d // 128))
+    gamma = rng.normal(1.0, 0.1, size=(d,)).astype(np.float32)
+    b = ptir.Builder()
+    x = b.parameter(F32, [m, d])
+    qp = b.parameter(ptir.UI8, [d, d // 2])
+    sp = b.parameter(ptir.F16, [d, d // 128])
+    g = b.parameter(F32, [d])
+    xn = ptir.rms_norm(x, g, 1e-5)
+    w = qp.dequantize(sp)
+    y = xn.dot_general(w, [], [1], [1])
+    b.set_results([x + y])
+    be.set_fusion(True)
+    be.set_buffer_plan(True)
+    prog = be.prepare(b.to_json())
+    qh, sh, gh = be.materialize(q), be.materialize(s), be.materialize(gamma)
+    replays = 0
+    for it in range(10):
+        xa = rng.normal(0, 1, size=(m, d)).astype(np.float32)
+        res = prog.run([be.materialize(xa), qh, sh, gh])
+        replays += int(lib().gptrs_cuda_last_run_replayed_graph())
+        got = be.to_literal(res[0])
+        want = pr.run_program(json.loads(b.to_json()), [xa, q, s, gamma])[0]
+        assert np.abs(got - want).max() <= 2e-2 * max(1.0, float(np.abs(want).max())), it
+        del res
+    assert replays >= 4, replays
