@@ -420,7 +420,7 @@ int attention_plan(const Model& m, int T, int max_ctx, size_t scratch_bytes, int
 // already in the device arrays. `rows`: number of rows that get logits (row indices in d_rows,
 // or all T rows in order when rows_identity).
 int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, bool rows_identity, float temperature,
-                    bool prefill_groups = false, bool skip_logits = false) {
+                    int prefill_groups = 0, bool skip_logits = false) {
     const auto& c = m.cfg;
     const int D = c.d_model;
     cudaStream_t st = m.stream;
@@ -594,7 +594,8 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
         // In a two-lane step the projections of the other lane outrank attention CTAs that wait for an SM.
         struct PriorityGuard { int saved; PriorityGuard() : saved(g_launch_priority) { g_launch_priority = 0; } ~PriorityGuard() { g_launch_priority = saved; } } guard;
         // token rows that come in per-sequence groups (a prompt chunk) share the K/V stream of their group
-        auto attention_fn = prefill_groups ? gptrs_cuda_paged_attention_prefill : gptrs_cuda_paged_attention_decode;
+        auto attention_fn = prefill_groups == 2 ? gptrs_cuda_paged_attention_prefill_blocks
+                            : prefill_groups ? gptrs_cuda_paged_attention_prefill : gptrs_cuda_paged_attention_decode;
         return attention_fn(at(m.q_rot, (size_t)m.QD() * 2, ln), pool, m.d_page_table.as<int32_t>(),
                                                  c.max_pages_per_seq, ints(m.d_slot, ln), ints(m.d_ctx, ln), out, ln.scratch,
                                                  ln.scratch_n, m.d_status.as<int32_t>(), ln.T, c.n_q_heads, c.n_kv_heads,
@@ -1195,15 +1196,22 @@ int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* h, const int32_t* h_
     if (n_logit_rows) GPTRS_CUDA_OK(cudaMemcpyAsync(m.d_rows.p, st + 4 * stride, (size_t)n_logit_rows * 4, cudaMemcpyHostToDevice, s));
     // Prefill chunks: when every aligned group of 16 / (query heads per kv head) rows belongs to one sequence,
     // the attention kernel streams the K/V pages once per group instead of once per row.
-    bool prefill_groups = false;
+    // GPTRS_PREFILL_BLOCKS=1: when every aligned block of four such groups (16 tokens at a group of 4) is one sequence, a
+    // CTA takes the whole block and the pages are streamed once for it. Off by default: measured 10 % slower (8 x 2048
+    // prompt tokens in 210 ms against 189 ms): the grouped kernel is bound by its mma.sync arithmetic, not by the K/V
+    // stream, and four warps that share one ring wait for each other.
+    int prefill_groups = 0;
     int attn_rows = T;
     if (!m.f32() && T >= 2) {
         const int grp = c.n_q_heads / c.n_kv_heads;
         if (grp == 1 || grp == 2 || grp == 4 || grp == 8) {
             const int tq = 16 / grp;
-            prefill_groups = tq > 1;
-            for (int i = 0; i < T && prefill_groups; ++i) prefill_groups = h_slots[i] == h_slots[i - i % tq];
-            if (prefill_groups) attn_rows = (T + tq - 1) / tq;
+            bool groups = tq > 1, blocks = true;
+            static const bool blocks_on = [] { const char* e = getenv("GPTRS_PREFILL_BLOCKS"); return e && atoi(e) != 0; }();
+            for (int i = 0; i < T && groups; ++i) groups = h_slots[i] == h_slots[i - i % tq];
+            for (int i = 0; i < T && blocks; ++i) blocks = h_slots[i] == h_slots[i - i % (4 * tq)];
+            if (blocks && blocks_on && T >= 4 * tq) { prefill_groups = 2; attn_rows = (T + 4 * tq - 1) / (4 * tq); }
+            else if (groups) { prefill_groups = 1; attn_rows = (T + tq - 1) / tq; }
         }
     }
     int chunk = 1;

@@ -337,6 +337,196 @@ __global__ void __launch_bounds__(kAttnWarps * 32, (kDepth <= 2) ? 3 : 2) paged_
     }
 }
 
+// Prefill over whole blocks of rows of ONE sequence: a CTA takes kAttnWarps * (16 / group) consecutive token rows
+// (16 tokens at a GQA group of 4). Every warp owns 16 / group of them as its 16-row MMA tile (row r = query head r % group
+// of its token r / group, each row with its own visible length, exactly as in the grouped kernel above), and ALL warps walk
+// ALL pages of the CTA's split from ONE ring of shared-memory stages: warp 0 issues the 8 KB bulk copies, a stage is
+// refilled once the four warps have arrived on its `empty` barrier. The K/V pages are thus streamed once per 16 tokens
+// instead of once per 4, and no warp merges with another at the end: it normalises and stores its own rows.
+template <int kDepth>
+__global__ void __launch_bounds__(kAttnWarps * 32, 3) paged_attention_block_kernel(const AttnParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];   // kDepth stages of one (page, head) block each
+    __shared__ __align__(8) uint64_t full_bar[kDepth];
+    __shared__ __align__(8) uint64_t empty_bar[kDepth];
+
+    const int split = blockIdx.x, h = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int group = p.Hq / p.Hkv;
+    const int tw = 16 / group;                        // tokens of a warp
+    const int b_cta = blockIdx.z * (kAttnWarps * tw);   // first token of the CTA
+    const int b = b_cta + warp * tw;                  // first token of this warp
+
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
+    const int tok_lo = b + g / group, tok_hi = b + (g + 8) / group;
+    const bool valid_lo = tok_lo < p.T, valid_hi = tok_hi < p.T;
+    const int len_lo = valid_lo ? clamped_len(p, tok_lo) : 0, len_hi = valid_hi ? clamped_len(p, tok_hi) : 0;
+    int len = 0, w_len = 0;   // the most any row of the CTA / of this warp may see
+    for (int i = 0; i < kAttnWarps * tw && b_cta + i < p.T; ++i) {
+        const int l = clamped_len(p, b_cta + i);
+        len = max(len, l);
+        if (i / tw == warp) w_len = max(w_len, l);
+    }
+    const int chunk_tokens = p.chunk_pages * kPageTokens;
+    const int first_tok = split * chunk_tokens;
+    if (first_tok >= len) return;  // whole CTA leaves together, before any barrier
+    const int n_tok = min(chunk_tokens, len - first_tok);
+    const int n_pages = (n_tok + kPageTokens - 1) / kPageTokens;
+    const int* pt = p.page_table + (size_t)p.slot[b_cta] * p.max_pages + first_tok / kPageTokens;
+
+    if (tid == 0) {
+        for (int s = 0; s < kDepth; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kAttnWarps); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    bool failed = false;
+    // warp 0 is also the producer: its lanes keep the ids of 32 pages at a time
+    int page_ids = 0, ids_base = -1;
+    auto issue = [&](int j) {   // all lanes of warp 0
+        if (j / 32 != ids_base) {
+            ids_base = j / 32;
+            const int idx = ids_base * 32 + lane;
+            page_ids = idx < n_pages ? pt[idx] : 0;
+        }
+        const int pg = __shfl_sync(0xffffffffu, page_ids, j & 31);
+        if (lane == 0) {
+            const int st = j % kDepth;
+            // a stage is free again when all warps have passed its previous use
+            if (j >= kDepth && !mbar_wait_bounded(&empty_bar[st], ((j / kDepth) + 1) & 1)) failed = true;
+            fence_proxy_async();
+            mbar_expect_tx(&full_bar[st], kPageHeadBytes);
+            bulk_g2s(smem + st * kPageHeadBytes, p.pool + ((size_t)pg * p.Hkv + h) * kPageHeadBytes, kPageHeadBytes, &full_bar[st]);
+        }
+    };
+    if (warp == 0)
+        for (int j = 0; j < kDepth && j < n_pages; ++j) issue(j);
+
+    uint32_t qf[8][4];
+    {
+        const __nv_bfloat16* qlo = p.q + ((size_t)(valid_lo ? tok_lo : b_cta) * p.Hq + h * group + g % group) * kHD;
+        const __nv_bfloat16* qhi = p.q + ((size_t)(valid_hi ? tok_hi : b_cta) * p.Hq + h * group + (g + 8) % group) * kHD;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            qf[ks][0] = valid_lo ? *reinterpret_cast<const uint32_t*>(qlo + ks * 16 + 2 * t) : 0u;
+            qf[ks][1] = valid_lo ? *reinterpret_cast<const uint32_t*>(qlo + ks * 16 + 8 + 2 * t) : 0u;
+            qf[ks][2] = valid_hi ? *reinterpret_cast<const uint32_t*>(qhi + ks * 16 + 2 * t) : 0u;
+            qf[ks][3] = valid_hi ? *reinterpret_cast<const uint32_t*>(qhi + ks * 16 + 8 + 2 * t) : 0u;
+        }
+    }
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;   // row g
+    float m_hi = -INFINITY, l_hi = 0.f;     // row g + 8
+    const uint32_t ring_addr = smem_u32(smem);
+    const int k_tok = ((lane >> 4) << 3) + (lane & 7), k_half = (lane >> 3) & 1;  // K ldmatrix
+    const int v_tok = (((lane >> 3) & 1) << 3) + (lane & 7), v_chunk = lane >> 4;  // V ldmatrix
+
+    for (int j = 0; j < n_pages; ++j) {
+        const int st = j % kDepth;
+        if (warp == 0 && j >= 1 && j + kDepth - 1 < n_pages) issue(j + kDepth - 1);   // into the stage page j - 1 used
+        if (!mbar_wait_bounded(&full_bar[st], (j / kDepth) & 1)) { failed = true; break; }
+        const int tok0 = first_tok + j * kPageTokens;
+        if (tok0 < w_len) {   // else no row of this warp sees the page (the later warps of the block do)
+            const uint32_t kb = ring_addr + st * kPageHeadBytes, vb = kb + kBlockBytes;
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t bf[4];
+                ldmatrix_x4(bf, kb + swz(k_tok, 2 * ks + k_half));
+                uint32_t a[4] = {qf[ks][0], qf[ks][2], qf[ks][1], qf[ks][3]};
+                mma_bf16_16816(s[0], a, bf[0], bf[1]);
+                mma_bf16_16816(s[1], a, bf[2], bf[3]);
+            }
+            float mx = -INFINITY, mxh = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int tok = tok0 + nt * 8 + 2 * t + e;
+                    float v = s[nt][e] * p.scale_log2;
+                    v = tok < len_lo ? v : -INFINITY;
+                    s[nt][e] = v;
+                    mx = fmaxf(mx, v);
+                    float u = s[nt][2 + e] * p.scale_log2;
+                    u = tok < len_hi ? u : -INFINITY;
+                    s[nt][2 + e] = u;
+                    mxh = fmaxf(mxh, u);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            mxh = fmaxf(mxh, __shfl_xor_sync(0xffffffffu, mxh, 1));
+            mxh = fmaxf(mxh, __shfl_xor_sync(0xffffffffu, mxh, 2));
+            // a row that sees nothing of this page keeps its maximum of -inf; 0 stands in for it in the exponents
+            const float m_new = fmaxf(m_run, mx), mh_new = fmaxf(m_hi, mxh);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new, mh_use = mh_new == -INFINITY ? 0.f : mh_new;
+            const float alpha = exp2f(m_run - m_use), alpha_hi = exp2f(m_hi - mh_use);
+            float pr[2][2], ph[2][2], psum = 0.f, ps = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    pr[nt][e] = exp2f(s[nt][e] - m_use);
+                    psum += pr[nt][e];
+                    ph[nt][e] = exp2f(s[nt][2 + e] - mh_use);
+                    ps += ph[nt][e];
+                }
+            l_run = l_run * alpha + psum;
+            m_run = m_new;
+            l_hi = l_hi * alpha_hi + ps;
+            m_hi = mh_new;
+            if (__any_sync(0xffffffffu, alpha != 1.f || alpha_hi != 1.f)) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { o[i][0] *= alpha; o[i][1] *= alpha; o[i][2] *= alpha_hi; o[i][3] *= alpha_hi; }
+            }
+            uint32_t pa[4] = {pack_bf16x2(pr[0][0], pr[0][1]), pack_bf16x2(ph[0][0], ph[0][1]),
+                              pack_bf16x2(pr[1][0], pr[1][1]), pack_bf16x2(ph[1][0], ph[1][1])};
+#pragma unroll
+            for (int np = 0; np < 8; ++np) {
+                uint32_t bf[4];
+                ldmatrix_x4_trans(bf, vb + swz(v_tok, 2 * np + v_chunk));
+                mma_bf16_16816(o[2 * np], pa, bf[0], bf[1]);
+                mma_bf16_16816(o[2 * np + 1], pa, bf[2], bf[3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[st]);
+    }
+    if (__any_sync(0xffffffffu, failed) && lane == 0) atomicExch(p.status, 1);
+
+    // ---- every warp finishes its own rows: g (values 0, 1 of a fragment) and g + 8 (values 2, 3) ----------------------
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = g + 8 * half;
+        const int tok = b + r / group;
+        const int row_len = half ? len_hi : len_lo;
+        if (tok >= p.T || first_tok >= row_len) continue;   // no such row, or this split holds nothing it may see
+        const int hq = h * group + r % group;
+        const int row_splits = (row_len + chunk_tokens - 1) / chunk_tokens;
+        const float M = half ? m_hi : m_run, L = half ? l_hi : l_run;
+        if (row_splits == 1) {
+            const float inv = 1.f / L;
+            __nv_bfloat16* dst = p.out + ((size_t)tok * p.Hq + hq) * kHD + 2 * t;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16x2(o[i][2 * half] * inv, o[i][2 * half + 1] * inv);
+        } else {
+            const size_t pi = ((size_t)tok * p.Hq + hq) * p.max_splits + split;
+            float* dst = p.part_o + pi * kHD + 2 * t;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][2 * half], o[i][2 * half + 1]);
+            if (t == 0) { p.part_ml[pi * 2] = M; p.part_ml[pi * 2 + 1] = L; }
+        }
+    }
+}
+
 // One CTA per (token, query head): merges the splits written by paged_attention_kernel.
 __global__ void __launch_bounds__(128) attention_combine_kernel(const AttnParams p) {
     const int b = blockIdx.x, hq = blockIdx.y, c = threadIdx.x;
@@ -491,7 +681,7 @@ int gptrs_cuda_rope_kv_append(const void* d_qkv, const int32_t* d_positions, con
     return launch_kernel(rope_append_kernel, grid, dim3(64), 0, as_stream(stream), 1, p);
 }
 
-static int paged_attention_launch(bool multi, const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+static int paged_attention_launch(int multi, const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
                                   int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
                                   void* d_out, void* d_scratch, size_t scratch_bytes, int32_t* d_status,
                                   int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
@@ -532,11 +722,13 @@ static int paged_attention_launch(bool multi, const void* d_q, const void* d_kv_
         GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_attention_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kAttnWarps * 2 * kPageHeadBytes));
     }
-    const size_t smem = (size_t)kAttnWarps * (multi ? 2 : depth) * kPageHeadBytes;
-    void (*attn_kernel)(AttnParams) = multi ? paged_attention_kernel<2, true>
-                                            : (depth == 3 ? paged_attention_kernel<3, false> : paged_attention_kernel<2, false>);
+    constexpr int kBlockDepth = 4;
+    const size_t smem = multi == 2 ? (size_t)kBlockDepth * kPageHeadBytes : (size_t)kAttnWarps * (multi ? 2 : depth) * kPageHeadBytes;
+    void (*attn_kernel)(AttnParams) = multi == 2 ? paged_attention_block_kernel<kBlockDepth>
+                                      : multi  ? paged_attention_kernel<2, true>
+                                               : (depth == 3 ? paged_attention_kernel<3, false> : paged_attention_kernel<2, false>);
     const int group = (int)(n_q_heads / n_kv_heads);
-    const int tq = multi ? 16 / group : 1;  // token rows per CTA
+    const int tq = multi == 2 ? kAttnWarps * (16 / group) : multi ? 16 / group : 1;  // token rows per CTA
     p.fixed_chunks = multi ? 1 : 0;
     cudaStream_t st = as_stream(stream);
     // tokens beyond 65535 go through blockIdx.z in slabs
@@ -569,7 +761,7 @@ int gptrs_cuda_paged_attention_decode(const void* d_q, const void* d_kv_pool, co
                                       int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
                                       int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
                                       void* stream) {
-    return paged_attention_launch(false, d_q, d_kv_pool, d_page_table, max_pages, d_slot, d_ctx_len, d_out, d_scratch,
+    return paged_attention_launch(0, d_q, d_kv_pool, d_page_table, max_pages, d_slot, d_ctx_len, d_out, d_scratch,
                                   scratch_bytes, d_status, n_tokens, n_q_heads, n_kv_heads, head_dim, max_ctx_len,
                                   chunk_pages, stream);
 }
@@ -586,7 +778,23 @@ int gptrs_cuda_paged_attention_prefill(const void* d_q, const void* d_kv_pool, c
         return fail(GPTRS_UNIMPLEMENTED, "paged_attention_prefill needs a GQA group of 1, 2, 4 or 8 query heads");
     // splits of a slab of 65535 CTAs along z would break the grouping of token rows
     GPTRS_REQUIRE(n_tokens <= 65535, "at most 65535 token rows per call");
-    return paged_attention_launch(true, d_q, d_kv_pool, d_page_table, max_pages, d_slot, d_ctx_len, d_out, d_scratch,
+    return paged_attention_launch(1, d_q, d_kv_pool, d_page_table, max_pages, d_slot, d_ctx_len, d_out, d_scratch,
+                                  scratch_bytes, d_status, n_tokens, n_q_heads, n_kv_heads, head_dim, max_ctx_len,
+                                  chunk_pages, stream);
+}
+
+int gptrs_cuda_paged_attention_prefill_blocks(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                              int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                              void* d_out, void* d_scratch, size_t scratch_bytes, int32_t* d_status,
+                                              int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
+                                              int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
+                                              void* stream) {
+    GPTRS_REQUIRE(n_kv_heads > 0 && n_q_heads % n_kv_heads == 0, "bad head counts");
+    const int64_t group = n_q_heads / n_kv_heads;
+    if (group != 1 && group != 2 && group != 4 && group != 8)
+        return fail(GPTRS_UNIMPLEMENTED, "paged_attention_prefill_blocks needs a GQA group of 1, 2, 4 or 8 query heads");
+    GPTRS_REQUIRE(n_tokens <= 65535, "at most 65535 token rows per call");
+    return paged_attention_launch(2, d_q, d_kv_pool, d_page_table, max_pages, d_slot, d_ctx_len, d_out, d_scratch,
                                   scratch_bytes, d_status, n_tokens, n_q_heads, n_kv_heads, head_dim, max_ctx_len,
                                   chunk_pages, stream);
 }

@@ -181,7 +181,7 @@ def rope_kv_append(qkv, positions, slot, page_table, cos, sin, rotary_dim, kv_po
 def paged_attention_decode(q, kv_pool, page_table, slot, ctx_len, n_q, n_kv, max_ctx_len, head_dim=128,
                            chunk_pages=None, status=None, prefill=False):
     """q bf16 [T][Hq][hd] -> out bf16 [T][Hq*hd]. prefill=True uses the prefill-chunk entry point (aligned groups
-    of 16 / (Hq / Hkv) rows must belong to one sequence)."""
+    of 16 / (Hq / Hkv) rows must belong to one sequence); prefill="blocks" the one that takes aligned blocks of four such groups."""
     t = q.shape[0]
     if chunk_pages is None:
         chunk_pages = lib().gptrs_cuda_attention_chunk_pages(max_ctx_len, t, n_kv)
@@ -190,7 +190,8 @@ def paged_attention_decode(q, kv_pool, page_table, slot, ctx_len, n_q, n_kv, max
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
     out = torch.empty((t, n_q * head_dim), dtype=torch.bfloat16, device=q.device)
-    fn = lib().gptrs_cuda_paged_attention_prefill if prefill else lib().gptrs_cuda_paged_attention_decode
+    fn = (lib().gptrs_cuda_paged_attention_prefill_blocks if prefill == "blocks" else lib().gptrs_cuda_paged_attention_prefill if prefill
+          else lib().gptrs_cuda_paged_attention_decode)
     check(fn(_ptr(q), _ptr(kv_pool), _ptr(page_table), page_table.shape[1], _ptr(slot), _ptr(ctx_len), _ptr(out),
              _ptr(scratch), nbytes, _ptr(status), t, n_q, n_kv, head_dim, max_ctx_len, chunk_pages, _stream()))
     return out, status

@@ -236,6 +236,16 @@ int gptrs_cuda_paged_attention_prefill(const void* d_q, const void* d_kv_pool, c
                                        int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
                                        void* stream);
 
+/* The same for rows that come in aligned BLOCKS of 4 * 16 / (n_q_heads / n_kv_heads) consecutive rows of one sequence (16
+ * tokens at a GQA group of 4; the last block may be short): a CTA takes a whole block, its four warps own a group of rows
+ * each and share one stream of K/V pages, so the pages are read once per block. */
+int gptrs_cuda_paged_attention_prefill_blocks(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                              int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                              void* d_out, void* d_scratch, size_t scratch_bytes, int32_t* d_status,
+                                              int64_t n_tokens, int64_t n_q_heads, int64_t n_kv_heads,
+                                              int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
+                                              void* stream);
+
 /* Allocation-free variant of gptrs_cuda_paged_attention_decode. It has no counterpart in gpt.rs.
  * It exists for callers that cannot allocate device memory themselves: a plugin inside a serving
  * process whose device memory pool belongs to the host application, or a caller that is in the

@@ -221,3 +221,34 @@ def test_context_length_above_the_launch_bound_is_clamped_and_flagged(cuda):
     want = _oracle_decode(stored[:1], lens[:1], n_q, n_kv, [q[0].float().cpu().numpy()])
     assert np.max(np.abs(out[0].float().cpu().numpy() - want[0])) <= 2e-2   # the well-formed row is unaffected
     assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.parametrize("l,n_q,n_kv,chunk", [(90, 8, 2, None), (131, 32, 8, 4), (300, 32, 8, 8), (70, 4, 4, None), (200, 16, 2, 4), (37, 8, 1, None), (16, 32, 8, None)])
+def test_prefill_blocks_entry_point(cuda, l, n_q, n_kv, chunk):
+    """gptrs_cuda_paged_attention_prefill_blocks: a CTA takes an aligned block of four row groups (16 tokens at a group of
+    four) of one sequence and streams the pages once for it. Same results as the one-row-per-CTA entry point and the
+    oracle: row counts that are not a multiple of the block, rows whose visible length ends in different splits, more
+    pages than the ring has stages, and a second sequence whose rows start at a block boundary."""
+    rng = np.random.default_rng(l * 5 + n_q)
+    l2 = 21
+    table, pool = _setup(rng, [l, l2], n_q, n_kv, cuda)
+    stored, q_rots, table_d = _fill(rng, [l, l2], n_q, n_kv, table, pool, cuda)
+    blk = 4 * (16 // (n_q // n_kv))
+    pad = (-l) % blk  # rows of sequence 1 must start a new block: repeat the last row of sequence 0
+    q = torch.cat([q_rots[0], q_rots[0][-1:].repeat(pad, 1, 1), q_rots[1]]).contiguous()
+    slot = torch.tensor([0] * (l + pad) + [1] * l2, dtype=torch.int32, device=cuda)
+    ctx = torch.tensor(list(range(1, l + 1)) + [l] * pad + list(range(1, l2 + 1)), dtype=torch.int32, device=cuda)
+    ref, st0 = ops.paged_attention_decode(q, pool, table_d, slot, ctx, n_q, n_kv, l, chunk_pages=chunk)
+    out, st1 = ops.paged_attention_decode(q, pool, table_d, slot, ctx, n_q, n_kv, l, chunk_pages=chunk, prefill="blocks")
+    torch.cuda.synchronize()
+    assert int(st0.item()) == 0 and int(st1.item()) == 0
+    got, base = out.float().cpu().numpy(), ref.float().cpu().numpy()
+    assert np.max(np.abs(got - base)) <= 8e-3, np.max(np.abs(got - base))  # both round to bf16 from slightly different sums
+    k_ref, v_ref, _ = stored[0]
+    for t in sorted({0, 1, 3, 4, 15, 16, 17, 63, 64, 65, l - 2, l - 1} & set(range(l))):
+        want = _oracle_decode([(k_ref[:t + 1], v_ref[:t + 1], None)], [t + 1], n_q, n_kv, [q[t].float().cpu().numpy()])
+        assert np.max(np.abs(got[t] - want[0])) <= 2e-2, t
+    k2, v2, _ = stored[1]
+    for t in (0, 5, l2 - 1):
+        want = _oracle_decode([(k2[:t + 1], v2[:t + 1], None)], [t + 1], n_q, n_kv, [q[l + pad + t].float().cpu().numpy()])
+        assert np.max(np.abs(got[l + pad + t] - want[0])) <= 2e-2, t
