@@ -903,7 +903,11 @@ UmmaPlan plan_umma(const MatmulParams& p, int small_tile_ctas_per_sm) {
     if (pct == 0) { const char* e = getenv("GPTRS_UMMA_CTAS_PCT"); pct = e ? atoi(e) : 250; if (pct <= 0) pct = 250; }
     // Row tile: 256 rows when that alone fills the GPU, otherwise tiles of up to 128 rows with a K split over what
     // is left of the SMs.
-    pl.big_tile = p.M > 128 && pl.n_blocks * ceil_div(p.M, 256) >= sm_count();
+    // (a wave that leaves SMs idle beats twice as many half-height tiles that each dequantise the weights again: 24 column
+    // tiles x 6 row tiles = 144 CTAs on 148 SMs; measured best with the threshold at 50-60 % of the SMs: 8 x 2048 prompt
+    // tokens prefill in 170 ms, 174 ms at 85 %, 190 ms when a full wave was demanded)
+    static const int big_pct = [] { const char* e = getenv("GPTRS_UMMA_BIG_TILE_PCT"); const int v = e ? atoi(e) : 55; return v > 0 ? v : 55; }();
+    pl.big_tile = p.M > 128 && pl.n_blocks * ceil_div(p.M, 256) * 100 >= sm_count() * big_pct;
     pl.m_blocks = pl.big_tile ? ceil_div(p.M, 256) : ceil_div(p.M, 128);
     // tiles of up to 64 rows fit two CTAs per SM, the 128-row tile one: never more CTAs than one wave of those
     const int ctas = p.M <= 64 ? sm_count() * pct / 100 : sm_count();
