@@ -42,6 +42,8 @@ __global__ void rope_f32_kernel(const RopeParams p) {
 
 struct CopyColsParams { const float* src; float* dst; int64_t rows, cols, src_stride, dst_stride; };
 __global__ void copy_cols_kernel(const CopyColsParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.rows * p.cols) return;
     const int64_t r = i / p.cols, c = i % p.cols;
@@ -54,6 +56,8 @@ struct PresentParams {
     int T, Hq, Hkv, hd, l0;
 };
 __global__ void present_kv_kernel(const PresentParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     const int64_t total = p.l0 + p.T;
     const int64_t n = (int64_t)p.Hkv * total * p.hd;
     const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -139,6 +143,8 @@ struct DequantParams {
     int transposed;  // != 0: destination is [N][K]; 0: the Linear layout [K][N]
 };
 __global__ void dequantize_kernel(const DequantParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n * p.k) return;
     const int64_t row = i / p.k, col = i % p.k;  // row = output channel, col = input channel

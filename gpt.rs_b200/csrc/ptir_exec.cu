@@ -45,6 +45,8 @@ struct CopyParams {
 
 template <typename T>
 __global__ void strided_copy_kernel(const CopyParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n) return;
     int64_t dyn = 0;
@@ -71,6 +73,8 @@ enum { C_LT, C_LE, C_EQ, C_GE, C_GT, C_NE };
 struct EwParams { const void* a; const void* b; const void* c; void* out; int64_t n; int op; int is_int; };
 
 __global__ void unary_kernel(const EwParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n) return;
     if (p.is_int) {
@@ -93,6 +97,8 @@ __global__ void unary_kernel(const EwParams p) {
 }
 
 __global__ void binary_kernel(const EwParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n) return;
     if (p.is_int) {
@@ -121,6 +127,8 @@ __global__ void binary_kernel(const EwParams p) {
 }
 
 __global__ void compare_kernel(const EwParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n) return;
     bool r;
@@ -135,6 +143,8 @@ __global__ void compare_kernel(const EwParams p) {
 }
 
 __global__ void select_kernel(const EwParams p) {  // a: pred (u8), b / c: 4-byte values
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n) return;
     static_cast<uint32_t*>(p.out)[i] = static_cast<const uint8_t*>(p.a)[i] ? static_cast<const uint32_t*>(p.b)[i]
@@ -144,6 +154,8 @@ __global__ void select_kernel(const EwParams p) {  // a: pred (u8), b / c: 4-byt
 // op: 0 f32->si32 (truncate, saturate, NaN -> 0), 1 si32->f32, 2 i1->f32, 3 i1->si32, 4 f32->i1, 5 si32->i1,
 //     6 f32->bf16, 7 bf16->f32, 8 f32->f16, 9 f16->f32 (round to nearest even)
 __global__ void cast_kernel(const EwParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n) return;
     switch (p.op) {
@@ -168,6 +180,8 @@ __global__ void cast_kernel(const EwParams p) {
 struct ReduceParams { const void* in; void* out; int64_t outer, axis, inner; int kind; int is_int; };
 // One warp per (outer, inner) pair; lanes stride over the reduced axis.
 __global__ void reduce_kernel(const ReduceParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t w = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (w >= p.outer * p.inner) return;
@@ -206,6 +220,8 @@ struct DotParams {
     int64_t a_sb, a_sm, a_sk, b_sb, b_sk, b_sn;
 };
 __global__ void dot_kernel(const DotParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.nb * p.m * p.n) return;
     const int64_t n = i % p.n, m = (i / p.n) % p.m, b = i / (p.n * p.m);
@@ -218,12 +234,16 @@ __global__ void dot_kernel(const DotParams p) {
 
 struct IotaParams { int* out; int64_t n, inner, dim; };
 __global__ void iota_kernel(const IotaParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i < p.n) p.out[i] = (int)((i / p.inner) % p.dim);
 }
 
 struct TakeParams { const uint32_t* w; const int* idx; uint32_t* out; int64_t n_idx, row, vocab; int* status; };
 __global__ void take_kernel(const TakeParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n_idx * p.row) return;
     const int64_t r = i / p.row, c = i % p.row;
@@ -234,6 +254,8 @@ __global__ void take_kernel(const TakeParams p) {
 
 struct GatherParams { const uint32_t* in; const int* idx; uint32_t* out; int64_t outer, axis_in, axis_out, inner; int* status; };
 __global__ void gather_kernel(const GatherParams p) {  // take_along_axis
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.outer * p.axis_out * p.inner) return;
     const int64_t in = i % p.inner, o = i / (p.inner * p.axis_out);
@@ -251,6 +273,8 @@ struct ReduceWindowParams {
     int kind;  // 0 sum, 1 max, 2 min
 };
 __global__ void reduce_window_kernel(const ReduceWindowParams p) {
+    pdl_launch_dependents();  // dependents still wait for this whole grid before reading its results
+    pdl_wait();
     const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= p.n_out) return;
     int o[4];
@@ -287,9 +311,8 @@ __global__ void reduce_window_kernel(const ReduceWindowParams p) {
 template <typename P>
 int launch_flat(void (*k)(P), int64_t n, const P& p, cudaStream_t st) {
     if (n <= 0) return GPTRS_OK;
-    k<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(p);
-    GPTRS_CUDA_OK(cudaGetLastError());
-    return GPTRS_OK;
+    // through the common launcher: under a recorded plan the launch carries the programmatic-dependent-launch attribute
+    return launch_kernel(k, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, 1, p);
 }
 
 std::vector<int64_t> row_major_strides(const std::vector<int64_t>& dims) {
@@ -1319,6 +1342,7 @@ int run_instructions(Plan& pl, gptrs_tensor* const* inputs, size_t n_inputs, gpt
 }
 
 std::atomic<int> g_plan_graphs{1};   // gptrs_cuda_set_plan_graphs
+std::atomic<int> g_plan_graph_pdl{[] { const char* e = getenv("GPTRS_PLAN_GRAPH_PDL"); return (e && e[0] == '0') ? 0 : 1; }()};
 thread_local int64_t g_last_graph_replays = 0;
 
 // Replay: take the results from the pool in the recorded order; launch the graph whose blocks they are.
@@ -1354,7 +1378,13 @@ bool capture_run(Plan& pl, gptrs_tensor* const* inputs, size_t n_inputs, gptrs_t
     std::vector<Tensor*> record;
     if (cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed) != cudaSuccess) { cudaGetLastError(); return false; }
     g_alloc_record = &record;
+    // recorded with programmatic dependent launch edges, like the engine's decode step: every kernel of the library waits
+    // (griddepcontrol.wait) before it reads what its predecessor wrote, so set-up and scheduling of a kernel overlap the
+    // one in front
+    const int pdl_before = g_use_pdl;
+    g_use_pdl = g_plan_graph_pdl.load(std::memory_order_relaxed) ? 1 : pdl_before;
     int rc = run_instructions(pl, inputs, n_inputs, outputs, st, launches);
+    g_use_pdl = pdl_before;
     g_alloc_record = nullptr;
     cudaGraph_t graph = nullptr;
     cudaError_t e = cudaStreamEndCapture(st, &graph);
