@@ -662,6 +662,33 @@ void rewrite_pass(Plan& pl, bool rms_pass) {
             }
             if (done) continue;
         }
+        // ---- gelu (erf form, activation.rs:96-113): Mul(Mul(x, 0.5), Add(Erf(Div(x, sqrt 2)), 1)), operands either way ----
+        if (is_bin(&in, "Mul") && in.out.dtype == GPTRS_F32) {
+            bool done = false;
+            for (int sw = 0; sw < 2 && !done; ++sw) {
+                const Inst* half = def_of(pl, in.operands[sw]);
+                const Inst* onep = def_of(pl, in.operands[1 - sw]);
+                if (!is_bin(half, "Mul") || !is_bin(onep, "Add")) continue;
+                for (int sw2 = 0; sw2 < 2 && !done; ++sw2) {
+                    float c05, c1, c2;
+                    if (half->operands[sw2].is_literal || !scalar_literal(pl, half->operands[1 - sw2], &c05) || c05 != 0.5f) continue;
+                    const Operand& x = half->operands[sw2];
+                    for (int sw3 = 0; sw3 < 2 && !done; ++sw3) {
+                        const Inst* erf = def_of(pl, onep->operands[sw3]);
+                        if (!is_un(erf, "Erf") || !scalar_literal(pl, onep->operands[1 - sw3], &c1) || c1 != 1.f) continue;
+                        const Inst* div = def_of(pl, erf->operands[0]);
+                        if (!is_bin(div, "Div") || !same_val(div->operands[0], x) || !scalar_literal(pl, div->operands[1], &c2) ||
+                            fabsf(c2 - 1.4142135f) > 1e-6f)
+                            continue;
+                        Inst f = in;
+                        f.op = Op::FusedGelu;
+                        f.operands = {x};
+                        in = f; ++pl.fused; done = true;
+                    }
+                }
+            }
+            if (done) continue;
+        }
         // ---- softmax over the last axis: Div(e, bcast(ReduceSum(e))), e = Exp(Sub(z, bcast(ReduceMax(z))))
         if (is_bin(&in, "Div")) {
             const Inst* e = def_of(pl, in.operands[0]);
@@ -680,6 +707,18 @@ void rewrite_pass(Plan& pl, bool rms_pass) {
             f.operands = {sub->operands[0]};
             in = f; ++pl.fused;
         }
+    }
+    sweep_dead(pl);
+    // gelu of a matmul + bias that nothing else reads: the activation moves into the matmul's epilogue
+    for (auto& in : pl.fn.body) {
+        if (in.dead || in.op != Op::FusedGelu) continue;
+        const Inst* mm = def_of(pl, in.operands[0]);
+        if (!mm || mm->dead || mm->op != Op::FusedMatmulBias || mm->axis == 1 || uses_of(pl, mm->id) != 1) continue;
+        Inst f = in;
+        f.op = Op::FusedMatmulBias;
+        f.axis = 1;
+        f.operands = mm->operands;
+        in = f;
     }
     sweep_dead(pl);
 }
@@ -1137,11 +1176,18 @@ int exec_inst(Exec& ex, const Inst& in, std::vector<Tensor*>& ops, Tensor** resu
             rc = gptrs_cuda_softmax_last_dim(static_cast<const float*>(ops[0]->data), static_cast<float*>(out->data), n_out / d, d, ex.st);
             break;
         }
-        case Op::FusedMatmulBias: {
+        case Op::FusedGelu: {
+            if ((rc = alloc_out())) return rc;
+            ++ex.launches;
+            rc = gptrs_cuda_gelu(static_cast<const float*>(ops[0]->data), static_cast<float*>(out->data), n_out, ex.st);
+            break;
+        }
+        case Op::FusedMatmulBias: {   // in.axis = 1: GELU on the sum
             if ((rc = alloc_out())) return rc;
             ++ex.launches;
             rc = gptrs_cuda_matmul_f32(static_cast<const float*>(ops[0]->data), static_cast<const float*>(ops[1]->data), static_cast<float*>(out->data),
-                                       ops[0]->dims[0], ops[1]->dims[1], ops[0]->dims[1], static_cast<const float*>(ops[2]->data), nullptr, 0, ex.st);
+                                       ops[0]->dims[0], ops[1]->dims[1], ops[0]->dims[1], static_cast<const float*>(ops[2]->data), nullptr,
+                                       in.axis == 1 ? 1 : 0, ex.st);
             break;
         }
         case Op::FusedAttentionDecode: {
@@ -1614,6 +1660,7 @@ Json fused_instruction_json(const Inst& in) {
     // CustomCallAttr is adjacently tagged (#[serde(tag = "kind", content = "value")], spec.rs:602-613)
     if (in.op == Op::FusedLayerNorm || in.op == Op::FusedRmsNorm || in.op == Op::FusedAddRmsNorm || in.op == Op::FusedAddLayerNorm)
         attrs.push_back({"eps", jobj({{"kind", jstr("F64")}, {"value", jnum((double)in.f0)}})});
+    if (in.op == Op::FusedMatmulBias && in.axis == 1) attrs.push_back({"activation", jobj({{"kind", jstr("String")}, {"value", jstr("gelu")}})});
     if (in.op == Op::FusedQuantMatmul) attrs.push_back({"group_size", jobj({{"kind", jstr("I64")}, {"value", jnum(in.sub == "w4" ? 128 : 0)}})});
     if (in.op == Op::FusedAttentionDecode) {
         std::vector<Json> g;

@@ -215,6 +215,7 @@ const char* fused_target(Op op) {
         case Op::FusedAttentionDecode: return "gpt_rs.cuda.attention_decode.f32.v1";
         case Op::FusedAddRmsNorm: return "gpt_rs.cuda.add_rms_norm.f32.v1";
         case Op::FusedAddLayerNorm: return "gpt_rs.cuda.add_layer_norm.f32.v1";
+        case Op::FusedGelu: return "gpt_rs.cuda.gelu.f32.v1";
         default: return nullptr;
     }
 }
@@ -340,10 +341,10 @@ int build_function(const Json& program, Function* fn, std::string* err) {
                 in.sub = in.sub == "gpt_rs.cuda.quant_matmul_w8a16.v1" ? "w8" : "w4";
             }
             for (Op f : {Op::FusedLayerNorm, Op::FusedRmsNorm, Op::FusedSoftmax, Op::FusedMatmulBias, Op::FusedAttentionDecode, Op::FusedAddRmsNorm,
-                         Op::FusedAddLayerNorm}) {
+                         Op::FusedAddLayerNorm, Op::FusedGelu}) {
                 if (in.op != Op::CustomCall || in.sub != fused_target(f)) continue;
                 const size_t want = f == Op::FusedLayerNorm || f == Op::FusedMatmulBias || f == Op::FusedAddRmsNorm ? 3
-                                    : f == Op::FusedRmsNorm ? 2 : f == Op::FusedSoftmax ? 1 : 4;
+                                    : f == Op::FusedRmsNorm ? 2 : (f == Op::FusedSoftmax || f == Op::FusedGelu) ? 1 : 4;
                 if (in.operands.size() != want) { *err = in.sub + ": wrong operand count"; return 1; }
                 in.op = f;
                 if (f == Op::FusedLayerNorm || f == Op::FusedRmsNorm || f == Op::FusedAddRmsNorm || f == Op::FusedAddLayerNorm) {
@@ -351,6 +352,14 @@ int build_function(const Json& program, Function* fn, std::string* err) {
                     const Json* v = attr_value(e, "F64");
                     if (!v || v->kind != Json::Number) { *err = in.sub + ": attribute eps (F64) is required"; return 1; }
                     in.f0 = (float)v->num;
+                }
+                if (f == Op::FusedMatmulBias) {   // optional: the activation applied to the sum ("gelu")
+                    const Json* a = attrs ? attrs->get("activation") : nullptr;
+                    const Json* v = attr_value(a, "String");
+                    if (v && v->kind == Json::String) {
+                        if (v->str != "gelu") { *err = in.sub + ": unknown activation '" + v->str + "'"; return 1; }
+                        in.axis = 1;
+                    }
                 }
                 if (f == Op::FusedAttentionDecode) {
                     const Json* g = attrs ? attrs->get("geometry") : nullptr;

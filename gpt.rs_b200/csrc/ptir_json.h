@@ -37,7 +37,7 @@ enum class Op {
     Slice, Concat, Iota, Take, Gather, DynamicSlice, DynamicUpdateSlice, ReduceWindow, Dequantize, CustomCall,
     // produced by the fusion rewrites of this backend
     FusedLayerNorm, FusedRmsNorm, FusedSoftmax, FusedMatmulBias, FusedAttentionDecode, FusedAddRmsNorm, FusedAddLayerNorm,
-    FusedQuantMatmul, Unsupported
+    FusedQuantMatmul, FusedGelu, Unsupported
 };
 
 struct TSpec {

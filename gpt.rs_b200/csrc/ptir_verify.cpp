@@ -253,6 +253,7 @@ int verify_function(const Function& fn, std::string* err) {
                 rc = expect_out(GPTRS_F32, s[0]->dims);
                 break;
             }
+            case Op::FusedGelu:
             case Op::FusedSoftmax:
                 if (!arity(1)) return bad("wrong operand count");
                 if (s[0]->dims.empty() || s[0]->dtype != GPTRS_F32) return bad("f32 rows expected");

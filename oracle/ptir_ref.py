@@ -273,7 +273,15 @@ def _cuda_custom_call(attr, ins, out_dims):
     if target == "gpt_rs.cuda.softmax_last_axis.f32.v1":
         return fr.softmax_last_dim(ins[0])
     if target == "gpt_rs.cuda.matmul_bias.f32.v1":
-        return fr.linear(ins[0], ins[1], ins[2])
+        y = fr.linear(ins[0], ins[1], ins[2])
+        act = attrs.get("activation")
+        if act is not None:
+            if act.get("value") != "gelu":
+                raise PtirError(f"unknown activation {act!r}")
+            y = fr.gelu(y)
+        return y
+    if target == "gpt_rs.cuda.gelu.f32.v1":
+        return fr.gelu(ins[0])
     if target == "gpt_rs.cuda.attention_decode.f32.v1":
         hq, hkv, hd, cap = val("geometry", "I64Array")
         q, k, v = ins[0].reshape(hq, 1, hd), ins[1], ins[2]

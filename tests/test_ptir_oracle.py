@@ -200,7 +200,11 @@ def test_pipeline_fuse_rewrites_to_custom_calls(kind):
     # each layer's softmax rewrite is absorbed by the attention rewrite that follows it, and the last block's residual add
     # is folded into the final norm (a rewrite of an already rewritten norm; the other sums stay: they are read again)
     folded = sum(t.startswith("gpt_rs.cuda.add_") for t in targets)
-    assert folded == 1 and len(targets) == n_fused - cfg.n_layers - folded
+    # ... and a GPT block's gelu rewrite is absorbed by the matmul + bias in front of it (attribute activation = "gelu")
+    gelus = [i for i in body1 if isinstance(i["op"], dict) and "CustomCall" in i["op"]
+             and i["op"]["CustomCall"]["attrs"].get("activation") == {"kind": "String", "value": "gelu"}]
+    assert len(gelus) == (cfg.n_layers if kind == "gpt" else 0)
+    assert folded == 1 and len(targets) == n_fused - cfg.n_layers - folded - len(gelus)
     assert all(t.startswith("gpt_rs.cuda.") and t.endswith(".f32.v1") for t in targets)
     assert targets.count("gpt_rs.cuda.attention_decode.f32.v1") == cfg.n_layers
     norm = "gpt_rs.cuda.layer_norm.f32.v1" if kind == "gpt" else "gpt_rs.cuda.rms_norm.f32.v1"

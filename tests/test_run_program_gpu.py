@@ -92,7 +92,34 @@ def test_functional_sequences(be, fusion):
     for a, e in zip(got, want):
         assert np.allclose(a, e, rtol=1e-4, atol=1e-5)
     st = be.run_program_stats()
-    assert (st["last_fused"] == 4) if fusion else (st["last_fused"] == 0)
+    assert (st["last_fused"] == 5) if fusion else (st["last_fused"] == 0)   # both norms, softmax, gelu, matmul + bias
+
+
+def test_gelu_moves_into_the_matmul_epilogue(be):
+    """gelu(x @ w + bias) whose sum nothing else reads runs as ONE launch; with a second reader of the sum the gelu
+    stays a launch of its own. The serialized form carries the activation as an attribute of the matmul CustomCall."""
+    rng = np.random.default_rng(21)
+    x = rng.uniform(-1, 1, size=(3, 64)).astype(np.float32)
+    w = rng.uniform(-1, 1, size=(64, 96)).astype(np.float32)
+    bias = rng.uniform(-1, 1, size=96).astype(np.float32)
+    for keep_sum, launches in ((False, 1), (True, 2)):
+        b = ptir.Builder()
+        px, pw, pb = (b.parameter(F32, list(a.shape)) for a in (x, w, bias))
+        y = ptir.linear(px, pw, pb)
+        b.set_results([ptir.gelu(y), y] if keep_sum else [ptir.gelu(y)])
+        got, want = _both(be, b, [x, w, bias], True)
+        for a, e in zip(got, want):
+            assert np.allclose(a, e, rtol=1e-4, atol=1e-5)
+        st = be.run_program_stats()
+        assert st["last_fused"] == 2 and st["last_launches"] == launches, st
+        text, n = be.pipeline_fuse(b.to_json())
+        calls = [i["op"]["CustomCall"] for i in json.loads(text)["functions"][0]["body"] if isinstance(i["op"], dict) and "CustomCall" in i["op"]]
+        assert n == 2 and len(calls) == launches
+        assert (calls[0]["attrs"].get("activation") == {"kind": "String", "value": "gelu"}) == (not keep_sum)
+        assert all(np.allclose(a, e, rtol=1e-4, atol=1e-5) for a, e in zip(pr.run_program(json.loads(text), [x, w, bias]), want))
+        again = [be.to_literal(h) for h in be.run_program(text, [be.materialize(a) for a in (x, w, bias)])]
+        for a, e in zip(again, want):
+            assert np.allclose(a, e, rtol=1e-4, atol=1e-5)
 
 
 def test_fusion_reduces_launches_and_keeps_escaping_values(be):
