@@ -589,6 +589,10 @@ int enqueue_forward(Model& m, int T, int max_ctx, int chunk_pages, int n_rows, b
                                                    c.n_q_heads, c.n_kv_heads, c.head_dim, c.context_length, ln.st);
         }
         unsigned char* pool = m.kv_pool.as<unsigned char>() + (size_t)l * m.pool_layer_bytes;
+        if (prefill_groups == 3)   // tensor cores: one CTA per tile of rows and kv head, never split along the keys
+            return gptrs_cuda_paged_attention_prefill_tc(at(m.q_rot, (size_t)m.QD() * 2, ln), pool, m.d_page_table.as<int32_t>(), c.max_pages_per_seq,
+                                                         ints(m.d_slot, ln), ints(m.d_ctx, ln), out, m.d_status.as<int32_t>(), ln.T, c.n_q_heads,
+                                                         c.n_kv_heads, c.head_dim, ln.st);
         const int splits = (max_ctx + ln.chunk * kPage - 1) / (ln.chunk * kPage);
         if (splits > 1) ++m.launches;
         // In a two-lane step the projections of the other lane outrank attention CTAs that wait for an SM.
@@ -1210,7 +1214,14 @@ int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* h, const int32_t* h_
             static const bool blocks_on = [] { const char* e = getenv("GPTRS_PREFILL_BLOCKS"); return e && atoi(e) != 0; }();
             for (int i = 0; i < T && groups; ++i) groups = h_slots[i] == h_slots[i - i % tq];
             for (int i = 0; i < T && blocks; ++i) blocks = h_slots[i] == h_slots[i - i % (4 * tq)];
-            if (blocks && blocks_on && T >= 4 * tq) { prefill_groups = 2; attn_rows = (T + 4 * tq - 1) / (4 * tq); }
+            // Default for chunks of at least four tiles: the tensor-core kernel, when every aligned tile of 128 / grp rows is
+            // one sequence (GPTRS_PREFILL_TC=0 keeps the grouped kernel).
+            static const bool tc_on = [] { const char* e = getenv("GPTRS_PREFILL_TC"); return !e || atoi(e) != 0; }();
+            const int tile = 128 / grp;
+            bool tiles = tc_on && c.head_dim == 128 && T >= 4 * tile;
+            for (int i = 0; i < T && tiles; ++i) tiles = h_slots[i] == h_slots[i - i % tile];
+            if (tiles) { prefill_groups = 3; attn_rows = (T + tile - 1) / tile; }
+            else if (blocks && blocks_on && T >= 4 * tq) { prefill_groups = 2; attn_rows = (T + 4 * tq - 1) / (4 * tq); }
             else if (groups) { prefill_groups = 1; attn_rows = (T + tq - 1) / tq; }
         }
     }

@@ -181,8 +181,16 @@ def rope_kv_append(qkv, positions, slot, page_table, cos, sin, rotary_dim, kv_po
 def paged_attention_decode(q, kv_pool, page_table, slot, ctx_len, n_q, n_kv, max_ctx_len, head_dim=128,
                            chunk_pages=None, status=None, prefill=False):
     """q bf16 [T][Hq][hd] -> out bf16 [T][Hq*hd]. prefill=True uses the prefill-chunk entry point (aligned groups
-    of 16 / (Hq / Hkv) rows must belong to one sequence); prefill="blocks" the one that takes aligned blocks of four such groups."""
+    of 16 / (Hq / Hkv) rows must belong to one sequence); prefill="blocks" the one that takes aligned blocks of four such groups;
+    prefill="tc" the tensor-core (tcgen05) kernel that takes aligned tiles of 128 / (Hq / Hkv) rows of one sequence."""
     t = q.shape[0]
+    if prefill == "tc":
+        if status is None:
+            status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        out = torch.empty((t, n_q * head_dim), dtype=torch.bfloat16, device=q.device)
+        check(lib().gptrs_cuda_paged_attention_prefill_tc(_ptr(q), _ptr(kv_pool), _ptr(page_table), page_table.shape[1], _ptr(slot),
+                                                          _ptr(ctx_len), _ptr(out), _ptr(status), t, n_q, n_kv, head_dim, _stream()))
+        return out, status
     if chunk_pages is None:
         chunk_pages = lib().gptrs_cuda_attention_chunk_pages(max_ctx_len, t, n_kv)
     nbytes = lib().gptrs_cuda_attention_scratch_bytes(t, n_q, max_ctx_len, chunk_pages)

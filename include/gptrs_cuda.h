@@ -246,6 +246,18 @@ int gptrs_cuda_paged_attention_prefill_blocks(const void* d_q, const void* d_kv_
                                               int64_t head_dim, int64_t max_ctx_len, int64_t chunk_pages,
                                               void* stream);
 
+/* The same prefill attention on the tcgen05 tensor cores (accumulators in tensor memory, K/V pages brought in by TMA
+ * tensor copies): a CTA takes 128 / (n_q_heads / n_kv_heads) consecutive rows (32 tokens at a GQA group of 4) x the query
+ * heads of one kv head and walks the visible keys in blocks of 128, so the rows must come in aligned TILES of that many
+ * rows of one sequence (the last tile may be short; a row whose slot differs from its tile's first row gets code 2 in
+ * *d_status and no output). No scratch: a tile is never split along the keys. q, out and the pool must be 16-byte aligned.
+ * Waits are bounded (code 3 in *d_status on a timeout). Replaces functional::attention on the prompt
+ * (crates/gpt-rs/src/ops/functional/attention.rs:337-541) together with gptrs_cuda_rope_kv_append. */
+int gptrs_cuda_paged_attention_prefill_tc(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
+                                          int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
+                                          void* d_out, int32_t* d_status, int64_t n_tokens, int64_t n_q_heads,
+                                          int64_t n_kv_heads, int64_t head_dim, void* stream);
+
 /* Allocation-free variant of gptrs_cuda_paged_attention_decode. It has no counterpart in gpt.rs.
  * It exists for callers that cannot allocate device memory themselves: a plugin inside a serving
  * process whose device memory pool belongs to the host application, or a caller that is in the

@@ -252,3 +252,51 @@ def test_prefill_blocks_entry_point(cuda, l, n_q, n_kv, chunk):
     for t in (0, 5, l2 - 1):
         want = _oracle_decode([(k2[:t + 1], v2[:t + 1], None)], [t + 1], n_q, n_kv, [q[l + pad + t].float().cpu().numpy()])
         assert np.max(np.abs(got[l + pad + t] - want[0])) <= 2e-2, t
+
+
+@pytest.mark.parametrize("l,n_q,n_kv", [(90, 8, 2), (131, 32, 8), (300, 32, 8), (70, 4, 4), (200, 16, 2), (37, 8, 1), (16, 32, 8), (700, 32, 8), (128, 32, 8), (1, 32, 8)])
+def test_prefill_tensor_core_entry_point(cuda, l, n_q, n_kv):
+    """gptrs_cuda_paged_attention_prefill_tc (tcgen05 / tensor memory): a CTA takes an aligned tile of 128 / group rows of
+    one sequence and walks its visible keys in blocks of 128. Same results as the one-row-per-CTA entry point and the
+    oracle: row counts that are not a multiple of the tile, contexts of one, exactly one and several key blocks, a last
+    block whose tail pages are never loaded, and a second sequence whose rows start at a tile boundary."""
+    rng = np.random.default_rng(l * 7 + n_q)
+    l2 = 21
+    table, pool = _setup(rng, [l, l2], n_q, n_kv, cuda)
+    stored, q_rots, table_d = _fill(rng, [l, l2], n_q, n_kv, table, pool, cuda)
+    tile = 128 // (n_q // n_kv)
+    pad = (-l) % tile  # rows of sequence 1 must start a new tile: repeat the last row of sequence 0
+    q = torch.cat([q_rots[0], q_rots[0][-1:].repeat(pad, 1, 1), q_rots[1]]).contiguous()
+    slot = torch.tensor([0] * (l + pad) + [1] * l2, dtype=torch.int32, device=cuda)
+    ctx = torch.tensor(list(range(1, l + 1)) + [l] * pad + list(range(1, l2 + 1)), dtype=torch.int32, device=cuda)
+    ref, st0 = ops.paged_attention_decode(q, pool, table_d, slot, ctx, n_q, n_kv, l)
+    out, st1 = ops.paged_attention_decode(q, pool, table_d, slot, ctx, n_q, n_kv, l, prefill="tc")
+    torch.cuda.synchronize()
+    assert int(st0.item()) == 0 and int(st1.item()) == 0
+    got, base = out.float().cpu().numpy(), ref.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    # both round P and the result to bf16 from different sums: one bf16 step (2^-8 relative) at the value's magnitude
+    assert np.all(np.abs(got - base) <= 8e-3 * np.maximum(1.0, np.abs(base))), np.max(np.abs(got - base))
+    k_ref, v_ref, _ = stored[0]
+    for t in sorted({0, 1, 3, 4, 15, 16, 17, 63, 64, 65, 127, 128, 129, 255, 256, l - 2, l - 1} & set(range(l))):
+        want = _oracle_decode([(k_ref[:t + 1], v_ref[:t + 1], None)], [t + 1], n_q, n_kv, [q[t].float().cpu().numpy()])
+        assert np.max(np.abs(got[t] - want[0])) <= 2e-2, t
+    k2, v2, _ = stored[1]
+    for t in (0, 5, l2 - 1):
+        want = _oracle_decode([(k2[:t + 1], v2[:t + 1], None)], [t + 1], n_q, n_kv, [q[l + pad + t].float().cpu().numpy()])
+        assert np.max(np.abs(got[l + pad + t] - want[0])) <= 2e-2, t
+
+
+def test_prefill_tensor_core_flags_a_tile_of_two_sequences(cuda):
+    rng = np.random.default_rng(3)
+    n_q, n_kv = 8, 2
+    table, pool = _setup(rng, [20, 20], n_q, n_kv, cuda)
+    stored, q_rots, table_d = _fill(rng, [20, 20], n_q, n_kv, table, pool, cuda)
+    q = torch.cat([q_rots[0], q_rots[1]]).contiguous()
+    slot = torch.tensor([0] * 20 + [1] * 20, dtype=torch.int32, device=cuda)   # rows 20..31 share a tile with sequence 0
+    ctx = torch.tensor(list(range(1, 21)) * 2, dtype=torch.int32, device=cuda)
+    out, st = ops.paged_attention_decode(q, pool, table_d, slot, ctx, n_q, n_kv, 20, prefill="tc")
+    torch.cuda.synchronize()
+    assert int(st.item()) == 2
+    ref, _ = ops.paged_attention_decode(q[:20].contiguous(), pool, table_d, slot[:20], ctx[:20], n_q, n_kv, 20)
+    assert np.max(np.abs(out[:20].float().cpu().numpy() - ref.float().cpu().numpy())) <= 1.2e-2   # the first sequence's rows are unaffected
