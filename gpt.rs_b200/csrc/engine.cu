@@ -1214,11 +1214,11 @@ int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* h, const int32_t* h_
             static const bool blocks_on = [] { const char* e = getenv("GPTRS_PREFILL_BLOCKS"); return e && atoi(e) != 0; }();
             for (int i = 0; i < T && groups; ++i) groups = h_slots[i] == h_slots[i - i % tq];
             for (int i = 0; i < T && blocks; ++i) blocks = h_slots[i] == h_slots[i - i % (4 * tq)];
-            // Default for chunks of at least four tiles: the tensor-core kernel, when every aligned tile of 128 / grp rows is
+            // Default for chunks of at least two tiles: the tensor-core kernel, when every aligned tile of 256 / grp rows is
             // one sequence (GPTRS_PREFILL_TC=0 keeps the grouped kernel).
             static const bool tc_on = [] { const char* e = getenv("GPTRS_PREFILL_TC"); return !e || atoi(e) != 0; }();
-            const int tile = 128 / grp;
-            bool tiles = tc_on && c.head_dim == 128 && T >= 4 * tile;
+            const int tile = 256 / grp;
+            bool tiles = tc_on && c.head_dim == 128 && T >= 2 * tile;
             for (int i = 0; i < T && tiles; ++i) tiles = h_slots[i] == h_slots[i - i % tile];
             if (tiles) { prefill_groups = 3; attn_rows = (T + tile - 1) / tile; }
             else if (blocks && blocks_on && T >= 4 * tq) { prefill_groups = 2; attn_rows = (T + 4 * tq - 1) / (4 * tq); }

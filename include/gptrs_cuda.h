@@ -247,7 +247,7 @@ int gptrs_cuda_paged_attention_prefill_blocks(const void* d_q, const void* d_kv_
                                               void* stream);
 
 /* The same prefill attention on the tcgen05 tensor cores (accumulators in tensor memory, K/V pages brought in by TMA
- * tensor copies): a CTA takes 128 / (n_q_heads / n_kv_heads) consecutive rows (32 tokens at a GQA group of 4) x the query
+ * tensor copies): a CTA takes 256 / (n_q_heads / n_kv_heads) consecutive rows (64 tokens at a GQA group of 4) x the query
  * heads of one kv head and walks the visible keys in blocks of 128, so the rows must come in aligned TILES of that many
  * rows of one sequence (the last tile may be short; a row whose slot differs from its tile's first row gets code 2 in
  * *d_status and no output). No scratch: a tile is never split along the keys. q, out and the pool must be 16-byte aligned.
@@ -257,6 +257,11 @@ int gptrs_cuda_paged_attention_prefill_tc(const void* d_q, const void* d_kv_pool
                                           int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,
                                           void* d_out, int32_t* d_status, int64_t n_tokens, int64_t n_q_heads,
                                           int64_t n_kv_heads, int64_t head_dim, void* stream);
+
+/* Debug: later launches of gptrs_cuda_paged_attention_prefill_tc record clock64 samples of one CTA (the longest tile of
+ * kv head 0) into d_stamps, 3 roles (the MMA warp, the first softmax thread of either row tile) x 16 key blocks x 8
+ * events of int64; nullptr switches the recording off again. Process-wide; not for concurrent use. */
+int gptrs_cuda_debug_prefill_tc_timing(void* d_stamps);
 
 /* Allocation-free variant of gptrs_cuda_paged_attention_decode. It has no counterpart in gpt.rs.
  * It exists for callers that cannot allocate device memory themselves: a plugin inside a serving

@@ -256,15 +256,15 @@ def test_prefill_blocks_entry_point(cuda, l, n_q, n_kv, chunk):
 
 @pytest.mark.parametrize("l,n_q,n_kv", [(90, 8, 2), (131, 32, 8), (300, 32, 8), (70, 4, 4), (200, 16, 2), (37, 8, 1), (16, 32, 8), (700, 32, 8), (128, 32, 8), (1, 32, 8)])
 def test_prefill_tensor_core_entry_point(cuda, l, n_q, n_kv):
-    """gptrs_cuda_paged_attention_prefill_tc (tcgen05 / tensor memory): a CTA takes an aligned tile of 128 / group rows of
-    one sequence and walks its visible keys in blocks of 128. Same results as the one-row-per-CTA entry point and the
+    """gptrs_cuda_paged_attention_prefill_tc (tcgen05 / tensor memory): a CTA takes an aligned tile of 256 / group rows of
+    one sequence (two row tiles of 128 that share the K/V blocks) and walks its visible keys in blocks of 128. Same results as the one-row-per-CTA entry point and the
     oracle: row counts that are not a multiple of the tile, contexts of one, exactly one and several key blocks, a last
     block whose tail pages are never loaded, and a second sequence whose rows start at a tile boundary."""
     rng = np.random.default_rng(l * 7 + n_q)
     l2 = 21
     table, pool = _setup(rng, [l, l2], n_q, n_kv, cuda)
     stored, q_rots, table_d = _fill(rng, [l, l2], n_q, n_kv, table, pool, cuda)
-    tile = 128 // (n_q // n_kv)
+    tile = 256 // (n_q // n_kv)
     pad = (-l) % tile  # rows of sequence 1 must start a new tile: repeat the last row of sequence 0
     q = torch.cat([q_rots[0], q_rots[0][-1:].repeat(pad, 1, 1), q_rots[1]]).contiguous()
     slot = torch.tensor([0] * (l + pad) + [1] * l2, dtype=torch.int32, device=cuda)
@@ -293,7 +293,7 @@ def test_prefill_tensor_core_flags_a_tile_of_two_sequences(cuda):
     table, pool = _setup(rng, [20, 20], n_q, n_kv, cuda)
     stored, q_rots, table_d = _fill(rng, [20, 20], n_q, n_kv, table, pool, cuda)
     q = torch.cat([q_rots[0], q_rots[1]]).contiguous()
-    slot = torch.tensor([0] * 20 + [1] * 20, dtype=torch.int32, device=cuda)   # rows 20..31 share a tile with sequence 0
+    slot = torch.tensor([0] * 20 + [1] * 20, dtype=torch.int32, device=cuda)   # rows 20..39 share a tile with sequence 0
     ctx = torch.tensor(list(range(1, 21)) * 2, dtype=torch.int32, device=cuda)
     out, st = ops.paged_attention_decode(q, pool, table_d, slot, ctx, n_q, n_kv, 20, prefill="tc")
     torch.cuda.synchronize()

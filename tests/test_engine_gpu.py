@@ -310,7 +310,7 @@ def test_generator_slides_the_context_window(cuda, kind):
 
 
 def test_long_prompt_chunks_take_the_tensor_core_attention(cuda):
-    """Prompt chunks of at least four 128-row tiles of one sequence run the tcgen05 prefill attention (32 tokens x 4 query
+    """Prompt chunks of at least two 256-row tiles of one sequence run the tcgen05 prefill attention (64 tokens x 4 query
     heads per CTA at this geometry): a 300-token prompt in chunks of 160 rows (the second chunk sees two key blocks and
     ends in a short tile) and two prompts packed into 256-row passes. Next-token logits against the oracle within 1.5e-2
     of the logit range, the bar of the other tensor-core-path tests."""
