@@ -189,6 +189,36 @@ def time_attention_kernel(ops, torch, dev, ctx_len: int, launches: int = 20, rag
     return ms, alg_bytes, chunk
 
 
+def time_prefill_attention(ops, torch, dev, ctx_len: int, n_seq: int = 4, launches: int = 5):
+    """CUDA-event time of the prefill attention of ONE layer over whole prompts of `ctx_len` tokens (row t of a
+    sequence sees keys 0..t; 32 query / 8 kv heads of 128, random page permutation): the tensor-core kernel and the
+    grouped mma.sync kernel on the same inputs. FLOPs counted: 4 x head_dim per visible (query, key) pair and head."""
+    n_q, n_kv = 32, 8
+    ctx_len = (ctx_len + 63) // 64 * 64   # every prompt starts a new 64-token tile of the tensor-core kernel
+    pages_per = (ctx_len + 15) // 16
+    total = n_seq * pages_per
+    pool = (torch.randn(total * n_kv * 2 * 16 * 128, device=dev) * 0.5).to(torch.bfloat16).view(torch.uint8)
+    table = torch.randperm(total, device=dev, dtype=torch.int32).view(n_seq, pages_per).contiguous()
+    q = torch.randn((n_seq * ctx_len, n_q, 128), device=dev).to(torch.bfloat16)
+    slot = torch.arange(n_seq, dtype=torch.int32, device=dev).repeat_interleave(ctx_len).contiguous()
+    ctx = torch.arange(1, ctx_len + 1, dtype=torch.int32, device=dev).repeat(n_seq).contiguous()
+    flops = 4.0 * 128 * n_q * n_seq * ctx_len * (ctx_len + 1) / 2
+    res = {}
+    for name, mode in (("paged_prefill_tc_kernel", "tc"), ("paged_attention_kernel<2,1>", True)):
+        for _ in range(2):
+            out, st = ops.paged_attention_decode(q, pool, table, slot, ctx, n_q, n_kv, ctx_len, prefill=mode)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(launches):
+            out, st = ops.paged_attention_decode(q, pool, table, slot, ctx, n_q, n_kv, ctx_len, prefill=mode)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / launches
+        res[name] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1), "status": int(st.item())}
+    return res, flops
+
+
 def time_gemv(ops, torch, dev, n=9216, k=3072, m=1, n_mats=64, iters=3, bits=4, pdl=True):
     """W4A16 / W8A16 matmul over a rotating set of distinct weight matrices (working set >> L2)."""
     if bits == 4:
@@ -666,7 +696,7 @@ def _main(out):
     ap.add_argument("--pdl", type=int, default=int(os.environ.get("GPTRS_PDL", "1")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the kernel microbenchmarks")
-    ap.add_argument("--microbench", default=None, choices=["attention", "attention-ragged", "gemv", "gemv-lm-head", "gemm64", "quant-linear", "prefill"],
+    ap.add_argument("--microbench", default=None, choices=["attention", "attention-ragged", "gemv", "gemv-lm-head", "gemm64", "quant-linear", "prefill", "prefill-attention"],
                     help="run only one kernel microbenchmark (used for ncu captures) and print its JSON")
     ap.add_argument("--ctx", type=int, default=PROMPT_LEN + 20, help="context length for --microbench attention")
     ap.add_argument("--workload", default="ministral3b-w4", choices=["ministral3b-w4", "gpt2-fp32", "dp512"],
@@ -735,6 +765,12 @@ def _main(out):
             ms, nbytes, chunk = time_attention_kernel(ops, torch, dev, args.ctx, launches=5)
             print(json.dumps({"kernel": "paged_attention_kernel", "us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / ms / 1e6,
                               "frac": nbytes / ms / 1e6 / peak, "chunk_pages": chunk, "ctx": args.ctx}), file=out)
+        elif args.microbench == "prefill-attention":
+            res, flops = time_prefill_attention(ops, torch, dev, args.ctx)
+            tf_peak = _tensor_peak()
+            print(json.dumps({"microbench": "prefill-attention", "workload": f"4 prompts of {(args.ctx + 63) // 64 * 64} tokens, causal, 32 q / 8 kv heads of 128, one layer",
+                              "flops": flops, "bf16_peak_tflops": tf_peak, "kernels": res,
+                              "frac_of_bf16_peak": round(res["paged_prefill_tc_kernel"]["tflops"] / tf_peak, 3) if tf_peak else None}), file=out)
         elif args.microbench == "attention-ragged":
             ms, nbytes, chunk = time_attention_kernel(ops, torch, dev, 8192, launches=5, ragged_seed=0)
             print(json.dumps({"kernel": "paged_attention_kernel", "workload": "batch 64, context lengths U{512..8192} (seed 0), 32 q / 8 kv heads of 128, random page permutation",
