@@ -61,6 +61,8 @@ struct PrefillParams {
     int T, Hq, Hkv, max_pages, max_len;
     float scale_log2;
     long long* timing;            // debug: clock64 samples of one CTA (nullptr = off)
+    int debug_starve;             // test switch: the K pages of the first block are never requested
+    uint32_t wait_limit;          // parked polls a wait may take (kWaitLimit unless the test switch lowers it)
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar_addr) {
@@ -177,7 +179,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const __g
     bool failed = false;
 
     auto wait = [&](uint64_t* bar, uint32_t parity) {   // whole warp; a timeout ends this warp's role
-        if (!failed && !mbar_wait_parked(smem_u32(bar), parity, kWaitLimit)) failed = true;
+        if (!failed && !mbar_wait_parked(smem_u32(bar), parity, p.wait_limit)) failed = true;
         failed = __any_sync(0xffffffffu, failed);
         return !failed;
     };
@@ -193,7 +195,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const __g
             const int keys = min(kKeys, max_len - kb * kKeys);
             return (kb < n_blocks && lane < (keys + kPageTokens - 1) / kPageTokens) ? pt[kb * kPagesPerBlock + lane] : 0;
         };
-        int pg_next = page_id(0);
+        int pg_next = page_id(0), n_req = 0;
         for (int kb = 0; kb < n_blocks; ++kb) {
             const int pg = pg_next;
             pg_next = page_id(kb + 1);
@@ -204,16 +206,17 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const __g
             const uint32_t bar = smem_u32(&full[kb & 1]), dst = base + (kb & 1) * kTileBytes;
             if (lane == 0) mbar_expect_tx_addr(bar, (uint32_t)pages * 2 * kPageTokens * 128);
             __syncwarp();
-            if (lane < pages) {   // two tensor copies per page: the two 64-column halves
+            if (lane < pages && !(p.debug_starve && kb == 0 && !is_v)) {   // two tensor copies per page: the two 64-column halves
                 const int row0 = ((pg * p.Hkv + hkv) * 2 + is_v) * kPageTokens;
                 tma_load_3d(dst + lane * (kPageTokens * 128), &p.kv_map, 0, 0, row0, bar);
                 tma_load_3d(dst + kHalfBytes + lane * (kPageTokens * 128), &p.kv_map, 0, 1, row0, bar);
             }
             __syncwarp();
+            n_req = kb + 1;
         }
-        // the copies of the last two blocks may still be in flight (always, if the consumer gave up): they write this CTA's
-        // shared memory, so wait for them (bounded) before leaving
-        for (int kb = max(n_blocks - 2, 0); kb < n_blocks; ++kb) mbar_wait_parked(smem_u32(&full[kb & 1]), (uint32_t)(kb >> 1) & 1u, kWaitLimit);
+        // the copies of the last two requested blocks may still be in flight (always, if the consumer gave up): they write
+        // this CTA's shared memory, so wait for them (bounded) before leaving
+        for (int kb = max(n_req - 2, 0); kb < n_req; ++kb) mbar_wait_parked(smem_u32(&full[kb & 1]), (uint32_t)(kb >> 1) & 1u, p.wait_limit);
         if (failed && lane == 0) atomicExch(p.status, 3);
     } else if (warp == kMmaWarp) {
         // ================= warp 8: MMA issue ==================================================================================
@@ -296,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const __g
         float m_run = -1e30f, l_run = 0.f;
         for (int kb = 0; kb < my_blocks; ++kb) {
             // ---- S of this block is complete, and with it every MMA issued before (this tile's previous P . V) -------------------
-            if (!mbar_wait_parked(s_bar_a, (uint32_t)kb & 1u, kWaitLimit)) failed = true;
+            if (!mbar_wait_parked(s_bar_a, (uint32_t)kb & 1u, p.wait_limit)) failed = true;
             failed = __any_sync(0xffffffffu, failed);
             if (failed) break;
             if (row == 0) PTC_STAMP(1 + ti, kb, 0);
@@ -359,7 +362,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const __g
         }
         // ---- O / l -> out ---------------------------------------------------------------------------------------------
         if (my_blocks > 0 && !failed) {
-            if (!mbar_wait_parked(smem_u32(&o_full[ti]), 0, kWaitLimit)) failed = true;
+            if (!mbar_wait_parked(smem_u32(&o_full[ti]), 0, p.wait_limit)) failed = true;
             failed = __any_sync(0xffffffffu, failed);
         }
         if (my_blocks > 0 && !failed) {
@@ -403,6 +406,8 @@ int encode_pool_map(const void* pool, CUtensorMap* map) {
 }
 
 long long* g_prefill_timing = nullptr;   // debug: see gptrs_cuda_debug_prefill_tc_timing
+int g_prefill_starve = 0;                // test switch: see gptrs_cuda_debug_prefill_tc_fault
+uint32_t g_prefill_wait_limit = 0;
 
 }  // namespace
 }  // namespace gptrs
@@ -410,6 +415,12 @@ long long* g_prefill_timing = nullptr;   // debug: see gptrs_cuda_debug_prefill_
 using namespace gptrs;
 
 extern "C" {
+
+int gptrs_cuda_debug_prefill_tc_fault(int starve, uint32_t wait_limit) {
+    g_prefill_starve = starve ? 1 : 0;
+    g_prefill_wait_limit = wait_limit;
+    return GPTRS_OK;
+}
 
 int gptrs_cuda_debug_prefill_tc_timing(void* d_stamps) {
     g_prefill_timing = static_cast<long long*>(d_stamps);
@@ -443,6 +454,8 @@ int gptrs_cuda_paged_attention_prefill_tc(const void* d_q, const void* d_kv_pool
     p.max_pages = (int)max_pages; p.max_len = (int)(max_pages * kPageTokens);
     p.scale_log2 = kLog2e / sqrtf((float)head_dim);
     p.timing = g_prefill_timing;
+    p.debug_starve = g_prefill_starve;
+    p.wait_limit = (g_prefill_starve && g_prefill_wait_limit) ? g_prefill_wait_limit : kWaitLimit;
     static PerDeviceOnce attr_once;
     if (attr_once.first_time())
         GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefillSmem));

@@ -258,6 +258,13 @@ int gptrs_cuda_paged_attention_prefill_tc(const void* d_q, const void* d_kv_pool
                                           void* d_out, int32_t* d_status, int64_t n_tokens, int64_t n_q_heads,
                                           int64_t n_kv_heads, int64_t head_dim, void* stream);
 
+/* Test switch for the failure path of gptrs_cuda_paged_attention_prefill_tc (no counterpart in the reference). While
+ * `starve` is non-zero the K pages of every CTA's first key block are never requested, so the waits that depend on them
+ * run out after `wait_limit` parked polls of about a microsecond (0 = the built-in 2^16); every warp then leaves its
+ * loop, code 3 lands in *d_status, the tensor memory is freed and the kernel returns with an unspecified result. Nothing
+ * faults and nothing waits without a bound. Process-wide; call with (0, 0) to switch it off again. */
+int gptrs_cuda_debug_prefill_tc_fault(int starve, uint32_t wait_limit);
+
 /* Debug: later launches of gptrs_cuda_paged_attention_prefill_tc record clock64 samples of one CTA (the longest tile of
  * kv head 0) into d_stamps, 3 roles (the MMA warp, the first softmax thread of either row tile) x 16 key blocks x 8
  * events of int64; nullptr switches the recording off again. Process-wide; not for concurrent use. */

@@ -68,3 +68,34 @@ def test_engine_reports_a_matmul_wait_that_ran_out(cuda, starved):
     check(lib().gptrs_cuda_debug_matmul_fault(0, 0))
     after = gen.step()   # the context is intact: the next step runs and samples ids in range
     assert after.shape == (n_seq,) and int(after.min()) >= 0 and int(after.max()) < cfg.vocab
+
+
+def test_prefill_attention_wait_runs_out_sets_status_and_recovers(cuda):
+    """The tensor-core prefill attention with the K pages of every CTA's first key block withheld: the MMA warp's wait for
+    them, then the softmax warps' waits for S and the page warps' waits for a free stage run out after 300 parked polls,
+    code 3 lands in the caller's status word, the kernel frees its tensor memory and returns; the next launch is correct."""
+    n_q, n_kv, l = 8, 2, 400   # 4 key blocks: every kind of wait is reached
+    pages = (l + 15) // 16
+    g = torch.Generator(device="cpu").manual_seed(5)
+    pool = (torch.randn(pages * n_kv * 2 * 16 * 128, generator=g) * 0.5).to(torch.bfloat16).to(cuda).view(torch.uint8)
+    table = torch.arange(pages, dtype=torch.int32, device=cuda).view(1, pages)
+    q = torch.randn(l, n_q, 128, generator=g).to(torch.bfloat16).to(cuda)
+    slot = torch.zeros(l, dtype=torch.int32, device=cuda)
+    ctx = torch.arange(1, l + 1, dtype=torch.int32, device=cuda)
+    want, st = ops.paged_attention_decode(q, pool, table, slot, ctx, n_q, n_kv, l)
+    good, st0 = ops.paged_attention_decode(q, pool, table, slot, ctx, n_q, n_kv, l, prefill="tc")
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and int(st0.item()) == 0
+    check(lib().gptrs_cuda_debug_prefill_tc_fault(1, 300))
+    try:
+        _, st1 = ops.paged_attention_decode(q, pool, table, slot, ctx, n_q, n_kv, l, prefill="tc")   # returns; the result is unspecified
+        torch.cuda.synchronize()
+        assert int(st1.item()) == 3
+    finally:
+        check(lib().gptrs_cuda_debug_prefill_tc_fault(0, 0))
+    again, st2 = ops.paged_attention_decode(q, pool, table, slot, ctx, n_q, n_kv, l, prefill="tc")
+    torch.cuda.synchronize()
+    assert int(st2.item()) == 0
+    assert torch.equal(again, good)
+    a, b = again.float().cpu().numpy(), want.float().cpu().numpy()
+    assert np.all(np.abs(a - b) <= 8e-3 * np.maximum(1.0, np.abs(b)))
