@@ -846,7 +846,7 @@ int check_status(Model& m) {
     if (st != 0) {
         cudaMemsetAsync(m.d_status.p, 0, 4, m.stream);
         return fail(GPTRS_EXECUTION, st == 2   ? "token or position id out of range"
-                                     : st == 3 ? "a bounded wait inside a tensor-core matmul kernel gave up"
+                                     : st == 3 ? "a bounded wait inside a tensor-core kernel (matmul or prefill attention) gave up"
                                      : st == 4 ? "a tensor-parallel peer did not deliver its partial sums in time"
                                                : "a bounded wait inside the attention kernel gave up");
     }
@@ -1214,12 +1214,15 @@ int gptrs_cuda_model_forward_with_decode_cache(gptrs_model* h, const int32_t* h_
             static const bool blocks_on = [] { const char* e = getenv("GPTRS_PREFILL_BLOCKS"); return e && atoi(e) != 0; }();
             for (int i = 0; i < T && groups; ++i) groups = h_slots[i] == h_slots[i - i % tq];
             for (int i = 0; i < T && blocks; ++i) blocks = h_slots[i] == h_slots[i - i % (4 * tq)];
-            // Default for chunks of at least two tiles: the tensor-core kernel, when every aligned tile of 256 / grp rows is
-            // one sequence (GPTRS_PREFILL_TC=0 keeps the grouped kernel).
+            // Default for chunks of at least two tiles: the tensor-core kernel, when every aligned tile of 256 / grp rows holds
+            // at most two sequences (the tail of one prompt and the head of the next; GPTRS_PREFILL_TC=0 keeps the grouped kernel).
             static const bool tc_on = [] { const char* e = getenv("GPTRS_PREFILL_TC"); return !e || atoi(e) != 0; }();
             const int tile = 256 / grp;
             bool tiles = tc_on && c.head_dim == 128 && T >= 2 * tile;
-            for (int i = 0; i < T && tiles; ++i) tiles = h_slots[i] == h_slots[i - i % tile];
+            for (int i = 0; i < T && tiles; ++i) {
+                const int t0 = i - i % tile, t1 = std::min(t0 + tile, T) - 1;
+                tiles = h_slots[i] == h_slots[t0] || h_slots[i] == h_slots[t1];
+            }
             if (tiles) { prefill_groups = 3; attn_rows = (T + tile - 1) / tile; }
             else if (blocks && blocks_on && T >= 4 * tq) { prefill_groups = 2; attn_rows = (T + 4 * tq - 1) / (4 * tq); }
             else if (groups) { prefill_groups = 1; attn_rows = (T + tq - 1) / tq; }

@@ -7,7 +7,8 @@
 //
 // One CTA (one per SM) takes 256 query rows = 256 / group consecutive tokens of ONE sequence x the `group` query heads of
 // one kv head, as two row tiles of 128 that share every K/V block brought into shared memory, and walks the visible
-// keys in blocks of 128 (8 pages). Per row tile i and key block:
+// keys in blocks of 128 (8 pages). A 256-row tile of the token list that holds the tail of one sequence and the head of
+// the next is served by two CTAs, one per sequence. Per row tile i and key block:
 //   S_i[128 x 128] = Q_i . K^T   tcgen05.mma, A = Q tile and B = K block in shared memory (K-major, 128-byte swizzle),
 //                                accumulator in tensor memory
 //   softmax                      warps 4 i .. 4 i + 3, thread r owns row r of the tile (TMEM lane r): scaled scores,
@@ -106,7 +107,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // debug time stamps of the CTA that takes the longest tile of kv head 0: role r (0 = MMA warp, 1 + i = first thread of row
 // tile i), block kb < 16, event e < 8
 #define PTC_STAMP(r, kb, e) \
-    do { if (p.timing && blockIdx.x == 0 && blockIdx.y == 0 && (kb) < 16) p.timing[((r) * 16 + (kb)) * 8 + (e)] = clock64(); } while (0)
+    do { if (p.timing && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (kb) < 16) p.timing[((r) * 16 + (kb)) * 8 + (e)] = clock64(); } while (0)
 
 __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const __grid_constant__ PrefillParams p) {
     // f32 accumulator, bf16 operands, N = 128, M = 128; the second one reads B with the contraction index as rows
@@ -128,6 +129,15 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const __g
     const int cta_tile = (int)gridDim.x - 1 - (int)blockIdx.x;   // the longest contexts of a chunk come last in the token list: start them first
     const int b = cta_tile * kTiles * tq, hkv = blockIdx.y;
 
+    // A tile of the token list may hold the tail of one sequence and the head of the next (prompts packed into one pass):
+    // blockIdx.z = 0 serves the rows of the first row's sequence, z = 1 those of the last row's sequence, if it is another
+    // one (else it leaves here, the whole CTA, before any barrier or allocation). Rows of a third sequence get no output
+    // and code 2.
+    pdl_wait();
+    const int slot_first = p.slot[b], slot_last = p.slot[min(b + kTiles * tq, p.T) - 1];
+    if (blockIdx.z == 1 && slot_last == slot_first) return;
+    const int slot0 = blockIdx.z == 0 ? slot_first : slot_last;
+
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_empty[i], 1); }
         for (int i = 0; i < kTiles; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_full[i], kRows); mbar_init(&o_full[i], 1); }
@@ -141,19 +151,21 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(const __g
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_holder;
-    // every CTA of this grid holds its tensor memory before a dependent grid may be scheduled
+    // every CTA of this grid holds its tensor memory (or has left) before a dependent grid may be scheduled
     pdl_launch_dependents();
-    pdl_wait();
 
     // ---- a softmax thread's row: token, head, visible length ---------------------------------------------------------
     const int my_tok = b + ti * tq + row / group, my_head = hkv * group + row % group;
-    const int slot0 = p.slot[b];
     int my_len = 0;
     if (is_softmax) {
         if (my_tok < p.T) {
-            my_len = p.ctx_len[my_tok];
-            if (my_len > p.max_len || my_len < 0) { atomicExch(p.status, 2); my_len = my_len < 0 ? 0 : p.max_len; }
-            if (p.slot[my_tok] != slot0) { atomicExch(p.status, 2); my_len = 0; }   // a CTA's rows are one sequence: the caller's contract
+            const int my_slot = p.slot[my_tok];
+            if (my_slot == slot0) {
+                my_len = p.ctx_len[my_tok];
+                if (my_len > p.max_len || my_len < 0) { atomicExch(p.status, 2); my_len = my_len < 0 ? 0 : p.max_len; }
+            } else if (my_slot != slot_first && my_slot != slot_last) {
+                atomicExch(p.status, 2);   // at most two sequences per tile: the caller's contract
+            }
         }
         const int warp_len = __reduce_max_sync(0xffffffffu, my_len);
         if (lane == 0) s_len[warp] = warp_len;
@@ -459,7 +471,7 @@ int gptrs_cuda_paged_attention_prefill_tc(const void* d_q, const void* d_kv_pool
     static PerDeviceOnce attr_once;
     if (attr_once.first_time())
         GPTRS_CUDA_OK(cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrefillSmem));
-    return launch_kernel(paged_prefill_tc_kernel, dim3((unsigned)tiles, (unsigned)n_kv_heads), dim3(kThreads), kPrefillSmem, as_stream(stream), 1, p);
+    return launch_kernel(paged_prefill_tc_kernel, dim3((unsigned)tiles, (unsigned)n_kv_heads, 2), dim3(kThreads), kPrefillSmem, as_stream(stream), 1, p);
 }
 
 }  // extern "C"

@@ -11,6 +11,7 @@ All arithmetic happens inside libgptrs_cuda.so; this file only marshals argument
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -238,13 +239,18 @@ class LoadedModel:
     def prefill_many(self, slots, prompts, chunk: int | None = None):
         """Appends one prompt to each of `slots` with the rows of all prompts packed into forward passes of up to
         `chunk` rows, so a pass may hold the tail of one sequence and the head of the next: the matmuls then see
-        full row tiles whatever the prompt lengths are. A pass is cut early where the next sequence would start
-        off the row alignment that lets the attention kernel share one K/V stream between the rows of a group.
+        full row tiles whatever the prompt lengths are. Where the grouped attention kernel would run, a pass is cut early
+        if the next sequence would start off the row alignment that lets the rows of a group share one K/V stream.
         Returns the greedy id that follows each prompt, in the order given."""
         cfg = self.config
         chunk = min(chunk or cfg.max_tokens, cfg.max_tokens)
         group = max(cfg.n_q_heads // max(cfg.n_kv_heads, 1), 1)
         align = max(16 // group, 1)
+        # passes the engine gives to the tensor-core prefill attention (the rule of gptrs_cuda_model_forward: paged bf16
+        # cache, heads of 128, at least two 256-row tiles) need no alignment: a tile may hold two sequences
+        if (cfg.weight_mode != MODE_F32 and cfg.head_dim == 128 and group in (1, 2, 4, 8) and chunk >= 2 * (256 // group)
+                and os.environ.get("GPTRS_PREFILL_TC", "1") != "0"):
+            align = 1
         max_rows = cfg.max_logit_rows if cfg.max_logit_rows > 0 else cfg.max_seqs
         first = [None] * len(prompts)
         tok, sl, pos, rows, owners = [], [], [], [], []

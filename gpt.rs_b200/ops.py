@@ -182,7 +182,7 @@ def paged_attention_decode(q, kv_pool, page_table, slot, ctx_len, n_q, n_kv, max
                            chunk_pages=None, status=None, prefill=False):
     """q bf16 [T][Hq][hd] -> out bf16 [T][Hq*hd]. prefill=True uses the prefill-chunk entry point (aligned groups
     of 16 / (Hq / Hkv) rows must belong to one sequence); prefill="blocks" the one that takes aligned blocks of four such groups;
-    prefill="tc" the tensor-core (tcgen05) kernel that takes aligned tiles of 256 / (Hq / Hkv) rows of one sequence."""
+    prefill="tc" the tensor-core (tcgen05) kernel that takes aligned tiles of 256 / (Hq / Hkv) rows of at most two sequences."""
     t = q.shape[0]
     if prefill == "tc":
         if status is None:

@@ -248,10 +248,11 @@ int gptrs_cuda_paged_attention_prefill_blocks(const void* d_q, const void* d_kv_
 
 /* The same prefill attention on the tcgen05 tensor cores (accumulators in tensor memory, K/V pages brought in by TMA
  * tensor copies): a CTA takes 256 / (n_q_heads / n_kv_heads) consecutive rows (64 tokens at a GQA group of 4) x the query
- * heads of one kv head and walks the visible keys in blocks of 128, so the rows must come in aligned TILES of that many
- * rows of one sequence (the last tile may be short; a row whose slot differs from its tile's first row gets code 2 in
- * *d_status and no output). No scratch: a tile is never split along the keys. q, out and the pool must be 16-byte aligned.
- * Waits are bounded (code 3 in *d_status on a timeout). Replaces functional::attention on the prompt
+ * heads of one kv head and walks the visible keys in blocks of 128. Every aligned TILE of that many rows may hold the rows
+ * of at most two sequences (the tail of one prompt and the head of the next, as in a packed prefill pass; the last tile may
+ * be short): a second CTA serves the second sequence. A row of a third sequence gets code 2 in *d_status and no output. No
+ * scratch: a tile is never split along the keys. q, out and the pool must be 16-byte aligned. Waits are bounded (code 3
+ * in *d_status on a timeout). Replaces functional::attention on the prompt
  * (crates/gpt-rs/src/ops/functional/attention.rs:337-541) together with gptrs_cuda_rope_kv_append. */
 int gptrs_cuda_paged_attention_prefill_tc(const void* d_q, const void* d_kv_pool, const int32_t* d_page_table,
                                           int64_t max_pages, const int32_t* d_slot, const int32_t* d_ctx_len,

@@ -310,21 +310,24 @@ def test_generator_slides_the_context_window(cuda, kind):
 
 
 def test_long_prompt_chunks_take_the_tensor_core_attention(cuda):
-    """Prompt chunks of at least two 256-row tiles of one sequence run the tcgen05 prefill attention (64 tokens x 4 query
-    heads per CTA at this geometry): a 300-token prompt in chunks of 160 rows (the second chunk sees two key blocks and
-    ends in a short tile) and two prompts packed into 256-row passes. Next-token logits against the oracle within 1.5e-2
-    of the logit range, the bar of the other tensor-core-path tests."""
+    """Prompt chunks of at least two 256-row tiles run the tcgen05 prefill attention (64 tokens x 4 query heads per CTA at
+    this geometry): a 300-token prompt in chunks of 160 rows (the second chunk sees two key blocks and ends in a short
+    tile) and two prompts packed into 256-row passes whose boundary falls inside a tile (the tail of one sequence and the
+    head of the next are served by two CTAs). Next-token logits against the oracle within 1.5e-2 of the logit range, the
+    bar of the other tensor-core-path tests."""
     cfg = mr.Cfg("ministral", n_layers=2, d_model=256, n_q=8, n_kv=2, hd=128, d_mlp=512, vocab=512, ctx=512, rot=128, theta=1e6)
     params = mr.random_params(cfg, seed=31, std=0.05)
     qparams = mr.quantised_params(cfg, params, "w4")
     rng = np.random.default_rng(77)
-    prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in (300, 256, 200)]
+    lens = (300, 250, 201)
+    prompts = [rng.integers(0, cfg.vocab, size=n).tolist() for n in lens]
     m = _load(cfg, params, mode=gm.MODE_W4A16, max_seqs=3, max_tokens=256, max_logit_rows=3, kv_pages=3 * 20 + 4, max_pages_per_seq=20)
     lg, tok = m.prefill(0, prompts[0], chunk=160, want_logits=True)
     want = mr.RefModel(cfg, qparams).forward(prompts[0])[-1]
     assert float(np.max(np.abs(lg - want))) / max(1.0, float(np.max(np.abs(want)))) <= 1.5e-2
-    first = m.prefill_many([1, 2], prompts[1:], chunk=256)
-    lg, _ = m.forward_with_decode_cache(first, [1, 2], [256, 200], [0, 1])
+    first = m.prefill_many([1, 2], prompts[1:], chunk=256)   # passes of 250 + 6 and 195 rows
+    assert [m.sequence_length(s) for s in (1, 2)] == [250, 201]
+    lg, _ = m.forward_with_decode_cache(first, [1, 2], [250, 201], [0, 1])
     for i, s in enumerate((1, 2)):
         ref = mr.RefModel(cfg, qparams)
         ref.forward(prompts[s])

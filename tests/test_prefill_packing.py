@@ -74,3 +74,18 @@ def test_logit_row_limit_and_continuation():
     # a second prompt appended to a slot continues at its length
     m.prefill_many([1], [np.arange(6)], chunk=64)
     assert m.passes[-1][2] == list(range(4, 10))
+
+
+def test_passes_for_the_tensor_core_attention_are_always_full():
+    """Heads of 128 on the paged bf16 path with passes of at least two 256-row tiles: the engine's tensor-core prefill
+    attention serves a tile that holds two sequences, so no pass is cut at a sequence boundary."""
+    cfg = gm.ModelConfig(gm.KIND_MINISTRAL, 1, 128, 32, 8, 128, 128, 1000, 4096, max_seqs=8, max_tokens=256, max_logit_rows=8,
+                         weight_mode=gm.MODE_W4A16)
+    m = _Recorder(cfg)
+    lens = (301, 77, 190, 255, 13)
+    rng = np.random.default_rng(1)
+    prompts = [rng.integers(0, 1000, size=n) for n in lens]
+    first = m.prefill_many(list(range(len(lens))), prompts, chunk=256)
+    assert first == [int(p[-1]) + 1000 for p in prompts]
+    assert [len(p[0]) for p in m.passes] == [256, 256, 256, sum(lens) - 3 * 256]
+    assert [t for p in m.passes for t in p[0]] == [int(t) for p in prompts for t in p]
